@@ -1,0 +1,135 @@
+// Host-side plumbing shared by every entry point: error strings, launch
+// counter, device status word, TMA descriptor encoding.
+#include "edb200_internal.h"
+
+#include <cstdarg>
+#include <cstdio>
+#include <mutex>
+
+namespace edb {
+
+static thread_local char g_last_error[512] = "";
+static std::atomic<int64_t> g_launches{0};
+
+edb200_status_t fail(edb200_status_t st, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_last_error, sizeof(g_last_error), fmt, ap);
+    va_end(ap);
+    return st;
+}
+
+edb200_status_t check_cuda(cudaError_t e, const char* what) {
+    if (e == cudaSuccess) return EDB200_OK;
+    return fail(EDB200_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+
+void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+static int* g_err_word[64] = {nullptr};
+static std::mutex g_err_mu;
+
+int* device_error_word() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    std::lock_guard<std::mutex> lk(g_err_mu);
+    if (g_err_word[dev] == nullptr) {
+        int* p = nullptr;
+        if (cudaMalloc(&p, sizeof(int)) != cudaSuccess) return nullptr;
+        cudaMemset(p, 0, sizeof(int));
+        g_err_word[dev] = p;
+    }
+    return g_err_word[dev];
+}
+
+edb200_status_t poll_device_error(cudaStream_t stream) {
+    int* w = device_error_word();
+    if (w == nullptr) return fail(EDB200_ERR_CUDA, "no CUDA device");
+    int host = 0;
+    cudaError_t e = cudaMemcpyAsync(&host, w, sizeof(int), cudaMemcpyDeviceToHost, stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+    if (e != cudaSuccess) return check_cuda(e, "poll_device_error");
+    if (host != 0) {
+        cudaMemsetAsync(w, 0, sizeof(int), stream);
+        return fail(EDB200_ERR_TIMEOUT, "device-side wait timed out (code %d)", host);
+    }
+    return EDB200_OK;
+}
+
+PFN_encodeTiled get_encode_tiled() {
+    static PFN_encodeTiled fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess) {
+            fn = reinterpret_cast<PFN_encodeTiled>(p);
+        }
+    });
+    return fn;
+}
+
+edb200_status_t make_tmap_2d(CUtensorMap* map, CUtensorMapDataType dt, int elem_bytes, const void* base,
+                             uint64_t inner, uint64_t outer, uint64_t pitch_bytes, uint32_t box_inner,
+                             uint32_t box_outer, CUtensorMapSwizzle swz) {
+    PFN_encodeTiled enc = get_encode_tiled();
+    if (enc == nullptr) return fail(EDB200_ERR_CUDA, "cuTensorMapEncodeTiled unavailable");
+    if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0 || (pitch_bytes & 15u) != 0 ||
+        ((uint64_t)box_inner * elem_bytes) % 16 != 0) {
+        return fail(EDB200_ERR_INVALID, "tensor map: base/pitch/box not 16-byte aligned");
+    }
+    cuuint64_t dims[2] = {inner, outer};
+    cuuint64_t strides[1] = {pitch_bytes};
+    cuuint32_t box[2] = {box_inner, box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(EDB200_ERR_CUDA, "cuTensorMapEncodeTiled(2d) failed: %d", (int)r);
+    return EDB200_OK;
+}
+
+edb200_status_t make_tmap_3d(CUtensorMap* map, CUtensorMapDataType dt, int elem_bytes, const void* base,
+                             uint64_t d0, uint64_t d1, uint64_t d2, uint64_t pitch1_bytes, uint64_t pitch2_bytes,
+                             uint32_t b0, uint32_t b1, uint32_t b2, CUtensorMapSwizzle swz) {
+    PFN_encodeTiled enc = get_encode_tiled();
+    if (enc == nullptr) return fail(EDB200_ERR_CUDA, "cuTensorMapEncodeTiled unavailable");
+    if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0 || (pitch1_bytes & 15u) != 0 || (pitch2_bytes & 15u) != 0 ||
+        ((uint64_t)b0 * elem_bytes) % 16 != 0) {
+        return fail(EDB200_ERR_INVALID, "tensor map: base/pitch/box not 16-byte aligned");
+    }
+    cuuint64_t dims[3] = {d0, d1, d2};
+    cuuint64_t strides[2] = {pitch1_bytes, pitch2_bytes};
+    cuuint32_t box[3] = {b0, b1, b2};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(map, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(EDB200_ERR_CUDA, "cuTensorMapEncodeTiled(3d) failed: %d", (int)r);
+    return EDB200_OK;
+}
+
+int sm_count() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        cudaDeviceProp p;
+        if (cudaGetDevice(&dev) == cudaSuccess && cudaGetDeviceProperties(&p, dev) == cudaSuccess) {
+            n = p.multiProcessorCount;
+        } else {
+            n = 148;
+        }
+    }
+    return n;
+}
+
+}  // namespace edb
+
+extern "C" {
+
+const char* edb200_last_error(void) { return edb::g_last_error; }
+
+const char* edb200_version(void) { return "edb200 0.1 (sm_100a)"; }
+
+int64_t edb200_launch_count(void) { return edb::g_launches.load(std::memory_order_relaxed); }
+
+}  // extern "C"

@@ -1,0 +1,359 @@
+// Memory-bound kernels of the DiT block: LayerNorm + adaLN modulate, the
+// bit-exact f32 modulate / residual-gate / RoPE ops of the reference's custom-op
+// surface, and the fused QK-RMSNorm + RoPE + head-major pack that feeds attention.
+// All global accesses are 128-bit where the layout allows; reductions use warp
+// shuffles.
+#include "edb200_internal.h"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+namespace edb {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) v += __shfl_xor_sync(0xffffffffu, v, m);
+    return v;
+}
+
+template <int THREADS>
+__device__ __forceinline__ float block_sum(float v, float* sh) {
+    v = warp_sum(v);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __syncthreads();  // protect sh from the previous reduction
+    if (lane == 0) sh[warp] = v;
+    __syncthreads();
+    float t = (lane < THREADS / 32) ? sh[lane] : 0.0f;
+    return warp_sum(t);
+}
+
+__device__ __forceinline__ void store_vec4(void* base, int dtype, int64_t elem_off, float a, float b, float c,
+                                           float d) {
+    if (dtype == EDB200_TYPE_F32) {
+        *reinterpret_cast<float4*>(static_cast<float*>(base) + elem_off) = make_float4(a, b, c, d);
+    } else if (dtype == EDB200_TYPE_BF16) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+        uint2 u;
+        u.x = *reinterpret_cast<uint32_t*>(&lo);
+        u.y = *reinterpret_cast<uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(base) + elem_off) = u;
+    } else {
+        __half2 lo = __floats2half2_rn(a, b), hi = __floats2half2_rn(c, d);
+        uint2 u;
+        u.x = *reinterpret_cast<uint32_t*>(&lo);
+        u.y = *reinterpret_cast<uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(static_cast<__half*>(base) + elem_off) = u;
+    }
+}
+
+__device__ __forceinline__ float4 load_vec4(const void* base, int dtype, int64_t elem_off) {
+    if (dtype == EDB200_TYPE_F32) {
+        return *reinterpret_cast<const float4*>(static_cast<const float*>(base) + elem_off);
+    }
+    const uint2 u = *reinterpret_cast<const uint2*>(static_cast<const uint16_t*>(base) + elem_off);
+    if (dtype == EDB200_TYPE_BF16) {
+        const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+        const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+        return make_float4(lo.x, lo.y, hi.x, hi.y);
+    }
+    const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&u.x));
+    const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&u.y));
+    return make_float4(lo.x, lo.y, hi.x, hi.y);
+}
+
+// ---------------------------------------------------- LayerNorm + modulate --
+// One CTA per token row.  y = (xn + xn*scale) + shift with xn = (x-mean)*rstd,
+// the association the reference's modulate uses
+// (src/core/backend/ggml/ed_ggml_modulation_ext.hpp:168-199) applied to ggml_norm's output.
+constexpr int LN_THREADS = 256;
+constexpr int LN_MAXV = 8;  // float4 per thread -> H <= 8192
+
+__global__ void __launch_bounds__(LN_THREADS)
+layernorm_modulate_kernel(const float* __restrict__ x, int64_t ldx, const float* __restrict__ shift,
+                          const float* __restrict__ scale, const float* __restrict__ ln_w,
+                          const float* __restrict__ ln_b, int H, float eps, void* __restrict__ y, int y_dtype,
+                          int64_t ldy) {
+    __shared__ float sh[LN_THREADS / 32];
+    const int64_t row = blockIdx.x;
+    const float* xr = x + row * ldx;
+    const int nvec = H >> 2;
+    float4 v[LN_MAXV];
+    float s = 0.0f;
+#pragma unroll
+    for (int i = 0; i < LN_MAXV; ++i) {
+        const int c = threadIdx.x + i * LN_THREADS;
+        if (c < nvec) {
+            v[i] = *reinterpret_cast<const float4*>(xr + 4 * c);
+            s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+        }
+    }
+    const float mean = block_sum<LN_THREADS>(s, sh) / static_cast<float>(H);
+    float q = 0.0f;
+#pragma unroll
+    for (int i = 0; i < LN_MAXV; ++i) {
+        const int c = threadIdx.x + i * LN_THREADS;
+        if (c < nvec) {
+            v[i].x -= mean;
+            v[i].y -= mean;
+            v[i].z -= mean;
+            v[i].w -= mean;
+            q += (v[i].x * v[i].x + v[i].y * v[i].y) + (v[i].z * v[i].z + v[i].w * v[i].w);
+        }
+    }
+    const float var = block_sum<LN_THREADS>(q, sh) / static_cast<float>(H);
+    const float rstd = 1.0f / sqrtf(var + eps);
+#pragma unroll
+    for (int i = 0; i < LN_MAXV; ++i) {
+        const int c = threadIdx.x + i * LN_THREADS;
+        if (c < nvec) {
+            float o[4] = {v[i].x * rstd, v[i].y * rstd, v[i].z * rstd, v[i].w * rstd};
+            if (ln_w != nullptr) {
+                const float4 w4 = __ldg(reinterpret_cast<const float4*>(ln_w) + c);
+                o[0] *= w4.x, o[1] *= w4.y, o[2] *= w4.z, o[3] *= w4.w;
+            }
+            if (ln_b != nullptr) {
+                const float4 b4 = __ldg(reinterpret_cast<const float4*>(ln_b) + c);
+                o[0] += b4.x, o[1] += b4.y, o[2] += b4.z, o[3] += b4.w;
+            }
+            if (scale != nullptr) {
+                const float4 sc = __ldg(reinterpret_cast<const float4*>(scale) + c);
+                o[0] = __fadd_rn(o[0], __fmul_rn(o[0], sc.x));
+                o[1] = __fadd_rn(o[1], __fmul_rn(o[1], sc.y));
+                o[2] = __fadd_rn(o[2], __fmul_rn(o[2], sc.z));
+                o[3] = __fadd_rn(o[3], __fmul_rn(o[3], sc.w));
+            }
+            if (shift != nullptr) {
+                const float4 sf = __ldg(reinterpret_cast<const float4*>(shift) + c);
+                o[0] = __fadd_rn(o[0], sf.x);
+                o[1] = __fadd_rn(o[1], sf.y);
+                o[2] = __fadd_rn(o[2], sf.z);
+                o[3] = __fadd_rn(o[3], sf.w);
+            }
+            store_vec4(y, y_dtype, row * ldy + 4 * c, o[0], o[1], o[2], o[3]);
+        }
+    }
+}
+
+// ------------------------------------------- bit-exact f32 modulate / gate --
+// y = (x + x*scale) + shift ; y = residual + x*gate, every op rounded to f32
+// separately (no FMA), broadcast of the [H] vectors over rows.
+// (src/core/backend/ggml/ed_ggml_modulation_ext.hpp:168-226, cuda/ed_cuda_modulation.cu:77-301)
+__global__ void fused_modulate_kernel(const float4* __restrict__ x, const float4* __restrict__ shift,
+                                      const float4* __restrict__ scale, float4* __restrict__ y, int64_t total4,
+                                      int h4) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total4) return;
+    const int c = static_cast<int>(i % h4);
+    const float4 xv = x[i], sc = __ldg(scale + c), sf = __ldg(shift + c);
+    float4 o;
+    o.x = __fadd_rn(__fadd_rn(xv.x, __fmul_rn(xv.x, sc.x)), sf.x);
+    o.y = __fadd_rn(__fadd_rn(xv.y, __fmul_rn(xv.y, sc.y)), sf.y);
+    o.z = __fadd_rn(__fadd_rn(xv.z, __fmul_rn(xv.z, sc.z)), sf.z);
+    o.w = __fadd_rn(__fadd_rn(xv.w, __fmul_rn(xv.w, sc.w)), sf.w);
+    y[i] = o;
+}
+
+__global__ void fused_residual_gate_kernel(const float4* __restrict__ res, const float4* __restrict__ x,
+                                           const float4* __restrict__ gate, float4* __restrict__ y, int64_t total4,
+                                           int h4) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total4) return;
+    const int c = static_cast<int>(i % h4);
+    const float4 rv = res[i], xv = x[i], g = __ldg(gate + c);
+    float4 o;
+    o.x = __fadd_rn(rv.x, __fmul_rn(xv.x, g.x));
+    o.y = __fadd_rn(rv.y, __fmul_rn(xv.y, g.y));
+    o.z = __fadd_rn(rv.z, __fmul_rn(xv.z, g.z));
+    o.w = __fadd_rn(rv.w, __fmul_rn(xv.w, g.w));
+    y[i] = o;
+}
+
+// ---------------------------------------- QK-RMSNorm + RoPE + head-major pack --
+// One warp per (token, head); lane owns 4 consecutive channels (two RoPE pairs)
+// of a 128-wide head, or 2 channels (one pair) of a 64-wide head.
+// q,k: x * rsqrt(mean(x^2)+eps) * w  (src/dit_models/components/common/normalization.cpp:42-61)
+// then y0 = x0*pe00 + x1*pe10, y1 = x0*pe01 + x1*pe11 with the stored
+// [[cos,-sin],[sin,cos]] table (src/core/backend/ggml/ed_ggml_rope_ext.hpp:105-184),
+// written head-major [head][token][d] like the reference's fused RoPE op.
+template <int D>
+__global__ void __launch_bounds__(256)
+qk_norm_rope_pack_kernel(const void* __restrict__ qkv, int in_dtype, int64_t ld, int64_t q_off, int64_t k_off,
+                         int64_t v_off, int64_t T, int n_heads, const float* __restrict__ q_w,
+                         const float* __restrict__ k_w, float eps, const float* __restrict__ pe, int64_t tok_off,
+                         int64_t L_total, void* __restrict__ q_out, void* __restrict__ k_out,
+                         void* __restrict__ v_out, int out_dtype) {
+    constexpr int E = D / 32;  // elements per lane: 4 or 2
+    const int64_t gw = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (gw >= T * n_heads) return;
+    const int64_t t = gw / n_heads;
+    const int h = static_cast<int>(gw % n_heads);
+    const int64_t row = t * ld;
+    const int64_t out_base = ((int64_t)h * L_total + tok_off + t) * D + lane * E;
+
+    float pe_v[E * 2];  // per pair: pe00, pe10, pe01, pe11  (ggml [row,col] = flat row + 2*col)
+    if (pe != nullptr) {
+        const float* pp = pe + ((tok_off + t) * (D / 2) + lane * (E / 2)) * 4;
+#pragma unroll
+        for (int p = 0; p < E / 2; ++p) {
+            const float4 m = __ldg(reinterpret_cast<const float4*>(pp) + p);
+            pe_v[4 * p + 0] = m.x;  // (row0,col0)
+            pe_v[4 * p + 1] = m.y;  // (row1,col0)
+            pe_v[4 * p + 2] = m.z;  // (row0,col1)
+            pe_v[4 * p + 3] = m.w;  // (row1,col1)
+        }
+    }
+#pragma unroll
+    for (int which = 0; which < 3; ++which) {
+        const int64_t off = row + (which == 0 ? q_off : which == 1 ? k_off : v_off) + (int64_t)h * D + lane * E;
+        float v[E];
+        if (E == 4) {
+            const float4 f = load_vec4(qkv, in_dtype, off);
+            v[0] = f.x, v[1] = f.y, v[2] = f.z, v[3] = f.w;
+        } else {
+            if (in_dtype == EDB200_TYPE_F32) {
+                const float2 f = *reinterpret_cast<const float2*>(static_cast<const float*>(qkv) + off);
+                v[0] = f.x, v[1] = f.y;
+            } else {
+                const uint32_t u = *reinterpret_cast<const uint32_t*>(static_cast<const uint16_t*>(qkv) + off);
+                const float2 f = in_dtype == EDB200_TYPE_BF16
+                                     ? __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u))
+                                     : __half22float2(*reinterpret_cast<const __half2*>(&u));
+                v[0] = f.x, v[1] = f.y;
+            }
+        }
+        void* dst = which == 0 ? q_out : which == 1 ? k_out : v_out;
+        if (which < 2) {
+            const float* w = which == 0 ? q_w : k_w;
+            if (w != nullptr) {
+                float ss = 0.0f;
+#pragma unroll
+                for (int e = 0; e < E; ++e) ss += v[e] * v[e];
+                ss = warp_sum(ss);
+                const float sc = 1.0f / sqrtf(ss / static_cast<float>(D) + eps);
+#pragma unroll
+                for (int e = 0; e < E; ++e) v[e] = (v[e] * sc) * __ldg(w + lane * E + e);
+            }
+            if (pe != nullptr) {
+#pragma unroll
+                for (int p = 0; p < E / 2; ++p) {
+                    const float x0 = v[2 * p], x1 = v[2 * p + 1];
+                    v[2 * p] = __fadd_rn(__fmul_rn(x0, pe_v[4 * p + 0]), __fmul_rn(x1, pe_v[4 * p + 1]));
+                    v[2 * p + 1] = __fadd_rn(__fmul_rn(x0, pe_v[4 * p + 2]), __fmul_rn(x1, pe_v[4 * p + 3]));
+                }
+            }
+        }
+        if (E == 4) {
+            store_vec4(dst, out_dtype, out_base, v[0], v[1], v[2], v[3]);
+        } else {
+            if (out_dtype == EDB200_TYPE_F32) {
+                *reinterpret_cast<float2*>(static_cast<float*>(dst) + out_base) = make_float2(v[0], v[1]);
+            } else if (out_dtype == EDB200_TYPE_BF16) {
+                *reinterpret_cast<__nv_bfloat162*>(static_cast<__nv_bfloat16*>(dst) + out_base) =
+                    __floats2bfloat162_rn(v[0], v[1]);
+            } else {
+                *reinterpret_cast<__half2*>(static_cast<__half*>(dst) + out_base) = __floats2half2_rn(v[0], v[1]);
+            }
+        }
+    }
+}
+
+__global__ void cast_kernel(const void* __restrict__ x, int in_dtype, void* __restrict__ y, int out_dtype,
+                            int64_t n4) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n4) return;
+    const float4 v = load_vec4(x, in_dtype, 4 * i);
+    store_vec4(y, out_dtype, 4 * i, v.x, v.y, v.z, v.w);
+}
+
+static bool dtype_ok(int dt) { return dt == EDB200_TYPE_F32 || dt == EDB200_TYPE_F16 || dt == EDB200_TYPE_BF16; }
+
+}  // namespace edb
+
+using namespace edb;
+
+extern "C" {
+
+edb200_status_t edb200_layernorm_modulate(const float* x, int64_t ldx, const float* shift, const float* scale,
+                                          const float* ln_weight, const float* ln_bias, int64_t rows, int64_t h,
+                                          float eps, void* y, int y_dtype, int64_t ldy, void* stream) {
+    if (x == nullptr || y == nullptr || rows <= 0 || h <= 0) {
+        return fail(EDB200_ERR_INVALID, "layernorm_modulate: null or empty argument");
+    }
+    if (h % 4 != 0 || h > 4 * LN_MAXV * LN_THREADS || ldx % 4 != 0 || ldy % 4 != 0 || !dtype_ok(y_dtype)) {
+        return fail(EDB200_ERR_UNSUPPORTED, "layernorm_modulate: h must be a multiple of 4 and <= 8192");
+    }
+    layernorm_modulate_kernel<<<static_cast<unsigned>(rows), LN_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
+        x, ldx, shift, scale, ln_weight, ln_bias, static_cast<int>(h), eps, y, y_dtype, ldy);
+    count_launch();
+    return check_cuda(cudaGetLastError(), "layernorm_modulate launch");
+}
+
+edb200_status_t edb200_fused_modulate(const float* x, const float* shift, const float* scale, float* y, int64_t rows,
+                                      int64_t h, void* stream) {
+    if (x == nullptr || shift == nullptr || scale == nullptr || y == nullptr || rows <= 0 || h <= 0 || h % 4) {
+        return fail(EDB200_ERR_INVALID, "fused_modulate: bad argument (h %% 4 == 0 required)");
+    }
+    const int64_t total4 = rows * h / 4;
+    fused_modulate_kernel<<<static_cast<unsigned>((total4 + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const float4*>(x), reinterpret_cast<const float4*>(shift),
+        reinterpret_cast<const float4*>(scale), reinterpret_cast<float4*>(y), total4, static_cast<int>(h / 4));
+    count_launch();
+    return check_cuda(cudaGetLastError(), "fused_modulate launch");
+}
+
+edb200_status_t edb200_fused_residual_gate(const float* residual, const float* x, const float* gate, float* y,
+                                           int64_t rows, int64_t h, void* stream) {
+    if (residual == nullptr || x == nullptr || gate == nullptr || y == nullptr || rows <= 0 || h <= 0 || h % 4) {
+        return fail(EDB200_ERR_INVALID, "fused_residual_gate: bad argument (h %% 4 == 0 required)");
+    }
+    const int64_t total4 = rows * h / 4;
+    fused_residual_gate_kernel<<<static_cast<unsigned>((total4 + 255) / 256), 256, 0,
+                                 static_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const float4*>(residual), reinterpret_cast<const float4*>(x),
+        reinterpret_cast<const float4*>(gate), reinterpret_cast<float4*>(y), total4, static_cast<int>(h / 4));
+    count_launch();
+    return check_cuda(cudaGetLastError(), "fused_residual_gate launch");
+}
+
+edb200_status_t edb200_qk_norm_rope_pack(const void* qkv, int in_dtype, int64_t ld, int64_t q_off, int64_t k_off,
+                                         int64_t v_off, int64_t tokens, int n_heads, int d_head, const float* q_weight,
+                                         const float* k_weight, float eps, const float* pe, int64_t tok_off,
+                                         int64_t l_total, void* q_out, void* k_out, void* v_out, int out_dtype,
+                                         void* stream) {
+    if (qkv == nullptr || q_out == nullptr || k_out == nullptr || v_out == nullptr || tokens <= 0 || n_heads <= 0) {
+        return fail(EDB200_ERR_INVALID, "qk_norm_rope_pack: null or empty argument");
+    }
+    if ((d_head != 64 && d_head != 128) || !dtype_ok(in_dtype) || !dtype_ok(out_dtype)) {
+        return fail(EDB200_ERR_UNSUPPORTED, "qk_norm_rope_pack: d_head must be 64 or 128");
+    }
+    if (ld % 4 || q_off % 4 || k_off % 4 || v_off % 4 || tok_off < 0 || tok_off + tokens > l_total) {
+        return fail(EDB200_ERR_INVALID, "qk_norm_rope_pack: offsets must be multiples of 4 and fit l_total");
+    }
+    const int64_t warps = tokens * n_heads;
+    const unsigned grid = static_cast<unsigned>((warps * 32 + 255) / 256);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (d_head == 128) {
+        qk_norm_rope_pack_kernel<128><<<grid, 256, 0, s>>>(qkv, in_dtype, ld, q_off, k_off, v_off, tokens, n_heads,
+                                                           q_weight, k_weight, eps, pe, tok_off, l_total, q_out,
+                                                           k_out, v_out, out_dtype);
+    } else {
+        qk_norm_rope_pack_kernel<64><<<grid, 256, 0, s>>>(qkv, in_dtype, ld, q_off, k_off, v_off, tokens, n_heads,
+                                                          q_weight, k_weight, eps, pe, tok_off, l_total, q_out, k_out,
+                                                          v_out, out_dtype);
+    }
+    count_launch();
+    return check_cuda(cudaGetLastError(), "qk_norm_rope_pack launch");
+}
+
+edb200_status_t edb200_cast(const void* x, int in_dtype, void* y, int out_dtype, int64_t n, void* stream) {
+    if (x == nullptr || y == nullptr || n <= 0 || n % 4 || !dtype_ok(in_dtype) || !dtype_ok(out_dtype)) {
+        return fail(EDB200_ERR_INVALID, "cast: bad argument (n %% 4 == 0 required)");
+    }
+    cast_kernel<<<static_cast<unsigned>((n / 4 + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        x, in_dtype, y, out_dtype, n / 4);
+    count_launch();
+    return check_cuda(cudaGetLastError(), "cast launch");
+}
+
+}  // extern "C"

@@ -1,0 +1,64 @@
+// Internal host-side declarations shared by the .cu files of libedb200.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <atomic>
+#include <string>
+
+#include "edb200_ops.h"
+
+namespace edb {
+
+// Records the message returned by edb200_last_error() and passes `st` through.
+edb200_status_t fail(edb200_status_t st, const char* fmt, ...);
+edb200_status_t check_cuda(cudaError_t e, const char* what);
+void count_launch(int n = 1);
+
+// Device status word shared by all kernels with bounded waits (zero = healthy).
+// Lazily allocated per device; never freed.
+int* device_error_word();
+// Reads and clears the status word (synchronises the stream).
+edb200_status_t poll_device_error(cudaStream_t stream);
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point (libcuda is
+// not linked directly).
+typedef CUresult (*PFN_encodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+PFN_encodeTiled get_encode_tiled();
+
+// 2-D row-major tensor map: dims {inner, outer}, row pitch in bytes, box {box_inner, box_outer}.
+edb200_status_t make_tmap_2d(CUtensorMap* map, CUtensorMapDataType dt, int elem_bytes, const void* base,
+                             uint64_t inner, uint64_t outer, uint64_t pitch_bytes, uint32_t box_inner,
+                             uint32_t box_outer, CUtensorMapSwizzle swz);
+edb200_status_t make_tmap_3d(CUtensorMap* map, CUtensorMapDataType dt, int elem_bytes, const void* base,
+                             uint64_t d0, uint64_t d1, uint64_t d2, uint64_t pitch1_bytes, uint64_t pitch2_bytes,
+                             uint32_t b0, uint32_t b1, uint32_t b2, CUtensorMapSwizzle swz);
+
+int sm_count();
+
+}  // namespace edb
+
+// Repacked quantised weight (device resident).
+struct edb200_qweight {
+    int ggml_type = 0;
+    int64_t n_out = 0;
+    int64_t k = 0;
+    // q8_0: qs = int8 [n_out][k]; sa = f16 scale plane [k/32][n_pad]; sb unused.
+    // q4_K: qs = packed nibbles [n_out][k/2] (two consecutive weights per byte,
+    //       low nibble first); sa = f16 (d*sc) plane, sb = f16 (dmin*m) plane,
+    //       both [k/32][n_pad]; sa32/sb32 = the same products in f32 for the
+    //       exact dequantiser.
+    void* qs = nullptr;
+    void* sa = nullptr;
+    void* sb = nullptr;
+    float* sa32 = nullptr;
+    float* sb32 = nullptr;
+    int64_t n_pad = 0;          // scale-plane row length (multiple of 8)
+    int64_t bytes = 0;
+    CUtensorMap map_qs;         // box {64 B, 256 rows}
+    CUtensorMap map_sa;         // box {256, 2}
+    CUtensorMap map_sb;
+};

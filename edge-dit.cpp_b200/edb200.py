@@ -1,0 +1,143 @@
+"""ctypes binding of libedb200.so (the C ABI declared in include/edb200_ops.h).
+
+This module only loads the shared library and declares argument types; all
+compute happens in the CUDA kernels behind the C entry points.  It fails loudly
+(ImportError / RuntimeError) when the library is missing or a call returns an
+error status -- there is no fallback path.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libedb200.so")
+
+OK = 0
+TYPE_F32, TYPE_F16, TYPE_Q8_0, TYPE_Q4_K, TYPE_I8, TYPE_BF16 = 0, 1, 8, 12, 24, 30
+ACT_NONE, ACT_GELU_TANH, ACT_SILU = 0, 1, 2
+
+c_i64 = C.c_int64
+c_vp = C.c_void_p
+
+
+class Epilogue(C.Structure):
+    _fields_ = [
+        ("bias", c_vp), ("act", C.c_int), ("out", c_vp), ("out_dtype", C.c_int), ("ldo", c_i64),
+        ("residual", c_vp), ("ld_res", c_i64), ("gate", c_vp),
+        ("split_n", c_i64), ("out2", c_vp), ("out2_dtype", C.c_int), ("ldo2", c_i64), ("act2", C.c_int),
+    ]
+
+
+class EdbError(RuntimeError):
+    def __init__(self, status: int, msg: str):
+        super().__init__(f"edb200 status {status}: {msg}")
+        self.status = status
+
+
+_SIGS = {
+    "edb200_last_error": (C.c_char_p, []),
+    "edb200_version": (C.c_char_p, []),
+    "edb200_launch_count": (c_i64, []),
+    "edb200_dequantize_rows": (C.c_int, [C.c_int, c_vp, c_vp, c_i64, c_i64, c_vp]),
+    "edb200_quantize_rows_q8_0": (C.c_int, [c_vp, c_vp, c_i64, c_i64, c_vp]),
+    "edb200_fill_normal": (C.c_int, [c_vp, c_i64, C.c_uint64, C.c_float, C.c_float, c_vp]),
+    "edb200_qweight_create": (C.c_int, [C.c_int, c_vp, c_i64, c_i64, c_vp, C.POINTER(c_vp)]),
+    "edb200_qweight_destroy": (None, [c_vp]),
+    "edb200_qweight_dequantize": (C.c_int, [c_vp, c_vp, c_vp]),
+    "edb200_qweight_bytes": (c_i64, [c_vp]),
+    "edb200_mul_mat_q": (C.c_int, [c_vp, c_vp, C.c_int, c_i64, c_i64, C.POINTER(Epilogue), c_vp]),
+    "edb200_mul_mat_q_pair": (C.c_int, [c_vp, c_vp, c_i64, c_i64, C.POINTER(Epilogue),
+                                        c_vp, c_vp, c_i64, c_i64, C.POINTER(Epilogue), C.c_int, c_vp]),
+    "edb200_gemv_q": (C.c_int, [c_vp, c_vp, c_i64, c_i64, C.c_int, c_vp, c_vp, c_i64, c_vp]),
+    "edb200_linear_f32": (C.c_int, [c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_i64, C.c_int, C.c_int, c_vp, c_i64,
+                                    c_vp]),
+    "edb200_layernorm_modulate": (C.c_int, [c_vp, c_i64, c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, C.c_float, c_vp,
+                                            C.c_int, c_i64, c_vp]),
+    "edb200_fused_modulate": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_vp]),
+    "edb200_fused_residual_gate": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_vp]),
+    "edb200_qk_norm_rope_pack": (C.c_int, [c_vp, C.c_int, c_i64, c_i64, c_i64, c_i64, c_i64, C.c_int, C.c_int,
+                                           c_vp, c_vp, C.c_float, c_vp, c_i64, c_i64, c_vp, c_vp, c_vp, C.c_int,
+                                           c_vp]),
+    "edb200_cast": (C.c_int, [c_vp, C.c_int, c_vp, C.c_int, c_i64, c_vp]),
+}
+
+_lib = None
+
+
+def declared_symbols():
+    """Names this binding expects; tests cross-check them against the header."""
+    return sorted(_SIGS)
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(f"{LIB_PATH} not built; run python edge-dit.cpp_b200/build.py")
+        l = C.CDLL(LIB_PATH)
+        for name, (res, args) in _SIGS.items():
+            fn = getattr(l, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = l
+    return _lib
+
+
+def check(status: int):
+    if status != OK:
+        raise EdbError(status, lib().edb200_last_error().decode())
+
+
+def ptr(t):
+    """Device pointer of a torch tensor (or None)."""
+    return None if t is None else c_vp(t.data_ptr())
+
+
+def torch_dtype_id(t) -> int:
+    import torch
+    return {torch.float32: TYPE_F32, torch.float16: TYPE_F16, torch.bfloat16: TYPE_BF16}[t.dtype]
+
+
+def current_stream():
+    import torch
+    return c_vp(torch.cuda.current_stream().cuda_stream)
+
+
+class QWeight:
+    """Owns an edb200_qweight_t built from raw ggml blocks (uint8 torch tensor on the device)."""
+
+    def __init__(self, ggml_type: int, blocks, n_out: int, k: int):
+        h = c_vp()
+        check(lib().edb200_qweight_create(ggml_type, ptr(blocks), n_out, k, current_stream(), C.byref(h)))
+        self.handle = h
+        self.ggml_type, self.n_out, self.k = ggml_type, n_out, k
+
+    def __del__(self):
+        if getattr(self, "handle", None) and _lib is not None:
+            _lib.edb200_qweight_destroy(self.handle)
+            self.handle = None
+
+
+def make_epilogue(out, bias=None, act=ACT_NONE, residual=None, gate=None, split_n=0, out2=None, act2=ACT_NONE,
+                  ldo=None, ldo2=None):
+    ep = Epilogue()
+    ep.bias = ptr(bias)
+    ep.act = act
+    ep.out = ptr(out)
+    ep.out_dtype = torch_dtype_id(out)
+    ep.ldo = out.stride(0) if ldo is None else ldo
+    ep.residual = ptr(residual)
+    ep.ld_res = residual.stride(0) if residual is not None else 0
+    ep.gate = ptr(gate)
+    ep.split_n = split_n
+    ep.out2 = ptr(out2)
+    ep.out2_dtype = torch_dtype_id(out2) if out2 is not None else 0
+    ep.ldo2 = (out2.stride(0) if ldo2 is None else ldo2) if out2 is not None else 0
+    ep.act2 = act2
+    return ep
+
+
+def mul_mat_q(w: QWeight, x, ep: Epilogue):
+    check(lib().edb200_mul_mat_q(w.handle, ptr(x), torch_dtype_id(x), x.shape[0], x.stride(0), C.byref(ep),
+                                 current_stream()))
