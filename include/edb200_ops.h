@@ -17,6 +17,12 @@
 #include <stddef.h>
 #include <stdint.h>
 
+#if defined(__GNUC__)
+#define EDB200_API __attribute__((visibility("default")))
+#else
+#define EDB200_API
+#endif
+
 #ifdef __cplusplus
 extern "C" {
 #endif
@@ -45,11 +51,11 @@ enum { EDB200_ACT_NONE = 0, EDB200_ACT_GELU_TANH = 1, EDB200_ACT_SILU = 2 };
 
 /* Message of the calling thread's last failed call ("" if none).  Stands in for
  * ed_get_last_error (include/edge-dit.h:333, src/edge_dit.cpp:347-353). */
-const char* edb200_last_error(void);
+EDB200_API const char* edb200_last_error(void);
 /* Library version string and the compute capability it was built for. */
-const char* edb200_version(void);
+EDB200_API const char* edb200_version(void);
 /* Number of kernels this library has launched in the calling process. */
-int64_t edb200_launch_count(void);
+EDB200_API int64_t edb200_launch_count(void);
 
 /* ------------------------------------------------------------------ codecs
  * ggml block codecs on the device.  Stand in for ggml_quantize_chunk /
@@ -57,12 +63,12 @@ int64_t edb200_launch_count(void);
 
 /* Dequantise `rows` rows of `k` weights from raw ggml blocks (q8_0: 34 B per 32,
  * q4_K: 144 B per 256) to f32, bit-exact with ggml's dequantize_row_*. */
-edb200_status_t edb200_dequantize_rows(int ggml_type, const void* blocks, float* out, int64_t rows, int64_t k,
+EDB200_API edb200_status_t edb200_dequantize_rows(int ggml_type, const void* blocks, float* out, int64_t rows, int64_t k,
                                        void* stream);
 /* Quantise f32 rows to raw q8_0 blocks, bit-exact with quantize_row_q8_0_ref. */
-edb200_status_t edb200_quantize_rows_q8_0(const float* x, void* blocks, int64_t rows, int64_t k, void* stream);
+EDB200_API edb200_status_t edb200_quantize_rows_q8_0(const float* x, void* blocks, int64_t rows, int64_t k, void* stream);
 /* Fill `n` floats with N(mean, std) from a counter-based generator (synthetic weights). */
-edb200_status_t edb200_fill_normal(float* out, int64_t n, uint64_t seed, float mean, float std, void* stream);
+EDB200_API edb200_status_t edb200_fill_normal(float* out, int64_t n, uint64_t seed, float mean, float std, void* stream);
 
 /* ----------------------------------------------------------------- weights
  * A quantised linear weight repacked once into the TMA-friendly device layout
@@ -74,13 +80,13 @@ typedef struct edb200_qweight edb200_qweight_t;
  * The raw buffer is not referenced after the call returns (the call
  * synchronises the stream).  Replaces the reference's bind_weights step
  * (src/core/runtime/model_loader.cpp:663-704) for the device copy. */
-edb200_status_t edb200_qweight_create(int ggml_type, const void* blocks, int64_t n_out, int64_t k, void* stream,
+EDB200_API edb200_status_t edb200_qweight_create(int ggml_type, const void* blocks, int64_t n_out, int64_t k, void* stream,
                                       edb200_qweight_t** out);
-void edb200_qweight_destroy(edb200_qweight_t* w);
+EDB200_API void edb200_qweight_destroy(edb200_qweight_t* w);
 /* Dequantise the repacked form back to f32 [n_out, k] (parity check of the repack). */
-edb200_status_t edb200_qweight_dequantize(const edb200_qweight_t* w, float* out, void* stream);
+EDB200_API edb200_status_t edb200_qweight_dequantize(const edb200_qweight_t* w, float* out, void* stream);
 /* Bytes of device memory held by the repacked weight. */
-int64_t edb200_qweight_bytes(const edb200_qweight_t* w);
+EDB200_API int64_t edb200_qweight_bytes(const edb200_qweight_t* w);
 
 /* ----------------------------------------------------------------- mul_mat
  * y[m, n_out] = x[m, k] . W^T (+ bias) with a fused epilogue.  Stands in for
@@ -110,11 +116,11 @@ typedef struct {
 
 /* x: [m, ldx] f16 or bf16, 16-byte aligned rows.  Tensor-core path (tcgen05);
  * for m <= 8 use edb200_gemv_q. */
-edb200_status_t edb200_mul_mat_q(const edb200_qweight_t* w, const void* x, int x_dtype, int64_t m, int64_t ldx,
+EDB200_API edb200_status_t edb200_mul_mat_q(const edb200_qweight_t* w, const void* x, int x_dtype, int64_t m, int64_t ldx,
                                  const edb200_epilogue_t* ep, void* stream);
 
 /* Two independent problems in one launch (txt and img streams of a joint block). */
-edb200_status_t edb200_mul_mat_q_pair(const edb200_qweight_t* w0, const void* x0, int64_t m0, int64_t ldx0,
+EDB200_API edb200_status_t edb200_mul_mat_q_pair(const edb200_qweight_t* w0, const void* x0, int64_t m0, int64_t ldx0,
                                       const edb200_epilogue_t* ep0, const edb200_qweight_t* w1, const void* x1,
                                       int64_t m1, int64_t ldx1, const edb200_epilogue_t* ep1, int x_dtype,
                                       void* stream);
@@ -122,12 +128,12 @@ edb200_status_t edb200_mul_mat_q_pair(const edb200_qweight_t* w0, const void* x0
 /* y[n_out] = act_in(x[k]) . W^T + bias for `m` (<= 8) f32 input rows; weight
  * streaming, HBM bound.  pre_silu applies SiLU to x first (adaLN producers:
  * Modulation::forward, src/dit_models/models/flux.hpp:1617-1634). */
-edb200_status_t edb200_gemv_q(const edb200_qweight_t* w, const float* x, int64_t m, int64_t ldx, int pre_silu,
+EDB200_API edb200_status_t edb200_gemv_q(const edb200_qweight_t* w, const float* x, int64_t m, int64_t ldx, int pre_silu,
                               const float* bias, float* y, int64_t ldy, void* stream);
 
 /* Dense f32 weight, small problems of the prelude / final layer:
  * y[m, n] = act(x[m, k] . W[n, k]^T + bias).  x f32, y f32. */
-edb200_status_t edb200_linear_f32(const float* w, const float* bias, const float* x, int64_t m, int64_t k,
+EDB200_API edb200_status_t edb200_linear_f32(const float* w, const float* bias, const float* x, int64_t m, int64_t k,
                                   int64_t n, int64_t ldx, int pre_silu, int act, float* y, int64_t ldy,
                                   void* stream);
 
@@ -138,7 +144,7 @@ edb200_status_t edb200_linear_f32(const float* w, const float* bias, const float
  * NULL; y f32/f16/bf16 [rows, ldy].  Fuses LayerNorm::forward
  * (src/core/backend/ggml/ggml_extend.hpp:8127-8155, ggml_norm eps 1e-6) with
  * dit::modulate (src/dit_models/components/common/modulation.cpp:9-47). */
-edb200_status_t edb200_layernorm_modulate(const float* x, int64_t ldx, const float* shift, const float* scale,
+EDB200_API edb200_status_t edb200_layernorm_modulate(const float* x, int64_t ldx, const float* shift, const float* scale,
                                           const float* ln_weight, const float* ln_bias, int64_t rows, int64_t h,
                                           float eps, void* y, int y_dtype, int64_t ldy, void* stream);
 
@@ -146,12 +152,12 @@ edb200_status_t edb200_layernorm_modulate(const float* x, int64_t ldx, const flo
  * fused_modulate_cpu_custom_op (src/core/backend/ggml/ed_ggml_modulation_ext.hpp:168-199)
  * and ed_cuda_fused_modulate_custom_compute (cuda/ed_cuda_modulation.cu:528-532).
  * x,y [rows, h] contiguous; shift/scale [h] broadcast over rows. */
-edb200_status_t edb200_fused_modulate(const float* x, const float* shift, const float* scale, float* y, int64_t rows,
+EDB200_API edb200_status_t edb200_fused_modulate(const float* x, const float* shift, const float* scale, float* y, int64_t rows,
                                       int64_t h, void* stream);
 
 /* y = residual + x*gate, f32, bit-identical to fused_residual_gate_cpu_custom_op
  * (src/core/backend/ggml/ed_ggml_modulation_ext.hpp:201-226). */
-edb200_status_t edb200_fused_residual_gate(const float* residual, const float* x, const float* gate, float* y,
+EDB200_API edb200_status_t edb200_fused_residual_gate(const float* residual, const float* x, const float* gate, float* y,
                                            int64_t rows, int64_t h, void* stream);
 
 /* Per-head RMSNorm of q and k (weights [d_head] or NULL), RoPE with the
@@ -163,7 +169,7 @@ edb200_status_t edb200_fused_residual_gate(const float* residual, const float* x
  * (src/core/backend/ggml/ed_ggml_rope_ext.hpp:226-262), the txt||img concat
  * (src/dit_models/models/flux.hpp:1842-1844) and attention_v_prep /
  * attention_qkv_pair_pack (src/core/backend/ggml/ed_ggml_attention_ext.hpp:269-369). */
-edb200_status_t edb200_qk_norm_rope_pack(const void* qkv, int in_dtype, int64_t ld, int64_t q_off, int64_t k_off,
+EDB200_API edb200_status_t edb200_qk_norm_rope_pack(const void* qkv, int in_dtype, int64_t ld, int64_t q_off, int64_t k_off,
                                          int64_t v_off, int64_t tokens, int n_heads, int d_head, const float* q_weight,
                                          const float* k_weight, float eps, const float* pe, int64_t tok_off,
                                          int64_t l_total, void* q_out, void* k_out, void* v_out, int out_dtype,
@@ -171,7 +177,7 @@ edb200_status_t edb200_qk_norm_rope_pack(const void* qkv, int in_dtype, int64_t 
 
 /* Elementwise dtype conversion (f32/f16/bf16), n a multiple of 4
  * (ggml_cast call sites, e.g. src/dit_models/models/flux.hpp:101-111). */
-edb200_status_t edb200_cast(const void* x, int in_dtype, void* y, int out_dtype, int64_t n, void* stream);
+EDB200_API edb200_status_t edb200_cast(const void* x, int in_dtype, void* y, int out_dtype, int64_t n, void* stream);
 
 #ifdef __cplusplus
 }
