@@ -546,8 +546,12 @@ static void fill_problem(gemm::Problem& p, const edb200_qweight_t* w, int64_t m,
 static edb200_status_t launch_qgemm(int nprob, const edb200_qweight_t* const* ws, const void* const* xs,
                                     const int64_t* ms, const int64_t* ldxs, const edb200_epilogue_t* const* eps,
                                     int x_dtype, cudaStream_t stream) {
-    if (x_dtype != EDB200_TYPE_F16 && x_dtype != EDB200_TYPE_BF16) {
-        return fail(EDB200_ERR_INVALID, "mul_mat_q: x_dtype must be f16 or bf16");
+    // tcgen05 kind::f16 raises an illegal-instruction fault when the A and B
+    // formats differ (measured on B200), and the dequantised weights are f16
+    // (rn(d*q) keeps 11 significant bits), so activations must be f16 too.
+    if (x_dtype != EDB200_TYPE_F16) {
+        return fail(x_dtype == EDB200_TYPE_BF16 ? EDB200_ERR_UNSUPPORTED : EDB200_ERR_INVALID,
+                    "mul_mat_q: x_dtype must be f16 (operands of one tcgen05.mma share a 16-bit format)");
     }
     for (int i = 0; i < nprob; ++i) {
         edb200_status_t st = validate_problem(ws[i], xs[i], ms[i], ldxs[i], eps[i]);

@@ -1,0 +1,248 @@
+// SageAttention-style INT8 quantisation of Q and K and the driver that runs
+// quantisation + the INT8-QK attention kernel out of one caller-provided
+// scratch buffer.
+//
+// Quantiser semantics follow the reference's CUDA kernels bit for bit
+// (src/core/backend/ggml/cuda/ed_cuda_sage_attn.cu):
+//   channel means   sequential f32 sum in token order, one division   (:209-244)
+//   Q               per 32-token tile of (q - qm): amax = max(1e-7, |.|),
+//                   scale = amax/127, q8 = rn_even(clamp(v * (1/scale), +-127)) (:61-138)
+//   K               the same per 64-token block of (k - km)            (:144-204)
+//   smooth-Q bias   bias[j] = sum_d qm[d] * K_orig[j][d], 32-lane xor butterfly
+//                   per 32 channels, then sequential over the groups  (:253-281)
+#include "edb200_internal.h"
+
+#include <cuda_fp16.h>
+
+namespace edb {
+namespace sage {
+
+constexpr int kQTile = 32;
+constexpr int kKBlock = 64;
+
+// x [HN, L, D] f16 -> mean [HN, D]; thread per (hn, d), sequential over tokens.
+template <int D>
+__global__ void __launch_bounds__(D)
+channel_mean_kernel(const __half* __restrict__ x, float* __restrict__ mean, int L) {
+    const int hn = blockIdx.x;
+    const int d = threadIdx.x;
+    const __half* p = x + (int64_t)hn * L * D + d;
+    float sum = 0.0f;
+    int t = 0;
+    for (; t + 8 <= L; t += 8) {
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = __half2float(p[(int64_t)(t + i) * D]);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) sum = __fadd_rn(sum, v[i]);
+    }
+    for (; t < L; ++t) sum = __fadd_rn(sum, __half2float(p[(int64_t)t * D]));
+    mean[hn * D + d] = __fdiv_rn(sum, static_cast<float>(L));
+}
+
+// One CTA (128 threads) per (token block, head).  BLK tokens share one scale.
+template <int D, int BLK>
+__global__ void __launch_bounds__(128)
+quant_block_kernel(const __half* __restrict__ x, const float* __restrict__ mean, int8_t* __restrict__ x8,
+                   float* __restrict__ scale, int L, int scale_stride) {
+    __shared__ float sh[4];
+    __shared__ float s_inv;
+    const int blk = blockIdx.x, hn = blockIdx.y, tid = threadIdx.x;
+    const int tok0 = blk * BLK;
+    const __half* xp = x + (int64_t)hn * L * D;
+    const float* mrow = mean ? mean + hn * D : nullptr;
+    constexpr int PER_THREAD = BLK * D / 128;
+    float vals[PER_THREAD];
+    float amax = 1e-7f;
+#pragma unroll
+    for (int i = 0; i < PER_THREAD; ++i) {
+        const int idx = tid + i * 128;
+        const int t = idx / D, d = idx % D;
+        float v = 0.0f;
+        if (tok0 + t < L) {
+            v = __half2float(xp[(int64_t)(tok0 + t) * D + d]);
+            if (mrow) v = __fsub_rn(v, mrow[d]);
+        }
+        vals[i] = v;
+        amax = fmaxf(amax, fabsf(v));
+    }
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
+    if ((tid & 31) == 0) sh[tid >> 5] = amax;
+    __syncthreads();
+    if (tid == 0) {
+        const float a = fmaxf(fmaxf(sh[0], sh[1]), fmaxf(sh[2], sh[3]));
+        const float sc = __fdiv_rn(a, 127.0f);
+        scale[(int64_t)hn * scale_stride + blk] = sc;
+        s_inv = __fdiv_rn(1.0f, sc);
+    }
+    __syncthreads();
+    const float inv = s_inv;
+    int8_t* op = x8 + (int64_t)hn * L * D;
+#pragma unroll
+    for (int i = 0; i < PER_THREAD; ++i) {
+        const int idx = tid + i * 128;
+        const int t = idx / D, d = idx % D;
+        if (tok0 + t < L) {
+            float v = __fmul_rn(vals[i], inv);
+            v = fmaxf(fminf(v, 127.0f), -127.0f);
+            op[(int64_t)(tok0 + t) * D + d] = static_cast<int8_t>(__float2int_rn(v));
+        }
+    }
+}
+
+// One warp per (key, head).
+template <int D>
+__global__ void __launch_bounds__(256)
+smooth_q_bias_kernel(const __half* __restrict__ k, const float* __restrict__ qm, float* __restrict__ bias, int L,
+                     int HN, int bias_stride) {
+    const int64_t gw = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (gw >= (int64_t)L * HN) return;
+    const int hn = static_cast<int>(gw / L);
+    const int tok = static_cast<int>(gw % L);
+    const __half* kp = k + ((int64_t)hn * L + tok) * D;
+    const float* q = qm + hn * D;
+    float total = 0.0f;
+#pragma unroll
+    for (int w = 0; w < D / 32; ++w) {
+        float part = __fmul_rn(__half2float(kp[w * 32 + lane]), q[w * 32 + lane]);
+#pragma unroll
+        for (int m = 16; m > 0; m >>= 1) part = __fadd_rn(part, __shfl_xor_sync(0xffffffffu, part, m));
+        total = __fadd_rn(total, part);
+    }
+    if (lane == 0) bias[(int64_t)hn * bias_stride + tok] = total;
+}
+
+struct Layout {
+    int64_t q8, k8, q_scale, k_scale, qm, km, bias, total;
+    int q_scale_stride, k_scale_stride, bias_stride;
+};
+
+static Layout make_layout(int hn, int64_t l, int d) {
+    Layout lo;
+    const int64_t lpad = (l + 127) / 128 * 128;
+    auto align = [](int64_t x) { return (x + 255) & ~int64_t(255); };
+    int64_t off = 0;
+    lo.q8 = off;
+    off = align(off + (int64_t)hn * l * d);
+    lo.k8 = off;
+    off = align(off + (int64_t)hn * l * d);
+    lo.q_scale_stride = static_cast<int>(lpad / kQTile);
+    lo.k_scale_stride = static_cast<int>(lpad / kKBlock);
+    lo.bias_stride = static_cast<int>(lpad);
+    lo.q_scale = off;
+    off = align(off + (int64_t)hn * lo.q_scale_stride * 4);
+    lo.k_scale = off;
+    off = align(off + (int64_t)hn * lo.k_scale_stride * 4);
+    lo.qm = off;
+    off = align(off + (int64_t)hn * d * 4);
+    lo.km = off;
+    off = align(off + (int64_t)hn * d * 4);
+    lo.bias = off;
+    off = align(off + (int64_t)hn * lo.bias_stride * 4);
+    lo.total = off;
+    return lo;
+}
+
+template <int D>
+static edb200_status_t quantize(const __half* q, const __half* k, int hn, int l, bool smooth_q, char* scratch,
+                                const Layout& lo, cudaStream_t s) {
+    float* qm = reinterpret_cast<float*>(scratch + lo.qm);
+    float* km = reinterpret_cast<float*>(scratch + lo.km);
+    channel_mean_kernel<D><<<hn, D, 0, s>>>(k, km, l);
+    if (smooth_q) channel_mean_kernel<D><<<hn, D, 0, s>>>(q, qm, l);
+    const int lpad = (l + 127) / 128 * 128;
+    quant_block_kernel<D, kQTile><<<dim3(lpad / kQTile, hn), 128, 0, s>>>(
+        q, smooth_q ? qm : nullptr, reinterpret_cast<int8_t*>(scratch + lo.q8),
+        reinterpret_cast<float*>(scratch + lo.q_scale), l, lo.q_scale_stride);
+    quant_block_kernel<D, kKBlock><<<dim3(lpad / kKBlock, hn), 128, 0, s>>>(
+        k, km, reinterpret_cast<int8_t*>(scratch + lo.k8), reinterpret_cast<float*>(scratch + lo.k_scale), l,
+        lo.k_scale_stride);
+    int launches = 3 + (smooth_q ? 1 : 0);
+    if (smooth_q) {
+        // the padded tail of each bias row is read by the attention kernel: keep it finite
+        cudaMemsetAsync(scratch + lo.bias, 0, (size_t)hn * lo.bias_stride * 4, s);
+        const int64_t warps = (int64_t)l * hn;
+        smooth_q_bias_kernel<D><<<static_cast<unsigned>((warps * 32 + 255) / 256), 256, 0, s>>>(
+            k, qm, reinterpret_cast<float*>(scratch + lo.bias), l, hn, lo.bias_stride);
+        ++launches;
+    }
+    count_launch(launches);
+    return check_cuda(cudaGetLastError(), "sage quantize launch");
+}
+
+}  // namespace sage
+}  // namespace edb
+
+using namespace edb;
+
+extern "C" edb200_status_t edb200_attention_sage_int8(const void* q_i8, const void* k_i8, const void* v_f16,
+                                                      const float* q_scale, int q_scale_stride,
+                                                      const float* k_scale, int k_scale_stride, const float* bias,
+                                                      int bias_stride, int hn, int64_t l, int d_head, float scale,
+                                                      void* out, int out_dtype, int64_t ld_out, void* stream);
+
+extern "C" {
+
+int64_t edb200_sage_scratch_bytes(int hn, int64_t l, int d_head) {
+    if (hn <= 0 || l <= 0 || d_head <= 0) return 0;
+    return sage::make_layout(hn, l, d_head).total;
+}
+
+edb200_status_t edb200_sage_scratch_layout(int hn, int64_t l, int d_head, int64_t* offsets, int* strides) {
+    if (offsets == nullptr || strides == nullptr || hn <= 0 || l <= 0 || d_head <= 0) {
+        return fail(EDB200_ERR_INVALID, "sage_scratch_layout: bad argument");
+    }
+    const sage::Layout lo = sage::make_layout(hn, l, d_head);
+    offsets[0] = lo.q8;
+    offsets[1] = lo.k8;
+    offsets[2] = lo.q_scale;
+    offsets[3] = lo.k_scale;
+    offsets[4] = lo.qm;
+    offsets[5] = lo.km;
+    offsets[6] = lo.bias;
+    offsets[7] = lo.total;
+    strides[0] = lo.q_scale_stride;
+    strides[1] = lo.k_scale_stride;
+    strides[2] = lo.bias_stride;
+    return EDB200_OK;
+}
+
+edb200_status_t edb200_sage_quantize_qk(const void* q_f16, const void* k_f16, int hn, int64_t l, int d_head,
+                                        int smooth_q, void* scratch, int64_t scratch_bytes, void* stream) {
+    if (q_f16 == nullptr || k_f16 == nullptr || scratch == nullptr || hn <= 0 || l <= 0) {
+        return fail(EDB200_ERR_INVALID, "sage_quantize_qk: null or empty argument");
+    }
+    if (d_head != 64 && d_head != 128) return fail(EDB200_ERR_UNSUPPORTED, "sage_quantize_qk: d_head must be 64 or 128");
+    const sage::Layout lo = sage::make_layout(hn, l, d_head);
+    if (scratch_bytes < lo.total || (reinterpret_cast<uintptr_t>(scratch) & 255u)) {
+        return fail(EDB200_ERR_INVALID, "sage_quantize_qk: scratch must be 256-byte aligned and hold %lld bytes",
+                    (long long)lo.total);
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (d_head == 128) {
+        return sage::quantize<128>(static_cast<const __half*>(q_f16), static_cast<const __half*>(k_f16), hn,
+                                   static_cast<int>(l), smooth_q != 0, static_cast<char*>(scratch), lo, s);
+    }
+    return sage::quantize<64>(static_cast<const __half*>(q_f16), static_cast<const __half*>(k_f16), hn,
+                              static_cast<int>(l), smooth_q != 0, static_cast<char*>(scratch), lo, s);
+}
+
+edb200_status_t edb200_sage_attention(const void* q_f16, const void* k_f16, const void* v_f16, int hn, int64_t l,
+                                      int d_head, float scale, int smooth_q, void* scratch, int64_t scratch_bytes,
+                                      void* out, int out_dtype, int64_t ld_out, void* stream) {
+    if (v_f16 == nullptr || out == nullptr) return fail(EDB200_ERR_INVALID, "sage_attention: null argument");
+    if (d_head != 128) return fail(EDB200_ERR_UNSUPPORTED, "sage_attention: d_head must be 128");
+    edb200_status_t st = edb200_sage_quantize_qk(q_f16, k_f16, hn, l, d_head, smooth_q, scratch, scratch_bytes, stream);
+    if (st != EDB200_OK) return st;
+    const sage::Layout lo = sage::make_layout(hn, l, d_head);
+    char* sc = static_cast<char*>(scratch);
+    return edb200_attention_sage_int8(sc + lo.q8, sc + lo.k8, v_f16, reinterpret_cast<const float*>(sc + lo.q_scale),
+                                      lo.q_scale_stride, reinterpret_cast<const float*>(sc + lo.k_scale),
+                                      lo.k_scale_stride,
+                                      smooth_q ? reinterpret_cast<const float*>(sc + lo.bias) : nullptr,
+                                      lo.bias_stride, hn, l, d_head, scale, out, out_dtype, ld_out, stream);
+}
+
+}  // extern "C"

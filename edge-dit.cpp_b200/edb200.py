@@ -60,6 +60,15 @@ _SIGS = {
                                            c_vp, c_vp, C.c_float, c_vp, c_i64, c_i64, c_vp, c_vp, c_vp, C.c_int,
                                            c_vp]),
     "edb200_cast": (C.c_int, [c_vp, C.c_int, c_vp, C.c_int, c_i64, c_vp]),
+    "edb200_attention_f16": (C.c_int, [c_vp, c_vp, c_vp, C.c_int, c_i64, c_i64, C.c_int, C.c_float, c_vp, C.c_int,
+                                       c_i64, c_vp]),
+    "edb200_sage_scratch_bytes": (c_i64, [C.c_int, c_i64, C.c_int]),
+    "edb200_sage_scratch_layout": (C.c_int, [C.c_int, c_i64, C.c_int, C.POINTER(c_i64), C.POINTER(C.c_int)]),
+    "edb200_sage_quantize_qk": (C.c_int, [c_vp, c_vp, C.c_int, c_i64, C.c_int, C.c_int, c_vp, c_i64, c_vp]),
+    "edb200_attention_sage_int8": (C.c_int, [c_vp, c_vp, c_vp, c_vp, C.c_int, c_vp, C.c_int, c_vp, C.c_int, C.c_int,
+                                             c_i64, C.c_int, C.c_float, c_vp, C.c_int, c_i64, c_vp]),
+    "edb200_sage_attention": (C.c_int, [c_vp, c_vp, c_vp, C.c_int, c_i64, C.c_int, C.c_float, C.c_int, c_vp, c_i64,
+                                        c_vp, C.c_int, c_i64, c_vp]),
 }
 
 _lib = None

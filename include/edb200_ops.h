@@ -114,8 +114,10 @@ typedef struct {
     int act2;
 } edb200_epilogue_t;
 
-/* x: [m, ldx] f16 or bf16, 16-byte aligned rows.  Tensor-core path (tcgen05);
- * for m <= 8 use edb200_gemv_q. */
+/* x: [m, ldx] f16 (x_dtype = EDB200_TYPE_F16), 16-byte aligned rows.  Tensor-core
+ * path (tcgen05 kind::f16: both operands share one 16-bit format and the weights
+ * dequantise to f16 = rn(d*q), so bf16 activations return EDB200_ERR_UNSUPPORTED).
+ * For m <= 8 use edb200_gemv_q. */
 EDB200_API edb200_status_t edb200_mul_mat_q(const edb200_qweight_t* w, const void* x, int x_dtype, int64_t m, int64_t ldx,
                                  const edb200_epilogue_t* ep, void* stream);
 
@@ -178,6 +180,44 @@ EDB200_API edb200_status_t edb200_qk_norm_rope_pack(const void* qkv, int in_dtyp
 /* Elementwise dtype conversion (f32/f16/bf16), n a multiple of 4
  * (ggml_cast call sites, e.g. src/dit_models/models/flux.hpp:101-111). */
 EDB200_API edb200_status_t edb200_cast(const void* x, int in_dtype, void* y, int out_dtype, int64_t n, void* stream);
+
+/* -------------------------------------------------------------- attention
+ * Non-causal softmax(Q K^T * scale) V.  q [hn, lq, d_head], k/v [hn, lk, d_head]
+ * f16 head-major (d contiguous); out [lq, ld_out] token-major with head h at
+ * columns h*d_head.., f32/f16/bf16.  d_head 64 or 128.  Stands in for
+ * ggml_ext_attention_ext -> ggml_flash_attn_ext / cuDNN SDPA
+ * (src/core/backend/ggml/ggml_extend.hpp:1749-1984, src/core/backend/cuDNN/ed_cudnn_sdpa.cu:1115)
+ * including the head-major -> [d*H, L] re-layout that follows it. */
+EDB200_API edb200_status_t edb200_attention_f16(const void* q, const void* k, const void* v, int hn, int64_t lq,
+                                                int64_t lk, int d_head, float scale, void* out, int out_dtype,
+                                                int64_t ld_out, void* stream);
+
+/* Sage path.  Scratch is caller-allocated like the reference's
+ * (src/core/backend/ggml/cuda/ed_cuda_sage_attn.h:19-71): query the size, pass a
+ * 256-byte aligned device buffer. */
+EDB200_API int64_t edb200_sage_scratch_bytes(int hn, int64_t l, int d_head);
+/* Byte offsets of {q8, k8, q_scale, k_scale, q_mean, k_mean, bias, total} and the
+ * row strides {q_scale, k_scale, bias} inside the scratch buffer. */
+EDB200_API edb200_status_t edb200_sage_scratch_layout(int hn, int64_t l, int d_head, int64_t* offsets, int* strides);
+/* INT8 quantisation of smoothed Q and K, bit-exact with the reference kernels
+ * sage_k_mean / sage_q_mean / sage_quant_q_perwarp / sage_quant_k_perblock_smoothk /
+ * sage_smooth_q_bias (src/core/backend/ggml/cuda/ed_cuda_sage_attn.cu:61-281). */
+EDB200_API edb200_status_t edb200_sage_quantize_qk(const void* q_f16, const void* k_f16, int hn, int64_t l, int d_head,
+                                                   int smooth_q, void* scratch, int64_t scratch_bytes, void* stream);
+/* INT8 QK^T attention on already quantised operands (main kernel of run_sage,
+ * src/core/backend/ggml/cuda/ed_cuda_sage_attn.cu:834-1122).  q_scale one per 32
+ * query rows, k_scale one per 64 keys, bias one per key (NULL = no smooth-Q);
+ * rows of all three must cover l rounded up to 128.  d_head 128. */
+EDB200_API edb200_status_t edb200_attention_sage_int8(const void* q_i8, const void* k_i8, const void* v_f16,
+                                                      const float* q_scale, int q_scale_stride,
+                                                      const float* k_scale, int k_scale_stride, const float* bias,
+                                                      int bias_stride, int hn, int64_t l, int d_head, float scale,
+                                                      void* out, int out_dtype, int64_t ld_out, void* stream);
+/* Quantise + attend (sage_attn_custom, src/core/backend/ggml/ed_ggml_sage_attn_ext.hpp:252-288). */
+EDB200_API edb200_status_t edb200_sage_attention(const void* q_f16, const void* k_f16, const void* v_f16, int hn,
+                                                 int64_t l, int d_head, float scale, int smooth_q, void* scratch,
+                                                 int64_t scratch_bytes, void* out, int out_dtype, int64_t ld_out,
+                                                 void* stream);
 
 #ifdef __cplusplus
 }

@@ -10,8 +10,24 @@ pytestmark = pytest.mark.gpu
 torch = pytest.importorskip("torch")
 
 
+_KEEP = []
+
+
 def dev(a, device):
-    return torch.from_numpy(np.ascontiguousarray(a)).to(device)
+    """Upload to the device and keep the tensor alive until the test ends: the C
+    ABI takes raw pointers, so a temporary freed by Python could be reused by the
+    caching allocator while a kernel still reads it."""
+    t = torch.from_numpy(np.ascontiguousarray(a)).to(device)
+    _KEEP.append(t)
+    return t
+
+
+@pytest.fixture(autouse=True)
+def _release_device_temporaries():
+    yield
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
+    _KEEP.clear()
 
 
 def sync_check(edb):
@@ -199,11 +215,11 @@ def _gemm_case(edb, cuda, wtype, m, n_out, k, x_dt, seed=11):
 
 @pytest.mark.parametrize("wtype,m,n_out,k,x_dt", [
     ("q8_0", 128, 256, 64, torch.float16),
-    ("q8_0", 128, 256, 256, torch.bfloat16),
-    ("q8_0", 300, 768, 3072, torch.bfloat16),     # ragged m, several k stages, 3 column tiles
+    ("q8_0", 128, 256, 256, torch.float16),
+    ("q8_0", 300, 768, 3072, torch.float16),      # ragged m, several k stages, 3 column tiles
     ("q8_0", 1000, 2048, 1024, torch.float16),    # more tiles than one wave of a small grid
-    ("q4_k", 128, 256, 256, torch.bfloat16),
-    ("q4_k", 333, 512, 3072, torch.bfloat16),
+    ("q4_k", 128, 256, 256, torch.float16),
+    ("q4_k", 333, 512, 3072, torch.float16),
 ])
 def test_mul_mat_q_plain(edb, cuda, wtype, m, n_out, k, x_dt):
     w, xt, xr, wd, _ = _gemm_case(edb, cuda, wtype, m, n_out, k, x_dt)
@@ -219,7 +235,7 @@ def test_mul_mat_q_plain(edb, cuda, wtype, m, n_out, k, x_dt):
 
 def test_mul_mat_q_bias_gelu_bf16_out(edb, cuda):
     m, n_out, k = 200, 512, 512
-    w, xt, xr, wd, rng = _gemm_case(edb, cuda, "q8_0", m, n_out, k, torch.bfloat16, seed=12)
+    w, xt, xr, wd, rng = _gemm_case(edb, cuda, "q8_0", m, n_out, k, torch.float16, seed=12)
     b = rng.standard_normal(n_out, dtype=np.float32)
     y = torch.zeros(m, n_out, dtype=torch.bfloat16, device=cuda)
     edb.mul_mat_q(w, xt, edb.make_epilogue(y, bias=dev(b, cuda), act=edb.ACT_GELU_TANH))
@@ -229,7 +245,7 @@ def test_mul_mat_q_bias_gelu_bf16_out(edb, cuda):
 
 def test_mul_mat_q_gated_residual_in_place(edb, cuda):
     m, n_out, k = 260, 768, 1024
-    w, xt, xr, wd, rng = _gemm_case(edb, cuda, "q8_0", m, n_out, k, torch.bfloat16, seed=13)
+    w, xt, xr, wd, rng = _gemm_case(edb, cuda, "q8_0", m, n_out, k, torch.float16, seed=13)
     b = rng.standard_normal(n_out, dtype=np.float32)
     g = rng.standard_normal(n_out, dtype=np.float32)
     res = rng.standard_normal((m, n_out), dtype=np.float32)
@@ -243,7 +259,7 @@ def test_mul_mat_q_column_split(edb, cuda):
     # FLUX single-block linear1: qkv columns to one buffer, GELU(mlp) columns into
     # the tail of the linear2 input buffer.
     m, n_out, k, split = 150, 1024, 512, 512
-    w, xt, xr, wd, rng = _gemm_case(edb, cuda, "q8_0", m, n_out, k, torch.bfloat16, seed=14)
+    w, xt, xr, wd, rng = _gemm_case(edb, cuda, "q8_0", m, n_out, k, torch.float16, seed=14)
     b = rng.standard_normal(n_out, dtype=np.float32)
     qkv = torch.zeros(m, split, dtype=torch.bfloat16, device=cuda)
     cat = torch.zeros(m, 256 + (n_out - split), dtype=torch.bfloat16, device=cuda)
@@ -257,13 +273,13 @@ def test_mul_mat_q_column_split(edb, cuda):
 
 
 def test_mul_mat_q_pair(edb, cuda):
-    w0, x0, xr0, wd0, _ = _gemm_case(edb, cuda, "q8_0", 512, 768, 512, torch.bfloat16, seed=15)
-    w1, x1, xr1, wd1, _ = _gemm_case(edb, cuda, "q8_0", 90, 256, 1024, torch.bfloat16, seed=16)
+    w0, x0, xr0, wd0, _ = _gemm_case(edb, cuda, "q8_0", 512, 768, 512, torch.float16, seed=15)
+    w1, x1, xr1, wd1, _ = _gemm_case(edb, cuda, "q8_0", 90, 256, 1024, torch.float16, seed=16)
     y0 = torch.zeros(512, 768, dtype=torch.float32, device=cuda)
     y1 = torch.zeros(90, 256, dtype=torch.float32, device=cuda)
     e0, e1 = edb.make_epilogue(y0), edb.make_epilogue(y1)
     edb.check(edb.lib().edb200_mul_mat_q_pair(w0.handle, edb.ptr(x0), 512, x0.stride(0), C.byref(e0), w1.handle,
-                                              edb.ptr(x1), 90, x1.stride(0), C.byref(e1), edb.TYPE_BF16,
+                                              edb.ptr(x1), 90, x1.stride(0), C.byref(e1), edb.TYPE_F16,
                                               edb.current_stream()))
     assert O.rel_l2(y0.cpu().numpy(), xr0 @ wd0.T) < 2e-3
     assert O.rel_l2(y1.cpu().numpy(), xr1 @ wd1.T) < 2e-3
@@ -281,10 +297,12 @@ def test_mul_mat_q_linearity(edb, cuda):
 
 
 def test_mul_mat_q_rejects_bad_arguments(edb, cuda):
-    w, xt, _, _, _ = _gemm_case(edb, cuda, "q8_0", 128, 256, 64, torch.bfloat16)
+    w, xt, _, _, _ = _gemm_case(edb, cuda, "q8_0", 128, 256, 64, torch.float16)
     y = torch.zeros(128, 256, dtype=torch.float32, device=cuda)
     with pytest.raises(edb.EdbError):
         edb.mul_mat_q(w, xt.float(), edb.make_epilogue(y))          # f32 activations are not accepted
+    with pytest.raises(edb.EdbError):
+        edb.mul_mat_q(w, xt.bfloat16(), edb.make_epilogue(y))       # operands must share the f16 format
     ep = edb.make_epilogue(y, split_n=100, out2=y)
     with pytest.raises(edb.EdbError):
         edb.mul_mat_q(w, xt, ep)                                     # split not a multiple of 256
