@@ -438,6 +438,8 @@ static edb200_status_t launch(const void* q, const void* k, const void* v, const
         attr_set = true;
     }
     dim3 grid((P.Lq + BQ - 1) / BQ, P.HN);
+    ProfScope prof(stream, PROF_ATTENTION, 4.0 * (double)P.Lq * (double)P.Lk * D * P.HN,
+                   (double)P.HN * D * ((double)P.Lq * (C::QK_ELEM + 2) + (double)P.Lk * (C::QK_ELEM + 2)));
     kern<<<grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(mq, mk, mv, P);
     count_launch();
     return check_cuda(cudaGetLastError(), "attention launch");

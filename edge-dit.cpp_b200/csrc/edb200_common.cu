@@ -5,6 +5,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <mutex>
+#include <vector>
 
 namespace edb {
 
@@ -122,9 +123,68 @@ int sm_count() {
     return n;
 }
 
+struct ProfRecord {
+    cudaEvent_t a, b;
+    ProfClass cls;
+    double flops, bytes;
+};
+static bool g_prof_on = false;
+static std::vector<ProfRecord> g_prof;
+static cudaEvent_t g_prof_pending = nullptr;
+
+bool profiling_enabled() { return g_prof_on; }
+
+void profile_begin_launch(cudaStream_t s) {
+    cudaEvent_t e;
+    cudaEventCreate(&e);
+    cudaEventRecord(e, s);
+    g_prof_pending = e;
+}
+
+void profile_end_launch(cudaStream_t s, ProfClass cls, double flops, double bytes) {
+    ProfRecord r;
+    r.a = g_prof_pending;
+    cudaEventCreate(&r.b);
+    cudaEventRecord(r.b, s);
+    r.cls = cls;
+    r.flops = flops;
+    r.bytes = bytes;
+    g_prof.push_back(r);
+}
+
 }  // namespace edb
 
 extern "C" {
+
+edb200_status_t edb200_profile_begin(void) {
+    edb::g_prof.clear();
+    edb::g_prof_on = true;
+    return EDB200_OK;
+}
+
+edb200_status_t edb200_profile_end(double* ms, double* flops, double* bytes, int64_t* launches) {
+    edb::g_prof_on = false;
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return edb::check_cuda(e, "profile_end");
+    for (int c = 0; c < edb::PROF_NCLASS; ++c) {
+        if (ms) ms[c] = 0;
+        if (flops) flops[c] = 0;
+        if (bytes) bytes[c] = 0;
+        if (launches) launches[c] = 0;
+    }
+    for (edb::ProfRecord& r : edb::g_prof) {
+        float t = 0.0f;
+        cudaEventElapsedTime(&t, r.a, r.b);
+        if (ms) ms[r.cls] += t;
+        if (flops) flops[r.cls] += r.flops;
+        if (bytes) bytes[r.cls] += r.bytes;
+        if (launches) launches[r.cls] += 1;
+        cudaEventDestroy(r.a);
+        cudaEventDestroy(r.b);
+    }
+    edb::g_prof.clear();
+    return EDB200_OK;
+}
 
 const char* edb200_last_error(void) { return edb::g_last_error; }
 

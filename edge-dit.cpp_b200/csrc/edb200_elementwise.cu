@@ -283,6 +283,8 @@ edb200_status_t edb200_layernorm_modulate(const float* x, int64_t ldx, const flo
     if (h % 4 != 0 || h > 4 * LN_MAXV * LN_THREADS || ldx % 4 != 0 || ldy % 4 != 0 || !dtype_ok(y_dtype)) {
         return fail(EDB200_ERR_UNSUPPORTED, "layernorm_modulate: h must be a multiple of 4 and <= 8192");
     }
+    ProfScope prof(static_cast<cudaStream_t>(stream), PROF_ELEMENTWISE, 0.0,
+                   (double)rows * (double)h * (4.0 + (y_dtype == EDB200_TYPE_F32 ? 4.0 : 2.0)));
     layernorm_modulate_kernel<<<static_cast<unsigned>(rows), LN_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
         x, ldx, shift, scale, ln_weight, ln_bias, static_cast<int>(h), eps, y, y_dtype, ldy);
     count_launch();
@@ -333,6 +335,9 @@ edb200_status_t edb200_qk_norm_rope_pack(const void* qkv, int in_dtype, int64_t 
     const int64_t warps = tokens * n_heads;
     const unsigned grid = static_cast<unsigned>((warps * 32 + 255) / 256);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    ProfScope prof(s, PROF_ELEMENTWISE, 0.0,
+                   (double)tokens * 3.0 * n_heads * d_head *
+                       ((in_dtype == EDB200_TYPE_F32 ? 4.0 : 2.0) + (out_dtype == EDB200_TYPE_F32 ? 4.0 : 2.0)));
     if (d_head == 128) {
         qk_norm_rope_pack_kernel<128><<<grid, 256, 0, s>>>(qkv, in_dtype, ld, q_off, k_off, v_off, tokens, n_heads,
                                                            q_weight, k_weight, eps, pe, tok_off, l_total, q_out,

@@ -1,0 +1,524 @@
+// FLUX.1 denoise-step executor: a fixed op schedule (no graph interpreter) over
+// device-resident activations.  Mirrors the reference graph
+// (src/dit_models/models/flux.hpp): Flux::forward_orig :3872-4527,
+// DoubleStreamBlock::forward :1747-1925, SingleStreamBlock::forward :2974-3034,
+// LastLayer::forward :3533-3559, Modulation::forward :1617-1634, and the runner
+// seam FluxRunner::compute :5158-5296 (host tensors in, host tensor out).
+//
+// Data layout in HBM for one step (T = T_txt + T_img, text rows first):
+//   X      f32 [T, H]        residual stream, both streams in one buffer so the
+//                            single-stream stack needs no concat
+//   XMOD   f16 [T, H]        LayerNorm+modulate output = GEMM operand
+//   QKV    f16 [T, 3H]       QKV projection output
+//   Q,K,V  f16 [heads, T, d] head-major attention operands (RoPE'd, RMS-normed)
+//   CAT    f16 [T, H + M]    [attention | GELU(mlp)] = linear2 operand of single
+//                            blocks; double blocks use its first H columns and HID
+//   HID    f16 [T, M]        GELU(mlp.0) of double blocks
+//   MODS   f32               every adaLN shift/scale/gate vector of the step
+#include "edb200_model.h"
+
+#include <cuda_fp16.h>
+#include <cmath>
+#include <cstring>
+
+using namespace edb;
+
+struct edb200_flux {
+    edb200_flux_config_t cfg;
+    ParamTable params;
+    Workspace ws;
+    // shape the workspace was prepared for
+    int lat_h = 0, lat_w = 0, n_txt = 0, n_img = 0;
+    // activations
+    float* X = nullptr;
+    void *XMOD = nullptr, *QKV = nullptr, *Q = nullptr, *K = nullptr, *V = nullptr, *CAT = nullptr, *HID = nullptr;
+    float *MODS = nullptr, *VEC = nullptr, *TMP_H = nullptr, *TEMB = nullptr, *TOK_IN = nullptr, *TOK_OUT = nullptr;
+    float *FIN = nullptr, *PE = nullptr, *FREQ = nullptr, *LAT_IN = nullptr, *LAT_OUT = nullptr, *CTX = nullptr,
+          *YVEC = nullptr;
+    void* SAGE = nullptr;
+    int64_t sage_bytes = 0;
+    float* tap = nullptr;
+    // host staging for compute_host
+    float* pinned = nullptr;
+    int64_t pinned_bytes = 0;
+};
+
+namespace {
+
+int64_t mods_per_step(const edb200_flux_config_t& c) {
+    return (int64_t)c.hidden_size * (12 * c.depth + 3 * c.depth_single_blocks + 2);
+}
+
+void register_params(edb200_flux* m) {
+    const edb200_flux_config_t& c = m->cfg;
+    const int64_t H = c.hidden_size, M = c.mlp_hidden, d = H / c.num_heads;
+    ParamTable& t = m->params;
+    auto lin = [&](const std::string& name, int64_t n_out, int64_t k, bool q) {
+        t.add(name + ".weight", n_out, k, q, c.wtype);
+        t.add(name + ".bias", 1, n_out, false, c.wtype);
+    };
+    // Which tensors are quantised follows tensor_should_be_converted
+    // (reference src/core/runtime/model_loader.cpp:2141-2172): the in/out
+    // embedders and final_layer stay f32.
+    lin("img_in", H, c.in_channels, false);
+    lin("txt_in", H, c.context_in_dim, false);
+    lin("time_in.in_layer", H, 256, false);
+    lin("time_in.out_layer", H, H, false);
+    if (c.guidance_embed) {
+        lin("guidance_in.in_layer", H, 256, false);
+        lin("guidance_in.out_layer", H, H, false);
+    }
+    lin("vector_in.in_layer", H, c.vec_in_dim, false);
+    lin("vector_in.out_layer", H, H, false);
+    for (int i = 0; i < c.depth; ++i) {
+        const std::string p = "double_blocks." + std::to_string(i) + ".";
+        for (const char* s : {"img", "txt"}) {
+            const std::string sp = p + s;
+            lin(sp + "_mod.lin", 6 * H, H, true);
+            lin(sp + "_attn.qkv", 3 * H, H, true);
+            t.add(sp + "_attn.norm.query_norm.scale", 1, d, false, c.wtype);
+            t.add(sp + "_attn.norm.key_norm.scale", 1, d, false, c.wtype);
+            lin(sp + "_attn.proj", H, H, true);
+            lin(sp + "_mlp.0", M, H, true);
+            lin(sp + "_mlp.2", H, M, true);
+        }
+    }
+    for (int i = 0; i < c.depth_single_blocks; ++i) {
+        const std::string p = "single_blocks." + std::to_string(i) + ".";
+        lin(p + "modulation.lin", 3 * H, H, true);
+        lin(p + "linear1", 3 * H + M, H, true);
+        lin(p + "linear2", H, H + M, true);
+        t.add(p + "norm.query_norm.scale", 1, d, false, c.wtype);
+        t.add(p + "norm.key_norm.scale", 1, d, false, c.wtype);
+    }
+    lin("final_layer.adaLN_modulation.1", 2 * H, H, false);
+    lin("final_layer.linear", c.in_channels, H, false);
+}
+
+// pe[L, d/2, 2, 2] = [[cos, -sin], [sin, cos]] per (token, pair); text tokens
+// first with all-zero ids, image token ids (0, row, col).  Follows
+// Rope::rope / embed_nd / gen_flux_ids (reference
+// src/dit_models/components/common/rope.hpp:77-127,201-260,130-199).
+std::vector<float> build_flux_pe(const edb200_flux_config_t& c, int h_tok, int w_tok, int n_txt) {
+    const int L = n_txt + h_tok * w_tok;
+    int half_total = 0;
+    for (int a = 0; a < 3; ++a) half_total += c.axes_dim[a] / 2;
+    std::vector<float> pe((size_t)L * half_total * 4, 0.0f);
+    int off = 0;
+    for (int a = 0; a < 3; ++a) {
+        const int dim = c.axes_dim[a], half = dim / 2;
+        std::vector<float> omega(half);
+        const float end = (dim * 1.f - 2) / dim;
+        const float step = half > 1 ? (end - 0.f) / (half - 1) : 0.f;
+        for (int i = 0; i < half; ++i) omega[i] = 1.0f / ::powf(1.f * c.theta, 0.f + i * step);
+        for (int t = 0; t < L; ++t) {
+            float pos = 0.0f;
+            if (t >= n_txt) {
+                const int it = t - n_txt;
+                pos = a == 0 ? 0.0f : a == 1 ? static_cast<float>(it / w_tok) : static_cast<float>(it % w_tok);
+            }
+            for (int j = 0; j < half; ++j) {
+                const float ang = pos * omega[j];
+                float* o = &pe[((size_t)t * half_total + off + j) * 4];
+                o[0] = std::cos(ang);
+                o[1] = -std::sin(ang);
+                o[2] = std::sin(ang);
+                o[3] = std::cos(ang);
+            }
+        }
+        off += half;
+    }
+    return pe;
+}
+
+#define EDB_TRY(expr)                          \
+    do {                                       \
+        edb200_status_t _st = (expr);          \
+        if (_st != EDB200_OK) return _st;      \
+    } while (0)
+
+edb200_epilogue_t make_ep(void* out, int dt, int64_t ldo, const float* bias) {
+    edb200_epilogue_t ep;
+    memset(&ep, 0, sizeof(ep));
+    ep.out = out;
+    ep.out_dtype = dt;
+    ep.ldo = ldo;
+    ep.bias = bias;
+    return ep;
+}
+
+struct Lin {
+    const edb200_qweight_t* w;
+    const float* b;
+};
+
+Lin qlin(edb200_flux* m, const std::string& name) {
+    Lin l;
+    l.w = m->params.get(name + ".weight")->qw;
+    l.b = m->params.get(name + ".bias")->f32;
+    return l;
+}
+
+const float* fparam(edb200_flux* m, const std::string& name) { return m->params.get(name)->f32; }
+
+edb200_status_t dense(edb200_flux* m, const std::string& name, const float* x, int64_t rows, int64_t ldx, int pre_silu,
+                      int act, float* y, int64_t ldy, cudaStream_t s) {
+    const Param* w = m->params.get(name + ".weight");
+    return edb200_linear_f32(w->f32, fparam(m, name + ".bias"), x, rows, w->spec.k, w->spec.n_out, ldx, pre_silu, act,
+                             y, ldy, s);
+}
+
+edb200_status_t attention(edb200_flux* m, int64_t T, void* out, int64_t ld_out, cudaStream_t s) {
+    const edb200_flux_config_t& c = m->cfg;
+    const int d = c.hidden_size / c.num_heads;
+    const float scale = 1.0f / std::sqrt(static_cast<float>(d));
+    if (c.attention == EDB200_ATTN_SAGE_INT8) {
+        return edb200_sage_attention(m->Q, m->K, m->V, c.num_heads, T, d, scale, c.sage_smooth_q, m->SAGE,
+                                     m->sage_bytes, out, EDB200_TYPE_F16, ld_out, s);
+    }
+    return edb200_attention_f16(m->Q, m->K, m->V, c.num_heads, T, T, d, scale, out, EDB200_TYPE_F16, ld_out, s);
+}
+
+}  // namespace
+
+extern "C" {
+
+edb200_status_t edb200_flux_create(const edb200_flux_config_t* cfg, edb200_flux_t** out) {
+    if (cfg == nullptr || out == nullptr) return fail(EDB200_ERR_INVALID, "flux_create: null argument");
+    const edb200_flux_config_t& c = *cfg;
+    if (c.hidden_size <= 0 || c.num_heads <= 0 || c.hidden_size % c.num_heads) {
+        return fail(EDB200_ERR_INVALID, "flux_create: hidden_size must be a positive multiple of num_heads");
+    }
+    const int d = c.hidden_size / c.num_heads;
+    if (d != 64 && d != 128) return fail(EDB200_ERR_UNSUPPORTED, "flux_create: head dim must be 64 or 128");
+    if (c.axes_dim[0] + c.axes_dim[1] + c.axes_dim[2] != d) {
+        return fail(EDB200_ERR_INVALID, "flux_create: axes_dim must sum to the head dim");
+    }
+    if (c.wtype != EDB200_TYPE_Q8_0 && c.wtype != EDB200_TYPE_Q4_K) {
+        return fail(EDB200_ERR_UNSUPPORTED, "flux_create: wtype must be q8_0 or q4_K");
+    }
+    const int blk = c.wtype == EDB200_TYPE_Q4_K ? 256 : 64;
+    if (c.hidden_size % 256 || c.mlp_hidden % 256 || (c.hidden_size + c.mlp_hidden) % blk) {
+        return fail(EDB200_ERR_UNSUPPORTED, "flux_create: hidden_size and mlp_hidden must be multiples of 256");
+    }
+    if (c.attention == EDB200_ATTN_SAGE_INT8 && d != 128) {
+        return fail(EDB200_ERR_UNSUPPORTED, "flux_create: INT8 attention needs head dim 128");
+    }
+    if (c.in_channels % 4 || c.context_in_dim % 4 || c.vec_in_dim % 4 || c.patch_size <= 0) {
+        return fail(EDB200_ERR_INVALID, "flux_create: input dims must be multiples of 4");
+    }
+    if (device_error_word() == nullptr) return fail(EDB200_ERR_CUDA, "flux_create: no CUDA device");
+    edb200_flux* m = new (std::nothrow) edb200_flux();
+    if (m == nullptr) return fail(EDB200_ERR_NOMEM, "flux_create: host allocation failed");
+    m->cfg = c;
+    register_params(m);
+    *out = m;
+    return EDB200_OK;
+}
+
+void edb200_flux_destroy(edb200_flux_t* m) {
+    if (m == nullptr) return;
+    if (m->pinned) cudaFreeHost(m->pinned);
+    delete m;
+}
+
+int edb200_flux_tensor_count(const edb200_flux_t* m) {
+    return m ? static_cast<int>(const_cast<edb200_flux_t*>(m)->params.params().size()) : 0;
+}
+
+edb200_status_t edb200_flux_tensor_info(const edb200_flux_t* m, int index, char* name, int name_cap, int* ggml_type,
+                                        int64_t* n_out, int64_t* k, int64_t* nbytes) {
+    if (m == nullptr || index < 0 || index >= edb200_flux_tensor_count(m)) {
+        return fail(EDB200_ERR_INVALID, "flux_tensor_info: bad index");
+    }
+    const Param& p = const_cast<edb200_flux_t*>(m)->params.params()[index];
+    if (name != nullptr && name_cap > 0) {
+        strncpy(name, p.spec.name.c_str(), name_cap - 1);
+        name[name_cap - 1] = '\0';
+    }
+    if (ggml_type) *ggml_type = p.spec.ggml_type;
+    if (n_out) *n_out = p.spec.n_out;
+    if (k) *k = p.spec.k;
+    if (nbytes) *nbytes = p.spec.n_out * ggml_row_bytes(p.spec.ggml_type, p.spec.k);
+    return EDB200_OK;
+}
+
+edb200_status_t edb200_flux_set_tensor(edb200_flux_t* m, const char* name, int ggml_type, const void* data,
+                                       int64_t nbytes, int on_device, void* stream) {
+    if (m == nullptr || name == nullptr) return fail(EDB200_ERR_INVALID, "flux_set_tensor: null argument");
+    return m->params.set(name, ggml_type, data, nbytes, on_device != 0, static_cast<cudaStream_t>(stream));
+}
+
+edb200_status_t edb200_flux_init_random(edb200_flux_t* m, uint64_t seed, float std, void* stream) {
+    if (m == nullptr) return fail(EDB200_ERR_INVALID, "flux_init_random: null model");
+    return m->params.init_random(seed, std, static_cast<cudaStream_t>(stream));
+}
+
+int64_t edb200_flux_weight_bytes(const edb200_flux_t* m) { return m ? m->params.device_bytes() : 0; }
+int64_t edb200_flux_workspace_bytes(const edb200_flux_t* m) { return m ? m->ws.capacity() : 0; }
+
+edb200_status_t edb200_flux_prepare(edb200_flux_t* m, int latent_h, int latent_w, int n_txt, void* stream) {
+    if (m == nullptr) return fail(EDB200_ERR_INVALID, "flux_prepare: null model");
+    const edb200_flux_config_t& c = m->cfg;
+    const int p = c.patch_size;
+    if (latent_h <= 0 || latent_w <= 0 || n_txt <= 0 || latent_h % p || latent_w % p) {
+        return fail(EDB200_ERR_INVALID, "flux_prepare: latent must be a positive multiple of the patch size");
+    }
+    if (m->lat_h == latent_h && m->lat_w == latent_w && m->n_txt == n_txt) return EDB200_OK;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int64_t H = c.hidden_size, M = c.mlp_hidden, d = H / c.num_heads;
+    const int h_tok = latent_h / p, w_tok = latent_w / p;
+    const int64_t n_img = (int64_t)h_tok * w_tok, T = n_img + n_txt;
+    const int lat_c = c.in_channels / (p * p);
+    const int64_t sage = c.attention == EDB200_ATTN_SAGE_INT8 ? edb200_sage_scratch_bytes(c.num_heads, T, (int)d) : 0;
+    const int64_t lat_elems = (int64_t)lat_c * latent_h * latent_w;
+    const int64_t pe_elems = T * (d / 2) * 4;
+    auto al = [](int64_t b) { return (b + 255) & ~int64_t(255); };
+    int64_t total = 0;
+    total += al(T * H * 4) + al(T * H * 2) + al(T * 3 * H * 2) + 3 * al(T * H * 2) + al(T * (H + M) * 2) +
+             al(T * M * 2);
+    total += al(mods_per_step(c) * 4) + 3 * al(H * 4) + al(256 * 4) + 2 * al(n_img * c.in_channels * 4);
+    total += al(n_img * H * 4) + al(pe_elems * 4) + al(128 * 4) + 2 * al(lat_elems * 4) +
+             al((int64_t)n_txt * c.context_in_dim * 4) + al(c.vec_in_dim * 4) + al(sage) + 4096;
+    cudaStreamSynchronize(s);
+    EDB_TRY(m->ws.reserve(total));
+    Workspace& w = m->ws;
+    m->X = w.take_n<float>(T * H);
+    m->XMOD = w.take(T * H * 2);
+    m->QKV = w.take(T * 3 * H * 2);
+    m->Q = w.take(T * H * 2);
+    m->K = w.take(T * H * 2);
+    m->V = w.take(T * H * 2);
+    m->CAT = w.take(T * (H + M) * 2);
+    m->HID = w.take(T * M * 2);
+    m->MODS = w.take_n<float>(mods_per_step(c));
+    m->VEC = w.take_n<float>(H);
+    m->TMP_H = w.take_n<float>(2 * H);
+    m->TEMB = w.take_n<float>(256);
+    m->TOK_IN = w.take_n<float>(n_img * c.in_channels);
+    m->TOK_OUT = w.take_n<float>(n_img * c.in_channels);
+    m->FIN = w.take_n<float>(n_img * H);
+    m->PE = w.take_n<float>(pe_elems);
+    m->FREQ = w.take_n<float>(128);
+    m->LAT_IN = w.take_n<float>(lat_elems);
+    m->LAT_OUT = w.take_n<float>(lat_elems);
+    m->CTX = w.take_n<float>((int64_t)n_txt * c.context_in_dim);
+    m->YVEC = w.take_n<float>(c.vec_in_dim);
+    m->SAGE = sage > 0 ? w.take(sage) : nullptr;
+    m->sage_bytes = sage;
+    if (m->YVEC == nullptr || (sage > 0 && m->SAGE == nullptr)) {
+        return fail(EDB200_ERR_NOMEM, "flux_prepare: workspace accounting error");
+    }
+    // position table and sinusoid frequencies are computed once per shape on the host
+    std::vector<float> pe = build_flux_pe(c, h_tok, w_tok, n_txt);
+    std::vector<float> freq(128);
+    for (int i = 0; i < 128; ++i) freq[i] = (float)std::exp(-std::log(10000) * i / 128);
+    cudaError_t e = cudaMemcpyAsync(m->PE, pe.data(), pe.size() * 4, cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(m->FREQ, freq.data(), 128 * 4, cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    if (e != cudaSuccess) return check_cuda(e, "flux_prepare upload");
+    // pinned staging for the host-tensor entry point
+    const int64_t need = (2 * lat_elems + (int64_t)n_txt * c.context_in_dim + c.vec_in_dim) * 4;
+    if (need > m->pinned_bytes) {
+        if (m->pinned) cudaFreeHost(m->pinned);
+        m->pinned = nullptr;
+        e = cudaMallocHost(reinterpret_cast<void**>(&m->pinned), need);
+        if (e != cudaSuccess) return fail(EDB200_ERR_NOMEM, "flux_prepare: cudaMallocHost: %s", cudaGetErrorString(e));
+        m->pinned_bytes = need;
+    }
+    m->lat_h = latent_h;
+    m->lat_w = latent_w;
+    m->n_txt = n_txt;
+    m->n_img = static_cast<int>(n_img);
+    return EDB200_OK;
+}
+
+edb200_status_t edb200_flux_set_tap(edb200_flux_t* m, float* tap) {
+    if (m == nullptr) return fail(EDB200_ERR_INVALID, "flux_set_tap: null model");
+    m->tap = tap;
+    return EDB200_OK;
+}
+
+edb200_status_t edb200_flux_step(edb200_flux_t* m, const float* latent, float timestep, const float* context,
+                                 const float* y, float guidance, float* out, void* stream) {
+    if (m == nullptr || latent == nullptr || context == nullptr || y == nullptr || out == nullptr) {
+        return fail(EDB200_ERR_INVALID, "flux_step: null argument");
+    }
+    if (m->lat_h == 0) return fail(EDB200_ERR_INVALID, "flux_step: call edb200_flux_prepare first");
+    EDB_TRY(m->params.all_loaded());
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const edb200_flux_config_t& c = m->cfg;
+    const int64_t H = c.hidden_size, M = c.mlp_hidden;
+    const int d = static_cast<int>(H / c.num_heads);
+    const int64_t n_txt = m->n_txt, n_img = m->n_img, T = n_txt + n_img;
+    const int lat_c = c.in_channels / (c.patch_size * c.patch_size);
+    const int F16 = EDB200_TYPE_F16;
+    float* X_txt = m->X;
+    float* X_img = m->X + n_txt * H;
+    __half* xmod = static_cast<__half*>(m->XMOD);
+    __half* qkv = static_cast<__half*>(m->QKV);
+    __half* cat = static_cast<__half*>(m->CAT);
+    __half* hid = static_cast<__half*>(m->HID);
+
+    // ---- prelude (Flux::forward_orig, flux.hpp:3886-3965)
+    launch_patchify(latent, m->TOK_IN, lat_c, m->lat_h, m->lat_w, c.patch_size, s);
+    EDB_TRY(dense(m, "img_in", m->TOK_IN, n_img, c.in_channels, 0, EDB200_ACT_NONE, X_img, H, s));
+    EDB_TRY(dense(m, "txt_in", context, n_txt, c.context_in_dim, 0, EDB200_ACT_NONE, X_txt, H, s));
+    launch_timestep_embedding(m->FREQ, timestep, 1000.0f, 128, m->TEMB, s);
+    EDB_TRY(dense(m, "time_in.in_layer", m->TEMB, 1, 256, 0, EDB200_ACT_SILU, m->TMP_H, H, s));
+    EDB_TRY(dense(m, "time_in.out_layer", m->TMP_H, 1, H, 0, EDB200_ACT_NONE, m->VEC, H, s));
+    if (c.guidance_embed) {
+        launch_timestep_embedding(m->FREQ, guidance, 1000.0f, 128, m->TEMB, s);
+        EDB_TRY(dense(m, "guidance_in.in_layer", m->TEMB, 1, 256, 0, EDB200_ACT_SILU, m->TMP_H, H, s));
+        EDB_TRY(dense(m, "guidance_in.out_layer", m->TMP_H, 1, H, 0, EDB200_ACT_NONE, m->TMP_H + H, H, s));
+        launch_add_inplace(m->VEC, m->TMP_H + H, H, s);
+    }
+    EDB_TRY(dense(m, "vector_in.in_layer", y, 1, c.vec_in_dim, 0, EDB200_ACT_SILU, m->TMP_H, H, s));
+    EDB_TRY(dense(m, "vector_in.out_layer", m->TMP_H, 1, H, 0, EDB200_ACT_NONE, m->TMP_H + H, H, s));
+    launch_add_inplace(m->VEC, m->TMP_H + H, H, s);
+
+    // ---- every adaLN vector of the step: lin(silu(vec)), weight streaming
+    float* mods = m->MODS;
+    for (int i = 0; i < c.depth; ++i) {
+        const std::string p = "double_blocks." + std::to_string(i) + ".";
+        for (int st = 0; st < 2; ++st) {
+            const Lin l = qlin(m, p + (st == 0 ? "img" : "txt") + "_mod.lin");
+            EDB_TRY(edb200_gemv_q(l.w, m->VEC, 1, H, 1, l.b, mods + ((int64_t)i * 12 + st * 6) * H, 6 * H, s));
+        }
+    }
+    float* smods = mods + (int64_t)c.depth * 12 * H;
+    for (int i = 0; i < c.depth_single_blocks; ++i) {
+        const Lin l = qlin(m, "single_blocks." + std::to_string(i) + ".modulation.lin");
+        EDB_TRY(edb200_gemv_q(l.w, m->VEC, 1, H, 1, l.b, smods + (int64_t)i * 3 * H, 3 * H, s));
+    }
+    float* fmods = smods + (int64_t)c.depth_single_blocks * 3 * H;
+    EDB_TRY(dense(m, "final_layer.adaLN_modulation.1", m->VEC, 1, H, 1, EDB200_ACT_NONE, fmods, 2 * H, s));
+
+    // ---- double-stream blocks
+    for (int i = 0; i < c.depth; ++i) {
+        const std::string p = "double_blocks." + std::to_string(i) + ".";
+        const float* im = mods + (int64_t)i * 12 * H;   // shift1 scale1 gate1 shift2 scale2 gate2
+        const float* tm = im + 6 * H;
+        EDB_TRY(edb200_layernorm_modulate(X_img, H, im, im + H, nullptr, nullptr, n_img, H, 1e-6f, xmod + n_txt * H,
+                                          F16, H, s));
+        EDB_TRY(edb200_layernorm_modulate(X_txt, H, tm, tm + H, nullptr, nullptr, n_txt, H, 1e-6f, xmod, F16, H, s));
+        {
+            const Lin li = qlin(m, p + "img_attn.qkv"), lt = qlin(m, p + "txt_attn.qkv");
+            edb200_epilogue_t ei = make_ep(qkv + n_txt * 3 * H, F16, 3 * H, li.b);
+            edb200_epilogue_t et = make_ep(qkv, F16, 3 * H, lt.b);
+            EDB_TRY(edb200_mul_mat_q_pair(li.w, xmod + n_txt * H, n_img, H, &ei, lt.w, xmod, n_txt, H, &et, F16, s));
+        }
+        EDB_TRY(edb200_qk_norm_rope_pack(qkv + n_txt * 3 * H, F16, 3 * H, 0, H, 2 * H, n_img, c.num_heads, d,
+                                         fparam(m, p + "img_attn.norm.query_norm.scale"),
+                                         fparam(m, p + "img_attn.norm.key_norm.scale"), 1e-6f, m->PE, n_txt, T, m->Q,
+                                         m->K, m->V, F16, s));
+        EDB_TRY(edb200_qk_norm_rope_pack(qkv, F16, 3 * H, 0, H, 2 * H, n_txt, c.num_heads, d,
+                                         fparam(m, p + "txt_attn.norm.query_norm.scale"),
+                                         fparam(m, p + "txt_attn.norm.key_norm.scale"), 1e-6f, m->PE, 0, T, m->Q, m->K,
+                                         m->V, F16, s));
+        EDB_TRY(attention(m, T, cat, H + M, s));
+        {
+            const Lin li = qlin(m, p + "img_attn.proj"), lt = qlin(m, p + "txt_attn.proj");
+            edb200_epilogue_t ei = make_ep(X_img, EDB200_TYPE_F32, H, li.b);
+            ei.residual = X_img, ei.ld_res = H, ei.gate = im + 2 * H;
+            edb200_epilogue_t et = make_ep(X_txt, EDB200_TYPE_F32, H, lt.b);
+            et.residual = X_txt, et.ld_res = H, et.gate = tm + 2 * H;
+            EDB_TRY(edb200_mul_mat_q_pair(li.w, cat + n_txt * (H + M), n_img, H + M, &ei, lt.w, cat, n_txt, H + M, &et,
+                                          F16, s));
+        }
+        EDB_TRY(edb200_layernorm_modulate(X_img, H, im + 3 * H, im + 4 * H, nullptr, nullptr, n_img, H, 1e-6f,
+                                          xmod + n_txt * H, F16, H, s));
+        EDB_TRY(edb200_layernorm_modulate(X_txt, H, tm + 3 * H, tm + 4 * H, nullptr, nullptr, n_txt, H, 1e-6f, xmod,
+                                          F16, H, s));
+        {
+            const Lin li = qlin(m, p + "img_mlp.0"), lt = qlin(m, p + "txt_mlp.0");
+            edb200_epilogue_t ei = make_ep(hid + n_txt * M, F16, M, li.b);
+            ei.act = EDB200_ACT_GELU_TANH;
+            edb200_epilogue_t et = make_ep(hid, F16, M, lt.b);
+            et.act = EDB200_ACT_GELU_TANH;
+            EDB_TRY(edb200_mul_mat_q_pair(li.w, xmod + n_txt * H, n_img, H, &ei, lt.w, xmod, n_txt, H, &et, F16, s));
+        }
+        {
+            const Lin li = qlin(m, p + "img_mlp.2"), lt = qlin(m, p + "txt_mlp.2");
+            edb200_epilogue_t ei = make_ep(X_img, EDB200_TYPE_F32, H, li.b);
+            ei.residual = X_img, ei.ld_res = H, ei.gate = im + 5 * H;
+            edb200_epilogue_t et = make_ep(X_txt, EDB200_TYPE_F32, H, lt.b);
+            et.residual = X_txt, et.ld_res = H, et.gate = tm + 5 * H;
+            EDB_TRY(edb200_mul_mat_q_pair(li.w, hid + n_txt * M, n_img, M, &ei, lt.w, hid, n_txt, M, &et, F16, s));
+        }
+        if (m->tap) {
+            cudaMemcpyAsync(m->tap + (int64_t)i * T * H, m->X, T * H * 4, cudaMemcpyDeviceToDevice, s);
+        }
+    }
+
+    // ---- single-stream blocks over [txt ; img]
+    for (int i = 0; i < c.depth_single_blocks; ++i) {
+        const std::string p = "single_blocks." + std::to_string(i) + ".";
+        const float* sm = smods + (int64_t)i * 3 * H;   // shift scale gate
+        EDB_TRY(edb200_layernorm_modulate(m->X, H, sm, sm + H, nullptr, nullptr, T, H, 1e-6f, xmod, F16, H, s));
+        {
+            const Lin l1 = qlin(m, p + "linear1");
+            edb200_epilogue_t ep = make_ep(qkv, F16, 3 * H, l1.b);
+            ep.split_n = 3 * H;
+            ep.out2 = cat + H;
+            ep.out2_dtype = F16;
+            ep.ldo2 = H + M;
+            ep.act2 = EDB200_ACT_GELU_TANH;
+            EDB_TRY(edb200_mul_mat_q(l1.w, xmod, F16, T, H, &ep, s));
+        }
+        EDB_TRY(edb200_qk_norm_rope_pack(qkv, F16, 3 * H, 0, H, 2 * H, T, c.num_heads, d,
+                                         fparam(m, p + "norm.query_norm.scale"), fparam(m, p + "norm.key_norm.scale"),
+                                         1e-6f, m->PE, 0, T, m->Q, m->K, m->V, F16, s));
+        EDB_TRY(attention(m, T, cat, H + M, s));
+        {
+            const Lin l2 = qlin(m, p + "linear2");
+            edb200_epilogue_t ep = make_ep(m->X, EDB200_TYPE_F32, H, l2.b);
+            ep.residual = m->X, ep.ld_res = H, ep.gate = sm + 2 * H;
+            EDB_TRY(edb200_mul_mat_q(l2.w, cat, F16, T, H + M, &ep, s));
+        }
+        if (m->tap) {
+            cudaMemcpyAsync(m->tap + (int64_t)(c.depth + i) * T * H, m->X, T * H * 4, cudaMemcpyDeviceToDevice, s);
+        }
+    }
+
+    // ---- final layer on the image rows + unpatchify (LastLayer::forward, flux.hpp:3533-3559)
+    EDB_TRY(edb200_layernorm_modulate(X_img, H, fmods, fmods + H, nullptr, nullptr, n_img, H, 1e-6f, m->FIN,
+                                      EDB200_TYPE_F32, H, s));
+    EDB_TRY(dense(m, "final_layer.linear", m->FIN, n_img, H, 0, EDB200_ACT_NONE, m->TOK_OUT, c.in_channels, s));
+    launch_unpatchify(m->TOK_OUT, out, lat_c, m->lat_h, m->lat_w, c.patch_size, s);
+    return check_cuda(cudaGetLastError(), "flux_step");
+}
+
+edb200_status_t edb200_flux_compute_host(edb200_flux_t* m, const float* latent, int latent_h, int latent_w,
+                                         float timestep, const float* context, int n_txt, const float* y,
+                                         float guidance, float* out, void* stream) {
+    if (m == nullptr || latent == nullptr || context == nullptr || y == nullptr || out == nullptr) {
+        return fail(EDB200_ERR_INVALID, "flux_compute_host: null argument");
+    }
+    EDB_TRY(edb200_flux_prepare(m, latent_h, latent_w, n_txt, stream));
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const edb200_flux_config_t& c = m->cfg;
+    const int lat_c = c.in_channels / (c.patch_size * c.patch_size);
+    const int64_t lat_elems = (int64_t)lat_c * latent_h * latent_w;
+    const int64_t ctx_elems = (int64_t)n_txt * c.context_in_dim;
+    // stage through pinned memory so the copies are truly asynchronous
+    float* p_lat = m->pinned;
+    float* p_ctx = p_lat + lat_elems;
+    float* p_y = p_ctx + ctx_elems;
+    float* p_out = p_y + c.vec_in_dim;
+    memcpy(p_lat, latent, lat_elems * 4);
+    memcpy(p_ctx, context, ctx_elems * 4);
+    memcpy(p_y, y, (size_t)c.vec_in_dim * 4);
+    cudaError_t e = cudaMemcpyAsync(m->LAT_IN, p_lat, lat_elems * 4, cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(m->CTX, p_ctx, ctx_elems * 4, cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(m->YVEC, p_y, (size_t)c.vec_in_dim * 4, cudaMemcpyHostToDevice, s);
+    if (e != cudaSuccess) return check_cuda(e, "flux_compute_host H2D");
+    EDB_TRY(edb200_flux_step(m, m->LAT_IN, timestep, m->CTX, m->YVEC, guidance, m->LAT_OUT, stream));
+    e = cudaMemcpyAsync(p_out, m->LAT_OUT, lat_elems * 4, cudaMemcpyDeviceToHost, s);
+    if (e != cudaSuccess) return check_cuda(e, "flux_compute_host D2H");
+    EDB_TRY(poll_device_error(s));   // synchronises the stream
+    memcpy(out, p_out, lat_elems * 4);
+    return EDB200_OK;
+}
+
+}  // extern "C"

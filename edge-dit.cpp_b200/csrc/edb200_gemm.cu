@@ -590,6 +590,13 @@ static edb200_status_t launch_qgemm(int nprob, const edb200_qweight_t* const* ws
         if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(qgemm)");
         attr_set[q4 ? 1 : 0] = true;
     }
+    double flops = 0.0, bytes = 0.0;
+    for (int i = 0; i < nprob; ++i) {
+        flops += 2.0 * (double)ms[i] * (double)ws[i]->n_out * (double)ws[i]->k;
+        bytes += (double)ws[i]->bytes + 2.0 * (double)ms[i] * (double)ws[i]->k +
+                 (double)ms[i] * (double)ws[i]->n_out * (eps[i]->out_dtype == EDB200_TYPE_F32 ? 4.0 : 2.0);
+    }
+    ProfScope prof(stream, PROF_GEMM, flops, bytes);
     kern<<<grid, gemm::NUM_THREADS, gemm::SMEM_BYTES, stream>>>(
         map_a[0], ws[0]->map_qs, ws[0]->map_sa, q4 ? ws[0]->map_sb : ws[0]->map_sa, map_a[1], w1->map_qs, w1->map_sa,
         q4 ? w1->map_sb : w1->map_sa, P);

@@ -39,6 +39,27 @@ edb200_status_t make_tmap_3d(CUtensorMap* map, CUtensorMapDataType dt, int elem_
 
 int sm_count();
 
+// Optional per-kernel-class timing (off by default).  While enabled every
+// launch site brackets its kernel with two CUDA events on the launching stream
+// and records the algorithmic work; edb200_profile_end sums them per class.
+enum ProfClass { PROF_GEMM = 0, PROF_ATTENTION = 1, PROF_GEMV = 2, PROF_ELEMENTWISE = 3, PROF_OTHER = 4, PROF_NCLASS = 5 };
+bool profiling_enabled();
+void profile_begin_launch(cudaStream_t s);
+void profile_end_launch(cudaStream_t s, ProfClass cls, double flops, double bytes);
+
+struct ProfScope {
+    cudaStream_t s;
+    ProfClass cls;
+    double flops, bytes;
+    bool on;
+    ProfScope(cudaStream_t stream, ProfClass c, double f, double b) : s(stream), cls(c), flops(f), bytes(b), on(profiling_enabled()) {
+        if (on) profile_begin_launch(s);
+    }
+    ~ProfScope() {
+        if (on) profile_end_launch(s, cls, flops, bytes);
+    }
+};
+
 }  // namespace edb
 
 // Repacked quantised weight (device resident).

@@ -1,0 +1,79 @@
+// Host-side building blocks shared by the per-family denoise-step executors:
+// a named parameter table (quantised weights repacked for the GEMM, f32 vectors
+// as plain device arrays) and a bump allocator for the step's activations.
+#pragma once
+
+#include <map>
+#include <string>
+#include <vector>
+
+#include "edb200_internal.h"
+
+namespace edb {
+
+struct ParamSpec {
+    std::string name;
+    int64_t n_out = 0;   // rows (1 for vectors)
+    int64_t k = 0;       // row length
+    bool quantised = false;
+    int ggml_type = EDB200_TYPE_F32;  // storage type expected by set_tensor
+};
+
+struct Param {
+    ParamSpec spec;
+    edb200_qweight_t* qw = nullptr;  // quantised linear weight
+    float* f32 = nullptr;            // everything else
+    bool loaded = false;
+};
+
+// Raw bytes of `rows` rows of `k` weights in a ggml type.
+int64_t ggml_row_bytes(int ggml_type, int64_t k);
+
+class ParamTable {
+public:
+    ~ParamTable();
+    void add(const std::string& name, int64_t n_out, int64_t k, bool quantised, int wtype);
+    Param* find(const std::string& name);
+    const Param* get(const std::string& name) const;
+    // Upload one tensor (host or device source) and, for quantised weights, repack it.
+    edb200_status_t set(const std::string& name, int ggml_type, const void* data, int64_t nbytes, bool on_device,
+                        cudaStream_t stream);
+    // Synthetic weights generated on the device: N(0, std) (norm scales 1 + N(0, std)),
+    // quantised with the device q8_0 / q4_K encoders.
+    edb200_status_t init_random(uint64_t seed, float std, cudaStream_t stream);
+    edb200_status_t all_loaded() const;
+    int64_t device_bytes() const { return bytes_; }
+    std::vector<Param>& params() { return params_; }
+
+private:
+    std::vector<Param> params_;
+    std::map<std::string, size_t> index_;
+    int64_t bytes_ = 0;
+};
+
+// One cudaMalloc carved into 256-byte aligned pieces.
+class Workspace {
+public:
+    ~Workspace();
+    edb200_status_t reserve(int64_t bytes);
+    void* take(int64_t bytes);   // nullptr when exhausted
+    template <typename T>
+    T* take_n(int64_t n) { return static_cast<T*>(take(n * (int64_t)sizeof(T))); }
+    int64_t capacity() const { return cap_; }
+    int64_t used() const { return used_; }
+
+private:
+    char* base_ = nullptr;
+    int64_t cap_ = 0, used_ = 0;
+};
+
+// Small kernels used by the executors (defined in edb200_model.cu).
+void launch_patchify(const float* latent, float* tokens, int C, int H, int W, int p, cudaStream_t s);
+void launch_unpatchify(const float* tokens, float* latent, int C, int H, int W, int p, cudaStream_t s);
+// out[j] = cos((t*freq[j])*scale), out[half+j] = sin(...); freq is a device table of `half` floats.
+void launch_timestep_embedding(const float* freq, float t, float scale, int half, float* out, cudaStream_t s);
+void launch_add_inplace(float* dst, const float* src, int64_t n, cudaStream_t s);
+// Device q4_K encoder used for synthetic weights (min/max per 32 sub-block).
+edb200_status_t quantize_rows_q4_k_device(const float* x, void* blocks, int64_t rows, int64_t k, cudaStream_t s);
+
+}  // namespace edb

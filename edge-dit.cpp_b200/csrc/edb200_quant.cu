@@ -381,6 +381,7 @@ static edb200_status_t launch_gemv_q(const edb200_qweight_t* w, const float* x, 
     const int rows_per_cta = GEMV_ROWS_PER_WARP * GEMV_WARPS;
     const int grid = static_cast<int>((w->n_out + rows_per_cta - 1) / rows_per_cta);
     const size_t smem = static_cast<size_t>(m) * w->k * sizeof(float);
+    ProfScope prof(stream, PROF_GEMV, 2.0 * (double)m * (double)w->n_out * (double)w->k, (double)w->bytes);
 #define EDB_GEMV_CASE(MM)                                                                                           \
     case MM: {                                                                                                      \
         auto kern = gemv_q_kernel<WT, MM>;                                                                          \
@@ -582,6 +583,7 @@ edb200_status_t edb200_linear_f32(const float* w, const float* bias, const float
         return fail(EDB200_ERR_INVALID, "linear_f32: null or empty argument");
     }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    ProfScope prof(s, PROF_OTHER, 2.0 * (double)m * (double)n * (double)k, 4.0 * ((double)n * k + (double)m * (k + n)));
     if (m <= 8 && (k % 4) == 0 && (reinterpret_cast<uintptr_t>(w) & 15u) == 0 && m * k * 4 <= 160 * 1024) {
         const size_t smem = static_cast<size_t>(m) * k * 4;
         const int grid = static_cast<int>((n + 7) / 8);

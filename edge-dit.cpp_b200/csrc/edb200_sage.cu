@@ -150,6 +150,8 @@ static edb200_status_t quantize(const __half* q, const __half* k, int hn, int l,
                                 const Layout& lo, cudaStream_t s) {
     float* qm = reinterpret_cast<float*>(scratch + lo.qm);
     float* km = reinterpret_cast<float*>(scratch + lo.km);
+    // algorithmic traffic: read q,k (f16) for the means, again for the quantisers, k once more for the bias; write int8
+    ProfScope prof(s, PROF_ELEMENTWISE, 0.0, (double)hn * l * D * (smooth_q ? 13.0 : 8.0));
     channel_mean_kernel<D><<<hn, D, 0, s>>>(k, km, l);
     if (smooth_q) channel_mean_kernel<D><<<hn, D, 0, s>>>(q, qm, l);
     const int lpad = (l + 127) / 128 * 128;

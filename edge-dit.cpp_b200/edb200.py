@@ -29,6 +29,18 @@ class Epilogue(C.Structure):
     ]
 
 
+class FluxConfig(C.Structure):
+    _fields_ = [
+        ("hidden_size", C.c_int), ("num_heads", C.c_int), ("depth", C.c_int), ("depth_single_blocks", C.c_int),
+        ("mlp_hidden", C.c_int), ("in_channels", C.c_int), ("context_in_dim", C.c_int), ("vec_in_dim", C.c_int),
+        ("patch_size", C.c_int), ("axes_dim", C.c_int * 3), ("theta", C.c_int), ("guidance_embed", C.c_int),
+        ("wtype", C.c_int), ("attention", C.c_int), ("sage_smooth_q", C.c_int),
+    ]
+
+
+ATTN_F16, ATTN_SAGE_INT8 = 0, 1
+
+
 class EdbError(RuntimeError):
     def __init__(self, status: int, msg: str):
         super().__init__(f"edb200 status {status}: {msg}")
@@ -39,6 +51,9 @@ _SIGS = {
     "edb200_last_error": (C.c_char_p, []),
     "edb200_version": (C.c_char_p, []),
     "edb200_launch_count": (c_i64, []),
+    "edb200_profile_begin": (C.c_int, []),
+    "edb200_profile_end": (C.c_int, [C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_double),
+                                     C.POINTER(c_i64)]),
     "edb200_dequantize_rows": (C.c_int, [C.c_int, c_vp, c_vp, c_i64, c_i64, c_vp]),
     "edb200_quantize_rows_q8_0": (C.c_int, [c_vp, c_vp, c_i64, c_i64, c_vp]),
     "edb200_fill_normal": (C.c_int, [c_vp, c_i64, C.c_uint64, C.c_float, C.c_float, c_vp]),
@@ -69,6 +84,20 @@ _SIGS = {
                                              c_i64, C.c_int, C.c_float, c_vp, C.c_int, c_i64, c_vp]),
     "edb200_sage_attention": (C.c_int, [c_vp, c_vp, c_vp, C.c_int, c_i64, C.c_int, C.c_float, C.c_int, c_vp, c_i64,
                                         c_vp, C.c_int, c_i64, c_vp]),
+    "edb200_flux_create": (C.c_int, [C.POINTER(FluxConfig), C.POINTER(c_vp)]),
+    "edb200_flux_destroy": (None, [c_vp]),
+    "edb200_flux_tensor_count": (C.c_int, [c_vp]),
+    "edb200_flux_tensor_info": (C.c_int, [c_vp, C.c_int, C.c_char_p, C.c_int, C.POINTER(C.c_int), C.POINTER(c_i64),
+                                          C.POINTER(c_i64), C.POINTER(c_i64)]),
+    "edb200_flux_set_tensor": (C.c_int, [c_vp, C.c_char_p, C.c_int, c_vp, c_i64, C.c_int, c_vp]),
+    "edb200_flux_init_random": (C.c_int, [c_vp, C.c_uint64, C.c_float, c_vp]),
+    "edb200_flux_weight_bytes": (c_i64, [c_vp]),
+    "edb200_flux_workspace_bytes": (c_i64, [c_vp]),
+    "edb200_flux_prepare": (C.c_int, [c_vp, C.c_int, C.c_int, C.c_int, c_vp]),
+    "edb200_flux_set_tap": (C.c_int, [c_vp, c_vp]),
+    "edb200_flux_step": (C.c_int, [c_vp, c_vp, C.c_float, c_vp, c_vp, C.c_float, c_vp, c_vp]),
+    "edb200_flux_compute_host": (C.c_int, [c_vp, c_vp, C.c_int, C.c_int, C.c_float, c_vp, C.c_int, c_vp, C.c_float,
+                                           c_vp, c_vp]),
 }
 
 _lib = None
@@ -150,3 +179,84 @@ def make_epilogue(out, bias=None, act=ACT_NONE, residual=None, gate=None, split_
 def mul_mat_q(w: QWeight, x, ep: Epilogue):
     check(lib().edb200_mul_mat_q(w.handle, ptr(x), torch_dtype_id(x), x.shape[0], x.stride(0), C.byref(ep),
                                  current_stream()))
+
+
+class FluxModel:
+    """Thin owner of an edb200_flux_t: the host-side mirror of the reference's
+    FluxModel adapter (src/dit_models/diffusion_model.hpp) over the C ABI."""
+
+    def __init__(self, hidden_size=3072, num_heads=24, depth=19, depth_single_blocks=38, mlp_hidden=None,
+                 in_channels=64, context_in_dim=4096, vec_in_dim=768, patch_size=2, axes_dim=(16, 56, 56),
+                 theta=10000, guidance_embed=True, wtype=TYPE_Q8_0, attention=ATTN_SAGE_INT8, sage_smooth_q=True):
+        cfg = FluxConfig()
+        cfg.hidden_size, cfg.num_heads, cfg.depth, cfg.depth_single_blocks = hidden_size, num_heads, depth, depth_single_blocks
+        cfg.mlp_hidden = mlp_hidden if mlp_hidden is not None else 4 * hidden_size
+        cfg.in_channels, cfg.context_in_dim, cfg.vec_in_dim, cfg.patch_size = in_channels, context_in_dim, vec_in_dim, patch_size
+        cfg.axes_dim = (C.c_int * 3)(*axes_dim)
+        cfg.theta, cfg.guidance_embed, cfg.wtype = theta, int(guidance_embed), wtype
+        cfg.attention, cfg.sage_smooth_q = attention, int(sage_smooth_q)
+        self.cfg = cfg
+        h = c_vp()
+        check(lib().edb200_flux_create(C.byref(cfg), C.byref(h)))
+        self.handle = h
+
+    def __del__(self):
+        if getattr(self, "handle", None) and _lib is not None:
+            _lib.edb200_flux_destroy(self.handle)
+            self.handle = None
+
+    def tensors(self):
+        out = []
+        n = lib().edb200_flux_tensor_count(self.handle)
+        buf = C.create_string_buffer(256)
+        t, no, k, nb = C.c_int(), c_i64(), c_i64(), c_i64()
+        for i in range(n):
+            check(lib().edb200_flux_tensor_info(self.handle, i, buf, 256, C.byref(t), C.byref(no), C.byref(k), C.byref(nb)))
+            out.append((buf.value.decode(), t.value, no.value, k.value, nb.value))
+        return out
+
+    def load_numpy(self, weights: dict):
+        """weights: {name: (ggml_type, ndarray)} as produced by oracle.flux_oracle.flux_make_weights."""
+        import numpy as np
+        for name, (t, arr) in weights.items():
+            a = np.ascontiguousarray(arr)
+            check(lib().edb200_flux_set_tensor(self.handle, name.encode(), t, a.ctypes.data_as(c_vp), a.nbytes, 0,
+                                               current_stream()))
+
+    def init_random(self, seed=0, std=0.02):
+        check(lib().edb200_flux_init_random(self.handle, seed, std, current_stream()))
+
+    def prepare(self, latent_h, latent_w, n_txt):
+        check(lib().edb200_flux_prepare(self.handle, latent_h, latent_w, n_txt, current_stream()))
+
+    def step(self, latent, timestep, context, y, guidance, out):
+        check(lib().edb200_flux_step(self.handle, ptr(latent), timestep, ptr(context), ptr(y), guidance, ptr(out),
+                                     current_stream()))
+
+    def compute_host(self, latent, timestep, context, y, guidance):
+        """numpy f32 in, numpy f32 out; host<->device copies happen inside the call."""
+        import numpy as np
+        latent = np.ascontiguousarray(latent, dtype=np.float32)
+        context = np.ascontiguousarray(context, dtype=np.float32)
+        y = np.ascontiguousarray(y, dtype=np.float32)
+        out = np.empty_like(latent)
+        check(lib().edb200_flux_compute_host(self.handle, latent.ctypes.data_as(c_vp), latent.shape[1], latent.shape[2],
+                                             timestep, context.ctypes.data_as(c_vp), context.shape[0],
+                                             y.ctypes.data_as(c_vp), guidance, out.ctypes.data_as(c_vp),
+                                             current_stream()))
+        return out
+
+
+PROF_CLASSES = ("gemm", "attention", "gemv", "elementwise", "other")
+
+
+def profile_begin():
+    check(lib().edb200_profile_begin())
+
+
+def profile_end():
+    ms, fl, by = (C.c_double * 5)(), (C.c_double * 5)(), (C.c_double * 5)()
+    n = (c_i64 * 5)()
+    check(lib().edb200_profile_end(ms, fl, by, n))
+    return {name: {"ms": ms[i], "flops": fl[i], "bytes": by[i], "launches": n[i]}
+            for i, name in enumerate(PROF_CLASSES)}

@@ -57,6 +57,16 @@ EDB200_API const char* edb200_version(void);
 /* Number of kernels this library has launched in the calling process. */
 EDB200_API int64_t edb200_launch_count(void);
 
+/* Per-kernel-class timing for measurement runs.  Between begin and end every
+ * kernel launch of this library is bracketed by CUDA events on its stream;
+ * end synchronises the device and fills arrays of 5 entries indexed by class
+ * {0 quantised GEMM, 1 attention, 2 GEMV, 3 memory-bound ops, 4 other} with the
+ * summed device time (ms), algorithmic FLOPs, algorithmic bytes and launch
+ * counts.  Counterpart of ED_PROFILE_RUNNER / ED_PROFILE_FLUX
+ * (src/core/backend/ggml/ggml_extend.hpp:2842, src/dit_models/models/flux.hpp:82-95). */
+EDB200_API edb200_status_t edb200_profile_begin(void);
+EDB200_API edb200_status_t edb200_profile_end(double* ms, double* flops, double* bytes, int64_t* launches);
+
 /* ------------------------------------------------------------------ codecs
  * ggml block codecs on the device.  Stand in for ggml_quantize_chunk /
  * type_traits->to_float as called from src/core/runtime/model_loader.cpp:663-704. */
@@ -218,6 +228,69 @@ EDB200_API edb200_status_t edb200_sage_attention(const void* q_f16, const void* 
                                                  int64_t l, int d_head, float scale, int smooth_q, void* scratch,
                                                  int64_t scratch_bytes, void* out, int out_dtype, int64_t ld_out,
                                                  void* stream);
+
+/* ------------------------------------------------- FLUX.1 denoise-step model
+ * A whole-step replacement at the reference's model seam
+ * DiffusionModel::compute(n_threads, DiffusionParams) -> sd::Tensor<float>
+ * (src/dit_models/diffusion_model.hpp:67-70) for FluxModel / FluxRunner::compute
+ * (src/dit_models/models/flux.hpp:5158-5296).  Field names follow FluxParams
+ * (src/dit_models/models/flux.hpp:3717-3745). */
+enum { EDB200_ATTN_F16 = 0, EDB200_ATTN_SAGE_INT8 = 1 };
+
+typedef struct {
+    int hidden_size;          /* 3072 */
+    int num_heads;            /* 24 */
+    int depth;                /* double-stream blocks, 19 */
+    int depth_single_blocks;  /* 38 */
+    int mlp_hidden;           /* hidden_size * mlp_ratio, 12288 */
+    int in_channels;          /* latent channels * patch^2, 64 */
+    int context_in_dim;       /* 4096 */
+    int vec_in_dim;           /* 768 */
+    int patch_size;           /* 2 */
+    int axes_dim[3];          /* RoPE axes, (16, 56, 56) */
+    int theta;                /* 10000 */
+    int guidance_embed;       /* 1 for FLUX.1-dev */
+    int wtype;                /* EDB200_TYPE_Q8_0 or EDB200_TYPE_Q4_K */
+    int attention;            /* EDB200_ATTN_* (ED_SAGE_ATTN in the reference) */
+    int sage_smooth_q;        /* ED_SAGE_SMOOTH_Q */
+} edb200_flux_config_t;
+
+typedef struct edb200_flux edb200_flux_t;
+
+EDB200_API edb200_status_t edb200_flux_create(const edb200_flux_config_t* cfg, edb200_flux_t** out);
+EDB200_API void edb200_flux_destroy(edb200_flux_t* m);
+/* Parameter table: names are the reference's tensor names without the
+ * "model.diffusion_model." prefix (e.g. "double_blocks.0.img_attn.qkv.weight").
+ * Stands in for GGMLRunner::get_param_tensors (src/core/backend/ggml/ggml_extend.hpp). */
+EDB200_API int edb200_flux_tensor_count(const edb200_flux_t* m);
+EDB200_API edb200_status_t edb200_flux_tensor_info(const edb200_flux_t* m, int index, char* name, int name_cap,
+                                                   int* ggml_type, int64_t* n_out, int64_t* k, int64_t* nbytes);
+/* Upload one tensor from host (on_device = 0) or device memory: raw ggml blocks
+ * for quantised weights, f32 for everything else. */
+EDB200_API edb200_status_t edb200_flux_set_tensor(edb200_flux_t* m, const char* name, int ggml_type, const void* data,
+                                                  int64_t nbytes, int on_device, void* stream);
+/* Synthetic weights N(0, std) generated and quantised on the device. */
+EDB200_API edb200_status_t edb200_flux_init_random(edb200_flux_t* m, uint64_t seed, float std, void* stream);
+EDB200_API int64_t edb200_flux_weight_bytes(const edb200_flux_t* m);
+EDB200_API int64_t edb200_flux_workspace_bytes(const edb200_flux_t* m);
+/* Allocate the activation workspace and build the RoPE table for one
+ * (latent height, latent width, text tokens) shape; a no-op when unchanged. */
+EDB200_API edb200_status_t edb200_flux_prepare(edb200_flux_t* m, int latent_h, int latent_w, int n_txt, void* stream);
+/* Optional debug tap: after block b (double blocks first) the f32 residual
+ * stream [n_txt + n_img, hidden] is copied to tap + b * T * hidden.  NULL disables. */
+EDB200_API edb200_status_t edb200_flux_set_tap(edb200_flux_t* m, float* tap);
+/* One denoise step on device-resident tensors, asynchronous on `stream`:
+ * latent/out f32 [C, H, W]; context f32 [n_txt, context_in_dim]; y f32 [vec_in_dim];
+ * timestep and guidance as the reference passes them (sigma in 0..1, guidance scale). */
+EDB200_API edb200_status_t edb200_flux_step(edb200_flux_t* m, const float* latent, float timestep,
+                                            const float* context, const float* y, float guidance, float* out,
+                                            void* stream);
+/* The same step with host tensors in and out (the reference's compute seam):
+ * prepares the shape if needed, copies through pinned staging, runs the step,
+ * copies the result back and synchronises. */
+EDB200_API edb200_status_t edb200_flux_compute_host(edb200_flux_t* m, const float* latent, int latent_h, int latent_w,
+                                                    float timestep, const float* context, int n_txt, const float* y,
+                                                    float guidance, float* out, void* stream);
 
 #ifdef __cplusplus
 }

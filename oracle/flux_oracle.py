@@ -113,6 +113,26 @@ def flux_make_weights(cfg: FluxConfig, seed: int = 0, std: float = 0.02):
     return out
 
 
+def flux_timing_weights(cfg: FluxConfig, seed: int = 0, std: float = 0.02, prefixes=("double_blocks.0.", "single_blocks.0.")):
+    """f32 weights for CPU *timing* only: uniform values of standard deviation
+    `std`, no quantisation round trip, only the tensors whose names start with
+    one of `prefixes`.  Values do not matter for a timing run; skipping the
+    normal generator and the block codec keeps the set-up to a few seconds."""
+    rng = np.random.default_rng(seed)
+    half = np.float32(std * 3.0 ** 0.5)
+    out = {}
+    for name, shape, _ in flux_tensor_specs(cfg):
+        if not name.startswith(tuple(prefixes)):
+            continue
+        w = rng.random(shape, dtype=np.float32)
+        w *= 2 * half
+        w -= half
+        if name.endswith(".scale"):
+            w += np.float32(1.0)
+        out[name] = (O.GGML_TYPE_F32, w)
+    return out
+
+
 class FluxOracle:
     def __init__(self, cfg: FluxConfig, weights: dict):
         self.cfg = cfg

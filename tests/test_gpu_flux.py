@@ -1,0 +1,112 @@
+"""GPU parity of the FLUX denoise-step executor against the numpy oracle.
+
+Tolerances are the ones the task states for this path: per-block output cosine
+>= 0.999 and relative L2 <= 1e-2, full-step latent relative L2 <= 2e-2, against
+the fp32 non-Sage CPU path on the same quantised weight bytes.
+"""
+import numpy as np
+import pytest
+
+from oracle import edb_oracle as O
+from oracle.flux_oracle import FluxConfig, FluxOracle, flux_make_weights
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+BLOCK_COS, BLOCK_REL, STEP_REL = 0.999, 1e-2, 2e-2
+
+
+def _inputs(cfg, lat_hw, n_txt, seed):
+    rng = np.random.default_rng(seed)
+    latent = rng.standard_normal((cfg.in_channels // 4, lat_hw[0], lat_hw[1]), dtype=np.float32)
+    ctx = rng.standard_normal((n_txt, cfg.context_in_dim), dtype=np.float32)
+    y = rng.standard_normal(cfg.vec_in_dim, dtype=np.float32)
+    return latent, ctx, y
+
+
+def _run_case(edb, cuda, cfg, lat_hw, n_txt, attention, seed=0):
+    weights = flux_make_weights(cfg, seed)
+    latent, ctx, y = _inputs(cfg, lat_hw, n_txt, seed + 100)
+    taps = {}
+    ref = FluxOracle(cfg, weights).forward(latent, 0.5, ctx, y, 3.5, taps)
+
+    model = edb.FluxModel(hidden_size=cfg.hidden_size, num_heads=cfg.num_heads, depth=cfg.depth,
+                          depth_single_blocks=cfg.depth_single_blocks, mlp_hidden=cfg.mlp_hidden,
+                          in_channels=cfg.in_channels, context_in_dim=cfg.context_in_dim, vec_in_dim=cfg.vec_in_dim,
+                          axes_dim=cfg.axes_dim, wtype=cfg.wtype, attention=attention)
+    names = {t[0] for t in model.tensors()}
+    assert names == set(weights)                      # same parameter table as the reference's tensor names
+    model.load_numpy(weights)
+    model.prepare(lat_hw[0], lat_hw[1], n_txt)
+    n_img = (lat_hw[0] // 2) * (lat_hw[1] // 2)
+    T = n_txt + n_img
+    nblk = cfg.depth + cfg.depth_single_blocks
+    tap = torch.zeros(nblk, T, cfg.hidden_size, dtype=torch.float32, device=cuda)
+    edb.check(edb.lib().edb200_flux_set_tap(model.handle, edb.ptr(tap)))
+    d_lat, d_ctx, d_y = (torch.from_numpy(a).to(cuda) for a in (latent, ctx, y))
+    d_out = torch.zeros_like(d_lat)
+    model.step(d_lat, 0.5, d_ctx, d_y, 3.5, d_out)
+    torch.cuda.synchronize()
+    got_taps = tap.cpu().numpy()
+    got = d_out.cpu().numpy()
+    assert np.isfinite(got).all()
+
+    report = []
+    for i in range(cfg.depth):
+        want = np.concatenate([taps[f"double{i}.txt"], taps[f"double{i}.img"]], axis=0)
+        report.append((f"double{i}", O.cosine(got_taps[i], want), O.rel_l2(got_taps[i], want)))
+    for i in range(cfg.depth_single_blocks):
+        want = taps[f"single{i}.x"]
+        g = got_taps[cfg.depth + i]
+        report.append((f"single{i}", O.cosine(g, want), O.rel_l2(g, want)))
+    for name, cos, rel in report:
+        assert cos >= BLOCK_COS and rel <= BLOCK_REL, (name, cos, rel, report)
+    step_rel = O.rel_l2(got, ref)
+    assert step_rel <= STEP_REL, (step_rel, report)
+
+    # the host-tensor entry point (copies inside) returns the same result
+    edb.check(edb.lib().edb200_flux_set_tap(model.handle, None))
+    host = model.compute_host(latent, 0.5, ctx, y, 3.5)
+    assert np.array_equal(host, got)
+    return report, step_rel
+
+
+@pytest.mark.parametrize("attention", ["f16", "sage"])
+def test_flux_small_step_parity(edb, cuda, attention):
+    cfg = FluxConfig(hidden_size=512, num_heads=4, depth=2, depth_single_blocks=2, context_in_dim=256, vec_in_dim=64)
+    att = edb.ATTN_F16 if attention == "f16" else edb.ATTN_SAGE_INT8
+    _run_case(edb, cuda, cfg, (32, 32), 40, att)
+
+
+def test_flux_q4_k_step_parity(edb, cuda):
+    cfg = FluxConfig(hidden_size=512, num_heads=4, depth=1, depth_single_blocks=2, context_in_dim=256, vec_in_dim=64,
+                     wtype=O.GGML_TYPE_Q4_K)
+    _run_case(edb, cuda, cfg, (16, 48), 24, edb.ATTN_SAGE_INT8, seed=3)
+
+
+def test_flux_full_width_block_parity(edb, cuda):
+    # FLUX.1 layer widths (hidden 3072, 24 heads x 128, mlp 12288, context 4096) with one block of each kind
+    cfg = FluxConfig(depth=1, depth_single_blocks=1)
+    _run_case(edb, cuda, cfg, (32, 48), 77, edb.ATTN_SAGE_INT8, seed=5)
+
+
+def test_flux_head_dim_64(edb, cuda):
+    cfg = FluxConfig(hidden_size=256, num_heads=4, depth=1, depth_single_blocks=1, context_in_dim=128, vec_in_dim=32,
+                     axes_dim=(16, 24, 24))
+    _run_case(edb, cuda, cfg, (16, 16), 8, edb.ATTN_F16, seed=7)
+
+
+def test_flux_rejects_unset_weights_and_bad_shapes(edb, cuda):
+    model = edb.FluxModel(hidden_size=512, num_heads=4, depth=1, depth_single_blocks=1, context_in_dim=256,
+                          vec_in_dim=64)
+    with pytest.raises(edb.EdbError):
+        model.prepare(31, 32, 8)                       # latent not a multiple of the patch size
+    model.prepare(32, 32, 8)
+    z = torch.zeros(16, 32, 32, device=cuda)
+    c = torch.zeros(8, 256, device=cuda)
+    y = torch.zeros(64, device=cuda)
+    with pytest.raises(edb.EdbError) as ei:
+        model.step(z, 0.5, c, y, 3.5, z.clone())
+    assert "has not been set" in str(ei.value)
+    with pytest.raises(edb.EdbError):
+        edb.FluxModel(hidden_size=500, num_heads=4)    # width not a multiple of 256
