@@ -275,13 +275,14 @@ def run_ours(args):
 
     # end to end through the host-tensor entry point
     h_lat, h_ctx, h_y = latent.cpu().numpy(), ctx.cpu().numpy(), y.cpu().numpy()
-    for _ in range(min(2, args.warmup)):
+    n_e2e = 1 if args.kernel_only else args.steps
+    for _ in range(0 if args.kernel_only else min(2, args.warmup)):
         model.compute_host(h_lat, 0.5, h_ctx, h_y, 3.5)
     barrier()
     t0 = time.perf_counter()
-    for _ in range(args.steps):
+    for _ in range(n_e2e):
         h_out = model.compute_host(h_lat, 0.5, h_ctx, h_y, 3.5)
-    e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / n_e2e
     barrier()
 
     # per-class device time of one extra step (CUDA events around every launch)
@@ -314,7 +315,10 @@ def run_ours(args):
     classes["attention"]["tflops"] = round(att_tflops, 1)
     classes["gemv"]["gbs"] = round(gemv["bytes"] / (gemv["ms"] * 1e-3) / 1e9, 1) if gemv["ms"] > 0 else 0.0
 
-    cpu_ms, cores, sample = cpu_sample(args.workload, args.cpu_budget)
+    if args.kernel_only:
+        cpu_ms, cores, sample = None, 0, "skipped (--kernel-only)"
+    else:
+        cpu_ms, cores, sample = cpu_sample(args.workload, args.cpu_budget)
     h2d = h_lat.nbytes + h_ctx.nbytes + h_y.nbytes
     line = {
         "metric": METRIC, "value": ms, "unit": "ms", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -347,6 +351,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="flux1024_q8_0", choices=sorted(WORKLOADS))
     ap.add_argument("--attention", default="sage", choices=["sage", "f16"])
+    ap.add_argument("--kernel-only", action="store_true",
+                    help="short run for profilers: one e2e call, no cpu_baseline leg")
     ap.add_argument("--cpu-budget", type=float, default=15.0, help="seconds of CPU work for the cpu_baseline sample")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
