@@ -173,7 +173,8 @@ edb200_status_t attention(edb200_flux* m, int64_t T, void* out, int64_t ld_out, 
     const int d = c.hidden_size / c.num_heads;
     const float scale = 1.0f / std::sqrt(static_cast<float>(d));
     if (c.attention == EDB200_ATTN_SAGE_INT8) {
-        return edb200_sage_attention(m->Q, m->K, m->V, c.num_heads, T, d, scale, c.sage_smooth_q, m->SAGE,
+        return edb200_sage_attention(m->Q, m->K, m->V, c.num_heads, T, d, scale,
+                                     (c.sage_smooth_q ? EDB200_SAGE_SMOOTH_Q : 0) | EDB200_SAGE_FAST_MEANS, m->SAGE,
                                      m->sage_bytes, out, EDB200_TYPE_F16, ld_out, s);
     }
     return edb200_attention_f16(m->Q, m->K, m->V, c.num_heads, T, T, d, scale, out, EDB200_TYPE_F16, ld_out, s);

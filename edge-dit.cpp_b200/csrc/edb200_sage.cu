@@ -40,6 +40,49 @@ channel_mean_kernel(const __half* __restrict__ x, float* __restrict__ mean, int 
     mean[hn * D + d] = __fdiv_rn(sum, static_cast<float>(L));
 }
 
+// Fast (not bit-compatible) channel means: the token axis is cut into chunks of
+// kMeanChunk rows that are summed in parallel, then the chunk sums are added in
+// chunk order.  Deterministic, but the f32 rounding differs from the sequential
+// sum above, so the means can differ in the last bits.  Any vector subtracted
+// from K cancels in the softmax, and the smooth-Q bias compensates the Q mean
+// exactly, so attention results are unaffected beyond rounding.
+constexpr int kMeanChunk = 128;
+
+template <int D>
+__global__ void __launch_bounds__(D)
+channel_partial_kernel(const __half* __restrict__ q, const __half* __restrict__ k, float* __restrict__ part_q,
+                       float* __restrict__ part_k, int L, int n_chunks) {
+    const int hn = blockIdx.x, chunk = blockIdx.y, d = threadIdx.x;
+    const __half* x = blockIdx.z == 0 ? k : q;
+    float* part = blockIdx.z == 0 ? part_k : part_q;
+    const int t0 = chunk * kMeanChunk;
+    const int t1 = min(L, t0 + kMeanChunk);
+    const __half* p = x + (int64_t)hn * L * D + d;
+    float s[4] = {0.f, 0.f, 0.f, 0.f};
+    int t = t0;
+    for (; t + 16 <= t1; t += 16) {
+        float v[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] = __half2float(p[(int64_t)(t + i) * D]);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) s[i & 3] += v[i];
+    }
+    for (; t < t1; ++t) s[0] += __half2float(p[(int64_t)t * D]);
+    part[((int64_t)hn * n_chunks + chunk) * D + d] = (s[0] + s[1]) + (s[2] + s[3]);
+}
+
+template <int D>
+__global__ void __launch_bounds__(D)
+channel_finalize_kernel(const float* __restrict__ part_q, const float* __restrict__ part_k, float* __restrict__ qm,
+                        float* __restrict__ km, int L, int n_chunks) {
+    const int hn = blockIdx.x, d = threadIdx.x;
+    const float* part = blockIdx.y == 0 ? part_k : part_q;
+    float* mean = blockIdx.y == 0 ? km : qm;
+    float s = 0.0f;
+    for (int c = 0; c < n_chunks; ++c) s += part[((int64_t)hn * n_chunks + c) * D + d];
+    mean[hn * D + d] = s / static_cast<float>(L);
+}
+
 // One CTA (128 threads) per (token block, head).  BLK tokens share one scale.
 template <int D, int BLK>
 __global__ void __launch_bounds__(128)
@@ -115,8 +158,8 @@ smooth_q_bias_kernel(const __half* __restrict__ k, const float* __restrict__ qm,
 }
 
 struct Layout {
-    int64_t q8, k8, q_scale, k_scale, qm, km, bias, total;
-    int q_scale_stride, k_scale_stride, bias_stride;
+    int64_t q8, k8, q_scale, k_scale, qm, km, bias, part_q, part_k, total;
+    int q_scale_stride, k_scale_stride, bias_stride, n_chunks;
 };
 
 static Layout make_layout(int hn, int64_t l, int d) {
@@ -141,19 +184,35 @@ static Layout make_layout(int hn, int64_t l, int d) {
     off = align(off + (int64_t)hn * d * 4);
     lo.bias = off;
     off = align(off + (int64_t)hn * lo.bias_stride * 4);
+    lo.n_chunks = static_cast<int>(lpad / kMeanChunk);
+    lo.part_q = off;
+    off = align(off + (int64_t)hn * lo.n_chunks * d * 4);
+    lo.part_k = off;
+    off = align(off + (int64_t)hn * lo.n_chunks * d * 4);
     lo.total = off;
     return lo;
 }
 
 template <int D>
-static edb200_status_t quantize(const __half* q, const __half* k, int hn, int l, bool smooth_q, char* scratch,
-                                const Layout& lo, cudaStream_t s) {
+static edb200_status_t quantize(const __half* q, const __half* k, int hn, int l, bool smooth_q, bool fast_means,
+                                char* scratch, const Layout& lo, cudaStream_t s) {
     float* qm = reinterpret_cast<float*>(scratch + lo.qm);
     float* km = reinterpret_cast<float*>(scratch + lo.km);
     // algorithmic traffic: read q,k (f16) for the means, again for the quantisers, k once more for the bias; write int8
     ProfScope prof(s, PROF_ELEMENTWISE, 0.0, (double)hn * l * D * (smooth_q ? 13.0 : 8.0));
-    channel_mean_kernel<D><<<hn, D, 0, s>>>(k, km, l);
-    if (smooth_q) channel_mean_kernel<D><<<hn, D, 0, s>>>(q, qm, l);
+    int launches = 0;
+    if (fast_means) {
+        float* pq = reinterpret_cast<float*>(scratch + lo.part_q);
+        float* pk = reinterpret_cast<float*>(scratch + lo.part_k);
+        const int nc = (l + kMeanChunk - 1) / kMeanChunk;
+        channel_partial_kernel<D><<<dim3(hn, nc, smooth_q ? 2 : 1), D, 0, s>>>(q, k, pq, pk, l, nc);
+        channel_finalize_kernel<D><<<dim3(hn, smooth_q ? 2 : 1), D, 0, s>>>(pq, pk, qm, km, l, nc);
+        launches += 2;
+    } else {
+        channel_mean_kernel<D><<<hn, D, 0, s>>>(k, km, l);
+        if (smooth_q) channel_mean_kernel<D><<<hn, D, 0, s>>>(q, qm, l);
+        launches += 1 + (smooth_q ? 1 : 0);
+    }
     const int lpad = (l + 127) / 128 * 128;
     quant_block_kernel<D, kQTile><<<dim3(lpad / kQTile, hn), 128, 0, s>>>(
         q, smooth_q ? qm : nullptr, reinterpret_cast<int8_t*>(scratch + lo.q8),
@@ -161,7 +220,7 @@ static edb200_status_t quantize(const __half* q, const __half* k, int hn, int l,
     quant_block_kernel<D, kKBlock><<<dim3(lpad / kKBlock, hn), 128, 0, s>>>(
         k, km, reinterpret_cast<int8_t*>(scratch + lo.k8), reinterpret_cast<float*>(scratch + lo.k_scale), l,
         lo.k_scale_stride);
-    int launches = 3 + (smooth_q ? 1 : 0);
+    launches += 2;
     if (smooth_q) {
         // the padded tail of each bias row is read by the attention kernel: keep it finite
         cudaMemsetAsync(scratch + lo.bias, 0, (size_t)hn * lo.bias_stride * 4, s);
@@ -225,10 +284,12 @@ edb200_status_t edb200_sage_quantize_qk(const void* q_f16, const void* k_f16, in
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (d_head == 128) {
         return sage::quantize<128>(static_cast<const __half*>(q_f16), static_cast<const __half*>(k_f16), hn,
-                                   static_cast<int>(l), smooth_q != 0, static_cast<char*>(scratch), lo, s);
+                                   static_cast<int>(l), (smooth_q & 1) != 0, (smooth_q & 2) != 0,
+                                   static_cast<char*>(scratch), lo, s);
     }
     return sage::quantize<64>(static_cast<const __half*>(q_f16), static_cast<const __half*>(k_f16), hn,
-                              static_cast<int>(l), smooth_q != 0, static_cast<char*>(scratch), lo, s);
+                              static_cast<int>(l), (smooth_q & 1) != 0, (smooth_q & 2) != 0,
+                              static_cast<char*>(scratch), lo, s);
 }
 
 edb200_status_t edb200_sage_attention(const void* q_f16, const void* k_f16, const void* v_f16, int hn, int64_t l,
@@ -243,7 +304,7 @@ edb200_status_t edb200_sage_attention(const void* q_f16, const void* k_f16, cons
     return edb200_attention_sage_int8(sc + lo.q8, sc + lo.k8, v_f16, reinterpret_cast<const float*>(sc + lo.q_scale),
                                       lo.q_scale_stride, reinterpret_cast<const float*>(sc + lo.k_scale),
                                       lo.k_scale_stride,
-                                      smooth_q ? reinterpret_cast<const float*>(sc + lo.bias) : nullptr,
+                                      (smooth_q & 1) ? reinterpret_cast<const float*>(sc + lo.bias) : nullptr,
                                       lo.bias_stride, hn, l, d_head, scale, out, out_dtype, ld_out, stream);
 }
 

@@ -209,6 +209,12 @@ EDB200_API int64_t edb200_sage_scratch_bytes(int hn, int64_t l, int d_head);
 /* Byte offsets of {q8, k8, q_scale, k_scale, q_mean, k_mean, bias, total} and the
  * row strides {q_scale, k_scale, bias} inside the scratch buffer. */
 EDB200_API edb200_status_t edb200_sage_scratch_layout(int hn, int64_t l, int d_head, int64_t* offsets, int* strides);
+/* `smooth_q` arguments below are a bit set: EDB200_SAGE_SMOOTH_Q subtracts the
+ * per-channel Q mean and adds the rank-1 bias back (ED_SAGE_SMOOTH_Q);
+ * EDB200_SAGE_FAST_MEANS computes the channel means with a chunked parallel sum
+ * instead of the reference's sequential one (deterministic, last-bit different;
+ * the means cancel in the softmax, so only rounding changes). */
+enum { EDB200_SAGE_SMOOTH_Q = 1, EDB200_SAGE_FAST_MEANS = 2 };
 /* INT8 quantisation of smoothed Q and K, bit-exact with the reference kernels
  * sage_k_mean / sage_q_mean / sage_quant_q_perwarp / sage_quant_k_perblock_smoothk /
  * sage_smooth_q_bias (src/core/backend/ggml/cuda/ed_cuda_sage_attn.cu:61-281). */
