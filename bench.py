@@ -239,6 +239,7 @@ def run_ours(args):
     attention = edb.ATTN_F16 if args.attention == "f16" else edb.ATTN_SAGE_INT8
     model = edb.FluxModel(attention=attention, **kw)
     model.init_random(seed=0, std=0.02)
+    init_launches = int(edb.lib().edb200_launch_count())
     model.prepare(lat[1], lat[2], n_txt)
     n_img = (lat[1] // 2) * (lat[2] // 2)
     tokens = n_img + n_txt
@@ -330,7 +331,7 @@ def run_ours(args):
                    "parallelism": "single GPU" if world == 1 else f"replicas x{world}",
                    "l2": "inputs larger than L2: 12.6 GB of weights stream through every step",
                    "weight_bytes": edb.lib().edb200_flux_weight_bytes(model.handle),
-                   "output_finite": finite},
+                   "output_finite": finite, "init_launches": init_launches},
         "e2e": {"value": e2e_ms, "unit": "ms", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": h_out.nbytes},
         "gpu_launches": int(launches),
         "clocks": clocks,

@@ -221,10 +221,17 @@ gemv_q_kernel(const uint8_t* __restrict__ qs, const __half* __restrict__ sa, con
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         const float4 xv = *reinterpret_cast<const float4*>(xp + 4 * j);
-                        part += static_cast<float>(static_cast<int8_t>(w[j] & 0xFF)) * xv.x;
-                        part += static_cast<float>(static_cast<int8_t>((w[j] >> 8) & 0xFF)) * xv.y;
-                        part += static_cast<float>(static_cast<int8_t>((w[j] >> 16) & 0xFF)) * xv.z;
-                        part += static_cast<float>(static_cast<int8_t>(w[j] >> 24)) * xv.w;
+                        // int8 -> f32 without conversion instructions: byte u = q + 128 placed in the
+                        // mantissa of 2^23 gives 8388608 + u exactly; subtract 8388736 to get q.
+                        const uint32_t u = w[j] ^ 0x80808080u;
+                        const float q0 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7650)) - 8388736.0f;
+                        const float q1 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7651)) - 8388736.0f;
+                        const float q2 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7652)) - 8388736.0f;
+                        const float q3 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7653)) - 8388736.0f;
+                        part = fmaf(q0, xv.x, part);
+                        part = fmaf(q1, xv.y, part);
+                        part = fmaf(q2, xv.z, part);
+                        part = fmaf(q3, xv.w, part);
                     }
                     acc[r][mm] += d[r] * part;
                 }
