@@ -8,8 +8,9 @@
 // One persistent CTA per SM, 512 threads, warp-specialised:
 //   warp 0      TMA producer: activation tile (bf16/f16, 128B swizzle), raw
 //               quantised weight tile and its per-32 scale rows, 4-stage ring
-//   warp 1      tcgen05.mma issuer (one lane), 128x256x16 kind::f16, fp32
-//               accumulators double-buffered in tensor memory (2 x 256 columns)
+//   warp 1      tcgen05.mma issuer (one lane): CTA tile 256x128, two 128x128x16 kind::f16
+//               MMAs per k16 share one dequantised weight tile; fp32 accumulators
+//               double-buffered in tensor memory (2 stages x 2 halves x 128 columns)
 //   warp 2      tensor-memory allocator
 //   warps 4-7   epilogue: tcgen05.ld, bias / GELU / gate*y+residual, stores
 //   warps 8-15  dequantisers: raw int8 / 4-bit payload -> f16 = rn(d*q) written
@@ -22,17 +23,18 @@
 namespace edb {
 namespace gemm {
 
-constexpr int BM = 128;
-constexpr int BN = 256;
+constexpr int BM = 256;      // rows per CTA tile = two 128-row MMA halves sharing one weight tile
+constexpr int MMA_M = 128;
+constexpr int BN = 128;
 constexpr int BK = 64;
 constexpr int LD_STAGES = 4;
-constexpr int B_STAGES = 2;
+constexpr int B_STAGES = 3;
 constexpr int ACC_STAGES = 2;
-constexpr int A_BYTES = BM * BK * 2;      // 16 KB
-constexpr int WQ_BYTES = BN * BK;         // 16 KB (q8_0); q4_K uses half of it
-constexpr int SC_PLANE_BYTES = 2 * BN * 2;  // two 32-blocks x 256 rows x f16
+constexpr int A_BYTES = BM * BK * 2;      // 32 KB
+constexpr int WQ_BYTES = BN * BK;         // 8 KB (q8_0); q4_K uses half of it
+constexpr int SC_PLANE_BYTES = 2 * BN * 2;  // two 32-blocks x 128 rows x f16
 constexpr int SC_BYTES = 2 * SC_PLANE_BYTES;
-constexpr int B_BYTES = BN * BK * 2;      // 32 KB
+constexpr int B_BYTES = BN * BK * 2;      // 16 KB
 
 constexpr int OFF_A = 0;
 constexpr int OFF_W = OFF_A + LD_STAGES * A_BYTES;
@@ -179,11 +181,11 @@ __device__ __forceinline__ uint32_t h2_sub_fma(uint32_t packed, __half2 bias, __
     return *reinterpret_cast<uint32_t*>(&h);
 }
 
-// q8_0: 256 rows x 64 int8 -> 256 rows x 64 f16 in the swizzled operand layout.
+// q8_0: 128 rows x 64 int8 -> 128 rows x 64 f16 in the swizzled operand layout.
 __device__ __forceinline__ void dequant_q8_0(const uint8_t* wq, const __half* sc, uint8_t* bdst, int dq_tid) {
     const __half2 k1152 = __float2half2_rn(1152.0f);
 #pragma unroll
-    for (int it = 0; it < 4; ++it) {
+    for (int it = 0; it < BN * 4 / 256; ++it) {
         const int id = it * 256 + dq_tid;
         const int row = id >> 2;
         const int c = id & 3;
@@ -206,13 +208,13 @@ __device__ __forceinline__ void dequant_q8_0(const uint8_t* wq, const __half* sc
     }
 }
 
-// q4_K: 256 rows x 32 bytes; byte i of a row holds weight k=i (low nibble, first
+// q4_K: 128 rows x 32 bytes; byte i of a row holds weight k=i (low nibble, first
 // 32-block) and weight k=32+i (high nibble, second 32-block).
 __device__ __forceinline__ void dequant_q4_k(const uint8_t* wq, const __half* sa, const __half* sb, uint8_t* bdst,
                                              int dq_tid) {
     const __half2 k1024 = __float2half2_rn(1024.0f);
 #pragma unroll
-    for (int it = 0; it < 2; ++it) {
+    for (int it = 0; it < BN * 2 / 256; ++it) {
         const int id = it * 256 + dq_tid;
         const int row = id >> 1;
         const int c = id & 1;  // bytes c*16 .. c*16+15
@@ -340,7 +342,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__
         }
     } else if (warp == 1) {
         // -------------------------------------------------------- MMA issuer
-        const uint32_t idesc = make_idesc(kDFmtF32, P.a_fmt, kFmtF16, 0, 0, BM, BN);
+        const uint32_t idesc = make_idesc(kDFmtF32, P.a_fmt, kFmtF16, 0, 0, MMA_M, BN);
         uint32_t s = 0, ph = 0, bs = 0, bph = 0, as = 0, aph = 0;
         bool ok = true;
         for (int t = blockIdx.x; ok && t < P.total_tiles; t += gridDim.x) {
@@ -351,7 +353,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__
                 break;
             }
             tc_fence_after_sync();
-            const uint32_t tmem_d = tmem_base + as * BN;
+            const uint32_t tmem_d = tmem_base + as * (2 * BN);
             for (int ks = 0; ks < ksteps; ++ks) {
                 if (!mbar_wait(&ld_full[s], ph, abort_flag, P.err) ||
                     !mbar_wait(&b_full[bs], bph, abort_flag, P.err)) {
@@ -364,9 +366,13 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__
                     const uint32_t b_addr = smem_u32(smem + OFF_B + bs * B_BYTES);
 #pragma unroll
                     for (int j = 0; j < BK / 16; ++j) {
-                        const uint64_t ad = make_smem_desc_sw128(a_addr + j * 32, 16, 1024);
                         const uint64_t bd = make_smem_desc_sw128(b_addr + j * 32, 16, 1024);
-                        mma_f16_ss(tmem_d, ad, bd, idesc, (ks > 0 || j > 0) ? 1u : 0u);
+#pragma unroll
+                        for (int h = 0; h < BM / MMA_M; ++h) {
+                            // rows h*128.. of the activation tile: 128 rows x 128 B further on
+                            const uint64_t ad = make_smem_desc_sw128(a_addr + h * (MMA_M * 128) + j * 32, 16, 1024);
+                            mma_f16_ss(tmem_d + h * BN, ad, bd, idesc, (ks > 0 || j > 0) ? 1u : 0u);
+                        }
                     }
                     mma_commit(&ld_empty[s]);
                     mma_commit(&b_empty[bs]);
@@ -402,15 +408,17 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__
                 break;
             }
             tc_fence_after_sync();
-            const int m = tc.m0 + quarter * 32 + lane;
-            const bool row_ok = m < pr.M;
-            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + as * BN;
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + as * (2 * BN);
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
+            for (int hc = 0; hc < (BM / MMA_M) * (BN / 32); ++hc) {
+                const int h = hc / (BN / 32), c = hc % (BN / 32);
+                const int m = tc.m0 + h * MMA_M + quarter * 32 + lane;
+                const bool row_ok = m < pr.M;
                 const int n = tc.n0 + c * 32;
-                if (n >= pr.N) break;   // uniform: N is a multiple of 32
+                if (n >= pr.N) continue;   // uniform: N is a multiple of 32
+                if (tc.m0 + h * MMA_M >= pr.M) continue;   // uniform: whole half beyond the last row
                 uint32_t r[32];
-                tmem_ld_32x32b_x32(taddr + c * 32, r);
+                tmem_ld_32x32b_x32(taddr + h * BN + c * 32, r);
                 tmem_wait_ld();
                 float v[32];
 #pragma unroll
@@ -511,7 +519,7 @@ static edb200_status_t validate_problem(const edb200_qweight_t* w, const void* x
     }
     if (ep->split_n > 0) {
         if (ep->split_n % gemm::BN != 0 || ep->split_n >= w->n_out || ep->out2 == nullptr || !dt_ok(ep->out2_dtype)) {
-            return fail(EDB200_ERR_INVALID, "mul_mat_q: split_n must be a multiple of 256 below n_out with out2 set");
+            return fail(EDB200_ERR_INVALID, "mul_mat_q: split_n must be a multiple of 128 below n_out with out2 set");
         }
         const int esz2 = ep->out2_dtype == EDB200_TYPE_F32 ? 4 : 2;
         if (ep->ldo2 < w->n_out - ep->split_n || (ep->ldo2 * esz2) % 16 != 0 ||

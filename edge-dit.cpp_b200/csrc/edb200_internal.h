@@ -79,7 +79,7 @@ struct edb200_qweight {
     float* sb32 = nullptr;
     int64_t n_pad = 0;          // scale-plane row length (multiple of 8)
     int64_t bytes = 0;
-    CUtensorMap map_qs;         // box {64 B, 256 rows}
-    CUtensorMap map_sa;         // box {256, 2}
+    CUtensorMap map_qs;         // box {64 B, 128 rows}
+    CUtensorMap map_sa;         // box {128, 2}
     CUtensorMap map_sb;
 };

@@ -58,16 +58,21 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
                  : "memory");
 }
 
+// Upper bound (ns) the hardware may keep a waiting thread suspended inside one
+// try_wait before it returns false; every failed try_wait is a shared-memory
+// access, so a long hint keeps polling traffic off the shared-memory port.
+constexpr uint32_t kTryWaitSuspendNs = 20000;
+
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t"
         ".reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t"
         "}\n"
         : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(kTryWaitSuspendNs)
         : "memory");
     return ok != 0;
 }

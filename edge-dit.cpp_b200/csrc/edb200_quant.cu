@@ -518,18 +518,18 @@ edb200_status_t edb200_qweight_create(int ggml_type, const void* blocks, int64_t
     edb200_status_t st;
     if (ggml_type == EDB200_TYPE_Q8_0) {
         st = make_tmap_2d(&w->map_qs, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w->qs, (uint64_t)k, (uint64_t)n_out,
-                          (uint64_t)k, 64, 256, CU_TENSOR_MAP_SWIZZLE_NONE);
+                          (uint64_t)k, 64, 128, CU_TENSOR_MAP_SWIZZLE_NONE);
     } else {
         st = make_tmap_2d(&w->map_qs, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w->qs, (uint64_t)k / 2, (uint64_t)n_out,
-                          (uint64_t)k / 2, 32, 256, CU_TENSOR_MAP_SWIZZLE_NONE);
+                          (uint64_t)k / 2, 32, 128, CU_TENSOR_MAP_SWIZZLE_NONE);
     }
     if (st == EDB200_OK) {
         st = make_tmap_2d(&w->map_sa, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, w->sa, (uint64_t)w->n_pad, (uint64_t)kb32,
-                          (uint64_t)w->n_pad * 2, 256, 2, CU_TENSOR_MAP_SWIZZLE_NONE);
+                          (uint64_t)w->n_pad * 2, 128, 2, CU_TENSOR_MAP_SWIZZLE_NONE);
     }
     if (st == EDB200_OK && ggml_type == EDB200_TYPE_Q4_K) {
         st = make_tmap_2d(&w->map_sb, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, w->sb, (uint64_t)w->n_pad, (uint64_t)kb32,
-                          (uint64_t)w->n_pad * 2, 256, 2, CU_TENSOR_MAP_SWIZZLE_NONE);
+                          (uint64_t)w->n_pad * 2, 128, 2, CU_TENSOR_MAP_SWIZZLE_NONE);
     }
     if (st != EDB200_OK) {
         edb200_qweight_destroy(w);

@@ -116,7 +116,7 @@ typedef struct {
     int64_t ld_res;
     const float* gate;     /* [n_out] f32 */
     /* Column split: columns >= split_n are written to out2[:, col - split_n]
-     * with act2 (0 = no split).  split_n must be a multiple of 256. */
+     * with act2 (0 = no split).  split_n must be a multiple of 128. */
     int64_t split_n;
     void* out2;
     int out2_dtype;
