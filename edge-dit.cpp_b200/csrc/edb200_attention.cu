@@ -11,14 +11,16 @@
 // Both keep the softmax in f32 base 2, P in f16 and the PV product in kind::f16
 // with f32 accumulation, V in f16 (as the reference feeds it).
 //
-// One CTA per (128-query tile, head); 256 threads, warp-specialised:
+// One CTA per (128-query tile, head); 640 threads, warp-specialised:
 //   warp 0     TMA producer (Q once; K and V tiles of 128 keys, 2-stage rings)
 //   warp 1     tcgen05.mma issuer: S_j = Q K_j^T into one of two S buffers in
 //              tensor memory, O += P_j V_j
 //   warp 2     tensor-memory allocator
-//   warps 4-7  softmax: one query row per thread; tcgen05.ld S, exp2, P -> shared
-//              memory (128B-swizzled K-major operand), lazy rescale of O in
-//              tensor memory (only when a row maximum grows by more than 2^8)
+//   warps 4-19 softmax: four threads per query row, each owning 32 score columns
+//              (four warps per scheduler hide the dependent-issue latency a
+//              single warp cannot); tcgen05.ld S, exp2, P -> shared memory
+//              (128B-swizzled K-major operand), lazy rescale of O in tensor
+//              memory (only when a row maximum grows by more than 2^8)
 #include "edb200_internal.h"
 #include "edb200_ptx.cuh"
 
@@ -28,9 +30,10 @@ namespace attn {
 constexpr int BQ = 128;   // query rows per CTA
 constexpr int BKV = 128;  // keys per block
 constexpr int KV_STAGES = 2;
-constexpr int NUM_THREADS = 256;
+constexpr int NSPLIT = 4;          // softmax threads per query row
+constexpr int NUM_THREADS = 128 + NSPLIT * 128;
 constexpr uint32_t TMEM_COLS = 512;
-constexpr uint32_t TMEM_S0 = 0, TMEM_S1 = 128, TMEM_O = 256;
+constexpr uint32_t TMEM_S0 = 0, TMEM_S1 = 128, TMEM_O = 256, TMEM_P = 384;
 constexpr float kRescaleThreshold = 8.0f;  // log2(256)
 
 struct Params {
@@ -53,13 +56,12 @@ struct Cfg {
     static constexpr int Q_BYTES = BQ * D * QK_ELEM;
     static constexpr int K_BYTES = BKV * D * QK_ELEM;
     static constexpr int V_BYTES = BKV * D * 2;
-    static constexpr int P_BYTES = BQ * BKV * 2;
     static constexpr int OFF_Q = 0;
     static constexpr int OFF_K = OFF_Q + Q_BYTES;
     static constexpr int OFF_V = OFF_K + KV_STAGES * K_BYTES;
-    static constexpr int OFF_P = OFF_V + KV_STAGES * V_BYTES;
-    static constexpr int OFF_BAR = OFF_P + P_BYTES;
-    static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
+    static constexpr int OFF_BAR = OFF_V + KV_STAGES * V_BYTES;
+    static constexpr int OFF_XCH = OFF_BAR + 256;                  // row-maximum exchange [2][NSPLIT][BQ] f32
+    static constexpr int SMEM_BYTES = OFF_XCH + 2 * NSPLIT * BQ * 4 + 1024;
     // Q/K panels: rows of 128 bytes (64 f16 or 128 int8); a tile is D*QK_ELEM/128 panels.
     static constexpr int QK_PANELS = D * QK_ELEM / 128;
     static constexpr int QK_PANEL_BYTES = 128 * 128;
@@ -114,9 +116,9 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(&s_full[i], 1);
-            mbar_init(&s_empty[i], 4);
+            mbar_init(&s_empty[i], 4 * NSPLIT);
         }
-        mbar_init(p_full, 4);
+        mbar_init(p_full, 4 * NSPLIT);
         mbar_init(pv_done, 1);
         *abort_flag = 0;
         fence_mbar_init();
@@ -168,7 +170,6 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                                        : make_idesc(kDFmtF32, kFmtF16, kFmtF16, 0, 0, BQ, BKV);
         const uint32_t idesc_pv = make_idesc(kDFmtF32, kFmtF16, kFmtF16, 0, 1, BQ, D);
         const uint32_t q_addr = smem_u32(smem + C::OFF_Q);
-        const uint32_t p_addr = smem_u32(smem + C::OFF_P);
         bool ok = mbar_wait(q_full, 0, abort_flag, P.err);
 
         auto issue_qk = [&](int j) -> bool {
@@ -216,11 +217,9 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 const uint32_t v_addr = smem_u32(smem + C::OFF_V + st * C::V_BYTES);
 #pragma unroll
                 for (int ks = 0; ks < BKV / 16; ++ks) {
-                    // P: K-major, two 64-key panels of 16 KB; V: MN-major, 16 keys = 2 KB per step
-                    const uint64_t ad =
-                        make_smem_desc_sw128(p_addr + (ks / 4) * (BQ * 128) + (ks % 4) * 32, 16, 1024);
+                    // P: tensor memory, 8 columns (16 keys) per step; V: MN-major, 16 keys = 2 KB per step
                     const uint64_t bd = make_smem_desc_sw128(v_addr + ks * 2048, BKV * 128, 1024);
-                    mma_f16_ss(tmem_base + TMEM_O, ad, bd, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+                    mma_f16_ts(tmem_base + TMEM_O, tmem_base + TMEM_P + ks * 8, bd, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
                 }
                 mma_commit(pv_done);
                 mma_commit(&v_empty[st]);
@@ -229,82 +228,94 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         }
     } else if (warp >= 4) {
         // ------------------------------------------------------------ softmax
+        // NSPLIT threads share one query row: thread `split` owns score columns
+        // [split*CW, split*CW+CW) and output columns [split*OW, split*OW+OW).  The
+        // row maximum is exchanged through shared memory behind a named barrier
+        // per lane quarter, so every thread of a row takes the same rescale decision.
+        constexpr int CW = BKV / NSPLIT;
+        constexpr int OW = D / NSPLIT;
         const int quarter = warp & 3;
+        const int split = (warp - 4) >> 2;
         const int r = quarter * 32 + lane;          // row inside the tile
         const int q_row = q0 + r;
         const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+        float* xch = reinterpret_cast<float*>(smem + C::OFF_XCH);   // [2][NSPLIT][BQ]
         float m_used = -INFINITY;
         float l_sum = 0.0f;
         float row_scale = P.scale_log2;
         const float* bias_row = nullptr;
         if (SAGE) {
             row_scale *= P.q_scale[(long long)hn * P.q_scale_stride + (q0 >> 5) + quarter];
-            if (P.bias != nullptr) bias_row = P.bias + (long long)hn * P.bias_stride;
+            if (P.bias != nullptr) bias_row = P.bias + (long long)hn * P.bias_stride + split * CW;
         }
-        uint8_t* p_smem = smem + C::OFF_P;
-        const uint32_t p_row_off = (r >> 3) * 1024 + (r & 7) * 128;
-        const uint32_t sw = r & 7;
         bool ok = true;
 
-        for (int j = 0; ok && j < n_kv; ++j) {
+        for (int j = 0; j < n_kv; ++j) {
+            // After an abort every wait returns false at once; the loop still runs to
+            // the end so that all threads of a row group meet at the named barrier.
             const int sb = j & 1;
-            if (!mbar_wait(&s_full[sb], static_cast<uint32_t>((j >> 1) & 1), abort_flag, P.err)) {
-                ok = false;
-                break;
-            }
+            ok = mbar_wait(&s_full[sb], static_cast<uint32_t>((j >> 1) & 1), abort_flag, P.err) && ok;
             tc_fence_after_sync();
-            float s[BKV];
+            float s[CW];
             {
-                const uint32_t taddr = tmem_base + lane_base + (sb ? TMEM_S1 : TMEM_S0);
-#pragma unroll
-                for (int c = 0; c < BKV / 32; ++c) {
-                    uint32_t rr[32];
-                    tmem_ld_32x32b_x32(taddr + c * 32, rr);
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) s[c * 32 + i] = __uint_as_float(rr[i]);
-                }
+                const uint32_t taddr = tmem_base + lane_base + (sb ? TMEM_S1 : TMEM_S0) + split * CW;
+                uint32_t rr[CW];
+                tmem_ld_cols<CW>(taddr, rr);
                 tmem_wait_ld();
+#pragma unroll
+                for (int i = 0; i < CW; ++i) s[i] = __uint_as_float(rr[i]);
             }
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&s_empty[sb]);
 
             // scores in the log2 domain
-            const int valid = P.Lk - j * BKV;  // columns >= valid are padding
+            const int valid = P.Lk - j * BKV - split * CW;  // own columns >= valid are padding
             if (SAGE) {
-                const float ks0 = P.k_scale[(long long)hn * P.k_scale_stride + 2 * j];
-                const float ks1 = P.k_scale[(long long)hn * P.k_scale_stride + 2 * j + 1];
-                const float c0 = row_scale * ks0, c1 = row_scale * ks1;
-#pragma unroll
-                for (int i = 0; i < BKV; ++i) {
-                    // s32 -> f32 without a conversion instruction: valid for |s| < 2^22
-                    const float f = __int_as_float(__float_as_int(s[i]) + 0x4B400000) - 12582912.0f;
-                    s[i] = f * (i < 64 ? c0 : c1);
-                }
+                const float ks = P.k_scale[(long long)hn * P.k_scale_stride + 2 * j + (split * CW >= 64 ? 1 : 0)];
+                const float c0 = row_scale * ks;
+                // s32 -> f32 without a conversion instruction (valid for |s| < 2^22):
+                // as_float(s + 0x4B400000) = 12582912 + s exactly.
                 if (bias_row != nullptr) {
                     const float4* b4 = reinterpret_cast<const float4*>(bias_row + j * BKV);
 #pragma unroll
-                    for (int i = 0; i < BKV / 4; ++i) {
+                    for (int i = 0; i < CW / 4; ++i) {
                         const float4 b = __ldg(b4 + i);
-                        s[4 * i + 0] = fmaf(b.x, P.scale_log2, s[4 * i + 0]);
-                        s[4 * i + 1] = fmaf(b.y, P.scale_log2, s[4 * i + 1]);
-                        s[4 * i + 2] = fmaf(b.z, P.scale_log2, s[4 * i + 2]);
-                        s[4 * i + 3] = fmaf(b.w, P.scale_log2, s[4 * i + 3]);
+                        const float bb[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float f = __int_as_float(__float_as_int(s[4 * i + e]) + 0x4B400000) - 12582912.0f;
+                            s[4 * i + e] = fmaf(f, c0, bb[e] * P.scale_log2);
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < CW; ++i) {
+                        const float f = __int_as_float(__float_as_int(s[i]) + 0x4B400000) - 12582912.0f;
+                        s[i] = f * c0;
                     }
                 }
             } else {
 #pragma unroll
-                for (int i = 0; i < BKV; ++i) s[i] *= row_scale;
+                for (int i = 0; i < CW; ++i) s[i] *= row_scale;
             }
-            if (valid < BKV) {
+            if (valid < CW) {
 #pragma unroll
-                for (int i = 0; i < BKV; ++i) {
+                for (int i = 0; i < CW; ++i) {
                     if (i >= valid) s[i] = -INFINITY;
                 }
             }
-            float mx = s[0];
+            float mx4[4] = {s[0], s[1], s[2], s[3]};
 #pragma unroll
-            for (int i = 1; i < BKV; ++i) mx = fmaxf(mx, s[i]);
+            for (int i = 4; i < CW; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], s[i]);
+            float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            if (NSPLIT > 1) {
+                float* xb = xch + (j & 1) * (NSPLIT * BQ);
+                xb[split * BQ + r] = mx;
+                named_bar_sync(1 + quarter, NSPLIT * 32);
+#pragma unroll
+                for (int sp = 0; sp < NSPLIT; ++sp) mx = fmaxf(mx, xb[sp * BQ + r]);
+            }
 
             // lazy rescale: keep exponentiating against the old maximum until it is stale by > 2^8
             float alpha = 1.0f;
@@ -314,77 +325,74 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 m_used = mx;
                 l_sum *= alpha;
             }
-            uint32_t p2[BKV / 2];
-            float part = 0.0f;
+            uint32_t p2[CW / 2];
+            float part[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int i = 0; i < BKV / 2; ++i) {
+            for (int i = 0; i < CW / 2; ++i) {
                 const float a = ex2(s[2 * i] - m_used);
                 const float b = ex2(s[2 * i + 1] - m_used);
-                part += a + b;
+                part[i & 3] += a + b;
                 p2[i] = pack_h2(a, b);
             }
-            l_sum += part;
+            l_sum += (part[0] + part[1]) + (part[2] + part[3]);
 
             // P buffer and O are free once the previous PV product has completed
             if (j > 0) {
-                if (!mbar_wait(pv_done, static_cast<uint32_t>((j - 1) & 1), abort_flag, P.err)) {
-                    ok = false;
-                    break;
-                }
+                ok = mbar_wait(pv_done, static_cast<uint32_t>((j - 1) & 1), abort_flag, P.err) && ok;
                 tc_fence_after_sync();
                 if (__any_sync(0xffffffffu, grow)) {
-                    const uint32_t oaddr = tmem_base + lane_base + TMEM_O;
-#pragma unroll 1
-                    for (int c = 0; c < D / 32; ++c) {
-                        uint32_t rr[32];
-                        tmem_ld_32x32b_x32(oaddr + c * 32, rr);
-                        tmem_wait_ld();
+                    const uint32_t oaddr = tmem_base + lane_base + TMEM_O + split * OW;
+                    uint32_t rr[OW];
+                    tmem_ld_cols<OW>(oaddr, rr);
+                    tmem_wait_ld();
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) rr[i] = __float_as_uint(__uint_as_float(rr[i]) * alpha);
-                        tmem_st_32x32b_x32(oaddr + c * 32, rr);
-                    }
+                    for (int i = 0; i < OW; ++i) rr[i] = __float_as_uint(__uint_as_float(rr[i]) * alpha);
+                    tmem_st_cols<OW>(oaddr, rr);
                     tmem_wait_st();
                 }
             }
-            // write P: row r, 16 chunks of 8 f16; chunk c lives in panel c/8 at swizzled slot (c%8)^(r%8)
-#pragma unroll
-            for (int c = 0; c < BKV / 8; ++c) {
-                const uint32_t off = (c >> 3) * (BQ * 128) + p_row_off + (((c & 7) ^ sw) << 4);
-                *reinterpret_cast<uint4*>(p_smem + off) =
-                    make_uint4(p2[4 * c], p2[4 * c + 1], p2[4 * c + 2], p2[4 * c + 3]);
-            }
-            fence_proxy_async_smem();
+            // P (f16 pairs, two keys per 32-bit column) goes to tensor memory as the A operand of PV
+            tmem_st_cols<CW / 2>(tmem_base + lane_base + TMEM_P + split * (CW / 2), p2);
+            tmem_wait_st();
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(p_full);
         }
 
         // ----------------------------------------------------------- epilogue
-        if (ok && mbar_wait(pv_done, static_cast<uint32_t>((n_kv - 1) & 1), abort_flag, P.err)) {
+        if (NSPLIT > 1) {
+            // row sum = fixed-order sum of the NSPLIT partial sums (all scaled by the same alphas)
+            float* xb = xch + (n_kv & 1) * (NSPLIT * BQ);
+            xb[split * BQ + r] = l_sum;
+            named_bar_sync(1 + quarter, NSPLIT * 32);
+            l_sum = 0.0f;
+#pragma unroll
+            for (int sp = 0; sp < NSPLIT; ++sp) l_sum += xb[sp * BQ + r];
+        }
+        ok = mbar_wait(pv_done, static_cast<uint32_t>((n_kv - 1) & 1), abort_flag, P.err) && ok;
+        if (ok) {
             tc_fence_after_sync();
             const float inv_l = 1.0f / l_sum;
-            const uint32_t oaddr = tmem_base + lane_base + TMEM_O;
+            const uint32_t oaddr = tmem_base + lane_base + TMEM_O + split * OW;
             const bool row_ok = q_row < P.Lq;
             char* obase = static_cast<char*>(P.out);
-            const long long ocol = (long long)q_row * P.ld_out + (long long)hn * D;
-#pragma unroll 1
-            for (int c = 0; c < D / 32; ++c) {
-                uint32_t rr[32];
-                tmem_ld_32x32b_x32(oaddr + c * 32, rr);
-                tmem_wait_ld();
-                if (!row_ok) continue;
-                float v[32];
+            const long long ocol = (long long)q_row * P.ld_out + (long long)hn * D + split * OW;
+            uint32_t rr[OW];
+            tmem_ld_cols<OW>(oaddr, rr);
+            tmem_wait_ld();
+            if (row_ok) {
+                float v[OW];
 #pragma unroll
-                for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(rr[i]) * inv_l;
+                for (int i = 0; i < OW; ++i) v[i] = __uint_as_float(rr[i]) * inv_l;
                 if (P.out_dtype == EDB200_TYPE_F32) {
-                    float4* o = reinterpret_cast<float4*>(obase + (ocol + c * 32) * 4);
+                    float4* o = reinterpret_cast<float4*>(obase + ocol * 4);
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) o[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                    for (int i = 0; i < OW / 4; ++i) o[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
                 } else {
-                    uint4* o = reinterpret_cast<uint4*>(obase + (ocol + c * 32) * 2);
+                    uint4* o = reinterpret_cast<uint4*>(obase + ocol * 2);
                     const bool bf = P.out_dtype == EDB200_TYPE_BF16;
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
+                    for (int i = 0; i < OW / 8; ++i) {
                         uint32_t u[4];
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {

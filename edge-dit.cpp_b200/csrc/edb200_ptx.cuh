@@ -58,21 +58,16 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
                  : "memory");
 }
 
-// Upper bound (ns) the hardware may keep a waiting thread suspended inside one
-// try_wait before it returns false; every failed try_wait is a shared-memory
-// access, so a long hint keeps polling traffic off the shared-memory port.
-constexpr uint32_t kTryWaitSuspendNs = 20000;
-
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t"
         ".reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t"
         "}\n"
         : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity), "r"(kTryWaitSuspendNs)
+        : "r"(smem_u32(bar)), "r"(parity)
         : "memory");
     return ok != 0;
 }
@@ -82,6 +77,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // word read by the host after the launch.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* err) {
     if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
     const unsigned long long t0 = globaltimer_ns();
     uint32_t spins = 0;
     while (true) {
@@ -185,6 +181,30 @@ __device__ __forceinline__ void tmem_st_32x32b_x16(uint32_t taddr, const uint32_
         ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
         "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
         : "memory");
+}
+
+template <int N>
+__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&r)[N]) {
+    static_assert(N == 16 || N == 32, "tmem_ld_cols: 16 or 32 columns");
+    if constexpr (N == 32) {
+        tmem_ld_32x32b_x32(taddr, r);
+    } else {
+        tmem_ld_32x32b_x16(taddr, r);
+    }
+}
+template <int N>
+__device__ __forceinline__ void tmem_st_cols(uint32_t taddr, const uint32_t (&r)[N]) {
+    static_assert(N == 16 || N == 32, "tmem_st_cols: 16 or 32 columns");
+    if constexpr (N == 32) {
+        tmem_st_32x32b_x32(taddr, r);
+    } else {
+        tmem_st_32x32b_x16(taddr, r);
+    }
+}
+
+// Named barrier among `nthreads` threads (ids 1..15; 0 is __syncthreads).
+__device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t nthreads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
