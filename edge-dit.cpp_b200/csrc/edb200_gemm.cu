@@ -5,16 +5,26 @@
 // Stands in for ggml_mul_mat on q8_0 / q4_K weights reached through
 // ggml_ext_linear (reference src/core/backend/ggml/ggml_extend.hpp:1308-1347).
 //
+// The kernel computes the transposed tile  D[n, m] = W[n, :] . x[m, :]  so that
+// the *weights* are the tcgen05 A operand.  A may live in tensor memory, which is
+// what makes the fusion cheap: the dequantisers write f16 weights straight into
+// tensor memory (tcgen05.st) and never touch shared memory with them.  Shared
+// memory bandwidth (128 B/clk/SM) is the binding resource of this kernel; per
+// 64-deep k-step a CTA moves 28 KB of activations in (TMA) and out (MMA B
+// operand) plus 8.5 KB of raw weights in and out, instead of also writing and
+// re-reading 16-32 KB of dequantised weights.
+//
 // One persistent CTA per SM, 512 threads, warp-specialised:
-//   warp 0      TMA producer: activation tile (bf16/f16, 128B swizzle), raw
-//               quantised weight tile and its per-32 scale rows, 4-stage ring
-//   warp 1      tcgen05.mma issuer (one lane): CTA tile 256x128, two 128x128x16 kind::f16
-//               MMAs per k16 share one dequantised weight tile; fp32 accumulators
-//               double-buffered in tensor memory (2 stages x 2 halves x 128 columns)
+//   warp 0      producer: TMA tile of 224 tokens x 64 k (f16, 128B swizzle) and one
+//               bulk copy of the 128-row x 64-k weight tile record, 5-stage ring
+//   warp 1      tcgen05.mma issuer (one lane): 128 x 224 x 16 kind::f16, A from
+//               tensor memory, B from shared memory; fp32 accumulators
+//               double-buffered in tensor memory (2 x 224 columns)
 //   warp 2      tensor-memory allocator
-//   warps 4-7   epilogue: tcgen05.ld, bias / GELU / gate*y+residual, stores
-//   warps 8-15  dequantisers: raw int8 / 4-bit payload -> f16 = rn(d*q) written
-//               straight into the 128B-swizzled K-major operand layout
+//   warps 4-7   epilogue: tcgen05.ld (lane = output feature, column = token),
+//               bias / GELU / gate*y+residual, stores coalesced across lanes
+//   warps 8-15  dequantisers: thread = one weight row x 32 k; int8 / 4-bit
+//               payload -> f16 -> tcgen05.st into one of two A stages
 // The dequantised f16 weight equals rn_f16(d*q) for q8_0 (one rounding of the
 // exact product) and rn_f16(a*q - b) for q4_K with a = rn_f16(d*sc), b = rn_f16(dmin*m).
 #include "edb200_internal.h"
@@ -23,30 +33,24 @@
 namespace edb {
 namespace gemm {
 
-constexpr int BM = 256;      // rows per CTA tile = two 128-row MMA halves sharing one weight tile
-constexpr int MMA_M = 128;
-constexpr int BN = 128;
+constexpr int TW = 128;            // weight rows (output features) per tile = tensor-memory lanes
+constexpr int TN = 224;            // tokens per tile = accumulator columns
 constexpr int BK = 64;
-constexpr int LD_STAGES = 4;
-constexpr int B_STAGES = 3;
+constexpr int LD_STAGES = 5;
+constexpr int A_STAGES = 2;
 constexpr int ACC_STAGES = 2;
-constexpr int A_BYTES = BM * BK * 2;      // 32 KB
-constexpr int WQ_BYTES = BN * BK;         // 8 KB (q8_0); q4_K uses half of it
-constexpr int SC_PLANE_BYTES = 2 * BN * 2;  // two 32-blocks x 128 rows x f16
-constexpr int SC_BYTES = 2 * SC_PLANE_BYTES;
-constexpr int B_BYTES = BN * BK * 2;      // 16 KB
-
-constexpr int OFF_A = 0;
-constexpr int OFF_W = OFF_A + LD_STAGES * A_BYTES;
-constexpr int OFF_B = OFF_W + LD_STAGES * WQ_BYTES;
-constexpr int OFF_S = OFF_B + B_STAGES * B_BYTES;
-constexpr int OFF_BAR = OFF_S + LD_STAGES * SC_BYTES;
+constexpr int X_BYTES = TN * BK * 2;          // 28 KB
+constexpr int W_BYTES_MAX = 9216;             // weight tile record (8704 / 5120 B) padded
+constexpr int STAGE_BYTES = X_BYTES + W_BYTES_MAX;
+constexpr int OFF_BAR = LD_STAGES * STAGE_BYTES;
 constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;  // + alignment slack
 
 constexpr int NUM_THREADS = 512;
 constexpr int DQ_WARPS = 8;
 constexpr int EPI_WARPS = 4;
 constexpr uint32_t TMEM_COLS = 512;
+constexpr uint32_t TMEM_ACC = 0;                       // 2 x 224 columns
+constexpr uint32_t TMEM_A = ACC_STAGES * TN;           // 2 x 32 columns (64 f16 per lane)
 
 struct Problem {
     const float* bias;
@@ -54,6 +58,7 @@ struct Problem {
     const float* residual;
     const float* gate;
     void* out2;
+    const uint8_t* tiles;      // repacked weight
     long long ldo, ld_res, ldo2, split_n;
     int out_dtype, act, out2_dtype, act2;
     int M, N, K;
@@ -64,12 +69,11 @@ struct Params {
     Problem p[2];
     int tiles0;       // tiles of problem 0
     int total_tiles;
-    uint32_t a_fmt;   // kFmtF16 / kFmtBF16
     int* err;
 };
 
 struct TileCoord {
-    int prob, m0, n0;
+    int prob, m0, n_tile;
 };
 
 __device__ __forceinline__ TileCoord tile_coord(const Params& P, int t) {
@@ -77,9 +81,9 @@ __device__ __forceinline__ TileCoord tile_coord(const Params& P, int t) {
     c.prob = (t >= P.tiles0) ? 1 : 0;
     const int tt = c.prob ? t - P.tiles0 : t;
     const int m_tiles = c.prob ? P.p[1].m_tiles : P.p[0].m_tiles;
-    // m fastest: CTAs running at the same time share one weight column block.
-    c.n0 = (tt / m_tiles) * BN;
-    c.m0 = (tt % m_tiles) * BM;
+    // token tile fastest: CTAs running at the same time share one weight tile row through L2.
+    c.n_tile = tt / m_tiles;
+    c.m0 = (tt % m_tiles) * TN;
     return c;
 }
 
@@ -96,75 +100,45 @@ __device__ __forceinline__ float apply_act(float v, int act) {
     return v;
 }
 
-__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
-    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-    return *reinterpret_cast<uint32_t*>(&h);
-}
-__device__ __forceinline__ uint32_t pack_f16(float a, float b) {
-    __half2 h = __floats2half2_rn(a, b);
-    return *reinterpret_cast<uint32_t*>(&h);
-}
-
-// One 32-column slice of one accumulator row.
-__device__ __forceinline__ void epilogue_store(const Problem& P, float (&v)[32], int m, int n, bool row_ok) {
-    if (P.bias != nullptr) {
-        const float4* b4 = reinterpret_cast<const float4*>(P.bias + n);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const float4 b = __ldg(b4 + j);
-            v[4 * j + 0] += b.x;
-            v[4 * j + 1] += b.y;
-            v[4 * j + 2] += b.z;
-            v[4 * j + 3] += b.w;
-        }
-    }
+// 32 tokens (m_first..m_first+31) of one output feature n; lanes of a warp hold
+// consecutive n, so every global access below is contiguous across the warp.
+__device__ __forceinline__ void epilogue_store(const Problem& P, float (&v)[32], int n, int m_first, bool n_ok) {
     const bool second = (P.split_n > 0) && (n >= P.split_n);
     const int act = second ? P.act2 : P.act;
-    if (act != EDB200_ACT_NONE) {
+    const float b = (P.bias != nullptr && n_ok) ? __ldg(P.bias + n) : 0.0f;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], act);
-    }
+    for (int i = 0; i < 32; ++i) v[i] = apply_act(v[i] + b, act);
+    const int rows = min(32, P.M - m_first);   // uniform across the warp
     if (!second && P.gate != nullptr) {
-        const float4* g4 = reinterpret_cast<const float4*>(P.gate + n);
-        const float4* r4 = reinterpret_cast<const float4*>(P.residual + (long long)m * P.ld_res + n);
+        const float g = n_ok ? __ldg(P.gate + n) : 0.0f;
+        const float* rp = P.residual + (long long)m_first * P.ld_res + n;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const float4 g = __ldg(g4 + j);
-            float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (row_ok) r = r4[j];
-            v[4 * j + 0] = r.x + g.x * v[4 * j + 0];
-            v[4 * j + 1] = r.y + g.y * v[4 * j + 1];
-            v[4 * j + 2] = r.z + g.z * v[4 * j + 2];
-            v[4 * j + 3] = r.w + g.w * v[4 * j + 3];
+        for (int i = 0; i < 32; ++i) {
+            if (i < rows && n_ok) v[i] = rp[(long long)i * P.ld_res] + g * v[i];
         }
     }
-    if (!row_ok) return;
+    if (!n_ok) return;
     const int dt = second ? P.out2_dtype : P.out_dtype;
     const long long ld = second ? P.ldo2 : P.ldo;
     const long long col = second ? (n - P.split_n) : n;
     char* base = reinterpret_cast<char*>(second ? P.out2 : P.out);
     if (dt == EDB200_TYPE_F32) {
-        float4* o = reinterpret_cast<float4*>(base + ((long long)m * ld + col) * 4);
+        float* o = reinterpret_cast<float*>(base) + (long long)m_first * ld + col;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+        for (int i = 0; i < 32; ++i) {
+            if (i < rows) o[(long long)i * ld] = v[i];
+        }
+    } else if (dt == EDB200_TYPE_BF16) {
+        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(base) + (long long)m_first * ld + col;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            if (i < rows) o[(long long)i * ld] = __float2bfloat16_rn(v[i]);
+        }
     } else {
-        uint4* o = reinterpret_cast<uint4*>(base + ((long long)m * ld + col) * 2);
-        const bool bf = (dt == EDB200_TYPE_BF16);
+        __half* o = reinterpret_cast<__half*>(base) + (long long)m_first * ld + col;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            uint4 u;
-            if (bf) {
-                u.x = pack_bf16(v[8 * j + 0], v[8 * j + 1]);
-                u.y = pack_bf16(v[8 * j + 2], v[8 * j + 3]);
-                u.z = pack_bf16(v[8 * j + 4], v[8 * j + 5]);
-                u.w = pack_bf16(v[8 * j + 6], v[8 * j + 7]);
-            } else {
-                u.x = pack_f16(v[8 * j + 0], v[8 * j + 1]);
-                u.y = pack_f16(v[8 * j + 2], v[8 * j + 3]);
-                u.z = pack_f16(v[8 * j + 4], v[8 * j + 5]);
-                u.w = pack_f16(v[8 * j + 6], v[8 * j + 7]);
-            }
-            o[j] = u;
+        for (int i = 0; i < 32; ++i) {
+            if (i < rows) o[(long long)i * ld] = __float2half_rn(v[i]);
         }
     }
 }
@@ -181,92 +155,69 @@ __device__ __forceinline__ uint32_t h2_sub_fma(uint32_t packed, __half2 bias, __
     return *reinterpret_cast<uint32_t*>(&h);
 }
 
-// q8_0: 128 rows x 64 int8 -> 128 rows x 64 f16 in the swizzled operand layout.
-__device__ __forceinline__ void dequant_q8_0(const uint8_t* wq, const __half* sc, uint8_t* bdst, int dq_tid) {
+// q8_0 tile record: payload [c][r][16 int8], scales [h][r] f16.  Thread (row r,
+// half h) converts weights h*32 .. h*32+31 of its row into 16 packed f16 pairs.
+__device__ __forceinline__ void dequant_q8_0(const uint8_t* tile, int r, int h, uint32_t (&o)[16]) {
     const __half2 k1152 = __float2half2_rn(1152.0f);
+    const __half2 d2 = __half2half2(*reinterpret_cast<const __half*>(tile + 8192 + (h * 128 + r) * 2));
 #pragma unroll
-    for (int it = 0; it < BN * 4 / 256; ++it) {
-        const int id = it * 256 + dq_tid;
-        const int row = id >> 2;
-        const int c = id & 3;
-        const uint4 raw = *reinterpret_cast<const uint4*>(wq + row * 64 + c * 16);
-        const __half2 d2 = __half2half2(sc[(c >> 1) * BN + row]);
+    for (int cc = 0; cc < 2; ++cc) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(tile + ((2 * h + cc) * 128 + r) * 16);
         const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-        uint32_t o[8];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const uint32_t x = w[j] ^ 0x80808080u;                       // q + 128 in each byte
             const uint32_t lo = __byte_perm(x, 0x64646464u, 0x4140);      // f16 (1024 + u0, 1024 + u1)
             const uint32_t hi = __byte_perm(x, 0x64646464u, 0x4342);
-            o[2 * j + 0] = h2_sub_mul(lo, k1152, d2);
-            o[2 * j + 1] = h2_sub_mul(hi, k1152, d2);
+            o[cc * 8 + 2 * j + 0] = h2_sub_mul(lo, k1152, d2);
+            o[cc * 8 + 2 * j + 1] = h2_sub_mul(hi, k1152, d2);
         }
-        const uint32_t rbase = (row >> 3) * 1024 + (row & 7) * 128;
-        const uint32_t sw = row & 7;
-        *reinterpret_cast<uint4*>(bdst + rbase + (((2 * c + 0) ^ sw) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
-        *reinterpret_cast<uint4*>(bdst + rbase + (((2 * c + 1) ^ sw) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
     }
 }
 
-// q4_K: 128 rows x 32 bytes; byte i of a row holds weight k=i (low nibble, first
-// 32-block) and weight k=32+i (high nibble, second 32-block).
-__device__ __forceinline__ void dequant_q4_k(const uint8_t* wq, const __half* sa, const __half* sb, uint8_t* bdst,
-                                             int dq_tid) {
+// q4_K tile record: payload [c][r][16 B] (low nibble = weight c*16+i, high nibble
+// = weight 32+c*16+i), a [h][r] f16 at +4096, b [h][r] f16 at +4608.
+__device__ __forceinline__ void dequant_q4_k(const uint8_t* tile, int r, int h, uint32_t (&o)[16]) {
     const __half2 k1024 = __float2half2_rn(1024.0f);
+    const __half2 a2 = __half2half2(*reinterpret_cast<const __half*>(tile + 4096 + (h * 128 + r) * 2));
+    const __half2 nb2 = __hneg2(__half2half2(*reinterpret_cast<const __half*>(tile + 4608 + (h * 128 + r) * 2)));
 #pragma unroll
-    for (int it = 0; it < BN * 2 / 256; ++it) {
-        const int id = it * 256 + dq_tid;
-        const int row = id >> 1;
-        const int c = id & 1;  // bytes c*16 .. c*16+15
-        const uint4 raw = *reinterpret_cast<const uint4*>(wq + row * 32 + c * 16);
-        const __half2 a_lo = __half2half2(sa[row]);
-        const __half2 a_hi = __half2half2(sa[BN + row]);
-        const __half2 nb_lo = __hneg2(__half2half2(sb[row]));
-        const __half2 nb_hi = __hneg2(__half2half2(sb[BN + row]));
+    for (int cc = 0; cc < 2; ++cc) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(tile + (cc * 128 + r) * 16);
         const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-        uint32_t lo_o[8], hi_o[8];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            const uint32_t xl = w[j] & 0x0F0F0F0Fu;
-            const uint32_t xh = (w[j] >> 4) & 0x0F0F0F0Fu;
-            lo_o[2 * j + 0] = h2_sub_fma(__byte_perm(xl, 0x64646464u, 0x4140), k1024, a_lo, nb_lo);
-            lo_o[2 * j + 1] = h2_sub_fma(__byte_perm(xl, 0x64646464u, 0x4342), k1024, a_lo, nb_lo);
-            hi_o[2 * j + 0] = h2_sub_fma(__byte_perm(xh, 0x64646464u, 0x4140), k1024, a_hi, nb_hi);
-            hi_o[2 * j + 1] = h2_sub_fma(__byte_perm(xh, 0x64646464u, 0x4342), k1024, a_hi, nb_hi);
+            const uint32_t x = (h ? (w[j] >> 4) : w[j]) & 0x0F0F0F0Fu;
+            o[cc * 8 + 2 * j + 0] = h2_sub_fma(__byte_perm(x, 0x64646464u, 0x4140), k1024, a2, nb2);
+            o[cc * 8 + 2 * j + 1] = h2_sub_fma(__byte_perm(x, 0x64646464u, 0x4342), k1024, a2, nb2);
         }
-        const uint32_t rbase = (row >> 3) * 1024 + (row & 7) * 128;
-        const uint32_t sw = row & 7;
-        // low nibbles: k = c*16 .. c*16+15 -> 16-byte chunks 2c, 2c+1; high: k+32 -> chunks 4+2c, 5+2c
-        *reinterpret_cast<uint4*>(bdst + rbase + (((2 * c + 0) ^ sw) << 4)) =
-            make_uint4(lo_o[0], lo_o[1], lo_o[2], lo_o[3]);
-        *reinterpret_cast<uint4*>(bdst + rbase + (((2 * c + 1) ^ sw) << 4)) =
-            make_uint4(lo_o[4], lo_o[5], lo_o[6], lo_o[7]);
-        *reinterpret_cast<uint4*>(bdst + rbase + (((4 + 2 * c + 0) ^ sw) << 4)) =
-            make_uint4(hi_o[0], hi_o[1], hi_o[2], hi_o[3]);
-        *reinterpret_cast<uint4*>(bdst + rbase + (((4 + 2 * c + 1) ^ sw) << 4)) =
-            make_uint4(hi_o[4], hi_o[5], hi_o[6], hi_o[7]);
     }
+}
+
+// 1-D bulk copy global -> shared, completion counted on an mbarrier (no multicast).
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes), "r"(smem_u32(bar))
+        : "memory");
 }
 
 template <int WT>  // EDB200_TYPE_Q8_0 or EDB200_TYPE_Q4_K
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-qgemm_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ CUtensorMap map_q0,
-             const __grid_constant__ CUtensorMap map_sa0, const __grid_constant__ CUtensorMap map_sb0,
-             const __grid_constant__ CUtensorMap map_a1, const __grid_constant__ CUtensorMap map_q1,
-             const __grid_constant__ CUtensorMap map_sa1, const __grid_constant__ CUtensorMap map_sb1,
+qgemm_kernel(const __grid_constant__ CUtensorMap map_x0, const __grid_constant__ CUtensorMap map_x1,
              const __grid_constant__ Params P) {
     constexpr bool kQ4 = (WT == EDB200_TYPE_Q4_K);
-    constexpr uint32_t kWqStageBytes = kQ4 ? (BN * BK / 2) : (BN * BK);
-    constexpr uint32_t kTxBytes = A_BYTES + kWqStageBytes + (kQ4 ? 2 : 1) * SC_PLANE_BYTES;
+    constexpr uint32_t kWBytes = kQ4 ? kQwTileBytesQ4 : kQwTileBytesQ8;
+    constexpr uint32_t kTxBytes = X_BYTES + kWBytes;
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
     uint64_t* ld_full = bars;                       // [LD_STAGES]
     uint64_t* ld_empty = ld_full + LD_STAGES;       // [LD_STAGES]
-    uint64_t* b_full = ld_empty + LD_STAGES;        // [B_STAGES]
-    uint64_t* b_empty = b_full + B_STAGES;          // [B_STAGES]
-    uint64_t* acc_full = b_empty + B_STAGES;        // [ACC_STAGES]
+    uint64_t* a_full = ld_empty + LD_STAGES;        // [A_STAGES]
+    uint64_t* a_empty = a_full + A_STAGES;          // [A_STAGES]
+    uint64_t* acc_full = a_empty + A_STAGES;        // [ACC_STAGES]
     uint64_t* acc_empty = acc_full + ACC_STAGES;    // [ACC_STAGES]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + ACC_STAGES);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -279,9 +230,9 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__
             mbar_init(&ld_full[i], 1);
             mbar_init(&ld_empty[i], 1 + DQ_WARPS);
         }
-        for (int i = 0; i < B_STAGES; ++i) {
-            mbar_init(&b_full[i], DQ_WARPS);
-            mbar_init(&b_empty[i], 1);
+        for (int i = 0; i < A_STAGES; ++i) {
+            mbar_init(&a_full[i], DQ_WARPS);
+            mbar_init(&a_empty[i], 1);
         }
         for (int i = 0; i < ACC_STAGES; ++i) {
             mbar_init(&acc_full[i], 1);
@@ -295,14 +246,8 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__
         tmem_relinquish();
     }
     if (warp == 0 && lane == 0) {
-        tma_prefetch_desc(&map_a0);
-        tma_prefetch_desc(&map_q0);
-        tma_prefetch_desc(&map_sa0);
-        if (P.total_tiles > P.tiles0) {
-            tma_prefetch_desc(&map_a1);
-            tma_prefetch_desc(&map_q1);
-            tma_prefetch_desc(&map_sa1);
-        }
+        tma_prefetch_desc(&map_x0);
+        if (P.total_tiles > P.tiles0) tma_prefetch_desc(&map_x1);
     }
     tc_fence_before_sync();
     __syncthreads();
@@ -310,29 +255,25 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0) {
-        // ------------------------------------------------------ TMA producer
+        // ---------------------------------------------------------- producer
         if (lane == 0) {
             uint32_t s = 0, ph = 0;
             bool ok = true;
             for (int t = blockIdx.x; ok && t < P.total_tiles; t += gridDim.x) {
                 const TileCoord tc = tile_coord(P, t);
-                const int ksteps = (tc.prob ? P.p[1].K : P.p[0].K) / BK;
-                const CUtensorMap* ma = tc.prob ? &map_a1 : &map_a0;
-                const CUtensorMap* mq = tc.prob ? &map_q1 : &map_q0;
-                const CUtensorMap* msa = tc.prob ? &map_sa1 : &map_sa0;
-                const CUtensorMap* msb = tc.prob ? &map_sb1 : &map_sb0;
+                const Problem& pr = tc.prob ? P.p[1] : P.p[0];
+                const int ksteps = pr.K / BK;
+                const CUtensorMap* mx = tc.prob ? &map_x1 : &map_x0;
+                const uint8_t* wsrc = pr.tiles + (long long)tc.n_tile * ksteps * kWBytes;
                 for (int ks = 0; ks < ksteps; ++ks) {
                     if (!mbar_wait(&ld_empty[s], ph ^ 1u, abort_flag, P.err)) {
                         ok = false;
                         break;
                     }
+                    uint8_t* stage = smem + s * STAGE_BYTES;
                     mbar_arrive_expect_tx(&ld_full[s], kTxBytes);
-                    tma_load_2d(smem + OFF_A + s * A_BYTES, ma, &ld_full[s], ks * BK, tc.m0);
-                    tma_load_2d(smem + OFF_W + s * WQ_BYTES, mq, &ld_full[s], kQ4 ? ks * (BK / 2) : ks * BK, tc.n0);
-                    tma_load_2d(smem + OFF_S + s * SC_BYTES, msa, &ld_full[s], tc.n0, ks * 2);
-                    if (kQ4) {
-                        tma_load_2d(smem + OFF_S + s * SC_BYTES + SC_PLANE_BYTES, msb, &ld_full[s], tc.n0, ks * 2);
-                    }
+                    tma_load_2d(stage, mx, &ld_full[s], ks * BK, tc.m0);
+                    bulk_load(stage + X_BYTES, wsrc + (long long)ks * kWBytes, kWBytes, &ld_full[s]);
                     if (++s == LD_STAGES) {
                         s = 0;
                         ph ^= 1u;
@@ -342,132 +283,130 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__
         }
     } else if (warp == 1) {
         // -------------------------------------------------------- MMA issuer
-        const uint32_t idesc = make_idesc(kDFmtF32, P.a_fmt, kFmtF16, 0, 0, MMA_M, BN);
-        uint32_t s = 0, ph = 0, bs = 0, bph = 0, as = 0, aph = 0;
+        const uint32_t idesc = make_idesc(kDFmtF32, kFmtF16, kFmtF16, 0, 0, TW, TN);
+        uint32_t s = 0, ph = 0, as = 0, aph = 0, cs = 0, cph = 0;
         bool ok = true;
         for (int t = blockIdx.x; ok && t < P.total_tiles; t += gridDim.x) {
             const TileCoord tc = tile_coord(P, t);
             const int ksteps = (tc.prob ? P.p[1].K : P.p[0].K) / BK;
-            if (!mbar_wait(&acc_empty[as], aph ^ 1u, abort_flag, P.err)) {
+            if (!mbar_wait(&acc_empty[cs], cph ^ 1u, abort_flag, P.err)) {
                 ok = false;
                 break;
             }
             tc_fence_after_sync();
-            const uint32_t tmem_d = tmem_base + as * (2 * BN);
+            const uint32_t tmem_d = tmem_base + TMEM_ACC + cs * TN;
             for (int ks = 0; ks < ksteps; ++ks) {
                 if (!mbar_wait(&ld_full[s], ph, abort_flag, P.err) ||
-                    !mbar_wait(&b_full[bs], bph, abort_flag, P.err)) {
+                    !mbar_wait(&a_full[as], aph, abort_flag, P.err)) {
                     ok = false;
                     break;
                 }
                 tc_fence_after_sync();
                 if (lane == 0) {
-                    const uint32_t a_addr = smem_u32(smem + OFF_A + s * A_BYTES);
-                    const uint32_t b_addr = smem_u32(smem + OFF_B + bs * B_BYTES);
+                    const uint32_t x_addr = smem_u32(smem + s * STAGE_BYTES);
+                    const uint32_t a_tmem = tmem_base + TMEM_A + as * (BK / 2);
 #pragma unroll
                     for (int j = 0; j < BK / 16; ++j) {
-                        const uint64_t bd = make_smem_desc_sw128(b_addr + j * 32, 16, 1024);
-#pragma unroll
-                        for (int h = 0; h < BM / MMA_M; ++h) {
-                            // rows h*128.. of the activation tile: 128 rows x 128 B further on
-                            const uint64_t ad = make_smem_desc_sw128(a_addr + h * (MMA_M * 128) + j * 32, 16, 1024);
-                            mma_f16_ss(tmem_d + h * BN, ad, bd, idesc, (ks > 0 || j > 0) ? 1u : 0u);
-                        }
+                        const uint64_t bd = make_smem_desc_sw128(x_addr + j * 32, 16, 1024);
+                        mma_f16_ts(tmem_d, a_tmem + j * 8, bd, idesc, (ks > 0 || j > 0) ? 1u : 0u);
                     }
                     mma_commit(&ld_empty[s]);
-                    mma_commit(&b_empty[bs]);
+                    mma_commit(&a_empty[as]);
                 }
                 __syncwarp();
                 if (++s == LD_STAGES) {
                     s = 0;
                     ph ^= 1u;
                 }
-                if (++bs == B_STAGES) {
-                    bs = 0;
-                    bph ^= 1u;
+                if (++as == A_STAGES) {
+                    as = 0;
+                    aph ^= 1u;
                 }
             }
             if (!ok) break;
-            if (lane == 0) mma_commit(&acc_full[as]);
+            if (lane == 0) mma_commit(&acc_full[cs]);
             __syncwarp();
-            if (++as == ACC_STAGES) {
-                as = 0;
-                aph ^= 1u;
+            if (++cs == ACC_STAGES) {
+                cs = 0;
+                cph ^= 1u;
             }
         }
     } else if (warp >= 4 && warp < 8) {
         // ----------------------------------------------------------- epilogue
         const int quarter = warp & 3;
-        uint32_t as = 0, aph = 0;
+        uint32_t cs = 0, cph = 0;
         bool ok = true;
         for (int t = blockIdx.x; ok && t < P.total_tiles; t += gridDim.x) {
             const TileCoord tc = tile_coord(P, t);
             const Problem& pr = tc.prob ? P.p[1] : P.p[0];
-            if (!mbar_wait(&acc_full[as], aph, abort_flag, P.err)) {
+            if (!mbar_wait(&acc_full[cs], cph, abort_flag, P.err)) {
                 ok = false;
                 break;
             }
             tc_fence_after_sync();
-            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + as * (2 * BN);
+            const int n = tc.n_tile * TW + quarter * 32 + lane;
+            const bool n_ok = n < pr.N;
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + TMEM_ACC + cs * TN;
 #pragma unroll 1
-            for (int hc = 0; hc < (BM / MMA_M) * (BN / 32); ++hc) {
-                const int h = hc / (BN / 32), c = hc % (BN / 32);
-                const int m = tc.m0 + h * MMA_M + quarter * 32 + lane;
-                const bool row_ok = m < pr.M;
-                const int n = tc.n0 + c * 32;
-                if (n >= pr.N) continue;   // uniform: N is a multiple of 32
-                if (tc.m0 + h * MMA_M >= pr.M) continue;   // uniform: whole half beyond the last row
+            for (int c = 0; c < TN / 32; ++c) {
+                const int m_first = tc.m0 + c * 32;
+                if (m_first >= pr.M) break;   // uniform
                 uint32_t r[32];
-                tmem_ld_32x32b_x32(taddr + h * BN + c * 32, r);
+                tmem_ld_32x32b_x32(taddr + c * 32, r);
                 tmem_wait_ld();
                 float v[32];
 #pragma unroll
                 for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-                epilogue_store(pr, v, m, n, row_ok);
+                epilogue_store(pr, v, n, m_first, n_ok);
             }
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&acc_empty[as]);
-            if (++as == ACC_STAGES) {
-                as = 0;
-                aph ^= 1u;
+            if (lane == 0) mbar_arrive(&acc_empty[cs]);
+            if (++cs == ACC_STAGES) {
+                cs = 0;
+                cph ^= 1u;
             }
         }
     } else if (warp >= 8) {
         // -------------------------------------------------------- dequantisers
-        const int dq_tid = threadIdx.x - 8 * 32;
-        uint32_t s = 0, ph = 0, bs = 0, bph = 0;
+        const int quarter = warp & 3;
+        const int h = (warp - 8) >> 2;           // which 32 of the 64 k of a step
+        const int r = quarter * 32 + lane;       // weight row of the tile = tensor-memory lane
+        const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+        uint32_t s = 0, ph = 0, as = 0, aph = 0;
         bool ok = true;
         for (int t = blockIdx.x; ok && t < P.total_tiles; t += gridDim.x) {
             const TileCoord tc = tile_coord(P, t);
             const int ksteps = (tc.prob ? P.p[1].K : P.p[0].K) / BK;
             for (int ks = 0; ks < ksteps; ++ks) {
                 if (!mbar_wait(&ld_full[s], ph, abort_flag, P.err) ||
-                    !mbar_wait(&b_empty[bs], bph ^ 1u, abort_flag, P.err)) {
+                    !mbar_wait(&a_empty[as], aph ^ 1u, abort_flag, P.err)) {
                     ok = false;
                     break;
                 }
-                const uint8_t* wq = smem + OFF_W + s * WQ_BYTES;
-                const __half* sc = reinterpret_cast<const __half*>(smem + OFF_S + s * SC_BYTES);
-                uint8_t* bdst = smem + OFF_B + bs * B_BYTES;
+                tc_fence_after_sync();
+                const uint8_t* tile = smem + s * STAGE_BYTES + X_BYTES;
+                uint32_t o[16];
                 if (kQ4) {
-                    dequant_q4_k(wq, sc, sc + 2 * BN, bdst, dq_tid);
+                    dequant_q4_k(tile, r, h, o);
                 } else {
-                    dequant_q8_0(wq, sc, bdst, dq_tid);
+                    dequant_q8_0(tile, r, h, o);
                 }
-                fence_proxy_async_smem();
+                tmem_st_32x32b_x16(tmem_base + lane_base + TMEM_A + as * (BK / 2) + h * 16, o);
+                tmem_wait_st();
+                tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) {
-                    mbar_arrive(&b_full[bs]);
+                    mbar_arrive(&a_full[as]);
                     mbar_arrive(&ld_empty[s]);
                 }
                 if (++s == LD_STAGES) {
                     s = 0;
                     ph ^= 1u;
                 }
-                if (++bs == B_STAGES) {
-                    bs = 0;
-                    bph ^= 1u;
+                if (++as == A_STAGES) {
+                    as = 0;
+                    aph ^= 1u;
                 }
             }
         }
@@ -518,7 +457,7 @@ static edb200_status_t validate_problem(const edb200_qweight_t* w, const void* x
         return fail(EDB200_ERR_INVALID, "mul_mat_q: bias must be 16-byte aligned");
     }
     if (ep->split_n > 0) {
-        if (ep->split_n % gemm::BN != 0 || ep->split_n >= w->n_out || ep->out2 == nullptr || !dt_ok(ep->out2_dtype)) {
+        if (ep->split_n % gemm::TW != 0 || ep->split_n >= w->n_out || ep->out2 == nullptr || !dt_ok(ep->out2_dtype)) {
             return fail(EDB200_ERR_INVALID, "mul_mat_q: split_n must be a multiple of 128 below n_out with out2 set");
         }
         const int esz2 = ep->out2_dtype == EDB200_TYPE_F32 ? 4 : 2;
@@ -547,8 +486,9 @@ static void fill_problem(gemm::Problem& p, const edb200_qweight_t* w, int64_t m,
     p.M = static_cast<int>(m);
     p.N = static_cast<int>(w->n_out);
     p.K = static_cast<int>(w->k);
-    p.m_tiles = static_cast<int>((m + gemm::BM - 1) / gemm::BM);
-    p.n_tiles = static_cast<int>((w->n_out + gemm::BN - 1) / gemm::BN);
+    p.tiles = w->tiles;
+    p.m_tiles = static_cast<int>((m + gemm::TN - 1) / gemm::TN);
+    p.n_tiles = static_cast<int>(w->n_tiles);
 }
 
 static edb200_status_t launch_qgemm(int nprob, const edb200_qweight_t* const* ws, const void* const* xs,
@@ -579,14 +519,12 @@ static edb200_status_t launch_qgemm(int nprob, const edb200_qweight_t* const* ws
     for (int i = 0; i < nprob; ++i) {
         fill_problem(P.p[i], ws[i], ms[i], eps[i]);
         edb200_status_t st = make_tmap_2d(&map_a[i], adt, 2, xs[i], (uint64_t)ws[i]->k, (uint64_t)ms[i],
-                                          (uint64_t)ldxs[i] * 2, gemm::BK, gemm::BM, CU_TENSOR_MAP_SWIZZLE_128B);
+                                          (uint64_t)ldxs[i] * 2, gemm::BK, gemm::TN, CU_TENSOR_MAP_SWIZZLE_128B);
         if (st != EDB200_OK) return st;
     }
     if (nprob == 1) map_a[1] = map_a[0];
-    const edb200_qweight_t* w1 = nprob == 2 ? ws[1] : ws[0];
     P.tiles0 = P.p[0].m_tiles * P.p[0].n_tiles;
     P.total_tiles = P.tiles0 + (nprob == 2 ? P.p[1].m_tiles * P.p[1].n_tiles : 0);
-    P.a_fmt = x_dtype == EDB200_TYPE_BF16 ? kFmtBF16 : kFmtF16;
     P.err = err;
 
     const int grid = P.total_tiles < sm_count() ? P.total_tiles : sm_count();
@@ -606,8 +544,7 @@ static edb200_status_t launch_qgemm(int nprob, const edb200_qweight_t* const* ws
     }
     ProfScope prof(stream, PROF_GEMM, flops, bytes);
     kern<<<grid, gemm::NUM_THREADS, gemm::SMEM_BYTES, stream>>>(
-        map_a[0], ws[0]->map_qs, ws[0]->map_sa, q4 ? ws[0]->map_sb : ws[0]->map_sa, map_a[1], w1->map_qs, w1->map_sa,
-        q4 ? w1->map_sb : w1->map_sa, P);
+        map_a[0], map_a[1], P);
     count_launch();
     return check_cuda(cudaGetLastError(), "qgemm launch");
 }

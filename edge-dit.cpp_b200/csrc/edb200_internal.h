@@ -62,24 +62,33 @@ struct ProfScope {
 
 }  // namespace edb
 
-// Repacked quantised weight (device resident).
+// Repacked quantised weight (device resident), tiled for the GEMM's
+// "one thread per weight row" dequantisers.
+//
+// The weight [n_out][k] is cut into tiles of kQwTileRows rows x kQwTileK weights.
+// Tile (t, s) = rows t*128.., weights s*64.. is one contiguous record of
+// `tile_bytes` at tiles + (t * ksteps + s) * tile_bytes, fetched with one bulk copy:
+//   q8_0 (8704 B): payload [c = 0..3][r = 0..127][16 int8]  = weights s*64 + c*16 + i of row r
+//                  scales  [h = 0..1][r] f16                 = d of 32-block 2s + h
+//   q4_K (5120 B): payload [c = 0..1][r][16 B], byte c*16+i = weight s*64+c*16+i (low nibble)
+//                  | weight s*64+32+c*16+i (high nibble): ggml's own nibble order
+//                  a [h][r] f16 = rn(d*sc), b [h][r] f16 = rn(dmin*m) of sub-block 2s + h
+//                  hdr (separate array): the 16 header bytes (d, dmin, scales[12]) of every
+//                  256-block, kept so the exact f32 dequantiser can be restated
+// Rows beyond n_out in the last tile are zero.
+constexpr int kQwTileRows = 128;
+constexpr int kQwTileK = 64;
+constexpr int kQwTileBytesQ8 = 4 * 128 * 16 + 2 * 128 * 2;          // 8704
+constexpr int kQwTileBytesQ4 = 2 * 128 * 16 + 2 * 2 * 128 * 2;      // 5120
+
 struct edb200_qweight {
     int ggml_type = 0;
     int64_t n_out = 0;
     int64_t k = 0;
-    // q8_0: qs = int8 [n_out][k]; sa = f16 scale plane [k/32][n_pad]; sb unused.
-    // q4_K: qs = packed nibbles [n_out][k/2] (two consecutive weights per byte,
-    //       low nibble first); sa = f16 (d*sc) plane, sb = f16 (dmin*m) plane,
-    //       both [k/32][n_pad]; sa32/sb32 = the same products in f32 for the
-    //       exact dequantiser.
-    void* qs = nullptr;
-    void* sa = nullptr;
-    void* sb = nullptr;
-    float* sa32 = nullptr;
-    float* sb32 = nullptr;
-    int64_t n_pad = 0;          // scale-plane row length (multiple of 8)
+    int64_t n_tiles = 0;      // ceil(n_out / 128)
+    int64_t ksteps = 0;       // k / 64
+    int tile_bytes = 0;
+    uint8_t* tiles = nullptr;
+    uint8_t* hdr = nullptr;   // q4_K only: [n_out][k/256][16]
     int64_t bytes = 0;
-    CUtensorMap map_qs;         // box {64 B, 128 rows}
-    CUtensorMap map_sa;         // box {128, 2}
-    CUtensorMap map_sb;
 };
