@@ -180,7 +180,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             if (!mbar_wait(&k_full[st], kph, abort_flag, P.err)) return false;
             if (!mbar_wait(&s_empty[sb], sph ^ 1u, abort_flag, P.err)) return false;
             tc_fence_after_sync();
-            if (lane == 0) {
+            if (elect_one()) {
                 const uint32_t k_addr = smem_u32(smem + C::OFF_K + st * C::K_BYTES);
                 const uint32_t tmem_s = tmem_base + (sb ? TMEM_S1 : TMEM_S0);
 #pragma unroll
@@ -213,7 +213,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 break;
             }
             tc_fence_after_sync();
-            if (lane == 0) {
+            if (elect_one()) {
                 const uint32_t v_addr = smem_u32(smem + C::OFF_V + st * C::V_BYTES);
 #pragma unroll
                 for (int ks = 0; ks < BKV / 16; ++ks) {

@@ -34,23 +34,26 @@ namespace edb {
 namespace gemm {
 
 constexpr int TW = 128;            // weight rows (output features) per tile = tensor-memory lanes
-constexpr int TN = 224;            // tokens per tile = accumulator columns
+constexpr int TN = 192;            // tokens per tile = accumulator columns
 constexpr int BK = 64;
+constexpr int WH = 2;              // weight tiles (128-row halves) per CTA tile, sharing one token tile
 constexpr int LD_STAGES = 5;
-constexpr int A_STAGES = 2;
-constexpr int ACC_STAGES = 2;
+constexpr int A_STAGES = 4;        // each holds 32 k of both weight halves
+constexpr int AK = 32;             // k per A stage
 constexpr int X_BYTES = TN * BK * 2;          // 28 KB
-constexpr int W_BYTES_MAX = 9216;             // weight tile record (8704 / 5120 B) padded
-constexpr int STAGE_BYTES = X_BYTES + W_BYTES_MAX;
+constexpr int W_BYTES_MAX = 8704;             // one weight tile record (8704 / 5120 B)
+constexpr int STAGE_BYTES = X_BYTES + WH * W_BYTES_MAX;   // 45 KB
 constexpr int OFF_BAR = LD_STAGES * STAGE_BYTES;
 constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;  // + alignment slack
 
-constexpr int NUM_THREADS = 512;
-constexpr int DQ_WARPS = 8;
-constexpr int EPI_WARPS = 4;
+constexpr int NUM_THREADS = 896;
+constexpr int EPI_WARPS = 8;       // warps 4-7 (weight half 0) and 8-11 (weight half 1)
+constexpr int DQ_WARPS = 16;       // warps 12-27: (lane quarter, weight half, k half of a 64-k stage)
+constexpr int DQ_WARPS_PER_STAGE = 8;   // warps that fill one A stage (one k half)
+constexpr int EC = 16;             // accumulator columns (tokens) per epilogue step
 constexpr uint32_t TMEM_COLS = 512;
-constexpr uint32_t TMEM_ACC = 0;                       // 2 x 224 columns
-constexpr uint32_t TMEM_A = ACC_STAGES * TN;           // 2 x 32 columns (64 f16 per lane)
+constexpr uint32_t TMEM_ACC = 0;                       // WH x 224 columns, one accumulator per weight half
+constexpr uint32_t TMEM_A = WH * TN;                   // A_STAGES x WH x 16 columns (32 f16 per lane each)
 
 struct Problem {
     const float* bias;
@@ -69,11 +72,12 @@ struct Params {
     Problem p[2];
     int tiles0;       // tiles of problem 0
     int total_tiles;
+    int dbg;          // EDB_DBG timing experiments only
     int* err;
 };
 
 struct TileCoord {
-    int prob, m0, n_tile;
+    int prob, m0, n_tile;   // n_tile = first of the WH consecutive weight tiles
 };
 
 __device__ __forceinline__ TileCoord tile_coord(const Params& P, int t) {
@@ -82,7 +86,7 @@ __device__ __forceinline__ TileCoord tile_coord(const Params& P, int t) {
     const int tt = c.prob ? t - P.tiles0 : t;
     const int m_tiles = c.prob ? P.p[1].m_tiles : P.p[0].m_tiles;
     // token tile fastest: CTAs running at the same time share one weight tile row through L2.
-    c.n_tile = tt / m_tiles;
+    c.n_tile = (tt / m_tiles) * WH;
     c.m0 = (tt % m_tiles) * TN;
     return c;
 }
@@ -100,20 +104,20 @@ __device__ __forceinline__ float apply_act(float v, int act) {
     return v;
 }
 
-// 32 tokens (m_first..m_first+31) of one output feature n; lanes of a warp hold
+// EC tokens (m_first..) of one output feature n; lanes of a warp hold
 // consecutive n, so every global access below is contiguous across the warp.
-__device__ __forceinline__ void epilogue_store(const Problem& P, float (&v)[32], int n, int m_first, bool n_ok) {
+__device__ __forceinline__ void epilogue_store(const Problem& P, float (&v)[EC], int n, int m_first, bool n_ok) {
     const bool second = (P.split_n > 0) && (n >= P.split_n);
     const int act = second ? P.act2 : P.act;
     const float b = (P.bias != nullptr && n_ok) ? __ldg(P.bias + n) : 0.0f;
 #pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = apply_act(v[i] + b, act);
-    const int rows = min(32, P.M - m_first);   // uniform across the warp
+    for (int i = 0; i < EC; ++i) v[i] = apply_act(v[i] + b, act);
+    const int rows = min(EC, P.M - m_first);   // uniform across the warp
     if (!second && P.gate != nullptr) {
         const float g = n_ok ? __ldg(P.gate + n) : 0.0f;
         const float* rp = P.residual + (long long)m_first * P.ld_res + n;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
+        for (int i = 0; i < EC; ++i) {
             if (i < rows && n_ok) v[i] = rp[(long long)i * P.ld_res] + g * v[i];
         }
     }
@@ -125,19 +129,19 @@ __device__ __forceinline__ void epilogue_store(const Problem& P, float (&v)[32],
     if (dt == EDB200_TYPE_F32) {
         float* o = reinterpret_cast<float*>(base) + (long long)m_first * ld + col;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
+        for (int i = 0; i < EC; ++i) {
             if (i < rows) o[(long long)i * ld] = v[i];
         }
     } else if (dt == EDB200_TYPE_BF16) {
         __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(base) + (long long)m_first * ld + col;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
+        for (int i = 0; i < EC; ++i) {
             if (i < rows) o[(long long)i * ld] = __float2bfloat16_rn(v[i]);
         }
     } else {
         __half* o = reinterpret_cast<__half*>(base) + (long long)m_first * ld + col;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
+        for (int i = 0; i < EC; ++i) {
             if (i < rows) o[(long long)i * ld] = __float2half_rn(v[i]);
         }
     }
@@ -208,7 +212,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x0, const __grid_constant__
              const __grid_constant__ Params P) {
     constexpr bool kQ4 = (WT == EDB200_TYPE_Q4_K);
     constexpr uint32_t kWBytes = kQ4 ? kQwTileBytesQ4 : kQwTileBytesQ8;
-    constexpr uint32_t kTxBytes = X_BYTES + kWBytes;
+    constexpr uint32_t kTxBytes = X_BYTES + WH * kWBytes;
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -217,9 +221,9 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x0, const __grid_constant__
     uint64_t* ld_empty = ld_full + LD_STAGES;       // [LD_STAGES]
     uint64_t* a_full = ld_empty + LD_STAGES;        // [A_STAGES]
     uint64_t* a_empty = a_full + A_STAGES;          // [A_STAGES]
-    uint64_t* acc_full = a_empty + A_STAGES;        // [ACC_STAGES]
-    uint64_t* acc_empty = acc_full + ACC_STAGES;    // [ACC_STAGES]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + ACC_STAGES);
+    uint64_t* acc_full = a_empty + A_STAGES;        // [1]
+    uint64_t* acc_empty = acc_full + 1;             // [1]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5;
@@ -231,13 +235,11 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x0, const __grid_constant__
             mbar_init(&ld_empty[i], 1 + DQ_WARPS);
         }
         for (int i = 0; i < A_STAGES; ++i) {
-            mbar_init(&a_full[i], DQ_WARPS);
+            mbar_init(&a_full[i], DQ_WARPS_PER_STAGE);
             mbar_init(&a_empty[i], 1);
         }
-        for (int i = 0; i < ACC_STAGES; ++i) {
-            mbar_init(&acc_full[i], 1);
-            mbar_init(&acc_empty[i], EPI_WARPS);
-        }
+        mbar_init(acc_full, 1);
+        mbar_init(acc_empty, EPI_WARPS);
         *abort_flag = 0;
         fence_mbar_init();
     }
@@ -271,9 +273,21 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x0, const __grid_constant__
                         break;
                     }
                     uint8_t* stage = smem + s * STAGE_BYTES;
+                    if (P.dbg & 2) {
+                        mbar_arrive(&ld_full[s]);
+                        if (++s == LD_STAGES) {
+                            s = 0;
+                            ph ^= 1u;
+                        }
+                        continue;
+                    }
                     mbar_arrive_expect_tx(&ld_full[s], kTxBytes);
                     tma_load_2d(stage, mx, &ld_full[s], ks * BK, tc.m0);
-                    bulk_load(stage + X_BYTES, wsrc + (long long)ks * kWBytes, kWBytes, &ld_full[s]);
+#pragma unroll
+                    for (int hw = 0; hw < WH; ++hw) {
+                        bulk_load(stage + X_BYTES + hw * W_BYTES_MAX,
+                                  wsrc + ((long long)hw * ksteps + ks) * kWBytes, kWBytes, &ld_full[s]);
+                    }
                     if (++s == LD_STAGES) {
                         s = 0;
                         ph ^= 1u;
@@ -284,129 +298,149 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x0, const __grid_constant__
     } else if (warp == 1) {
         // -------------------------------------------------------- MMA issuer
         const uint32_t idesc = make_idesc(kDFmtF32, kFmtF16, kFmtF16, 0, 0, TW, TN);
-        uint32_t s = 0, ph = 0, as = 0, aph = 0, cs = 0, cph = 0;
+        uint32_t s = 0, ph = 0, as = 0, aph = 0, cph = 0;
         bool ok = true;
         for (int t = blockIdx.x; ok && t < P.total_tiles; t += gridDim.x) {
             const TileCoord tc = tile_coord(P, t);
             const int ksteps = (tc.prob ? P.p[1].K : P.p[0].K) / BK;
-            if (!mbar_wait(&acc_empty[cs], cph ^ 1u, abort_flag, P.err)) {
+            if (!mbar_wait(acc_empty, cph ^ 1u, abort_flag, P.err)) {
                 ok = false;
                 break;
             }
             tc_fence_after_sync();
-            const uint32_t tmem_d = tmem_base + TMEM_ACC + cs * TN;
-            for (int ks = 0; ks < ksteps; ++ks) {
-                if (!mbar_wait(&ld_full[s], ph, abort_flag, P.err) ||
-                    !mbar_wait(&a_full[as], aph, abort_flag, P.err)) {
+            for (int ks = 0; ok && ks < ksteps; ++ks) {
+                if (!mbar_wait(&ld_full[s], ph, abort_flag, P.err)) {
                     ok = false;
                     break;
                 }
-                tc_fence_after_sync();
-                if (lane == 0) {
-                    const uint32_t x_addr = smem_u32(smem + s * STAGE_BYTES);
-                    const uint32_t a_tmem = tmem_base + TMEM_A + as * (BK / 2);
+                const uint32_t x_addr = smem_u32(smem + s * STAGE_BYTES);
 #pragma unroll
-                    for (int j = 0; j < BK / 16; ++j) {
-                        const uint64_t bd = make_smem_desc_sw128(x_addr + j * 32, 16, 1024);
-                        mma_f16_ts(tmem_d, a_tmem + j * 8, bd, idesc, (ks > 0 || j > 0) ? 1u : 0u);
+                for (int kh = 0; kh < BK / AK; ++kh) {
+                    if (!mbar_wait(&a_full[as], aph, abort_flag, P.err)) {
+                        ok = false;
+                        break;
                     }
-                    mma_commit(&ld_empty[s]);
-                    mma_commit(&a_empty[as]);
+                    tc_fence_after_sync();
+                    if (elect_one()) {
+#pragma unroll
+                        for (int j = 0; j < AK / 16; ++j) {
+                            const uint64_t bd = make_smem_desc_sw128(x_addr + (kh * (AK / 16) + j) * 32, 16, 1024);
+#pragma unroll
+                            for (int hw = 0; hw < WH; ++hw) {
+                                const uint32_t a_tmem = tmem_base + TMEM_A + as * (WH * 16) + hw * 16 + j * 8;
+                                mma_f16_ts(tmem_base + TMEM_ACC + hw * TN, a_tmem, bd, idesc,
+                                           (ks > 0 || kh > 0 || j > 0) ? 1u : 0u);
+                            }
+                        }
+                        mma_commit(&a_empty[as]);
+                        if (kh == BK / AK - 1) mma_commit(&ld_empty[s]);
+                    }
+                    __syncwarp();
+                    if (++as == A_STAGES) {
+                        as = 0;
+                        aph ^= 1u;
+                    }
                 }
-                __syncwarp();
                 if (++s == LD_STAGES) {
                     s = 0;
                     ph ^= 1u;
                 }
-                if (++as == A_STAGES) {
-                    as = 0;
-                    aph ^= 1u;
-                }
             }
             if (!ok) break;
-            if (lane == 0) mma_commit(&acc_full[cs]);
+            if (elect_one()) mma_commit(acc_full);
             __syncwarp();
-            if (++cs == ACC_STAGES) {
-                cs = 0;
-                cph ^= 1u;
-            }
+            cph ^= 1u;
         }
-    } else if (warp >= 4 && warp < 8) {
+    } else if (warp >= 4 && warp < 12) {
         // ----------------------------------------------------------- epilogue
         const int quarter = warp & 3;
-        uint32_t cs = 0, cph = 0;
+        const int hw = warp >= 8 ? 1 : 0;        // weight half this warp drains
+        uint32_t cph = 0;
         bool ok = true;
         for (int t = blockIdx.x; ok && t < P.total_tiles; t += gridDim.x) {
             const TileCoord tc = tile_coord(P, t);
             const Problem& pr = tc.prob ? P.p[1] : P.p[0];
-            if (!mbar_wait(&acc_full[cs], cph, abort_flag, P.err)) {
+            if (!mbar_wait(acc_full, cph, abort_flag, P.err)) {
                 ok = false;
                 break;
             }
             tc_fence_after_sync();
-            const int n = tc.n_tile * TW + quarter * 32 + lane;
+            const int n = (tc.n_tile + hw) * TW + quarter * 32 + lane;
             const bool n_ok = n < pr.N;
-            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + TMEM_ACC + cs * TN;
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + TMEM_ACC + hw * TN;
+            if ((tc.n_tile + hw) * TW < pr.N) {   // uniform: the whole half may lie beyond N
 #pragma unroll 1
-            for (int c = 0; c < TN / 32; ++c) {
-                const int m_first = tc.m0 + c * 32;
-                if (m_first >= pr.M) break;   // uniform
-                uint32_t r[32];
-                tmem_ld_32x32b_x32(taddr + c * 32, r);
-                tmem_wait_ld();
-                float v[32];
+                for (int c = 0; c < TN / EC; ++c) {
+                    const int m_first = tc.m0 + c * EC;
+                    if (m_first >= pr.M || (P.dbg & 8)) break;   // uniform
+                    uint32_t r[EC];
+                    tmem_ld_32x32b_x16(taddr + c * EC, r);
+                    tmem_wait_ld();
+                    float v[EC];
 #pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-                epilogue_store(pr, v, n, m_first, n_ok);
+                    for (int j = 0; j < EC; ++j) v[j] = __uint_as_float(r[j]);
+                    epilogue_store(pr, v, n, m_first, n_ok);
+                }
             }
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&acc_empty[cs]);
-            if (++cs == ACC_STAGES) {
-                cs = 0;
-                cph ^= 1u;
-            }
+            if (lane == 0) mbar_arrive(acc_empty);
+            cph ^= 1u;
         }
-    } else if (warp >= 8) {
+    } else if (warp >= 12) {
         // -------------------------------------------------------- dequantisers
+        // Every warp owns one k half (32 k) of every 64-k stage, so consecutive A
+        // stages are filled by different warps and a warp has a whole stage's MMA
+        // time for its load -> convert -> tcgen05.st -> arrive chain.
         const int quarter = warp & 3;
-        const int h = (warp - 8) >> 2;           // which 32 of the 64 k of a step
+        const int hw = ((warp - 12) >> 2) & 1;   // weight half
+        const int kh = (warp - 12) >> 3;         // k half of each stage
         const int r = quarter * 32 + lane;       // weight row of the tile = tensor-memory lane
         const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
-        uint32_t s = 0, ph = 0, as = 0, aph = 0;
+        uint32_t s = 0, ph = 0;
+        uint32_t kstep_total = 0;   // 64-k stages processed so far (all tiles)
         bool ok = true;
         for (int t = blockIdx.x; ok && t < P.total_tiles; t += gridDim.x) {
             const TileCoord tc = tile_coord(P, t);
             const int ksteps = (tc.prob ? P.p[1].K : P.p[0].K) / BK;
-            for (int ks = 0; ks < ksteps; ++ks) {
-                if (!mbar_wait(&ld_full[s], ph, abort_flag, P.err) ||
-                    !mbar_wait(&a_empty[as], aph ^ 1u, abort_flag, P.err)) {
+            for (int ks = 0; ok && ks < ksteps; ++ks) {
+                if (!mbar_wait(&ld_full[s], ph, abort_flag, P.err)) {
                     ok = false;
                     break;
                 }
-                tc_fence_after_sync();
-                const uint8_t* tile = smem + s * STAGE_BYTES + X_BYTES;
-                uint32_t o[16];
-                if (kQ4) {
-                    dequant_q4_k(tile, r, h, o);
-                } else {
-                    dequant_q8_0(tile, r, h, o);
+                const uint8_t* tile = smem + s * STAGE_BYTES + X_BYTES + hw * W_BYTES_MAX;
+                {
+                    uint32_t o[16];
+                    if (P.dbg & 1) {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) o[i] = 0;
+                    } else if (kQ4) {
+                        dequant_q4_k(tile, r, kh, o);
+                    } else {
+                        dequant_q8_0(tile, r, kh, o);
+                    }
+                    // this warp's A stage of step ks: stages alternate between the two k halves
+                    const uint32_t as = (2u * static_cast<uint32_t>(kstep_total) + kh) % A_STAGES;
+                    const uint32_t aph = ((2u * static_cast<uint32_t>(kstep_total) + kh) / A_STAGES) & 1u;
+                    if (!mbar_wait(&a_empty[as], aph ^ 1u, abort_flag, P.err)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    if (!(P.dbg & 4)) {
+                        tmem_st_32x32b_x16(tmem_base + lane_base + TMEM_A + as * (WH * 16) + hw * 16, o);
+                        tmem_wait_st();
+                    }
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&a_full[as]);
+                    ++kstep_total;
                 }
-                tmem_st_32x32b_x16(tmem_base + lane_base + TMEM_A + as * (BK / 2) + h * 16, o);
-                tmem_wait_st();
-                tc_fence_before_sync();
                 __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive(&a_full[as]);
-                    mbar_arrive(&ld_empty[s]);
-                }
+                if (lane == 0) mbar_arrive(&ld_empty[s]);
                 if (++s == LD_STAGES) {
                     s = 0;
                     ph ^= 1u;
-                }
-                if (++as == A_STAGES) {
-                    as = 0;
-                    aph ^= 1u;
                 }
             }
         }
@@ -488,7 +522,7 @@ static void fill_problem(gemm::Problem& p, const edb200_qweight_t* w, int64_t m,
     p.K = static_cast<int>(w->k);
     p.tiles = w->tiles;
     p.m_tiles = static_cast<int>((m + gemm::TN - 1) / gemm::TN);
-    p.n_tiles = static_cast<int>(w->n_tiles);
+    p.n_tiles = static_cast<int>((w->n_tiles + gemm::WH - 1) / gemm::WH);   // CTA tiles of WH weight tiles
 }
 
 static edb200_status_t launch_qgemm(int nprob, const edb200_qweight_t* const* ws, const void* const* xs,
@@ -526,6 +560,14 @@ static edb200_status_t launch_qgemm(int nprob, const edb200_qweight_t* const* ws
     P.tiles0 = P.p[0].m_tiles * P.p[0].n_tiles;
     P.total_tiles = P.tiles0 + (nprob == 2 ? P.p[1].m_tiles * P.p[1].n_tiles : 0);
     P.err = err;
+    {
+        static int dbg = -1;
+        if (dbg < 0) {
+            const char* e = getenv("EDB200_GEMM_DEBUG");
+            dbg = e ? atoi(e) : 0;
+        }
+        P.dbg = dbg;
+    }
 
     const int grid = P.total_tiles < sm_count() ? P.total_tiles : sm_count();
     const bool q4 = ws[0]->ggml_type == EDB200_TYPE_Q4_K;

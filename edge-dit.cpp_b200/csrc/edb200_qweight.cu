@@ -268,7 +268,8 @@ edb200_status_t edb200_qweight_create(int ggml_type, const void* blocks, int64_t
     w->n_tiles = (n_out + kQwTileRows - 1) / kQwTileRows;
     w->ksteps = k / kQwTileK;
     w->tile_bytes = ggml_type == EDB200_TYPE_Q8_0 ? kQwTileBytesQ8 : kQwTileBytesQ4;
-    const int64_t tiles_bytes = w->n_tiles * w->ksteps * w->tile_bytes;
+    // one spare (zero) tile row so that the GEMM may always fetch weight tiles in pairs
+    const int64_t tiles_bytes = (w->n_tiles + (w->n_tiles & 1)) * w->ksteps * w->tile_bytes;
     const int64_t hdr_bytes = ggml_type == EDB200_TYPE_Q4_K ? n_out * (k / 256) * 16 : 0;
     cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&w->tiles), tiles_bytes);
     if (e == cudaSuccess && hdr_bytes > 0) e = cudaMalloc(reinterpret_cast<void**>(&w->hdr), hdr_bytes);
@@ -277,7 +278,7 @@ edb200_status_t edb200_qweight_create(int ggml_type, const void* blocks, int64_t
         return fail(EDB200_ERR_NOMEM, "qweight_create: cudaMalloc: %s", cudaGetErrorString(e));
     }
     w->bytes = tiles_bytes + hdr_bytes;
-    if (n_out % kQwTileRows) cudaMemsetAsync(w->tiles, 0, tiles_bytes, s);   // zero the padding rows
+    if ((n_out % kQwTileRows) || (w->n_tiles & 1)) cudaMemsetAsync(w->tiles, 0, tiles_bytes, s);   // zero the padding
     if (ggml_type == EDB200_TYPE_Q8_0) {
         const int64_t nb = n_out * (k / 32);
         repack_q8_0_kernel<<<static_cast<unsigned>((nb + 255) / 256), 256, 0, s>>>(
