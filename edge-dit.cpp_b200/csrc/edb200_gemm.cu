@@ -36,24 +36,20 @@ namespace gemm {
 constexpr int TW = 128;            // weight rows (output features) per tile = tensor-memory lanes
 constexpr int TN = 192;            // tokens per tile = accumulator columns
 constexpr int BK = 64;
-constexpr int WH = 2;              // weight tiles (128-row halves) per CTA tile, sharing one token tile
 constexpr int LD_STAGES = 5;
-constexpr int A_STAGES = 4;        // each holds 32 k of both weight halves
 constexpr int AK = 32;             // k per A stage
 constexpr int X_BYTES = TN * BK * 2;          // 28 KB
 constexpr int W_BYTES_MAX = 8704;             // one weight tile record (8704 / 5120 B)
-constexpr int STAGE_BYTES = X_BYTES + WH * W_BYTES_MAX;   // 45 KB
+constexpr int STAGE_BYTES = X_BYTES + 2 * W_BYTES_MAX;    // 41 KB (room for two weight tiles)
 constexpr int OFF_BAR = LD_STAGES * STAGE_BYTES;
 constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;  // + alignment slack
 
 constexpr int NUM_THREADS = 896;
 constexpr int EPI_WARPS = 8;       // warps 4-7 (weight half 0) and 8-11 (weight half 1)
-constexpr int DQ_WARPS = 16;       // warps 12-27: (lane quarter, weight half, k half of a 64-k stage)
-constexpr int DQ_WARPS_PER_STAGE = 8;   // warps that fill one A stage (one k half)
+constexpr int DQ_WARPS = 16;       // warps 12-27
 constexpr int EC = 16;             // accumulator columns (tokens) per epilogue step
 constexpr uint32_t TMEM_COLS = 512;
-constexpr uint32_t TMEM_ACC = 0;                       // WH x 224 columns, one accumulator per weight half
-constexpr uint32_t TMEM_A = WH * TN;                   // A_STAGES x WH x 16 columns (32 f16 per lane each)
+constexpr uint32_t TMEM_ACC = 0;                       // 384 accumulator columns, A stages above them
 
 struct Problem {
     const float* bias;
@@ -80,13 +76,13 @@ struct TileCoord {
     int prob, m0, n_tile;   // n_tile = first of the WH consecutive weight tiles
 };
 
-__device__ __forceinline__ TileCoord tile_coord(const Params& P, int t) {
+__device__ __forceinline__ TileCoord tile_coord(const Params& P, int t, int wh) {
     TileCoord c;
     c.prob = (t >= P.tiles0) ? 1 : 0;
     const int tt = c.prob ? t - P.tiles0 : t;
     const int m_tiles = c.prob ? P.p[1].m_tiles : P.p[0].m_tiles;
     // token tile fastest: CTAs running at the same time share one weight tile row through L2.
-    c.n_tile = (tt / m_tiles) * WH;
+    c.n_tile = (tt / m_tiles) * wh;
     c.m0 = (tt % m_tiles) * TN;
     return c;
 }
@@ -206,24 +202,35 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint
         : "memory");
 }
 
-template <int WT>  // EDB200_TYPE_Q8_0 or EDB200_TYPE_Q4_K
+// WH = weight tiles (128-row halves) per CTA tile.
+//   WH = 2: 256 weight rows x 192 tokens, one accumulator set (epilogue not overlapped):
+//           least operand traffic per MAC, best for long reductions
+//   WH = 1: 128 weight rows x 192 tokens, accumulators double-buffered (epilogue
+//           overlaps the next tile's main loop), twice as many tiles
+template <int WT, int WH>  // WT: EDB200_TYPE_Q8_0 or EDB200_TYPE_Q4_K
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 qgemm_kernel(const __grid_constant__ CUtensorMap map_x0, const __grid_constant__ CUtensorMap map_x1,
              const __grid_constant__ Params P) {
     constexpr bool kQ4 = (WT == EDB200_TYPE_Q4_K);
     constexpr uint32_t kWBytes = kQ4 ? kQwTileBytesQ4 : kQwTileBytesQ8;
     constexpr uint32_t kTxBytes = X_BYTES + WH * kWBytes;
+    constexpr int ACC_STAGES = WH == 1 ? 2 : 1;
+    constexpr int A_COLS = WH * 16;                  // tensor-memory columns of one A stage (32 k per weight half)
+    constexpr int A_STAGES = 128 / A_COLS;           // 8 or 4
+    constexpr uint32_t TMEM_A = 384;                 // accumulators occupy WH * ACC_STAGES * TN = 384 columns
+    constexpr int DQ_PER_LD = WH == 1 ? 8 : 16;      // dequantiser warps that read one shared-memory stage
+    static_assert(WH * ACC_STAGES * TN == 384, "tensor-memory plan");
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
     uint64_t* ld_full = bars;                       // [LD_STAGES]
     uint64_t* ld_empty = ld_full + LD_STAGES;       // [LD_STAGES]
-    uint64_t* a_full = ld_empty + LD_STAGES;        // [A_STAGES]
-    uint64_t* a_empty = a_full + A_STAGES;          // [A_STAGES]
-    uint64_t* acc_full = a_empty + A_STAGES;        // [1]
-    uint64_t* acc_empty = acc_full + 1;             // [1]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 1);
+    uint64_t* a_full = ld_empty + LD_STAGES;        // [8]
+    uint64_t* a_empty = a_full + 8;                 // [8]
+    uint64_t* acc_full = a_empty + 8;               // [2]
+    uint64_t* acc_empty = acc_full + 2;             // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5;
@@ -232,14 +239,16 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x0, const __grid_constant__
     if (threadIdx.x == 0) {
         for (int i = 0; i < LD_STAGES; ++i) {
             mbar_init(&ld_full[i], 1);
-            mbar_init(&ld_empty[i], 1 + DQ_WARPS);
+            mbar_init(&ld_empty[i], 1 + DQ_PER_LD);
         }
         for (int i = 0; i < A_STAGES; ++i) {
-            mbar_init(&a_full[i], DQ_WARPS_PER_STAGE);
+            mbar_init(&a_full[i], 4 * WH);
             mbar_init(&a_empty[i], 1);
         }
-        mbar_init(acc_full, 1);
-        mbar_init(acc_empty, EPI_WARPS);
+        for (int i = 0; i < ACC_STAGES; ++i) {
+            mbar_init(&acc_full[i], 1);
+            mbar_init(&acc_empty[i], EPI_WARPS);
+        }
         *abort_flag = 0;
         fence_mbar_init();
     }
@@ -258,29 +267,21 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x0, const __grid_constant__
 
     if (warp == 0) {
         // ---------------------------------------------------------- producer
-        if (lane == 0) {
-            uint32_t s = 0, ph = 0;
-            bool ok = true;
-            for (int t = blockIdx.x; ok && t < P.total_tiles; t += gridDim.x) {
-                const TileCoord tc = tile_coord(P, t);
-                const Problem& pr = tc.prob ? P.p[1] : P.p[0];
-                const int ksteps = pr.K / BK;
-                const CUtensorMap* mx = tc.prob ? &map_x1 : &map_x0;
-                const uint8_t* wsrc = pr.tiles + (long long)tc.n_tile * ksteps * kWBytes;
-                for (int ks = 0; ks < ksteps; ++ks) {
-                    if (!mbar_wait(&ld_empty[s], ph ^ 1u, abort_flag, P.err)) {
-                        ok = false;
-                        break;
-                    }
+        uint32_t s = 0, ph = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; ok && t < P.total_tiles; t += gridDim.x) {
+            const TileCoord tc = tile_coord(P, t, WH);
+            const Problem& pr = tc.prob ? P.p[1] : P.p[0];
+            const int ksteps = pr.K / BK;
+            const CUtensorMap* mx = tc.prob ? &map_x1 : &map_x0;
+            const uint8_t* wsrc = pr.tiles + (long long)tc.n_tile * ksteps * kWBytes;
+            for (int ks = 0; ks < ksteps; ++ks) {
+                if (!mbar_wait(&ld_empty[s], ph ^ 1u, abort_flag, P.err)) {
+                    ok = false;
+                    break;
+                }
+                if (elect_one()) {
                     uint8_t* stage = smem + s * STAGE_BYTES;
-                    if (P.dbg & 2) {
-                        mbar_arrive(&ld_full[s]);
-                        if (++s == LD_STAGES) {
-                            s = 0;
-                            ph ^= 1u;
-                        }
-                        continue;
-                    }
                     mbar_arrive_expect_tx(&ld_full[s], kTxBytes);
                     tma_load_2d(stage, mx, &ld_full[s], ks * BK, tc.m0);
 #pragma unroll
@@ -288,26 +289,30 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x0, const __grid_constant__
                         bulk_load(stage + X_BYTES + hw * W_BYTES_MAX,
                                   wsrc + ((long long)hw * ksteps + ks) * kWBytes, kWBytes, &ld_full[s]);
                     }
-                    if (++s == LD_STAGES) {
-                        s = 0;
-                        ph ^= 1u;
-                    }
+                }
+                __syncwarp();
+                if (++s == LD_STAGES) {
+                    s = 0;
+                    ph ^= 1u;
                 }
             }
         }
     } else if (warp == 1) {
         // -------------------------------------------------------- MMA issuer
+        // tcgen05 instructions are issued under elect.sync: issuing them from an
+        // `if (lane == 0)` branch costs ~100 cycles per batch on B200.
         const uint32_t idesc = make_idesc(kDFmtF32, kFmtF16, kFmtF16, 0, 0, TW, TN);
-        uint32_t s = 0, ph = 0, as = 0, aph = 0, cph = 0;
+        uint32_t s = 0, ph = 0, as = 0, aph = 0, cs = 0, cph = 0;
         bool ok = true;
         for (int t = blockIdx.x; ok && t < P.total_tiles; t += gridDim.x) {
-            const TileCoord tc = tile_coord(P, t);
+            const TileCoord tc = tile_coord(P, t, WH);
             const int ksteps = (tc.prob ? P.p[1].K : P.p[0].K) / BK;
-            if (!mbar_wait(acc_empty, cph ^ 1u, abort_flag, P.err)) {
+            if (!mbar_wait(&acc_empty[cs], cph ^ 1u, abort_flag, P.err)) {
                 ok = false;
                 break;
             }
             tc_fence_after_sync();
+            const uint32_t tmem_d = tmem_base + TMEM_ACC + cs * (WH * TN);
             for (int ks = 0; ok && ks < ksteps; ++ks) {
                 if (!mbar_wait(&ld_full[s], ph, abort_flag, P.err)) {
                     ok = false;
@@ -327,9 +332,8 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x0, const __grid_constant__
                             const uint64_t bd = make_smem_desc_sw128(x_addr + (kh * (AK / 16) + j) * 32, 16, 1024);
 #pragma unroll
                             for (int hw = 0; hw < WH; ++hw) {
-                                const uint32_t a_tmem = tmem_base + TMEM_A + as * (WH * 16) + hw * 16 + j * 8;
-                                mma_f16_ts(tmem_base + TMEM_ACC + hw * TN, a_tmem, bd, idesc,
-                                           (ks > 0 || kh > 0 || j > 0) ? 1u : 0u);
+                                const uint32_t a_tmem = tmem_base + TMEM_A + as * A_COLS + hw * 16 + j * 8;
+                                mma_f16_ts(tmem_d + hw * TN, a_tmem, bd, idesc, (ks > 0 || kh > 0 || j > 0) ? 1u : 0u);
                             }
                         }
                         mma_commit(&a_empty[as]);
@@ -347,30 +351,37 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x0, const __grid_constant__
                 }
             }
             if (!ok) break;
-            if (elect_one()) mma_commit(acc_full);
+            if (elect_one()) mma_commit(&acc_full[cs]);
             __syncwarp();
-            cph ^= 1u;
+            if (++cs == ACC_STAGES) {
+                cs = 0;
+                cph ^= 1u;
+            }
         }
     } else if (warp >= 4 && warp < 12) {
         // ----------------------------------------------------------- epilogue
+        // WH = 2: warps 4-7 drain weight half 0, warps 8-11 half 1.
+        // WH = 1: both warp sets drain the one half, alternating 16-token steps.
         const int quarter = warp & 3;
-        const int hw = warp >= 8 ? 1 : 0;        // weight half this warp drains
-        uint32_t cph = 0;
+        const int set = warp >= 8 ? 1 : 0;
+        const int hw = WH == 2 ? set : 0;
+        uint32_t cs = 0, cph = 0;
         bool ok = true;
         for (int t = blockIdx.x; ok && t < P.total_tiles; t += gridDim.x) {
-            const TileCoord tc = tile_coord(P, t);
+            const TileCoord tc = tile_coord(P, t, WH);
             const Problem& pr = tc.prob ? P.p[1] : P.p[0];
-            if (!mbar_wait(acc_full, cph, abort_flag, P.err)) {
+            if (!mbar_wait(&acc_full[cs], cph, abort_flag, P.err)) {
                 ok = false;
                 break;
             }
             tc_fence_after_sync();
             const int n = (tc.n_tile + hw) * TW + quarter * 32 + lane;
             const bool n_ok = n < pr.N;
-            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + TMEM_ACC + hw * TN;
+            const uint32_t taddr =
+                tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + TMEM_ACC + (cs * WH + hw) * TN;
             if ((tc.n_tile + hw) * TW < pr.N) {   // uniform: the whole half may lie beyond N
 #pragma unroll 1
-                for (int c = 0; c < TN / EC; ++c) {
+                for (int c = (WH == 1 ? set : 0); c < TN / EC; c += (WH == 1 ? 2 : 1)) {
                     const int m_first = tc.m0 + c * EC;
                     if (m_first >= pr.M || (P.dbg & 8)) break;   // uniform
                     uint32_t r[EC];
@@ -384,63 +395,65 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x0, const __grid_constant__
             }
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(acc_empty);
-            cph ^= 1u;
+            if (lane == 0) mbar_arrive(&acc_empty[cs]);
+            if (++cs == ACC_STAGES) {
+                cs = 0;
+                cph ^= 1u;
+            }
         }
     } else if (warp >= 12) {
         // -------------------------------------------------------- dequantisers
-        // Every warp owns one k half (32 k) of every 64-k stage, so consecutive A
-        // stages are filled by different warps and a warp has a whole stage's MMA
-        // time for its load -> convert -> tcgen05.st -> arrive chain.
+        // Every warp converts 32 k of 32 weight rows per job and has a whole 64-k
+        // stage's MMA time (or two, WH = 1) for its load -> convert -> tcgen05.st ->
+        // arrive chain, so the chain's latency stays off the tensor pipe's critical path.
+        //   WH = 2: warp = (lane quarter, weight half, k half), works on every stage
+        //   WH = 1: warp = (lane quarter, k half, stage parity), works on every other stage
         const int quarter = warp & 3;
-        const int hw = ((warp - 12) >> 2) & 1;   // weight half
-        const int kh = (warp - 12) >> 3;         // k half of each stage
+        const int b2 = ((warp - 12) >> 2) & 1;
+        const int b3 = (warp - 12) >> 3;
+        const int hw = WH == 2 ? b2 : 0;
+        const int kh = WH == 2 ? b3 : b2;
+        const uint32_t par = WH == 2 ? 0u : static_cast<uint32_t>(b3);
         const int r = quarter * 32 + lane;       // weight row of the tile = tensor-memory lane
         const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
-        uint32_t s = 0, ph = 0;
-        uint32_t kstep_total = 0;   // 64-k stages processed so far (all tiles)
+        uint32_t g = 0;   // 64-k stages seen so far (all tiles)
         bool ok = true;
         for (int t = blockIdx.x; ok && t < P.total_tiles; t += gridDim.x) {
-            const TileCoord tc = tile_coord(P, t);
+            const TileCoord tc = tile_coord(P, t, WH);
             const int ksteps = (tc.prob ? P.p[1].K : P.p[0].K) / BK;
-            for (int ks = 0; ok && ks < ksteps; ++ks) {
+            for (int ks = 0; ok && ks < ksteps; ++ks, ++g) {
+                if (WH == 1 && (g & 1u) != par) continue;
+                const uint32_t s = g % LD_STAGES;
+                const uint32_t ph = (g / LD_STAGES) & 1u;
                 if (!mbar_wait(&ld_full[s], ph, abort_flag, P.err)) {
                     ok = false;
                     break;
                 }
                 const uint8_t* tile = smem + s * STAGE_BYTES + X_BYTES + hw * W_BYTES_MAX;
-                {
-                    uint32_t o[16];
-                    if (P.dbg & 1) {
+                uint32_t o[16];
+                if (P.dbg & 1) {
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) o[i] = 0;
-                    } else if (kQ4) {
-                        dequant_q4_k(tile, r, kh, o);
-                    } else {
-                        dequant_q8_0(tile, r, kh, o);
-                    }
-                    // this warp's A stage of step ks: stages alternate between the two k halves
-                    const uint32_t as = (2u * static_cast<uint32_t>(kstep_total) + kh) % A_STAGES;
-                    const uint32_t aph = ((2u * static_cast<uint32_t>(kstep_total) + kh) / A_STAGES) & 1u;
-                    if (!mbar_wait(&a_empty[as], aph ^ 1u, abort_flag, P.err)) {
-                        ok = false;
-                        break;
-                    }
-                    tc_fence_after_sync();
-                    if (!(P.dbg & 4)) {
-                        tmem_st_32x32b_x16(tmem_base + lane_base + TMEM_A + as * (WH * 16) + hw * 16, o);
-                        tmem_wait_st();
-                    }
-                    tc_fence_before_sync();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&a_full[as]);
-                    ++kstep_total;
+                    for (int i = 0; i < 16; ++i) o[i] = 0;
+                } else if (kQ4) {
+                    dequant_q4_k(tile, r, kh, o);
+                } else {
+                    dequant_q8_0(tile, r, kh, o);
                 }
+                const uint32_t ai = 2u * g + kh;                 // running A stage number
+                const uint32_t as = ai % A_STAGES;
+                const uint32_t aph = (ai / A_STAGES) & 1u;
+                if (!mbar_wait(&a_empty[as], aph ^ 1u, abort_flag, P.err)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after_sync();
+                tmem_st_32x32b_x16(tmem_base + lane_base + TMEM_A + as * A_COLS + hw * 16, o);
+                tmem_wait_st();
+                tc_fence_before_sync();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&ld_empty[s]);
-                if (++s == LD_STAGES) {
-                    s = 0;
-                    ph ^= 1u;
+                if (lane == 0) {
+                    mbar_arrive(&a_full[as]);
+                    mbar_arrive(&ld_empty[s]);
                 }
             }
         }
@@ -503,7 +516,8 @@ static edb200_status_t validate_problem(const edb200_qweight_t* w, const void* x
     return EDB200_OK;
 }
 
-static void fill_problem(gemm::Problem& p, const edb200_qweight_t* w, int64_t m, const edb200_epilogue_t* ep) {
+static void fill_problem(gemm::Problem& p, const edb200_qweight_t* w, int64_t m, const edb200_epilogue_t* ep,
+                         int wh) {
     p.bias = ep->bias;
     p.out = ep->out;
     p.residual = ep->residual;
@@ -522,7 +536,7 @@ static void fill_problem(gemm::Problem& p, const edb200_qweight_t* w, int64_t m,
     p.K = static_cast<int>(w->k);
     p.tiles = w->tiles;
     p.m_tiles = static_cast<int>((m + gemm::TN - 1) / gemm::TN);
-    p.n_tiles = static_cast<int>((w->n_tiles + gemm::WH - 1) / gemm::WH);   // CTA tiles of WH weight tiles
+    p.n_tiles = static_cast<int>((w->n_tiles + wh - 1) / wh);   // CTA tiles of `wh` weight tiles
 }
 
 static edb200_status_t launch_qgemm(int nprob, const edb200_qweight_t* const* ws, const void* const* xs,
@@ -545,13 +559,25 @@ static edb200_status_t launch_qgemm(int nprob, const edb200_qweight_t* const* ws
     int* err = device_error_word();
     if (err == nullptr) return fail(EDB200_ERR_CUDA, "mul_mat_q: no CUDA device");
 
+    // Two weight tiles per CTA (least operand traffic, epilogue not overlapped) pay off
+    // when the reduction is long; short reductions take one tile with double-buffered
+    // accumulators.  EDB200_GEMM_WH=1|2 overrides the choice (tuning only).
+    int wh = ws[0]->k >= 8192 ? 2 : 1;
+    {
+        static int force = -1;
+        if (force < 0) {
+            const char* e = getenv("EDB200_GEMM_WH");
+            force = e ? atoi(e) : 0;
+        }
+        if (force == 1 || force == 2) wh = force;
+    }
     gemm::Params P;
     memset(&P, 0, sizeof(P));
     CUtensorMap map_a[2];
     const CUtensorMapDataType adt =
         x_dtype == EDB200_TYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     for (int i = 0; i < nprob; ++i) {
-        fill_problem(P.p[i], ws[i], ms[i], eps[i]);
+        fill_problem(P.p[i], ws[i], ms[i], eps[i], wh);
         edb200_status_t st = make_tmap_2d(&map_a[i], adt, 2, xs[i], (uint64_t)ws[i]->k, (uint64_t)ms[i],
                                           (uint64_t)ldxs[i] * 2, gemm::BK, gemm::TN, CU_TENSOR_MAP_SWIZZLE_128B);
         if (st != EDB200_OK) return st;
@@ -571,12 +597,16 @@ static edb200_status_t launch_qgemm(int nprob, const edb200_qweight_t* const* ws
 
     const int grid = P.total_tiles < sm_count() ? P.total_tiles : sm_count();
     const bool q4 = ws[0]->ggml_type == EDB200_TYPE_Q4_K;
-    auto kern = q4 ? gemm::qgemm_kernel<EDB200_TYPE_Q4_K> : gemm::qgemm_kernel<EDB200_TYPE_Q8_0>;
-    static bool attr_set[2] = {false, false};
-    if (!attr_set[q4 ? 1 : 0]) {
+    using KernT = void (*)(const CUtensorMap, const CUtensorMap, const gemm::Params);
+    static const KernT kerns[4] = {gemm::qgemm_kernel<EDB200_TYPE_Q8_0, 1>, gemm::qgemm_kernel<EDB200_TYPE_Q8_0, 2>,
+                                   gemm::qgemm_kernel<EDB200_TYPE_Q4_K, 1>, gemm::qgemm_kernel<EDB200_TYPE_Q4_K, 2>};
+    const int ki = (q4 ? 2 : 0) + (wh - 1);
+    KernT kern = kerns[ki];
+    static bool attr_set[4] = {false, false, false, false};
+    if (!attr_set[ki]) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm::SMEM_BYTES);
         if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(qgemm)");
-        attr_set[q4 ? 1 : 0] = true;
+        attr_set[ki] = true;
     }
     double flops = 0.0, bytes = 0.0;
     for (int i = 0; i < nprob; ++i) {
