@@ -8,23 +8,25 @@
 // The kernel computes the transposed tile  D[n, m] = W[n, :] . x[m, :]  so that
 // the *weights* are the tcgen05 A operand.  A may live in tensor memory, which is
 // what makes the fusion cheap: the dequantisers write f16 weights straight into
-// tensor memory (tcgen05.st) and never touch shared memory with them.  Shared
-// memory bandwidth (128 B/clk/SM) is the binding resource of this kernel; per
-// 64-deep k-step a CTA moves 28 KB of activations in (TMA) and out (MMA B
-// operand) plus 8.5 KB of raw weights in and out, instead of also writing and
-// re-reading 16-32 KB of dequantised weights.
+// tensor memory (tcgen05.st) and never touch shared memory with them.  Per 64-deep
+// k-step a CTA moves 24 KB of activations in (TMA) and out (MMA B operand) plus
+// 8.5 KB of raw weights per weight tile, instead of also writing and re-reading
+// 16-32 KB of dequantised weights.
 //
-// One persistent CTA per SM, 512 threads, warp-specialised:
-//   warp 0      producer: TMA tile of 224 tokens x 64 k (f16, 128B swizzle) and one
-//               bulk copy of the 128-row x 64-k weight tile record, 5-stage ring
-//   warp 1      tcgen05.mma issuer (one lane): 128 x 224 x 16 kind::f16, A from
-//               tensor memory, B from shared memory; fp32 accumulators
-//               double-buffered in tensor memory (2 x 224 columns)
-//   warp 2      tensor-memory allocator
-//   warps 4-7   epilogue: tcgen05.ld (lane = output feature, column = token),
-//               bias / GELU / gate*y+residual, stores coalesced across lanes
-//   warps 8-15  dequantisers: thread = one weight row x 32 k; int8 / 4-bit
-//               payload -> f16 -> tcgen05.st into one of two A stages
+// One persistent CTA per SM, 896 threads, warp-specialised:
+//   warp 0       producer (elect.sync): TMA tile of 192 tokens x 64 k (f16, 128B
+//                swizzle) and one bulk copy per 128-row x 64-k weight tile record,
+//                5-stage ring
+//   warp 1       tcgen05.mma issuer (elect.sync): 128 x 192 x 16 kind::f16, A from
+//                tensor memory, B from shared memory, four MMAs per A-stage
+//                barrier; fp32 accumulators in tensor memory (384 columns)
+//   warp 2       tensor-memory allocator
+//   warps 4-11   epilogue: tcgen05.ld (lane = output feature, column = token),
+//                bias / GELU / gate*y+residual, stores coalesced across lanes
+//   warps 12-27  dequantisers: thread = one weight row x 32 k; int8 / 4-bit
+//                payload -> f16 -> tcgen05.st into one of four 32-column A stages
+// Issuing tcgen05.mma / tcgen05.commit from an `if (lane == 0)` branch costs about a
+// hundred cycles per batch on B200; elect.sync issue runs at the tensor pipe's rate.
 // The dequantised f16 weight equals rn_f16(d*q) for q8_0 (one rounding of the
 // exact product) and rn_f16(a*q - b) for q4_K with a = rn_f16(d*sc), b = rn_f16(dmin*m).
 #include "edb200_internal.h"
@@ -37,8 +39,7 @@ constexpr int TW = 128;            // weight rows (output features) per tile = t
 constexpr int TN = 192;            // tokens per tile = accumulator columns
 constexpr int BK = 64;
 constexpr int LD_STAGES = 5;
-constexpr int AK = 32;             // k per A stage
-constexpr int X_BYTES = TN * BK * 2;          // 28 KB
+constexpr int X_BYTES = TN * BK * 2;          // 24 KB
 constexpr int W_BYTES_MAX = 8704;             // one weight tile record (8704 / 5120 B)
 constexpr int STAGE_BYTES = X_BYTES + 2 * W_BYTES_MAX;    // 41 KB (room for two weight tiles)
 constexpr int OFF_BAR = LD_STAGES * STAGE_BYTES;
@@ -46,7 +47,6 @@ constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;  // + alignment slack
 
 constexpr int NUM_THREADS = 896;
 constexpr int EPI_WARPS = 8;       // warps 4-7 (weight half 0) and 8-11 (weight half 1)
-constexpr int DQ_WARPS = 16;       // warps 12-27
 constexpr int EC = 16;             // accumulator columns (tokens) per epilogue step
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t TMEM_ACC = 0;                       // 384 accumulator columns, A stages above them
@@ -68,7 +68,6 @@ struct Params {
     Problem p[2];
     int tiles0;       // tiles of problem 0
     int total_tiles;
-    int dbg;          // EDB_DBG timing experiments only
     int* err;
 };
 
@@ -215,8 +214,9 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x0, const __grid_constant__
     constexpr uint32_t kWBytes = kQ4 ? kQwTileBytesQ4 : kQwTileBytesQ8;
     constexpr uint32_t kTxBytes = X_BYTES + WH * kWBytes;
     constexpr int ACC_STAGES = WH == 1 ? 2 : 1;
-    constexpr int A_COLS = WH * 16;                  // tensor-memory columns of one A stage (32 k per weight half)
-    constexpr int A_STAGES = 128 / A_COLS;           // 8 or 4
+    constexpr int A_COLS = 32;                       // tensor-memory columns of one A stage
+    constexpr int AKW = 64 / WH;                     // k per A stage: 32 k of both halves, or 64 k of the one half
+    constexpr int A_STAGES = 128 / A_COLS;           // 4
     constexpr uint32_t TMEM_A = 384;                 // accumulators occupy WH * ACC_STAGES * TN = 384 columns
     constexpr int DQ_PER_LD = WH == 1 ? 8 : 16;      // dequantiser warps that read one shared-memory stage
     static_assert(WH * ACC_STAGES * TN == 384, "tensor-memory plan");
@@ -242,7 +242,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x0, const __grid_constant__
             mbar_init(&ld_empty[i], 1 + DQ_PER_LD);
         }
         for (int i = 0; i < A_STAGES; ++i) {
-            mbar_init(&a_full[i], 4 * WH);
+            mbar_init(&a_full[i], 8);
             mbar_init(&a_empty[i], 1);
         }
         for (int i = 0; i < ACC_STAGES; ++i) {
@@ -320,7 +320,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x0, const __grid_constant__
                 }
                 const uint32_t x_addr = smem_u32(smem + s * STAGE_BYTES);
 #pragma unroll
-                for (int kh = 0; kh < BK / AK; ++kh) {
+                for (int kh = 0; kh < BK / AKW; ++kh) {
                     if (!mbar_wait(&a_full[as], aph, abort_flag, P.err)) {
                         ok = false;
                         break;
@@ -328,16 +328,17 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x0, const __grid_constant__
                     tc_fence_after_sync();
                     if (elect_one()) {
 #pragma unroll
-                        for (int j = 0; j < AK / 16; ++j) {
-                            const uint64_t bd = make_smem_desc_sw128(x_addr + (kh * (AK / 16) + j) * 32, 16, 1024);
+                        for (int j = 0; j < AKW / 16; ++j) {
+                            const uint64_t bd = make_smem_desc_sw128(x_addr + (kh * (AKW / 16) + j) * 32, 16, 1024);
 #pragma unroll
                             for (int hw = 0; hw < WH; ++hw) {
+                                // WH = 2: columns [hw*16 + j*8 ...) ; WH = 1: columns [j*8 ...) of the stage
                                 const uint32_t a_tmem = tmem_base + TMEM_A + as * A_COLS + hw * 16 + j * 8;
                                 mma_f16_ts(tmem_d + hw * TN, a_tmem, bd, idesc, (ks > 0 || kh > 0 || j > 0) ? 1u : 0u);
                             }
                         }
                         mma_commit(&a_empty[as]);
-                        if (kh == BK / AK - 1) mma_commit(&ld_empty[s]);
+                        if (kh == BK / AKW - 1) mma_commit(&ld_empty[s]);
                     }
                     __syncwarp();
                     if (++as == A_STAGES) {
@@ -383,7 +384,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x0, const __grid_constant__
 #pragma unroll 1
                 for (int c = (WH == 1 ? set : 0); c < TN / EC; c += (WH == 1 ? 2 : 1)) {
                     const int m_first = tc.m0 + c * EC;
-                    if (m_first >= pr.M || (P.dbg & 8)) break;   // uniform
+                    if (m_first >= pr.M) break;   // uniform
                     uint32_t r[EC];
                     tmem_ld_32x32b_x16(taddr + c * EC, r);
                     tmem_wait_ld();
@@ -431,15 +432,12 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x0, const __grid_constant__
                 }
                 const uint8_t* tile = smem + s * STAGE_BYTES + X_BYTES + hw * W_BYTES_MAX;
                 uint32_t o[16];
-                if (P.dbg & 1) {
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) o[i] = 0;
-                } else if (kQ4) {
+                if (kQ4) {
                     dequant_q4_k(tile, r, kh, o);
                 } else {
                     dequant_q8_0(tile, r, kh, o);
                 }
-                const uint32_t ai = 2u * g + kh;                 // running A stage number
+                const uint32_t ai = WH == 2 ? 2u * g + kh : g;   // running A stage number
                 const uint32_t as = ai % A_STAGES;
                 const uint32_t aph = (ai / A_STAGES) & 1u;
                 if (!mbar_wait(&a_empty[as], aph ^ 1u, abort_flag, P.err)) {
@@ -447,7 +445,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x0, const __grid_constant__
                     break;
                 }
                 tc_fence_after_sync();
-                tmem_st_32x32b_x16(tmem_base + lane_base + TMEM_A + as * A_COLS + hw * 16, o);
+                tmem_st_32x32b_x16(tmem_base + lane_base + TMEM_A + as * A_COLS + (WH == 2 ? hw : kh) * 16, o);
                 tmem_wait_st();
                 tc_fence_before_sync();
                 __syncwarp();
@@ -586,14 +584,6 @@ static edb200_status_t launch_qgemm(int nprob, const edb200_qweight_t* const* ws
     P.tiles0 = P.p[0].m_tiles * P.p[0].n_tiles;
     P.total_tiles = P.tiles0 + (nprob == 2 ? P.p[1].m_tiles * P.p[1].n_tiles : 0);
     P.err = err;
-    {
-        static int dbg = -1;
-        if (dbg < 0) {
-            const char* e = getenv("EDB200_GEMM_DEBUG");
-            dbg = e ? atoi(e) : 0;
-        }
-        P.dbg = dbg;
-    }
 
     const int grid = P.total_tiles < sm_count() ? P.total_tiles : sm_count();
     const bool q4 = ws[0]->ggml_type == EDB200_TYPE_Q4_K;
