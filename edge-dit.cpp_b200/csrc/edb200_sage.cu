@@ -14,6 +14,8 @@
 
 #include <cuda_fp16.h>
 
+#include <cstdint>
+
 namespace edb {
 namespace sage {
 
@@ -233,6 +235,43 @@ static edb200_status_t quantize(const __half* q, const __half* k, int hn, int l,
     return check_cuda(cudaGetLastError(), "sage quantize launch");
 }
 
+// ---------------------------------------------------------------------------
+// Key-mean entry point without any caller- or library-side allocation: the chunk
+// sums of the fast channel mean live in this fixed device array.  Every partial
+// sum that the finalize pass reads is written by the partial pass of the same
+// call, so nothing in the array has to start at zero.
+constexpr int64_t kStaticScratchBytes = 1 << 20;   // 1 MiB = 2048 chunk rows of 128 floats
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+static float* g_static_scratch_ptr[kMaxDevices];   // resolved once per device
+
+static edb200_status_t static_scratch(float** out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return check_cuda(e, "cudaGetDevice");
+    if (dev < 0 || dev >= kMaxDevices) return fail(EDB200_ERR_UNSUPPORTED, "static scratch: device ordinal %d", dev);
+    if (g_static_scratch_ptr[dev] == nullptr) {
+        void* ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+        if (e != cudaSuccess) return check_cuda(e, "cudaGetSymbolAddress(static scratch)");
+        if (ptr == nullptr) return fail(EDB200_ERR_CUDA, "static scratch: null device address");
+        g_static_scratch_ptr[dev] = static_cast<float*>(ptr);
+    }
+    *out = g_static_scratch_ptr[dev];
+    return EDB200_OK;
+}
+
+template <int D>
+static edb200_status_t key_means_static(const __half* k, int hn, int l, float* part, float* mean_out, cudaStream_t s) {
+    const int nc = (l + kMeanChunk - 1) / kMeanChunk;
+    ProfScope prof(s, PROF_ELEMENTWISE, 0.0, (double)hn * l * D * 2.0);
+    channel_partial_kernel<D><<<dim3(hn, nc, 1), D, 0, s>>>(nullptr, k, nullptr, part, l, nc);
+    channel_finalize_kernel<D><<<dim3(hn, 1), D, 0, s>>>(nullptr, part, nullptr, mean_out, l, nc);
+    count_launch(2);
+    return check_cuda(cudaGetLastError(), "sage key means launch");
+}
+
 }  // namespace sage
 }  // namespace edb
 
@@ -306,6 +345,31 @@ edb200_status_t edb200_sage_attention(const void* q_f16, const void* k_f16, cons
                                       lo.k_scale_stride,
                                       (smooth_q & 1) ? reinterpret_cast<const float*>(sc + lo.bias) : nullptr,
                                       lo.bias_stride, hn, l, d_head, scale, out, out_dtype, ld_out, stream);
+}
+
+edb200_status_t edb200_sage_key_means_static(const void* k_f16, int hn, int64_t l, int d_head, float* mean_out,
+                                             void* stream) {
+    if (k_f16 == nullptr || mean_out == nullptr || hn <= 0 || l <= 0) {
+        return fail(EDB200_ERR_INVALID, "sage_key_means_static: null or empty argument");
+    }
+    if (d_head != 64 && d_head != 128) {
+        return fail(EDB200_ERR_UNSUPPORTED, "sage_key_means_static: d_head must be 64 or 128");
+    }
+    const int64_t nc = (l + sage::kMeanChunk - 1) / sage::kMeanChunk;
+    const int64_t need = (int64_t)hn * nc * d_head * 4;
+    if (l > INT32_MAX || need > sage::kStaticScratchBytes) {
+        return fail(EDB200_ERR_UNSUPPORTED,
+                    "sage_key_means_static: hn * ceil(l/128) * d_head * 4 = %lld bytes exceeds the fixed %lld-byte scratch",
+                    (long long)need, (long long)sage::kStaticScratchBytes);
+    }
+    float* part = nullptr;
+    edb200_status_t st = sage::static_scratch(&part);
+    if (st != EDB200_OK) return st;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (d_head == 128) {
+        return sage::key_means_static<128>(static_cast<const __half*>(k_f16), hn, static_cast<int>(l), part, mean_out, s);
+    }
+    return sage::key_means_static<64>(static_cast<const __half*>(k_f16), hn, static_cast<int>(l), part, mean_out, s);
 }
 
 }  // extern "C"

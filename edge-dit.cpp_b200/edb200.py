@@ -84,6 +84,7 @@ _SIGS = {
                                              c_i64, C.c_int, C.c_float, c_vp, C.c_int, c_i64, c_vp]),
     "edb200_sage_attention": (C.c_int, [c_vp, c_vp, c_vp, C.c_int, c_i64, C.c_int, C.c_float, C.c_int, c_vp, c_i64,
                                         c_vp, C.c_int, c_i64, c_vp]),
+    "edb200_sage_key_means_static": (C.c_int, [c_vp, C.c_int, c_i64, C.c_int, c_vp, c_vp]),
     "edb200_flux_create": (C.c_int, [C.POINTER(FluxConfig), C.POINTER(c_vp)]),
     "edb200_flux_destroy": (None, [c_vp]),
     "edb200_flux_tensor_count": (C.c_int, [c_vp]),

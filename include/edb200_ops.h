@@ -234,6 +234,20 @@ EDB200_API edb200_status_t edb200_sage_attention(const void* q_f16, const void* 
                                                  int64_t l, int d_head, float scale, int smooth_q, void* scratch,
                                                  int64_t scratch_bytes, void* out, int out_dtype, int64_t ld_out,
                                                  void* stream);
+/* Per-channel key means (the smooth-K vector, chunked sum as with
+ * EDB200_SAGE_FAST_MEANS) for callers that cannot hand over or allocate device
+ * scratch.  No counterpart in the reference, whose means always live in the
+ * caller's scratch buffer.  The chunk sums go to a 1 MiB array that is part of the
+ * library image, so the call performs no allocation of any kind; mean_out
+ * [hn, d_head] f32 is the only buffer the caller provides.
+ *  - Limit: hn * ceil(l / 128) * d_head * 4 bytes <= 1 MiB (24 heads x 128 reach
+ *    10880 tokens); larger problems return EDB200_ERR_UNSUPPORTED.
+ *  - The first call on each device looks up the array's device address; make that
+ *    call before starting a stream capture.
+ *  - All calls on one device share the array: two calls whose kernels may overlap
+ *    (different streams, no ordering) race on it.  Nothing in it needs clearing. */
+EDB200_API edb200_status_t edb200_sage_key_means_static(const void* k_f16, int hn, int64_t l, int d_head,
+                                                        float* mean_out, void* stream);
 
 /* ------------------------------------------------- FLUX.1 denoise-step model
  * A whole-step replacement at the reference's model seam
