@@ -11,29 +11,39 @@
 // Both keep the softmax in f32 base 2, P in f16 and the PV product in kind::f16
 // with f32 accumulation, V in f16 (as the reference feeds it).
 //
-// One CTA per (128-query tile, head); 640 threads, warp-specialised:
-//   warp 0     TMA producer (Q once; K and V tiles of 128 keys, 2-stage rings)
-//   warp 1     tcgen05.mma issuer: S_j = Q K_j^T into one of two S buffers in
-//              tensor memory, O += P_j V_j
-//   warp 2     tensor-memory allocator
-//   warps 4-19 softmax: four threads per query row, each owning 32 score columns
-//              (four warps per scheduler hide the dependent-issue latency a
-//              single warp cannot); tcgen05.ld S, exp2, P -> shared memory
-//              (128B-swizzled K-major operand), lazy rescale of O in tensor
-//              memory (only when a row maximum grows by more than 2^8)
+// One CTA per (256-query slab, head): two 128-row query tiles share every K/V tile
+// that is fetched, and while the softmax threads of one tile work the tensor pipe
+// runs the other tile's products.  384 threads, warp-specialised:
+//   warp 0      TMA producer (both Q tiles once; K and V tiles of 128 keys, 2-stage rings)
+//   warp 1      tcgen05.mma issuer (elect.sync), in the order
+//               S0=Q0 K_0^T, S1=Q1 K_0^T, then per key block j:
+//               O0 += P0 V_j, S0 = Q0 K_{j+1}^T, O1 += P1 V_j, S1 = Q1 K_{j+1}^T
+//   warp 2      tensor-memory allocator
+//   warps 4-7   softmax of query tile 0: one thread per query row owns all 128 scores
+//               of the row (no cross-thread exchange), tcgen05.ld, packed f32x2
+//               arithmetic, exp2, P as f16 pairs back into the tile's own S columns
+//               (tcgen05.st) where the PV product reads it as its A operand
+//   warps 8-11  the same for query tile 1
+// Tensor memory: S0 | S1 | O0 | O1, 128 columns each.  P_t overlays S_t, so S_t of the
+// next key block is issued after O_t += P_t V; the tensor pipe executes in issue
+// order, which is also why a completed S_t implies the tile's previous PV product
+// has finished and O_t may be rescaled in place (only when a row maximum grows by
+// more than 2^8).
 #include "edb200_internal.h"
 #include "edb200_ptx.cuh"
 
 namespace edb {
 namespace attn {
 
-constexpr int BQ = 128;   // query rows per CTA
+constexpr int BQ = 128;   // query rows per tile (two tiles per CTA)
+constexpr int QT = 2;     // query tiles per CTA
 constexpr int BKV = 128;  // keys per block
 constexpr int KV_STAGES = 2;
-constexpr int NSPLIT = 4;          // softmax threads per query row
-constexpr int NUM_THREADS = 128 + NSPLIT * 128;
+constexpr int BIAS_STAGES = 4;      // smooth-Q bias ring (one 512-byte row piece per key block)
+constexpr int NUM_THREADS = 128 + QT * 128;
 constexpr uint32_t TMEM_COLS = 512;
-constexpr uint32_t TMEM_S0 = 0, TMEM_S1 = 128, TMEM_O = 256, TMEM_P = 384;
+constexpr uint32_t TMEM_S = 0, TMEM_O = 256;       // + tile * 128
+constexpr uint32_t TMEM_P_OFF = 0;                 // P_t (f16 pairs) = S_t columns [0, 64)
 constexpr float kRescaleThreshold = 8.0f;  // log2(256)
 
 struct Params {
@@ -53,15 +63,15 @@ struct Params {
 template <int D, bool SAGE>
 struct Cfg {
     static constexpr int QK_ELEM = SAGE ? 1 : 2;
-    static constexpr int Q_BYTES = BQ * D * QK_ELEM;
+    static constexpr int Q_BYTES = BQ * D * QK_ELEM;      // one query tile
     static constexpr int K_BYTES = BKV * D * QK_ELEM;
     static constexpr int V_BYTES = BKV * D * 2;
     static constexpr int OFF_Q = 0;
-    static constexpr int OFF_K = OFF_Q + Q_BYTES;
+    static constexpr int OFF_K = OFF_Q + QT * Q_BYTES;
     static constexpr int OFF_V = OFF_K + KV_STAGES * K_BYTES;
     static constexpr int OFF_BAR = OFF_V + KV_STAGES * V_BYTES;
-    static constexpr int OFF_XCH = OFF_BAR + 256;                  // row-maximum exchange [2][NSPLIT][BQ] f32
-    static constexpr int SMEM_BYTES = OFF_XCH + 2 * NSPLIT * BQ * 4 + 1024;
+    static constexpr int OFF_BIAS = OFF_BAR + 256;
+    static constexpr int SMEM_BYTES = OFF_BIAS + BIAS_STAGES * BKV * 4 + 1024;
     // Q/K panels: rows of 128 bytes (64 f16 or 128 int8); a tile is D*QK_ELEM/128 panels.
     static constexpr int QK_PANELS = D * QK_ELEM / 128;
     static constexpr int QK_PANEL_BYTES = 128 * 128;
@@ -80,6 +90,124 @@ __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
     return *reinterpret_cast<uint32_t*>(&h);
 }
 
+// Two f32 operations per instruction (sm_100 packed f32x2 pipe).
+__device__ __forceinline__ void fma2(float& d0, float& d1, float a0, float a1, float b0, float b1, float c0, float c1) {
+    asm("{\n .reg .b64 a, b, c, d;\n mov.b64 a, {%2, %3};\n mov.b64 b, {%4, %5};\n mov.b64 c, {%6, %7};\n"
+        " fma.rn.f32x2 d, a, b, c;\n mov.b64 {%0, %1}, d;\n}"
+        : "=f"(d0), "=f"(d1)
+        : "f"(a0), "f"(a1), "f"(b0), "f"(b1), "f"(c0), "f"(c1));
+}
+__device__ __forceinline__ void add2(float& d0, float& d1, float a0, float a1, float b0, float b1) {
+    asm("{\n .reg .b64 a, b, d;\n mov.b64 a, {%2, %3};\n mov.b64 b, {%4, %5};\n"
+        " add.rn.f32x2 d, a, b;\n mov.b64 {%0, %1}, d;\n}"
+        : "=f"(d0), "=f"(d1)
+        : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
+}
+__device__ __forceinline__ void mul2(float& d0, float& d1, float a0, float a1, float b0, float b1) {
+    asm("{\n .reg .b64 a, b, d;\n mov.b64 a, {%2, %3};\n mov.b64 b, {%4, %5};\n"
+        " mul.rn.f32x2 d, a, b;\n mov.b64 {%0, %1}, d;\n}"
+        : "=f"(d0), "=f"(d1)
+        : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
+}
+
+// s32 -> f32 without a conversion instruction (valid for |s| < 2^22):
+// as_float(s + 0x4B400000) = 12582912 + s exactly.
+constexpr int kMagicInt = 0x4B400000;
+constexpr float kMagicFloat = 12582912.0f;
+
+// Half a score row (64 columns, raw tensor-memory words) -> maximum of the scaled
+// scores.  `valid` = columns of this half that are real keys (>= 64: all).
+// With a smooth-Q bias the words are replaced by the f32 scores
+// v = s * (q_scale * k_scale) + bias (softmax scale not yet applied: `cq` is c0 / sl2),
+// so that the second pass only needs one multiply-add per score.
+template <bool SAGE>
+__device__ __forceinline__ float half_row_max(uint32_t (&rr)[64], float c0, float cq, const float4* bias, float sl2,
+                                              int valid) {
+    if (SAGE && bias == nullptr) {
+        int mi[4] = {INT_MIN, INT_MIN, INT_MIN, INT_MIN};
+        if (valid >= 64) {
+#pragma unroll
+            for (int i = 0; i < 64; ++i) mi[i & 3] = max(mi[i & 3], static_cast<int>(rr[i]));
+        } else {
+#pragma unroll
+            for (int i = 0; i < 64; ++i) {
+                if (i < valid) mi[i & 3] = max(mi[i & 3], static_cast<int>(rr[i]));
+            }
+        }
+        const int m = max(max(mi[0], mi[1]), max(mi[2], mi[3]));
+        return m == INT_MIN ? -INFINITY : static_cast<float>(m) * c0;   // c0 > 0
+    }
+    float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+    if (SAGE) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const float4 b = bias[i];   // shared memory, same address in every lane
+            float f0 = __int_as_float(static_cast<int>(rr[4 * i + 0]) + kMagicInt);
+            float f1 = __int_as_float(static_cast<int>(rr[4 * i + 1]) + kMagicInt);
+            float f2 = __int_as_float(static_cast<int>(rr[4 * i + 2]) + kMagicInt);
+            float f3 = __int_as_float(static_cast<int>(rr[4 * i + 3]) + kMagicInt);
+            add2(f0, f1, f0, f1, -kMagicFloat, -kMagicFloat);
+            add2(f2, f3, f2, f3, -kMagicFloat, -kMagicFloat);
+            fma2(f0, f1, f0, f1, cq, cq, b.x, b.y);
+            fma2(f2, f3, f2, f3, cq, cq, b.z, b.w);
+            rr[4 * i + 0] = __float_as_uint(f0);
+            rr[4 * i + 1] = __float_as_uint(f1);
+            rr[4 * i + 2] = __float_as_uint(f2);
+            rr[4 * i + 3] = __float_as_uint(f3);
+            if (valid >= 64) {
+                mx[0] = fmaxf(mx[0], f0);
+                mx[1] = fmaxf(mx[1], f1);
+                mx[2] = fmaxf(mx[2], f2);
+                mx[3] = fmaxf(mx[3], f3);
+            } else {
+                if (4 * i + 0 < valid) mx[0] = fmaxf(mx[0], f0);
+                if (4 * i + 1 < valid) mx[1] = fmaxf(mx[1], f1);
+                if (4 * i + 2 < valid) mx[2] = fmaxf(mx[2], f2);
+                if (4 * i + 3 < valid) mx[3] = fmaxf(mx[3], f3);
+            }
+        }
+        return fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * sl2;   // sl2 > 0
+    }
+    if (valid >= 64) {
+#pragma unroll
+        for (int i = 0; i < 64; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(rr[i]));
+    } else {
+#pragma unroll
+        for (int i = 0; i < 64; ++i) {
+            if (i < valid) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(rr[i]));
+        }
+    }
+    return fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * c0;   // c0 > 0
+}
+
+// Half a score row -> P = exp2(score * c0 - m) as 32 packed f16 pairs; the pair
+// (sum0, sum1) accumulates the row sum.  RAW_INT: the words are s32 dot products,
+// otherwise f32 scores.
+template <bool RAW_INT>
+__device__ __forceinline__ void half_row_exp(const uint32_t (&rr)[64], uint32_t (&p2)[32], float c0, float m, int valid,
+                                             float& sum0, float& sum1) {
+    const float negm = -m;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+        float e0, e1;
+        if (RAW_INT) {
+            float f0 = __int_as_float(static_cast<int>(rr[2 * i + 0]) + kMagicInt);
+            float f1 = __int_as_float(static_cast<int>(rr[2 * i + 1]) + kMagicInt);
+            add2(f0, f1, f0, f1, -kMagicFloat, -kMagicFloat);
+            fma2(e0, e1, f0, f1, c0, c0, negm, negm);
+        } else {
+            fma2(e0, e1, __uint_as_float(rr[2 * i]), __uint_as_float(rr[2 * i + 1]), c0, c0, negm, negm);
+        }
+        float a = ex2(e0), b = ex2(e1);
+        if (valid < 64) {
+            if (2 * i + 0 >= valid) a = 0.0f;
+            if (2 * i + 1 >= valid) b = 0.0f;
+        }
+        add2(sum0, sum1, sum0, sum1, a, b);
+        p2[i] = pack_h2(a, b);
+    }
+}
+
 template <int D, bool SAGE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -93,16 +221,15 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     uint64_t* k_empty = k_full + KV_STAGES;  // [2]
     uint64_t* v_full = k_empty + KV_STAGES;  // [2]
     uint64_t* v_empty = v_full + KV_STAGES;  // [2]
-    uint64_t* s_full = v_empty + KV_STAGES;  // [2]
-    uint64_t* s_empty = s_full + 2;          // [2]
-    uint64_t* p_full = s_empty + 2;          // [1]
-    uint64_t* pv_done = p_full + 1;          // [1]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 1);
+    uint64_t* s_full = v_empty + KV_STAGES;  // [QT]
+    uint64_t* p_full = s_full + QT;          // [QT]
+    uint64_t* o_done = p_full + QT;          // [QT]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + QT);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int q0 = blockIdx.x * BQ;
+    const int q0 = blockIdx.x * (QT * BQ);
     const int hn = blockIdx.y;
     const int n_kv = (P.Lk + BKV - 1) / BKV;
 
@@ -114,12 +241,11 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             mbar_init(&v_full[i], 1);
             mbar_init(&v_empty[i], 1);
         }
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < QT; ++i) {
             mbar_init(&s_full[i], 1);
-            mbar_init(&s_empty[i], 4 * NSPLIT);
+            mbar_init(&p_full[i], 4);
+            mbar_init(&o_done[i], 1);
         }
-        mbar_init(p_full, 4 * NSPLIT);
-        mbar_init(pv_done, 1);
         *abort_flag = 0;
         fence_mbar_init();
     }
@@ -139,21 +265,33 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 
     if (warp == 0) {
         // ------------------------------------------------------ TMA producer
-        if (lane == 0) {
-            mbar_arrive_expect_tx(q_full, C::Q_BYTES);
+        if (elect_one()) {
+            mbar_arrive_expect_tx(q_full, QT * C::Q_BYTES);
 #pragma unroll
-            for (int p = 0; p < C::QK_PANELS; ++p) {
-                tma_load_3d(smem + C::OFF_Q + p * C::QK_PANEL_BYTES, &map_q, q_full, p * (128 / C::QK_ELEM), q0, hn);
+            for (int t = 0; t < QT; ++t) {
+#pragma unroll
+                for (int p = 0; p < C::QK_PANELS; ++p) {
+                    tma_load_3d(smem + C::OFF_Q + t * C::Q_BYTES + p * C::QK_PANEL_BYTES, &map_q, q_full,
+                                p * (128 / C::QK_ELEM), q0 + t * BQ, hn);
+                }
             }
             for (int j = 0; j < n_kv; ++j) {
                 const int st = j % KV_STAGES;
                 const uint32_t ph = (j / KV_STAGES) & 1;
                 if (!mbar_wait(&k_empty[st], ph ^ 1u, abort_flag, P.err)) break;
-                mbar_arrive_expect_tx(&k_full[st], C::K_BYTES);
+                const bool with_bias = SAGE && P.bias != nullptr;
+                mbar_arrive_expect_tx(&k_full[st], C::K_BYTES + (with_bias ? BKV * 4 : 0));
 #pragma unroll
                 for (int p = 0; p < C::QK_PANELS; ++p) {
                     tma_load_3d(smem + C::OFF_K + st * C::K_BYTES + p * C::QK_PANEL_BYTES, &map_k, &k_full[st],
                                 p * (128 / C::QK_ELEM), j * BKV, hn);
+                }
+                if (with_bias) {
+                    // The bias piece of key block j is read by the softmax threads until their P of block j
+                    // is complete.  Piece j + 4 is fetched after S(j + 2) of the second query tile finished,
+                    // which the issue order puts after P(j + 1) of both tiles: four stages cannot collide.
+                    bulk_load_1d(smem + C::OFF_BIAS + (j % BIAS_STAGES) * (BKV * 4),
+                                 P.bias + (long long)hn * P.bias_stride + (long long)j * BKV, BKV * 4, &k_full[st]);
                 }
                 if (!mbar_wait(&v_empty[st], ph ^ 1u, abort_flag, P.err)) break;
                 mbar_arrive_expect_tx(&v_full[st], C::V_BYTES);
@@ -169,20 +307,17 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         const uint32_t idesc_qk = SAGE ? make_idesc(kDFmtS32, kFmtS8, kFmtS8, 0, 0, BQ, BKV)
                                        : make_idesc(kDFmtF32, kFmtF16, kFmtF16, 0, 0, BQ, BKV);
         const uint32_t idesc_pv = make_idesc(kDFmtF32, kFmtF16, kFmtF16, 0, 1, BQ, D);
-        const uint32_t q_addr = smem_u32(smem + C::OFF_Q);
         bool ok = mbar_wait(q_full, 0, abort_flag, P.err);
 
-        auto issue_qk = [&](int j) -> bool {
+        // S_t = Q_t K_j^T.  S_t is free: the tile's previous PV product was issued before.
+        auto issue_qk = [&](int t, int j) -> bool {
             const int st = j % KV_STAGES;
-            const uint32_t kph = (j / KV_STAGES) & 1;
-            const int sb = j & 1;
-            const uint32_t sph = (j >> 1) & 1;
-            if (!mbar_wait(&k_full[st], kph, abort_flag, P.err)) return false;
-            if (!mbar_wait(&s_empty[sb], sph ^ 1u, abort_flag, P.err)) return false;
+            if (!mbar_wait(&k_full[st], static_cast<uint32_t>((j / KV_STAGES) & 1), abort_flag, P.err)) return false;
             tc_fence_after_sync();
             if (elect_one()) {
+                const uint32_t q_addr = smem_u32(smem + C::OFF_Q + t * C::Q_BYTES);
                 const uint32_t k_addr = smem_u32(smem + C::OFF_K + st * C::K_BYTES);
-                const uint32_t tmem_s = tmem_base + (sb ? TMEM_S1 : TMEM_S0);
+                const uint32_t tmem_s = tmem_base + TMEM_S + t * 128;
 #pragma unroll
                 for (int ks = 0; ks < C::QK_KSTEPS; ++ks) {
                     const uint32_t off = (ks / 4) * C::QK_PANEL_BYTES + (ks % 4) * 32;
@@ -194,205 +329,182 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                         mma_f16_ss(tmem_s, ad, bd, idesc_qk, ks > 0 ? 1u : 0u);
                     }
                 }
-                mma_commit(&s_full[sb]);
-                mma_commit(&k_empty[st]);
+                mma_commit(&s_full[t]);
+                if (t == QT - 1) mma_commit(&k_empty[st]);
+            }
+            __syncwarp();
+            return true;
+        };
+        // O_t += P_t V_j
+        auto issue_pv = [&](int t, int j) -> bool {
+            const int st = j % KV_STAGES;
+            if (!mbar_wait(&v_full[st], static_cast<uint32_t>((j / KV_STAGES) & 1), abort_flag, P.err) ||
+                !mbar_wait(&p_full[t], static_cast<uint32_t>(j & 1), abort_flag, P.err)) {
+                return false;
+            }
+            tc_fence_after_sync();
+            if (elect_one()) {
+                const uint32_t v_addr = smem_u32(smem + C::OFF_V + st * C::V_BYTES);
+                const uint32_t tmem_p = tmem_base + TMEM_S + t * 128 + TMEM_P_OFF;
+#pragma unroll
+                for (int ks = 0; ks < BKV / 16; ++ks) {
+                    // P: tensor memory, 8 columns (16 keys) per step; V: MN-major, 16 keys = 2 KB per step
+                    const uint64_t bd = make_smem_desc_sw128(v_addr + ks * 2048, BKV * 128, 1024);
+                    mma_f16_ts(tmem_base + TMEM_O + t * 128, tmem_p + ks * 8, bd, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+                }
+                if (t == QT - 1) mma_commit(&v_empty[st]);
+                if (j == n_kv - 1) mma_commit(&o_done[t]);
             }
             __syncwarp();
             return true;
         };
 
-        if (ok) ok = issue_qk(0);
+        for (int t = 0; ok && t < QT; ++t) ok = issue_qk(t, 0);
         for (int j = 0; ok && j < n_kv; ++j) {
-            if (j + 1 < n_kv) {
-                if (!issue_qk(j + 1)) break;
-            }
-            const int st = j % KV_STAGES;
-            const uint32_t vph = (j / KV_STAGES) & 1;
-            if (!mbar_wait(&v_full[st], vph, abort_flag, P.err) ||
-                !mbar_wait(p_full, static_cast<uint32_t>(j & 1), abort_flag, P.err)) {
-                break;
-            }
-            tc_fence_after_sync();
-            if (elect_one()) {
-                const uint32_t v_addr = smem_u32(smem + C::OFF_V + st * C::V_BYTES);
 #pragma unroll
-                for (int ks = 0; ks < BKV / 16; ++ks) {
-                    // P: tensor memory, 8 columns (16 keys) per step; V: MN-major, 16 keys = 2 KB per step
-                    const uint64_t bd = make_smem_desc_sw128(v_addr + ks * 2048, BKV * 128, 1024);
-                    mma_f16_ts(tmem_base + TMEM_O, tmem_base + TMEM_P + ks * 8, bd, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
-                }
-                mma_commit(pv_done);
-                mma_commit(&v_empty[st]);
+            for (int t = 0; t < QT; ++t) {
+                if (ok) ok = issue_pv(t, j);
+                if (ok && j + 1 < n_kv) ok = issue_qk(t, j + 1);
             }
-            __syncwarp();
         }
     } else if (warp >= 4) {
         // ------------------------------------------------------------ softmax
-        // NSPLIT threads share one query row: thread `split` owns score columns
-        // [split*CW, split*CW+CW) and output columns [split*OW, split*OW+OW).  The
-        // row maximum is exchanged through shared memory behind a named barrier
-        // per lane quarter, so every thread of a row takes the same rescale decision.
-        constexpr int CW = BKV / NSPLIT;
-        constexpr int OW = D / NSPLIT;
+        const int t = (warp - 4) >> 2;              // query tile
         const int quarter = warp & 3;
-        const int split = (warp - 4) >> 2;
-        const int r = quarter * 32 + lane;          // row inside the tile
-        const int q_row = q0 + r;
+        const int r = quarter * 32 + lane;          // row inside the tile = tensor-memory lane
+        const int q_row = q0 + t * BQ + r;
         const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
-        float* xch = reinterpret_cast<float*>(smem + C::OFF_XCH);   // [2][NSPLIT][BQ]
+        const uint32_t s_addr = tmem_base + lane_base + TMEM_S + t * 128;
+        const uint32_t p_addr = s_addr + TMEM_P_OFF;
+        const uint32_t o_addr = tmem_base + lane_base + TMEM_O + t * 128;
         float m_used = -INFINITY;
-        float l_sum = 0.0f;
+        float sum0 = 0.0f, sum1 = 0.0f;
         float row_scale = P.scale_log2;
+        float q_scale = 1.0f;
         const float* bias_row = nullptr;
+        const float* ks_row = nullptr;
         if (SAGE) {
-            row_scale *= P.q_scale[(long long)hn * P.q_scale_stride + (q0 >> 5) + quarter];
-            if (P.bias != nullptr) bias_row = P.bias + (long long)hn * P.bias_stride + split * CW;
+            // a query tile that lies wholly beyond Lq (second tile of the last slab) has no scale row
+            if (q0 + t * BQ < P.Lq) {
+                q_scale = P.q_scale[(long long)hn * P.q_scale_stride + ((q0 + t * BQ) >> 5) + quarter];
+            }
+            row_scale *= q_scale;
+            ks_row = P.k_scale + (long long)hn * P.k_scale_stride;
+            if (P.bias != nullptr) bias_row = P.bias + (long long)hn * P.bias_stride;
         }
         bool ok = true;
 
-        for (int j = 0; j < n_kv; ++j) {
-            // After an abort every wait returns false at once; the loop still runs to
-            // the end so that all threads of a row group meet at the named barrier.
-            const int sb = j & 1;
-            ok = mbar_wait(&s_full[sb], static_cast<uint32_t>((j >> 1) & 1), abort_flag, P.err) && ok;
-            tc_fence_after_sync();
-            float s[CW];
-            {
-                const uint32_t taddr = tmem_base + lane_base + (sb ? TMEM_S1 : TMEM_S0) + split * CW;
-                uint32_t rr[CW];
-                tmem_ld_cols<CW>(taddr, rr);
-                tmem_wait_ld();
-#pragma unroll
-                for (int i = 0; i < CW; ++i) s[i] = __uint_as_float(rr[i]);
+        for (int j = 0; ok && j < n_kv; ++j) {
+            if (!mbar_wait(&s_full[t], static_cast<uint32_t>(j & 1), abort_flag, P.err)) {
+                ok = false;
+                break;
             }
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&s_empty[sb]);
-
-            // scores in the log2 domain
-            const int valid = P.Lk - j * BKV - split * CW;  // own columns >= valid are padding
+            tc_fence_after_sync();
+            const int valid = P.Lk - j * BKV;       // columns >= valid are padding (last block only)
+            float c0 = row_scale, c1 = row_scale;     // score multipliers of the two 64-key halves
+            float cq0 = 1.0f, cq1 = 1.0f;             // the same without the softmax scale
             if (SAGE) {
-                const float ks = P.k_scale[(long long)hn * P.k_scale_stride + 2 * j + (split * CW >= 64 ? 1 : 0)];
-                const float c0 = row_scale * ks;
-                // s32 -> f32 without a conversion instruction (valid for |s| < 2^22):
-                // as_float(s + 0x4B400000) = 12582912 + s exactly.
-                if (bias_row != nullptr) {
-                    const float4* b4 = reinterpret_cast<const float4*>(bias_row + j * BKV);
+                const float k0 = __ldg(ks_row + 2 * j), k1 = __ldg(ks_row + 2 * j + 1);
+                c0 *= k0;
+                c1 *= k1;
+                cq0 = q_scale * k0;
+                cq1 = q_scale * k1;
+            }
+            const bool biased = SAGE && bias_row != nullptr;   // uniform over the CTA
+
+            // Each 64-key half of the block is one online-softmax step of its own: load, maximum,
+            // exponentials, P.  Nothing is read twice and 64 scores are live at a time.
 #pragma unroll
-                    for (int i = 0; i < CW / 4; ++i) {
-                        const float4 b = __ldg(b4 + i);
-                        const float bb[4] = {b.x, b.y, b.z, b.w};
+            for (int h = 0; h < 2; ++h) {
+                const float ch = h ? c1 : c0;
+                const int valid_h = valid - 64 * h;
+                uint32_t rr[64];
+                tmem_ld_cols<64>(s_addr + 64 * h, rr);
+                tmem_wait_ld();
+                const float4* bias_h =
+                    biased ? reinterpret_cast<const float4*>(smem + C::OFF_BIAS + (j % BIAS_STAGES) * (BKV * 4)) + 16 * h
+                           : nullptr;
+                const float mx = half_row_max<SAGE>(rr, ch, h ? cq1 : cq0, bias_h, P.scale_log2, valid_h);
+                // lazy rescale: keep exponentiating against the old maximum until it is stale by > 2^8
+                float alpha = 1.0f;
+                const bool grow = mx > m_used + kRescaleThreshold;
+                if (grow) {
+                    alpha = ex2(m_used - mx);   // 0 on the very first half (m_used = -inf)
+                    m_used = mx;
+                    sum0 *= alpha;
+                    sum1 *= alpha;
+                }
+                if ((j > 0 || h > 0) && __any_sync(0xffffffffu, grow)) {
+                    if (j > 0) {
+                        // S_t(j) complete => O_t += P_t V_{j-1} complete; the next PV waits for this thread's P
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const float f = __int_as_float(__float_as_int(s[4 * i + e]) + 0x4B400000) - 12582912.0f;
-                            s[4 * i + e] = fmaf(f, c0, bb[e] * P.scale_log2);
+                        for (int c = 0; c < D / 32; ++c) {
+                            uint32_t oo[32];
+                            tmem_ld_cols<32>(o_addr + c * 32, oo);
+                            tmem_wait_ld();
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) oo[i] = __float_as_uint(__uint_as_float(oo[i]) * alpha);
+                            tmem_st_cols<32>(o_addr + c * 32, oo);
                         }
                     }
-                } else {
+                    if (h > 0) {
+                        // the first half's P of this block was written against the older maximum
+                        uint32_t pp[32];
+                        tmem_wait_st();
+                        tmem_ld_cols<32>(p_addr, pp);
+                        tmem_wait_ld();
+                        const __half2 a2 = __float2half2_rn(alpha);
 #pragma unroll
-                    for (int i = 0; i < CW; ++i) {
-                        const float f = __int_as_float(__float_as_int(s[i]) + 0x4B400000) - 12582912.0f;
-                        s[i] = f * c0;
+                        for (int i = 0; i < 32; ++i) {
+                            __half2 v = __hmul2(*reinterpret_cast<__half2*>(&pp[i]), a2);
+                            pp[i] = *reinterpret_cast<uint32_t*>(&v);
+                        }
+                        tmem_st_cols<32>(p_addr, pp);
                     }
                 }
-            } else {
-#pragma unroll
-                for (int i = 0; i < CW; ++i) s[i] *= row_scale;
-            }
-            if (valid < CW) {
-#pragma unroll
-                for (int i = 0; i < CW; ++i) {
-                    if (i >= valid) s[i] = -INFINITY;
+                // P = exp2(score - m) as f16 pairs into S columns [32h, 32h + 32): the first half's own
+                // columns, all of them consumed by now
+                uint32_t p2[32];
+                if (SAGE && !biased) {
+                    half_row_exp<true>(rr, p2, ch, m_used, valid_h, sum0, sum1);
+                } else {
+                    half_row_exp<false>(rr, p2, biased ? P.scale_log2 : ch, m_used, valid_h, sum0, sum1);
                 }
+                tmem_st_cols<32>(p_addr + 32 * h, p2);
             }
-            float mx4[4] = {s[0], s[1], s[2], s[3]};
-#pragma unroll
-            for (int i = 4; i < CW; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], s[i]);
-            float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-            if (NSPLIT > 1) {
-                float* xb = xch + (j & 1) * (NSPLIT * BQ);
-                xb[split * BQ + r] = mx;
-                named_bar_sync(1 + quarter, NSPLIT * 32);
-#pragma unroll
-                for (int sp = 0; sp < NSPLIT; ++sp) mx = fmaxf(mx, xb[sp * BQ + r]);
-            }
-
-            // lazy rescale: keep exponentiating against the old maximum until it is stale by > 2^8
-            float alpha = 1.0f;
-            const bool grow = mx > m_used + kRescaleThreshold;
-            if (grow) {
-                alpha = ex2(m_used - mx);   // 0 on the first block (m_used = -inf)
-                m_used = mx;
-                l_sum *= alpha;
-            }
-            uint32_t p2[CW / 2];
-            float part[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-            for (int i = 0; i < CW / 2; ++i) {
-                const float a = ex2(s[2 * i] - m_used);
-                const float b = ex2(s[2 * i + 1] - m_used);
-                part[i & 3] += a + b;
-                p2[i] = pack_h2(a, b);
-            }
-            l_sum += (part[0] + part[1]) + (part[2] + part[3]);
-
-            // P buffer and O are free once the previous PV product has completed
-            if (j > 0) {
-                ok = mbar_wait(pv_done, static_cast<uint32_t>((j - 1) & 1), abort_flag, P.err) && ok;
-                tc_fence_after_sync();
-                if (__any_sync(0xffffffffu, grow)) {
-                    const uint32_t oaddr = tmem_base + lane_base + TMEM_O + split * OW;
-                    uint32_t rr[OW];
-                    tmem_ld_cols<OW>(oaddr, rr);
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int i = 0; i < OW; ++i) rr[i] = __float_as_uint(__uint_as_float(rr[i]) * alpha);
-                    tmem_st_cols<OW>(oaddr, rr);
-                    tmem_wait_st();
-                }
-            }
-            // P (f16 pairs, two keys per 32-bit column) goes to tensor memory as the A operand of PV
-            tmem_st_cols<CW / 2>(tmem_base + lane_base + TMEM_P + split * (CW / 2), p2);
             tmem_wait_st();
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(p_full);
+            if (elect_one()) mbar_arrive(&p_full[t]);
         }
 
         // ----------------------------------------------------------- epilogue
-        if (NSPLIT > 1) {
-            // row sum = fixed-order sum of the NSPLIT partial sums (all scaled by the same alphas)
-            float* xb = xch + (n_kv & 1) * (NSPLIT * BQ);
-            xb[split * BQ + r] = l_sum;
-            named_bar_sync(1 + quarter, NSPLIT * 32);
-            l_sum = 0.0f;
-#pragma unroll
-            for (int sp = 0; sp < NSPLIT; ++sp) l_sum += xb[sp * BQ + r];
-        }
-        ok = mbar_wait(pv_done, static_cast<uint32_t>((n_kv - 1) & 1), abort_flag, P.err) && ok;
+        if (ok) ok = mbar_wait(&o_done[t], 0, abort_flag, P.err);
         if (ok) {
             tc_fence_after_sync();
-            const float inv_l = 1.0f / l_sum;
-            const uint32_t oaddr = tmem_base + lane_base + TMEM_O + split * OW;
+            const float inv_l = 1.0f / (sum0 + sum1);
             const bool row_ok = q_row < P.Lq;
             char* obase = static_cast<char*>(P.out);
-            const long long ocol = (long long)q_row * P.ld_out + (long long)hn * D + split * OW;
-            uint32_t rr[OW];
-            tmem_ld_cols<OW>(oaddr, rr);
-            tmem_wait_ld();
-            if (row_ok) {
-                float v[OW];
+            const long long ocol = (long long)q_row * P.ld_out + (long long)hn * D;
 #pragma unroll
-                for (int i = 0; i < OW; ++i) v[i] = __uint_as_float(rr[i]) * inv_l;
+            for (int c = 0; c < D / 32; ++c) {
+                __syncwarp();
+                uint32_t oo[32];
+                tmem_ld_cols<32>(o_addr + c * 32, oo);
+                tmem_wait_ld();
+                if (!row_ok) continue;
+                float v[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(oo[i]) * inv_l;
                 if (P.out_dtype == EDB200_TYPE_F32) {
-                    float4* o = reinterpret_cast<float4*>(obase + ocol * 4);
+                    float4* o = reinterpret_cast<float4*>(obase + (ocol + c * 32) * 4);
 #pragma unroll
-                    for (int i = 0; i < OW / 4; ++i) o[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                    for (int i = 0; i < 8; ++i) o[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
                 } else {
-                    uint4* o = reinterpret_cast<uint4*>(obase + ocol * 2);
+                    uint4* o = reinterpret_cast<uint4*>(obase + (ocol + c * 32) * 2);
                     const bool bf = P.out_dtype == EDB200_TYPE_BF16;
 #pragma unroll
-                    for (int i = 0; i < OW / 8; ++i) {
+                    for (int i = 0; i < 4; ++i) {
                         uint32_t u[4];
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
@@ -445,7 +557,7 @@ static edb200_status_t launch(const void* q, const void* k, const void* v, const
         if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(attention)");
         attr_set = true;
     }
-    dim3 grid((P.Lq + BQ - 1) / BQ, P.HN);
+    dim3 grid((P.Lq + QT * BQ - 1) / (QT * BQ), P.HN);
     ProfScope prof(stream, PROF_ATTENTION, 4.0 * (double)P.Lq * (double)P.Lk * D * P.HN,
                    (double)P.HN * D * ((double)P.Lq * (C::QK_ELEM + 2) + (double)P.Lk * (C::QK_ELEM + 2)));
     kern<<<grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(mq, mk, mv, P);

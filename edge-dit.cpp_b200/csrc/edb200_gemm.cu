@@ -193,14 +193,6 @@ __device__ __forceinline__ void dequant_q4_k(const uint8_t* tile, int r, int h, 
     }
 }
 
-// 1-D bulk copy global -> shared, completion counted on an mbarrier (no multicast).
-__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
-    asm volatile(
-        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes), "r"(smem_u32(bar))
-        : "memory");
-}
-
 // WH = weight tiles (128-row halves) per CTA tile.
 //   WH = 2: 256 weight rows x 192 tokens, one accumulator set (epilogue not overlapped):
 //           least operand traffic per MAC, best for long reductions
@@ -286,7 +278,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x0, const __grid_constant__
                     tma_load_2d(stage, mx, &ld_full[s], ks * BK, tc.m0);
 #pragma unroll
                     for (int hw = 0; hw < WH; ++hw) {
-                        bulk_load(stage + X_BYTES + hw * W_BYTES_MAX,
+                        bulk_load_1d(stage + X_BYTES + hw * W_BYTES_MAX,
                                   wsrc + ((long long)hw * ksteps + ks) * kWBytes, kWBytes, &ld_full[s]);
                     }
                 }

@@ -185,8 +185,11 @@ __device__ __forceinline__ void tmem_st_32x32b_x16(uint32_t taddr, const uint32_
 
 template <int N>
 __device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&r)[N]) {
-    static_assert(N == 16 || N == 32, "tmem_ld_cols: 16 or 32 columns");
-    if constexpr (N == 32) {
+    static_assert(N == 16 || N == 32 || N == 64, "tmem_ld_cols: 16, 32 or 64 columns");
+    if constexpr (N == 64) {
+        tmem_ld_32x32b_x32(taddr, reinterpret_cast<uint32_t(&)[32]>(r[0]));
+        tmem_ld_32x32b_x32(taddr + 32, reinterpret_cast<uint32_t(&)[32]>(r[32]));
+    } else if constexpr (N == 32) {
         tmem_ld_32x32b_x32(taddr, r);
     } else {
         tmem_ld_32x32b_x16(taddr, r);
@@ -194,12 +197,23 @@ __device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&r)[N]) {
 }
 template <int N>
 __device__ __forceinline__ void tmem_st_cols(uint32_t taddr, const uint32_t (&r)[N]) {
-    static_assert(N == 16 || N == 32, "tmem_st_cols: 16 or 32 columns");
-    if constexpr (N == 32) {
+    static_assert(N == 16 || N == 32 || N == 64, "tmem_st_cols: 16, 32 or 64 columns");
+    if constexpr (N == 64) {
+        tmem_st_32x32b_x32(taddr, reinterpret_cast<const uint32_t(&)[32]>(r[0]));
+        tmem_st_32x32b_x32(taddr + 32, reinterpret_cast<const uint32_t(&)[32]>(r[32]));
+    } else if constexpr (N == 32) {
         tmem_st_32x32b_x32(taddr, r);
     } else {
         tmem_st_32x32b_x16(taddr, r);
     }
+}
+
+// 1-D bulk copy global -> shared, completion counted on an mbarrier (both addresses 16-byte aligned, bytes a multiple of 16).
+__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes), "r"(smem_u32(bar))
+        : "memory");
 }
 
 // Named barrier among `nthreads` threads (ids 1..15; 0 is __syncthreads).

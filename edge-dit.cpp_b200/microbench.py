@@ -49,6 +49,7 @@ def main():
     ap.add_argument("--l", type=int, default=4608)
     ap.add_argument("--d", type=int, default=128)
     ap.add_argument("--sage", action="store_true")
+    ap.add_argument("--no-smooth-q", action="store_true", help="Sage attention without the smooth-Q bias")
     ap.add_argument("--exact-means", action="store_true")
     ap.add_argument("--rows", type=int, default=4608)
     ap.add_argument("--h", type=int, default=3072)
@@ -117,12 +118,14 @@ def main():
             scratch = torch.empty(n, dtype=torch.uint8, device=dev)
             offs, strides = (C.c_int64 * 8)(), (C.c_int * 3)()
             edb.check(lib.edb200_sage_scratch_layout(a.hn, a.l, a.d, offs, strides))
-            edb.check(lib.edb200_sage_quantize_qk(edb.ptr(q), edb.ptr(k), a.hn, a.l, a.d, 3, edb.ptr(scratch), n, st))
+            edb.check(lib.edb200_sage_quantize_qk(edb.ptr(q), edb.ptr(k), a.hn, a.l, a.d, 2 if a.no_smooth_q else 3,
+                                                  edb.ptr(scratch), n, st))
             base = scratch.data_ptr()
+            bias = 0 if a.no_smooth_q else base + offs[6]
 
             def run():
                 edb.check(lib.edb200_attention_sage_int8(base + offs[0], base + offs[1], edb.ptr(v), base + offs[2],
-                                                         strides[0], base + offs[3], strides[1], base + offs[6],
+                                                         strides[0], base + offs[3], strides[1], bias,
                                                          strides[2], a.hn, a.l, a.d, scale, edb.ptr(out),
                                                          edb.TYPE_F16, out.stride(0), st))
         else:
