@@ -12,23 +12,26 @@
 // with f32 accumulation, V in f16 (as the reference feeds it).
 //
 // One CTA per (256-query slab, head): two 128-row query tiles share every K/V tile
-// that is fetched, and while the softmax threads of one tile work the tensor pipe
-// runs the other tile's products.  384 threads, warp-specialised:
-//   warp 0      TMA producer (both Q tiles once; K and V tiles of 128 keys, 2-stage rings)
-//   warp 1      tcgen05.mma issuer (elect.sync), in the order
-//               S0=Q0 K_0^T, S1=Q1 K_0^T, then per key block j:
-//               O0 += P0 V_j, S0 = Q0 K_{j+1}^T, O1 += P1 V_j, S1 = Q1 K_{j+1}^T
+// that is fetched.  The exponentials bound this kernel (16 ex2 per clock per SM:
+// 1024 clocks for a 128 x 128 score tile, as long as its two f16 products), so
+// the design keeps the softmax threads busy all the time.  384 threads,
+// warp-specialised:
+//   warp 0      TMA producer (both Q tiles once; K and V tiles of 128 keys, 2-stage
+//               rings; with a smooth-Q bias its 512-byte row piece per key tile)
+//   warp 1      tcgen05.mma issuer (elect.sync).  Scores are produced per 64-key
+//               half g into buffer g % 2 of the tile's 128 S columns; per half and
+//               query tile t:  O_t += P_t[g] V_g,  then  S_t[g + 2] = Q_t K_{g+2}^T
 //   warp 2      tensor-memory allocator
-//   warps 4-7   softmax of query tile 0: one thread per query row owns all 128 scores
-//               of the row (no cross-thread exchange), tcgen05.ld, packed f32x2
-//               arithmetic, exp2, P as f16 pairs back into the tile's own S columns
-//               (tcgen05.st) where the PV product reads it as its A operand
+//   warps 4-7   softmax of query tile 0: one thread per query row owns all 64 scores
+//               of the half (no cross-thread exchange), tcgen05.ld, packed f32x2
+//               arithmetic, exp2, P as f16 pairs back over the first 32 columns of
+//               the buffer just read (tcgen05.st), where the PV product reads it as
+//               its A operand
 //   warps 8-11  the same for query tile 1
-// Tensor memory: S0 | S1 | O0 | O1, 128 columns each.  P_t overlays S_t, so S_t of the
-// next key block is issued after O_t += P_t V; the tensor pipe executes in issue
-// order, which is also why a completed S_t implies the tile's previous PV product
-// has finished and O_t may be rescaled in place (only when a row maximum grows by
-// more than 2^8).
+// Tensor memory: S0 | S1 | O0 | O1, 128 columns each.  The tensor pipe executes in
+// issue order, so S_t[g + 2] may overwrite the buffer once O_t += P_t[g] V_g has been
+// issued.  O_t is rescaled in place, after the tile's last PV product has completed,
+// only when a row maximum grows by more than 2^8.
 #include "edb200_internal.h"
 #include "edb200_ptx.cuh"
 
@@ -37,13 +40,13 @@ namespace attn {
 
 constexpr int BQ = 128;   // query rows per tile (two tiles per CTA)
 constexpr int QT = 2;     // query tiles per CTA
-constexpr int BKV = 128;  // keys per block
+constexpr int BKV = 128;  // keys per K/V tile in shared memory
+constexpr int HK = 64;    // keys per softmax step (half a tile): S is double-buffered per query tile
 constexpr int KV_STAGES = 2;
 constexpr int BIAS_STAGES = 4;      // smooth-Q bias ring (one 512-byte row piece per key block)
 constexpr int NUM_THREADS = 128 + QT * 128;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t TMEM_S = 0, TMEM_O = 256;       // + tile * 128
-constexpr uint32_t TMEM_P_OFF = 0;                 // P_t (f16 pairs) = S_t columns [0, 64)
 constexpr float kRescaleThreshold = 8.0f;  // log2(256)
 
 struct Params {
@@ -180,10 +183,30 @@ __device__ __forceinline__ float half_row_max(uint32_t (&rr)[64], float c0, floa
     return fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * c0;   // c0 > 0
 }
 
+// exp2 of two non-positive-ish arguments (<= 8 by the lazy-rescale rule) on the FMA
+// pipe: round to nearest integer with the 1.5 * 2^23 trick, degree-3 polynomial of
+// 2^f on [-0.5, 0.5] (relative error 7.5e-5, below the f16 rounding of P), integer
+// part added into the exponent field.  Relieves the 16-per-clock-per-SM ex2 unit.
+__device__ __forceinline__ void ex2_poly2(float e0, float e1, float& a, float& b) {
+    e0 = fmaxf(e0, -126.0f);
+    e1 = fmaxf(e1, -126.0f);
+    float r0, r1, x0, x1, f0, f1, p0, p1;
+    add2(r0, r1, e0, e1, kMagicFloat, kMagicFloat);
+    add2(x0, x1, r0, r1, -kMagicFloat, -kMagicFloat);
+    fma2(f0, f1, x0, x1, -1.0f, -1.0f, e0, e1);
+    fma2(p0, p1, f0, f1, 0.05517162f, 0.05517162f, 0.24261113f, 0.24261113f);
+    fma2(p0, p1, p0, p1, f0, f1, 0.69326097f, 0.69326097f);
+    fma2(p0, p1, p0, p1, f0, f1, 0.99992806f, 0.99992806f);
+    a = __int_as_float(__float_as_int(p0) + (__float_as_int(r0) << 23));
+    b = __int_as_float(__float_as_int(p1) + (__float_as_int(r1) << 23));
+}
+
+constexpr int kPolyEvery = 4;   // one score pair in kPolyEvery takes the polynomial path
+
 // Half a score row -> P = exp2(score * c0 - m) as 32 packed f16 pairs; the pair
 // (sum0, sum1) accumulates the row sum.  RAW_INT: the words are s32 dot products,
-// otherwise f32 scores.
-template <bool RAW_INT>
+// otherwise f32 scores.  MASKED: columns >= valid are padding and get P = 0.
+template <bool RAW_INT, bool MASKED>
 __device__ __forceinline__ void half_row_exp(const uint32_t (&rr)[64], uint32_t (&p2)[32], float c0, float m, int valid,
                                              float& sum0, float& sum1) {
     const float negm = -m;
@@ -198,8 +221,14 @@ __device__ __forceinline__ void half_row_exp(const uint32_t (&rr)[64], uint32_t 
         } else {
             fma2(e0, e1, __uint_as_float(rr[2 * i]), __uint_as_float(rr[2 * i + 1]), c0, c0, negm, negm);
         }
-        float a = ex2(e0), b = ex2(e1);
-        if (valid < 64) {
+        float a, b;
+        if (i % kPolyEvery == kPolyEvery - 1) {
+            ex2_poly2(e0, e1, a, b);
+        } else {
+            a = ex2(e0);
+            b = ex2(e1);
+        }
+        if (MASKED) {
             if (2 * i + 0 >= valid) a = 0.0f;
             if (2 * i + 1 >= valid) b = 0.0f;
         }
@@ -221,9 +250,10 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     uint64_t* k_empty = k_full + KV_STAGES;  // [2]
     uint64_t* v_full = k_empty + KV_STAGES;  // [2]
     uint64_t* v_empty = v_full + KV_STAGES;  // [2]
-    uint64_t* s_full = v_empty + KV_STAGES;  // [QT]
-    uint64_t* p_full = s_full + QT;          // [QT]
-    uint64_t* o_done = p_full + QT;          // [QT]
+    uint64_t* s_full = v_empty + KV_STAGES;  // [QT][2]  S of (tile, half) complete
+    uint64_t* p_full = s_full + QT * 2;      // [QT][2]  P of (tile, half) written
+    uint64_t* pv_done = p_full + QT * 2;     // [QT]     one phase per PV product of the tile
+    uint64_t* o_done = pv_done + QT;         // [QT]     the tile's last PV product
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + QT);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -237,13 +267,16 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         mbar_init(q_full, 1);
         for (int i = 0; i < KV_STAGES; ++i) {
             mbar_init(&k_full[i], 1);
-            mbar_init(&k_empty[i], 1);
+            mbar_init(&k_empty[i], QT);
             mbar_init(&v_full[i], 1);
-            mbar_init(&v_empty[i], 1);
+            mbar_init(&v_empty[i], QT);
         }
         for (int i = 0; i < QT; ++i) {
-            mbar_init(&s_full[i], 1);
-            mbar_init(&p_full[i], 4);
+            for (int b = 0; b < 2; ++b) {
+                mbar_init(&s_full[i * 2 + b], 1);
+                mbar_init(&p_full[i * 2 + b], 4);
+            }
+            mbar_init(&pv_done[i], 1);
             mbar_init(&o_done[i], 1);
         }
         *abort_flag = 0;
@@ -302,22 +335,28 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 }
             }
         }
-    } else if (warp == 1) {
-        // -------------------------------------------------------- MMA issuer
-        const uint32_t idesc_qk = SAGE ? make_idesc(kDFmtS32, kFmtS8, kFmtS8, 0, 0, BQ, BKV)
-                                       : make_idesc(kDFmtF32, kFmtF16, kFmtF16, 0, 0, BQ, BKV);
+    } else if (warp == 1 || warp == 3) {
+        // ------------------------------------------- MMA issuers, one per query tile
+        // (one thread cannot issue the small products of both tiles fast enough)
+        const int t = warp >> 1;
+        const uint32_t idesc_qk = SAGE ? make_idesc(kDFmtS32, kFmtS8, kFmtS8, 0, 0, BQ, HK)
+                                       : make_idesc(kDFmtF32, kFmtF16, kFmtF16, 0, 0, BQ, HK);
         const uint32_t idesc_pv = make_idesc(kDFmtF32, kFmtF16, kFmtF16, 0, 1, BQ, D);
         bool ok = mbar_wait(q_full, 0, abort_flag, P.err);
+        const int n_half = 2 * n_kv;     // 64-key halves; half g = keys [64 g, 64 g + 64) = block g/2, buffer g%2
 
-        // S_t = Q_t K_j^T.  S_t is free: the tile's previous PV product was issued before.
-        auto issue_qk = [&](int t, int j) -> bool {
+        // S_t[g % 2] = Q_t K_g^T.  The buffer is free: the PV product that read P from it
+        // (half g - 2) was issued before, and the tensor pipe runs in issue order.
+        auto issue_qk = [&](int g) -> bool {
+            const int j = g >> 1, hb = g & 1;
             const int st = j % KV_STAGES;
             if (!mbar_wait(&k_full[st], static_cast<uint32_t>((j / KV_STAGES) & 1), abort_flag, P.err)) return false;
             tc_fence_after_sync();
             if (elect_one()) {
                 const uint32_t q_addr = smem_u32(smem + C::OFF_Q + t * C::Q_BYTES);
-                const uint32_t k_addr = smem_u32(smem + C::OFF_K + st * C::K_BYTES);
-                const uint32_t tmem_s = tmem_base + TMEM_S + t * 128;
+                // K-major rows of 128 bytes: 64 keys further = 64 rows = 8 KB inside every panel
+                const uint32_t k_addr = smem_u32(smem + C::OFF_K + st * C::K_BYTES) + hb * (HK * 128);
+                const uint32_t tmem_s = tmem_base + TMEM_S + t * 128 + hb * HK;
 #pragma unroll
                 for (int ks = 0; ks < C::QK_KSTEPS; ++ks) {
                     const uint32_t off = (ks / 4) * C::QK_PANEL_BYTES + (ks % 4) * 32;
@@ -329,43 +368,42 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                         mma_f16_ss(tmem_s, ad, bd, idesc_qk, ks > 0 ? 1u : 0u);
                     }
                 }
-                mma_commit(&s_full[t]);
-                if (t == QT - 1) mma_commit(&k_empty[st]);
+                mma_commit(&s_full[t * 2 + hb]);
+                if (hb == 1) mma_commit(&k_empty[st]);
             }
             __syncwarp();
             return true;
         };
-        // O_t += P_t V_j
-        auto issue_pv = [&](int t, int j) -> bool {
+        // O_t += P_t[g % 2] V_g
+        auto issue_pv = [&](int g) -> bool {
+            const int j = g >> 1, hb = g & 1;
             const int st = j % KV_STAGES;
             if (!mbar_wait(&v_full[st], static_cast<uint32_t>((j / KV_STAGES) & 1), abort_flag, P.err) ||
-                !mbar_wait(&p_full[t], static_cast<uint32_t>(j & 1), abort_flag, P.err)) {
+                !mbar_wait(&p_full[t * 2 + hb], static_cast<uint32_t>(j & 1), abort_flag, P.err)) {
                 return false;
             }
             tc_fence_after_sync();
             if (elect_one()) {
                 const uint32_t v_addr = smem_u32(smem + C::OFF_V + st * C::V_BYTES);
-                const uint32_t tmem_p = tmem_base + TMEM_S + t * 128 + TMEM_P_OFF;
+                const uint32_t tmem_p = tmem_base + TMEM_S + t * 128 + hb * HK;
 #pragma unroll
-                for (int ks = 0; ks < BKV / 16; ++ks) {
+                for (int ks = 0; ks < HK / 16; ++ks) {
                     // P: tensor memory, 8 columns (16 keys) per step; V: MN-major, 16 keys = 2 KB per step
-                    const uint64_t bd = make_smem_desc_sw128(v_addr + ks * 2048, BKV * 128, 1024);
-                    mma_f16_ts(tmem_base + TMEM_O + t * 128, tmem_p + ks * 8, bd, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+                    const uint64_t bd = make_smem_desc_sw128(v_addr + (hb * (HK / 16) + ks) * 2048, BKV * 128, 1024);
+                    mma_f16_ts(tmem_base + TMEM_O + t * 128, tmem_p + ks * 8, bd, idesc_pv, (g > 0 || ks > 0) ? 1u : 0u);
                 }
-                if (t == QT - 1) mma_commit(&v_empty[st]);
-                if (j == n_kv - 1) mma_commit(&o_done[t]);
+                mma_commit(&pv_done[t]);
+                if (g == n_half - 1) mma_commit(&o_done[t]);
+                if (hb == 1) mma_commit(&v_empty[st]);
             }
             __syncwarp();
             return true;
         };
 
-        for (int t = 0; ok && t < QT; ++t) ok = issue_qk(t, 0);
-        for (int j = 0; ok && j < n_kv; ++j) {
-#pragma unroll
-            for (int t = 0; t < QT; ++t) {
-                if (ok) ok = issue_pv(t, j);
-                if (ok && j + 1 < n_kv) ok = issue_qk(t, j + 1);
-            }
+        for (int g = 0; ok && g < 2; ++g) ok = issue_qk(g);
+        for (int g = 0; ok && g < n_half; ++g) {
+            ok = issue_pv(g);
+            if (ok && g + 2 < n_half) ok = issue_qk(g + 2);
         }
     } else if (warp >= 4) {
         // ------------------------------------------------------------ softmax
@@ -375,7 +413,6 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         const int q_row = q0 + t * BQ + r;
         const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
         const uint32_t s_addr = tmem_base + lane_base + TMEM_S + t * 128;
-        const uint32_t p_addr = s_addr + TMEM_P_OFF;
         const uint32_t o_addr = tmem_base + lane_base + TMEM_O + t * 128;
         float m_used = -INFINITY;
         float sum0 = 0.0f, sum1 = 0.0f;
@@ -394,88 +431,91 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         }
         bool ok = true;
 
-        for (int j = 0; ok && j < n_kv; ++j) {
-            if (!mbar_wait(&s_full[t], static_cast<uint32_t>(j & 1), abort_flag, P.err)) {
-                ok = false;
-                break;
-            }
-            tc_fence_after_sync();
-            const int valid = P.Lk - j * BKV;       // columns >= valid are padding (last block only)
-            float c0 = row_scale, c1 = row_scale;     // score multipliers of the two 64-key halves
-            float cq0 = 1.0f, cq1 = 1.0f;             // the same without the softmax scale
+        const bool biased = SAGE && bias_row != nullptr;   // uniform over the CTA
+        const int n_half = 2 * n_kv;
+        // One online-softmax step per 64-key half g: its scores sit in buffer g % 2 of the tile's S
+        // columns, and the other buffer is filled by the tensor pipe meanwhile, so a softmax warp goes
+        // from one half straight to the next.
+        // The tensor-memory read of half g + 1 is issued before P of half g is stored, so its
+        // latency and that of the store / barrier hand-over overlap.
+        uint32_t rr[64];
+        ok = mbar_wait(&s_full[t * 2], 0, abort_flag, P.err);
+        tc_fence_after_sync();
+        if (ok) tmem_ld_cols<64>(s_addr, rr);
+        for (int g = 0; ok && g < n_half; ++g) {
+            const int j = g >> 1, hb = g & 1;
+            const int valid = P.Lk - g * HK;        // columns >= valid are padding (last block only)
+            float c0 = row_scale;                   // score multiplier
+            float cq = 1.0f;                        // the same without the softmax scale
             if (SAGE) {
-                const float k0 = __ldg(ks_row + 2 * j), k1 = __ldg(ks_row + 2 * j + 1);
-                c0 *= k0;
-                c1 *= k1;
-                cq0 = q_scale * k0;
-                cq1 = q_scale * k1;
+                const float kscale = __ldg(ks_row + g);
+                c0 *= kscale;
+                cq = q_scale * kscale;
             }
-            const bool biased = SAGE && bias_row != nullptr;   // uniform over the CTA
-
-            // Each 64-key half of the block is one online-softmax step of its own: load, maximum,
-            // exponentials, P.  Nothing is read twice and 64 scores are live at a time.
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const float ch = h ? c1 : c0;
-                const int valid_h = valid - 64 * h;
-                uint32_t rr[64];
-                tmem_ld_cols<64>(s_addr + 64 * h, rr);
-                tmem_wait_ld();
-                const float4* bias_h =
-                    biased ? reinterpret_cast<const float4*>(smem + C::OFF_BIAS + (j % BIAS_STAGES) * (BKV * 4)) + 16 * h
-                           : nullptr;
-                const float mx = half_row_max<SAGE>(rr, ch, h ? cq1 : cq0, bias_h, P.scale_log2, valid_h);
-                // lazy rescale: keep exponentiating against the old maximum until it is stale by > 2^8
-                float alpha = 1.0f;
-                const bool grow = mx > m_used + kRescaleThreshold;
-                if (grow) {
-                    alpha = ex2(m_used - mx);   // 0 on the very first half (m_used = -inf)
-                    m_used = mx;
-                    sum0 *= alpha;
-                    sum1 *= alpha;
+            const uint32_t sb_addr = s_addr + hb * HK;
+            tmem_wait_ld();
+            const float4* bias_h =
+                biased ? reinterpret_cast<const float4*>(smem + C::OFF_BIAS + (j % BIAS_STAGES) * (BKV * 4)) + 16 * hb
+                       : nullptr;
+            const float mx = half_row_max<SAGE>(rr, c0, cq, bias_h, P.scale_log2, valid);
+            // lazy rescale: keep exponentiating against the old maximum until it is stale by > 2^8
+            float alpha = 1.0f;
+            const bool grow = mx > m_used + kRescaleThreshold;
+            if (grow) {
+                alpha = ex2(m_used - mx);   // 0 on the very first half (m_used = -inf)
+                m_used = mx;
+                sum0 *= alpha;
+                sum1 *= alpha;
+            }
+            if (g > 0 && __any_sync(0xffffffffu, grow)) {
+                // O_t holds the PV products up to half g - 1; the next one waits for this thread's P.
+                // S(g) complete means the product of half g - 2 has completed, so pv_done is in
+                // phase g - 1 or g and the parity wait below cannot alias.
+                if (!mbar_wait(&pv_done[t], static_cast<uint32_t>((g - 1) & 1), abort_flag, P.err)) {
+                    ok = false;
+                    break;
                 }
-                if ((j > 0 || h > 0) && __any_sync(0xffffffffu, grow)) {
-                    if (j > 0) {
-                        // S_t(j) complete => O_t += P_t V_{j-1} complete; the next PV waits for this thread's P
+                tc_fence_after_sync();
 #pragma unroll
-                        for (int c = 0; c < D / 32; ++c) {
-                            uint32_t oo[32];
-                            tmem_ld_cols<32>(o_addr + c * 32, oo);
-                            tmem_wait_ld();
+                for (int c = 0; c < D / 32; ++c) {
+                    uint32_t oo[32];
+                    tmem_ld_cols<32>(o_addr + c * 32, oo);
+                    tmem_wait_ld();
 #pragma unroll
-                            for (int i = 0; i < 32; ++i) oo[i] = __float_as_uint(__uint_as_float(oo[i]) * alpha);
-                            tmem_st_cols<32>(o_addr + c * 32, oo);
-                        }
-                    }
-                    if (h > 0) {
-                        // the first half's P of this block was written against the older maximum
-                        uint32_t pp[32];
-                        tmem_wait_st();
-                        tmem_ld_cols<32>(p_addr, pp);
-                        tmem_wait_ld();
-                        const __half2 a2 = __float2half2_rn(alpha);
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            __half2 v = __hmul2(*reinterpret_cast<__half2*>(&pp[i]), a2);
-                            pp[i] = *reinterpret_cast<uint32_t*>(&v);
-                        }
-                        tmem_st_cols<32>(p_addr, pp);
-                    }
+                    for (int i = 0; i < 32; ++i) oo[i] = __float_as_uint(__uint_as_float(oo[i]) * alpha);
+                    tmem_st_cols<32>(o_addr + c * 32, oo);
                 }
-                // P = exp2(score - m) as f16 pairs into S columns [32h, 32h + 32): the first half's own
-                // columns, all of them consumed by now
-                uint32_t p2[32];
+            }
+            // P = exp2(score - m) as f16 pairs over the first 32 columns of the buffer just read
+            uint32_t p2[32];
+            const float ce = biased ? P.scale_log2 : c0;
+            if (valid >= HK) {   // uniform; only the last key block can be ragged
                 if (SAGE && !biased) {
-                    half_row_exp<true>(rr, p2, ch, m_used, valid_h, sum0, sum1);
+                    half_row_exp<true, false>(rr, p2, ce, m_used, valid, sum0, sum1);
                 } else {
-                    half_row_exp<false>(rr, p2, biased ? P.scale_log2 : ch, m_used, valid_h, sum0, sum1);
+                    half_row_exp<false, false>(rr, p2, ce, m_used, valid, sum0, sum1);
                 }
-                tmem_st_cols<32>(p_addr + 32 * h, p2);
+            } else {
+                if (SAGE && !biased) {
+                    half_row_exp<true, true>(rr, p2, ce, m_used, valid, sum0, sum1);
+                } else {
+                    half_row_exp<false, true>(rr, p2, ce, m_used, valid, sum0, sum1);
+                }
             }
+            if (g + 1 < n_half) {
+                // all of rr has been consumed; the other buffer holds the next half
+                if (!mbar_wait(&s_full[t * 2 + (hb ^ 1)], static_cast<uint32_t>(((g + 1) >> 1) & 1), abort_flag, P.err)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after_sync();
+                tmem_ld_cols<64>(s_addr + (hb ^ 1) * HK, rr);
+            }
+            tmem_st_cols<32>(sb_addr, p2);
             tmem_wait_st();
             tc_fence_before_sync();
             __syncwarp();
-            if (elect_one()) mbar_arrive(&p_full[t]);
+            if (elect_one()) mbar_arrive(&p_full[t * 2 + hb]);
         }
 
         // ----------------------------------------------------------- epilogue
