@@ -17,9 +17,11 @@ that are generated and quantised on the device.
   cpu_baseline  the numpy oracle timed on this box's host cores on a bounded
              sample (whole blocks at full token count), extrapolated to a step
 
-With --gpus N > 1 every rank runs the same step on its own GPU (replicas; the
-path's sequence-parallel exchange is not part of this benchmark yet) and rank 0
-reports the slowest rank's time.
+With --gpus N > 1 (launched by torch.distributed.run, one process per GPU) the N
+ranks share ONE step by Ulysses sequence parallelism: every rank keeps all weights,
+owns 1/N of the tokens for the linears and norms and 1/N of the heads for
+attention; the two exchanges per block run over NCCL inside the library.  The
+total work is fixed ("scaling": "strong") and rank 0 reports the slowest rank's time.
 """
 from __future__ import annotations
 
@@ -240,6 +242,12 @@ def run_ours(args):
     model = edb.FluxModel(attention=attention, **kw)
     model.init_random(seed=0, std=0.02)
     init_launches = int(edb.lib().edb200_launch_count())
+    comm = None
+    if world > 1:
+        # Ulysses sequence parallelism: every rank holds all weights, 1/N of the tokens for the
+        # per-token work and 1/N of the heads for attention (NCCL exchange inside the library)
+        comm = edb.Comm()
+        model.set_comm(comm)
     model.prepare(lat[1], lat[2], n_txt)
     n_img = (lat[1] // 2) * (lat[2] // 2)
     tokens = n_img + n_txt
@@ -310,7 +318,10 @@ def run_ours(args):
         "kernel": "qgemm_kernel (dequant-fused q8_0 GEMM, tcgen05 kind::f16)",
         "bound": "tensor", "achieved": gemm_tflops, "peak": peaks["tflops"], "unit": "TFLOP/s",
         "frac": gemm_tflops / peaks["tflops"], "peak_source": peaks["source"] + " bf16 sustained",
-        "launches_per_step": gemm["launches"], "ms_per_step": gemm["ms"], "traffic": None,
+        "launches_per_step": gemm["launches"], "ms_per_step": gemm["ms"],
+        # DRAM bytes of one launch of the 4608 x 9216 x 3072 shape from the ncu capture summarised in
+        # profiles/qgemm_kernel_q8_0.md (algorithmic bytes of that launch: 143.3e6)
+        "traffic": 112.8e6 if args.workload == "flux1024_q8_0" else None,
     }
     classes = {k: {"ms": round(v["ms"], 3), "launches": v["launches"]} for k, v in prof.items()}
     classes["attention"]["tflops"] = round(att_tflops, 1)
@@ -323,12 +334,14 @@ def run_ours(args):
     h2d = h_lat.nbytes + h_ctx.nbytes + h_y.nbytes
     line = {
         "metric": METRIC, "value": ms, "unit": "ms", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": ms, "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
+        "ms_per_step": ms, "higher_is_better": False, "scaling": "weak" if world == 1 else "strong",
+        "vs_baseline": None,
         "dtype": "f16 operands / f32 accumulate (q8_0 weights dequantised to f16, INT8 QK^T)",
         "data": "synthetic",
-        "tokens_per_s": world * tokens / (ms / 1e3),
+        "tokens_per_s": tokens / (ms / 1e3),
         "config": {"workload": args.workload, "tokens": tokens, "attention": args.attention,
-                   "parallelism": "single GPU" if world == 1 else f"replicas x{world}",
+                   "parallelism": "single GPU" if world == 1 else f"ulysses sequence parallel x{world} (one step "
+                   "shared by all ranks: tokens split for linears/norms, heads split for attention)",
                    "l2": "inputs larger than L2: 12.6 GB of weights stream through every step",
                    "weight_bytes": edb.lib().edb200_flux_weight_bytes(model.handle),
                    "output_finite": finite, "init_launches": init_launches},

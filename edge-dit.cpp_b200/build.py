@@ -1,7 +1,8 @@
 """Builds libedb200.so (all CUDA kernels + the C ABI) in-tree for sm_100a.
 
 Usage: python edge-dit.cpp_b200/build.py [--force] [--verbose]
-The shared library has no Python or torch dependency; it links cudart only.
+The shared library has no Python or torch dependency; it links cudart only
+(NCCL, used by the sequence-parallel exchange, is resolved with dlopen at run time).
 """
 from __future__ import annotations
 
@@ -73,7 +74,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         sys.stderr.write("\n".join(log))
     if failed:
         raise RuntimeError("nvcc failed; see " + os.path.join(objdir, "ptxas.log"))
-    link = [nvcc, "-shared", "-o", OUT] + objs + ["-gencode", "arch=compute_100a,code=sm_100a", "-lcudart"]
+    link = [nvcc, "-shared", "-o", OUT] + objs + ["-gencode", "arch=compute_100a,code=sm_100a", "-lcudart", "-ldl"]
     subprocess.run(link, check=True)
     with open(STAMP, "w") as fh:
         fh.write(dig)

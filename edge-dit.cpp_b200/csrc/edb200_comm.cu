@@ -1,0 +1,269 @@
+// Sequence-parallel (Ulysses) redistribution between the ranks of one node.
+//
+// Every rank owns T_loc = T / P consecutive tokens for the per-token work (norms,
+// linears, residuals) and H / P heads for attention.  Around attention the layout
+// changes twice:
+//   heads a2a   [H, T_loc, d] on every rank  ->  [H/P, T, d]   (Q, K and V)
+//   tokens a2a  [T, (H/P) d]  on every rank  ->  [T_loc, H d]  (attention output)
+// This stands in for the reference's SP pack / split / gather callbacks and their
+// NCCL all-to-all (src/parallel/sp_parallel.cpp:99-469,793-831,
+// src/parallel/nccl_process_group.cpp:394-459).
+//
+// The head-major layout makes every message of the first exchange one contiguous
+// run on both sides, so it needs no pack or unpack kernel at all: one grouped
+// ncclSend / ncclRecv per (peer, head, tensor).  The second exchange lands in a
+// staging buffer ordered by source rank and one small copy kernel interleaves the
+// head groups into the token-major rows that the next linear reads.
+//
+// NCCL is resolved at run time from the already loaded libnccl.so.2 (the process
+// that owns the ranks brings it); the library itself links cudart only.
+#include "edb200_internal.h"
+
+#include <dlfcn.h>
+
+#include <cstring>
+#include <mutex>
+#include <vector>
+
+namespace edb {
+namespace {
+
+struct NcclId {
+    char internal[128];
+};
+using nccl_comm_t = void*;
+constexpr int kNcclUint8 = 1;
+
+struct NcclApi {
+    int (*GetUniqueId)(NcclId*) = nullptr;
+    int (*CommInitRank)(nccl_comm_t*, int, NcclId, int) = nullptr;
+    int (*CommDestroy)(nccl_comm_t) = nullptr;
+    int (*GroupStart)() = nullptr;
+    int (*GroupEnd)() = nullptr;
+    int (*Send)(const void*, size_t, int, int, nccl_comm_t, cudaStream_t) = nullptr;
+    int (*Recv)(void*, size_t, int, int, nccl_comm_t, cudaStream_t) = nullptr;
+    const char* (*GetErrorString)(int) = nullptr;
+    bool ok = false;
+};
+
+NcclApi* nccl_api() {
+    static NcclApi api;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+        if (h == nullptr) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+        if (h == nullptr) return;
+        auto sym = [&](const char* n) { return dlsym(h, n); };
+        api.GetUniqueId = reinterpret_cast<decltype(api.GetUniqueId)>(sym("ncclGetUniqueId"));
+        api.CommInitRank = reinterpret_cast<decltype(api.CommInitRank)>(sym("ncclCommInitRank"));
+        api.CommDestroy = reinterpret_cast<decltype(api.CommDestroy)>(sym("ncclCommDestroy"));
+        api.GroupStart = reinterpret_cast<decltype(api.GroupStart)>(sym("ncclGroupStart"));
+        api.GroupEnd = reinterpret_cast<decltype(api.GroupEnd)>(sym("ncclGroupEnd"));
+        api.Send = reinterpret_cast<decltype(api.Send)>(sym("ncclSend"));
+        api.Recv = reinterpret_cast<decltype(api.Recv)>(sym("ncclRecv"));
+        api.GetErrorString = reinterpret_cast<decltype(api.GetErrorString)>(sym("ncclGetErrorString"));
+        api.ok = api.GetUniqueId && api.CommInitRank && api.CommDestroy && api.GroupStart && api.GroupEnd && api.Send &&
+                 api.Recv && api.GetErrorString;
+    });
+    return api.ok ? &api : nullptr;
+}
+
+edb200_status_t check_nccl(int r, const char* what) {
+    if (r == 0) return EDB200_OK;
+    NcclApi* a = nccl_api();
+    return fail(EDB200_ERR_CUDA, "%s: NCCL error %d (%s)", what, r, a ? a->GetErrorString(r) : "?");
+}
+
+__global__ void interleave_heads_kernel(const uint4* __restrict__ staging, uint4* __restrict__ out, int world,
+                                        long long t_loc, int chunk16, long long ld16) {
+    // staging [world][t_loc][chunk16] -> out[t][p * chunk16 + c], 16-byte units
+    const long long total = (long long)world * t_loc * chunk16;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int c = static_cast<int>(i % chunk16);
+        const long long t = (i / chunk16) % t_loc;
+        const int p = static_cast<int>(i / ((long long)chunk16 * t_loc));
+        out[t * ld16 + (long long)p * chunk16 + c] = staging[i];
+    }
+}
+
+}  // namespace
+}  // namespace edb
+
+using namespace edb;
+
+struct edb200_comm {
+    nccl_comm_t comm = nullptr;
+    int rank = 0, world = 1;
+};
+
+extern "C" {
+
+edb200_status_t edb200_sp_shard(int64_t n_tokens, int64_t n_txt, int rank, int world, int64_t* t_loc,
+                                int64_t* n_txt_local, int64_t* img_first) {
+    if (world <= 0 || rank < 0 || rank >= world || n_tokens <= 0 || n_txt < 0 || n_txt > n_tokens) {
+        return fail(EDB200_ERR_INVALID, "sp_shard: bad argument");
+    }
+    if (n_tokens % world) {
+        return fail(EDB200_ERR_UNSUPPORTED, "sp_shard: %lld tokens do not divide over %d ranks", (long long)n_tokens, world);
+    }
+    const int64_t tl = n_tokens / world;
+    const int64_t first = (int64_t)rank * tl;
+    int64_t txt = n_txt - first;
+    if (txt < 0) txt = 0;
+    if (txt > tl) txt = tl;
+    if (t_loc) *t_loc = tl;
+    if (n_txt_local) *n_txt_local = txt;
+    if (img_first) *img_first = (first > n_txt ? first : n_txt) - n_txt;
+    return EDB200_OK;
+}
+
+int edb200_sp_heads_plan(int rank, int world, int heads, int64_t t_loc, int64_t row_bytes, int* peer,
+                         int64_t* send_off, int64_t* recv_off, int64_t* bytes, int cap) {
+    if (world <= 0 || rank < 0 || rank >= world || heads <= 0 || heads % world || t_loc <= 0 || row_bytes <= 0) return -1;
+    const int hp = heads / world;
+    const int n = world * hp;
+    if (peer == nullptr) return n;
+    if (cap < n) return -1;
+    const int64_t T = t_loc * world;
+    int i = 0;
+    for (int p = 0; p < world; ++p) {
+        for (int hl = 0; hl < hp; ++hl, ++i) {
+            peer[i] = p;
+            bytes[i] = t_loc * row_bytes;
+            // to rank p: its head hl is this rank's head p*hp + hl, all local tokens
+            send_off[i] = ((int64_t)(p * hp + hl) * t_loc) * row_bytes;
+            // from rank p: tokens [p*t_loc, (p+1)*t_loc) of local head hl
+            recv_off[i] = ((int64_t)hl * T + (int64_t)p * t_loc) * row_bytes;
+        }
+    }
+    return n;
+}
+
+edb200_status_t edb200_comm_unique_id(void* id128) {
+    if (id128 == nullptr) return fail(EDB200_ERR_INVALID, "comm_unique_id: null argument");
+    NcclApi* a = nccl_api();
+    if (a == nullptr) return fail(EDB200_ERR_UNSUPPORTED, "comm_unique_id: libnccl.so.2 not available");
+    NcclId id;
+    EDB_TRY(check_nccl(a->GetUniqueId(&id), "ncclGetUniqueId"));
+    memcpy(id128, id.internal, 128);
+    return EDB200_OK;
+}
+
+edb200_status_t edb200_comm_create(const void* id128, int rank, int world, edb200_comm_t** out) {
+    if (id128 == nullptr || out == nullptr || world <= 0 || rank < 0 || rank >= world) {
+        return fail(EDB200_ERR_INVALID, "comm_create: bad argument");
+    }
+    NcclApi* a = nccl_api();
+    if (a == nullptr) return fail(EDB200_ERR_UNSUPPORTED, "comm_create: libnccl.so.2 not available");
+    NcclId id;
+    memcpy(id.internal, id128, 128);
+    edb200_comm* c = new (std::nothrow) edb200_comm();
+    if (c == nullptr) return fail(EDB200_ERR_NOMEM, "comm_create: host allocation failed");
+    c->rank = rank;
+    c->world = world;
+    edb200_status_t st = check_nccl(a->CommInitRank(&c->comm, world, id, rank), "ncclCommInitRank");
+    if (st != EDB200_OK) {
+        delete c;
+        return st;
+    }
+    *out = c;
+    return EDB200_OK;
+}
+
+void edb200_comm_destroy(edb200_comm_t* c) {
+    if (c == nullptr) return;
+    NcclApi* a = nccl_api();
+    if (a != nullptr && c->comm != nullptr) a->CommDestroy(c->comm);
+    delete c;
+}
+
+int edb200_comm_rank(const edb200_comm_t* c) { return c ? c->rank : 0; }
+int edb200_comm_world(const edb200_comm_t* c) { return c ? c->world : 1; }
+
+edb200_status_t edb200_sp_all_to_all_heads(edb200_comm_t* c, const void* const* send, void* const* recv, int n_tensors,
+                                           int heads, int64_t t_loc, int64_t row_bytes, void* stream) {
+    if (c == nullptr || send == nullptr || recv == nullptr || n_tensors <= 0) {
+        return fail(EDB200_ERR_INVALID, "sp_all_to_all_heads: null argument");
+    }
+    NcclApi* a = nccl_api();
+    if (a == nullptr) return fail(EDB200_ERR_UNSUPPORTED, "sp_all_to_all_heads: libnccl.so.2 not available");
+    const int n = edb200_sp_heads_plan(c->rank, c->world, heads, t_loc, row_bytes, nullptr, nullptr, nullptr, nullptr, 0);
+    if (n < 0) return fail(EDB200_ERR_INVALID, "sp_all_to_all_heads: heads must divide over the ranks");
+    std::vector<int> peer(n);
+    std::vector<int64_t> so(n), ro(n), nb(n);
+    edb200_sp_heads_plan(c->rank, c->world, heads, t_loc, row_bytes, peer.data(), so.data(), ro.data(), nb.data(), n);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    EDB_TRY(check_nccl(a->GroupStart(), "ncclGroupStart"));
+    int rc = 0;
+    for (int t = 0; t < n_tensors && rc == 0; ++t) {
+        const char* sb = static_cast<const char*>(send[t]);
+        char* rb = static_cast<char*>(recv[t]);
+        for (int i = 0; i < n && rc == 0; ++i) {
+            rc = a->Send(sb + so[i], (size_t)nb[i], kNcclUint8, peer[i], c->comm, s);
+            if (rc == 0) rc = a->Recv(rb + ro[i], (size_t)nb[i], kNcclUint8, peer[i], c->comm, s);
+        }
+    }
+    const int rc_end = a->GroupEnd();
+    EDB_TRY(check_nccl(rc, "ncclSend/ncclRecv"));
+    return check_nccl(rc_end, "ncclGroupEnd");
+}
+
+edb200_status_t edb200_sp_all_to_all_tokens(edb200_comm_t* c, const void* send, void* staging, void* out, int64_t t_loc,
+                                            int64_t chunk_bytes, int64_t ld_out_bytes, void* stream) {
+    if (c == nullptr || send == nullptr || staging == nullptr || out == nullptr || t_loc <= 0 || chunk_bytes <= 0) {
+        return fail(EDB200_ERR_INVALID, "sp_all_to_all_tokens: bad argument");
+    }
+    if (chunk_bytes % 16 || ld_out_bytes % 16 || ld_out_bytes < chunk_bytes * c->world ||
+        (reinterpret_cast<uintptr_t>(staging) & 15u) || (reinterpret_cast<uintptr_t>(out) & 15u)) {
+        return fail(EDB200_ERR_INVALID, "sp_all_to_all_tokens: rows must be multiples of 16 bytes and 16-byte aligned");
+    }
+    NcclApi* a = nccl_api();
+    if (a == nullptr) return fail(EDB200_ERR_UNSUPPORTED, "sp_all_to_all_tokens: libnccl.so.2 not available");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const size_t piece = (size_t)(t_loc * chunk_bytes);
+    EDB_TRY(check_nccl(a->GroupStart(), "ncclGroupStart"));
+    int rc = 0;
+    for (int p = 0; p < c->world && rc == 0; ++p) {
+        rc = a->Send(static_cast<const char*>(send) + (size_t)p * piece, piece, kNcclUint8, p, c->comm, s);
+        if (rc == 0) rc = a->Recv(static_cast<char*>(staging) + (size_t)p * piece, piece, kNcclUint8, p, c->comm, s);
+    }
+    const int rc_end = a->GroupEnd();
+    EDB_TRY(check_nccl(rc, "ncclSend/ncclRecv"));
+    EDB_TRY(check_nccl(rc_end, "ncclGroupEnd"));
+    const long long total16 = (long long)c->world * t_loc * (chunk_bytes / 16);
+    const int threads = 256;
+    long long blocks = (total16 + threads - 1) / threads;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    ProfScope prof(s, PROF_ELEMENTWISE, 0.0, 2.0 * (double)total16 * 16.0);
+    interleave_heads_kernel<<<static_cast<unsigned>(blocks), threads, 0, s>>>(
+        static_cast<const uint4*>(staging), static_cast<uint4*>(out), c->world, t_loc, static_cast<int>(chunk_bytes / 16),
+        ld_out_bytes / 16);
+    count_launch();
+    return check_cuda(cudaGetLastError(), "sp interleave launch");
+}
+
+edb200_status_t edb200_sp_all_gather_rows(edb200_comm_t* c, const void* send, void* recv, const int64_t* row_first,
+                                          const int64_t* row_count, int64_t row_bytes, void* stream) {
+    if (c == nullptr || recv == nullptr || row_first == nullptr || row_count == nullptr || row_bytes <= 0) {
+        return fail(EDB200_ERR_INVALID, "sp_all_gather_rows: bad argument");
+    }
+    NcclApi* a = nccl_api();
+    if (a == nullptr) return fail(EDB200_ERR_UNSUPPORTED, "sp_all_gather_rows: libnccl.so.2 not available");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const size_t mine = (size_t)(row_count[c->rank] * row_bytes);
+    EDB_TRY(check_nccl(a->GroupStart(), "ncclGroupStart"));
+    int rc = 0;
+    for (int p = 0; p < c->world && rc == 0; ++p) {
+        if (mine > 0) rc = a->Send(send, mine, kNcclUint8, p, c->comm, s);
+        const size_t theirs = (size_t)(row_count[p] * row_bytes);
+        if (rc == 0 && theirs > 0) {
+            rc = a->Recv(static_cast<char*>(recv) + (size_t)(row_first[p] * row_bytes), theirs, kNcclUint8, p, c->comm, s);
+        }
+    }
+    const int rc_end = a->GroupEnd();
+    EDB_TRY(check_nccl(rc, "ncclSend/ncclRecv"));
+    return check_nccl(rc_end, "ncclGroupEnd");
+}
+
+}  // extern "C"

@@ -20,6 +20,7 @@
 #include <cuda_fp16.h>
 #include <cmath>
 #include <cstring>
+#include <vector>
 
 using namespace edb;
 
@@ -37,6 +38,12 @@ struct edb200_flux {
           *YVEC = nullptr;
     void* SAGE = nullptr;
     int64_t sage_bytes = 0;
+    // sequence-parallel execution (world > 1): this rank's token slice and exchange buffers
+    edb200_comm_t* comm = nullptr;
+    int rank = 0, world = 1;
+    int64_t t_loc = 0, txt_l = 0, img_l = 0, img_first = 0;
+    void *QL = nullptr, *KL = nullptr, *VL = nullptr, *AOUT = nullptr, *STG = nullptr;
+    float* TOK_LOC = nullptr;
     float* tap = nullptr;
     // host staging for compute_host
     float* pinned = nullptr;
@@ -131,12 +138,6 @@ std::vector<float> build_flux_pe(const edb200_flux_config_t& c, int h_tok, int w
     return pe;
 }
 
-#define EDB_TRY(expr)                          \
-    do {                                       \
-        edb200_status_t _st = (expr);          \
-        if (_st != EDB200_OK) return _st;      \
-    } while (0)
-
 edb200_epilogue_t make_ep(void* out, int dt, int64_t ldo, const float* bias) {
     edb200_epilogue_t ep;
     memset(&ep, 0, sizeof(ep));
@@ -168,16 +169,65 @@ edb200_status_t dense(edb200_flux* m, const std::string& name, const float* x, i
                              y, ldy, s);
 }
 
+// Attention over the whole sequence.  Single GPU: all heads, output straight into `out`.
+// Sequence parallel: Q/K/V of the local tokens (QL/KL/VL, head-major) are exchanged for
+// all tokens of this rank's heads, attention runs on those, and its output is exchanged
+// back into the local token rows of `out` (FLUX forward_sp, flux.hpp:1928-2369).
 edb200_status_t attention(edb200_flux* m, int64_t T, void* out, int64_t ld_out, cudaStream_t s) {
     const edb200_flux_config_t& c = m->cfg;
     const int d = c.hidden_size / c.num_heads;
+    const int heads = c.num_heads / m->world;
     const float scale = 1.0f / std::sqrt(static_cast<float>(d));
-    if (c.attention == EDB200_ATTN_SAGE_INT8) {
-        return edb200_sage_attention(m->Q, m->K, m->V, c.num_heads, T, d, scale,
-                                     (c.sage_smooth_q ? EDB200_SAGE_SMOOTH_Q : 0) | EDB200_SAGE_FAST_MEANS, m->SAGE,
-                                     m->sage_bytes, out, EDB200_TYPE_F16, ld_out, s);
+    void* att_out = out;
+    int64_t att_ld = ld_out;
+    if (m->world > 1) {
+        const void* send[3] = {m->QL, m->KL, m->VL};
+        void* recv[3] = {m->Q, m->K, m->V};
+        EDB_TRY(edb200_sp_all_to_all_heads(m->comm, send, recv, 3, c.num_heads, m->t_loc, (int64_t)d * 2, s));
+        att_out = m->AOUT;
+        att_ld = (int64_t)heads * d;
     }
-    return edb200_attention_f16(m->Q, m->K, m->V, c.num_heads, T, T, d, scale, out, EDB200_TYPE_F16, ld_out, s);
+    if (c.attention == EDB200_ATTN_SAGE_INT8) {
+        EDB_TRY(edb200_sage_attention(m->Q, m->K, m->V, heads, T, d, scale,
+                                      (c.sage_smooth_q ? EDB200_SAGE_SMOOTH_Q : 0) | EDB200_SAGE_FAST_MEANS, m->SAGE,
+                                      m->sage_bytes, att_out, EDB200_TYPE_F16, att_ld, s));
+    } else {
+        EDB_TRY(edb200_attention_f16(m->Q, m->K, m->V, heads, T, T, d, scale, att_out, EDB200_TYPE_F16, att_ld, s));
+    }
+    if (m->world > 1) {
+        EDB_TRY(edb200_sp_all_to_all_tokens(m->comm, m->AOUT, m->STG, out, m->t_loc, (int64_t)heads * d * 2, ld_out * 2, s));
+    }
+    return EDB200_OK;
+}
+
+// Row-count-tolerant wrappers: under sequence parallelism a rank may own no text rows.
+edb200_status_t ln_mod(const float* x, int64_t H, const float* shift, const float* scale, int64_t rows, void* y,
+                       int y_dtype, cudaStream_t s) {
+    if (rows == 0) return EDB200_OK;
+    return edb200_layernorm_modulate(x, H, shift, scale, nullptr, nullptr, rows, H, 1e-6f, y, y_dtype, H, s);
+}
+
+edb200_status_t mm_pair(const edb200_qweight_t* w0, const void* x0, int64_t m0, int64_t ldx0, const edb200_epilogue_t* e0,
+                        const edb200_qweight_t* w1, const void* x1, int64_t m1, int64_t ldx1, const edb200_epilogue_t* e1,
+                        cudaStream_t s) {
+    if (m0 > 0 && m1 > 0) return edb200_mul_mat_q_pair(w0, x0, m0, ldx0, e0, w1, x1, m1, ldx1, e1, EDB200_TYPE_F16, s);
+    if (m0 > 0) return edb200_mul_mat_q(w0, x0, EDB200_TYPE_F16, m0, ldx0, e0, s);
+    if (m1 > 0) return edb200_mul_mat_q(w1, x1, EDB200_TYPE_F16, m1, ldx1, e1, s);
+    return EDB200_OK;
+}
+
+edb200_status_t qk_pack(edb200_flux* m, const __half* qkv, int64_t rows, int64_t local_first, const float* qs,
+                        const float* ks, cudaStream_t s) {
+    if (rows == 0) return EDB200_OK;
+    const edb200_flux_config_t& c = m->cfg;
+    const int64_t H = c.hidden_size;
+    const int d = static_cast<int>(H / c.num_heads);
+    const bool sp = m->world > 1;
+    // the position table is indexed by the global row: shift it by this rank's first token
+    const float* pe = m->PE + (int64_t)m->rank * m->t_loc * (d / 2) * 4;
+    return edb200_qk_norm_rope_pack(qkv, EDB200_TYPE_F16, 3 * H, 0, H, 2 * H, rows, c.num_heads, d, qs, ks, 1e-6f, pe,
+                                    local_first, m->t_loc, sp ? m->QL : m->Q, sp ? m->KL : m->K, sp ? m->VL : m->V,
+                                    EDB200_TYPE_F16, s);
 }
 
 }  // namespace
@@ -271,7 +321,15 @@ edb200_status_t edb200_flux_prepare(edb200_flux_t* m, int latent_h, int latent_w
     const int h_tok = latent_h / p, w_tok = latent_w / p;
     const int64_t n_img = (int64_t)h_tok * w_tok, T = n_img + n_txt;
     const int lat_c = c.in_channels / (p * p);
-    const int64_t sage = c.attention == EDB200_ATTN_SAGE_INT8 ? edb200_sage_scratch_bytes(c.num_heads, T, (int)d) : 0;
+    int64_t t_loc = T, txt_l = n_txt, img_first = 0;
+    if (m->world > 1) {
+        if (c.num_heads % m->world) {
+            return fail(EDB200_ERR_UNSUPPORTED, "flux_prepare: %d heads do not divide over %d ranks", c.num_heads, m->world);
+        }
+        EDB_TRY(edb200_sp_shard(T, n_txt, m->rank, m->world, &t_loc, &txt_l, &img_first));
+    }
+    const int64_t sage =
+        c.attention == EDB200_ATTN_SAGE_INT8 ? edb200_sage_scratch_bytes(c.num_heads / m->world, T, (int)d) : 0;
     const int64_t lat_elems = (int64_t)lat_c * latent_h * latent_w;
     const int64_t pe_elems = T * (d / 2) * 4;
     auto al = [](int64_t b) { return (b + 255) & ~int64_t(255); };
@@ -281,6 +339,7 @@ edb200_status_t edb200_flux_prepare(edb200_flux_t* m, int latent_h, int latent_w
     total += al(mods_per_step(c) * 4) + 3 * al(H * 4) + al(256 * 4) + 2 * al(n_img * c.in_channels * 4);
     total += al(n_img * H * 4) + al(pe_elems * 4) + al(128 * 4) + 2 * al(lat_elems * 4) +
              al((int64_t)n_txt * c.context_in_dim * 4) + al(c.vec_in_dim * 4) + al(sage) + 4096;
+    if (m->world > 1) total += 5 * al(t_loc * H * 2) + al(n_img * c.in_channels * 4);
     cudaStreamSynchronize(s);
     EDB_TRY(m->ws.reserve(total));
     Workspace& w = m->ws;
@@ -307,6 +366,21 @@ edb200_status_t edb200_flux_prepare(edb200_flux_t* m, int latent_h, int latent_w
     m->YVEC = w.take_n<float>(c.vec_in_dim);
     m->SAGE = sage > 0 ? w.take(sage) : nullptr;
     m->sage_bytes = sage;
+    m->QL = m->KL = m->VL = m->AOUT = m->STG = nullptr;
+    m->TOK_LOC = nullptr;
+    if (m->world > 1) {
+        m->QL = w.take(t_loc * H * 2);
+        m->KL = w.take(t_loc * H * 2);
+        m->VL = w.take(t_loc * H * 2);
+        m->AOUT = w.take(t_loc * H * 2);   // [T, (heads / world) * d] = the same number of elements
+        m->STG = w.take(t_loc * H * 2);
+        m->TOK_LOC = w.take_n<float>(n_img * c.in_channels);
+        if (m->TOK_LOC == nullptr) return fail(EDB200_ERR_NOMEM, "flux_prepare: workspace accounting error");
+    }
+    m->t_loc = t_loc;
+    m->txt_l = txt_l;
+    m->img_l = t_loc - txt_l;
+    m->img_first = img_first;
     if (m->YVEC == nullptr || (sage > 0 && m->SAGE == nullptr)) {
         return fail(EDB200_ERR_NOMEM, "flux_prepare: workspace accounting error");
     }
@@ -334,6 +408,15 @@ edb200_status_t edb200_flux_prepare(edb200_flux_t* m, int latent_h, int latent_w
     return EDB200_OK;
 }
 
+edb200_status_t edb200_flux_set_comm(edb200_flux_t* m, edb200_comm_t* comm) {
+    if (m == nullptr) return fail(EDB200_ERR_INVALID, "flux_set_comm: null model");
+    m->comm = comm;
+    m->rank = comm ? edb200_comm_rank(comm) : 0;
+    m->world = comm ? edb200_comm_world(comm) : 1;
+    m->lat_h = m->lat_w = m->n_txt = 0;   // the workspace must be prepared again
+    return EDB200_OK;
+}
+
 edb200_status_t edb200_flux_set_tap(edb200_flux_t* m, float* tap) {
     if (m == nullptr) return fail(EDB200_ERR_INVALID, "flux_set_tap: null model");
     m->tap = tap;
@@ -350,8 +433,10 @@ edb200_status_t edb200_flux_step(edb200_flux_t* m, const float* latent, float ti
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const edb200_flux_config_t& c = m->cfg;
     const int64_t H = c.hidden_size, M = c.mlp_hidden;
-    const int d = static_cast<int>(H / c.num_heads);
-    const int64_t n_txt = m->n_txt, n_img = m->n_img, T = n_txt + n_img;
+    const int64_t T = (int64_t)m->n_txt + m->n_img;   // whole sequence (attention length)
+    // rows this rank owns: all of them on one GPU, a slice [text rows ; image rows] otherwise
+    const int64_t n_txt = m->txt_l, n_img = m->img_l, TL = m->t_loc;
+    const int64_t txt_first = m->world > 1 ? (int64_t)m->rank * TL : 0;   // first owned text row (if any)
     const int lat_c = c.in_channels / (c.patch_size * c.patch_size);
     const int F16 = EDB200_TYPE_F16;
     float* X_txt = m->X;
@@ -363,8 +448,14 @@ edb200_status_t edb200_flux_step(edb200_flux_t* m, const float* latent, float ti
 
     // ---- prelude (Flux::forward_orig, flux.hpp:3886-3965)
     launch_patchify(latent, m->TOK_IN, lat_c, m->lat_h, m->lat_w, c.patch_size, s);
-    EDB_TRY(dense(m, "img_in", m->TOK_IN, n_img, c.in_channels, 0, EDB200_ACT_NONE, X_img, H, s));
-    EDB_TRY(dense(m, "txt_in", context, n_txt, c.context_in_dim, 0, EDB200_ACT_NONE, X_txt, H, s));
+    if (n_img > 0) {
+        EDB_TRY(dense(m, "img_in", m->TOK_IN + m->img_first * c.in_channels, n_img, c.in_channels, 0, EDB200_ACT_NONE,
+                      X_img, H, s));
+    }
+    if (n_txt > 0) {
+        EDB_TRY(dense(m, "txt_in", context + txt_first * c.context_in_dim, n_txt, c.context_in_dim, 0, EDB200_ACT_NONE,
+                      X_txt, H, s));
+    }
     launch_timestep_embedding(m->FREQ, timestep, 1000.0f, 128, m->TEMB, s);
     EDB_TRY(dense(m, "time_in.in_layer", m->TEMB, 1, 256, 0, EDB200_ACT_SILU, m->TMP_H, H, s));
     EDB_TRY(dense(m, "time_in.out_layer", m->TMP_H, 1, H, 0, EDB200_ACT_NONE, m->VEC, H, s));
@@ -400,23 +491,18 @@ edb200_status_t edb200_flux_step(edb200_flux_t* m, const float* latent, float ti
         const std::string p = "double_blocks." + std::to_string(i) + ".";
         const float* im = mods + (int64_t)i * 12 * H;   // shift1 scale1 gate1 shift2 scale2 gate2
         const float* tm = im + 6 * H;
-        EDB_TRY(edb200_layernorm_modulate(X_img, H, im, im + H, nullptr, nullptr, n_img, H, 1e-6f, xmod + n_txt * H,
-                                          F16, H, s));
-        EDB_TRY(edb200_layernorm_modulate(X_txt, H, tm, tm + H, nullptr, nullptr, n_txt, H, 1e-6f, xmod, F16, H, s));
+        EDB_TRY(ln_mod(X_img, H, im, im + H, n_img, xmod + n_txt * H, F16, s));
+        EDB_TRY(ln_mod(X_txt, H, tm, tm + H, n_txt, xmod, F16, s));
         {
             const Lin li = qlin(m, p + "img_attn.qkv"), lt = qlin(m, p + "txt_attn.qkv");
             edb200_epilogue_t ei = make_ep(qkv + n_txt * 3 * H, F16, 3 * H, li.b);
             edb200_epilogue_t et = make_ep(qkv, F16, 3 * H, lt.b);
-            EDB_TRY(edb200_mul_mat_q_pair(li.w, xmod + n_txt * H, n_img, H, &ei, lt.w, xmod, n_txt, H, &et, F16, s));
+            EDB_TRY(mm_pair(li.w, xmod + n_txt * H, n_img, H, &ei, lt.w, xmod, n_txt, H, &et, s));
         }
-        EDB_TRY(edb200_qk_norm_rope_pack(qkv + n_txt * 3 * H, F16, 3 * H, 0, H, 2 * H, n_img, c.num_heads, d,
-                                         fparam(m, p + "img_attn.norm.query_norm.scale"),
-                                         fparam(m, p + "img_attn.norm.key_norm.scale"), 1e-6f, m->PE, n_txt, T, m->Q,
-                                         m->K, m->V, F16, s));
-        EDB_TRY(edb200_qk_norm_rope_pack(qkv, F16, 3 * H, 0, H, 2 * H, n_txt, c.num_heads, d,
-                                         fparam(m, p + "txt_attn.norm.query_norm.scale"),
-                                         fparam(m, p + "txt_attn.norm.key_norm.scale"), 1e-6f, m->PE, 0, T, m->Q, m->K,
-                                         m->V, F16, s));
+        EDB_TRY(qk_pack(m, qkv + n_txt * 3 * H, n_img, n_txt, fparam(m, p + "img_attn.norm.query_norm.scale"),
+                        fparam(m, p + "img_attn.norm.key_norm.scale"), s));
+        EDB_TRY(qk_pack(m, qkv, n_txt, 0, fparam(m, p + "txt_attn.norm.query_norm.scale"),
+                        fparam(m, p + "txt_attn.norm.key_norm.scale"), s));
         EDB_TRY(attention(m, T, cat, H + M, s));
         {
             const Lin li = qlin(m, p + "img_attn.proj"), lt = qlin(m, p + "txt_attn.proj");
@@ -424,20 +510,17 @@ edb200_status_t edb200_flux_step(edb200_flux_t* m, const float* latent, float ti
             ei.residual = X_img, ei.ld_res = H, ei.gate = im + 2 * H;
             edb200_epilogue_t et = make_ep(X_txt, EDB200_TYPE_F32, H, lt.b);
             et.residual = X_txt, et.ld_res = H, et.gate = tm + 2 * H;
-            EDB_TRY(edb200_mul_mat_q_pair(li.w, cat + n_txt * (H + M), n_img, H + M, &ei, lt.w, cat, n_txt, H + M, &et,
-                                          F16, s));
+            EDB_TRY(mm_pair(li.w, cat + n_txt * (H + M), n_img, H + M, &ei, lt.w, cat, n_txt, H + M, &et, s));
         }
-        EDB_TRY(edb200_layernorm_modulate(X_img, H, im + 3 * H, im + 4 * H, nullptr, nullptr, n_img, H, 1e-6f,
-                                          xmod + n_txt * H, F16, H, s));
-        EDB_TRY(edb200_layernorm_modulate(X_txt, H, tm + 3 * H, tm + 4 * H, nullptr, nullptr, n_txt, H, 1e-6f, xmod,
-                                          F16, H, s));
+        EDB_TRY(ln_mod(X_img, H, im + 3 * H, im + 4 * H, n_img, xmod + n_txt * H, F16, s));
+        EDB_TRY(ln_mod(X_txt, H, tm + 3 * H, tm + 4 * H, n_txt, xmod, F16, s));
         {
             const Lin li = qlin(m, p + "img_mlp.0"), lt = qlin(m, p + "txt_mlp.0");
             edb200_epilogue_t ei = make_ep(hid + n_txt * M, F16, M, li.b);
             ei.act = EDB200_ACT_GELU_TANH;
             edb200_epilogue_t et = make_ep(hid, F16, M, lt.b);
             et.act = EDB200_ACT_GELU_TANH;
-            EDB_TRY(edb200_mul_mat_q_pair(li.w, xmod + n_txt * H, n_img, H, &ei, lt.w, xmod, n_txt, H, &et, F16, s));
+            EDB_TRY(mm_pair(li.w, xmod + n_txt * H, n_img, H, &ei, lt.w, xmod, n_txt, H, &et, s));
         }
         {
             const Lin li = qlin(m, p + "img_mlp.2"), lt = qlin(m, p + "txt_mlp.2");
@@ -445,10 +528,10 @@ edb200_status_t edb200_flux_step(edb200_flux_t* m, const float* latent, float ti
             ei.residual = X_img, ei.ld_res = H, ei.gate = im + 5 * H;
             edb200_epilogue_t et = make_ep(X_txt, EDB200_TYPE_F32, H, lt.b);
             et.residual = X_txt, et.ld_res = H, et.gate = tm + 5 * H;
-            EDB_TRY(edb200_mul_mat_q_pair(li.w, hid + n_txt * M, n_img, M, &ei, lt.w, hid, n_txt, M, &et, F16, s));
+            EDB_TRY(mm_pair(li.w, hid + n_txt * M, n_img, M, &ei, lt.w, hid, n_txt, M, &et, s));
         }
         if (m->tap) {
-            cudaMemcpyAsync(m->tap + (int64_t)i * T * H, m->X, T * H * 4, cudaMemcpyDeviceToDevice, s);
+            cudaMemcpyAsync(m->tap + (int64_t)i * TL * H, m->X, TL * H * 4, cudaMemcpyDeviceToDevice, s);
         }
     }
 
@@ -456,7 +539,7 @@ edb200_status_t edb200_flux_step(edb200_flux_t* m, const float* latent, float ti
     for (int i = 0; i < c.depth_single_blocks; ++i) {
         const std::string p = "single_blocks." + std::to_string(i) + ".";
         const float* sm = smods + (int64_t)i * 3 * H;   // shift scale gate
-        EDB_TRY(edb200_layernorm_modulate(m->X, H, sm, sm + H, nullptr, nullptr, T, H, 1e-6f, xmod, F16, H, s));
+        EDB_TRY(ln_mod(m->X, H, sm, sm + H, TL, xmod, F16, s));
         {
             const Lin l1 = qlin(m, p + "linear1");
             edb200_epilogue_t ep = make_ep(qkv, F16, 3 * H, l1.b);
@@ -465,27 +548,40 @@ edb200_status_t edb200_flux_step(edb200_flux_t* m, const float* latent, float ti
             ep.out2_dtype = F16;
             ep.ldo2 = H + M;
             ep.act2 = EDB200_ACT_GELU_TANH;
-            EDB_TRY(edb200_mul_mat_q(l1.w, xmod, F16, T, H, &ep, s));
+            EDB_TRY(edb200_mul_mat_q(l1.w, xmod, F16, TL, H, &ep, s));
         }
-        EDB_TRY(edb200_qk_norm_rope_pack(qkv, F16, 3 * H, 0, H, 2 * H, T, c.num_heads, d,
-                                         fparam(m, p + "norm.query_norm.scale"), fparam(m, p + "norm.key_norm.scale"),
-                                         1e-6f, m->PE, 0, T, m->Q, m->K, m->V, F16, s));
+        EDB_TRY(qk_pack(m, qkv, TL, 0, fparam(m, p + "norm.query_norm.scale"), fparam(m, p + "norm.key_norm.scale"), s));
         EDB_TRY(attention(m, T, cat, H + M, s));
         {
             const Lin l2 = qlin(m, p + "linear2");
             edb200_epilogue_t ep = make_ep(m->X, EDB200_TYPE_F32, H, l2.b);
             ep.residual = m->X, ep.ld_res = H, ep.gate = sm + 2 * H;
-            EDB_TRY(edb200_mul_mat_q(l2.w, cat, F16, T, H + M, &ep, s));
+            EDB_TRY(edb200_mul_mat_q(l2.w, cat, F16, TL, H + M, &ep, s));
         }
         if (m->tap) {
-            cudaMemcpyAsync(m->tap + (int64_t)(c.depth + i) * T * H, m->X, T * H * 4, cudaMemcpyDeviceToDevice, s);
+            cudaMemcpyAsync(m->tap + (int64_t)(c.depth + i) * TL * H, m->X, TL * H * 4, cudaMemcpyDeviceToDevice, s);
         }
     }
 
     // ---- final layer on the image rows + unpatchify (LastLayer::forward, flux.hpp:3533-3559)
-    EDB_TRY(edb200_layernorm_modulate(X_img, H, fmods, fmods + H, nullptr, nullptr, n_img, H, 1e-6f, m->FIN,
-                                      EDB200_TYPE_F32, H, s));
-    EDB_TRY(dense(m, "final_layer.linear", m->FIN, n_img, H, 0, EDB200_ACT_NONE, m->TOK_OUT, c.in_channels, s));
+    EDB_TRY(ln_mod(X_img, H, fmods, fmods + H, n_img, m->FIN, EDB200_TYPE_F32, s));
+    if (m->world == 1) {
+        EDB_TRY(dense(m, "final_layer.linear", m->FIN, n_img, H, 0, EDB200_ACT_NONE, m->TOK_OUT, c.in_channels, s));
+    } else {
+        // every rank projects its image rows, then all ranks gather the whole token grid
+        if (n_img > 0) {
+            EDB_TRY(dense(m, "final_layer.linear", m->FIN, n_img, H, 0, EDB200_ACT_NONE, m->TOK_LOC, c.in_channels, s));
+        }
+        std::vector<int64_t> first(m->world), count(m->world);
+        for (int r = 0; r < m->world; ++r) {
+            int64_t tl = 0, tx = 0, f = 0;
+            EDB_TRY(edb200_sp_shard(T, m->n_txt, r, m->world, &tl, &tx, &f));
+            first[r] = f;
+            count[r] = tl - tx;
+        }
+        EDB_TRY(edb200_sp_all_gather_rows(m->comm, m->TOK_LOC, m->TOK_OUT, first.data(), count.data(),
+                                          (int64_t)c.in_channels * 4, s));
+    }
     launch_unpatchify(m->TOK_OUT, out, lat_c, m->lat_h, m->lat_w, c.patch_size, s);
     return check_cuda(cudaGetLastError(), "flux_step");
 }

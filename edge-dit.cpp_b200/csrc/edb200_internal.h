@@ -62,6 +62,12 @@ struct ProfScope {
 
 }  // namespace edb
 
+#define EDB_TRY(expr)                          \
+    do {                                       \
+        edb200_status_t _st = (expr);          \
+        if (_st != EDB200_OK) return _st;      \
+    } while (0)
+
 // Repacked quantised weight (device resident), tiled for the GEMM's
 // "one thread per weight row" dequantisers.
 //

@@ -1,5 +1,5 @@
-// Thin inline-PTX wrappers for sm_100a: mbarrier, TMA (cp.async.bulk.tensor, no
-// multicast anywhere), tensor memory (tcgen05.alloc/ld/st) and tcgen05.mma.
+// Thin inline-PTX wrappers for sm_100a: mbarrier, TMA (cp.async.bulk.tensor, every
+// copy addressed to the issuing CTA only), tensor memory (tcgen05.alloc/ld/st) and tcgen05.mma.
 // Every wait in this file is bounded: it gives up after a wall-clock limit,
 // raises a per-CTA abort flag and lets the caller fall through to teardown.
 #pragma once

@@ -85,6 +85,19 @@ _SIGS = {
     "edb200_sage_attention": (C.c_int, [c_vp, c_vp, c_vp, C.c_int, c_i64, C.c_int, C.c_float, C.c_int, c_vp, c_i64,
                                         c_vp, C.c_int, c_i64, c_vp]),
     "edb200_sage_key_means_static": (C.c_int, [c_vp, C.c_int, c_i64, C.c_int, c_vp, c_vp]),
+    "edb200_sp_shard": (C.c_int, [c_i64, c_i64, C.c_int, C.c_int, C.POINTER(c_i64), C.POINTER(c_i64), C.POINTER(c_i64)]),
+    "edb200_sp_heads_plan": (C.c_int, [C.c_int, C.c_int, C.c_int, c_i64, c_i64, C.POINTER(C.c_int), C.POINTER(c_i64),
+                                       C.POINTER(c_i64), C.POINTER(c_i64), C.c_int]),
+    "edb200_comm_unique_id": (C.c_int, [c_vp]),
+    "edb200_comm_create": (C.c_int, [c_vp, C.c_int, C.c_int, C.POINTER(c_vp)]),
+    "edb200_comm_destroy": (None, [c_vp]),
+    "edb200_comm_rank": (C.c_int, [c_vp]),
+    "edb200_comm_world": (C.c_int, [c_vp]),
+    "edb200_sp_all_to_all_heads": (C.c_int, [c_vp, C.POINTER(c_vp), C.POINTER(c_vp), C.c_int, C.c_int, c_i64, c_i64,
+                                             c_vp]),
+    "edb200_sp_all_to_all_tokens": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_vp]),
+    "edb200_sp_all_gather_rows": (C.c_int, [c_vp, c_vp, c_vp, C.POINTER(c_i64), C.POINTER(c_i64), c_i64, c_vp]),
+    "edb200_flux_set_comm": (C.c_int, [c_vp, c_vp]),
     "edb200_flux_create": (C.c_int, [C.POINTER(FluxConfig), C.POINTER(c_vp)]),
     "edb200_flux_destroy": (None, [c_vp]),
     "edb200_flux_tensor_count": (C.c_int, [c_vp]),
@@ -182,6 +195,47 @@ def mul_mat_q(w: QWeight, x, ep: Epilogue):
                                  current_stream()))
 
 
+def sp_shard(n_tokens, n_txt, rank, world):
+    """(t_loc, n_txt_local, img_first) of `rank`'s token slice."""
+    a, b, c = c_i64(), c_i64(), c_i64()
+    check(lib().edb200_sp_shard(n_tokens, n_txt, rank, world, C.byref(a), C.byref(b), C.byref(c)))
+    return a.value, b.value, c.value
+
+
+def sp_heads_plan(rank, world, heads, t_loc, row_bytes):
+    """Messages of the heads exchange as (peer, send_off, recv_off, bytes) tuples."""
+    n = lib().edb200_sp_heads_plan(rank, world, heads, t_loc, row_bytes, None, None, None, None, 0)
+    if n < 0:
+        raise EdbError(1, "sp_heads_plan: bad argument")
+    peer, so, ro, nb = (C.c_int * n)(), (c_i64 * n)(), (c_i64 * n)(), (c_i64 * n)()
+    lib().edb200_sp_heads_plan(rank, world, heads, t_loc, row_bytes, peer, so, ro, nb, n)
+    return [(peer[i], so[i], ro[i], nb[i]) for i in range(n)]
+
+
+class Comm:
+    """NCCL communicator of the library over the ranks of an initialised torch.distributed
+    group (one process per GPU); torch.distributed only carries the 128-byte id."""
+
+    def __init__(self):
+        import torch
+        import torch.distributed as dist
+        rank, world = dist.get_rank(), dist.get_world_size()
+        buf = C.create_string_buffer(128)
+        if rank == 0:
+            check(lib().edb200_comm_unique_id(buf))
+        obj = [bytes(buf.raw)]
+        dist.broadcast_object_list(obj, src=0)
+        h = c_vp()
+        check(lib().edb200_comm_create(obj[0], rank, world, C.byref(h)))
+        self.handle, self.rank, self.world = h, rank, world
+        torch.cuda.synchronize()
+
+    def close(self):
+        if getattr(self, "handle", None) and _lib is not None:
+            _lib.edb200_comm_destroy(self.handle)
+            self.handle = None
+
+
 class FluxModel:
     """Thin owner of an edb200_flux_t: the host-side mirror of the reference's
     FluxModel adapter (src/dit_models/diffusion_model.hpp) over the C ABI."""
@@ -223,6 +277,11 @@ class FluxModel:
             a = np.ascontiguousarray(arr)
             check(lib().edb200_flux_set_tensor(self.handle, name.encode(), t, a.ctypes.data_as(c_vp), a.nbytes, 0,
                                                current_stream()))
+
+    def set_comm(self, comm):
+        """Sequence-parallel execution over `comm` (None = single GPU); call before prepare."""
+        self._comm = comm  # keep the communicator alive as long as the model uses it
+        check(lib().edb200_flux_set_comm(self.handle, comm.handle if comm is not None else None))
 
     def init_random(self, seed=0, std=0.02):
         check(lib().edb200_flux_init_random(self.handle, seed, std, current_stream()))

@@ -249,6 +249,50 @@ EDB200_API edb200_status_t edb200_sage_attention(const void* q_f16, const void* 
 EDB200_API edb200_status_t edb200_sage_key_means_static(const void* k_f16, int hn, int64_t l, int d_head,
                                                         float* mean_out, void* stream);
 
+/* --------------------------------------- sequence-parallel (Ulysses) exchange
+ * One process per GPU.  Every rank owns n_tokens / world consecutive tokens of the
+ * [text ; image] sequence for the per-token work and heads / world heads for
+ * attention.  Replaces the reference's SP pack / split / gather callbacks
+ * (src/parallel/sp_parallel.cpp:99-469,793-831) and NCCL all-to-all
+ * (src/parallel/nccl_process_group.cpp:394-459). */
+typedef struct edb200_comm edb200_comm_t;
+/* Token slice of `rank`: t_loc tokens, of which the first n_txt_local are text
+ * rows; img_first = index of its first image token among the image tokens.
+ * Pure host arithmetic (no device needed). */
+EDB200_API edb200_status_t edb200_sp_shard(int64_t n_tokens, int64_t n_txt, int rank, int world, int64_t* t_loc,
+                                           int64_t* n_txt_local, int64_t* img_first);
+/* Message list of the heads exchange [heads, t_loc, row] -> [heads/world, T, row]:
+ * message i goes to and comes from peer[i], `bytes[i]` bytes from send_off[i] of the
+ * send buffer and to recv_off[i] of the receive buffer.  Returns the number of
+ * messages (call with peer == NULL to size the arrays), -1 on a bad argument.
+ * Pure host arithmetic; the NCCL path below executes exactly this list. */
+EDB200_API int edb200_sp_heads_plan(int rank, int world, int heads, int64_t t_loc, int64_t row_bytes, int* peer,
+                                    int64_t* send_off, int64_t* recv_off, int64_t* bytes, int cap);
+/* NCCL communicator over the ranks of one node (libnccl.so.2 is resolved from the
+ * running process at first use).  Rank 0 makes the 128-byte id, the host program
+ * distributes it (e.g. torch.distributed broadcast), every rank calls create. */
+EDB200_API edb200_status_t edb200_comm_unique_id(void* id128);
+EDB200_API edb200_status_t edb200_comm_create(const void* id128, int rank, int world, edb200_comm_t** out);
+EDB200_API void edb200_comm_destroy(edb200_comm_t* c);
+EDB200_API int edb200_comm_rank(const edb200_comm_t* c);
+EDB200_API int edb200_comm_world(const edb200_comm_t* c);
+/* Heads exchange of n_tensors buffers (Q, K, V) in one NCCL group; no pack or
+ * unpack kernel: every message is contiguous on both sides. */
+EDB200_API edb200_status_t edb200_sp_all_to_all_heads(edb200_comm_t* c, const void* const* send, void* const* recv,
+                                                      int n_tensors, int heads, int64_t t_loc, int64_t row_bytes,
+                                                      void* stream);
+/* Tokens exchange of the attention output: send [T, chunk] (this rank's heads, all
+ * tokens) -> out [t_loc, world * chunk] with row pitch ld_out_bytes (all heads,
+ * this rank's tokens), through `staging` (world * t_loc * chunk bytes). */
+EDB200_API edb200_status_t edb200_sp_all_to_all_tokens(edb200_comm_t* c, const void* send, void* staging, void* out,
+                                                       int64_t t_loc, int64_t chunk_bytes, int64_t ld_out_bytes,
+                                                       void* stream);
+/* All-gather of row blocks of unequal length: rank p contributes row_count[p] rows
+ * that land at row row_first[p] of every rank's `recv`. */
+EDB200_API edb200_status_t edb200_sp_all_gather_rows(edb200_comm_t* c, const void* send, void* recv,
+                                                     const int64_t* row_first, const int64_t* row_count,
+                                                     int64_t row_bytes, void* stream);
+
 /* ------------------------------------------------- FLUX.1 denoise-step model
  * A whole-step replacement at the reference's model seam
  * DiffusionModel::compute(n_threads, DiffusionParams) -> sd::Tensor<float>
@@ -311,6 +355,12 @@ EDB200_API edb200_status_t edb200_flux_step(edb200_flux_t* m, const float* laten
 EDB200_API edb200_status_t edb200_flux_compute_host(edb200_flux_t* m, const float* latent, int latent_h, int latent_w,
                                                     float timestep, const float* context, int n_txt, const float* y,
                                                     float guidance, float* out, void* stream);
+
+/* Sequence-parallel execution of the step (FLUX forward_sp, src/dit_models/models/flux.hpp:4529-5156):
+ * call before edb200_flux_prepare; NULL returns to single-GPU execution.  Every
+ * rank passes the full inputs and receives the full output latent; n_tokens and
+ * num_heads must divide by the communicator size.  The communicator is borrowed. */
+EDB200_API edb200_status_t edb200_flux_set_comm(edb200_flux_t* m, edb200_comm_t* comm);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,82 @@
+"""Sequence-parallel FLUX step on 2 (and 4) GPUs against the single-GPU step of the same
+model: one process per GPU, NCCL exchange inside the library.  Skipped on a 1-GPU box."""
+import os
+import socket
+
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, lib_dir, attention, lat_hw, n_txt, ret):
+    import importlib.util
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)   # carries the NCCL id only
+    spec = importlib.util.spec_from_file_location("edb200", os.path.join(lib_dir, "edb200.py"))
+    edb = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(edb)
+    dev = torch.device("cuda", rank)
+    model = edb.FluxModel(hidden_size=512, num_heads=4, depth=2, depth_single_blocks=2, mlp_hidden=1024,
+                          in_channels=64, context_in_dim=64, vec_in_dim=32, axes_dim=(16, 56, 56),
+                          attention=attention, sage_smooth_q=True)
+    model.init_random(seed=7, std=0.05)
+    g = torch.Generator(device="cpu").manual_seed(11)
+    latent = torch.randn(16, lat_hw, lat_hw, generator=g).to(dev)
+    ctx = torch.randn(n_txt, 64, generator=g).to(dev)
+    y = torch.randn(32, generator=g).to(dev)
+    ref = torch.empty_like(latent)
+    model.prepare(lat_hw, lat_hw, n_txt)
+    model.step(latent, 0.5, ctx, y, 3.5, ref)
+    torch.cuda.synchronize()
+    comm = edb.Comm()
+    model.set_comm(comm)
+    model.prepare(lat_hw, lat_hw, n_txt)
+    out = torch.empty_like(latent)
+    for _ in range(2):   # twice: the exchange buffers are reused
+        out.fill_(float("nan"))
+        model.step(latent, 0.5, ctx, y, 3.5, out)
+        torch.cuda.synchronize()
+    a, b = out.cpu().numpy(), ref.cpu().numpy()
+    err = float(np.linalg.norm(a - b) / np.linalg.norm(b))
+    ret[rank] = (bool(np.isfinite(a).all()), err)
+    dist.barrier()
+    model.set_comm(None)
+    comm.close()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("attention", ["f16", "sage"])
+def test_flux_step_sequence_parallel_matches_single_gpu(edb, cuda, world, attention):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    lib_dir = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "edge-dit.cpp_b200")
+    port = _free_port()
+    att = edb.ATTN_SAGE_INT8 if attention == "sage" else edb.ATTN_F16
+    # 24 x 24 latent -> 144 image tokens + 16 text tokens = 160: rank 0 owns text and image rows
+    procs = [ctx.Process(target=_worker, args=(r, world, port, lib_dir, att, 24, 16, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+        assert p.exitcode == 0
+    for r in range(world):
+        finite, err = ret[r]
+        assert finite
+        # same arithmetic per output element on every rank count; only the tile shapes differ
+        assert err <= 1e-5, (r, err)
