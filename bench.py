@@ -329,6 +329,8 @@ def run_ours(args):
 
     if args.kernel_only:
         cpu_ms, cores, sample = None, 0, "skipped (--kernel-only)"
+    elif world > 1:
+        cpu_ms, cores, sample = None, 0, "reported at N=1 only"
     else:
         cpu_ms, cores, sample = cpu_sample(args.workload, args.cpu_budget)
     h2d = h_lat.nbytes + h_ctx.nbytes + h_y.nbytes

@@ -61,6 +61,10 @@ struct Params {
     const float* bias;     // [HN, bias_stride] f32 per key (smooth-Q) or NULL
     int q_scale_stride, k_scale_stride, bias_stride;
     int* err;
+    // Sequence-parallel output (t_loc > 0): query row r belongs to rank r / t_loc and is
+    // stored into that rank's buffer (peer-mapped) at row r % t_loc; `out` is unused.
+    void* out_peer[8];
+    int t_loc;
 };
 
 template <int D, bool SAGE>
@@ -525,7 +529,12 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             const float inv_l = 1.0f / (sum0 + sum1);
             const bool row_ok = q_row < P.Lq;
             char* obase = static_cast<char*>(P.out);
-            const long long ocol = (long long)q_row * P.ld_out + (long long)hn * D;
+            long long orow = q_row;
+            if (P.t_loc > 0 && row_ok) {
+                obase = static_cast<char*>(P.out_peer[q_row / P.t_loc]);
+                orow = q_row % P.t_loc;
+            }
+            const long long ocol = orow * P.ld_out + (long long)hn * D;
 #pragma unroll
             for (int c = 0; c < D / 32; ++c) {
                 __syncwarp();
@@ -612,9 +621,34 @@ using namespace edb;
 
 extern "C" {
 
+// Fills the peer-output part of the kernel parameters: the column block of this rank's heads
+// inside every rank's [t_loc, ld_out] buffer.
+static edb200_status_t set_peer_out(attn::Params& P, const edb200_sp_peers_t* dst, int hn, int d_head, int out_dtype) {
+    if (dst == nullptr) return EDB200_OK;
+    if (dst->world <= 0 || dst->world > 8 || dst->rank < 0 || dst->rank >= dst->world || dst->t_loc <= 0 ||
+        dst->t_loc * dst->world < P.Lq) {
+        return fail(EDB200_ERR_INVALID, "attention: bad peer description");
+    }
+    const int esz = out_dtype == EDB200_TYPE_F32 ? 4 : 2;
+    for (int r = 0; r < dst->world; ++r) {
+        if (dst->buf[0][r] == nullptr) return fail(EDB200_ERR_INVALID, "attention: null peer buffer");
+        P.out_peer[r] = static_cast<char*>(dst->buf[0][r]) + (int64_t)dst->rank * hn * d_head * esz;
+    }
+    P.t_loc = static_cast<int>(dst->t_loc);
+    P.out = P.out_peer[dst->rank];
+    return EDB200_OK;
+}
+
 edb200_status_t edb200_attention_f16(const void* q, const void* k, const void* v, int hn, int64_t lq, int64_t lk,
                                      int d_head, float scale, void* out, int out_dtype, int64_t ld_out,
                                      void* stream) {
+    return edb200_attention_f16_sp(q, k, v, hn, lq, lk, d_head, scale, out, out_dtype, ld_out, nullptr, stream);
+}
+
+edb200_status_t edb200_attention_f16_sp(const void* q, const void* k, const void* v, int hn, int64_t lq, int64_t lk,
+                                        int d_head, float scale, void* out, int out_dtype, int64_t ld_out,
+                                        const edb200_sp_peers_t* dst, void* stream) {
+    if (dst != nullptr && out == nullptr) out = dst->buf[0][dst->rank < 8 && dst->rank >= 0 ? dst->rank : 0];
     if (q == nullptr || k == nullptr || v == nullptr || out == nullptr || hn <= 0 || lq <= 0 || lk <= 0) {
         return fail(EDB200_ERR_INVALID, "attention_f16: null or empty argument");
     }
@@ -638,6 +672,7 @@ edb200_status_t edb200_attention_f16(const void* q, const void* k, const void* v
     P.HN = hn;
     P.scale_log2 = scale * 1.4426950408889634f;
     P.err = err;
+    EDB_TRY(set_peer_out(P, dst, hn, d_head, out_dtype));
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (d_head == 128) return attn::launch<128, false>(q, k, v, P, s);
     return attn::launch<64, false>(q, k, v, P, s);
@@ -648,6 +683,16 @@ edb200_status_t edb200_attention_sage_int8(const void* q_i8, const void* k_i8, c
                                            int k_scale_stride, const float* bias, int bias_stride, int hn, int64_t l,
                                            int d_head, float scale, void* out, int out_dtype, int64_t ld_out,
                                            void* stream) {
+    return edb200_attention_sage_int8_sp(q_i8, k_i8, v_f16, q_scale, q_scale_stride, k_scale, k_scale_stride, bias,
+                                         bias_stride, hn, l, d_head, scale, out, out_dtype, ld_out, nullptr, stream);
+}
+
+edb200_status_t edb200_attention_sage_int8_sp(const void* q_i8, const void* k_i8, const void* v_f16,
+                                              const float* q_scale, int q_scale_stride, const float* k_scale,
+                                              int k_scale_stride, const float* bias, int bias_stride, int hn,
+                                              int64_t l, int d_head, float scale, void* out, int out_dtype,
+                                              int64_t ld_out, const edb200_sp_peers_t* dst, void* stream) {
+    if (dst != nullptr && out == nullptr) out = dst->buf[0][dst->rank < 8 && dst->rank >= 0 ? dst->rank : 0];
     if (q_i8 == nullptr || k_i8 == nullptr || v_f16 == nullptr || q_scale == nullptr || k_scale == nullptr ||
         out == nullptr || hn <= 0 || l <= 0) {
         return fail(EDB200_ERR_INVALID, "attention_sage_int8: null or empty argument");
@@ -679,6 +724,7 @@ edb200_status_t edb200_attention_sage_int8(const void* q_i8, const void* k_i8, c
     P.k_scale_stride = k_scale_stride;
     P.bias_stride = bias_stride;
     P.err = err;
+    EDB_TRY(set_peer_out(P, dst, hn, d_head, out_dtype));
     return attn::launch<128, true>(q_i8, k_i8, v_f16, P, static_cast<cudaStream_t>(stream));
 }
 

@@ -17,6 +17,12 @@
 //
 // NCCL is resolved at run time from the already loaded libnccl.so.2 (the process
 // that owns the ranks brings it); the library itself links cudart only.
+//
+// The faster path needs no exchange kernels at all: once every rank's workspace is
+// mapped into its peers (CUDA IPC over NVLink, edb200_comm_map_peers) the producing
+// kernels store each result row straight into the owning rank's buffer (Q/K/V pack
+// kernel, attention epilogue) and a one-kernel flag barrier (edb200_sp_barrier)
+// orders producers and consumers across GPUs.
 #include "edb200_internal.h"
 
 #include <dlfcn.h>
@@ -87,6 +93,37 @@ __global__ void interleave_heads_kernel(const uint4* __restrict__ staging, uint4
     }
 }
 
+// Cross-GPU barrier of one kernel per rank: thread p tells rank p "rank `rank` has reached
+// epoch e" (a release store at system scope into p's flag word for this rank, after a
+// system fence that orders the stream's earlier peer stores), then waits until rank p has
+// told this rank the same.  The wait is bounded; on expiry the error word is set.
+struct BarrierArgs {
+    uint32_t* flags[8];   // flags[p] = rank p's flag array (8 words, 64 bytes apart)
+    int rank, world;
+    uint32_t epoch;
+    int* err;
+};
+
+__global__ void sp_barrier_kernel(const BarrierArgs a) {
+    const int p = threadIdx.x;
+    if (p >= a.world) return;
+    __threadfence_system();
+    uint32_t* theirs = a.flags[p] + a.rank * 16;
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(theirs), "r"(a.epoch) : "memory");
+    const uint32_t* mine = a.flags[a.rank] + p * 16;
+    const long long t0 = clock64();
+    uint32_t v;
+    for (;;) {
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+        if (static_cast<int32_t>(v - a.epoch) >= 0) break;
+        if (clock64() - t0 > 4000000000ll) {   // about two seconds of SM clocks
+            atomicExch(a.err, 3);
+            break;
+        }
+        __nanosleep(100);
+    }
+}
+
 }  // namespace
 }  // namespace edb
 
@@ -95,6 +132,11 @@ using namespace edb;
 struct edb200_comm {
     nccl_comm_t comm = nullptr;
     int rank = 0, world = 1;
+    // peer mappings of one device allocation per rank (same size and layout on every rank)
+    char* base[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    bool mapped = false;
+    int64_t flags_off = 0;   // 8 flag words of 64 bytes each inside the allocation
+    uint32_t epoch = 0;
 };
 
 extern "C" {
@@ -173,9 +215,125 @@ edb200_status_t edb200_comm_create(const void* id128, int rank, int world, edb20
 
 void edb200_comm_destroy(edb200_comm_t* c) {
     if (c == nullptr) return;
+    edb200_comm_unmap_peers(c);
     NcclApi* a = nccl_api();
     if (a != nullptr && c->comm != nullptr) a->CommDestroy(c->comm);
     delete c;
+}
+
+// Host-side rendezvous over NCCL: every rank sends `bytes` to every rank.
+static edb200_status_t nccl_all_gather_small(edb200_comm_t* c, const void* dev_send, void* dev_recv, size_t bytes,
+                                             cudaStream_t s) {
+    NcclApi* a = nccl_api();
+    EDB_TRY(check_nccl(a->GroupStart(), "ncclGroupStart"));
+    int rc = 0;
+    for (int p = 0; p < c->world && rc == 0; ++p) {
+        rc = a->Send(dev_send, bytes, kNcclUint8, p, c->comm, s);
+        if (rc == 0) rc = a->Recv(static_cast<char*>(dev_recv) + (size_t)p * bytes, bytes, kNcclUint8, p, c->comm, s);
+    }
+    const int rc_end = a->GroupEnd();
+    EDB_TRY(check_nccl(rc, "ncclSend/ncclRecv"));
+    EDB_TRY(check_nccl(rc_end, "ncclGroupEnd"));
+    return check_cuda(cudaStreamSynchronize(s), "comm rendezvous");
+}
+
+edb200_status_t edb200_comm_unmap_peers(edb200_comm_t* c) {
+    if (c == nullptr) return fail(EDB200_ERR_INVALID, "comm_unmap_peers: null communicator");
+    if (!c->mapped) return EDB200_OK;
+    // nobody may still be writing into a mapping that is about to go away
+    cudaDeviceSynchronize();
+    char* dev = nullptr;
+    if (cudaMalloc(reinterpret_cast<void**>(&dev), 16 * 9) == cudaSuccess) {
+        nccl_all_gather_small(c, dev, dev + 16, 16, nullptr);
+        cudaFree(dev);
+    }
+    for (int p = 0; p < c->world; ++p) {
+        if (p != c->rank && c->base[p] != nullptr) cudaIpcCloseMemHandle(c->base[p]);
+        c->base[p] = nullptr;
+    }
+    c->mapped = false;
+    return EDB200_OK;
+}
+
+edb200_status_t edb200_comm_map_peers(edb200_comm_t* c, void* base, int64_t bytes, int64_t flags_off, void* stream) {
+    if (c == nullptr || base == nullptr || bytes <= 0 || flags_off < 0 || flags_off + 8 * 64 > bytes || flags_off % 64) {
+        return fail(EDB200_ERR_INVALID, "comm_map_peers: bad argument");
+    }
+    if (c->world > 8) return fail(EDB200_ERR_UNSUPPORTED, "comm_map_peers: at most 8 ranks");
+    if (nccl_api() == nullptr) return fail(EDB200_ERR_UNSUPPORTED, "comm_map_peers: libnccl.so.2 not available");
+    EDB_TRY(edb200_comm_unmap_peers(c));
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    cudaIpcMemHandle_t mine;
+    cudaError_t e = cudaIpcGetMemHandle(&mine, base);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(EDB200_ERR_UNSUPPORTED, "comm_map_peers: cudaIpcGetMemHandle: %s", cudaGetErrorString(e));
+    }
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    char* dev = nullptr;
+    e = cudaMalloc(reinterpret_cast<void**>(&dev), 64 * 9);
+    if (e != cudaSuccess) return check_cuda(e, "comm_map_peers scratch");
+    cudaMemcpyAsync(dev, &mine, 64, cudaMemcpyHostToDevice, s);
+    cudaMemsetAsync(static_cast<char*>(base) + flags_off, 0, 8 * 64, s);
+    edb200_status_t st = nccl_all_gather_small(c, dev, dev + 64, 64, s);
+    cudaIpcMemHandle_t all[8];
+    if (st == EDB200_OK) st = check_cuda(cudaMemcpy(all, dev + 64, (size_t)c->world * 64, cudaMemcpyDeviceToHost), "handles");
+    cudaFree(dev);
+    if (st != EDB200_OK) return st;
+    for (int p = 0; p < c->world; ++p) {
+        if (p == c->rank) {
+            c->base[p] = static_cast<char*>(base);
+            continue;
+        }
+        void* ptr = nullptr;
+        e = cudaIpcOpenMemHandle(&ptr, all[p], cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            for (int q = 0; q < p; ++q) {
+                if (q != c->rank && c->base[q]) cudaIpcCloseMemHandle(c->base[q]);
+                c->base[q] = nullptr;
+            }
+            return fail(EDB200_ERR_UNSUPPORTED, "comm_map_peers: cudaIpcOpenMemHandle(rank %d): %s", p,
+                        cudaGetErrorString(e));
+        }
+        c->base[p] = static_cast<char*>(ptr);
+    }
+    c->mapped = true;
+    c->flags_off = flags_off;
+    c->epoch = 0;
+    // every rank has cleared its flags (the rendezvous above came after the memset in stream order
+    // only for this rank): meet once more before anybody signals
+    char* dev2 = nullptr;
+    e = cudaMalloc(reinterpret_cast<void**>(&dev2), 16 * 9);
+    if (e != cudaSuccess) return check_cuda(e, "comm_map_peers scratch");
+    st = nccl_all_gather_small(c, dev2, dev2 + 16, 16, s);
+    cudaFree(dev2);
+    return st;
+}
+
+int edb200_comm_peers_mapped(const edb200_comm_t* c) { return c != nullptr && c->mapped ? 1 : 0; }
+
+void* edb200_comm_peer_ptr(const edb200_comm_t* c, int peer, const void* local_ptr) {
+    if (c == nullptr || !c->mapped || peer < 0 || peer >= c->world || local_ptr == nullptr) return nullptr;
+    return c->base[peer] + (static_cast<const char*>(local_ptr) - c->base[c->rank]);
+}
+
+edb200_status_t edb200_sp_barrier(edb200_comm_t* c, void* stream) {
+    if (c == nullptr || !c->mapped) return fail(EDB200_ERR_INVALID, "sp_barrier: peers are not mapped");
+    int* err = device_error_word();
+    if (err == nullptr) return fail(EDB200_ERR_CUDA, "sp_barrier: no CUDA device");
+    BarrierArgs a;
+    memset(&a, 0, sizeof(a));
+    for (int p = 0; p < c->world; ++p) a.flags[p] = reinterpret_cast<uint32_t*>(c->base[p] + c->flags_off);
+    a.rank = c->rank;
+    a.world = c->world;
+    a.epoch = ++c->epoch;
+    a.err = err;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    ProfScope prof(s, PROF_OTHER, 0.0, 0.0);
+    sp_barrier_kernel<<<1, 32, 0, s>>>(a);
+    count_launch();
+    return check_cuda(cudaGetLastError(), "sp_barrier launch");
 }
 
 int edb200_comm_rank(const edb200_comm_t* c) { return c ? c->rank : 0; }

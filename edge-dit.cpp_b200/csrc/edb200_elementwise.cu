@@ -5,6 +5,8 @@
 // shuffles.
 #include "edb200_internal.h"
 
+#include <cstring>
+
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -175,13 +177,24 @@ __global__ void fused_residual_gate_kernel(const float4* __restrict__ res, const
 // then y0 = x0*pe00 + x1*pe10, y1 = x0*pe01 + x1*pe11 with the stored
 // [[cos,-sin],[sin,cos]] table (src/core/backend/ggml/ed_ggml_rope_ext.hpp:105-184),
 // written head-major [head][token][d] like the reference's fused RoPE op.
+// Sequence-parallel destination: head h of the local tokens belongs to rank h / hp and is
+// stored straight into that rank's [hp, L_total, D] buffers (peer-mapped pointers), at the
+// global token position.  hp == 0: plain local output.
+struct PackPeers {
+    void* q[8];
+    void* k[8];
+    void* v[8];
+    int hp;
+    long long global_first;   // global position of this rank's token 0
+};
+
 template <int D>
 __global__ void __launch_bounds__(256)
 qk_norm_rope_pack_kernel(const void* __restrict__ qkv, int in_dtype, int64_t ld, int64_t q_off, int64_t k_off,
                          int64_t v_off, int64_t T, int n_heads, const float* __restrict__ q_w,
                          const float* __restrict__ k_w, float eps, const float* __restrict__ pe, int64_t tok_off,
                          int64_t L_total, void* __restrict__ q_out, void* __restrict__ k_out,
-                         void* __restrict__ v_out, int out_dtype) {
+                         void* __restrict__ v_out, int out_dtype, const PackPeers peers) {
     constexpr int E = D / 32;  // elements per lane: 4 or 2
     const int64_t gw = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
@@ -189,7 +202,14 @@ qk_norm_rope_pack_kernel(const void* __restrict__ qkv, int in_dtype, int64_t ld,
     const int64_t t = gw / n_heads;
     const int h = static_cast<int>(gw % n_heads);
     const int64_t row = t * ld;
-    const int64_t out_base = ((int64_t)h * L_total + tok_off + t) * D + lane * E;
+    int64_t out_base = ((int64_t)h * L_total + tok_off + t) * D + lane * E;
+    if (peers.hp > 0) {
+        const int dst_rank = h / peers.hp;
+        out_base = ((int64_t)(h % peers.hp) * L_total + peers.global_first + tok_off + t) * D + lane * E;
+        q_out = peers.q[dst_rank];
+        k_out = peers.k[dst_rank];
+        v_out = peers.v[dst_rank];
+    }
 
     float pe_v[E * 2];  // per pair: pe00, pe10, pe01, pe11  (ggml [row,col] = flat row + 2*col)
     if (pe != nullptr) {
@@ -318,18 +338,19 @@ edb200_status_t edb200_fused_residual_gate(const float* residual, const float* x
     return check_cuda(cudaGetLastError(), "fused_residual_gate launch");
 }
 
-edb200_status_t edb200_qk_norm_rope_pack(const void* qkv, int in_dtype, int64_t ld, int64_t q_off, int64_t k_off,
-                                         int64_t v_off, int64_t tokens, int n_heads, int d_head, const float* q_weight,
-                                         const float* k_weight, float eps, const float* pe, int64_t tok_off,
-                                         int64_t l_total, void* q_out, void* k_out, void* v_out, int out_dtype,
-                                         void* stream) {
+static edb200_status_t qk_pack_launch(const void* qkv, int in_dtype, int64_t ld, int64_t q_off, int64_t k_off,
+                                      int64_t v_off, int64_t tokens, int n_heads, int d_head, const float* q_weight,
+                                      const float* k_weight, float eps, const float* pe, int64_t tok_off,
+                                      int64_t l_total, void* q_out, void* k_out, void* v_out, int out_dtype,
+                                      const PackPeers& peers, void* stream) {
     if (qkv == nullptr || q_out == nullptr || k_out == nullptr || v_out == nullptr || tokens <= 0 || n_heads <= 0) {
         return fail(EDB200_ERR_INVALID, "qk_norm_rope_pack: null or empty argument");
     }
     if ((d_head != 64 && d_head != 128) || !dtype_ok(in_dtype) || !dtype_ok(out_dtype)) {
         return fail(EDB200_ERR_UNSUPPORTED, "qk_norm_rope_pack: d_head must be 64 or 128");
     }
-    if (ld % 4 || q_off % 4 || k_off % 4 || v_off % 4 || tok_off < 0 || tok_off + tokens > l_total) {
+    if (ld % 4 || q_off % 4 || k_off % 4 || v_off % 4 || tok_off < 0 ||
+        peers.global_first + tok_off + tokens > l_total) {
         return fail(EDB200_ERR_INVALID, "qk_norm_rope_pack: offsets must be multiples of 4 and fit l_total");
     }
     const int64_t warps = tokens * n_heads;
@@ -341,14 +362,53 @@ edb200_status_t edb200_qk_norm_rope_pack(const void* qkv, int in_dtype, int64_t 
     if (d_head == 128) {
         qk_norm_rope_pack_kernel<128><<<grid, 256, 0, s>>>(qkv, in_dtype, ld, q_off, k_off, v_off, tokens, n_heads,
                                                            q_weight, k_weight, eps, pe, tok_off, l_total, q_out,
-                                                           k_out, v_out, out_dtype);
+                                                           k_out, v_out, out_dtype, peers);
     } else {
         qk_norm_rope_pack_kernel<64><<<grid, 256, 0, s>>>(qkv, in_dtype, ld, q_off, k_off, v_off, tokens, n_heads,
                                                           q_weight, k_weight, eps, pe, tok_off, l_total, q_out, k_out,
-                                                          v_out, out_dtype);
+                                                          v_out, out_dtype, peers);
     }
     count_launch();
     return check_cuda(cudaGetLastError(), "qk_norm_rope_pack launch");
+}
+
+edb200_status_t edb200_qk_norm_rope_pack(const void* qkv, int in_dtype, int64_t ld, int64_t q_off, int64_t k_off,
+                                         int64_t v_off, int64_t tokens, int n_heads, int d_head, const float* q_weight,
+                                         const float* k_weight, float eps, const float* pe, int64_t tok_off,
+                                         int64_t l_total, void* q_out, void* k_out, void* v_out, int out_dtype,
+                                         void* stream) {
+    PackPeers none;
+    memset(&none, 0, sizeof(none));
+    return qk_pack_launch(qkv, in_dtype, ld, q_off, k_off, v_off, tokens, n_heads, d_head, q_weight, k_weight, eps, pe,
+                          tok_off, l_total, q_out, k_out, v_out, out_dtype, none, stream);
+}
+
+edb200_status_t edb200_qk_norm_rope_pack_sp(const void* qkv, int in_dtype, int64_t ld, int64_t q_off, int64_t k_off,
+                                            int64_t v_off, int64_t tokens, int n_heads, int d_head,
+                                            const float* q_weight, const float* k_weight, float eps, const float* pe,
+                                            int64_t tok_off, int64_t l_total, const edb200_sp_peers_t* dst,
+                                            int out_dtype, void* stream) {
+    if (dst == nullptr || dst->world <= 0 || dst->world > 8 || dst->rank < 0 || dst->rank >= dst->world ||
+        n_heads % dst->world || dst->t_loc <= 0) {
+        return fail(EDB200_ERR_INVALID, "qk_norm_rope_pack_sp: bad peer description");
+    }
+    PackPeers pp;
+    memset(&pp, 0, sizeof(pp));
+    for (int r = 0; r < dst->world; ++r) {
+        pp.q[r] = dst->buf[0][r];
+        pp.k[r] = dst->buf[1][r];
+        pp.v[r] = dst->buf[2][r];
+        if (pp.q[r] == nullptr || pp.k[r] == nullptr || pp.v[r] == nullptr) {
+            return fail(EDB200_ERR_INVALID, "qk_norm_rope_pack_sp: null peer buffer");
+        }
+    }
+    pp.hp = n_heads / dst->world;
+    pp.global_first = (long long)dst->rank * dst->t_loc;
+    // the position table is addressed by tok_off + t of the local slice: shift it to the global rows
+    const float* pe_g = pe ? pe + pp.global_first * (d_head / 2) * 4 : nullptr;
+    return qk_pack_launch(qkv, in_dtype, ld, q_off, k_off, v_off, tokens, n_heads, d_head, q_weight, k_weight, eps,
+                          pe_g, tok_off, l_total, pp.q[dst->rank], pp.k[dst->rank], pp.v[dst->rank], out_dtype, pp,
+                          stream);
 }
 
 edb200_status_t edb200_cast(const void* x, int in_dtype, void* y, int out_dtype, int64_t n, void* stream) {

@@ -19,6 +19,7 @@
 
 #include <cuda_fp16.h>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <vector>
 
@@ -44,6 +45,9 @@ struct edb200_flux {
     int64_t t_loc = 0, txt_l = 0, img_l = 0, img_first = 0;
     void *QL = nullptr, *KL = nullptr, *VL = nullptr, *AOUT = nullptr, *STG = nullptr;
     float* TOK_LOC = nullptr;
+    // peer-memory exchange: producers store into the owning rank's buffers, flag barriers order them
+    bool p2p = false;
+    edb200_sp_peers_t qkv_peers, cat_peers;
     float* tap = nullptr;
     // host staging for compute_host
     float* pinned = nullptr;
@@ -178,6 +182,22 @@ edb200_status_t attention(edb200_flux* m, int64_t T, void* out, int64_t ld_out, 
     const int d = c.hidden_size / c.num_heads;
     const int heads = c.num_heads / m->world;
     const float scale = 1.0f / std::sqrt(static_cast<float>(d));
+    if (m->p2p) {
+        // Q/K/V rows were stored into their owners by the pack kernels; wait until every rank's are in,
+        // let the attention epilogue store each output row into its owner's `out` rows, and meet
+        // again before those rows are read.  The second barrier also tells the peers that this
+        // rank has finished reading its Q/K/V, so the next block's pack kernels may overwrite them.
+        EDB_TRY(edb200_sp_barrier(m->comm, s));
+        if (c.attention == EDB200_ATTN_SAGE_INT8) {
+            EDB_TRY(edb200_sage_attention_sp(m->Q, m->K, m->V, heads, T, d, scale,
+                                             (c.sage_smooth_q ? EDB200_SAGE_SMOOTH_Q : 0) | EDB200_SAGE_FAST_MEANS,
+                                             m->SAGE, m->sage_bytes, nullptr, EDB200_TYPE_F16, ld_out, &m->cat_peers, s));
+        } else {
+            EDB_TRY(edb200_attention_f16_sp(m->Q, m->K, m->V, heads, T, T, d, scale, nullptr, EDB200_TYPE_F16, ld_out,
+                                            &m->cat_peers, s));
+        }
+        return edb200_sp_barrier(m->comm, s);
+    }
     void* att_out = out;
     int64_t att_ld = ld_out;
     if (m->world > 1) {
@@ -223,6 +243,10 @@ edb200_status_t qk_pack(edb200_flux* m, const __half* qkv, int64_t rows, int64_t
     const int64_t H = c.hidden_size;
     const int d = static_cast<int>(H / c.num_heads);
     const bool sp = m->world > 1;
+    if (m->p2p) {
+        return edb200_qk_norm_rope_pack_sp(qkv, EDB200_TYPE_F16, 3 * H, 0, H, 2 * H, rows, c.num_heads, d, qs, ks, 1e-6f,
+                                           m->PE, local_first, m->t_loc * m->world, &m->qkv_peers, EDB200_TYPE_F16, s);
+    }
     // the position table is indexed by the global row: shift it by this rank's first token
     const float* pe = m->PE + (int64_t)m->rank * m->t_loc * (d / 2) * 4;
     return edb200_qk_norm_rope_pack(qkv, EDB200_TYPE_F16, 3 * H, 0, H, 2 * H, rows, c.num_heads, d, qs, ks, 1e-6f, pe,
@@ -341,6 +365,9 @@ edb200_status_t edb200_flux_prepare(edb200_flux_t* m, int latent_h, int latent_w
              al((int64_t)n_txt * c.context_in_dim * 4) + al(c.vec_in_dim * 4) + al(sage) + 4096;
     if (m->world > 1) total += 5 * al(t_loc * H * 2) + al(n_img * c.in_channels * 4);
     cudaStreamSynchronize(s);
+    if (m->comm != nullptr) EDB_TRY(edb200_comm_unmap_peers(m->comm));   // collective; the old workspace goes away
+    m->p2p = false;
+    if (m->world > 1) total += 1024;
     EDB_TRY(m->ws.reserve(total));
     Workspace& w = m->ws;
     m->X = w.take_n<float>(T * H);
@@ -377,6 +404,32 @@ edb200_status_t edb200_flux_prepare(edb200_flux_t* m, int latent_h, int latent_w
         m->TOK_LOC = w.take_n<float>(n_img * c.in_channels);
         if (m->TOK_LOC == nullptr) return fail(EDB200_ERR_NOMEM, "flux_prepare: workspace accounting error");
     }
+    if (m->world > 1) {
+        void* flags = w.take(8 * 64);
+        if (flags == nullptr) return fail(EDB200_ERR_NOMEM, "flux_prepare: workspace accounting error");
+        const char* how = getenv("EDB200_SP_EXCHANGE");   // "nccl" keeps the library exchanges (comparison runs)
+        const bool want_p2p = how == nullptr || strcmp(how, "nccl") != 0;
+        // every rank takes the same decision: the mapping call is collective
+        edb200_status_t st = want_p2p ? edb200_comm_map_peers(m->comm, w.base(), w.capacity(),
+                                                              static_cast<char*>(flags) - static_cast<char*>(w.base()), s)
+                                      : EDB200_ERR_UNSUPPORTED;
+        if (st == EDB200_OK) {
+            m->p2p = true;
+            memset(&m->qkv_peers, 0, sizeof(m->qkv_peers));
+            memset(&m->cat_peers, 0, sizeof(m->cat_peers));
+            m->qkv_peers.world = m->cat_peers.world = m->world;
+            m->qkv_peers.rank = m->cat_peers.rank = m->rank;
+            m->qkv_peers.t_loc = m->cat_peers.t_loc = t_loc;
+            for (int r = 0; r < m->world; ++r) {
+                m->qkv_peers.buf[0][r] = edb200_comm_peer_ptr(m->comm, r, m->Q);
+                m->qkv_peers.buf[1][r] = edb200_comm_peer_ptr(m->comm, r, m->K);
+                m->qkv_peers.buf[2][r] = edb200_comm_peer_ptr(m->comm, r, m->V);
+                m->cat_peers.buf[0][r] = edb200_comm_peer_ptr(m->comm, r, m->CAT);
+            }
+        } else if (st != EDB200_ERR_UNSUPPORTED) {
+            return st;
+        }
+    }
     m->t_loc = t_loc;
     m->txt_l = txt_l;
     m->img_l = t_loc - txt_l;
@@ -410,10 +463,12 @@ edb200_status_t edb200_flux_prepare(edb200_flux_t* m, int latent_h, int latent_w
 
 edb200_status_t edb200_flux_set_comm(edb200_flux_t* m, edb200_comm_t* comm) {
     if (m == nullptr) return fail(EDB200_ERR_INVALID, "flux_set_comm: null model");
+    if (m->comm != nullptr && m->comm != comm) edb200_comm_unmap_peers(m->comm);   // collective
     m->comm = comm;
     m->rank = comm ? edb200_comm_rank(comm) : 0;
     m->world = comm ? edb200_comm_world(comm) : 1;
     m->lat_h = m->lat_w = m->n_txt = 0;   // the workspace must be prepared again
+    m->p2p = false;
     return EDB200_OK;
 }
 

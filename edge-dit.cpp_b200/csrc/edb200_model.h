@@ -61,6 +61,7 @@ public:
     T* take_n(int64_t n) { return static_cast<T*>(take(n * (int64_t)sizeof(T))); }
     int64_t capacity() const { return cap_; }
     int64_t used() const { return used_; }
+    void* base() const { return base_; }
 
 private:
     char* base_ = nullptr;

@@ -277,11 +277,6 @@ static edb200_status_t key_means_static(const __half* k, int hn, int l, float* p
 
 using namespace edb;
 
-extern "C" edb200_status_t edb200_attention_sage_int8(const void* q_i8, const void* k_i8, const void* v_f16,
-                                                      const float* q_scale, int q_scale_stride,
-                                                      const float* k_scale, int k_scale_stride, const float* bias,
-                                                      int bias_stride, int hn, int64_t l, int d_head, float scale,
-                                                      void* out, int out_dtype, int64_t ld_out, void* stream);
 
 extern "C" {
 
@@ -334,17 +329,27 @@ edb200_status_t edb200_sage_quantize_qk(const void* q_f16, const void* k_f16, in
 edb200_status_t edb200_sage_attention(const void* q_f16, const void* k_f16, const void* v_f16, int hn, int64_t l,
                                       int d_head, float scale, int smooth_q, void* scratch, int64_t scratch_bytes,
                                       void* out, int out_dtype, int64_t ld_out, void* stream) {
-    if (v_f16 == nullptr || out == nullptr) return fail(EDB200_ERR_INVALID, "sage_attention: null argument");
+    return edb200_sage_attention_sp(q_f16, k_f16, v_f16, hn, l, d_head, scale, smooth_q, scratch, scratch_bytes, out,
+                                    out_dtype, ld_out, nullptr, stream);
+}
+
+edb200_status_t edb200_sage_attention_sp(const void* q_f16, const void* k_f16, const void* v_f16, int hn, int64_t l,
+                                         int d_head, float scale, int smooth_q, void* scratch, int64_t scratch_bytes,
+                                         void* out, int out_dtype, int64_t ld_out, const edb200_sp_peers_t* dst,
+                                         void* stream) {
+    if (v_f16 == nullptr || (out == nullptr && dst == nullptr)) {
+        return fail(EDB200_ERR_INVALID, "sage_attention: null argument");
+    }
     if (d_head != 128) return fail(EDB200_ERR_UNSUPPORTED, "sage_attention: d_head must be 128");
     edb200_status_t st = edb200_sage_quantize_qk(q_f16, k_f16, hn, l, d_head, smooth_q, scratch, scratch_bytes, stream);
     if (st != EDB200_OK) return st;
     const sage::Layout lo = sage::make_layout(hn, l, d_head);
     char* sc = static_cast<char*>(scratch);
-    return edb200_attention_sage_int8(sc + lo.q8, sc + lo.k8, v_f16, reinterpret_cast<const float*>(sc + lo.q_scale),
-                                      lo.q_scale_stride, reinterpret_cast<const float*>(sc + lo.k_scale),
-                                      lo.k_scale_stride,
-                                      (smooth_q & 1) ? reinterpret_cast<const float*>(sc + lo.bias) : nullptr,
-                                      lo.bias_stride, hn, l, d_head, scale, out, out_dtype, ld_out, stream);
+    return edb200_attention_sage_int8_sp(sc + lo.q8, sc + lo.k8, v_f16, reinterpret_cast<const float*>(sc + lo.q_scale),
+                                         lo.q_scale_stride, reinterpret_cast<const float*>(sc + lo.k_scale),
+                                         lo.k_scale_stride,
+                                         (smooth_q & 1) ? reinterpret_cast<const float*>(sc + lo.bias) : nullptr,
+                                         lo.bias_stride, hn, l, d_head, scale, out, out_dtype, ld_out, dst, stream);
 }
 
 edb200_status_t edb200_sage_key_means_static(const void* k_f16, int hn, int64_t l, int d_head, float* mean_out,

@@ -97,6 +97,19 @@ _SIGS = {
                                              c_vp]),
     "edb200_sp_all_to_all_tokens": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_vp]),
     "edb200_sp_all_gather_rows": (C.c_int, [c_vp, c_vp, c_vp, C.POINTER(c_i64), C.POINTER(c_i64), c_i64, c_vp]),
+    "edb200_comm_map_peers": (C.c_int, [c_vp, c_vp, c_i64, c_i64, c_vp]),
+    "edb200_comm_unmap_peers": (C.c_int, [c_vp]),
+    "edb200_comm_peers_mapped": (C.c_int, [c_vp]),
+    "edb200_comm_peer_ptr": (c_vp, [c_vp, C.c_int, c_vp]),
+    "edb200_sp_barrier": (C.c_int, [c_vp, c_vp]),
+    "edb200_qk_norm_rope_pack_sp": (C.c_int, [c_vp, C.c_int, c_i64, c_i64, c_i64, c_i64, c_i64, C.c_int, C.c_int, c_vp,
+                                              c_vp, C.c_float, c_vp, c_i64, c_i64, c_vp, C.c_int, c_vp]),
+    "edb200_attention_f16_sp": (C.c_int, [c_vp, c_vp, c_vp, C.c_int, c_i64, c_i64, C.c_int, C.c_float, c_vp, C.c_int,
+                                          c_i64, c_vp, c_vp]),
+    "edb200_attention_sage_int8_sp": (C.c_int, [c_vp, c_vp, c_vp, c_vp, C.c_int, c_vp, C.c_int, c_vp, C.c_int, C.c_int,
+                                                c_i64, C.c_int, C.c_float, c_vp, C.c_int, c_i64, c_vp, c_vp]),
+    "edb200_sage_attention_sp": (C.c_int, [c_vp, c_vp, c_vp, C.c_int, c_i64, C.c_int, C.c_float, C.c_int, c_vp, c_i64,
+                                           c_vp, C.c_int, c_i64, c_vp, c_vp]),
     "edb200_flux_set_comm": (C.c_int, [c_vp, c_vp]),
     "edb200_flux_create": (C.c_int, [C.POINTER(FluxConfig), C.POINTER(c_vp)]),
     "edb200_flux_destroy": (None, [c_vp]),

@@ -49,6 +49,16 @@ enum {
 
 enum { EDB200_ACT_NONE = 0, EDB200_ACT_GELU_TANH = 1, EDB200_ACT_SILU = 2 };
 
+/* Buffers of every rank of the group as this GPU addresses them (peer mappings over
+ * NVLink, see edb200_comm_map_peers): buf[i][r] = buffer i of rank r.  Kernels that
+ * take this description store their results straight into the owning rank's memory,
+ * so the exchange costs no extra pass over the data. */
+typedef struct {
+    int world, rank;
+    int64_t t_loc;        /* tokens per rank */
+    void* buf[3][8];
+} edb200_sp_peers_t;
+
 /* Message of the calling thread's last failed call ("" if none).  Stands in for
  * ed_get_last_error (include/edge-dit.h:333, src/edge_dit.cpp:347-353). */
 EDB200_API const char* edb200_last_error(void);
@@ -186,6 +196,17 @@ EDB200_API edb200_status_t edb200_qk_norm_rope_pack(const void* qkv, int in_dtyp
                                          const float* k_weight, float eps, const float* pe, int64_t tok_off,
                                          int64_t l_total, void* q_out, void* k_out, void* v_out, int out_dtype,
                                          void* stream);
+/* The same with the heads exchange of sequence parallelism fused in: head h of the
+ * local tokens is written into rank h / (n_heads / world)'s
+ * [n_heads / world, l_total, d_head] q, k, v buffers (dst->buf[0..2]) at global token
+ * position rank * t_loc + tok_off + t; `pe` is the table of the whole sequence.
+ * Replaces the SP pack callbacks plus the seq->head all-to-all
+ * (src/parallel/sp_parallel.cpp:99-469, src/parallel/nccl_process_group.cpp:394-459). */
+EDB200_API edb200_status_t edb200_qk_norm_rope_pack_sp(const void* qkv, int in_dtype, int64_t ld, int64_t q_off,
+                                                       int64_t k_off, int64_t v_off, int64_t tokens, int n_heads,
+                                                       int d_head, const float* q_weight, const float* k_weight,
+                                                       float eps, const float* pe, int64_t tok_off, int64_t l_total,
+                                                       const edb200_sp_peers_t* dst, int out_dtype, void* stream);
 
 /* Elementwise dtype conversion (f32/f16/bf16), n a multiple of 4
  * (ggml_cast call sites, e.g. src/dit_models/models/flux.hpp:101-111). */
@@ -276,6 +297,25 @@ EDB200_API edb200_status_t edb200_comm_create(const void* id128, int rank, int w
 EDB200_API void edb200_comm_destroy(edb200_comm_t* c);
 EDB200_API int edb200_comm_rank(const edb200_comm_t* c);
 EDB200_API int edb200_comm_world(const edb200_comm_t* c);
+/* Peer memory.  Every rank passes ONE device allocation of the same size and layout
+ * (`base`, from cudaMalloc); afterwards edb200_comm_peer_ptr translates an address
+ * inside this rank's allocation into the same place of `peer`'s allocation as
+ * addressed from this GPU (CUDA IPC mapping, plain loads and stores over NVLink).
+ * flags_off names 512 bytes inside the allocation that the barrier below owns.
+ * Collective over the communicator (it meets the other ranks); returns
+ * EDB200_ERR_UNSUPPORTED where IPC mappings are not available, and the NCCL
+ * exchanges below remain usable.  unmap is collective too and must come before the
+ * allocation is freed. */
+EDB200_API edb200_status_t edb200_comm_map_peers(edb200_comm_t* c, void* base, int64_t bytes, int64_t flags_off,
+                                                 void* stream);
+EDB200_API edb200_status_t edb200_comm_unmap_peers(edb200_comm_t* c);
+EDB200_API int edb200_comm_peers_mapped(const edb200_comm_t* c);
+EDB200_API void* edb200_comm_peer_ptr(const edb200_comm_t* c, int peer, const void* local_ptr);
+/* Barrier across the ranks' streams, one small kernel per rank: everything this rank
+ * enqueued before it (including its stores into peer memory) is visible to every
+ * rank's work enqueued after it.  The device-side wait gives up after about two
+ * seconds and reports EDB200_ERR_TIMEOUT at the next status poll. */
+EDB200_API edb200_status_t edb200_sp_barrier(edb200_comm_t* c, void* stream);
 /* Heads exchange of n_tensors buffers (Q, K, V) in one NCCL group; no pack or
  * unpack kernel: every message is contiguous on both sides. */
 EDB200_API edb200_status_t edb200_sp_all_to_all_heads(edb200_comm_t* c, const void* const* send, void* const* recv,
@@ -292,6 +332,25 @@ EDB200_API edb200_status_t edb200_sp_all_to_all_tokens(edb200_comm_t* c, const v
 EDB200_API edb200_status_t edb200_sp_all_gather_rows(edb200_comm_t* c, const void* send, void* recv,
                                                      const int64_t* row_first, const int64_t* row_count,
                                                      int64_t row_bytes, void* stream);
+
+/* Attention with the tokens exchange of sequence parallelism fused in: this rank
+ * computes `hn` heads for all l tokens and stores query row r into rank r / t_loc's
+ * buffer dst->buf[0][..] (row r % t_loc, columns (rank * hn + head) * d_head .., row
+ * pitch ld_out).  `out` may be NULL.  Replaces the head->seq all-to-all and its
+ * pack / recv-prep kernels (src/core/backend/ggml/cuda/ed_cuda_sp_flux.cu:443-1628). */
+EDB200_API edb200_status_t edb200_attention_f16_sp(const void* q, const void* k, const void* v, int hn, int64_t lq,
+                                                   int64_t lk, int d_head, float scale, void* out, int out_dtype,
+                                                   int64_t ld_out, const edb200_sp_peers_t* dst, void* stream);
+EDB200_API edb200_status_t edb200_attention_sage_int8_sp(const void* q_i8, const void* k_i8, const void* v_f16,
+                                                         const float* q_scale, int q_scale_stride,
+                                                         const float* k_scale, int k_scale_stride, const float* bias,
+                                                         int bias_stride, int hn, int64_t l, int d_head, float scale,
+                                                         void* out, int out_dtype, int64_t ld_out,
+                                                         const edb200_sp_peers_t* dst, void* stream);
+EDB200_API edb200_status_t edb200_sage_attention_sp(const void* q_f16, const void* k_f16, const void* v_f16, int hn,
+                                                    int64_t l, int d_head, float scale, int smooth_q, void* scratch,
+                                                    int64_t scratch_bytes, void* out, int out_dtype, int64_t ld_out,
+                                                    const edb200_sp_peers_t* dst, void* stream);
 
 /* ------------------------------------------------- FLUX.1 denoise-step model
  * A whole-step replacement at the reference's model seam

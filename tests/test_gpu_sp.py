@@ -1,5 +1,5 @@
 """Sequence-parallel FLUX step on 2 (and 4) GPUs against the single-GPU step of the same
-model: one process per GPU, NCCL exchange inside the library.  Skipped on a 1-GPU box."""
+model: one process per GPU, both exchange paths of the library.  Skipped on a 1-GPU box."""
 import os
 import socket
 
@@ -17,8 +17,9 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, lib_dir, attention, lat_hw, n_txt, ret):
+def _worker(rank, world, port, lib_dir, attention, lat_hw, n_txt, exchange, ret):
     import importlib.util
+    os.environ["EDB200_SP_EXCHANGE"] = exchange
     import torch.distributed as dist
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
@@ -58,8 +59,10 @@ def _worker(rank, world, port, lib_dir, attention, lat_hw, n_txt, ret):
 
 
 @pytest.mark.parametrize("world", [2, 4])
-@pytest.mark.parametrize("attention", ["f16", "sage"])
-def test_flux_step_sequence_parallel_matches_single_gpu(edb, cuda, world, attention):
+@pytest.mark.parametrize("attention,exchange", [("f16", "peer"), ("sage", "peer"), ("sage", "nccl")])
+def test_flux_step_sequence_parallel_matches_single_gpu(edb, cuda, world, attention, exchange):
+    """exchange = "peer": producers store into the owning rank's memory (CUDA IPC mappings) and a
+    flag barrier orders them; "nccl": grouped ncclSend / ncclRecv plus one interleave kernel."""
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
@@ -69,7 +72,7 @@ def test_flux_step_sequence_parallel_matches_single_gpu(edb, cuda, world, attent
     port = _free_port()
     att = edb.ATTN_SAGE_INT8 if attention == "sage" else edb.ATTN_F16
     # 24 x 24 latent -> 144 image tokens + 16 text tokens = 160: rank 0 owns text and image rows
-    procs = [ctx.Process(target=_worker, args=(r, world, port, lib_dir, att, 24, 16, ret)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, lib_dir, att, 24, 16, exchange, ret)) for r in range(world)]
     for p in procs:
         p.start()
     for p in procs:
