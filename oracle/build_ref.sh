@@ -1,0 +1,16 @@
+#!/bin/sh
+# Compiles the reference's header-only CPU callbacks, from where they lie in the reference
+# tree, against ref_shim/ggml.h into oracle/_ref/libedref_cpu.so.  Test infrastructure.
+# Usage: sh oracle/build_ref.sh [reference root, default /root/reference]
+set -e
+HERE="$(cd "$(dirname "$0")" && pwd)"
+REF="${1:-/root/reference}"
+SRC="$REF/src/core/backend/ggml"
+if [ ! -f "$SRC/ed_ggml_modulation_ext.hpp" ]; then
+    echo "build_ref.sh: reference tree not found at $REF (nothing built)" >&2
+    exit 0
+fi
+mkdir -p "$HERE/_ref"
+g++ -O2 -std=c++17 -fPIC -shared -ffp-contract=off -I "$HERE/ref_shim" -I "$SRC" \
+    "$HERE/ref_driver.cpp" -o "$HERE/_ref/libedref_cpu.so"
+echo "$HERE/_ref/libedref_cpu.so"

@@ -12,7 +12,7 @@ the reference ships no golden vectors for them.  What *is* pinned:
     (tests/test_oracle_codecs.py);
   * modulate / residual-gate / RoPE / rms-norm-mul(f16): bit-exact against the
     reference's own CPU custom-op callbacks compiled from the reference tree
-    (oracle/build_ref.sh -> oracle/_ref/libedref.so, fixtures in tests/golden/).
+    (oracle/build_ref.sh -> oracle/_ref/libedref_cpu.so, fixtures in tests/golden/).
 
 Each function cites the reference file:line it follows (paths are relative to
 the reference project root).
