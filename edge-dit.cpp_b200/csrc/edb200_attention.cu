@@ -65,6 +65,7 @@ struct Params {
     // stored into that rank's buffer (peer-mapped) at row r % t_loc; `out` is unused.
     void* out_peer[8];
     int t_loc;
+    int one;   // always 1: an operand the compiler cannot fold (see magic_i2f_biased)
 };
 
 template <int D, bool SAGE>
@@ -122,24 +123,34 @@ __device__ __forceinline__ void mul2(float& d0, float& d1, float a0, float a1, f
 constexpr int kMagicInt = 0x4B400000;
 constexpr float kMagicFloat = 12582912.0f;
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
+// s32 dot product -> f32 (valid for |s| < 2^22): as_float(s + 0x4B400000) = 12582912 + s
+// exactly.  The add is written as a multiply-add by a run-time 1 so that it issues on the
+// FMA pipe, which has twice the integer-add pipe's rate and is the less loaded one here.
+__device__ __forceinline__ float magic_i2f_biased(uint32_t s, int one) {
+    int r;
+    asm("mad.lo.s32 %0, %1, %2, %3;" : "=r"(r) : "r"(static_cast<int>(s)), "r"(one), "r"(kMagicInt));
+    return __int_as_float(r);
+}
+
 // Half a score row (64 columns, raw tensor-memory words) -> maximum of the scaled
-// scores.  `valid` = columns of this half that are real keys (>= 64: all).
+// scores.  MASKED: only the first `valid` columns are real keys.
 // With a smooth-Q bias the words are replaced by the f32 scores
 // v = s * (q_scale * k_scale) + bias (softmax scale not yet applied: `cq` is c0 / sl2),
-// so that the second pass only needs one multiply-add per score.
-template <bool SAGE>
+// so that the second sweep only needs one multiply-add per score.
+template <bool SAGE, bool MASKED>
 __device__ __forceinline__ float half_row_max(uint32_t (&rr)[64], float c0, float cq, const float4* bias, float sl2,
-                                              int valid) {
+                                              int valid, int one) {
     if (SAGE && bias == nullptr) {
         int mi[4] = {INT_MIN, INT_MIN, INT_MIN, INT_MIN};
-        if (valid >= 64) {
 #pragma unroll
-            for (int i = 0; i < 64; ++i) mi[i & 3] = max(mi[i & 3], static_cast<int>(rr[i]));
-        } else {
-#pragma unroll
-            for (int i = 0; i < 64; ++i) {
-                if (i < valid) mi[i & 3] = max(mi[i & 3], static_cast<int>(rr[i]));
-            }
+        for (int i = 0; i < 64; ++i) {
+            if (!MASKED || i < valid) mi[i & 3] = max(mi[i & 3], static_cast<int>(rr[i]));
         }
         const int m = max(max(mi[0], mi[1]), max(mi[2], mi[3]));
         return m == INT_MIN ? -INFINITY : static_cast<float>(m) * c0;   // c0 > 0
@@ -149,10 +160,10 @@ __device__ __forceinline__ float half_row_max(uint32_t (&rr)[64], float c0, floa
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
             const float4 b = bias[i];   // shared memory, same address in every lane
-            float f0 = __int_as_float(static_cast<int>(rr[4 * i + 0]) + kMagicInt);
-            float f1 = __int_as_float(static_cast<int>(rr[4 * i + 1]) + kMagicInt);
-            float f2 = __int_as_float(static_cast<int>(rr[4 * i + 2]) + kMagicInt);
-            float f3 = __int_as_float(static_cast<int>(rr[4 * i + 3]) + kMagicInt);
+            float f0 = magic_i2f_biased(rr[4 * i + 0], one);
+            float f1 = magic_i2f_biased(rr[4 * i + 1], one);
+            float f2 = magic_i2f_biased(rr[4 * i + 2], one);
+            float f3 = magic_i2f_biased(rr[4 * i + 3], one);
             add2(f0, f1, f0, f1, -kMagicFloat, -kMagicFloat);
             add2(f2, f3, f2, f3, -kMagicFloat, -kMagicFloat);
             fma2(f0, f1, f0, f1, cq, cq, b.x, b.y);
@@ -161,30 +172,28 @@ __device__ __forceinline__ float half_row_max(uint32_t (&rr)[64], float c0, floa
             rr[4 * i + 1] = __float_as_uint(f1);
             rr[4 * i + 2] = __float_as_uint(f2);
             rr[4 * i + 3] = __float_as_uint(f3);
-            if (valid >= 64) {
-                mx[0] = fmaxf(mx[0], f0);
-                mx[1] = fmaxf(mx[1], f1);
-                mx[2] = fmaxf(mx[2], f2);
-                mx[3] = fmaxf(mx[3], f3);
-            } else {
-                if (4 * i + 0 < valid) mx[0] = fmaxf(mx[0], f0);
-                if (4 * i + 1 < valid) mx[1] = fmaxf(mx[1], f1);
-                if (4 * i + 2 < valid) mx[2] = fmaxf(mx[2], f2);
-                if (4 * i + 3 < valid) mx[3] = fmaxf(mx[3], f3);
+            if (MASKED) {
+                if (4 * i + 0 >= valid) f0 = -INFINITY;
+                if (4 * i + 1 >= valid) f1 = -INFINITY;
+                if (4 * i + 2 >= valid) f2 = -INFINITY;
+                if (4 * i + 3 >= valid) f3 = -INFINITY;
             }
+            mx[i & 1] = max3(mx[i & 1], f0, f1);
+            mx[2 + (i & 1)] = max3(mx[2 + (i & 1)], f2, f3);
         }
         return fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * sl2;   // sl2 > 0
-    }
-    if (valid >= 64) {
-#pragma unroll
-        for (int i = 0; i < 64; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(rr[i]));
     } else {
 #pragma unroll
-        for (int i = 0; i < 64; ++i) {
-            if (i < valid) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(rr[i]));
+        for (int i = 0; i < 32; ++i) {
+            float f0 = __uint_as_float(rr[2 * i]), f1 = __uint_as_float(rr[2 * i + 1]);
+            if (MASKED) {
+                if (2 * i + 0 >= valid) f0 = -INFINITY;
+                if (2 * i + 1 >= valid) f1 = -INFINITY;
+            }
+            mx[i & 3] = max3(mx[i & 3], f0, f1);
         }
+        return fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * c0;   // c0 > 0
     }
-    return fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * c0;   // c0 > 0
 }
 
 // exp2 of two non-positive-ish arguments (<= 8 by the lazy-rescale rule) on the FMA
@@ -212,14 +221,14 @@ constexpr int kPolyEvery = 4;   // one score pair in kPolyEvery takes the polyno
 // otherwise f32 scores.  MASKED: columns >= valid are padding and get P = 0.
 template <bool RAW_INT, bool MASKED>
 __device__ __forceinline__ void half_row_exp(const uint32_t (&rr)[64], uint32_t (&p2)[32], float c0, float m, int valid,
-                                             float& sum0, float& sum1) {
+                                             float& sum0, float& sum1, int one) {
     const float negm = -m;
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
         float e0, e1;
         if (RAW_INT) {
-            float f0 = __int_as_float(static_cast<int>(rr[2 * i + 0]) + kMagicInt);
-            float f1 = __int_as_float(static_cast<int>(rr[2 * i + 1]) + kMagicInt);
+            float f0 = magic_i2f_biased(rr[2 * i + 0], one);
+            float f1 = magic_i2f_biased(rr[2 * i + 1], one);
             add2(f0, f1, f0, f1, -kMagicFloat, -kMagicFloat);
             fma2(e0, e1, f0, f1, c0, c0, negm, negm);
         } else {
@@ -461,7 +470,8 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             const float4* bias_h =
                 biased ? reinterpret_cast<const float4*>(smem + C::OFF_BIAS + (j % BIAS_STAGES) * (BKV * 4)) + 16 * hb
                        : nullptr;
-            const float mx = half_row_max<SAGE>(rr, c0, cq, bias_h, P.scale_log2, valid);
+            const float mx = valid >= HK ? half_row_max<SAGE, false>(rr, c0, cq, bias_h, P.scale_log2, valid, P.one)
+                                         : half_row_max<SAGE, true>(rr, c0, cq, bias_h, P.scale_log2, valid, P.one);
             // lazy rescale: keep exponentiating against the old maximum until it is stale by > 2^8
             float alpha = 1.0f;
             const bool grow = mx > m_used + kRescaleThreshold;
@@ -495,15 +505,15 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             const float ce = biased ? P.scale_log2 : c0;
             if (valid >= HK) {   // uniform; only the last key block can be ragged
                 if (SAGE && !biased) {
-                    half_row_exp<true, false>(rr, p2, ce, m_used, valid, sum0, sum1);
+                    half_row_exp<true, false>(rr, p2, ce, m_used, valid, sum0, sum1, P.one);
                 } else {
-                    half_row_exp<false, false>(rr, p2, ce, m_used, valid, sum0, sum1);
+                    half_row_exp<false, false>(rr, p2, ce, m_used, valid, sum0, sum1, P.one);
                 }
             } else {
                 if (SAGE && !biased) {
-                    half_row_exp<true, true>(rr, p2, ce, m_used, valid, sum0, sum1);
+                    half_row_exp<true, true>(rr, p2, ce, m_used, valid, sum0, sum1, P.one);
                 } else {
-                    half_row_exp<false, true>(rr, p2, ce, m_used, valid, sum0, sum1);
+                    half_row_exp<false, true>(rr, p2, ce, m_used, valid, sum0, sum1, P.one);
                 }
             }
             if (g + 1 < n_half) {
@@ -664,6 +674,7 @@ edb200_status_t edb200_attention_f16_sp(const void* q, const void* k, const void
     if (err == nullptr) return fail(EDB200_ERR_CUDA, "attention_f16: no CUDA device");
     attn::Params P;
     memset(&P, 0, sizeof(P));
+    P.one = 1;
     P.out = out;
     P.ld_out = ld_out;
     P.out_dtype = out_dtype;
@@ -711,6 +722,7 @@ edb200_status_t edb200_attention_sage_int8_sp(const void* q_i8, const void* k_i8
     if (err == nullptr) return fail(EDB200_ERR_CUDA, "attention_sage_int8: no CUDA device");
     attn::Params P;
     memset(&P, 0, sizeof(P));
+    P.one = 1;
     P.out = out;
     P.ld_out = ld_out;
     P.out_dtype = out_dtype;

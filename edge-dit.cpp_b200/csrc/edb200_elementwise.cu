@@ -186,6 +186,12 @@ struct PackPeers {
     void* v[8];
     int hp;
     long long global_first;   // global position of this rank's token 0
+    // Whole-row RMSNorm (Wan: over all heads before the head split, wan.hpp:3504-3532):
+    // rstd per token computed beforehand, weights indexed by head * D + channel.
+    const float* rstd_q;
+    const float* rstd_k;
+    int w_head_stride;        // 0: one [D] weight vector for every head, D: [heads * D]
+    int skip_mask;            // bit i set: tensor i (0 q, 1 k, 2 v) is not produced
 };
 
 template <int D>
@@ -225,6 +231,7 @@ qk_norm_rope_pack_kernel(const void* __restrict__ qkv, int in_dtype, int64_t ld,
     }
 #pragma unroll
     for (int which = 0; which < 3; ++which) {
+        if ((peers.skip_mask >> which) & 1) continue;   // uniform
         const int64_t off = row + (which == 0 ? q_off : which == 1 ? k_off : v_off) + (int64_t)h * D + lane * E;
         float v[E];
         if (E == 4) {
@@ -245,14 +252,21 @@ qk_norm_rope_pack_kernel(const void* __restrict__ qkv, int in_dtype, int64_t ld,
         void* dst = which == 0 ? q_out : which == 1 ? k_out : v_out;
         if (which < 2) {
             const float* w = which == 0 ? q_w : k_w;
+            const float* rstd = which == 0 ? peers.rstd_q : peers.rstd_k;
             if (w != nullptr) {
-                float ss = 0.0f;
+                float sc;
+                if (rstd != nullptr) {
+                    sc = __ldg(rstd + t);
+                } else {
+                    float ss = 0.0f;
 #pragma unroll
-                for (int e = 0; e < E; ++e) ss += v[e] * v[e];
-                ss = warp_sum(ss);
-                const float sc = 1.0f / sqrtf(ss / static_cast<float>(D) + eps);
+                    for (int e = 0; e < E; ++e) ss += v[e] * v[e];
+                    ss = warp_sum(ss);
+                    sc = 1.0f / sqrtf(ss / static_cast<float>(D) + eps);
+                }
+                const float* wh = w + (int64_t)h * peers.w_head_stride + lane * E;
 #pragma unroll
-                for (int e = 0; e < E; ++e) v[e] = (v[e] * sc) * __ldg(w + lane * E + e);
+                for (int e = 0; e < E; ++e) v[e] = (v[e] * sc) * __ldg(wh + e);
             }
             if (pe != nullptr) {
 #pragma unroll
@@ -343,7 +357,9 @@ static edb200_status_t qk_pack_launch(const void* qkv, int in_dtype, int64_t ld,
                                       const float* k_weight, float eps, const float* pe, int64_t tok_off,
                                       int64_t l_total, void* q_out, void* k_out, void* v_out, int out_dtype,
                                       const PackPeers& peers, void* stream) {
-    if (qkv == nullptr || q_out == nullptr || k_out == nullptr || v_out == nullptr || tokens <= 0 || n_heads <= 0) {
+    const bool need[3] = {!(peers.skip_mask & 1), !(peers.skip_mask & 2), !(peers.skip_mask & 4)};
+    if (qkv == nullptr || (need[0] && q_out == nullptr) || (need[1] && k_out == nullptr) ||
+        (need[2] && v_out == nullptr) || tokens <= 0 || n_heads <= 0) {
         return fail(EDB200_ERR_INVALID, "qk_norm_rope_pack: null or empty argument");
     }
     if ((d_head != 64 && d_head != 128) || !dtype_ok(in_dtype) || !dtype_ok(out_dtype)) {
@@ -409,6 +425,71 @@ edb200_status_t edb200_qk_norm_rope_pack_sp(const void* qkv, int in_dtype, int64
     return qk_pack_launch(qkv, in_dtype, ld, q_off, k_off, v_off, tokens, n_heads, d_head, q_weight, k_weight, eps,
                           pe_g, tok_off, l_total, pp.q[dst->rank], pp.k[dst->rank], pp.v[dst->rank], out_dtype, pp,
                           stream);
+}
+
+// rstd[row] = 1/sqrt(mean(x[row, :]^2) + eps); one warp per row, 16-byte loads.
+__global__ void __launch_bounds__(256)
+row_rstd_kernel(const void* __restrict__ x, int dtype, int64_t ld, int64_t rows, int cols, float eps,
+                float* __restrict__ out) {
+    const int64_t row = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    float ss = 0.0f;
+    for (int c = lane * 4; c < cols; c += 128) {
+        const float4 f = load_vec4(x, dtype, row * ld + c);
+        ss += (f.x * f.x + f.y * f.y) + (f.z * f.z + f.w * f.w);
+    }
+    ss = warp_sum(ss);
+    if (lane == 0) out[row] = 1.0f / sqrtf(ss / static_cast<float>(cols) + eps);
+}
+
+edb200_status_t edb200_row_rstd(const void* x, int dtype, int64_t ld, int64_t rows, int64_t cols, float eps, float* out,
+                                void* stream) {
+    if (x == nullptr || out == nullptr || rows <= 0 || cols <= 0 || cols % 4 || ld % 4 || !dtype_ok(dtype)) {
+        return fail(EDB200_ERR_INVALID, "row_rstd: bad argument (cols and ld multiples of 4)");
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    ProfScope prof(s, PROF_ELEMENTWISE, 0.0, (double)rows * cols * (dtype == EDB200_TYPE_F32 ? 4.0 : 2.0));
+    row_rstd_kernel<<<static_cast<unsigned>((rows * 32 + 255) / 256), 256, 0, s>>>(x, dtype, ld, rows,
+                                                                                   static_cast<int>(cols), eps, out);
+    count_launch();
+    return check_cuda(cudaGetLastError(), "row_rstd launch");
+}
+
+edb200_status_t edb200_qk_rownorm_rope_pack(const void* qkv, int in_dtype, int64_t ld, int64_t q_off, int64_t k_off,
+                                            int64_t v_off, int64_t tokens, int n_heads, int d_head,
+                                            const float* q_weight, const float* k_weight, const float* rstd_q,
+                                            const float* rstd_k, const float* pe, int64_t tok_off, int64_t l_total,
+                                            void* q_out, void* k_out, void* v_out, int out_dtype,
+                                            const edb200_sp_peers_t* dst, void* stream) {
+    PackPeers pp;
+    memset(&pp, 0, sizeof(pp));
+    pp.rstd_q = rstd_q;
+    pp.rstd_k = rstd_k;
+    pp.w_head_stride = d_head;
+    if ((q_weight != nullptr && rstd_q == nullptr) || (k_weight != nullptr && rstd_k == nullptr)) {
+        return fail(EDB200_ERR_INVALID, "qk_rownorm_rope_pack: a weight needs its row rstd");
+    }
+    const float* pe_g = pe;
+    if (dst != nullptr) {
+        if (dst->world <= 0 || dst->world > 8 || dst->rank < 0 || dst->rank >= dst->world || n_heads % dst->world ||
+            dst->t_loc <= 0) {
+            return fail(EDB200_ERR_INVALID, "qk_rownorm_rope_pack: bad peer description");
+        }
+        for (int r = 0; r < dst->world; ++r) {
+            pp.q[r] = dst->buf[0][r];
+            pp.k[r] = dst->buf[1][r];
+            pp.v[r] = dst->buf[2][r];
+        }
+        pp.hp = n_heads / dst->world;
+        pp.global_first = (long long)dst->rank * dst->t_loc;
+        pe_g = pe ? pe + pp.global_first * (d_head / 2) * 4 : nullptr;
+        q_out = pp.q[dst->rank], k_out = pp.k[dst->rank], v_out = pp.v[dst->rank];
+    } else {
+        pp.skip_mask = (q_out == nullptr ? 1 : 0) | (k_out == nullptr ? 2 : 0) | (v_out == nullptr ? 4 : 0);
+    }
+    return qk_pack_launch(qkv, in_dtype, ld, q_off, k_off, v_off, tokens, n_heads, d_head, q_weight, k_weight, 0.0f,
+                          pe_g, tok_off, l_total, q_out, k_out, v_out, out_dtype, pp, stream);
 }
 
 edb200_status_t edb200_cast(const void* x, int in_dtype, void* y, int out_dtype, int64_t n, void* stream) {

@@ -208,6 +208,25 @@ EDB200_API edb200_status_t edb200_qk_norm_rope_pack_sp(const void* qkv, int in_d
                                                        float eps, const float* pe, int64_t tok_off, int64_t l_total,
                                                        const edb200_sp_peers_t* dst, int out_dtype, void* stream);
 
+/* Whole-row RMSNorm in two parts (Wan norms q and k over all heads before the head
+ * split: WanSelfAttention::forward, src/dit_models/models/wan.hpp:3504-3532; ggml-side
+ * RMSNorm, src/core/backend/ggml/ggml_extend.hpp:8248-8282):
+ *   out[row] = 1 / sqrt(mean(x[row, 0..cols)^2) + eps)                       */
+EDB200_API edb200_status_t edb200_row_rstd(const void* x, int dtype, int64_t ld, int64_t rows, int64_t cols, float eps,
+                                           float* out, void* stream);
+/* ... and the pack that applies it: like edb200_qk_norm_rope_pack, but q and k are
+ * scaled by rstd_q / rstd_k [tokens] and by weights over the whole row
+ * [n_heads * d_head]; weight NULL = no norm, pe NULL = no RoPE, an output pointer
+ * NULL = that tensor is skipped (cross-attention packs q alone, or k and v alone).
+ * dst != NULL stores into the owning ranks as edb200_qk_norm_rope_pack_sp does. */
+EDB200_API edb200_status_t edb200_qk_rownorm_rope_pack(const void* qkv, int in_dtype, int64_t ld, int64_t q_off,
+                                                       int64_t k_off, int64_t v_off, int64_t tokens, int n_heads,
+                                                       int d_head, const float* q_weight, const float* k_weight,
+                                                       const float* rstd_q, const float* rstd_k, const float* pe,
+                                                       int64_t tok_off, int64_t l_total, void* q_out, void* k_out,
+                                                       void* v_out, int out_dtype, const edb200_sp_peers_t* dst,
+                                                       void* stream);
+
 /* Elementwise dtype conversion (f32/f16/bf16), n a multiple of 4
  * (ggml_cast call sites, e.g. src/dit_models/models/flux.hpp:101-111). */
 EDB200_API edb200_status_t edb200_cast(const void* x, int in_dtype, void* y, int out_dtype, int64_t n, void* stream);
