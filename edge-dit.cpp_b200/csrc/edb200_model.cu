@@ -263,7 +263,12 @@ edb200_status_t ParamTable::init_random(uint64_t seed, float std, cudaStream_t s
         st = edb200_fill_normal(tmp, n, name_seed(seed, p.spec.name), 0.0f, std, stream);
         if (st != EDB200_OK) break;
         const std::string& nm = p.spec.name;
-        if (nm.size() > 6 && nm.compare(nm.size() - 6, 6, ".scale") == 0) {
+        auto ends_with = [&](const char* suf) {
+            const size_t n = strlen(suf);
+            return nm.size() >= n && nm.compare(nm.size() - n, n, suf) == 0;
+        };
+        // norm weights are centred on one
+        if (ends_with(".scale") || ends_with(".norm_q.weight") || ends_with(".norm_k.weight") || ends_with("norm3.weight")) {
             add_one_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, stream>>>(tmp, n);
             count_launch();
         }

@@ -115,6 +115,7 @@ gemv_f32_kernel(const float* __restrict__ w, const float* __restrict__ bias, con
         if (lane == 0) {
             v += bias ? bias[n] : 0.0f;
             if (act == EDB200_ACT_SILU) v = v / (1.0f + __expf(-v));
+            if (act == EDB200_ACT_GELU_ERF) v = 0.5f * v * (1.0f + erff(v * 0.70710678118654752f));
             if (act == EDB200_ACT_GELU_TANH) {
                 v = 0.5f * v * (1.0f + tanhf(0.7978845608028654f * v * (1.0f + 0.044715f * v * v)));
             }
@@ -165,6 +166,7 @@ sgemm_nt_kernel(const float* __restrict__ w, const float* __restrict__ bias, con
             if (nn >= n_out) continue;
             float v = acc[i][j] + (bias ? bias[nn] : 0.0f);
             if (act == EDB200_ACT_SILU) v = v / (1.0f + __expf(-v));
+            if (act == EDB200_ACT_GELU_ERF) v = 0.5f * v * (1.0f + erff(v * 0.70710678118654752f));
             if (act == EDB200_ACT_GELU_TANH) {
                 v = 0.5f * v * (1.0f + tanhf(0.7978845608028654f * v * (1.0f + 0.044715f * v * v)));
             }

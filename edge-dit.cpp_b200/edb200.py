@@ -29,6 +29,16 @@ class Epilogue(C.Structure):
     ]
 
 
+class WanConfig(C.Structure):
+    """edb200_wan_config_t"""
+    _fields_ = [
+        ("dim", C.c_int), ("num_heads", C.c_int), ("ffn_dim", C.c_int), ("num_layers", C.c_int),
+        ("in_dim", C.c_int), ("out_dim", C.c_int), ("text_dim", C.c_int), ("freq_dim", C.c_int),
+        ("patch_size", C.c_int * 3), ("axes_dim", C.c_int * 3), ("theta", C.c_int),
+        ("wtype", C.c_int), ("attention", C.c_int), ("sage_smooth_q", C.c_int),
+    ]
+
+
 class FluxConfig(C.Structure):
     _fields_ = [
         ("hidden_size", C.c_int), ("num_heads", C.c_int), ("depth", C.c_int), ("depth_single_blocks", C.c_int),
@@ -111,6 +121,24 @@ _SIGS = {
     "edb200_sage_attention_sp": (C.c_int, [c_vp, c_vp, c_vp, C.c_int, c_i64, C.c_int, C.c_float, C.c_int, c_vp, c_i64,
                                            c_vp, C.c_int, c_i64, c_vp, c_vp]),
     "edb200_flux_set_comm": (C.c_int, [c_vp, c_vp]),
+    "edb200_row_rstd": (C.c_int, [c_vp, C.c_int, c_i64, c_i64, c_i64, C.c_float, c_vp, c_vp]),
+    "edb200_qk_rownorm_rope_pack": (C.c_int, [c_vp, C.c_int, c_i64, c_i64, c_i64, c_i64, c_i64, C.c_int, C.c_int, c_vp,
+                                              c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_vp, c_vp, c_vp, C.c_int, c_vp,
+                                              c_vp]),
+    "edb200_wan_create": (C.c_int, [C.POINTER(WanConfig), C.POINTER(c_vp)]),
+    "edb200_wan_destroy": (None, [c_vp]),
+    "edb200_wan_tensor_count": (C.c_int, [c_vp]),
+    "edb200_wan_tensor_info": (C.c_int, [c_vp, C.c_int, C.c_char_p, C.c_int, C.POINTER(C.c_int), C.POINTER(c_i64),
+                                         C.POINTER(c_i64), C.POINTER(c_i64)]),
+    "edb200_wan_set_tensor": (C.c_int, [c_vp, C.c_char_p, C.c_int, c_vp, c_i64, C.c_int, c_vp]),
+    "edb200_wan_init_random": (C.c_int, [c_vp, C.c_uint64, C.c_float, c_vp]),
+    "edb200_wan_weight_bytes": (c_i64, [c_vp]),
+    "edb200_wan_workspace_bytes": (c_i64, [c_vp]),
+    "edb200_wan_prepare": (C.c_int, [c_vp, C.c_int, C.c_int, C.c_int, C.c_int, c_vp]),
+    "edb200_wan_set_tap": (C.c_int, [c_vp, c_vp]),
+    "edb200_wan_set_comm": (C.c_int, [c_vp, c_vp]),
+    "edb200_wan_step": (C.c_int, [c_vp, c_vp, C.c_float, c_vp, c_vp, c_vp]),
+    "edb200_wan_compute_host": (C.c_int, [c_vp, c_vp, C.c_int, C.c_int, C.c_int, C.c_float, c_vp, C.c_int, c_vp, c_vp]),
     "edb200_flux_create": (C.c_int, [C.POINTER(FluxConfig), C.POINTER(c_vp)]),
     "edb200_flux_destroy": (None, [c_vp]),
     "edb200_flux_tensor_count": (C.c_int, [c_vp]),
@@ -317,6 +345,65 @@ class FluxModel:
                                              timestep, context.ctypes.data_as(c_vp), context.shape[0],
                                              y.ctypes.data_as(c_vp), guidance, out.ctypes.data_as(c_vp),
                                              current_stream()))
+        return out
+
+
+class WanModel:
+    """Thin owner of an edb200_wan_t (host-side mirror of the reference's WanModel adapter,
+    src/dit_models/diffusion_model.hpp) over the C ABI."""
+
+    def __init__(self, dim=5120, num_heads=40, ffn_dim=13824, num_layers=40, in_dim=16, out_dim=16, text_dim=4096,
+                 freq_dim=256, patch_size=(1, 2, 2), axes_dim=(44, 42, 42), theta=10000, wtype=TYPE_Q8_0,
+                 attention=ATTN_SAGE_INT8, sage_smooth_q=True):
+        cfg = WanConfig()
+        cfg.dim, cfg.num_heads, cfg.ffn_dim, cfg.num_layers = dim, num_heads, ffn_dim, num_layers
+        cfg.in_dim, cfg.out_dim, cfg.text_dim, cfg.freq_dim = in_dim, out_dim, text_dim, freq_dim
+        cfg.patch_size = (C.c_int * 3)(*patch_size)
+        cfg.axes_dim = (C.c_int * 3)(*axes_dim)
+        cfg.theta, cfg.wtype, cfg.attention, cfg.sage_smooth_q = theta, wtype, attention, int(sage_smooth_q)
+        self.cfg = cfg
+        h = c_vp()
+        check(lib().edb200_wan_create(C.byref(cfg), C.byref(h)))
+        self.handle = h
+
+    def __del__(self):
+        if getattr(self, "handle", None) and _lib is not None:
+            _lib.edb200_wan_destroy(self.handle)
+            self.handle = None
+
+    def load_numpy(self, weights: dict):
+        """weights: {name: (ggml_type, ndarray)} as produced by oracle.wan_oracle.wan_make_weights."""
+        import numpy as np
+        for name, (t, arr) in weights.items():
+            a = np.ascontiguousarray(arr)
+            check(lib().edb200_wan_set_tensor(self.handle, name.encode(), t, a.ctypes.data_as(c_vp), a.nbytes, 0,
+                                              current_stream()))
+
+    def init_random(self, seed=0, std=0.02):
+        check(lib().edb200_wan_init_random(self.handle, seed, std, current_stream()))
+
+    def set_comm(self, comm):
+        self._comm = comm
+        check(lib().edb200_wan_set_comm(self.handle, comm.handle if comm is not None else None))
+
+    def set_tap(self, tap):
+        self._tap = tap
+        check(lib().edb200_wan_set_tap(self.handle, ptr(tap)))
+
+    def prepare(self, frames, lat_h, lat_w, n_ctx):
+        check(lib().edb200_wan_prepare(self.handle, frames, lat_h, lat_w, n_ctx, current_stream()))
+
+    def step(self, latent, timestep, context, out):
+        check(lib().edb200_wan_step(self.handle, ptr(latent), timestep, ptr(context), ptr(out), current_stream()))
+
+    def compute_host(self, latent, timestep, context):
+        import numpy as np
+        latent = np.ascontiguousarray(latent, dtype=np.float32)
+        context = np.ascontiguousarray(context, dtype=np.float32)
+        out = np.empty((self.cfg.out_dim,) + latent.shape[1:], dtype=np.float32)
+        check(lib().edb200_wan_compute_host(self.handle, latent.ctypes.data_as(c_vp), latent.shape[1], latent.shape[2],
+                                            latent.shape[3], timestep, context.ctypes.data_as(c_vp), context.shape[0],
+                                            out.ctypes.data_as(c_vp), current_stream()))
         return out
 
 

@@ -47,7 +47,7 @@ enum {
     EDB200_TYPE_BF16 = 30
 };
 
-enum { EDB200_ACT_NONE = 0, EDB200_ACT_GELU_TANH = 1, EDB200_ACT_SILU = 2 };
+enum { EDB200_ACT_NONE = 0, EDB200_ACT_GELU_TANH = 1, EDB200_ACT_SILU = 2, EDB200_ACT_GELU_ERF = 3 /* dense f32 linear only */ };
 
 /* Buffers of every rank of the group as this GPU addresses them (peer mappings over
  * NVLink, see edb200_comm_map_peers): buf[i][r] = buffer i of rank r.  Kernels that
@@ -439,6 +439,54 @@ EDB200_API edb200_status_t edb200_flux_compute_host(edb200_flux_t* m, const floa
  * rank passes the full inputs and receives the full output latent; n_tokens and
  * num_heads must divide by the communicator size.  The communicator is borrowed. */
 EDB200_API edb200_status_t edb200_flux_set_comm(edb200_flux_t* m, edb200_comm_t* comm);
+
+/* -------------------------------------------------- Wan 2.1 (t2v) denoise step
+ * The same seam for WanModel / WanRunner::compute (src/dit_models/models/wan.hpp:4811-5529,
+ * graph Wan::forward :4759-4808).  Field names follow WanParams (:4382-4405). */
+typedef struct {
+    int dim;            /* 5120 */
+    int num_heads;      /* 40 (head dim 128) */
+    int ffn_dim;        /* 13824 */
+    int num_layers;     /* 40 */
+    int in_dim;         /* latent channels, 16 */
+    int out_dim;        /* 16 */
+    int text_dim;       /* 4096 */
+    int freq_dim;       /* 256 */
+    int patch_size[3];  /* (1, 2, 2) */
+    int axes_dim[3];    /* (44, 42, 42) over (t, h, w) */
+    int theta;
+    int wtype;          /* EDB200_TYPE_Q8_0 / EDB200_TYPE_Q4_K for the block linears */
+    int attention;      /* self-attention: EDB200_ATTN_F16 / EDB200_ATTN_SAGE_INT8; cross-attention is always f16 */
+    int sage_smooth_q;
+} edb200_wan_config_t;
+
+typedef struct edb200_wan edb200_wan_t;
+
+EDB200_API edb200_status_t edb200_wan_create(const edb200_wan_config_t* cfg, edb200_wan_t** out);
+EDB200_API void edb200_wan_destroy(edb200_wan_t* m);
+EDB200_API int edb200_wan_tensor_count(const edb200_wan_t* m);
+EDB200_API edb200_status_t edb200_wan_tensor_info(const edb200_wan_t* m, int index, char* name, int name_cap,
+                                                  int* ggml_type, int64_t* n_out, int64_t* k, int64_t* nbytes);
+EDB200_API edb200_status_t edb200_wan_set_tensor(edb200_wan_t* m, const char* name, int ggml_type, const void* data,
+                                                 int64_t nbytes, int on_device, void* stream);
+EDB200_API edb200_status_t edb200_wan_init_random(edb200_wan_t* m, uint64_t seed, float std, void* stream);
+EDB200_API int64_t edb200_wan_weight_bytes(const edb200_wan_t* m);
+EDB200_API int64_t edb200_wan_workspace_bytes(const edb200_wan_t* m);
+/* Latent [in_dim, frames, lat_h, lat_w] (frames, lat_h, lat_w multiples of the patch), n_ctx text tokens. */
+EDB200_API edb200_status_t edb200_wan_prepare(edb200_wan_t* m, int frames, int lat_h, int lat_w, int n_ctx,
+                                              void* stream);
+/* Optional f32 tap [num_layers, tokens (this rank's), dim]: residual stream after every block. */
+EDB200_API edb200_status_t edb200_wan_set_tap(edb200_wan_t* m, float* tap);
+/* Sequence parallel over `comm` (WanAttentionBlock::forward_sp, wan.hpp:4189-4235): before prepare. */
+EDB200_API edb200_status_t edb200_wan_set_comm(edb200_wan_t* m, edb200_comm_t* comm);
+/* One denoise step on device tensors: latent f32 [in_dim, frames, lat_h, lat_w], context f32
+ * [n_ctx, text_dim], out f32 like latent. */
+EDB200_API edb200_status_t edb200_wan_step(edb200_wan_t* m, const float* latent, float timestep, const float* context,
+                                           float* out, void* stream);
+/* The same with host tensors (DiffusionModel::compute seam); synchronises. */
+EDB200_API edb200_status_t edb200_wan_compute_host(edb200_wan_t* m, const float* latent, int frames, int lat_h,
+                                                   int lat_w, float timestep, const float* context, int n_ctx,
+                                                   float* out, void* stream);
 
 #ifdef __cplusplus
 }
