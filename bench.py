@@ -45,7 +45,65 @@ WORKLOADS = {
     "flux512_q8_0": (dict(hidden_size=3072, num_heads=24, depth=19, depth_single_blocks=38), (16, 64, 64), 512),
     "flux_tiny": (dict(hidden_size=512, num_heads=4, depth=2, depth_single_blocks=2, context_in_dim=256,
                        vec_in_dim=64), (16, 32, 32), 64),
+    # FLUX.1 2048^2 with q4_K weights (16384 + 512 tokens), the sequence-parallel configuration
+    "flux2048_q4_k": (dict(hidden_size=3072, num_heads=24, depth=19, depth_single_blocks=38, wtype=12),
+                      (16, 256, 256), 512),
+    # Wan 2.1 14B: latent [16, 21, 90, 160] -> 75,600 video tokens, 512 text tokens (name starts with "wan")
+    "wan14b_q8_0": (dict(), (16, 21, 90, 160), 512),
+    "wan_small": (dict(dim=1024, num_heads=8, ffn_dim=2048, num_layers=4, text_dim=256), (16, 5, 32, 32), 64),
 }
+
+
+class Case:
+    """One workload on this rank's GPU: the model, its device inputs and the two ways of running a step."""
+
+    def __init__(self, edb, torch, name, attention, dev):
+        import numpy as np
+        kw, lat, n_txt = WORKLOADS[name]
+        self.wan = name.startswith("wan")
+        g = torch.Generator(device=dev).manual_seed(1234)
+        self.latent = torch.randn(lat, generator=g, device=dev)
+        g.manual_seed(1235)
+        if self.wan:
+            self.model = edb.WanModel(attention=attention, **kw)
+            self.ctx = torch.randn(n_txt, self.model.cfg.text_dim, generator=g, device=dev)
+            ps = tuple(self.model.cfg.patch_size)
+            self.tokens = (lat[1] // ps[0]) * (lat[2] // ps[1]) * (lat[3] // ps[2])
+            self.attn_tokens = self.tokens
+            self.y = None
+        else:
+            self.model = edb.FluxModel(attention=attention, **kw)
+            self.ctx = torch.randn(n_txt, self.model.cfg.context_in_dim, generator=g, device=dev)
+            self.y = torch.randn(self.model.cfg.vec_in_dim, generator=g, device=dev)
+            self.tokens = (lat[1] // 2) * (lat[2] // 2) + n_txt
+        self.lat, self.n_txt = lat, n_txt
+        self.out = torch.empty_like(self.latent)
+        self.edb, self.np = edb, np
+
+    def prepare(self):
+        if self.wan:
+            self.model.prepare(self.lat[1], self.lat[2], self.lat[3], self.n_txt)
+        else:
+            self.model.prepare(self.lat[1], self.lat[2], self.n_txt)
+
+    def step(self):
+        if self.wan:
+            self.model.step(self.latent, 500.0, self.ctx, self.out)
+        else:
+            self.model.step(self.latent, 0.5, self.ctx, self.y, 3.5, self.out)
+
+    def host_inputs(self):
+        self.h = [t.cpu().numpy() for t in ((self.latent, self.ctx) if self.wan else (self.latent, self.ctx, self.y))]
+        return sum(a.nbytes for a in self.h)
+
+    def step_host(self):
+        if self.wan:
+            return self.model.compute_host(self.h[0], 500.0, self.h[1])
+        return self.model.compute_host(self.h[0], 0.5, self.h[1], self.h[2], 3.5)
+
+    def weight_bytes(self):
+        lib = self.edb.lib()
+        return lib.edb200_wan_weight_bytes(self.model.handle) if self.wan else lib.edb200_flux_weight_bytes(self.model.handle)
 
 
 def load_pkg(name):
@@ -237,9 +295,9 @@ def run_ours(args):
 
     load_pkg("build").build()
     edb = load_pkg("edb200")
-    kw, lat, n_txt = WORKLOADS[args.workload]
     attention = edb.ATTN_F16 if args.attention == "f16" else edb.ATTN_SAGE_INT8
-    model = edb.FluxModel(attention=attention, **kw)
+    case = Case(edb, torch, args.workload, attention, dev)
+    model = case.model
     model.init_random(seed=0, std=0.02)
     init_launches = int(edb.lib().edb200_launch_count())
     comm = None
@@ -248,16 +306,9 @@ def run_ours(args):
         # per-token work and 1/N of the heads for attention (NCCL exchange inside the library)
         comm = edb.Comm()
         model.set_comm(comm)
-    model.prepare(lat[1], lat[2], n_txt)
-    n_img = (lat[1] // 2) * (lat[2] // 2)
-    tokens = n_img + n_txt
-
-    g = torch.Generator(device=dev).manual_seed(1234)
-    latent = torch.randn(lat, generator=g, device=dev)
-    g.manual_seed(1235)
-    ctx = torch.randn(n_txt, model.cfg.context_in_dim, generator=g, device=dev)
-    y = torch.randn(model.cfg.vec_in_dim, generator=g, device=dev)
-    out = torch.empty_like(latent)
+    case.prepare()
+    tokens = case.tokens
+    out = case.out
 
     def barrier():
         if dist is not None:
@@ -265,7 +316,7 @@ def run_ours(args):
         torch.cuda.synchronize()
 
     for _ in range(args.warmup):
-        model.step(latent, 0.5, ctx, y, 3.5, out)
+        case.step()
     barrier()
     launches0 = edb.lib().edb200_launch_count()
     sampler = ClockSampler(visible_gpu_index(local_rank))
@@ -274,7 +325,7 @@ def run_ours(args):
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
-        model.step(latent, 0.5, ctx, y, 3.5, out)
+        case.step()
     e1.record()
     barrier()
     clocks = sampler.stop() if rank == 0 else None
@@ -283,20 +334,20 @@ def run_ours(args):
     finite = bool(torch.isfinite(out).all().item())
 
     # end to end through the host-tensor entry point
-    h_lat, h_ctx, h_y = latent.cpu().numpy(), ctx.cpu().numpy(), y.cpu().numpy()
+    h2d = case.host_inputs()
     n_e2e = 1 if args.kernel_only else args.steps
     for _ in range(0 if args.kernel_only else min(2, args.warmup)):
-        model.compute_host(h_lat, 0.5, h_ctx, h_y, 3.5)
+        case.step_host()
     barrier()
     t0 = time.perf_counter()
     for _ in range(n_e2e):
-        h_out = model.compute_host(h_lat, 0.5, h_ctx, h_y, 3.5)
+        h_out = case.step_host()
     e2e_ms = (time.perf_counter() - t0) * 1e3 / n_e2e
     barrier()
 
     # per-class device time of one extra step (CUDA events around every launch)
     edb.profile_begin()
-    model.step(latent, 0.5, ctx, y, 3.5, out)
+    case.step()
     prof = edb.profile_end()
 
     if dist is not None:
@@ -332,10 +383,12 @@ def run_ours(args):
     elif world > 1:
         cpu_ms, cores, sample = None, 0, "reported at N=1 only"
     else:
-        cpu_ms, cores, sample = cpu_sample(args.workload, args.cpu_budget)
-    h2d = h_lat.nbytes + h_ctx.nbytes + h_y.nbytes
+        if args.workload.startswith("flux") and args.workload != "flux2048_q4_k":
+            cpu_ms, cores, sample = cpu_sample(args.workload, args.cpu_budget)
+        else:
+            cpu_ms, cores, sample = None, 0, "not sampled for this workload (default workload only)"
     line = {
-        "metric": METRIC, "value": ms, "unit": "ms", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "metric": METRIC if args.workload == "flux1024_q8_0" else f"DiT ms/denoise-step ({args.workload})", "value": ms, "unit": "ms", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms, "higher_is_better": False, "scaling": "weak" if world == 1 else "strong",
         "vs_baseline": None,
         "dtype": "f16 operands / f32 accumulate (q8_0 weights dequantised to f16, INT8 QK^T)",
@@ -344,8 +397,8 @@ def run_ours(args):
         "config": {"workload": args.workload, "tokens": tokens, "attention": args.attention,
                    "parallelism": "single GPU" if world == 1 else f"ulysses sequence parallel x{world} (one step "
                    "shared by all ranks: tokens split for linears/norms, heads split for attention)",
-                   "l2": "inputs larger than L2: 12.6 GB of weights stream through every step",
-                   "weight_bytes": edb.lib().edb200_flux_weight_bytes(model.handle),
+                   "l2": "inputs larger than L2: the quantised weights (GBs) stream through every step",
+                   "weight_bytes": case.weight_bytes(),
                    "output_finite": finite, "init_launches": init_launches},
         "e2e": {"value": e2e_ms, "unit": "ms", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": h_out.nbytes},
         "gpu_launches": int(launches),

@@ -62,6 +62,7 @@ struct Problem {
     int out_dtype, act, out2_dtype, act2;
     int M, N, K;
     int m_tiles, n_tiles;
+    int chunk;   // token tiles per L2-resident activation chunk (tile order below)
 };
 
 struct Params {
@@ -79,10 +80,21 @@ __device__ __forceinline__ TileCoord tile_coord(const Params& P, int t, int wh) 
     TileCoord c;
     c.prob = (t >= P.tiles0) ? 1 : 0;
     const int tt = c.prob ? t - P.tiles0 : t;
-    const int m_tiles = c.prob ? P.p[1].m_tiles : P.p[0].m_tiles;
-    // token tile fastest: CTAs running at the same time share one weight tile row through L2.
-    c.n_tile = (tt / m_tiles) * wh;
-    c.m0 = (tt % m_tiles) * TN;
+    const Problem& pr = c.prob ? P.p[1] : P.p[0];
+    // Order: activation chunk (pr.chunk token tiles, sized to stay in L2) > weight tile row > token
+    // tile.  CTAs running at the same time share one weight tile row through L2, and all weight
+    // rows pass over a chunk before the next chunk is touched, so neither operand is re-read
+    // from DRAM more than (number of chunks) times, however many tokens there are.
+    const int per_chunk = pr.chunk * pr.n_tiles;
+    const int full = pr.m_tiles / pr.chunk;
+    int chunk_idx = tt / per_chunk, r = tt % per_chunk, width = pr.chunk;
+    if (chunk_idx >= full) {   // the last, narrower chunk
+        chunk_idx = full;
+        r = tt - full * per_chunk;
+        width = pr.m_tiles - full * pr.chunk;
+    }
+    c.n_tile = (r / width) * wh;
+    c.m0 = (chunk_idx * pr.chunk + r % width) * TN;
     return c;
 }
 
@@ -527,6 +539,14 @@ static void fill_problem(gemm::Problem& p, const edb200_qweight_t* w, int64_t m,
     p.tiles = w->tiles;
     p.m_tiles = static_cast<int>((m + gemm::TN - 1) / gemm::TN);
     p.n_tiles = static_cast<int>((w->n_tiles + wh - 1) / wh);   // CTA tiles of `wh` weight tiles
+    {
+        // about 32 MB of f16 activations per chunk: a quarter of the 126 MB L2
+        const int64_t per_tile = (int64_t)gemm::TN * w->k * 2;
+        int64_t ch = (32ll << 20) / per_tile;
+        if (ch < 4) ch = 4;
+        if (ch > p.m_tiles) ch = p.m_tiles;
+        p.chunk = static_cast<int>(ch);
+    }
 }
 
 static edb200_status_t launch_qgemm(int nprob, const edb200_qweight_t* const* ws, const void* const* xs,
