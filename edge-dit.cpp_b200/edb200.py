@@ -29,6 +29,15 @@ class Epilogue(C.Structure):
     ]
 
 
+class SD3Config(C.Structure):
+    """edb200_sd3_config_t"""
+    _fields_ = [
+        ("hidden_size", C.c_int), ("num_heads", C.c_int), ("depth", C.c_int), ("mlp_hidden", C.c_int),
+        ("in_channels", C.c_int), ("out_channels", C.c_int), ("patch_size", C.c_int), ("adm_in_channels", C.c_int),
+        ("context_size", C.c_int), ("pos_embed_max_size", C.c_int), ("wtype", C.c_int), ("attention", C.c_int),
+    ]
+
+
 class WanConfig(C.Structure):
     """edb200_wan_config_t"""
     _fields_ = [
@@ -125,6 +134,19 @@ _SIGS = {
     "edb200_qk_rownorm_rope_pack": (C.c_int, [c_vp, C.c_int, c_i64, c_i64, c_i64, c_i64, c_i64, C.c_int, C.c_int, c_vp,
                                               c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_vp, c_vp, c_vp, C.c_int, c_vp,
                                               c_vp]),
+    "edb200_sd3_create": (C.c_int, [C.POINTER(SD3Config), C.POINTER(c_vp)]),
+    "edb200_sd3_destroy": (None, [c_vp]),
+    "edb200_sd3_tensor_count": (C.c_int, [c_vp]),
+    "edb200_sd3_tensor_info": (C.c_int, [c_vp, C.c_int, C.c_char_p, C.c_int, C.POINTER(C.c_int), C.POINTER(c_i64),
+                                         C.POINTER(c_i64), C.POINTER(c_i64)]),
+    "edb200_sd3_set_tensor": (C.c_int, [c_vp, C.c_char_p, C.c_int, c_vp, c_i64, C.c_int, c_vp]),
+    "edb200_sd3_init_random": (C.c_int, [c_vp, C.c_uint64, C.c_float, c_vp]),
+    "edb200_sd3_weight_bytes": (c_i64, [c_vp]),
+    "edb200_sd3_prepare": (C.c_int, [c_vp, C.c_int, C.c_int, C.c_int, c_vp]),
+    "edb200_sd3_set_tap": (C.c_int, [c_vp, c_vp]),
+    "edb200_sd3_step": (C.c_int, [c_vp, c_vp, C.c_float, c_vp, c_vp, c_vp, c_vp]),
+    "edb200_sd3_compute_host": (C.c_int, [c_vp, c_vp, C.c_int, C.c_int, C.c_float, c_vp, C.c_int, c_vp, c_vp, c_vp]),
+    "edb200_cfg_combine": (C.c_int, [c_vp, c_vp, C.c_float, c_vp, c_i64, c_vp]),
     "edb200_wan_create": (C.c_int, [C.POINTER(WanConfig), C.POINTER(c_vp)]),
     "edb200_wan_destroy": (None, [c_vp]),
     "edb200_wan_tensor_count": (C.c_int, [c_vp]),
@@ -345,6 +367,69 @@ class FluxModel:
                                              timestep, context.ctypes.data_as(c_vp), context.shape[0],
                                              y.ctypes.data_as(c_vp), guidance, out.ctypes.data_as(c_vp),
                                              current_stream()))
+        return out
+
+
+class SD3Model:
+    """Thin owner of an edb200_sd3_t (host-side mirror of the reference's MMDiTModel adapter,
+    src/dit_models/diffusion_model.hpp) over the C ABI; one call is one batch-1 pass."""
+
+    def __init__(self, hidden_size=1536, num_heads=24, depth=24, mlp_hidden=None, in_channels=16, out_channels=16,
+                 patch_size=2, adm_in_channels=2048, context_size=4096, pos_embed_max_size=192, wtype=TYPE_Q8_0,
+                 attention=ATTN_F16):
+        cfg = SD3Config()
+        cfg.hidden_size, cfg.num_heads, cfg.depth = hidden_size, num_heads, depth
+        cfg.mlp_hidden = mlp_hidden if mlp_hidden is not None else 4 * hidden_size
+        cfg.in_channels, cfg.out_channels, cfg.patch_size = in_channels, out_channels, patch_size
+        cfg.adm_in_channels, cfg.context_size, cfg.pos_embed_max_size = adm_in_channels, context_size, pos_embed_max_size
+        cfg.wtype, cfg.attention = wtype, attention
+        self.cfg = cfg
+        h = c_vp()
+        check(lib().edb200_sd3_create(C.byref(cfg), C.byref(h)))
+        self.handle = h
+
+    def __del__(self):
+        if getattr(self, "handle", None) and _lib is not None:
+            _lib.edb200_sd3_destroy(self.handle)
+            self.handle = None
+
+    def tensor_names(self):
+        buf = C.create_string_buffer(256)
+        out = []
+        for i in range(lib().edb200_sd3_tensor_count(self.handle)):
+            check(lib().edb200_sd3_tensor_info(self.handle, i, buf, 256, None, None, None, None))
+            out.append(buf.value.decode())
+        return out
+
+    def load_numpy(self, weights: dict):
+        import numpy as np
+        for name, (t, arr) in weights.items():
+            a = np.ascontiguousarray(arr)
+            check(lib().edb200_sd3_set_tensor(self.handle, name.encode(), t, a.ctypes.data_as(c_vp), a.nbytes, 0,
+                                              current_stream()))
+
+    def init_random(self, seed=0, std=0.02):
+        check(lib().edb200_sd3_init_random(self.handle, seed, std, current_stream()))
+
+    def set_tap(self, tap):
+        self._tap = tap
+        check(lib().edb200_sd3_set_tap(self.handle, ptr(tap)))
+
+    def prepare(self, lat_h, lat_w, n_ctx):
+        check(lib().edb200_sd3_prepare(self.handle, lat_h, lat_w, n_ctx, current_stream()))
+
+    def step(self, latent, timestep, context, y, out):
+        check(lib().edb200_sd3_step(self.handle, ptr(latent), timestep, ptr(context), ptr(y), ptr(out), current_stream()))
+
+    def compute_host(self, latent, timestep, context, y):
+        import numpy as np
+        latent = np.ascontiguousarray(latent, dtype=np.float32)
+        context = np.ascontiguousarray(context, dtype=np.float32)
+        y = np.ascontiguousarray(y, dtype=np.float32)
+        out = np.empty((self.cfg.out_channels,) + latent.shape[1:], dtype=np.float32)
+        check(lib().edb200_sd3_compute_host(self.handle, latent.ctypes.data_as(c_vp), latent.shape[1], latent.shape[2],
+                                            timestep, context.ctypes.data_as(c_vp), context.shape[0],
+                                            y.ctypes.data_as(c_vp), out.ctypes.data_as(c_vp), current_stream()))
         return out
 
 

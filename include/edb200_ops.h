@@ -440,6 +440,50 @@ EDB200_API edb200_status_t edb200_flux_compute_host(edb200_flux_t* m, const floa
  * num_heads must divide by the communicator size.  The communicator is borrowed. */
 EDB200_API edb200_status_t edb200_flux_set_comm(edb200_flux_t* m, edb200_comm_t* comm);
 
+/* ------------------------------------------------ SD3-medium (MMDiT) denoise pass
+ * The same seam for MMDiTModel / MMDiTRunner::compute (src/dit_models/models/mmdit.hpp:3403-3487;
+ * members :3165-3182).  One call is one batch-1 pass; classifier-free guidance runs the
+ * conditional and the unconditional pass and combines them with edb200_cfg_combine. */
+typedef struct {
+    int hidden_size;        /* 1536 = 64 * depth */
+    int num_heads;          /* 24 (head dim 64) */
+    int depth;              /* 24 joint blocks; the last one's context side is pre_only */
+    int mlp_hidden;         /* 4 * hidden_size */
+    int in_channels;        /* latent channels, 16 */
+    int out_channels;       /* 16 */
+    int patch_size;         /* 2 */
+    int adm_in_channels;    /* pooled vector, 2048 */
+    int context_size;       /* 4096 */
+    int pos_embed_max_size; /* 192 */
+    int wtype;              /* EDB200_TYPE_Q8_0 / EDB200_TYPE_Q4_K */
+    int attention;          /* EDB200_ATTN_F16 (head dim 64 has no INT8 kernel in this build) */
+} edb200_sd3_config_t;
+
+typedef struct edb200_sd3 edb200_sd3_t;
+
+EDB200_API edb200_status_t edb200_sd3_create(const edb200_sd3_config_t* cfg, edb200_sd3_t** out);
+EDB200_API void edb200_sd3_destroy(edb200_sd3_t* m);
+EDB200_API int edb200_sd3_tensor_count(const edb200_sd3_t* m);
+EDB200_API edb200_status_t edb200_sd3_tensor_info(const edb200_sd3_t* m, int index, char* name, int name_cap,
+                                                  int* ggml_type, int64_t* n_out, int64_t* k, int64_t* nbytes);
+EDB200_API edb200_status_t edb200_sd3_set_tensor(edb200_sd3_t* m, const char* name, int ggml_type, const void* data,
+                                                 int64_t nbytes, int on_device, void* stream);
+EDB200_API edb200_status_t edb200_sd3_init_random(edb200_sd3_t* m, uint64_t seed, float std, void* stream);
+EDB200_API int64_t edb200_sd3_weight_bytes(const edb200_sd3_t* m);
+EDB200_API edb200_status_t edb200_sd3_prepare(edb200_sd3_t* m, int lat_h, int lat_w, int n_ctx, void* stream);
+/* Optional f32 tap [depth, n_ctx + image tokens, hidden]: both streams after every block. */
+EDB200_API edb200_status_t edb200_sd3_set_tap(edb200_sd3_t* m, float* tap);
+/* latent f32 [in_channels, lat_h, lat_w], context f32 [n_ctx, context_size], y f32 [adm_in_channels]. */
+EDB200_API edb200_status_t edb200_sd3_step(edb200_sd3_t* m, const float* latent, float timestep, const float* context,
+                                           const float* y, float* out, void* stream);
+EDB200_API edb200_status_t edb200_sd3_compute_host(edb200_sd3_t* m, const float* latent, int lat_h, int lat_w,
+                                                   float timestep, const float* context, int n_ctx, const float* y,
+                                                   float* out, void* stream);
+/* out = uncond + scale * (cond - uncond), f32, n a multiple of 4: the pipeline-side CFG combine
+ * (src/pipelines/sd3_pipeline.cpp:631-669, src/pipelines/flux_pipeline.cpp:1218-1258). */
+EDB200_API edb200_status_t edb200_cfg_combine(const float* uncond, const float* cond, float scale, float* out, int64_t n,
+                                              void* stream);
+
 /* -------------------------------------------------- Wan 2.1 (t2v) denoise step
  * The same seam for WanModel / WanRunner::compute (src/dit_models/models/wan.hpp:4811-5529,
  * graph Wan::forward :4759-4808).  Field names follow WanParams (:4382-4405). */

@@ -83,3 +83,62 @@ def test_flux_step_sequence_parallel_matches_single_gpu(edb, cuda, world, attent
         assert finite
         # same arithmetic per output element on every rank count; only the tile shapes differ
         assert err <= 1e-5, (r, err)
+
+
+def _wan_worker(rank, world, port, lib_dir, exchange, ret):
+    import importlib.util
+    import torch.distributed as dist
+    os.environ["EDB200_SP_EXCHANGE"] = exchange
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    spec = importlib.util.spec_from_file_location("edb200", os.path.join(lib_dir, "edb200.py"))
+    edb = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(edb)
+    dev = torch.device("cuda", rank)
+    model = edb.WanModel(dim=512, num_heads=4, ffn_dim=1024, num_layers=2, text_dim=128)
+    model.init_random(seed=9, std=0.05)
+    g = torch.Generator(device="cpu").manual_seed(12)
+    latent = torch.randn(16, 2, 16, 20, generator=g).to(dev)     # 2 * 8 * 10 = 160 video tokens
+    ctx = torch.randn(24, 128, generator=g).to(dev)
+    ref = torch.empty_like(latent)
+    model.prepare(2, 16, 20, 24)
+    model.step(latent, 500.0, ctx, ref)
+    torch.cuda.synchronize()
+    comm = edb.Comm()
+    model.set_comm(comm)
+    model.prepare(2, 16, 20, 24)
+    out = torch.empty_like(latent)
+    for _ in range(2):
+        out.fill_(float("nan"))
+        model.step(latent, 500.0, ctx, out)
+        torch.cuda.synchronize()
+    a, b = out.cpu().numpy(), ref.cpu().numpy()
+    ret[rank] = (bool(np.isfinite(a).all()), float(np.linalg.norm(a - b) / np.linalg.norm(b)))
+    dist.barrier()
+    model.set_comm(None)
+    comm.close()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("exchange", ["peer", "nccl"])
+def test_wan_step_sequence_parallel_matches_single_gpu(edb, cuda, world, exchange):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    lib_dir = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "edge-dit.cpp_b200")
+    port = _free_port()
+    procs = [ctx.Process(target=_wan_worker, args=(r, world, port, lib_dir, exchange, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+        assert p.exitcode == 0
+    for r in range(world):
+        finite, err = ret[r]
+        assert finite
+        assert err <= 1e-5, (r, err)
