@@ -46,6 +46,19 @@ def _digest() -> str:
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
+    """Builds the library unless the stamp says it is current.  Safe to call from several
+    processes at once (one rank per GPU): a file lock serialises them and the library is
+    moved into place atomically, so nobody ever loads a half-written file."""
+    import fcntl
+    with open(os.path.join(HERE, ".build.lock"), "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            return _build_locked(force, verbose)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+
+
+def _build_locked(force: bool, verbose: bool) -> str:
     dig = _digest()
     if not force and os.path.exists(OUT) and os.path.exists(STAMP):
         with open(STAMP) as fh:
@@ -74,8 +87,10 @@ def build(force: bool = False, verbose: bool = False) -> str:
         sys.stderr.write("\n".join(log))
     if failed:
         raise RuntimeError("nvcc failed; see " + os.path.join(objdir, "ptxas.log"))
-    link = [nvcc, "-shared", "-o", OUT] + objs + ["-gencode", "arch=compute_100a,code=sm_100a", "-lcudart", "-ldl"]
+    tmp = OUT + f".tmp{os.getpid()}"
+    link = [nvcc, "-shared", "-o", tmp] + objs + ["-gencode", "arch=compute_100a,code=sm_100a", "-lcudart", "-ldl"]
     subprocess.run(link, check=True)
+    os.replace(tmp, OUT)
     with open(STAMP, "w") as fh:
         fh.write(dig)
     return OUT

@@ -20,8 +20,8 @@ def _model(edb, cfg):
                         pos_embed_max_size=cfg.pos_embed_max_size, wtype=cfg.wtype)
 
 
-def _run_case(edb, cuda, cfg, lat_hw, n_ctx, seed=0, timestep=500.0):
-    weights = sd3_make_weights(cfg, seed, std=0.05)
+def _run_case(edb, cuda, cfg, lat_hw, n_ctx, seed=0, timestep=500.0, std=0.05):
+    weights = sd3_make_weights(cfg, seed, std=std)
     rng = np.random.default_rng(seed + 100)
     latent = rng.standard_normal((cfg.in_channels,) + lat_hw, dtype=np.float32)
     ctx = rng.standard_normal((n_ctx, cfg.context_size), dtype=np.float32)
@@ -74,7 +74,8 @@ def test_sd3_medium_width_parity(edb, cuda):
     # SD3-medium widths (hidden 1536, 24 heads x 64, mlp 6144, context 4096, pooled 2048, 154 text tokens)
     # with two joint blocks and a 64 x 64 latent (1024 image tokens) under a small position table
     cfg = SD3Config(depth=2, num_heads_override=24, pos_embed_max_size=48)
-    _run_case(edb, cuda, cfg, (64, 64), 154, seed=5)
+    # weights N(0, 0.02) as the workload definition states
+    _run_case(edb, cuda, cfg, (64, 64), 154, seed=5, std=0.02)
 
 
 def test_cfg_combine(edb, cuda):
@@ -84,4 +85,4 @@ def test_cfg_combine(edb, cuda):
     edb.check(edb.lib().edb200_cfg_combine(edb.ptr(u), edb.ptr(c), 4.5, edb.ptr(out), u.numel(), edb.current_stream()))
     torch.cuda.synchronize()
     want = u + 4.5 * (c - u)
-    assert torch.allclose(out, want, rtol=0, atol=1e-6)
+    assert torch.allclose(out, want, rtol=1e-6, atol=1e-5)   # the kernel contracts s * (c - u) + u into one FMA
