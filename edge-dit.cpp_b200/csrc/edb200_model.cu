@@ -268,7 +268,8 @@ edb200_status_t ParamTable::init_random(uint64_t seed, float std, cudaStream_t s
             return nm.size() >= n && nm.compare(nm.size() - n, n, suf) == 0;
         };
         // norm weights are centred on one
-        if (ends_with(".scale") || ends_with(".norm_q.weight") || ends_with(".norm_k.weight") || ends_with("norm3.weight")) {
+        if (ends_with(".scale") || ends_with(".norm_q.weight") || ends_with(".norm_k.weight") || ends_with("norm3.weight") ||
+            ends_with(".norm_added_q.weight") || ends_with(".norm_added_k.weight") || ends_with("txt_norm.weight")) {
             add_one_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, stream>>>(tmp, n);
             count_launch();
         }

@@ -1,0 +1,474 @@
+// Qwen-Image denoise-pass executor: the op schedule of QwenImageModel::forward_orig
+// (reference src/dit_models/models/qwen_image.hpp:3116-3301, QwenImageTransformerBlock::forward
+// :2825-2967, QwenImageAttention::forward :2276-2470, AdaLayerNormContinuous :3040-3070) on the
+// kernels of this library.
+//
+// Text rows first, image rows after them, in every [T, ...] buffer.  With t = time embedding:
+//   m_img, m_txt = mod.1(silu(t))                      weight-streaming GEMVs, all up front
+//   XMOD = modulate(LN(stream), shift1, scale1)        both streams
+//   Q|K|V = XMOD W{q,k,v} + b                          three two-problem GEMM launches into one [T, 3H] buffer
+//   Q,K  = rope(RMSNorm_d(q) w), V -> head-major       pack kernel (per-head norm, text and image weights)
+//   ATT  = attention over text + image                 INT8-QK or f16
+//   stream += gate1 * (ATT Wout + b)                   two-problem GEMM, fused epilogue
+//   stream += gate2 * net.2(gelu(net.0.proj(modulate(LN(stream), shift2, scale2))))
+// The reference's 1/128 K/V pre-scale and 1/32, 1/128 linear pre-scales keep f16 accumulators in
+// range and cancel exactly; accumulation here is f32, so they are not needed.
+#include "edb200_model.h"
+
+#include <cuda_fp16.h>
+
+#include <cmath>
+#include <cstring>
+#include <vector>
+
+using namespace edb;
+
+struct edb200_qwen {
+    edb200_qwen_config_t cfg;
+    ParamTable params;
+    Workspace ws;
+    int lat_h = 0, lat_w = 0, n_txt = 0, n_img = 0;
+    float* X = nullptr;   // [n_txt + n_img, H]
+    void *XMOD = nullptr, *QKV = nullptr, *Q = nullptr, *K = nullptr, *V = nullptr, *ATT = nullptr, *HID = nullptr,
+         *CTXN = nullptr;
+    float *MODS = nullptr, *TVEC = nullptr, *TMP = nullptr, *TEMB = nullptr, *FREQ = nullptr, *PE = nullptr, *RSTD = nullptr,
+          *TOK_IN = nullptr, *TOK_OUT = nullptr, *LAT_IN = nullptr, *LAT_OUT = nullptr, *CTX_IN = nullptr;
+    void* SAGE = nullptr;
+    int64_t sage_bytes = 0;
+    float* tap = nullptr;
+    float* pinned = nullptr;
+    int64_t pinned_bytes = 0;
+};
+
+namespace {
+
+struct Lin {
+    const edb200_qweight_t* w;
+    const float* b;
+};
+
+int64_t hidden(const edb200_qwen_config_t& c) { return (int64_t)c.num_heads * c.head_dim; }
+
+Lin qlin(edb200_qwen* m, const std::string& name) {
+    Lin l;
+    l.w = m->params.get(name + ".weight")->qw;
+    l.b = m->params.get(name + ".bias")->f32;
+    return l;
+}
+
+const float* fparam(edb200_qwen* m, const std::string& name) { return m->params.get(name)->f32; }
+
+edb200_epilogue_t make_ep(void* out, int dt, int64_t ldo, const float* bias) {
+    edb200_epilogue_t ep;
+    memset(&ep, 0, sizeof(ep));
+    ep.out = out;
+    ep.out_dtype = dt;
+    ep.ldo = ldo;
+    ep.bias = bias;
+    return ep;
+}
+
+void register_params(edb200_qwen* m) {
+    const edb200_qwen_config_t& c = m->cfg;
+    const int64_t H = hidden(c), M = c.mlp_hidden;
+    ParamTable& t = m->params;
+    // Quantised: 2-D weights whose row length is a multiple of 256 (tensor_should_be_converted,
+    // reference src/core/runtime/model_loader.cpp:2141-2172); img_in (row length 64) stays f32.
+    auto lin = [&](const std::string& name, int64_t n_out, int64_t k) {
+        t.add(name + ".weight", n_out, k, k % 256 == 0, c.wtype);
+        t.add(name + ".bias", 1, n_out, false, c.wtype);
+    };
+    lin("time_text_embed.timestep_embedder.linear_1", H, 256);
+    lin("time_text_embed.timestep_embedder.linear_2", H, H);
+    t.add("txt_norm.weight", 1, c.joint_attention_dim, false, c.wtype);
+    lin("img_in", H, c.in_channels);
+    lin("txt_in", H, c.joint_attention_dim);
+    for (int i = 0; i < c.num_layers; ++i) {
+        const std::string p = "transformer_blocks." + std::to_string(i) + ".";
+        lin(p + "img_mod.1", 6 * H, H);
+        lin(p + "txt_mod.1", 6 * H, H);
+        for (const char* l : {"to_q", "to_k", "to_v", "add_q_proj", "add_k_proj", "add_v_proj", "to_out.0", "to_add_out"}) {
+            lin(p + "attn." + l, H, H);
+        }
+        for (const char* n : {"norm_q", "norm_k", "norm_added_q", "norm_added_k"}) {
+            t.add(p + "attn." + n + ".weight", 1, c.head_dim, false, c.wtype);
+        }
+        for (const char* s : {"img_mlp", "txt_mlp"}) {
+            lin(p + s + ".net.0.proj", M, H);
+            lin(p + s + ".net.2", H, M);
+        }
+    }
+    lin("norm_out.linear", 2 * H, H);
+    lin("proj_out", (int64_t)c.patch_size * c.patch_size * c.out_channels, H);
+}
+
+// pe[L, d/2, 2, 2]: text ids (s, s, s) with s = max(h_tok/2, w_tok/2) + j first, then image ids
+// (0, row - h_tok/2, col - w_tok/2) (gen_qwen_image_ids, reference
+// src/dit_models/components/common/rope.hpp:405-438; gen_flux_img_ids with scale_rope :142-182).
+std::vector<float> build_qwen_pe(const edb200_qwen_config_t& c, int h_tok, int w_tok, int n_txt) {
+    const int L = n_txt + h_tok * w_tok;
+    int half_total = 0;
+    for (int a = 0; a < 3; ++a) half_total += c.axes_dim[a] / 2;
+    std::vector<float> pe((size_t)L * half_total * 4, 0.0f);
+    const int start = std::max(h_tok / 2, w_tok / 2);
+    int off = 0;
+    for (int a = 0; a < 3; ++a) {
+        const int dim = c.axes_dim[a], half = dim / 2;
+        std::vector<float> omega(half);
+        const float end = (dim * 1.f - 2) / dim;
+        const float step = half > 1 ? (end - 0.f) / (half - 1) : 0.f;
+        for (int i = 0; i < half; ++i) omega[i] = 1.0f / ::powf(1.f * c.theta, 0.f + i * step);
+        for (int t = 0; t < L; ++t) {
+            float pos;
+            if (t < n_txt) {
+                pos = static_cast<float>(start + t);
+            } else {
+                const int it = t - n_txt;
+                pos = a == 0 ? 0.0f : a == 1 ? static_cast<float>(it / w_tok - h_tok / 2) : static_cast<float>(it % w_tok - w_tok / 2);
+            }
+            for (int j = 0; j < half; ++j) {
+                const float ang = pos * omega[j];
+                float* o = &pe[((size_t)t * half_total + off + j) * 4];
+                o[0] = std::cos(ang);
+                o[1] = -std::sin(ang);
+                o[2] = std::sin(ang);
+                o[3] = std::cos(ang);
+            }
+        }
+        off += half;
+    }
+    return pe;
+}
+
+// y[row, c] = f16(x[row, c] * rstd[row] * w[c])   (txt_norm: RMSNorm over the whole context row)
+__global__ void rms_apply_kernel(const float* __restrict__ x, const float* __restrict__ rstd, const float* __restrict__ w,
+                                 __half* __restrict__ y, int cols, int64_t total) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    y[i] = __float2half_rn((x[i] * rstd[i / cols]) * w[i % cols]);
+}
+
+edb200_status_t ln_mod(const float* x, int64_t H, const float* shift, const float* scale, int64_t rows, void* y,
+                       int y_dtype, cudaStream_t s) {
+    if (rows == 0) return EDB200_OK;
+    return edb200_layernorm_modulate(x, H, shift, scale, nullptr, nullptr, rows, H, 1e-6f, y, y_dtype, H, s);
+}
+
+}  // namespace
+
+extern "C" {
+
+edb200_status_t edb200_qwen_create(const edb200_qwen_config_t* cfg, edb200_qwen_t** out) {
+    if (cfg == nullptr || out == nullptr) return fail(EDB200_ERR_INVALID, "qwen_create: null argument");
+    const edb200_qwen_config_t& c = *cfg;
+    if (c.num_heads <= 0 || c.num_layers <= 0 || (c.head_dim != 64 && c.head_dim != 128)) {
+        return fail(EDB200_ERR_UNSUPPORTED, "qwen_create: head dim must be 64 or 128");
+    }
+    const int64_t H = hidden(c);
+    if (c.axes_dim[0] + c.axes_dim[1] + c.axes_dim[2] != c.head_dim) {
+        return fail(EDB200_ERR_INVALID, "qwen_create: axes_dim must sum to the head dim");
+    }
+    if (c.wtype != EDB200_TYPE_Q8_0 && c.wtype != EDB200_TYPE_Q4_K) {
+        return fail(EDB200_ERR_UNSUPPORTED, "qwen_create: wtype must be q8_0 or q4_K");
+    }
+    if (H % 256 || c.mlp_hidden % 256 || H > 8192 || c.joint_attention_dim % 256) {
+        return fail(EDB200_ERR_UNSUPPORTED, "qwen_create: hidden (<= 8192), mlp_hidden and joint_attention_dim must be multiples of 256");
+    }
+    if (c.attention == EDB200_ATTN_SAGE_INT8 && c.head_dim != 128) {
+        return fail(EDB200_ERR_UNSUPPORTED, "qwen_create: INT8 attention needs head dim 128");
+    }
+    const int pf = c.patch_size * c.patch_size * c.out_channels;
+    if (c.patch_size <= 0 || pf % 32 || c.in_channels % 4 || c.in_channels % (c.patch_size * c.patch_size)) {
+        return fail(EDB200_ERR_UNSUPPORTED, "qwen_create: patch_size^2 * out_channels must be a multiple of 32");
+    }
+    if (device_error_word() == nullptr) return fail(EDB200_ERR_CUDA, "qwen_create: no CUDA device");
+    edb200_qwen* m = new (std::nothrow) edb200_qwen();
+    if (m == nullptr) return fail(EDB200_ERR_NOMEM, "qwen_create: host allocation failed");
+    m->cfg = c;
+    register_params(m);
+    *out = m;
+    return EDB200_OK;
+}
+
+void edb200_qwen_destroy(edb200_qwen_t* m) {
+    if (m == nullptr) return;
+    if (m->pinned) cudaFreeHost(m->pinned);
+    delete m;
+}
+
+int edb200_qwen_tensor_count(const edb200_qwen_t* m) {
+    return m ? static_cast<int>(const_cast<edb200_qwen_t*>(m)->params.params().size()) : 0;
+}
+
+edb200_status_t edb200_qwen_tensor_info(const edb200_qwen_t* m, int index, char* name, int name_cap, int* ggml_type,
+                                        int64_t* n_out, int64_t* k, int64_t* nbytes) {
+    if (m == nullptr || index < 0 || index >= edb200_qwen_tensor_count(m)) {
+        return fail(EDB200_ERR_INVALID, "qwen_tensor_info: bad index");
+    }
+    const Param& p = const_cast<edb200_qwen_t*>(m)->params.params()[index];
+    if (name != nullptr && name_cap > 0) {
+        strncpy(name, p.spec.name.c_str(), name_cap - 1);
+        name[name_cap - 1] = '\0';
+    }
+    if (ggml_type) *ggml_type = p.spec.ggml_type;
+    if (n_out) *n_out = p.spec.n_out;
+    if (k) *k = p.spec.k;
+    if (nbytes) *nbytes = p.spec.n_out * ggml_row_bytes(p.spec.ggml_type, p.spec.k);
+    return EDB200_OK;
+}
+
+edb200_status_t edb200_qwen_set_tensor(edb200_qwen_t* m, const char* name, int ggml_type, const void* data,
+                                       int64_t nbytes, int on_device, void* stream) {
+    if (m == nullptr || name == nullptr) return fail(EDB200_ERR_INVALID, "qwen_set_tensor: null argument");
+    return m->params.set(name, ggml_type, data, nbytes, on_device != 0, static_cast<cudaStream_t>(stream));
+}
+
+edb200_status_t edb200_qwen_init_random(edb200_qwen_t* m, uint64_t seed, float std, void* stream) {
+    if (m == nullptr) return fail(EDB200_ERR_INVALID, "qwen_init_random: null model");
+    return m->params.init_random(seed, std, static_cast<cudaStream_t>(stream));
+}
+
+int64_t edb200_qwen_weight_bytes(const edb200_qwen_t* m) { return m ? m->params.device_bytes() : 0; }
+
+edb200_status_t edb200_qwen_set_tap(edb200_qwen_t* m, float* tap) {
+    if (m == nullptr) return fail(EDB200_ERR_INVALID, "qwen_set_tap: null model");
+    m->tap = tap;
+    return EDB200_OK;
+}
+
+edb200_status_t edb200_qwen_prepare(edb200_qwen_t* m, int lat_h, int lat_w, int n_txt, void* stream) {
+    if (m == nullptr) return fail(EDB200_ERR_INVALID, "qwen_prepare: null model");
+    const edb200_qwen_config_t& c = m->cfg;
+    const int p = c.patch_size;
+    if (lat_h <= 0 || lat_w <= 0 || n_txt <= 0 || lat_h % p || lat_w % p) {
+        return fail(EDB200_ERR_INVALID, "qwen_prepare: latent must be a positive multiple of the patch size");
+    }
+    if (m->lat_h == lat_h && m->lat_w == lat_w && m->n_txt == n_txt) return EDB200_OK;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int64_t H = hidden(c), M = c.mlp_hidden, d = c.head_dim;
+    const int h_tok = lat_h / p, w_tok = lat_w / p;
+    const int64_t n_img = (int64_t)h_tok * w_tok, T = n_img + n_txt;
+    const int lat_c = c.in_channels / (p * p);
+    const int64_t pf_out = (int64_t)c.out_channels * p * p;
+    const int64_t lat_in = (int64_t)lat_c * lat_h * lat_w, lat_out = (int64_t)c.out_channels * lat_h * lat_w;
+    const int64_t sage = c.attention == EDB200_ATTN_SAGE_INT8 ? edb200_sage_scratch_bytes(c.num_heads, T, (int)d) : 0;
+    const int64_t pe_elems = T * (d / 2) * 4;
+    auto al = [](int64_t b) { return (b + 255) & ~int64_t(255); };
+    int64_t total = al(T * H * 4) + al(T * H * 2) + al(T * 3 * H * 2) + 4 * al(T * H * 2) + al(T * M * 2);
+    total += al(((int64_t)12 * c.num_layers + 2) * H * 4) + al(H * 4) + al(H * 4) + al(256 * 4) + al(128 * 4) + al(pe_elems * 4);
+    total += al((int64_t)n_txt * c.joint_attention_dim * 2) + al(n_txt * 4) + al(n_img * c.in_channels * 4) +
+             al(n_img * pf_out * 4) + al(lat_in * 4) + al(lat_out * 4) + al((int64_t)n_txt * c.joint_attention_dim * 4) +
+             al(sage) + 8192;
+    cudaStreamSynchronize(s);
+    EDB_TRY(m->ws.reserve(total));
+    Workspace& w = m->ws;
+    m->X = w.take_n<float>(T * H);
+    m->XMOD = w.take(T * H * 2);
+    m->QKV = w.take(T * 3 * H * 2);
+    m->Q = w.take(T * H * 2);
+    m->K = w.take(T * H * 2);
+    m->V = w.take(T * H * 2);
+    m->ATT = w.take(T * H * 2);
+    m->HID = w.take(T * M * 2);
+    m->MODS = w.take_n<float>(((int64_t)12 * c.num_layers + 2) * H);
+    m->TVEC = w.take_n<float>(H);
+    m->TMP = w.take_n<float>(H);
+    m->TEMB = w.take_n<float>(256);
+    m->FREQ = w.take_n<float>(128);
+    m->PE = w.take_n<float>(pe_elems);
+    m->CTXN = w.take((int64_t)n_txt * c.joint_attention_dim * 2);
+    m->RSTD = w.take_n<float>(n_txt);
+    m->TOK_IN = w.take_n<float>(n_img * c.in_channels);
+    m->TOK_OUT = w.take_n<float>(n_img * pf_out);
+    m->LAT_IN = w.take_n<float>(lat_in);
+    m->LAT_OUT = w.take_n<float>(lat_out);
+    m->CTX_IN = w.take_n<float>((int64_t)n_txt * c.joint_attention_dim);
+    m->SAGE = sage > 0 ? w.take(sage) : nullptr;
+    m->sage_bytes = sage;
+    if (m->CTX_IN == nullptr || (sage > 0 && m->SAGE == nullptr)) {
+        return fail(EDB200_ERR_NOMEM, "qwen_prepare: workspace accounting error");
+    }
+    std::vector<float> pe = build_qwen_pe(c, h_tok, w_tok, n_txt);
+    std::vector<float> freq(128);
+    for (int i = 0; i < 128; ++i) freq[i] = (float)std::exp(-std::log(10000) * i / 128);
+    cudaError_t e = cudaMemcpyAsync(m->PE, pe.data(), pe.size() * 4, cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(m->FREQ, freq.data(), 128 * 4, cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    if (e != cudaSuccess) return check_cuda(e, "qwen_prepare upload");
+    const int64_t need = (lat_in + lat_out + (int64_t)n_txt * c.joint_attention_dim) * 4;
+    if (need > m->pinned_bytes) {
+        if (m->pinned) cudaFreeHost(m->pinned);
+        m->pinned = nullptr;
+        e = cudaMallocHost(reinterpret_cast<void**>(&m->pinned), need);
+        if (e != cudaSuccess) return fail(EDB200_ERR_NOMEM, "qwen_prepare: cudaMallocHost: %s", cudaGetErrorString(e));
+        m->pinned_bytes = need;
+    }
+    m->lat_h = lat_h;
+    m->lat_w = lat_w;
+    m->n_txt = n_txt;
+    m->n_img = static_cast<int>(n_img);
+    return EDB200_OK;
+}
+
+edb200_status_t edb200_qwen_step(edb200_qwen_t* m, const float* latent, float timestep, const float* context, float* out,
+                                 void* stream) {
+    if (m == nullptr || latent == nullptr || context == nullptr || out == nullptr) {
+        return fail(EDB200_ERR_INVALID, "qwen_step: null argument");
+    }
+    if (m->lat_h == 0) return fail(EDB200_ERR_INVALID, "qwen_step: call edb200_qwen_prepare first");
+    EDB_TRY(m->params.all_loaded());
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const edb200_qwen_config_t& c = m->cfg;
+    const int64_t H = hidden(c), M = c.mlp_hidden;
+    const int d = c.head_dim;
+    const int p = c.patch_size;
+    const int64_t n_txt = m->n_txt, n_img = m->n_img, T = n_txt + n_img;
+    const int lat_c = c.in_channels / (p * p);
+    const int64_t pf_out = (int64_t)c.out_channels * p * p;
+    const int F16 = EDB200_TYPE_F16;
+    float* X_txt = m->X;
+    float* X_img = m->X + n_txt * H;
+    __half* xmod = static_cast<__half*>(m->XMOD);
+    __half* qkv = static_cast<__half*>(m->QKV);
+    __half* att = static_cast<__half*>(m->ATT);
+    __half* hid = static_cast<__half*>(m->HID);
+
+    // ---- prelude (forward_orig, qwen_image.hpp:3131-3160)
+    launch_patchify(latent, m->TOK_IN, lat_c, m->lat_h, m->lat_w, p, s);
+    {
+        const Param* w = m->params.get("img_in.weight");
+        EDB_TRY(edb200_linear_f32(w->f32, fparam(m, "img_in.bias"), m->TOK_IN, n_img, c.in_channels, H, c.in_channels, 0,
+                                  EDB200_ACT_NONE, X_img, H, s));
+    }
+    EDB_TRY(edb200_row_rstd(context, EDB200_TYPE_F32, c.joint_attention_dim, n_txt, c.joint_attention_dim, 1e-6f, m->RSTD, s));
+    {
+        const int64_t total = n_txt * c.joint_attention_dim;
+        rms_apply_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, s>>>(
+            context, m->RSTD, fparam(m, "txt_norm.weight"), static_cast<__half*>(m->CTXN), c.joint_attention_dim, total);
+        count_launch();
+        const Lin l = qlin(m, "txt_in");
+        edb200_epilogue_t ep = make_ep(X_txt, EDB200_TYPE_F32, H, l.b);
+        EDB_TRY(edb200_mul_mat_q(l.w, m->CTXN, F16, n_txt, c.joint_attention_dim, &ep, s));
+    }
+    launch_timestep_embedding(m->FREQ, timestep, 1.0f, 128, m->TEMB, s);
+    {
+        const Lin l1 = qlin(m, "time_text_embed.timestep_embedder.linear_1");
+        const Lin l2 = qlin(m, "time_text_embed.timestep_embedder.linear_2");
+        EDB_TRY(edb200_gemv_q(l1.w, m->TEMB, 1, 256, 0, l1.b, m->TMP, H, s));
+        EDB_TRY(edb200_gemv_q(l2.w, m->TMP, 1, H, 1, l2.b, m->TVEC, H, s));   // SiLU between the two
+    }
+
+    // ---- every adaLN vector of the pass: mod.1(silu(t)), weight streaming
+    float* mods = m->MODS;
+    for (int i = 0; i < c.num_layers; ++i) {
+        const std::string pb = "transformer_blocks." + std::to_string(i) + ".";
+        const Lin li = qlin(m, pb + "img_mod.1"), lt = qlin(m, pb + "txt_mod.1");
+        EDB_TRY(edb200_gemv_q(li.w, m->TVEC, 1, H, 1, li.b, mods + (int64_t)i * 12 * H, 6 * H, s));
+        EDB_TRY(edb200_gemv_q(lt.w, m->TVEC, 1, H, 1, lt.b, mods + ((int64_t)i * 12 + 6) * H, 6 * H, s));
+    }
+    float* fmods = mods + (int64_t)c.num_layers * 12 * H;
+    {
+        const Lin lf = qlin(m, "norm_out.linear");
+        EDB_TRY(edb200_gemv_q(lf.w, m->TVEC, 1, H, 1, lf.b, fmods, 2 * H, s));
+    }
+
+    // ---- blocks (QwenImageTransformerBlock::forward, qwen_image.hpp:2825-2967)
+    for (int i = 0; i < c.num_layers; ++i) {
+        const std::string pb = "transformer_blocks." + std::to_string(i) + ".";
+        const std::string pa = pb + "attn.";
+        const float* im = mods + (int64_t)i * 12 * H;   // shift1 scale1 gate1 shift2 scale2 gate2
+        const float* tm = im + 6 * H;
+        EDB_TRY(ln_mod(X_img, H, im, im + H, n_img, xmod + n_txt * H, F16, s));
+        EDB_TRY(ln_mod(X_txt, H, tm, tm + H, n_txt, xmod, F16, s));
+        {
+            const char* img_names[3] = {"to_q", "to_k", "to_v"};
+            const char* txt_names[3] = {"add_q_proj", "add_k_proj", "add_v_proj"};
+            for (int j = 0; j < 3; ++j) {
+                const Lin li = qlin(m, pa + img_names[j]), lt = qlin(m, pa + txt_names[j]);
+                edb200_epilogue_t ei = make_ep(qkv + n_txt * 3 * H + j * H, F16, 3 * H, li.b);
+                edb200_epilogue_t et = make_ep(qkv + j * H, F16, 3 * H, lt.b);
+                EDB_TRY(edb200_mul_mat_q_pair(li.w, xmod + n_txt * H, n_img, H, &ei, lt.w, xmod, n_txt, H, &et, F16, s));
+            }
+        }
+        EDB_TRY(edb200_qk_norm_rope_pack(qkv + n_txt * 3 * H, F16, 3 * H, 0, H, 2 * H, n_img, c.num_heads, d,
+                                         fparam(m, pa + "norm_q.weight"), fparam(m, pa + "norm_k.weight"), 1e-6f, m->PE,
+                                         n_txt, T, m->Q, m->K, m->V, F16, s));
+        EDB_TRY(edb200_qk_norm_rope_pack(qkv, F16, 3 * H, 0, H, 2 * H, n_txt, c.num_heads, d,
+                                         fparam(m, pa + "norm_added_q.weight"), fparam(m, pa + "norm_added_k.weight"),
+                                         1e-6f, m->PE, 0, T, m->Q, m->K, m->V, F16, s));
+        {
+            const float scale = 1.0f / std::sqrt(static_cast<float>(d));
+            if (c.attention == EDB200_ATTN_SAGE_INT8) {
+                EDB_TRY(edb200_sage_attention(m->Q, m->K, m->V, c.num_heads, T, d, scale,
+                                              (c.sage_smooth_q ? EDB200_SAGE_SMOOTH_Q : 0) | EDB200_SAGE_FAST_MEANS,
+                                              m->SAGE, m->sage_bytes, att, F16, H, s));
+            } else {
+                EDB_TRY(edb200_attention_f16(m->Q, m->K, m->V, c.num_heads, T, T, d, scale, att, F16, H, s));
+            }
+        }
+        {
+            const Lin li = qlin(m, pa + "to_out.0"), lt = qlin(m, pa + "to_add_out");
+            edb200_epilogue_t ei = make_ep(X_img, EDB200_TYPE_F32, H, li.b);
+            ei.residual = X_img, ei.ld_res = H, ei.gate = im + 2 * H;
+            edb200_epilogue_t et = make_ep(X_txt, EDB200_TYPE_F32, H, lt.b);
+            et.residual = X_txt, et.ld_res = H, et.gate = tm + 2 * H;
+            EDB_TRY(edb200_mul_mat_q_pair(li.w, att + n_txt * H, n_img, H, &ei, lt.w, att, n_txt, H, &et, F16, s));
+        }
+        EDB_TRY(ln_mod(X_img, H, im + 3 * H, im + 4 * H, n_img, xmod + n_txt * H, F16, s));
+        EDB_TRY(ln_mod(X_txt, H, tm + 3 * H, tm + 4 * H, n_txt, xmod, F16, s));
+        {
+            const Lin i0 = qlin(m, pb + "img_mlp.net.0.proj"), t0 = qlin(m, pb + "txt_mlp.net.0.proj");
+            edb200_epilogue_t ei = make_ep(hid + n_txt * M, F16, M, i0.b);
+            ei.act = EDB200_ACT_GELU_TANH;
+            edb200_epilogue_t et = make_ep(hid, F16, M, t0.b);
+            et.act = EDB200_ACT_GELU_TANH;
+            EDB_TRY(edb200_mul_mat_q_pair(i0.w, xmod + n_txt * H, n_img, H, &ei, t0.w, xmod, n_txt, H, &et, F16, s));
+            const Lin i2 = qlin(m, pb + "img_mlp.net.2"), t2 = qlin(m, pb + "txt_mlp.net.2");
+            edb200_epilogue_t fi = make_ep(X_img, EDB200_TYPE_F32, H, i2.b);
+            fi.residual = X_img, fi.ld_res = H, fi.gate = im + 5 * H;
+            edb200_epilogue_t ft = make_ep(X_txt, EDB200_TYPE_F32, H, t2.b);
+            ft.residual = X_txt, ft.ld_res = H, ft.gate = tm + 5 * H;
+            EDB_TRY(edb200_mul_mat_q_pair(i2.w, hid + n_txt * M, n_img, M, &fi, t2.w, hid, n_txt, M, &ft, F16, s));
+        }
+        if (m->tap) cudaMemcpyAsync(m->tap + (int64_t)i * T * H, m->X, T * H * 4, cudaMemcpyDeviceToDevice, s);
+    }
+
+    // ---- norm_out: (scale, shift) order (AdaLayerNormContinuous, qwen_image.hpp:3062-3068), proj_out, unpatchify
+    EDB_TRY(ln_mod(X_img, H, fmods + H, fmods, n_img, xmod, F16, s));
+    {
+        const Lin lf = qlin(m, "proj_out");
+        edb200_epilogue_t ep = make_ep(m->TOK_OUT, EDB200_TYPE_F32, pf_out, lf.b);
+        EDB_TRY(edb200_mul_mat_q(lf.w, xmod, F16, n_img, H, &ep, s));
+    }
+    launch_unpatchify(m->TOK_OUT, out, c.out_channels, m->lat_h, m->lat_w, p, s);
+    return check_cuda(cudaGetLastError(), "qwen_step");
+}
+
+edb200_status_t edb200_qwen_compute_host(edb200_qwen_t* m, const float* latent, int lat_h, int lat_w, float timestep,
+                                         const float* context, int n_txt, float* out, void* stream) {
+    if (m == nullptr || latent == nullptr || context == nullptr || out == nullptr) {
+        return fail(EDB200_ERR_INVALID, "qwen_compute_host: null argument");
+    }
+    EDB_TRY(edb200_qwen_prepare(m, lat_h, lat_w, n_txt, stream));
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const edb200_qwen_config_t& c = m->cfg;
+    const int lat_c = c.in_channels / (c.patch_size * c.patch_size);
+    const int64_t lat_in = (int64_t)lat_c * lat_h * lat_w, lat_out = (int64_t)c.out_channels * lat_h * lat_w;
+    const int64_t ctx_elems = (int64_t)n_txt * c.joint_attention_dim;
+    float* p_lat = m->pinned;
+    float* p_ctx = p_lat + lat_in;
+    float* p_out = p_ctx + ctx_elems;
+    memcpy(p_lat, latent, lat_in * 4);
+    memcpy(p_ctx, context, ctx_elems * 4);
+    cudaError_t e = cudaMemcpyAsync(m->LAT_IN, p_lat, lat_in * 4, cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(m->CTX_IN, p_ctx, ctx_elems * 4, cudaMemcpyHostToDevice, s);
+    if (e != cudaSuccess) return check_cuda(e, "qwen_compute_host H2D");
+    EDB_TRY(edb200_qwen_step(m, m->LAT_IN, timestep, m->CTX_IN, m->LAT_OUT, stream));
+    e = cudaMemcpyAsync(p_out, m->LAT_OUT, lat_out * 4, cudaMemcpyDeviceToHost, s);
+    if (e != cudaSuccess) return check_cuda(e, "qwen_compute_host D2H");
+    EDB_TRY(poll_device_error(s));   // synchronises the stream
+    memcpy(out, p_out, lat_out * 4);
+    return EDB200_OK;
+}
+
+}  // extern "C"

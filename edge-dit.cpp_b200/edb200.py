@@ -29,6 +29,16 @@ class Epilogue(C.Structure):
     ]
 
 
+class QwenConfig(C.Structure):
+    """edb200_qwen_config_t"""
+    _fields_ = [
+        ("num_layers", C.c_int), ("num_heads", C.c_int), ("head_dim", C.c_int), ("mlp_hidden", C.c_int),
+        ("in_channels", C.c_int), ("out_channels", C.c_int), ("joint_attention_dim", C.c_int), ("patch_size", C.c_int),
+        ("axes_dim", C.c_int * 3), ("theta", C.c_int), ("wtype", C.c_int), ("attention", C.c_int),
+        ("sage_smooth_q", C.c_int),
+    ]
+
+
 class SD3Config(C.Structure):
     """edb200_sd3_config_t"""
     _fields_ = [
@@ -134,6 +144,18 @@ _SIGS = {
     "edb200_qk_rownorm_rope_pack": (C.c_int, [c_vp, C.c_int, c_i64, c_i64, c_i64, c_i64, c_i64, C.c_int, C.c_int, c_vp,
                                               c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_vp, c_vp, c_vp, C.c_int, c_vp,
                                               c_vp]),
+    "edb200_qwen_create": (C.c_int, [C.POINTER(QwenConfig), C.POINTER(c_vp)]),
+    "edb200_qwen_destroy": (None, [c_vp]),
+    "edb200_qwen_tensor_count": (C.c_int, [c_vp]),
+    "edb200_qwen_tensor_info": (C.c_int, [c_vp, C.c_int, C.c_char_p, C.c_int, C.POINTER(C.c_int), C.POINTER(c_i64),
+                                          C.POINTER(c_i64), C.POINTER(c_i64)]),
+    "edb200_qwen_set_tensor": (C.c_int, [c_vp, C.c_char_p, C.c_int, c_vp, c_i64, C.c_int, c_vp]),
+    "edb200_qwen_init_random": (C.c_int, [c_vp, C.c_uint64, C.c_float, c_vp]),
+    "edb200_qwen_weight_bytes": (c_i64, [c_vp]),
+    "edb200_qwen_prepare": (C.c_int, [c_vp, C.c_int, C.c_int, C.c_int, c_vp]),
+    "edb200_qwen_set_tap": (C.c_int, [c_vp, c_vp]),
+    "edb200_qwen_step": (C.c_int, [c_vp, c_vp, C.c_float, c_vp, c_vp, c_vp]),
+    "edb200_qwen_compute_host": (C.c_int, [c_vp, c_vp, C.c_int, C.c_int, C.c_float, c_vp, C.c_int, c_vp, c_vp]),
     "edb200_sd3_create": (C.c_int, [C.POINTER(SD3Config), C.POINTER(c_vp)]),
     "edb200_sd3_destroy": (None, [c_vp]),
     "edb200_sd3_tensor_count": (C.c_int, [c_vp]),
@@ -367,6 +389,68 @@ class FluxModel:
                                              timestep, context.ctypes.data_as(c_vp), context.shape[0],
                                              y.ctypes.data_as(c_vp), guidance, out.ctypes.data_as(c_vp),
                                              current_stream()))
+        return out
+
+
+class QwenModel:
+    """Thin owner of an edb200_qwen_t (host-side mirror of the reference's QwenImageModel adapter,
+    src/dit_models/diffusion_model.hpp) over the C ABI; one call is one batch-1 pass."""
+
+    def __init__(self, num_layers=60, num_heads=24, head_dim=128, mlp_hidden=None, in_channels=64, out_channels=16,
+                 joint_attention_dim=3584, patch_size=2, axes_dim=(16, 56, 56), theta=10000, wtype=TYPE_Q4_K,
+                 attention=ATTN_SAGE_INT8, sage_smooth_q=True):
+        cfg = QwenConfig()
+        cfg.num_layers, cfg.num_heads, cfg.head_dim = num_layers, num_heads, head_dim
+        cfg.mlp_hidden = mlp_hidden if mlp_hidden is not None else 4 * num_heads * head_dim
+        cfg.in_channels, cfg.out_channels, cfg.joint_attention_dim, cfg.patch_size = in_channels, out_channels, joint_attention_dim, patch_size
+        cfg.axes_dim = (C.c_int * 3)(*axes_dim)
+        cfg.theta, cfg.wtype, cfg.attention, cfg.sage_smooth_q = theta, wtype, attention, int(sage_smooth_q)
+        self.cfg = cfg
+        h = c_vp()
+        check(lib().edb200_qwen_create(C.byref(cfg), C.byref(h)))
+        self.handle = h
+
+    def __del__(self):
+        if getattr(self, "handle", None) and _lib is not None:
+            _lib.edb200_qwen_destroy(self.handle)
+            self.handle = None
+
+    def tensor_names(self):
+        buf = C.create_string_buffer(256)
+        out = []
+        for i in range(lib().edb200_qwen_tensor_count(self.handle)):
+            check(lib().edb200_qwen_tensor_info(self.handle, i, buf, 256, None, None, None, None))
+            out.append(buf.value.decode())
+        return out
+
+    def load_numpy(self, weights: dict):
+        import numpy as np
+        for name, (t, arr) in weights.items():
+            a = np.ascontiguousarray(arr)
+            check(lib().edb200_qwen_set_tensor(self.handle, name.encode(), t, a.ctypes.data_as(c_vp), a.nbytes, 0,
+                                               current_stream()))
+
+    def init_random(self, seed=0, std=0.02):
+        check(lib().edb200_qwen_init_random(self.handle, seed, std, current_stream()))
+
+    def set_tap(self, tap):
+        self._tap = tap
+        check(lib().edb200_qwen_set_tap(self.handle, ptr(tap)))
+
+    def prepare(self, lat_h, lat_w, n_txt):
+        check(lib().edb200_qwen_prepare(self.handle, lat_h, lat_w, n_txt, current_stream()))
+
+    def step(self, latent, timestep, context, out):
+        check(lib().edb200_qwen_step(self.handle, ptr(latent), timestep, ptr(context), ptr(out), current_stream()))
+
+    def compute_host(self, latent, timestep, context):
+        import numpy as np
+        latent = np.ascontiguousarray(latent, dtype=np.float32)
+        context = np.ascontiguousarray(context, dtype=np.float32)
+        out = np.empty((self.cfg.out_channels,) + latent.shape[1:], dtype=np.float32)
+        check(lib().edb200_qwen_compute_host(self.handle, latent.ctypes.data_as(c_vp), latent.shape[1], latent.shape[2],
+                                             timestep, context.ctypes.data_as(c_vp), context.shape[0],
+                                             out.ctypes.data_as(c_vp), current_stream()))
         return out
 
 

@@ -484,6 +484,46 @@ EDB200_API edb200_status_t edb200_sd3_compute_host(edb200_sd3_t* m, const float*
 EDB200_API edb200_status_t edb200_cfg_combine(const float* uncond, const float* cond, float scale, float* out, int64_t n,
                                               void* stream);
 
+/* ---------------------------------------------------- Qwen-Image denoise pass
+ * The same seam for QwenImageModel (src/dit_models/models/qwen_image.hpp:3116-3301; members
+ * QwenImageParams :3074-3114).  One call is one batch-1 pass (CFG = two passes + combine). */
+typedef struct {
+    int num_layers;           /* 60 */
+    int num_heads;            /* 24 */
+    int head_dim;             /* 128 */
+    int mlp_hidden;           /* 12288 */
+    int in_channels;          /* 64 = 16 latent channels x 2 x 2 patch */
+    int out_channels;         /* 16 */
+    int joint_attention_dim;  /* 3584 */
+    int patch_size;           /* 2 */
+    int axes_dim[3];          /* (16, 56, 56) */
+    int theta;
+    int wtype;                /* EDB200_TYPE_Q8_0 / EDB200_TYPE_Q4_K: every 2-D weight with row length % 256 == 0 */
+    int attention;            /* EDB200_ATTN_F16 / EDB200_ATTN_SAGE_INT8 */
+    int sage_smooth_q;
+} edb200_qwen_config_t;
+
+typedef struct edb200_qwen edb200_qwen_t;
+
+EDB200_API edb200_status_t edb200_qwen_create(const edb200_qwen_config_t* cfg, edb200_qwen_t** out);
+EDB200_API void edb200_qwen_destroy(edb200_qwen_t* m);
+EDB200_API int edb200_qwen_tensor_count(const edb200_qwen_t* m);
+EDB200_API edb200_status_t edb200_qwen_tensor_info(const edb200_qwen_t* m, int index, char* name, int name_cap,
+                                                   int* ggml_type, int64_t* n_out, int64_t* k, int64_t* nbytes);
+EDB200_API edb200_status_t edb200_qwen_set_tensor(edb200_qwen_t* m, const char* name, int ggml_type, const void* data,
+                                                  int64_t nbytes, int on_device, void* stream);
+EDB200_API edb200_status_t edb200_qwen_init_random(edb200_qwen_t* m, uint64_t seed, float std, void* stream);
+EDB200_API int64_t edb200_qwen_weight_bytes(const edb200_qwen_t* m);
+EDB200_API edb200_status_t edb200_qwen_prepare(edb200_qwen_t* m, int lat_h, int lat_w, int n_txt, void* stream);
+/* Optional f32 tap [num_layers, n_txt + image tokens, hidden]: both streams after every block. */
+EDB200_API edb200_status_t edb200_qwen_set_tap(edb200_qwen_t* m, float* tap);
+/* latent f32 [in_channels / patch^2, lat_h, lat_w], context f32 [n_txt, joint_attention_dim]. */
+EDB200_API edb200_status_t edb200_qwen_step(edb200_qwen_t* m, const float* latent, float timestep, const float* context,
+                                            float* out, void* stream);
+EDB200_API edb200_status_t edb200_qwen_compute_host(edb200_qwen_t* m, const float* latent, int lat_h, int lat_w,
+                                                    float timestep, const float* context, int n_txt, float* out,
+                                                    void* stream);
+
 /* -------------------------------------------------- Wan 2.1 (t2v) denoise step
  * The same seam for WanModel / WanRunner::compute (src/dit_models/models/wan.hpp:4811-5529,
  * graph Wan::forward :4759-4808).  Field names follow WanParams (:4382-4405). */
