@@ -424,4 +424,16 @@ edb200_status_t edb200_sp_all_gather_rows(edb200_comm_t* c, const void* send, vo
     return check_nccl(rc_end, "ncclGroupEnd");
 }
 
+edb200_status_t edb200_cfg_parallel_combine(edb200_comm_t* c, const float* mine, float scale, float* gathered, float* out,
+                                            int64_t n, void* stream) {
+    if (c == nullptr || mine == nullptr || gathered == nullptr || out == nullptr || n <= 0 || n % 4) {
+        return fail(EDB200_ERR_INVALID, "cfg_parallel_combine: bad argument (n %% 4 == 0 required)");
+    }
+    if (c->world != 2) return fail(EDB200_ERR_UNSUPPORTED, "cfg_parallel_combine: the communicator must have 2 ranks");
+    const int64_t first[2] = {0, 1}, count[2] = {1, 1};
+    EDB_TRY(edb200_sp_all_gather_rows(c, mine, gathered, first, count, n * 4, stream));
+    // rank 0 ran the conditional branch, rank 1 the unconditional one
+    return edb200_cfg_combine(gathered + n, gathered, scale, out, n, stream);
+}
+
 }  // extern "C"

@@ -139,6 +139,7 @@ _SIGS = {
                                                 c_i64, C.c_int, C.c_float, c_vp, C.c_int, c_i64, c_vp, c_vp]),
     "edb200_sage_attention_sp": (C.c_int, [c_vp, c_vp, c_vp, C.c_int, c_i64, C.c_int, C.c_float, C.c_int, c_vp, c_i64,
                                            c_vp, C.c_int, c_i64, c_vp, c_vp]),
+    "edb200_cfg_parallel_combine": (C.c_int, [c_vp, c_vp, C.c_float, c_vp, c_vp, c_i64, c_vp]),
     "edb200_flux_set_comm": (C.c_int, [c_vp, c_vp]),
     "edb200_row_rstd": (C.c_int, [c_vp, C.c_int, c_i64, c_i64, c_i64, C.c_float, c_vp, c_vp]),
     "edb200_qk_rownorm_rope_pack": (C.c_int, [c_vp, C.c_int, c_i64, c_i64, c_i64, c_i64, c_i64, C.c_int, C.c_int, c_vp,

@@ -371,6 +371,13 @@ EDB200_API edb200_status_t edb200_sage_attention_sp(const void* q_f16, const voi
                                                     int64_t scratch_bytes, void* out, int out_dtype, int64_t ld_out,
                                                     const edb200_sp_peers_t* dst, void* stream);
 
+/* CFG-parallel step on a 2-rank communicator (cfg_all_gather, src/parallel/cfg_parallel.cpp:38-108):
+ * rank 0 has run the conditional pass, rank 1 the unconditional one; both receive
+ * out = uncond + scale * (cond - uncond).  `gathered` is scratch for 2 * n floats.  Combine it with
+ * sequence parallelism by giving every branch its own edb200_comm_t for the model. */
+EDB200_API edb200_status_t edb200_cfg_parallel_combine(edb200_comm_t* c, const float* mine, float scale,
+                                                       float* gathered, float* out, int64_t n, void* stream);
+
 /* ------------------------------------------------- FLUX.1 denoise-step model
  * A whole-step replacement at the reference's model seam
  * DiffusionModel::compute(n_threads, DiffusionParams) -> sd::Tensor<float>

@@ -142,3 +142,55 @@ def test_wan_step_sequence_parallel_matches_single_gpu(edb, cuda, world, exchang
         finite, err = ret[r]
         assert finite
         assert err <= 1e-5, (r, err)
+
+
+def _cfg_worker(rank, world, port, lib_dir, ret):
+    import importlib.util
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    spec = importlib.util.spec_from_file_location("edb200", os.path.join(lib_dir, "edb200.py"))
+    edb = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(edb)
+    dev = torch.device("cuda", rank)
+    model = edb.SD3Model(hidden_size=512, num_heads=8, depth=2, adm_in_channels=64, context_size=128, pos_embed_max_size=16)
+    model.init_random(seed=4, std=0.05)
+    g = torch.Generator(device="cpu").manual_seed(21)
+    latent = torch.randn(16, 16, 24, generator=g).to(dev)
+    ctx_c, ctx_u = torch.randn(11, 128, generator=g).to(dev), torch.zeros(11, 128, device=dev)
+    y_c, y_u = torch.randn(64, generator=g).to(dev), torch.zeros(64, device=dev)
+    model.prepare(16, 24, 11)
+    cond, uncond = torch.empty_like(latent), torch.empty_like(latent)
+    model.step(latent, 500.0, ctx_c, y_c, cond)
+    model.step(latent, 500.0, ctx_u, y_u, uncond)
+    want = uncond + 4.0 * (cond - uncond)          # both passes on one GPU
+    comm = edb.Comm()
+    mine = cond if rank == 0 else uncond            # CFG parallel: one pass per rank
+    gathered = torch.empty(2, latent.numel(), device=dev)
+    out = torch.empty_like(latent)
+    edb.check(edb.lib().edb200_cfg_parallel_combine(comm.handle, edb.ptr(mine), 4.0, edb.ptr(gathered), edb.ptr(out),
+                                                    latent.numel(), edb.current_stream()))
+    torch.cuda.synchronize()
+    ret[rank] = bool(torch.allclose(out, want, rtol=1e-6, atol=1e-5))
+    dist.barrier()
+    comm.close()
+    dist.destroy_process_group()
+
+
+def test_cfg_parallel_combine_on_two_gpus(edb, cuda):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    lib_dir = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "edge-dit.cpp_b200")
+    port = _free_port()
+    procs = [ctx.Process(target=_cfg_worker, args=(r, 2, port, lib_dir, ret)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+        assert p.exitcode == 0
+    assert ret[0] and ret[1]
