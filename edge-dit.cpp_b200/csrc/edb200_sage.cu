@@ -85,7 +85,9 @@ channel_finalize_kernel(const float* __restrict__ part_q, const float* __restric
     mean[hn * D + d] = s / static_cast<float>(L);
 }
 
-// One CTA (128 threads) per (token block, head).  BLK tokens share one scale.
+// One CTA (128 threads) per (token block, head).  BLK tokens share one scale.  Every thread
+// owns runs of 8 consecutive channels (16-byte loads, 8-byte stores); the arithmetic per
+// element and the (exact) maximum are those of the reference kernels.
 template <int D, int BLK>
 __global__ void __launch_bounds__(128)
 quant_block_kernel(const __half* __restrict__ x, const float* __restrict__ mean, int8_t* __restrict__ x8,
@@ -96,20 +98,37 @@ quant_block_kernel(const __half* __restrict__ x, const float* __restrict__ mean,
     const int tok0 = blk * BLK;
     const __half* xp = x + (int64_t)hn * L * D;
     const float* mrow = mean ? mean + hn * D : nullptr;
-    constexpr int PER_THREAD = BLK * D / 128;
-    float vals[PER_THREAD];
+    constexpr int VPT = BLK * D / 8 / 128;   // 8-channel vectors per thread
+    float vals[VPT][8];
     float amax = 1e-7f;
 #pragma unroll
-    for (int i = 0; i < PER_THREAD; ++i) {
+    for (int i = 0; i < VPT; ++i) {
         const int idx = tid + i * 128;
-        const int t = idx / D, d = idx % D;
-        float v = 0.0f;
-        if (tok0 + t < L) {
-            v = __half2float(xp[(int64_t)(tok0 + t) * D + d]);
-            if (mrow) v = __fsub_rn(v, mrow[d]);
+        const int t = idx / (D / 8), d0 = (idx % (D / 8)) * 8;
+        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+        const bool live = tok0 + t < L;
+        if (live) raw = *reinterpret_cast<const uint4*>(xp + (int64_t)(tok0 + t) * D + d0);
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+        float m8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        if (mrow != nullptr) {
+            const float4 m0 = __ldg(reinterpret_cast<const float4*>(mrow + d0));
+            const float4 m1 = __ldg(reinterpret_cast<const float4*>(mrow + d0 + 4));
+            m8[0] = m0.x, m8[1] = m0.y, m8[2] = m0.z, m8[3] = m0.w;
+            m8[4] = m1.x, m8[5] = m1.y, m8[6] = m1.z, m8[7] = m1.w;
         }
-        vals[i] = v;
-        amax = fmaxf(amax, fabsf(v));
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[e]));
+            float v0 = f.x, v1 = f.y;
+            if (mrow != nullptr) {
+                v0 = __fsub_rn(v0, m8[2 * e]);
+                v1 = __fsub_rn(v1, m8[2 * e + 1]);
+            }
+            if (!live) v0 = v1 = 0.0f;
+            vals[i][2 * e] = v0;
+            vals[i][2 * e + 1] = v1;
+            amax = fmaxf(amax, fmaxf(fabsf(v0), fabsf(v1)));
+        }
     }
 #pragma unroll
     for (int m = 16; m > 0; m >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
@@ -125,38 +144,60 @@ quant_block_kernel(const __half* __restrict__ x, const float* __restrict__ mean,
     const float inv = s_inv;
     int8_t* op = x8 + (int64_t)hn * L * D;
 #pragma unroll
-    for (int i = 0; i < PER_THREAD; ++i) {
+    for (int i = 0; i < VPT; ++i) {
         const int idx = tid + i * 128;
-        const int t = idx / D, d = idx % D;
+        const int t = idx / (D / 8), d0 = (idx % (D / 8)) * 8;
         if (tok0 + t < L) {
-            float v = __fmul_rn(vals[i], inv);
-            v = fmaxf(fminf(v, 127.0f), -127.0f);
-            op[(int64_t)(tok0 + t) * D + d] = static_cast<int8_t>(__float2int_rn(v));
+            uint32_t packed[2] = {0u, 0u};
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                float v = __fmul_rn(vals[i][e], inv);
+                v = fmaxf(fminf(v, 127.0f), -127.0f);
+                packed[e >> 2] |= (static_cast<uint32_t>(__float2int_rn(v)) & 0xffu) << (8 * (e & 3));
+            }
+            *reinterpret_cast<uint2*>(op + (int64_t)(tok0 + t) * D + d0) = make_uint2(packed[0], packed[1]);
         }
     }
 }
 
-// One warp per (key, head).
+// One thread per (key, head): bias = sum_d qm[d] * k[d], added in the order of the
+// reference's warp kernel (per 32 channels the xor-butterfly tree 16, 8, 4, 2, 1 over
+// the lanes, then the four group sums one after the other), so the result is bit-identical
+// without any shuffle.
 template <int D>
 __global__ void __launch_bounds__(256)
 smooth_q_bias_kernel(const __half* __restrict__ k, const float* __restrict__ qm, float* __restrict__ bias, int L,
                      int HN, int bias_stride) {
-    const int64_t gw = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    const int lane = threadIdx.x & 31;
-    if (gw >= (int64_t)L * HN) return;
-    const int hn = static_cast<int>(gw / L);
-    const int tok = static_cast<int>(gw % L);
-    const __half* kp = k + ((int64_t)hn * L + tok) * D;
-    const float* q = qm + hn * D;
+    __shared__ float q_sh[D];
+    const int hn = blockIdx.y;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) q_sh[i] = qm[hn * D + i];
+    __syncthreads();
+    const int tok = blockIdx.x * blockDim.x + threadIdx.x;
+    if (tok >= L) return;
+    const uint4* kp = reinterpret_cast<const uint4*>(k + ((int64_t)hn * L + tok) * D);
     float total = 0.0f;
 #pragma unroll
     for (int w = 0; w < D / 32; ++w) {
-        float part = __fmul_rn(__half2float(kp[w * 32 + lane]), q[w * 32 + lane]);
+        float p[32];
 #pragma unroll
-        for (int m = 16; m > 0; m >>= 1) part = __fadd_rn(part, __shfl_xor_sync(0xffffffffu, part, m));
-        total = __fadd_rn(total, part);
+        for (int v = 0; v < 4; ++v) {
+            const uint4 raw = kp[w * 4 + v];
+            const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&u[e]));
+                p[v * 8 + 2 * e] = __fmul_rn(f.x, q_sh[w * 32 + v * 8 + 2 * e]);
+                p[v * 8 + 2 * e + 1] = __fmul_rn(f.y, q_sh[w * 32 + v * 8 + 2 * e + 1]);
+            }
+        }
+#pragma unroll
+        for (int m = 16; m > 0; m >>= 1) {
+#pragma unroll
+            for (int i = 0; i < m; ++i) p[i] = __fadd_rn(p[i], p[i + m]);
+        }
+        total = __fadd_rn(total, p[0]);
     }
-    if (lane == 0) bias[(int64_t)hn * bias_stride + tok] = total;
+    bias[(int64_t)hn * bias_stride + tok] = total;
 }
 
 struct Layout {
@@ -226,8 +267,7 @@ static edb200_status_t quantize(const __half* q, const __half* k, int hn, int l,
     if (smooth_q) {
         // the padded tail of each bias row is read by the attention kernel: keep it finite
         cudaMemsetAsync(scratch + lo.bias, 0, (size_t)hn * lo.bias_stride * 4, s);
-        const int64_t warps = (int64_t)l * hn;
-        smooth_q_bias_kernel<D><<<static_cast<unsigned>((warps * 32 + 255) / 256), 256, 0, s>>>(
+        smooth_q_bias_kernel<D><<<dim3((l + 255) / 256, hn), 256, 0, s>>>(
             k, qm, reinterpret_cast<float*>(scratch + lo.bias), l, hn, lo.bias_stride);
         ++launches;
     }
