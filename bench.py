@@ -51,6 +51,11 @@ WORKLOADS = {
     # Wan 2.1 14B: latent [16, 21, 90, 160] -> 75,600 video tokens, 512 text tokens (name starts with "wan")
     "wan14b_q8_0": (dict(), (16, 21, 90, 160), 512),
     "wan_small": (dict(dim=1024, num_heads=8, ffn_dim=2048, num_layers=4, text_dim=256), (16, 5, 32, 32), 64),
+    # SD3-medium 512^2: 1024 image + 154 text tokens, q8_0, f16 attention (head dim 64); a step is the
+    # conditional and the unconditional pass plus the CFG combine (name starts with "sd3")
+    "sd3_medium_q8_0": (dict(), (16, 64, 64), 154),
+    # Qwen-Image 1328^2: 6889 image + 256 text tokens, q4_K; a step is two passes plus the CFG combine
+    "qwen_image_q4_k": (dict(), (16, 166, 166), 256),
 }
 
 
@@ -61,10 +66,26 @@ class Case:
         import numpy as np
         kw, lat, n_txt = WORKLOADS[name]
         self.wan = name.startswith("wan")
+        self.family = name.split("_")[0] if name.split("_")[0] in ("sd3", "qwen") else ("wan" if self.wan else "flux")
         g = torch.Generator(device=dev).manual_seed(1234)
         self.latent = torch.randn(lat, generator=g, device=dev)
         g.manual_seed(1235)
-        if self.wan:
+        self.torch = torch
+        if self.family in ("sd3", "qwen"):
+            # classifier-free guidance: two batch-1 passes per step
+            if self.family == "sd3":
+                self.model = edb.SD3Model(**kw)
+                self.ctx = torch.randn(n_txt, self.model.cfg.context_size, generator=g, device=dev)
+                self.y = torch.randn(self.model.cfg.adm_in_channels, generator=g, device=dev)
+                self.y0 = torch.zeros_like(self.y)
+            else:
+                self.model = edb.QwenModel(attention=attention, **kw)
+                self.ctx = torch.randn(n_txt, self.model.cfg.joint_attention_dim, generator=g, device=dev)
+                self.y = None
+            self.ctx0 = torch.zeros_like(self.ctx)
+            self.cond, self.uncond = torch.empty_like(self.latent), torch.empty_like(self.latent)
+            self.tokens = (lat[1] // 2) * (lat[2] // 2) + n_txt
+        elif self.wan:
             self.model = edb.WanModel(attention=attention, **kw)
             self.ctx = torch.randn(n_txt, self.model.cfg.text_dim, generator=g, device=dev)
             ps = tuple(self.model.cfg.patch_size)
@@ -81,29 +102,60 @@ class Case:
         self.edb, self.np = edb, np
 
     def prepare(self):
-        if self.wan:
+        if self.family in ("sd3", "qwen"):
+            self.model.prepare(self.lat[1], self.lat[2], self.n_txt)
+        elif self.wan:
             self.model.prepare(self.lat[1], self.lat[2], self.lat[3], self.n_txt)
         else:
             self.model.prepare(self.lat[1], self.lat[2], self.n_txt)
 
+    def _combine(self):
+        e = self.edb
+        e.check(e.lib().edb200_cfg_combine(e.ptr(self.uncond), e.ptr(self.cond), 4.5, e.ptr(self.out), self.out.numel(),
+                                           e.current_stream()))
+
     def step(self):
-        if self.wan:
+        if self.family == "sd3":
+            self.model.step(self.latent, 500.0, self.ctx, self.y, self.cond)
+            self.model.step(self.latent, 500.0, self.ctx0, self.y0, self.uncond)
+            self._combine()
+        elif self.family == "qwen":
+            self.model.step(self.latent, 500.0, self.ctx, self.cond)
+            self.model.step(self.latent, 500.0, self.ctx0, self.uncond)
+            self._combine()
+        elif self.wan:
             self.model.step(self.latent, 500.0, self.ctx, self.out)
         else:
             self.model.step(self.latent, 0.5, self.ctx, self.y, 3.5, self.out)
 
     def host_inputs(self):
-        self.h = [t.cpu().numpy() for t in ((self.latent, self.ctx) if self.wan else (self.latent, self.ctx, self.y))]
+        if self.family == "sd3":
+            ts = (self.latent, self.ctx, self.y, self.ctx0, self.y0)
+        elif self.family == "qwen":
+            ts = (self.latent, self.ctx, self.ctx0)
+        else:
+            ts = (self.latent, self.ctx) if self.wan else (self.latent, self.ctx, self.y)
+        self.h = [t.cpu().numpy() for t in ts]
         return sum(a.nbytes for a in self.h)
 
     def step_host(self):
+        if self.family == "sd3":
+            c = self.model.compute_host(self.h[0], 500.0, self.h[1], self.h[2])
+            u = self.model.compute_host(self.h[0], 500.0, self.h[3], self.h[4])
+            return u + 4.5 * (c - u)
+        if self.family == "qwen":
+            c = self.model.compute_host(self.h[0], 500.0, self.h[1])
+            u = self.model.compute_host(self.h[0], 500.0, self.h[2])
+            return u + 4.5 * (c - u)
         if self.wan:
             return self.model.compute_host(self.h[0], 500.0, self.h[1])
         return self.model.compute_host(self.h[0], 0.5, self.h[1], self.h[2], 3.5)
 
     def weight_bytes(self):
         lib = self.edb.lib()
-        return lib.edb200_wan_weight_bytes(self.model.handle) if self.wan else lib.edb200_flux_weight_bytes(self.model.handle)
+        fn = {"sd3": lib.edb200_sd3_weight_bytes, "qwen": lib.edb200_qwen_weight_bytes, "wan": lib.edb200_wan_weight_bytes,
+              "flux": lib.edb200_flux_weight_bytes}[self.family]
+        return fn(self.model.handle)
 
 
 def load_pkg(name):
@@ -304,6 +356,8 @@ def run_ours(args):
     if world > 1:
         # Ulysses sequence parallelism: every rank holds all weights, 1/N of the tokens for the
         # per-token work and 1/N of the heads for attention (NCCL exchange inside the library)
+        if case.family in ("sd3", "qwen"):
+            raise SystemExit(f"bench.py: workload {args.workload} has no sequence-parallel path; use --gpus 1")
         comm = edb.Comm()
         model.set_comm(comm)
     case.prepare()

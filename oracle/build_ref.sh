@@ -1,7 +1,7 @@
 #!/bin/sh
 # Compiles the reference's header-only CPU callbacks, from where they lie in the reference
 # tree, against ref_shim/ggml.h into oracle/_ref/libedref_cpu.so.  Test infrastructure.
-# Usage: sh oracle/build_ref.sh [reference root, default /root/reference]
+# Usage: sh oracle/build_ref.sh [reference root]
 set -e
 HERE="$(cd "$(dirname "$0")" && pwd)"
 REF="${1:-/root/reference}"
