@@ -192,4 +192,56 @@ const char* edb200_version(void) { return "edb200 0.1 (sm_100a)"; }
 
 int64_t edb200_launch_count(void) { return edb::g_launches.load(std::memory_order_relaxed); }
 
+// ---------------------------------------------------------------- CUDA graphs
+struct edb200_graph {
+    cudaGraphExec_t exec = nullptr;
+    int64_t launches = 0;   // kernels of this library recorded in the graph
+};
+
+static thread_local int64_t g_capture_launches0 = 0;
+
+edb200_status_t edb200_graph_begin(void* stream) {
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (s == nullptr) return edb::fail(EDB200_ERR_INVALID, "graph_begin: capture needs a non-default stream");
+    if (edb::profiling_enabled()) return edb::fail(EDB200_ERR_INVALID, "graph_begin: end the profile first");
+    g_capture_launches0 = edb::g_launches.load(std::memory_order_relaxed);
+    return edb::check_cuda(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal), "cudaStreamBeginCapture");
+}
+
+edb200_status_t edb200_graph_end(void* stream, edb200_graph_t** out) {
+    if (out == nullptr) return edb::fail(EDB200_ERR_INVALID, "graph_end: null argument");
+    cudaGraph_t graph = nullptr;
+    cudaError_t e = cudaStreamEndCapture(static_cast<cudaStream_t>(stream), &graph);
+    if (e != cudaSuccess || graph == nullptr) {
+        cudaGetLastError();
+        return edb::fail(EDB200_ERR_CUDA, "graph_end: cudaStreamEndCapture: %s", cudaGetErrorString(e));
+    }
+    edb200_graph* g = new (std::nothrow) edb200_graph();
+    if (g == nullptr) {
+        cudaGraphDestroy(graph);
+        return edb::fail(EDB200_ERR_NOMEM, "graph_end: host allocation failed");
+    }
+    e = cudaGraphInstantiate(&g->exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (e != cudaSuccess) {
+        delete g;
+        return edb::check_cuda(e, "cudaGraphInstantiate");
+    }
+    g->launches = edb::g_launches.load(std::memory_order_relaxed) - g_capture_launches0;
+    *out = g;
+    return EDB200_OK;
+}
+
+edb200_status_t edb200_graph_launch(edb200_graph_t* g, void* stream) {
+    if (g == nullptr || g->exec == nullptr) return edb::fail(EDB200_ERR_INVALID, "graph_launch: null graph");
+    edb::count_launch(static_cast<int>(g->launches));
+    return edb::check_cuda(cudaGraphLaunch(g->exec, static_cast<cudaStream_t>(stream)), "cudaGraphLaunch");
+}
+
+void edb200_graph_destroy(edb200_graph_t* g) {
+    if (g == nullptr) return;
+    if (g->exec != nullptr) cudaGraphExecDestroy(g->exec);
+    delete g;
+}
+
 }  // extern "C"

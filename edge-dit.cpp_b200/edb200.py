@@ -140,6 +140,10 @@ _SIGS = {
     "edb200_sage_attention_sp": (C.c_int, [c_vp, c_vp, c_vp, C.c_int, c_i64, C.c_int, C.c_float, C.c_int, c_vp, c_i64,
                                            c_vp, C.c_int, c_i64, c_vp, c_vp]),
     "edb200_cfg_parallel_combine": (C.c_int, [c_vp, c_vp, C.c_float, c_vp, c_vp, c_i64, c_vp]),
+    "edb200_graph_begin": (C.c_int, [c_vp]),
+    "edb200_graph_end": (C.c_int, [c_vp, C.POINTER(c_vp)]),
+    "edb200_graph_launch": (C.c_int, [c_vp, c_vp]),
+    "edb200_graph_destroy": (None, [c_vp]),
     "edb200_flux_set_comm": (C.c_int, [c_vp, c_vp]),
     "edb200_row_rstd": (C.c_int, [c_vp, C.c_int, c_i64, c_i64, c_i64, C.c_float, c_vp, c_vp]),
     "edb200_qk_rownorm_rope_pack": (C.c_int, [c_vp, C.c_int, c_i64, c_i64, c_i64, c_i64, c_i64, C.c_int, C.c_int, c_vp,
@@ -575,6 +579,28 @@ class WanModel:
                                             latent.shape[3], timestep, context.ctypes.data_as(c_vp), context.shape[0],
                                             out.ctypes.data_as(c_vp), current_stream()))
         return out
+
+
+class Graph:
+    """Records what `fn()` enqueues on the current (non-default) stream and replays it."""
+
+    def __init__(self, fn):
+        check(lib().edb200_graph_begin(current_stream()))
+        try:
+            fn()
+        finally:
+            h = c_vp()
+            st = lib().edb200_graph_end(current_stream(), C.byref(h))
+        check(st)
+        self.handle = h
+
+    def launch(self):
+        check(lib().edb200_graph_launch(self.handle, current_stream()))
+
+    def __del__(self):
+        if getattr(self, "handle", None) and _lib is not None:
+            _lib.edb200_graph_destroy(self.handle)
+            self.handle = None
 
 
 PROF_CLASSES = ("gemm", "attention", "gemv", "elementwise", "other")

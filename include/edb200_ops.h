@@ -77,6 +77,20 @@ EDB200_API int64_t edb200_launch_count(void);
 EDB200_API edb200_status_t edb200_profile_begin(void);
 EDB200_API edb200_status_t edb200_profile_end(double* ms, double* flops, double* bytes, int64_t* launches);
 
+/* CUDA graphs.  Everything this library enqueues on `stream` between begin and end (for
+ * example one whole edb200_*_step with fixed buffers) is recorded instead of executed and
+ * can then be replayed with one launch: a step of several hundred small kernels stops being
+ * bound by launch overhead.  Run the sequence once normally first (the first call of a kernel
+ * sets attributes that cannot be captured), use a non-default stream, keep every buffer the
+ * sequence touches alive and in place, and do not capture the NCCL exchange path.  Counterpart
+ * of the reference's compiled-graph cache (ED_CACHE_COMPILED_GRAPHS,
+ * src/dit_models/models/flux.hpp:5243-5270). */
+typedef struct edb200_graph edb200_graph_t;
+EDB200_API edb200_status_t edb200_graph_begin(void* stream);
+EDB200_API edb200_status_t edb200_graph_end(void* stream, edb200_graph_t** out);
+EDB200_API edb200_status_t edb200_graph_launch(edb200_graph_t* g, void* stream);
+EDB200_API void edb200_graph_destroy(edb200_graph_t* g);
+
 /* ------------------------------------------------------------------ codecs
  * ggml block codecs on the device.  Stand in for ggml_quantize_chunk /
  * type_traits->to_float as called from src/core/runtime/model_loader.cpp:663-704. */

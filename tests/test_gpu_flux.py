@@ -110,3 +110,32 @@ def test_flux_rejects_unset_weights_and_bad_shapes(edb, cuda):
     assert "has not been set" in str(ei.value)
     with pytest.raises(edb.EdbError):
         edb.FluxModel(hidden_size=500, num_heads=4)    # width not a multiple of 256
+
+
+def test_flux_step_replayed_from_a_cuda_graph(edb, cuda):
+    """One step recorded with edb200_graph_begin/end and replayed gives the eager step's bits."""
+    model = edb.FluxModel(hidden_size=512, num_heads=4, depth=1, depth_single_blocks=2, context_in_dim=256, vec_in_dim=64)
+    model.init_random(seed=2, std=0.05)
+    model.prepare(32, 32, 24)
+    g = torch.Generator(device="cpu").manual_seed(3)
+    lat = torch.randn(16, 32, 32, generator=g).to(cuda)
+    ctx = torch.randn(24, 256, generator=g).to(cuda)
+    y = torch.randn(64, generator=g).to(cuda)
+    eager, replay = torch.empty_like(lat), torch.full_like(lat, float("nan"))
+    model.step(lat, 0.5, ctx, y, 3.5, eager)
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream(device=cuda)
+    with torch.cuda.stream(side):
+        model.step(lat, 0.5, ctx, y, 3.5, replay)        # warm on this stream
+        side.synchronize()
+        launches0 = edb.lib().edb200_launch_count()
+        graph = edb.Graph(lambda: model.step(lat, 0.5, ctx, y, 3.5, replay))
+        per_step = edb.lib().edb200_launch_count() - launches0
+        replay.fill_(float("nan"))
+        for _ in range(2):
+            graph.launch()
+        side.synchronize()
+        assert edb.lib().edb200_launch_count() - launches0 == 3 * per_step   # replays count their kernels
+    assert torch.equal(eager, replay)
+    with pytest.raises(edb.EdbError):
+        edb.check(edb.lib().edb200_graph_begin(None))    # the default stream cannot be captured
