@@ -18,6 +18,7 @@
 #include <cuda_fp16.h>
 
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <vector>
 
@@ -38,6 +39,15 @@ struct edb200_qwen {
     float* tap = nullptr;
     float* pinned = nullptr;
     int64_t pinned_bytes = 0;
+    // sequence-parallel execution (world > 1): this rank's slice [text rows ; image rows] of the
+    // [text ; image] sequence and the exchange buffers (see edb200_flux.cu for the scheme)
+    edb200_comm_t* comm = nullptr;
+    int rank = 0, world = 1;
+    int64_t t_loc = 0, txt_l = 0, img_l = 0, img_first = 0;
+    bool p2p = false;
+    void *QL = nullptr, *KL = nullptr, *VL = nullptr, *AOUT = nullptr, *STG = nullptr;
+    float* TOK_LOC = nullptr;
+    edb200_sp_peers_t qkv_peers, att_peers;
 };
 
 namespace {
@@ -154,6 +164,75 @@ edb200_status_t ln_mod(const float* x, int64_t H, const float* shift, const floa
     return edb200_layernorm_modulate(x, H, shift, scale, nullptr, nullptr, rows, H, 1e-6f, y, y_dtype, H, s);
 }
 
+// Row-count-tolerant two-problem GEMM: under sequence parallelism a rank may own no text rows.
+edb200_status_t mm_pair(const edb200_qweight_t* w0, const void* x0, int64_t m0, int64_t ldx0, const edb200_epilogue_t* e0,
+                        const edb200_qweight_t* w1, const void* x1, int64_t m1, int64_t ldx1, const edb200_epilogue_t* e1,
+                        cudaStream_t s) {
+    if (m0 > 0 && m1 > 0) return edb200_mul_mat_q_pair(w0, x0, m0, ldx0, e0, w1, x1, m1, ldx1, e1, EDB200_TYPE_F16, s);
+    if (m0 > 0) return edb200_mul_mat_q(w0, x0, EDB200_TYPE_F16, m0, ldx0, e0, s);
+    if (m1 > 0) return edb200_mul_mat_q(w1, x1, EDB200_TYPE_F16, m1, ldx1, e1, s);
+    return EDB200_OK;
+}
+
+edb200_status_t qk_pack(edb200_qwen* m, const __half* qkv, int64_t rows, int64_t local_first, const float* qs,
+                        const float* ks, cudaStream_t s) {
+    if (rows == 0) return EDB200_OK;
+    const edb200_qwen_config_t& c = m->cfg;
+    const int64_t H = hidden(c);
+    const int d = c.head_dim;
+    const bool sp = m->world > 1;
+    if (m->p2p) {
+        return edb200_qk_norm_rope_pack_sp(qkv, EDB200_TYPE_F16, 3 * H, 0, H, 2 * H, rows, c.num_heads, d, qs, ks, 1e-6f,
+                                           m->PE, local_first, m->t_loc * m->world, &m->qkv_peers, EDB200_TYPE_F16, s);
+    }
+    const float* pe = m->PE + (int64_t)m->rank * m->t_loc * (d / 2) * 4;   // position rows of this rank's tokens
+    return edb200_qk_norm_rope_pack(qkv, EDB200_TYPE_F16, 3 * H, 0, H, 2 * H, rows, c.num_heads, d, qs, ks, 1e-6f, pe,
+                                    local_first, m->t_loc, sp ? m->QL : m->Q, sp ? m->KL : m->K, sp ? m->VL : m->V,
+                                    EDB200_TYPE_F16, s);
+}
+
+// Joint attention over the whole sequence into the local rows of ATT (single GPU, NCCL exchange,
+// or peer-memory exchange with flag barriers; QwenImageTransformerBlock::forward_sp, qwen_image.hpp:2969-3040).
+edb200_status_t joint_attention(edb200_qwen* m, int64_t T, cudaStream_t s) {
+    const edb200_qwen_config_t& c = m->cfg;
+    const int64_t H = hidden(c);
+    const int d = c.head_dim;
+    const int heads = c.num_heads / m->world;
+    const float scale = 1.0f / std::sqrt(static_cast<float>(d));
+    const int flags = (c.sage_smooth_q ? EDB200_SAGE_SMOOTH_Q : 0) | EDB200_SAGE_FAST_MEANS;
+    const bool sage = c.attention == EDB200_ATTN_SAGE_INT8;
+    if (m->p2p) {
+        EDB_TRY(edb200_sp_barrier(m->comm, s));
+        if (sage) {
+            EDB_TRY(edb200_sage_attention_sp(m->Q, m->K, m->V, heads, T, d, scale, flags, m->SAGE, m->sage_bytes, nullptr,
+                                             EDB200_TYPE_F16, H, &m->att_peers, s));
+        } else {
+            EDB_TRY(edb200_attention_f16_sp(m->Q, m->K, m->V, heads, T, T, d, scale, nullptr, EDB200_TYPE_F16, H,
+                                            &m->att_peers, s));
+        }
+        return edb200_sp_barrier(m->comm, s);
+    }
+    void* att_out = m->ATT;
+    int64_t att_ld = H;
+    if (m->world > 1) {
+        const void* send[3] = {m->QL, m->KL, m->VL};
+        void* recv[3] = {m->Q, m->K, m->V};
+        EDB_TRY(edb200_sp_all_to_all_heads(m->comm, send, recv, 3, c.num_heads, m->t_loc, (int64_t)d * 2, s));
+        att_out = m->AOUT;
+        att_ld = (int64_t)heads * d;
+    }
+    if (sage) {
+        EDB_TRY(edb200_sage_attention(m->Q, m->K, m->V, heads, T, d, scale, flags, m->SAGE, m->sage_bytes, att_out,
+                                      EDB200_TYPE_F16, att_ld, s));
+    } else {
+        EDB_TRY(edb200_attention_f16(m->Q, m->K, m->V, heads, T, T, d, scale, att_out, EDB200_TYPE_F16, att_ld, s));
+    }
+    if (m->world > 1) {
+        EDB_TRY(edb200_sp_all_to_all_tokens(m->comm, m->AOUT, m->STG, m->ATT, m->t_loc, (int64_t)heads * d * 2, H * 2, s));
+    }
+    return EDB200_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -230,6 +309,17 @@ edb200_status_t edb200_qwen_init_random(edb200_qwen_t* m, uint64_t seed, float s
 
 int64_t edb200_qwen_weight_bytes(const edb200_qwen_t* m) { return m ? m->params.device_bytes() : 0; }
 
+edb200_status_t edb200_qwen_set_comm(edb200_qwen_t* m, edb200_comm_t* comm) {
+    if (m == nullptr) return fail(EDB200_ERR_INVALID, "qwen_set_comm: null model");
+    if (m->comm != nullptr && m->comm != comm) edb200_comm_unmap_peers(m->comm);   // collective
+    m->comm = comm;
+    m->rank = comm ? edb200_comm_rank(comm) : 0;
+    m->world = comm ? edb200_comm_world(comm) : 1;
+    m->lat_h = m->lat_w = m->n_txt = 0;   // the workspace must be prepared again
+    m->p2p = false;
+    return EDB200_OK;
+}
+
 edb200_status_t edb200_qwen_set_tap(edb200_qwen_t* m, float* tap) {
     if (m == nullptr) return fail(EDB200_ERR_INVALID, "qwen_set_tap: null model");
     m->tap = tap;
@@ -251,7 +341,15 @@ edb200_status_t edb200_qwen_prepare(edb200_qwen_t* m, int lat_h, int lat_w, int 
     const int lat_c = c.in_channels / (p * p);
     const int64_t pf_out = (int64_t)c.out_channels * p * p;
     const int64_t lat_in = (int64_t)lat_c * lat_h * lat_w, lat_out = (int64_t)c.out_channels * lat_h * lat_w;
-    const int64_t sage = c.attention == EDB200_ATTN_SAGE_INT8 ? edb200_sage_scratch_bytes(c.num_heads, T, (int)d) : 0;
+    int64_t t_loc = T, txt_l = n_txt, img_first = 0;
+    if (m->world > 1) {
+        if (c.num_heads % m->world) {
+            return fail(EDB200_ERR_UNSUPPORTED, "qwen_prepare: %d heads do not divide over %d ranks", c.num_heads, m->world);
+        }
+        EDB_TRY(edb200_sp_shard(T, n_txt, m->rank, m->world, &t_loc, &txt_l, &img_first));
+    }
+    const int64_t sage =
+        c.attention == EDB200_ATTN_SAGE_INT8 ? edb200_sage_scratch_bytes(c.num_heads / m->world, T, (int)d) : 0;
     const int64_t pe_elems = T * (d / 2) * 4;
     auto al = [](int64_t b) { return (b + 255) & ~int64_t(255); };
     int64_t total = al(T * H * 4) + al(T * H * 2) + al(T * 3 * H * 2) + 4 * al(T * H * 2) + al(T * M * 2);
@@ -259,7 +357,10 @@ edb200_status_t edb200_qwen_prepare(edb200_qwen_t* m, int lat_h, int lat_w, int 
     total += al((int64_t)n_txt * c.joint_attention_dim * 2) + al(n_txt * 4) + al(n_img * c.in_channels * 4) +
              al(n_img * pf_out * 4) + al(lat_in * 4) + al(lat_out * 4) + al((int64_t)n_txt * c.joint_attention_dim * 4) +
              al(sage) + 8192;
+    if (m->world > 1) total += 5 * al(t_loc * H * 2) + al(n_img * pf_out * 4) + 1024;
     cudaStreamSynchronize(s);
+    if (m->comm != nullptr) EDB_TRY(edb200_comm_unmap_peers(m->comm));   // collective; the old workspace goes away
+    m->p2p = false;
     EDB_TRY(m->ws.reserve(total));
     Workspace& w = m->ws;
     m->X = w.take_n<float>(T * H);
@@ -288,6 +389,43 @@ edb200_status_t edb200_qwen_prepare(edb200_qwen_t* m, int lat_h, int lat_w, int 
     if (m->CTX_IN == nullptr || (sage > 0 && m->SAGE == nullptr)) {
         return fail(EDB200_ERR_NOMEM, "qwen_prepare: workspace accounting error");
     }
+    m->QL = m->KL = m->VL = m->AOUT = m->STG = nullptr;
+    m->TOK_LOC = nullptr;
+    if (m->world > 1) {
+        void* flags = w.take(8 * 64);
+        m->QL = w.take(t_loc * H * 2);
+        m->KL = w.take(t_loc * H * 2);
+        m->VL = w.take(t_loc * H * 2);
+        m->AOUT = w.take(t_loc * H * 2);
+        m->STG = w.take(t_loc * H * 2);
+        m->TOK_LOC = w.take_n<float>(n_img * pf_out);
+        if (flags == nullptr || m->TOK_LOC == nullptr) return fail(EDB200_ERR_NOMEM, "qwen_prepare: workspace accounting error");
+        const char* how = getenv("EDB200_SP_EXCHANGE");
+        const bool want_p2p = how == nullptr || strcmp(how, "nccl") != 0;
+        edb200_status_t st = want_p2p ? edb200_comm_map_peers(m->comm, w.base(), w.capacity(),
+                                                              static_cast<char*>(flags) - static_cast<char*>(w.base()), s)
+                                      : EDB200_ERR_UNSUPPORTED;
+        if (st == EDB200_OK) {
+            m->p2p = true;
+            memset(&m->qkv_peers, 0, sizeof(m->qkv_peers));
+            memset(&m->att_peers, 0, sizeof(m->att_peers));
+            m->qkv_peers.world = m->att_peers.world = m->world;
+            m->qkv_peers.rank = m->att_peers.rank = m->rank;
+            m->qkv_peers.t_loc = m->att_peers.t_loc = t_loc;
+            for (int r = 0; r < m->world; ++r) {
+                m->qkv_peers.buf[0][r] = edb200_comm_peer_ptr(m->comm, r, m->Q);
+                m->qkv_peers.buf[1][r] = edb200_comm_peer_ptr(m->comm, r, m->K);
+                m->qkv_peers.buf[2][r] = edb200_comm_peer_ptr(m->comm, r, m->V);
+                m->att_peers.buf[0][r] = edb200_comm_peer_ptr(m->comm, r, m->ATT);
+            }
+        } else if (st != EDB200_ERR_UNSUPPORTED) {
+            return st;
+        }
+    }
+    m->t_loc = t_loc;
+    m->txt_l = txt_l;
+    m->img_l = t_loc - txt_l;
+    m->img_first = img_first;
     std::vector<float> pe = build_qwen_pe(c, h_tok, w_tok, n_txt);
     std::vector<float> freq(128);
     for (int i = 0; i < 128; ++i) freq[i] = (float)std::exp(-std::log(10000) * i / 128);
@@ -320,9 +458,11 @@ edb200_status_t edb200_qwen_step(edb200_qwen_t* m, const float* latent, float ti
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const edb200_qwen_config_t& c = m->cfg;
     const int64_t H = hidden(c), M = c.mlp_hidden;
-    const int d = c.head_dim;
     const int p = c.patch_size;
-    const int64_t n_txt = m->n_txt, n_img = m->n_img, T = n_txt + n_img;
+    const int64_t T = (int64_t)m->n_txt + m->n_img;            // whole sequence (attention length)
+    const int64_t n_txt = m->txt_l, n_img = m->img_l;          // rows this rank owns
+    const int64_t txt_first = m->world > 1 ? (int64_t)m->rank * m->t_loc : 0;
+    const bool sp = m->world > 1;
     const int lat_c = c.in_channels / (p * p);
     const int64_t pf_out = (int64_t)c.out_channels * p * p;
     const int F16 = EDB200_TYPE_F16;
@@ -337,14 +477,17 @@ edb200_status_t edb200_qwen_step(edb200_qwen_t* m, const float* latent, float ti
     launch_patchify(latent, m->TOK_IN, lat_c, m->lat_h, m->lat_w, p, s);
     {
         const Param* w = m->params.get("img_in.weight");
-        EDB_TRY(edb200_linear_f32(w->f32, fparam(m, "img_in.bias"), m->TOK_IN, n_img, c.in_channels, H, c.in_channels, 0,
-                                  EDB200_ACT_NONE, X_img, H, s));
+        if (n_img > 0) {
+            EDB_TRY(edb200_linear_f32(w->f32, fparam(m, "img_in.bias"), m->TOK_IN + m->img_first * c.in_channels, n_img,
+                                      c.in_channels, H, c.in_channels, 0, EDB200_ACT_NONE, X_img, H, s));
+        }
     }
-    EDB_TRY(edb200_row_rstd(context, EDB200_TYPE_F32, c.joint_attention_dim, n_txt, c.joint_attention_dim, 1e-6f, m->RSTD, s));
-    {
+    if (n_txt > 0) {
+        const float* ctx_l = context + txt_first * c.joint_attention_dim;
+        EDB_TRY(edb200_row_rstd(ctx_l, EDB200_TYPE_F32, c.joint_attention_dim, n_txt, c.joint_attention_dim, 1e-6f, m->RSTD, s));
         const int64_t total = n_txt * c.joint_attention_dim;
         rms_apply_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, s>>>(
-            context, m->RSTD, fparam(m, "txt_norm.weight"), static_cast<__half*>(m->CTXN), c.joint_attention_dim, total);
+            ctx_l, m->RSTD, fparam(m, "txt_norm.weight"), static_cast<__half*>(m->CTXN), c.joint_attention_dim, total);
         count_launch();
         const Lin l = qlin(m, "txt_in");
         edb200_epilogue_t ep = make_ep(X_txt, EDB200_TYPE_F32, H, l.b);
@@ -387,32 +530,20 @@ edb200_status_t edb200_qwen_step(edb200_qwen_t* m, const float* latent, float ti
                 const Lin li = qlin(m, pa + img_names[j]), lt = qlin(m, pa + txt_names[j]);
                 edb200_epilogue_t ei = make_ep(qkv + n_txt * 3 * H + j * H, F16, 3 * H, li.b);
                 edb200_epilogue_t et = make_ep(qkv + j * H, F16, 3 * H, lt.b);
-                EDB_TRY(edb200_mul_mat_q_pair(li.w, xmod + n_txt * H, n_img, H, &ei, lt.w, xmod, n_txt, H, &et, F16, s));
+                EDB_TRY(mm_pair(li.w, xmod + n_txt * H, n_img, H, &ei, lt.w, xmod, n_txt, H, &et, s));
             }
         }
-        EDB_TRY(edb200_qk_norm_rope_pack(qkv + n_txt * 3 * H, F16, 3 * H, 0, H, 2 * H, n_img, c.num_heads, d,
-                                         fparam(m, pa + "norm_q.weight"), fparam(m, pa + "norm_k.weight"), 1e-6f, m->PE,
-                                         n_txt, T, m->Q, m->K, m->V, F16, s));
-        EDB_TRY(edb200_qk_norm_rope_pack(qkv, F16, 3 * H, 0, H, 2 * H, n_txt, c.num_heads, d,
-                                         fparam(m, pa + "norm_added_q.weight"), fparam(m, pa + "norm_added_k.weight"),
-                                         1e-6f, m->PE, 0, T, m->Q, m->K, m->V, F16, s));
-        {
-            const float scale = 1.0f / std::sqrt(static_cast<float>(d));
-            if (c.attention == EDB200_ATTN_SAGE_INT8) {
-                EDB_TRY(edb200_sage_attention(m->Q, m->K, m->V, c.num_heads, T, d, scale,
-                                              (c.sage_smooth_q ? EDB200_SAGE_SMOOTH_Q : 0) | EDB200_SAGE_FAST_MEANS,
-                                              m->SAGE, m->sage_bytes, att, F16, H, s));
-            } else {
-                EDB_TRY(edb200_attention_f16(m->Q, m->K, m->V, c.num_heads, T, T, d, scale, att, F16, H, s));
-            }
-        }
+        EDB_TRY(qk_pack(m, qkv + n_txt * 3 * H, n_img, n_txt, fparam(m, pa + "norm_q.weight"),
+                        fparam(m, pa + "norm_k.weight"), s));
+        EDB_TRY(qk_pack(m, qkv, n_txt, 0, fparam(m, pa + "norm_added_q.weight"), fparam(m, pa + "norm_added_k.weight"), s));
+        EDB_TRY(joint_attention(m, T, s));
         {
             const Lin li = qlin(m, pa + "to_out.0"), lt = qlin(m, pa + "to_add_out");
             edb200_epilogue_t ei = make_ep(X_img, EDB200_TYPE_F32, H, li.b);
             ei.residual = X_img, ei.ld_res = H, ei.gate = im + 2 * H;
             edb200_epilogue_t et = make_ep(X_txt, EDB200_TYPE_F32, H, lt.b);
             et.residual = X_txt, et.ld_res = H, et.gate = tm + 2 * H;
-            EDB_TRY(edb200_mul_mat_q_pair(li.w, att + n_txt * H, n_img, H, &ei, lt.w, att, n_txt, H, &et, F16, s));
+            EDB_TRY(mm_pair(li.w, att + n_txt * H, n_img, H, &ei, lt.w, att, n_txt, H, &et, s));
         }
         EDB_TRY(ln_mod(X_img, H, im + 3 * H, im + 4 * H, n_img, xmod + n_txt * H, F16, s));
         EDB_TRY(ln_mod(X_txt, H, tm + 3 * H, tm + 4 * H, n_txt, xmod, F16, s));
@@ -422,23 +553,35 @@ edb200_status_t edb200_qwen_step(edb200_qwen_t* m, const float* latent, float ti
             ei.act = EDB200_ACT_GELU_TANH;
             edb200_epilogue_t et = make_ep(hid, F16, M, t0.b);
             et.act = EDB200_ACT_GELU_TANH;
-            EDB_TRY(edb200_mul_mat_q_pair(i0.w, xmod + n_txt * H, n_img, H, &ei, t0.w, xmod, n_txt, H, &et, F16, s));
+            EDB_TRY(mm_pair(i0.w, xmod + n_txt * H, n_img, H, &ei, t0.w, xmod, n_txt, H, &et, s));
             const Lin i2 = qlin(m, pb + "img_mlp.net.2"), t2 = qlin(m, pb + "txt_mlp.net.2");
             edb200_epilogue_t fi = make_ep(X_img, EDB200_TYPE_F32, H, i2.b);
             fi.residual = X_img, fi.ld_res = H, fi.gate = im + 5 * H;
             edb200_epilogue_t ft = make_ep(X_txt, EDB200_TYPE_F32, H, t2.b);
             ft.residual = X_txt, ft.ld_res = H, ft.gate = tm + 5 * H;
-            EDB_TRY(edb200_mul_mat_q_pair(i2.w, hid + n_txt * M, n_img, M, &fi, t2.w, hid, n_txt, M, &ft, F16, s));
+            EDB_TRY(mm_pair(i2.w, hid + n_txt * M, n_img, M, &fi, t2.w, hid, n_txt, M, &ft, s));
         }
-        if (m->tap) cudaMemcpyAsync(m->tap + (int64_t)i * T * H, m->X, T * H * 4, cudaMemcpyDeviceToDevice, s);
+        if (m->tap) {
+            cudaMemcpyAsync(m->tap + (int64_t)i * m->t_loc * H, m->X, m->t_loc * H * 4, cudaMemcpyDeviceToDevice, s);
+        }
     }
 
     // ---- norm_out: (scale, shift) order (AdaLayerNormContinuous, qwen_image.hpp:3062-3068), proj_out, unpatchify
     EDB_TRY(ln_mod(X_img, H, fmods + H, fmods, n_img, xmod, F16, s));
-    {
+    if (n_img > 0) {
         const Lin lf = qlin(m, "proj_out");
-        edb200_epilogue_t ep = make_ep(m->TOK_OUT, EDB200_TYPE_F32, pf_out, lf.b);
+        edb200_epilogue_t ep = make_ep(sp ? m->TOK_LOC : m->TOK_OUT, EDB200_TYPE_F32, pf_out, lf.b);
         EDB_TRY(edb200_mul_mat_q(lf.w, xmod, F16, n_img, H, &ep, s));
+    }
+    if (sp) {
+        std::vector<int64_t> first(m->world), count(m->world);
+        for (int r = 0; r < m->world; ++r) {
+            int64_t tl = 0, tx = 0, f = 0;
+            EDB_TRY(edb200_sp_shard(T, m->n_txt, r, m->world, &tl, &tx, &f));
+            first[r] = f;
+            count[r] = tl - tx;
+        }
+        EDB_TRY(edb200_sp_all_gather_rows(m->comm, m->TOK_LOC, m->TOK_OUT, first.data(), count.data(), pf_out * 4, s));
     }
     launch_unpatchify(m->TOK_OUT, out, c.out_channels, m->lat_h, m->lat_w, p, s);
     return check_cuda(cudaGetLastError(), "qwen_step");

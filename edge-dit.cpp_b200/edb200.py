@@ -159,6 +159,7 @@ _SIGS = {
     "edb200_qwen_weight_bytes": (c_i64, [c_vp]),
     "edb200_qwen_prepare": (C.c_int, [c_vp, C.c_int, C.c_int, C.c_int, c_vp]),
     "edb200_qwen_set_tap": (C.c_int, [c_vp, c_vp]),
+    "edb200_qwen_set_comm": (C.c_int, [c_vp, c_vp]),
     "edb200_qwen_step": (C.c_int, [c_vp, c_vp, C.c_float, c_vp, c_vp, c_vp]),
     "edb200_qwen_compute_host": (C.c_int, [c_vp, c_vp, C.c_int, C.c_int, C.c_float, c_vp, C.c_int, c_vp, c_vp]),
     "edb200_sd3_create": (C.c_int, [C.POINTER(SD3Config), C.POINTER(c_vp)]),
@@ -437,6 +438,10 @@ class QwenModel:
 
     def init_random(self, seed=0, std=0.02):
         check(lib().edb200_qwen_init_random(self.handle, seed, std, current_stream()))
+
+    def set_comm(self, comm):
+        self._comm = comm
+        check(lib().edb200_qwen_set_comm(self.handle, comm.handle if comm is not None else None))
 
     def set_tap(self, tap):
         self._tap = tap

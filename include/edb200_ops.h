@@ -538,6 +538,8 @@ EDB200_API int64_t edb200_qwen_weight_bytes(const edb200_qwen_t* m);
 EDB200_API edb200_status_t edb200_qwen_prepare(edb200_qwen_t* m, int lat_h, int lat_w, int n_txt, void* stream);
 /* Optional f32 tap [num_layers, n_txt + image tokens, hidden]: both streams after every block. */
 EDB200_API edb200_status_t edb200_qwen_set_tap(edb200_qwen_t* m, float* tap);
+/* Sequence parallel over `comm` (QwenImageTransformerBlock::forward_sp, qwen_image.hpp:2969-3040): before prepare. */
+EDB200_API edb200_status_t edb200_qwen_set_comm(edb200_qwen_t* m, edb200_comm_t* comm);
 /* latent f32 [in_channels / patch^2, lat_h, lat_w], context f32 [n_txt, joint_attention_dim]. */
 EDB200_API edb200_status_t edb200_qwen_step(edb200_qwen_t* m, const float* latent, float timestep, const float* context,
                                             float* out, void* stream);

@@ -194,3 +194,62 @@ def test_cfg_parallel_combine_on_two_gpus(edb, cuda):
         p.join(300)
         assert p.exitcode == 0
     assert ret[0] and ret[1]
+
+
+def _qwen_worker(rank, world, port, lib_dir, exchange, ret):
+    import importlib.util
+    import torch.distributed as dist
+    os.environ["EDB200_SP_EXCHANGE"] = exchange
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    spec = importlib.util.spec_from_file_location("edb200", os.path.join(lib_dir, "edb200.py"))
+    edb = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(edb)
+    dev = torch.device("cuda", rank)
+    model = edb.QwenModel(num_layers=2, num_heads=4, joint_attention_dim=256)
+    model.init_random(seed=13, std=0.05)
+    g = torch.Generator(device="cpu").manual_seed(14)
+    latent = torch.randn(16, 24, 24, generator=g).to(dev)        # 144 image tokens + 16 text tokens = 160
+    ctx = torch.randn(16, 256, generator=g).to(dev)
+    ref = torch.empty_like(latent)
+    model.prepare(24, 24, 16)
+    model.step(latent, 500.0, ctx, ref)
+    torch.cuda.synchronize()
+    comm = edb.Comm()
+    model.set_comm(comm)
+    model.prepare(24, 24, 16)
+    out = torch.empty_like(latent)
+    for _ in range(2):
+        out.fill_(float("nan"))
+        model.step(latent, 500.0, ctx, out)
+        torch.cuda.synchronize()
+    a, b = out.cpu().numpy(), ref.cpu().numpy()
+    ret[rank] = (bool(np.isfinite(a).all()), float(np.linalg.norm(a - b) / np.linalg.norm(b)))
+    dist.barrier()
+    model.set_comm(None)
+    comm.close()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("exchange", ["peer", "nccl"])
+def test_qwen_pass_sequence_parallel_matches_single_gpu(edb, cuda, world, exchange):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    lib_dir = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "edge-dit.cpp_b200")
+    port = _free_port()
+    procs = [ctx.Process(target=_qwen_worker, args=(r, world, port, lib_dir, exchange, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+        assert p.exitcode == 0
+    for r in range(world):
+        finite, err = ret[r]
+        assert finite
+        assert err <= 1e-5, (r, err)
