@@ -356,7 +356,7 @@ def run_ours(args):
     if world > 1:
         # Ulysses sequence parallelism: every rank holds all weights, 1/N of the tokens for the
         # per-token work and 1/N of the heads for attention (NCCL exchange inside the library)
-        if case.family in ("sd3", "qwen"):
+        if case.family == "sd3":
             raise SystemExit(f"bench.py: workload {args.workload} has no sequence-parallel path; use --gpus 1")
         comm = edb.Comm()
         model.set_comm(comm)
