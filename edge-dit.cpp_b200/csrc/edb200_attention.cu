@@ -35,6 +35,8 @@
 #include "edb200_internal.h"
 #include "edb200_ptx.cuh"
 
+#include <cstdlib>
+
 namespace edb {
 namespace attn {
 
@@ -66,6 +68,7 @@ struct Params {
     void* out_peer[8];
     int t_loc;
     int one;   // always 1: an operand the compiler cannot fold (see magic_i2f_biased)
+    int qt;    // query tiles this launch gives every CTA: 2, or 1 when two would leave SMs without a CTA
 };
 
 template <int D, bool SAGE>
@@ -272,7 +275,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int q0 = blockIdx.x * (QT * BQ);
+    const int q0 = blockIdx.x * (P.qt * BQ);
     const int hn = blockIdx.y;
     const int n_kv = (P.Lk + BKV - 1) / BKV;
 
@@ -280,9 +283,9 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         mbar_init(q_full, 1);
         for (int i = 0; i < KV_STAGES; ++i) {
             mbar_init(&k_full[i], 1);
-            mbar_init(&k_empty[i], QT);
+            mbar_init(&k_empty[i], P.qt);
             mbar_init(&v_full[i], 1);
-            mbar_init(&v_empty[i], QT);
+            mbar_init(&v_empty[i], P.qt);
         }
         for (int i = 0; i < QT; ++i) {
             for (int b = 0; b < 2; ++b) {
@@ -312,9 +315,8 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     if (warp == 0) {
         // ------------------------------------------------------ TMA producer
         if (elect_one()) {
-            mbar_arrive_expect_tx(q_full, QT * C::Q_BYTES);
-#pragma unroll
-            for (int t = 0; t < QT; ++t) {
+            mbar_arrive_expect_tx(q_full, P.qt * C::Q_BYTES);
+            for (int t = 0; t < P.qt; ++t) {
 #pragma unroll
                 for (int p = 0; p < C::QK_PANELS; ++p) {
                     tma_load_3d(smem + C::OFF_Q + t * C::Q_BYTES + p * C::QK_PANEL_BYTES, &map_q, q_full,
@@ -348,7 +350,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 }
             }
         }
-    } else if (warp == 1 || warp == 3) {
+    } else if (warp == 1 || (warp == 3 && P.qt == 2)) {
         // ------------------------------------------- MMA issuers, one per query tile
         // (one thread cannot issue the small products of both tiles fast enough)
         const int t = warp >> 1;
@@ -418,7 +420,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             ok = issue_pv(g);
             if (ok && g + 2 < n_half) ok = issue_qk(g + 2);
         }
-    } else if (warp >= 4) {
+    } else if (warp >= 4 && warp < 4 + 4 * P.qt) {
         // ------------------------------------------------------------ softmax
         const int t = (warp - 4) >> 2;              // query tile
         const int quarter = warp & 3;
@@ -594,8 +596,24 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 }
 
 template <int D, bool SAGE>
-static edb200_status_t launch(const void* q, const void* k, const void* v, const Params& P, cudaStream_t stream) {
+static edb200_status_t launch(const void* q, const void* k, const void* v, const Params& P_in, cudaStream_t stream) {
     using C = Cfg<D, SAGE>;
+    Params P = P_in;
+    // Two query tiles per CTA share K/V and overlap softmax with the tensor pipe; when that leaves SMs
+    // without a CTA (few heads per rank under sequence parallelism) one tile per CTA fills the GPU better.
+    // One CTA fits per SM (it holds all of tensor memory), so the kernel runs in waves; a two-tile CTA
+    // takes about 1.5x as long as a one-tile CTA.
+    {
+        const int64_t sms = sm_count();
+        const int64_t w2 = (((P.Lq + QT * BQ - 1) / (QT * BQ)) * P.HN + sms - 1) / sms;
+        const int64_t w1 = (((P.Lq + BQ - 1) / BQ) * P.HN + sms - 1) / sms;
+        P.qt = (P.Lq > BQ && 2 * w1 < 3 * w2) ? 1 : QT;
+    }
+    if (const char* e = getenv("EDB200_ATTN_QT")) {   // tuning and tests: force one of the two schedules
+        if (e[0] == '1') P.qt = 1;
+        if (e[0] == '2') P.qt = QT;
+    }
+
     CUtensorMap mq, mk, mv;
     const CUtensorMapDataType qk_dt = SAGE ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     const int es = C::QK_ELEM;
@@ -616,7 +634,7 @@ static edb200_status_t launch(const void* q, const void* k, const void* v, const
         if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(attention)");
         attr_set = true;
     }
-    dim3 grid((P.Lq + QT * BQ - 1) / (QT * BQ), P.HN);
+    dim3 grid((P.Lq + P.qt * BQ - 1) / (P.qt * BQ), P.HN);
     ProfScope prof(stream, PROF_ATTENTION, 4.0 * (double)P.Lq * (double)P.Lk * D * P.HN,
                    (double)P.HN * D * ((double)P.Lq * (C::QK_ELEM + 2) + (double)P.Lk * (C::QK_ELEM + 2)));
     kern<<<grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(mq, mk, mv, P);

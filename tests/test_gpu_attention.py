@@ -11,6 +11,13 @@ pytestmark = pytest.mark.gpu
 torch = pytest.importorskip("torch")
 
 
+@pytest.fixture(autouse=True, params=["1", "2"], ids=["one_tile_per_cta", "two_tiles_per_cta"])
+def _schedule(request, monkeypatch):
+    # the launcher picks one or two 128-query tiles per CTA from the grid size; the small
+    # shapes here would only reach one of them, so every test runs under both
+    monkeypatch.setenv("EDB200_ATTN_QT", request.param)
+
+
 def _qkv(hn, lq, lk, d, seed, mean_shift=0.0):
     rng = np.random.default_rng(seed)
     q = rng.standard_normal((hn, lq, d), dtype=np.float32)
