@@ -166,7 +166,7 @@ __device__ __forceinline__ uint32_t h2_sub_fma(uint32_t packed, __half2 bias, __
     return *reinterpret_cast<uint32_t*>(&h);
 }
 
-// q8_0 tile record: payload [c][r][16 int8], scales [h][r] f16.  Thread (row r,
+// q8_0 tile record: payload [c][r][16 bytes u = q + 128], scales [h][r] f16.  Thread (row r,
 // half h) converts weights h*32 .. h*32+31 of its row into 16 packed f16 pairs.
 __device__ __forceinline__ void dequant_q8_0(const uint8_t* tile, int r, int h, uint32_t (&o)[16]) {
     const __half2 k1152 = __float2half2_rn(1152.0f);
@@ -177,7 +177,7 @@ __device__ __forceinline__ void dequant_q8_0(const uint8_t* tile, int r, int h, 
         const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            const uint32_t x = w[j] ^ 0x80808080u;                       // q + 128 in each byte
+            const uint32_t x = w[j];                                      // bytes hold u = q + 128
             const uint32_t lo = __byte_perm(x, 0x64646464u, 0x4140);      // f16 (1024 + u0, 1024 + u1)
             const uint32_t hi = __byte_perm(x, 0x64646464u, 0x4342);
             o[cc * 8 + 2 * j + 0] = h2_sub_mul(lo, k1152, d2);

@@ -74,7 +74,7 @@ struct ProfScope {
 // The weight [n_out][k] is cut into tiles of kQwTileRows rows x kQwTileK weights.
 // Tile (t, s) = rows t*128.., weights s*64.. is one contiguous record of
 // `tile_bytes` at tiles + (t * ksteps + s) * tile_bytes, fetched with one bulk copy:
-//   q8_0 (8704 B): payload [c = 0..3][r = 0..127][16 int8]  = weights s*64 + c*16 + i of row r
+//   q8_0 (8704 B): payload [c = 0..3][r = 0..127][16 bytes q + 128] = weights s*64 + c*16 + i of row r
 //                  scales  [h = 0..1][r] f16                 = d of 32-block 2s + h
 //   q4_K (5120 B): payload [c = 0..1][r][16 B], byte c*16+i = weight s*64+c*16+i (low nibble)
 //                  | weight s*64+32+c*16+i (high nibble): ggml's own nibble order

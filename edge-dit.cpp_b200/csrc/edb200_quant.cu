@@ -175,6 +175,92 @@ sgemm_nt_kernel(const float* __restrict__ w, const float* __restrict__ bias, con
     }
 }
 
+
+__device__ __forceinline__ float apply_act(float v, int act) {
+    if (act == EDB200_ACT_SILU) v = v / (1.0f + __expf(-v));
+    if (act == EDB200_ACT_GELU_ERF) v = 0.5f * v * (1.0f + erff(v * 0.70710678118654752f));
+    if (act == EDB200_ACT_GELU_TANH) v = 0.5f * v * (1.0f + tanhf(0.7978845608028654f * v * (1.0f + 0.044715f * v * v)));
+    return v;
+}
+
+// Register-tiled variant for aligned shapes (k % 16 == 0, 16-byte aligned rows): 64 tokens x
+// 128 outputs per CTA, 4 x 8 outputs per thread, 16-k slabs double-buffered in shared memory
+// with the next slab's global loads in flight during the multiply.  Every output is one
+// accumulator summed over k in ascending order, like the simple kernel above.
+constexpr int SG_BM = 64, SG_BN = 128, SG_BK = 16;
+
+__global__ void __launch_bounds__(256)
+sgemm_nt_tiled_kernel(const float* __restrict__ w, const float* __restrict__ bias, const float* __restrict__ x,
+                      int64_t ldx, int act, float* __restrict__ y, int64_t ldy, int m, int n_out, int k) {
+    __shared__ __align__(16) float xs[2][SG_BK][SG_BM + 4];
+    __shared__ __align__(16) float ws[2][SG_BK][SG_BN + 4];
+    const int tid = threadIdx.x;
+    const int tx = tid & 15, ty = tid >> 4;
+    const int m0 = blockIdx.y * SG_BM, n0 = blockIdx.x * SG_BN;
+    const int lr = tid >> 2, lq = (tid & 3) * 4;   // loader: row of the tile, first of its 4 k
+    const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float* xrow = (m0 + lr < m) ? x + (int64_t)(m0 + lr) * ldx + lq : nullptr;
+    const float* wrow0 = (n0 + lr < n_out) ? w + (int64_t)(n0 + lr) * k + lq : nullptr;
+    const float* wrow1 = (n0 + 64 + lr < n_out) ? w + (int64_t)(n0 + 64 + lr) * k + lq : nullptr;
+
+    float acc[4][8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = 0.0f;
+
+    float4 gx = xrow ? *reinterpret_cast<const float4*>(xrow) : zero;
+    float4 gw0 = wrow0 ? __ldg(reinterpret_cast<const float4*>(wrow0)) : zero;
+    float4 gw1 = wrow1 ? __ldg(reinterpret_cast<const float4*>(wrow1)) : zero;
+    int buf = 0;
+    for (int k0 = 0; k0 < k; k0 += SG_BK) {
+        xs[buf][lq + 0][lr] = gx.x;
+        xs[buf][lq + 1][lr] = gx.y;
+        xs[buf][lq + 2][lr] = gx.z;
+        xs[buf][lq + 3][lr] = gx.w;
+        ws[buf][lq + 0][lr] = gw0.x;
+        ws[buf][lq + 1][lr] = gw0.y;
+        ws[buf][lq + 2][lr] = gw0.z;
+        ws[buf][lq + 3][lr] = gw0.w;
+        ws[buf][lq + 0][64 + lr] = gw1.x;
+        ws[buf][lq + 1][64 + lr] = gw1.y;
+        ws[buf][lq + 2][64 + lr] = gw1.z;
+        ws[buf][lq + 3][64 + lr] = gw1.w;
+        __syncthreads();
+        if (k0 + SG_BK < k) {
+            gx = xrow ? *reinterpret_cast<const float4*>(xrow + k0 + SG_BK) : zero;
+            gw0 = wrow0 ? __ldg(reinterpret_cast<const float4*>(wrow0 + k0 + SG_BK)) : zero;
+            gw1 = wrow1 ? __ldg(reinterpret_cast<const float4*>(wrow1 + k0 + SG_BK)) : zero;
+        }
+#pragma unroll
+        for (int c = 0; c < SG_BK; ++c) {
+            const float4 a4 = *reinterpret_cast<const float4*>(&xs[buf][c][ty * 4]);
+            const float4 b0 = *reinterpret_cast<const float4*>(&ws[buf][c][tx * 4]);
+            const float4 b1 = *reinterpret_cast<const float4*>(&ws[buf][c][64 + tx * 4]);
+            const float a[4] = {a4.x, a4.y, a4.z, a4.w};
+            const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        buf ^= 1;   // the other buffer was last read before the barrier above
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int mm = m0 + ty * 4 + i;
+        if (mm >= m) continue;
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int nn = n0 + hh * 64 + tx * 4 + j;
+                if (nn < n_out) y[(int64_t)mm * ldy + nn] = apply_act(acc[i][hh * 4 + j] + (bias ? bias[nn] : 0.0f), act);
+            }
+        }
+    }
+}
+
 }  // namespace edb
 
 using namespace edb;
@@ -252,8 +338,15 @@ edb200_status_t edb200_linear_f32(const float* w, const float* bias, const float
 #undef EDB_GEMVF_CASE
     } else {
         if (pre_silu) return fail(EDB200_ERR_UNSUPPORTED, "linear_f32: pre_silu only for m <= 8");
-        dim3 grid(static_cast<unsigned>((n + 63) / 64), static_cast<unsigned>((m + 63) / 64));
-        sgemm_nt_kernel<<<grid, 256, 0, s>>>(w, bias, x, ldx, act, y, ldy, (int)m, (int)n, (int)k);
+        const bool aligned = (k % SG_BK) == 0 && (ldx % 4) == 0 && ((reinterpret_cast<uintptr_t>(w) |
+                                                                       reinterpret_cast<uintptr_t>(x)) & 15u) == 0;
+        if (aligned) {
+            dim3 grid(static_cast<unsigned>((n + SG_BN - 1) / SG_BN), static_cast<unsigned>((m + SG_BM - 1) / SG_BM));
+            sgemm_nt_tiled_kernel<<<grid, 256, 0, s>>>(w, bias, x, ldx, act, y, ldy, (int)m, (int)n, (int)k);
+        } else {
+            dim3 grid(static_cast<unsigned>((n + 63) / 64), static_cast<unsigned>((m + 63) / 64));
+            sgemm_nt_kernel<<<grid, 256, 0, s>>>(w, bias, x, ldx, act, y, ldy, (int)m, (int)n, (int)k);
+        }
     }
     count_launch();
     return check_cuda(cudaGetLastError(), "linear_f32 launch");

@@ -23,7 +23,10 @@ __global__ void repack_q8_0_kernel(const uint8_t* __restrict__ blocks, uint8_t* 
     for (int i = 0; i < 17; ++i) w[i] = p[i];
     uint32_t o[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) o[i] = static_cast<uint32_t>(w[1 + 2 * i]) | (static_cast<uint32_t>(w[2 + 2 * i]) << 16);
+    for (int i = 0; i < 8; ++i) {
+        // stored as u = q + 128 (sign bit flipped): the consumers build floats from the unsigned byte
+        o[i] = (static_cast<uint32_t>(w[1 + 2 * i]) | (static_cast<uint32_t>(w[2 + 2 * i]) << 16)) ^ 0x80808080u;
+    }
     const int64_t t = n / kQwTileRows;
     const int r = static_cast<int>(n % kQwTileRows);
     const int64_t s = b >> 1;
@@ -74,7 +77,7 @@ __global__ void qweight_dequant_q8_0_kernel(const uint8_t* __restrict__ tiles, f
     const int64_t n = idx / k, kk = idx % k;
     const uint8_t* tile = tiles + ((n / kQwTileRows) * ksteps + (kk >> 6)) * kQwTileBytesQ8;
     const int r = static_cast<int>(n % kQwTileRows), e = static_cast<int>(kk & 63);
-    const int8_t q = static_cast<int8_t>(tile[((e >> 4) * 128 + r) * 16 + (e & 15)]);
+    const int q = static_cast<int>(tile[((e >> 4) * 128 + r) * 16 + (e & 15)]) - 128;
     const __half d = *reinterpret_cast<const __half*>(tile + 8192 + ((e >> 5) * 128 + r) * 2);
     out[idx] = __fmul_rn(static_cast<float>(q), __half2float(d));
 }
@@ -114,9 +117,9 @@ __device__ __forceinline__ float dot16_s8(const uint4& raw, const float* xp) {
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
         const float4 xv = *reinterpret_cast<const float4*>(xp + 4 * j);
-        // int8 -> f32 without conversion instructions: byte u = q + 128 placed in the
-        // mantissa of 2^23 gives 8388608 + u exactly; subtract 8388736 to get q.
-        const uint32_t u = w[j] ^ 0x80808080u;
+        // int8 -> f32 without conversion instructions: the stored byte u = q + 128 placed in
+        // the mantissa of 2^23 gives 8388608 + u exactly; subtract 8388736 to get q.
+        const uint32_t u = w[j];
         const float q0 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7650)) - 8388736.0f;
         const float q1 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7651)) - 8388736.0f;
         const float q2 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7652)) - 8388736.0f;

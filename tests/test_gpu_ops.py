@@ -185,7 +185,10 @@ def test_gemv_q(edb, cuda, wtype, m):
     assert O.rel_l2(y.cpu().numpy(), ref) < (2e-3 if wtype == "q4_k" else 1e-5)
 
 
-@pytest.mark.parametrize("m,k,n,act", [(1, 256, 3072, 2), (300, 64, 200, 0), (70, 4096, 128, 1)])
+@pytest.mark.parametrize("m,k,n,act", [(1, 256, 3072, 2), (300, 64, 200, 0), (70, 4096, 128, 1),
+                                         (512, 4096, 3072, 0),   # FLUX txt_in: tiled kernel, full tiles
+                                         (130, 48, 64, 0),       # ragged m, one partial n tile
+                                         (77, 24, 200, 3)])      # k not a multiple of 16: simple kernel
 def test_linear_f32(edb, cuda, m, k, n, act):
     rng = np.random.default_rng(10)
     w = rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.05)
@@ -195,7 +198,8 @@ def test_linear_f32(edb, cuda, m, k, n, act):
     edb.check(edb.lib().edb200_linear_f32(edb.ptr(dev(w, cuda)), edb.ptr(dev(b, cuda)), edb.ptr(dev(x, cuda)), m, k,
                                           n, k, 0, act, edb.ptr(y), n, edb.current_stream()))
     ref = O.linear(x, w, b)
-    ref = {0: lambda v: v, 1: O.gelu_tanh, 2: O.silu}[act](ref)
+    from oracle.wan_oracle import gelu_erf
+    ref = {0: lambda v: v, 1: O.gelu_tanh, 2: O.silu, 3: gelu_erf}[act](ref)
     assert O.rel_l2(y.cpu().numpy(), ref) < 1e-5
 
 
