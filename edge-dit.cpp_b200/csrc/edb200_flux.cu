@@ -492,6 +492,10 @@ edb200_status_t edb200_flux_step(edb200_flux_t* m, const float* latent, float ti
     // rows this rank owns: all of them on one GPU, a slice [text rows ; image rows] otherwise
     const int64_t n_txt = m->txt_l, n_img = m->img_l, TL = m->t_loc;
     const int64_t txt_first = m->world > 1 ? (int64_t)m->rank * TL : 0;   // first owned text row (if any)
+    // A sequence-parallel rank's out-projections have few output tiles and long reductions: let
+    // them be cut along k (their adds into the residual stream are then unordered).  A single
+    // GPU keeps every sum in one fixed order.
+    const int split_k = m->world > 1 ? EDB200_SPLIT_K_UNORDERED : EDB200_SPLIT_K_NEVER;
     const int lat_c = c.in_channels / (c.patch_size * c.patch_size);
     const int F16 = EDB200_TYPE_F16;
     float* X_txt = m->X;
@@ -562,9 +566,9 @@ edb200_status_t edb200_flux_step(edb200_flux_t* m, const float* latent, float ti
         {
             const Lin li = qlin(m, p + "img_attn.proj"), lt = qlin(m, p + "txt_attn.proj");
             edb200_epilogue_t ei = make_ep(X_img, EDB200_TYPE_F32, H, li.b);
-            ei.residual = X_img, ei.ld_res = H, ei.gate = im + 2 * H;
+            ei.residual = X_img, ei.ld_res = H, ei.gate = im + 2 * H, ei.split_k = split_k;
             edb200_epilogue_t et = make_ep(X_txt, EDB200_TYPE_F32, H, lt.b);
-            et.residual = X_txt, et.ld_res = H, et.gate = tm + 2 * H;
+            et.residual = X_txt, et.ld_res = H, et.gate = tm + 2 * H, et.split_k = split_k;
             EDB_TRY(mm_pair(li.w, cat + n_txt * (H + M), n_img, H + M, &ei, lt.w, cat, n_txt, H + M, &et, s));
         }
         EDB_TRY(ln_mod(X_img, H, im + 3 * H, im + 4 * H, n_img, xmod + n_txt * H, F16, s));
@@ -580,9 +584,9 @@ edb200_status_t edb200_flux_step(edb200_flux_t* m, const float* latent, float ti
         {
             const Lin li = qlin(m, p + "img_mlp.2"), lt = qlin(m, p + "txt_mlp.2");
             edb200_epilogue_t ei = make_ep(X_img, EDB200_TYPE_F32, H, li.b);
-            ei.residual = X_img, ei.ld_res = H, ei.gate = im + 5 * H;
+            ei.residual = X_img, ei.ld_res = H, ei.gate = im + 5 * H, ei.split_k = split_k;
             edb200_epilogue_t et = make_ep(X_txt, EDB200_TYPE_F32, H, lt.b);
-            et.residual = X_txt, et.ld_res = H, et.gate = tm + 5 * H;
+            et.residual = X_txt, et.ld_res = H, et.gate = tm + 5 * H, et.split_k = split_k;
             EDB_TRY(mm_pair(li.w, hid + n_txt * M, n_img, M, &ei, lt.w, hid, n_txt, M, &et, s));
         }
         if (m->tap) {
@@ -610,7 +614,7 @@ edb200_status_t edb200_flux_step(edb200_flux_t* m, const float* latent, float ti
         {
             const Lin l2 = qlin(m, p + "linear2");
             edb200_epilogue_t ep = make_ep(m->X, EDB200_TYPE_F32, H, l2.b);
-            ep.residual = m->X, ep.ld_res = H, ep.gate = sm + 2 * H;
+            ep.residual = m->X, ep.ld_res = H, ep.gate = sm + 2 * H, ep.split_k = split_k;
             EDB_TRY(edb200_mul_mat_q(l2.w, cat, F16, TL, H + M, &ep, s));
         }
         if (m->tap) {

@@ -63,6 +63,7 @@ struct Problem {
     int M, N, K;
     int m_tiles, n_tiles;
     int chunk;   // token tiles per L2-resident activation chunk (tile order below)
+    int ksplit;  // parts the reduction is cut into (1: whole k per tile); parts add into `out` atomically
 };
 
 struct Params {
@@ -74,13 +75,17 @@ struct Params {
 
 struct TileCoord {
     int prob, m0, n_tile;   // n_tile = first of the WH consecutive weight tiles
+    int kpart;              // which part of the reduction (0 .. ksplit-1)
 };
 
 __device__ __forceinline__ TileCoord tile_coord(const Params& P, int t, int wh) {
     TileCoord c;
     c.prob = (t >= P.tiles0) ? 1 : 0;
-    const int tt = c.prob ? t - P.tiles0 : t;
+    int tt = c.prob ? t - P.tiles0 : t;
     const Problem& pr = c.prob ? P.p[1] : P.p[0];
+    const int mn_tiles = pr.m_tiles * pr.n_tiles;
+    c.kpart = tt / mn_tiles;   // reduction part outermost: 0 for unsplit problems
+    tt -= c.kpart * mn_tiles;
     // Order: activation chunk (pr.chunk token tiles, sized to stay in L2) > weight tile row > token
     // tile.  CTAs running at the same time share one weight tile row through L2, and all weight
     // rows pass over a chunk before the next chunk is touched, so neither operand is re-read
@@ -113,7 +118,22 @@ __device__ __forceinline__ float apply_act(float v, int act) {
 
 // EC tokens (m_first..) of one output feature n; lanes of a warp hold
 // consecutive n, so every global access below is contiguous across the warp.
-__device__ __forceinline__ void epilogue_store(const Problem& P, float (&v)[EC], int n, int m_first, bool n_ok) {
+__device__ __forceinline__ void epilogue_store(const Problem& P, float (&v)[EC], int n, int m_first, bool n_ok,
+                                               int kpart) {
+    if (P.ksplit > 1) {
+        // Split reduction (host guarantees: gated residual in place, f32, no activation):
+        // out += gate * (partial + bias once).  The parts of one output add in any order.
+        if (!n_ok) return;
+        const float b = (P.bias != nullptr && kpart == 0) ? __ldg(P.bias + n) : 0.0f;
+        const float g = __ldg(P.gate + n);
+        const int rows = min(EC, P.M - m_first);
+        float* o = reinterpret_cast<float*>(P.out) + (long long)m_first * P.ldo + n;
+#pragma unroll
+        for (int i = 0; i < EC; ++i) {
+            if (i < rows) atomicAdd(o + (long long)i * P.ldo, g * (v[i] + b));
+        }
+        return;
+    }
     const bool second = (P.split_n > 0) && (n >= P.split_n);
     const int act = second ? P.act2 : P.act;
     const float b = (P.bias != nullptr && n_ok) ? __ldg(P.bias + n) : 0.0f;
@@ -276,10 +296,12 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x0, const __grid_constant__
         for (int t = blockIdx.x; ok && t < P.total_tiles; t += gridDim.x) {
             const TileCoord tc = tile_coord(P, t, WH);
             const Problem& pr = tc.prob ? P.p[1] : P.p[0];
-            const int ksteps = pr.K / BK;
+            const int ksteps_all = pr.K / BK;
+            const int k_first = tc.kpart * (ksteps_all / pr.ksplit);
+            const int k_last = k_first + ksteps_all / pr.ksplit;
             const CUtensorMap* mx = tc.prob ? &map_x1 : &map_x0;
-            const uint8_t* wsrc = pr.tiles + (long long)tc.n_tile * ksteps * kWBytes;
-            for (int ks = 0; ks < ksteps; ++ks) {
+            const uint8_t* wsrc = pr.tiles + (long long)tc.n_tile * ksteps_all * kWBytes;
+            for (int ks = k_first; ks < k_last; ++ks) {
                 if (!mbar_wait(&ld_empty[s], ph ^ 1u, abort_flag, P.err)) {
                     ok = false;
                     break;
@@ -291,7 +313,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x0, const __grid_constant__
 #pragma unroll
                     for (int hw = 0; hw < WH; ++hw) {
                         bulk_load_1d(stage + X_BYTES + hw * W_BYTES_MAX,
-                                  wsrc + ((long long)hw * ksteps + ks) * kWBytes, kWBytes, &ld_full[s]);
+                                  wsrc + ((long long)hw * ksteps_all + ks) * kWBytes, kWBytes, &ld_full[s]);
                     }
                 }
                 __syncwarp();
@@ -310,7 +332,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x0, const __grid_constant__
         bool ok = true;
         for (int t = blockIdx.x; ok && t < P.total_tiles; t += gridDim.x) {
             const TileCoord tc = tile_coord(P, t, WH);
-            const int ksteps = (tc.prob ? P.p[1].K : P.p[0].K) / BK;
+            const int ksteps = (tc.prob ? P.p[1].K / P.p[1].ksplit : P.p[0].K / P.p[0].ksplit) / BK;
             if (!mbar_wait(&acc_empty[cs], cph ^ 1u, abort_flag, P.err)) {
                 ok = false;
                 break;
@@ -395,7 +417,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x0, const __grid_constant__
                     float v[EC];
 #pragma unroll
                     for (int j = 0; j < EC; ++j) v[j] = __uint_as_float(r[j]);
-                    epilogue_store(pr, v, n, m_first, n_ok);
+                    epilogue_store(pr, v, n, m_first, n_ok, tc.kpart);
                 }
             }
             tc_fence_before_sync();
@@ -425,7 +447,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x0, const __grid_constant__
         bool ok = true;
         for (int t = blockIdx.x; ok && t < P.total_tiles; t += gridDim.x) {
             const TileCoord tc = tile_coord(P, t, WH);
-            const int ksteps = (tc.prob ? P.p[1].K : P.p[0].K) / BK;
+            const int ksteps = (tc.prob ? P.p[1].K / P.p[1].ksplit : P.p[0].K / P.p[0].ksplit) / BK;
             for (int ks = 0; ok && ks < ksteps; ++ks, ++g) {
                 if (WH == 1 && (g & 1u) != par) continue;
                 const uint32_t s = g % LD_STAGES;
@@ -502,6 +524,9 @@ static edb200_status_t validate_problem(const edb200_qweight_t* w, const void* x
             return fail(EDB200_ERR_INVALID, "mul_mat_q: gated residual needs f32 out, residual and aligned pointers");
         }
     }
+    if (ep->split_k != EDB200_SPLIT_K_NEVER && ep->split_k != EDB200_SPLIT_K_UNORDERED) {
+        return fail(EDB200_ERR_INVALID, "mul_mat_q: split_k must be EDB200_SPLIT_K_NEVER or EDB200_SPLIT_K_UNORDERED");
+    }
     if (ep->bias != nullptr && (reinterpret_cast<uintptr_t>(ep->bias) & 15u)) {
         return fail(EDB200_ERR_INVALID, "mul_mat_q: bias must be 16-byte aligned");
     }
@@ -537,6 +562,7 @@ static void fill_problem(gemm::Problem& p, const edb200_qweight_t* w, int64_t m,
     p.N = static_cast<int>(w->n_out);
     p.K = static_cast<int>(w->k);
     p.tiles = w->tiles;
+    p.ksplit = 1;
     p.m_tiles = static_cast<int>((m + gemm::TN - 1) / gemm::TN);
     p.n_tiles = static_cast<int>((w->n_tiles + wh - 1) / wh);   // CTA tiles of `wh` weight tiles
     {
@@ -592,9 +618,43 @@ static edb200_status_t launch_qgemm(int nprob, const edb200_qweight_t* const* ws
                                           (uint64_t)ldxs[i] * 2, gemm::BK, gemm::TN, CU_TENSOR_MAP_SWIZZLE_128B);
         if (st != EDB200_OK) return st;
     }
-    if (nprob == 1) map_a[1] = map_a[0];
-    P.tiles0 = P.p[0].m_tiles * P.p[0].n_tiles;
-    P.total_tiles = P.tiles0 + (nprob == 2 ? P.p[1].m_tiles * P.p[1].n_tiles : 0);
+    if (nprob == 1) {
+        map_a[1] = map_a[0];
+        P.p[1].ksplit = 1;
+    }
+    // Long reductions into few outputs (the out-projections of a sequence-parallel rank) leave most
+    // SMs without a tile.  When every problem of the launch asks for it (split_k =
+    // EDB200_SPLIT_K_UNORDERED) and is an in-place gated residual, the reduction is cut into up to 4
+    // parts, each a tile of its own, while every tile still gets its own CTA; the parts add
+    // `gate * partial` into the f32 residual stream with atomics, in whatever order they finish.
+    {
+        int base_tiles = 0;
+        bool eligible = true;
+        for (int i = 0; i < nprob; ++i) {
+            const edb200_epilogue_t* ep = eps[i];
+            base_tiles += P.p[i].m_tiles * P.p[i].n_tiles;
+            eligible = eligible && ep->split_k == EDB200_SPLIT_K_UNORDERED && ws[i]->k >= 8192 &&
+                       ep->gate != nullptr && ep->out == ep->residual && ep->ldo == ep->ld_res &&
+                       ep->out_dtype == EDB200_TYPE_F32 && ep->act == EDB200_ACT_NONE && ep->split_n == 0;
+        }
+        if (eligible) {
+            int parts = sm_count() / base_tiles;
+            if (parts > 4) parts = 4;
+            for (; parts > 1; --parts) {
+                bool divides = true;
+                for (int i = 0; i < nprob; ++i) {
+                    const int64_t ksteps = ws[i]->k / gemm::BK;
+                    divides = divides && ksteps % parts == 0 && ksteps / parts >= 16;
+                }
+                if (divides) break;
+            }
+            if (parts > 1) {
+                for (int i = 0; i < nprob; ++i) P.p[i].ksplit = parts;
+            }
+        }
+    }
+    P.tiles0 = P.p[0].m_tiles * P.p[0].n_tiles * P.p[0].ksplit;
+    P.total_tiles = P.tiles0 + (nprob == 2 ? P.p[1].m_tiles * P.p[1].n_tiles * P.p[1].ksplit : 0);
     P.err = err;
 
     const int grid = P.total_tiles < sm_count() ? P.total_tiles : sm_count();

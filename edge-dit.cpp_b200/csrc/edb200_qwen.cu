@@ -463,6 +463,8 @@ edb200_status_t edb200_qwen_step(edb200_qwen_t* m, const float* latent, float ti
     const int64_t n_txt = m->txt_l, n_img = m->img_l;          // rows this rank owns
     const int64_t txt_first = m->world > 1 ? (int64_t)m->rank * m->t_loc : 0;
     const bool sp = m->world > 1;
+    // few output tiles per rank: let the long out-projection reductions be cut along k (unordered adds)
+    const int split_k = sp ? EDB200_SPLIT_K_UNORDERED : EDB200_SPLIT_K_NEVER;
     const int lat_c = c.in_channels / (p * p);
     const int64_t pf_out = (int64_t)c.out_channels * p * p;
     const int F16 = EDB200_TYPE_F16;
@@ -540,9 +542,9 @@ edb200_status_t edb200_qwen_step(edb200_qwen_t* m, const float* latent, float ti
         {
             const Lin li = qlin(m, pa + "to_out.0"), lt = qlin(m, pa + "to_add_out");
             edb200_epilogue_t ei = make_ep(X_img, EDB200_TYPE_F32, H, li.b);
-            ei.residual = X_img, ei.ld_res = H, ei.gate = im + 2 * H;
+            ei.residual = X_img, ei.ld_res = H, ei.gate = im + 2 * H, ei.split_k = split_k;
             edb200_epilogue_t et = make_ep(X_txt, EDB200_TYPE_F32, H, lt.b);
-            et.residual = X_txt, et.ld_res = H, et.gate = tm + 2 * H;
+            et.residual = X_txt, et.ld_res = H, et.gate = tm + 2 * H, et.split_k = split_k;
             EDB_TRY(mm_pair(li.w, att + n_txt * H, n_img, H, &ei, lt.w, att, n_txt, H, &et, s));
         }
         EDB_TRY(ln_mod(X_img, H, im + 3 * H, im + 4 * H, n_img, xmod + n_txt * H, F16, s));
@@ -556,9 +558,9 @@ edb200_status_t edb200_qwen_step(edb200_qwen_t* m, const float* latent, float ti
             EDB_TRY(mm_pair(i0.w, xmod + n_txt * H, n_img, H, &ei, t0.w, xmod, n_txt, H, &et, s));
             const Lin i2 = qlin(m, pb + "img_mlp.net.2"), t2 = qlin(m, pb + "txt_mlp.net.2");
             edb200_epilogue_t fi = make_ep(X_img, EDB200_TYPE_F32, H, i2.b);
-            fi.residual = X_img, fi.ld_res = H, fi.gate = im + 5 * H;
+            fi.residual = X_img, fi.ld_res = H, fi.gate = im + 5 * H, fi.split_k = split_k;
             edb200_epilogue_t ft = make_ep(X_txt, EDB200_TYPE_F32, H, t2.b);
-            ft.residual = X_txt, ft.ld_res = H, ft.gate = tm + 5 * H;
+            ft.residual = X_txt, ft.ld_res = H, ft.gate = tm + 5 * H, ft.split_k = split_k;
             EDB_TRY(mm_pair(i2.w, hid + n_txt * M, n_img, M, &fi, t2.w, hid, n_txt, M, &ft, s));
         }
         if (m->tap) {

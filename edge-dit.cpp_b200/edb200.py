@@ -16,6 +16,7 @@ LIB_PATH = os.path.join(HERE, "libedb200.so")
 OK = 0
 TYPE_F32, TYPE_F16, TYPE_Q8_0, TYPE_Q4_K, TYPE_I8, TYPE_BF16 = 0, 1, 8, 12, 24, 30
 ACT_NONE, ACT_GELU_TANH, ACT_SILU = 0, 1, 2
+SPLIT_K_NEVER, SPLIT_K_UNORDERED = 0, 1
 
 c_i64 = C.c_int64
 c_vp = C.c_void_p
@@ -26,6 +27,7 @@ class Epilogue(C.Structure):
         ("bias", c_vp), ("act", C.c_int), ("out", c_vp), ("out_dtype", C.c_int), ("ldo", c_i64),
         ("residual", c_vp), ("ld_res", c_i64), ("gate", c_vp),
         ("split_n", c_i64), ("out2", c_vp), ("out2_dtype", C.c_int), ("ldo2", c_i64), ("act2", C.c_int),
+        ("split_k", C.c_int),
     ]
 
 
@@ -263,7 +265,7 @@ class QWeight:
 
 
 def make_epilogue(out, bias=None, act=ACT_NONE, residual=None, gate=None, split_n=0, out2=None, act2=ACT_NONE,
-                  ldo=None, ldo2=None):
+                  ldo=None, ldo2=None, split_k=0):
     ep = Epilogue()
     ep.bias = ptr(bias)
     ep.act = act
@@ -278,6 +280,7 @@ def make_epilogue(out, bias=None, act=ACT_NONE, residual=None, gate=None, split_
     ep.out2_dtype = torch_dtype_id(out2) if out2 is not None else 0
     ep.ldo2 = (out2.stride(0) if ldo2 is None else ldo2) if out2 is not None else 0
     ep.act2 = act2
+    ep.split_k = split_k
     return ep
 
 

@@ -47,6 +47,7 @@ enum {
     EDB200_TYPE_BF16 = 30
 };
 
+enum { EDB200_SPLIT_K_NEVER = 0, EDB200_SPLIT_K_UNORDERED = 1 };
 enum { EDB200_ACT_NONE = 0, EDB200_ACT_GELU_TANH = 1, EDB200_ACT_SILU = 2, EDB200_ACT_GELU_ERF = 3 /* dense f32 linear only */ };
 
 /* Buffers of every rank of the group as this GPU addresses them (peer mappings over
@@ -146,6 +147,13 @@ typedef struct {
     int out2_dtype;
     int64_t ldo2;
     int act2;
+    /* EDB200_SPLIT_K_NEVER (0): every output is one sum over k in a fixed order; the same bits
+     * every run.  EDB200_SPLIT_K_UNORDERED: an in-place gated residual (out == residual, f32,
+     * no activation, no column split, k >= 8192) whose output tiles are fewer than half the
+     * SMs may cut the reduction into up to 4 parts that add into `out` with atomics; the order
+     * of those adds, hence the last bit of the result, can differ between runs.  The
+     * sequence-parallel executors ask for it: a rank's out-projections have few output tiles. */
+    int split_k;
 } edb200_epilogue_t;
 
 /* x: [m, ldx] f16 (x_dtype = EDB200_TYPE_F16), 16-byte aligned rows.  Tensor-core

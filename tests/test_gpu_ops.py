@@ -259,6 +259,35 @@ def test_mul_mat_q_gated_residual_in_place(edb, cuda):
     assert O.rel_l2(stream.cpu().numpy(), ref) < 2e-3
 
 
+@pytest.mark.parametrize("wtype,m,n_out,k", [("q8_0", 260, 768, 8192),     # 6 tiles -> 4 reduction parts
+                                              ("q4_k", 576, 3072, 15360),   # a FLUX out-projection on 1/8 of the tokens
+                                              ("q8_0", 100, 256, 12288)])   # 192 k-steps: 4 parts of 48
+def test_mul_mat_q_split_reduction(edb, cuda, wtype, m, n_out, k):
+    # few output tiles and a long reduction: on request the launch cuts k into parts that add
+    # into the residual stream with atomics; the result must still be the gated residual
+    w, xt, xr, wd, rng = _gemm_case(edb, cuda, wtype, m, n_out, k, torch.float16, seed=15)
+    b = rng.standard_normal(n_out, dtype=np.float32)
+    g = rng.standard_normal(n_out, dtype=np.float32)
+    res = rng.standard_normal((m, n_out), dtype=np.float32)
+    stream = dev(res, cuda)
+    launches = edb.lib().edb200_launch_count()
+    edb.mul_mat_q(w, xt, edb.make_epilogue(stream, bias=dev(b, cuda), residual=stream, gate=dev(g, cuda),
+                                           split_k=edb.SPLIT_K_UNORDERED))
+    assert edb.lib().edb200_launch_count() == launches + 1, "a split reduction is still one kernel"
+    ref = res + g[None] * (xr @ wd.T + b)
+    got = stream.cpu().numpy()
+    assert np.isfinite(got).all()
+    assert O.rel_l2(got, ref) < 2e-3, O.rel_l2(got, ref)
+    # without the request the same call sums every output in one fixed order: same bits twice
+    outs = []
+    for _ in range(2):
+        stream = dev(res, cuda)
+        edb.mul_mat_q(w, xt, edb.make_epilogue(stream, bias=dev(b, cuda), residual=stream, gate=dev(g, cuda)))
+        outs.append(stream.cpu().numpy())
+    assert np.array_equal(outs[0], outs[1]), "unsplit sums differ between runs"
+    assert O.rel_l2(outs[0], got) < 1e-4, ("split vs unsplit", O.rel_l2(outs[0], got))
+
+
 def test_mul_mat_q_column_split(edb, cuda):
     # FLUX single-block linear1: qkv columns to one buffer, GELU(mlp) columns into
     # the tail of the linear2 input buffer.
