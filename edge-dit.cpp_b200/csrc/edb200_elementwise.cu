@@ -170,6 +170,21 @@ __global__ void fused_residual_gate_kernel(const float4* __restrict__ res, const
     y[i] = o;
 }
 
+// Sampler update of one step (flux_pipeline.cpp:1290-1297): every operation rounded on its own.
+__global__ void euler_update_kernel(float* __restrict__ x, const float* __restrict__ v, float sigma, float sigma_next,
+                                    int64_t n) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float xi = x[i];
+    const float denoised = __fadd_rn(__fmul_rn(v[i], -sigma), xi);   // model_out * c_out + x * c_skip, c_skip = 1
+    if (sigma == 0.0f) {
+        x[i] = denoised;
+    } else {
+        const float d = __fdiv_rn(__fsub_rn(xi, denoised), sigma);
+        x[i] = __fadd_rn(xi, __fmul_rn(d, __fsub_rn(sigma_next, sigma)));
+    }
+}
+
 // ---------------------------------------- QK-RMSNorm + RoPE + head-major pack --
 // One warp per (token, head); lane owns 4 consecutive channels (two RoPE pairs)
 // of a 128-wide head, or 2 channels (one pair) of a 64-wide head.
@@ -350,6 +365,15 @@ edb200_status_t edb200_fused_residual_gate(const float* residual, const float* x
         reinterpret_cast<const float4*>(gate), reinterpret_cast<float4*>(y), total4, static_cast<int>(h / 4));
     count_launch();
     return check_cuda(cudaGetLastError(), "fused_residual_gate launch");
+}
+
+edb200_status_t edb200_euler_update(float* x, const float* model_out, float sigma, float sigma_next, int64_t n,
+                                    void* stream) {
+    if (x == nullptr || model_out == nullptr || n <= 0) return fail(EDB200_ERR_INVALID, "euler_update: null or empty argument");
+    euler_update_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        x, model_out, sigma, sigma_next, n);
+    count_launch();
+    return check_cuda(cudaGetLastError(), "euler_update launch");
 }
 
 static edb200_status_t qk_pack_launch(const void* qkv, int in_dtype, int64_t ld, int64_t q_off, int64_t k_off,

@@ -102,6 +102,7 @@ _SIGS = {
                                             C.c_int, c_i64, c_vp]),
     "edb200_fused_modulate": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_vp]),
     "edb200_fused_residual_gate": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_vp]),
+    "edb200_euler_update": (C.c_int, [c_vp, c_vp, C.c_float, C.c_float, c_i64, c_vp]),
     "edb200_qk_norm_rope_pack": (C.c_int, [c_vp, C.c_int, c_i64, c_i64, c_i64, c_i64, c_i64, C.c_int, C.c_int,
                                            c_vp, c_vp, C.c_float, c_vp, c_i64, c_i64, c_vp, c_vp, c_vp, C.c_int,
                                            c_vp]),
@@ -289,6 +290,11 @@ def mul_mat_q(w: QWeight, x, ep: Epilogue):
                                  current_stream()))
 
 
+def euler_update(x, model_out, sigma, sigma_next):
+    """In place on the device: x <- x + ((x - denoised)/sigma)*(sigma_next - sigma), denoised = x - sigma*model_out."""
+    check(lib().edb200_euler_update(ptr(x), ptr(model_out), sigma, sigma_next, x.numel(), current_stream()))
+
+
 def sp_shard(n_tokens, n_txt, rank, world):
     """(t_loc, n_txt_local, img_first) of `rank`'s token slice."""
     a, b, c = c_i64(), c_i64(), c_i64()
@@ -386,6 +392,18 @@ class FluxModel:
     def step(self, latent, timestep, context, y, guidance, out):
         check(lib().edb200_flux_step(self.handle, ptr(latent), timestep, ptr(context), ptr(y), guidance, ptr(out),
                                      current_stream()))
+
+    def denoise(self, latent, sigmas, context, y, guidance, velocity=None):
+        """The sampler loop with the latent resident on the device: for each consecutive pair of
+        `sigmas` one step at timestep sigma and the reference's Euler update in place
+        (src/dit_models/pipelines/flux_pipeline.cpp:1111-1116, :1290-1297).  Nothing returns to
+        the host between steps.  `velocity` is scratch of the latent's shape."""
+        import torch
+        v = torch.empty_like(latent) if velocity is None else velocity
+        for sigma, sigma_next in zip(sigmas[:-1], sigmas[1:]):
+            self.step(latent, float(sigma), context, y, guidance, v)
+            euler_update(latent, v, float(sigma), float(sigma_next))
+        return latent
 
     def compute_host(self, latent, timestep, context, y, guidance):
         """numpy f32 in, numpy f32 out; host<->device copies happen inside the call."""

@@ -204,6 +204,15 @@ EDB200_API edb200_status_t edb200_fused_modulate(const float* x, const float* sh
 EDB200_API edb200_status_t edb200_fused_residual_gate(const float* residual, const float* x, const float* gate, float* y,
                                            int64_t rows, int64_t h, void* stream);
 
+/* The sampler's latent update of one denoise step, in place on the device, so that the latent
+ * never returns to the host between steps (src/dit_models/pipelines/flux_pipeline.cpp:1111-1112,
+ * :1290-1297; the same form in sd3_pipeline.cpp):
+ *   denoised = model_out * (-sigma) + x;
+ *   sigma == 0 ? x = denoised : x += ((x - denoised) / sigma) * (sigma_next - sigma)
+ * f32, each operation rounded on its own in that order (no FMA contraction): the reference's bits. */
+EDB200_API edb200_status_t edb200_euler_update(float* x, const float* model_out, float sigma, float sigma_next, int64_t n,
+                                    void* stream);
+
 /* Per-head RMSNorm of q and k (weights [d_head] or NULL), RoPE with the
  * reference's pe table [l_total, d_head/2, 2, 2] (NULL = none), and head-major
  * pack of q, k, v into [n_heads, l_total, d_head] at token offset tok_off.

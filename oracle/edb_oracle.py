@@ -253,6 +253,19 @@ def residual_gate(residual: np.ndarray, x: np.ndarray, gate: np.ndarray) -> np.n
     return (residual + (x * gate).astype(np.float32)).astype(np.float32)
 
 
+def euler_update(x: np.ndarray, model_out: np.ndarray, sigma: float, sigma_next: float) -> np.ndarray:
+    """The sampler's per-step latent update (src/dit_models/pipelines/flux_pipeline.cpp:1111-1112,
+    :1290-1297): denoised = model_out*(-sigma) + x; x + ((x - denoised)/sigma)*(sigma_next - sigma),
+    or denoised itself when sigma == 0.  float32 operation by operation."""
+    f = np.float32
+    x = x.astype(f)
+    denoised = ((model_out.astype(f) * f(-sigma)).astype(f) + x).astype(f)
+    if f(sigma) == f(0.0):
+        return denoised
+    d = ((x - denoised).astype(f) / f(sigma)).astype(f)
+    return (x + (d * (f(sigma_next) - f(sigma))).astype(f)).astype(f)
+
+
 def gelu_tanh(x: np.ndarray) -> np.ndarray:
     """0.5*x*(1+tanh(sqrt(2/pi)*x*(1+0.044715*x*x)))
     (src/core/backend/ggml/ed_ggml_sp_flux_ext.hpp:675-679; ggml_gelu call site

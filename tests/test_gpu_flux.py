@@ -139,3 +139,31 @@ def test_flux_step_replayed_from_a_cuda_graph(edb, cuda):
     assert torch.equal(eager, replay)
     with pytest.raises(edb.EdbError):
         edb.check(edb.lib().edb200_graph_begin(None))    # the default stream cannot be captured
+
+
+def test_flux_denoise_loop_stays_on_the_device(edb, cuda):
+    """Three sampler steps (step + Euler update in place, nothing copied to the host in between)
+    against the oracle's step and update applied in the same order."""
+    cfg = FluxConfig(hidden_size=512, num_heads=4, depth=1, depth_single_blocks=1, context_in_dim=256, vec_in_dim=64)
+    weights = flux_make_weights(cfg, 9)
+    latent, ctx, y = _inputs(cfg, (16, 16), 12, 109)
+    sigmas = [1.0, 0.7, 0.35, 0.0]
+    oracle = FluxOracle(cfg, weights)
+    want = latent.copy()
+    for s, s_next in zip(sigmas[:-1], sigmas[1:]):
+        want = O.euler_update(want, oracle.forward(want, s, ctx, y, 3.5), s, s_next)
+
+    model = edb.FluxModel(hidden_size=cfg.hidden_size, num_heads=cfg.num_heads, depth=cfg.depth,
+                          depth_single_blocks=cfg.depth_single_blocks, mlp_hidden=cfg.mlp_hidden,
+                          in_channels=cfg.in_channels, context_in_dim=cfg.context_in_dim, vec_in_dim=cfg.vec_in_dim,
+                          axes_dim=cfg.axes_dim, wtype=cfg.wtype, attention=edb.ATTN_SAGE_INT8)
+    model.load_numpy(weights)
+    model.prepare(16, 16, 12)
+    d_lat, d_ctx, d_y = (torch.from_numpy(a).to(cuda) for a in (latent, ctx, y))
+    launches = edb.lib().edb200_launch_count()
+    model.denoise(d_lat, sigmas, d_ctx, d_y, 3.5)
+    torch.cuda.synchronize()
+    assert edb.lib().edb200_launch_count() > launches + 3
+    got = d_lat.cpu().numpy()
+    assert np.isfinite(got).all()
+    assert O.rel_l2(got, want) <= STEP_REL, O.rel_l2(got, want)

@@ -115,6 +115,17 @@ def test_fused_residual_gate_bit_exact(edb, cuda):
     assert np.array_equal(y.cpu().numpy().view(np.uint32), O.residual_gate(r, x, g[None]).view(np.uint32))
 
 
+@pytest.mark.parametrize("sigma,sigma_next", [(1.0, 0.9), (0.37, 0.0), (0.0, 0.0), (0.0123, 0.0045)])
+def test_euler_update_bit_exact(edb, cuda, sigma, sigma_next):
+    rng = np.random.default_rng(31)
+    x = rng.standard_normal(16 * 33 * 47, dtype=np.float32)
+    v = rng.standard_normal(x.size, dtype=np.float32)
+    dx = dev(x, cuda)
+    edb.euler_update(dx, dev(v, cuda), sigma, sigma_next)
+    want = O.euler_update(x, v, sigma, sigma_next)
+    assert np.array_equal(dx.cpu().numpy().view(np.uint32), want.view(np.uint32))
+
+
 @pytest.mark.parametrize("h,dt", [(3072, "bf16"), (1536, "f32"), (5120, "f16")])
 def test_layernorm_modulate(edb, cuda, h, dt):
     rng = np.random.default_rng(7)

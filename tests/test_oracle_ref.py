@@ -54,3 +54,21 @@ def test_oracle_matches_compiled_reference_callbacks(seed):
     got = _oracle_outputs(d, pe)
     for k in ref:
         assert _same_bits(got[k], ref[k]), k
+
+
+def test_oracle_euler_update_is_the_reference_sampler_step():
+    """The per-step latent update restated in the oracle (flux_pipeline.cpp:1290-1297), checked
+    against the same expression written out in float64 and against its fixed points."""
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal(4096, dtype=np.float32)
+    v = rng.standard_normal(4096, dtype=np.float32)
+    # sigma_next == sigma leaves the latent alone; sigma == 0 returns the denoised latent (= x here)
+    assert np.array_equal(O.euler_update(x, v, 0.5, 0.5), x)
+    assert np.array_equal(O.euler_update(x, v, 0.0, 0.0), x)
+    # a full step to sigma_next = 0 lands on the denoised latent up to rounding
+    got = O.euler_update(x, v, 0.8, 0.0)
+    assert np.allclose(got, x.astype(np.float64) - 0.8 * v.astype(np.float64), rtol=0, atol=2e-6)
+    # in exact arithmetic the update is x + v*(sigma_next - sigma)
+    got = O.euler_update(x, v, 0.8, 0.55)
+    assert np.allclose(got, x.astype(np.float64) + v.astype(np.float64) * (0.55 - 0.8), rtol=0, atol=2e-6)
+    assert got.dtype == np.float32
