@@ -170,11 +170,19 @@ __global__ void fused_residual_gate_kernel(const float4* __restrict__ res, const
     y[i] = o;
 }
 
+__global__ void advance_step_kernel(int* step) { *step += 1; }
+
 // Sampler update of one step (flux_pipeline.cpp:1290-1297): every operation rounded on its own.
+// `sched` != NULL: sigma = sched[*step], sigma_next = sched[*step + 1], read on the device.
 __global__ void euler_update_kernel(float* __restrict__ x, const float* __restrict__ v, float sigma, float sigma_next,
-                                    int64_t n) {
+                                    const float* __restrict__ sched, const int* __restrict__ step, int64_t n) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
+    if (sched != nullptr) {
+        const int k = *step;
+        sigma = sched[k];
+        sigma_next = sched[k + 1];
+    }
     const float xi = x[i];
     const float denoised = __fadd_rn(__fmul_rn(v[i], -sigma), xi);   // model_out * c_out + x * c_skip, c_skip = 1
     if (sigma == 0.0f) {
@@ -371,9 +379,22 @@ edb200_status_t edb200_euler_update(float* x, const float* model_out, float sigm
                                     void* stream) {
     if (x == nullptr || model_out == nullptr || n <= 0) return fail(EDB200_ERR_INVALID, "euler_update: null or empty argument");
     euler_update_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        x, model_out, sigma, sigma_next, n);
+        x, model_out, sigma, sigma_next, nullptr, nullptr, n);
     count_launch();
     return check_cuda(cudaGetLastError(), "euler_update launch");
+}
+
+edb200_status_t edb200_euler_update_sched(float* x, const float* model_out, const float* sigmas, int* step, int64_t n,
+                                          void* stream) {
+    if (x == nullptr || model_out == nullptr || sigmas == nullptr || step == nullptr || n <= 0) {
+        return fail(EDB200_ERR_INVALID, "euler_update_sched: null or empty argument");
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    euler_update_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, s>>>(x, model_out, 0.0f, 0.0f, sigmas, step, n);
+    count_launch();
+    advance_step_kernel<<<1, 1, 0, s>>>(step);   // after every thread above has read the old value (stream order)
+    count_launch();
+    return check_cuda(cudaGetLastError(), "euler_update_sched launch");
 }
 
 static edb200_status_t qk_pack_launch(const void* qkv, int in_dtype, int64_t ld, int64_t q_off, int64_t k_off,

@@ -478,8 +478,9 @@ edb200_status_t edb200_flux_set_tap(edb200_flux_t* m, float* tap) {
     return EDB200_OK;
 }
 
-edb200_status_t edb200_flux_step(edb200_flux_t* m, const float* latent, float timestep, const float* context,
-                                 const float* y, float guidance, float* out, void* stream) {
+static edb200_status_t flux_step_body(edb200_flux_t* m, const float* latent, float timestep, const float* sched,
+                                      const int* sched_step, const float* context, const float* y, float guidance,
+                                      float* out, void* stream) {
     if (m == nullptr || latent == nullptr || context == nullptr || y == nullptr || out == nullptr) {
         return fail(EDB200_ERR_INVALID, "flux_step: null argument");
     }
@@ -515,7 +516,11 @@ edb200_status_t edb200_flux_step(edb200_flux_t* m, const float* latent, float ti
         EDB_TRY(dense(m, "txt_in", context + txt_first * c.context_in_dim, n_txt, c.context_in_dim, 0, EDB200_ACT_NONE,
                       X_txt, H, s));
     }
-    launch_timestep_embedding(m->FREQ, timestep, 1000.0f, 128, m->TEMB, s);
+    if (sched != nullptr) {
+        launch_timestep_embedding_sched(m->FREQ, sched, sched_step, 1000.0f, 128, m->TEMB, s);
+    } else {
+        launch_timestep_embedding(m->FREQ, timestep, 1000.0f, 128, m->TEMB, s);
+    }
     EDB_TRY(dense(m, "time_in.in_layer", m->TEMB, 1, 256, 0, EDB200_ACT_SILU, m->TMP_H, H, s));
     EDB_TRY(dense(m, "time_in.out_layer", m->TMP_H, 1, H, 0, EDB200_ACT_NONE, m->VEC, H, s));
     if (c.guidance_embed) {
@@ -643,6 +648,18 @@ edb200_status_t edb200_flux_step(edb200_flux_t* m, const float* latent, float ti
     }
     launch_unpatchify(m->TOK_OUT, out, lat_c, m->lat_h, m->lat_w, c.patch_size, s);
     return check_cuda(cudaGetLastError(), "flux_step");
+}
+
+edb200_status_t edb200_flux_step(edb200_flux_t* m, const float* latent, float timestep, const float* context,
+                                 const float* y, float guidance, float* out, void* stream) {
+    return flux_step_body(m, latent, timestep, nullptr, nullptr, context, y, guidance, out, stream);
+}
+
+edb200_status_t edb200_flux_step_sched(edb200_flux_t* m, const float* latent, const float* sigmas, const int* step,
+                                       const float* context, const float* y, float guidance, float* out,
+                                       void* stream) {
+    if (sigmas == nullptr || step == nullptr) return fail(EDB200_ERR_INVALID, "flux_step_sched: null schedule");
+    return flux_step_body(m, latent, 0.0f, sigmas, step, context, y, guidance, out, stream);
 }
 
 edb200_status_t edb200_flux_compute_host(edb200_flux_t* m, const float* latent, int latent_h, int latent_w,

@@ -103,6 +103,7 @@ _SIGS = {
     "edb200_fused_modulate": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_vp]),
     "edb200_fused_residual_gate": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_vp]),
     "edb200_euler_update": (C.c_int, [c_vp, c_vp, C.c_float, C.c_float, c_i64, c_vp]),
+    "edb200_euler_update_sched": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_i64, c_vp]),
     "edb200_qk_norm_rope_pack": (C.c_int, [c_vp, C.c_int, c_i64, c_i64, c_i64, c_i64, c_i64, C.c_int, C.c_int,
                                            c_vp, c_vp, C.c_float, c_vp, c_i64, c_i64, c_vp, c_vp, c_vp, C.c_int,
                                            c_vp]),
@@ -204,6 +205,7 @@ _SIGS = {
     "edb200_flux_prepare": (C.c_int, [c_vp, C.c_int, C.c_int, C.c_int, c_vp]),
     "edb200_flux_set_tap": (C.c_int, [c_vp, c_vp]),
     "edb200_flux_step": (C.c_int, [c_vp, c_vp, C.c_float, c_vp, c_vp, C.c_float, c_vp, c_vp]),
+    "edb200_flux_step_sched": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, C.c_float, c_vp, c_vp]),
     "edb200_flux_compute_host": (C.c_int, [c_vp, c_vp, C.c_int, C.c_int, C.c_float, c_vp, C.c_int, c_vp, C.c_float,
                                            c_vp, c_vp]),
 }
@@ -403,6 +405,31 @@ class FluxModel:
         for sigma, sigma_next in zip(sigmas[:-1], sigmas[1:]):
             self.step(latent, float(sigma), context, y, guidance, v)
             euler_update(latent, v, float(sigma), float(sigma_next))
+        return latent
+
+    def denoise_graph(self, latent, sigmas, context, y, guidance, velocity=None):
+        """`denoise` with one recorded (step + update) replayed for every step: the schedule lives in
+        device memory and a device counter walks through it, so the recording holds no sigma.
+        Must run on a non-default stream (stream capture)."""
+        import torch
+        v = torch.empty_like(latent) if velocity is None else velocity
+        sched = torch.tensor([float(x) for x in sigmas], dtype=torch.float32, device=latent.device)
+        step = torch.zeros(1, dtype=torch.int32, device=latent.device)
+        n = latent.numel()
+
+        def one():
+            check(lib().edb200_flux_step_sched(self.handle, ptr(latent), ptr(sched), ptr(step), ptr(context), ptr(y),
+                                               guidance, ptr(v), current_stream()))
+            check(lib().edb200_euler_update_sched(ptr(latent), ptr(v), ptr(sched), ptr(step), n, current_stream()))
+
+        saved = latent.clone()
+        one()                      # warm: first-call attribute settings happen outside the recording
+        latent.copy_(saved)
+        step.zero_()
+        graph = Graph(one)         # recording executes nothing
+        for _ in range(len(sigmas) - 1):
+            graph.launch()
+        torch.cuda.current_stream().synchronize()
         return latent
 
     def compute_host(self, latent, timestep, context, y, guidance):

@@ -212,6 +212,12 @@ EDB200_API edb200_status_t edb200_fused_residual_gate(const float* residual, con
  * f32, each operation rounded on its own in that order (no FMA contraction): the reference's bits. */
 EDB200_API edb200_status_t edb200_euler_update(float* x, const float* model_out, float sigma, float sigma_next, int64_t n,
                                     void* stream);
+/* The same update with the schedule on the device: sigma = sigmas[*step], sigma_next =
+ * sigmas[*step + 1]; afterwards *step is incremented (a second, one-thread kernel).  Together with
+ * edb200_flux_step_sched this makes one recorded step + update (edb200_graph_*) replayable for
+ * every step of a schedule: nothing in it depends on a by-value sigma. */
+EDB200_API edb200_status_t edb200_euler_update_sched(float* x, const float* model_out, const float* sigmas, int* step,
+                                          int64_t n, void* stream);
 
 /* Per-head RMSNorm of q and k (weights [d_head] or NULL), RoPE with the
  * reference's pe table [l_total, d_head/2, 2, 2] (NULL = none), and head-major
@@ -465,6 +471,11 @@ EDB200_API edb200_status_t edb200_flux_set_tap(edb200_flux_t* m, float* tap);
 EDB200_API edb200_status_t edb200_flux_step(edb200_flux_t* m, const float* latent, float timestep,
                                             const float* context, const float* y, float guidance, float* out,
                                             void* stream);
+/* The same step with the timestep read on the device: timestep = sigmas[*step] (f32 device array,
+ * int device word).  See edb200_euler_update_sched. */
+EDB200_API edb200_status_t edb200_flux_step_sched(edb200_flux_t* m, const float* latent, const float* sigmas,
+                                                  const int* step, const float* context, const float* y,
+                                                  float guidance, float* out, void* stream);
 /* The same step with host tensors in and out (the reference's compute seam):
  * prepares the shape if needed, copies through pinned staging, runs the step,
  * copies the result back and synchronises. */

@@ -167,3 +167,12 @@ def test_flux_denoise_loop_stays_on_the_device(edb, cuda):
     got = d_lat.cpu().numpy()
     assert np.isfinite(got).all()
     assert O.rel_l2(got, want) <= STEP_REL, O.rel_l2(got, want)
+
+    # the same loop as ONE recorded (step + update) replayed three times, schedule and step counter
+    # in device memory: the eager loop's bits
+    g_lat = torch.from_numpy(latent).to(cuda)
+    side = torch.cuda.Stream(device=cuda)
+    with torch.cuda.stream(side):
+        model.denoise_graph(g_lat, sigmas, d_ctx, d_y, 3.5)
+    torch.cuda.synchronize()
+    assert torch.equal(g_lat, d_lat)
