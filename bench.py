@@ -111,6 +111,11 @@ class Case:
 
     def _combine(self):
         e = self.edb
+        if self.family == "qwen":   # Qwen-Image's per-patch norm-preserving combine (qwen_image_pipeline.cpp:29-85)
+            c, h, w = self.cond.shape
+            e.check(e.lib().edb200_cfg_combine_rescaled(e.ptr(self.uncond), e.ptr(self.cond), 4.0, 2, c, h, w,
+                                                        e.ptr(self.out), e.current_stream()))
+            return
         e.check(e.lib().edb200_cfg_combine(e.ptr(self.uncond), e.ptr(self.cond), 4.5, e.ptr(self.out), self.out.numel(),
                                            e.current_stream()))
 

@@ -139,6 +139,40 @@ __global__ void cfg_combine_kernel(const float4* __restrict__ u, const float4* _
     o[i] = make_float4(a.x + s * (b.x - a.x), a.y + s * (b.y - a.y), a.z + s * (b.z - a.z), a.w + s * (b.w - a.w));
 }
 
+// Qwen-Image's guidance combine (ed_qwen_apply_true_cfg, src/dit_models/pipelines/qwen_image_pipeline.cpp:29-85):
+// per p x p latent patch (all channels), guided = u + s*(c - u) in f32, then scaled by
+// ||c|| / ||guided|| with both sums of squares accumulated in double in the order (dy, dx, channel).
+// One thread per patch walks its p*p*C values in that order, so the result has the reference's bits.
+__global__ void cfg_combine_rescaled_kernel(const float* __restrict__ cond, const float* __restrict__ uncond, float s,
+                                            int p, int C, int H, int W, float* __restrict__ out) {
+    const int pw = W / p, ph = H / p;
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= pw * ph) return;
+    const int px = (idx % pw) * p, py = (idx / pw) * p;
+    double cond_sq = 0.0, guided_sq = 0.0;
+    for (int dy = 0; dy < p; ++dy) {
+        for (int dx = 0; dx < p; ++dx) {
+            for (int c = 0; c < C; ++c) {
+                const int64_t off = (px + dx) + (int64_t)W * ((py + dy) + (int64_t)H * c);
+                const float cv = cond[off], uv = uncond[off];
+                const float g = __fadd_rn(uv, __fmul_rn(s, __fsub_rn(cv, uv)));
+                cond_sq = __dadd_rn(cond_sq, __dmul_rn((double)cv, (double)cv));
+                guided_sq = __dadd_rn(guided_sq, __dmul_rn((double)g, (double)g));
+            }
+        }
+    }
+    const float rescale = guided_sq > 0.0 ? (float)__ddiv_rn(__dsqrt_rn(cond_sq), __dsqrt_rn(guided_sq)) : 0.0f;
+    for (int dy = 0; dy < p; ++dy) {
+        for (int dx = 0; dx < p; ++dx) {
+            for (int c = 0; c < C; ++c) {
+                const int64_t off = (px + dx) + (int64_t)W * ((py + dy) + (int64_t)H * c);
+                const float cv = cond[off], uv = uncond[off];
+                out[off] = __fmul_rn(__fadd_rn(uv, __fmul_rn(s, __fsub_rn(cv, uv))), rescale);
+            }
+        }
+    }
+}
+
 edb200_status_t ln_mod(const float* x, int64_t H, const float* shift, const float* scale, int64_t rows, void* y,
                        int y_dtype, cudaStream_t s) {
     if (rows == 0) return EDB200_OK;
@@ -161,6 +195,21 @@ edb200_status_t edb200_cfg_combine(const float* uncond, const float* cond, float
         reinterpret_cast<float4*>(out), n / 4);
     count_launch();
     return check_cuda(cudaGetLastError(), "cfg_combine launch");
+}
+
+edb200_status_t edb200_cfg_combine_rescaled(const float* uncond, const float* cond, float scale, int patch_size,
+                                            int channels, int height, int width, float* out, void* stream) {
+    if (uncond == nullptr || cond == nullptr || out == nullptr || patch_size <= 0 || channels <= 0 || height <= 0 ||
+        width <= 0 || height % patch_size || width % patch_size) {
+        return fail(EDB200_ERR_INVALID, "cfg_combine_rescaled: bad argument (height, width multiples of the patch size)");
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int patches = (height / patch_size) * (width / patch_size);
+    ProfScope prof(s, PROF_ELEMENTWISE, 0.0, 20.0 * (double)channels * height * width);
+    cfg_combine_rescaled_kernel<<<(patches + 127) / 128, 128, 0, s>>>(cond, uncond, scale, patch_size, channels, height,
+                                                                      width, out);
+    count_launch();
+    return check_cuda(cudaGetLastError(), "cfg_combine_rescaled launch");
 }
 
 edb200_status_t edb200_sd3_create(const edb200_sd3_config_t* cfg, edb200_sd3_t** out) {

@@ -179,6 +179,7 @@ _SIGS = {
     "edb200_sd3_step": (C.c_int, [c_vp, c_vp, C.c_float, c_vp, c_vp, c_vp, c_vp]),
     "edb200_sd3_compute_host": (C.c_int, [c_vp, c_vp, C.c_int, C.c_int, C.c_float, c_vp, C.c_int, c_vp, c_vp, c_vp]),
     "edb200_cfg_combine": (C.c_int, [c_vp, c_vp, C.c_float, c_vp, c_i64, c_vp]),
+    "edb200_cfg_combine_rescaled": (C.c_int, [c_vp, c_vp, C.c_float, C.c_int, C.c_int, C.c_int, C.c_int, c_vp, c_vp]),
     "edb200_wan_create": (C.c_int, [C.POINTER(WanConfig), C.POINTER(c_vp)]),
     "edb200_wan_destroy": (None, [c_vp]),
     "edb200_wan_tensor_count": (C.c_int, [c_vp]),

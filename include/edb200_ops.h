@@ -532,6 +532,12 @@ EDB200_API edb200_status_t edb200_sd3_compute_host(edb200_sd3_t* m, const float*
  * (src/pipelines/sd3_pipeline.cpp:631-669, src/pipelines/flux_pipeline.cpp:1218-1258). */
 EDB200_API edb200_status_t edb200_cfg_combine(const float* uncond, const float* cond, float scale, float* out, int64_t n,
                                               void* stream);
+/* Qwen-Image's guidance combine (ed_qwen_apply_true_cfg, src/dit_models/pipelines/qwen_image_pipeline.cpp:29-85):
+ * out = guided * (||cond|| / ||guided||) with guided = uncond + scale * (cond - uncond) and the two norms taken
+ * per patch_size x patch_size latent patch over all channels (sums of squares in double, order dy, dx, channel);
+ * 0 where ||guided|| is 0.  Tensors f32 [channels, height, width].  Bit-identical to the reference. */
+EDB200_API edb200_status_t edb200_cfg_combine_rescaled(const float* uncond, const float* cond, float scale, int patch_size,
+                                            int channels, int height, int width, float* out, void* stream);
 
 /* ---------------------------------------------------- Qwen-Image denoise pass
  * The same seam for QwenImageModel (src/dit_models/models/qwen_image.hpp:3116-3301; members

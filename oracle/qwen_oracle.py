@@ -159,3 +159,27 @@ class QwenOracle:
         m = self.lin("norm_out.linear", O.silu(t_emb)).reshape(2, -1)          # (scale, shift)
         out = self.lin("proj_out", O.modulate(O.layer_norm(img), m[1:2], m[0:1]))
         return O.unpatchify(out, h_tok, w_tok, p)
+
+
+def true_cfg(cond: np.ndarray, uncond: np.ndarray, cfg_scale: float, patch_size: int) -> np.ndarray:
+    """ed_qwen_apply_true_cfg (src/dit_models/pipelines/qwen_image_pipeline.cpp:29-85) on [C, H, W]:
+    guided = uncond + s*(cond - uncond) in f32; per patch (all channels) the sums of squares of cond
+    and guided are accumulated in double in the order (dy, dx, channel); out = guided * f32(sqrt/sqrt)."""
+    f = np.float32
+    C, H, W = cond.shape
+    p = patch_size
+    guided = (uncond + (f(cfg_scale) * (cond - uncond).astype(f)).astype(f)).astype(f)
+    out = np.empty_like(guided)
+    for py in range(0, H, p):
+        for px in range(0, W, p):
+            cs = gs = 0.0
+            for dy in range(p):
+                for dx in range(p):
+                    for c in range(C):
+                        cv = float(cond[c, py + dy, px + dx])
+                        gv = float(guided[c, py + dy, px + dx])
+                        cs += cv * cv
+                        gs += gv * gv
+            r = f(np.sqrt(cs) / np.sqrt(gs)) if gs > 0.0 else f(0.0)
+            out[:, py:py + p, px:px + p] = (guided[:, py:py + p, px:px + p] * r).astype(f)
+    return out

@@ -67,3 +67,26 @@ def test_qwen_full_width_block_parity(edb, cuda):
     # Qwen-Image widths (hidden 3072, 24 heads x 128, mlp 12288, text 3584, q4_K) with one block
     cfg = QwenConfig(num_layers=1)
     _run_case(edb, cuda, cfg, (32, 48), 77, edb.ATTN_SAGE_INT8, seed=5)
+
+
+def test_qwen_guidance_combine_bit_exact(edb, cuda):
+    """edb200_cfg_combine_rescaled against the oracle's restatement of the reference's per-patch
+    norm-preserving guidance combine, bit for bit, including a patch whose guided value is all zero."""
+    from oracle.qwen_oracle import true_cfg
+    rng = np.random.default_rng(41)
+    C_, H_, W_ = 16, 12, 20
+    cond = rng.standard_normal((C_, H_, W_), dtype=np.float32)
+    uncond = rng.standard_normal((C_, H_, W_), dtype=np.float32)
+    cond[:, 2:4, 6:8] = 0.0
+    uncond[:, 2:4, 6:8] = 0.0
+    out = torch.full((C_, H_, W_), float("nan"), dtype=torch.float32, device=cuda)
+    d_c, d_u = torch.from_numpy(cond).to(cuda), torch.from_numpy(uncond).to(cuda)
+    edb.check(edb.lib().edb200_cfg_combine_rescaled(edb.ptr(d_u), edb.ptr(d_c), 4.0, 2, C_, H_, W_, edb.ptr(out),
+                                                    edb.current_stream()))
+    want = true_cfg(cond, uncond, 4.0, 2)
+    got = out.cpu().numpy()
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    assert not got[:, 2:4, 6:8].any()
+    with pytest.raises(edb.EdbError):
+        edb.check(edb.lib().edb200_cfg_combine_rescaled(edb.ptr(d_u), edb.ptr(d_c), 4.0, 2, C_, 11, W_, edb.ptr(out),
+                                                        edb.current_stream()))

@@ -72,3 +72,23 @@ def test_oracle_euler_update_is_the_reference_sampler_step():
     got = O.euler_update(x, v, 0.8, 0.55)
     assert np.allclose(got, x.astype(np.float64) + v.astype(np.float64) * (0.55 - 0.8), rtol=0, atol=2e-6)
     assert got.dtype == np.float32
+
+
+def test_oracle_qwen_guidance_combine_keeps_the_conditional_norm():
+    """Restated ed_qwen_apply_true_cfg (qwen_image_pipeline.cpp:29-85): every 2x2 patch of the result
+    has the conditional prediction's norm, and equal branches pass through unchanged."""
+    from oracle.qwen_oracle import true_cfg
+    rng = np.random.default_rng(6)
+    cond = rng.standard_normal((16, 8, 10), dtype=np.float32)
+    uncond = rng.standard_normal((16, 8, 10), dtype=np.float32)
+    out = true_cfg(cond, uncond, 4.0, 2)
+    for py in range(0, 8, 2):
+        for px in range(0, 10, 2):
+            a = np.linalg.norm(out[:, py:py + 2, px:px + 2].astype(np.float64))
+            b = np.linalg.norm(cond[:, py:py + 2, px:px + 2].astype(np.float64))
+            assert abs(a - b) <= 1e-5 * b
+    assert np.array_equal(true_cfg(cond, cond, 4.0, 2), cond)
+    # direction is the plain guided combine's
+    g = uncond + np.float32(4.0) * (cond - uncond)
+    cosv = np.sum(out.astype(np.float64) * g) / (np.linalg.norm(out.astype(np.float64)) * np.linalg.norm(g.astype(np.float64)))
+    assert cosv > 0.95
