@@ -172,6 +172,12 @@ __global__ void fused_residual_gate_kernel(const float4* __restrict__ res, const
 
 __global__ void advance_step_kernel(int* step) { *step += 1; }
 
+// SD3's form of the sampler update (sd3_pipeline.cpp:697): x += model_out * (sigma_next - sigma).
+__global__ void flow_update_kernel(float* __restrict__ x, const float* __restrict__ v, float dt, int64_t n) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] = __fadd_rn(x[i], __fmul_rn(v[i], dt));
+}
+
 // Sampler update of one step (flux_pipeline.cpp:1290-1297): every operation rounded on its own.
 // `sched` != NULL: sigma = sched[*step], sigma_next = sched[*step + 1], read on the device.
 __global__ void euler_update_kernel(float* __restrict__ x, const float* __restrict__ v, float sigma, float sigma_next,
@@ -382,6 +388,15 @@ edb200_status_t edb200_euler_update(float* x, const float* model_out, float sigm
         x, model_out, sigma, sigma_next, nullptr, nullptr, n);
     count_launch();
     return check_cuda(cudaGetLastError(), "euler_update launch");
+}
+
+edb200_status_t edb200_flow_update(float* x, const float* model_out, float sigma, float sigma_next, int64_t n,
+                                   void* stream) {
+    if (x == nullptr || model_out == nullptr || n <= 0) return fail(EDB200_ERR_INVALID, "flow_update: null or empty argument");
+    flow_update_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        x, model_out, sigma_next - sigma, n);
+    count_launch();
+    return check_cuda(cudaGetLastError(), "flow_update launch");
 }
 
 edb200_status_t edb200_euler_update_sched(float* x, const float* model_out, const float* sigmas, int* step, int64_t n,

@@ -104,6 +104,7 @@ _SIGS = {
     "edb200_fused_residual_gate": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_vp]),
     "edb200_euler_update": (C.c_int, [c_vp, c_vp, C.c_float, C.c_float, c_i64, c_vp]),
     "edb200_euler_update_sched": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_i64, c_vp]),
+    "edb200_flow_update": (C.c_int, [c_vp, c_vp, C.c_float, C.c_float, c_i64, c_vp]),
     "edb200_qk_norm_rope_pack": (C.c_int, [c_vp, C.c_int, c_i64, c_i64, c_i64, c_i64, c_i64, C.c_int, C.c_int,
                                            c_vp, c_vp, C.c_float, c_vp, c_i64, c_i64, c_vp, c_vp, c_vp, C.c_int,
                                            c_vp]),

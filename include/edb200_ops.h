@@ -212,6 +212,10 @@ EDB200_API edb200_status_t edb200_fused_residual_gate(const float* residual, con
  * f32, each operation rounded on its own in that order (no FMA contraction): the reference's bits. */
 EDB200_API edb200_status_t edb200_euler_update(float* x, const float* model_out, float sigma, float sigma_next, int64_t n,
                                     void* stream);
+/* SD3's form of the same update (src/dit_models/pipelines/sd3_pipeline.cpp:697):
+ * x += model_out * (sigma_next - sigma), f32, the difference, the product and the sum each rounded. */
+EDB200_API edb200_status_t edb200_flow_update(float* x, const float* model_out, float sigma, float sigma_next, int64_t n,
+                                   void* stream);
 /* The same update with the schedule on the device: sigma = sigmas[*step], sigma_next =
  * sigmas[*step + 1]; afterwards *step is incremented (a second, one-thread kernel).  Together with
  * edb200_flux_step_sched this makes one recorded step + update (edb200_graph_*) replayable for

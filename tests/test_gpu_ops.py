@@ -124,6 +124,13 @@ def test_euler_update_bit_exact(edb, cuda, sigma, sigma_next):
     edb.euler_update(dx, dev(v, cuda), sigma, sigma_next)
     want = O.euler_update(x, v, sigma, sigma_next)
     assert np.array_equal(dx.cpu().numpy().view(np.uint32), want.view(np.uint32))
+    # SD3's form: x += model_out * (sigma_next - sigma)
+    dx = dev(x, cuda)
+    edb.check(edb.lib().edb200_flow_update(edb.ptr(dx), edb.ptr(dev(v, cuda)), sigma, sigma_next, x.size,
+                                           edb.current_stream()))
+    dt = np.float32(np.float32(sigma_next) - np.float32(sigma))
+    want = (x + (v * dt).astype(np.float32)).astype(np.float32)
+    assert np.array_equal(dx.cpu().numpy().view(np.uint32), want.view(np.uint32))
 
 
 @pytest.mark.parametrize("h,dt", [(3072, "bf16"), (1536, "f32"), (5120, "f16")])
