@@ -51,6 +51,10 @@ private:
     int64_t bytes_ = 0;
 };
 
+// Loads every tensor of a GGUF file that `table` knows (edb200_gguf.cu).
+edb200_status_t load_gguf(ParamTable& table, const char* path, const char* strip_prefix, cudaStream_t stream,
+                          int* n_loaded);
+
 // One cudaMalloc carved into 256-byte aligned pieces.
 class Workspace {
 public:

@@ -302,6 +302,12 @@ edb200_status_t edb200_qwen_set_tensor(edb200_qwen_t* m, const char* name, int g
     return m->params.set(name, ggml_type, data, nbytes, on_device != 0, static_cast<cudaStream_t>(stream));
 }
 
+edb200_status_t edb200_qwen_load_gguf(edb200_qwen_t* m, const char* path, const char* strip_prefix, int* n_loaded,
+                                    void* stream) {
+    if (m == nullptr || path == nullptr) return fail(EDB200_ERR_INVALID, "qwen_load_gguf: null argument");
+    return load_gguf(m->params, path, strip_prefix, static_cast<cudaStream_t>(stream), n_loaded);
+}
+
 edb200_status_t edb200_qwen_init_random(edb200_qwen_t* m, uint64_t seed, float std, void* stream) {
     if (m == nullptr) return fail(EDB200_ERR_INVALID, "qwen_init_random: null model");
     return m->params.init_random(seed, std, static_cast<cudaStream_t>(stream));

@@ -206,6 +206,16 @@ _SIGS = {
     "edb200_flux_workspace_bytes": (c_i64, [c_vp]),
     "edb200_flux_prepare": (C.c_int, [c_vp, C.c_int, C.c_int, C.c_int, c_vp]),
     "edb200_flux_set_tap": (C.c_int, [c_vp, c_vp]),
+    "edb200_gguf_open": (C.c_int, [C.c_char_p, C.POINTER(c_vp)]),
+    "edb200_gguf_close": (None, [c_vp]),
+    "edb200_gguf_tensor_count": (C.c_int, [c_vp]),
+    "edb200_gguf_tensor_info": (C.c_int, [c_vp, C.c_int, C.c_char_p, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int),
+                                          C.POINTER(c_i64), C.POINTER(c_i64)]),
+    "edb200_gguf_tensor_data": (c_vp, [c_vp, C.c_int]),
+    "edb200_flux_load_gguf": (C.c_int, [c_vp, C.c_char_p, C.c_char_p, C.POINTER(C.c_int), c_vp]),
+    "edb200_sd3_load_gguf": (C.c_int, [c_vp, C.c_char_p, C.c_char_p, C.POINTER(C.c_int), c_vp]),
+    "edb200_qwen_load_gguf": (C.c_int, [c_vp, C.c_char_p, C.c_char_p, C.POINTER(C.c_int), c_vp]),
+    "edb200_wan_load_gguf": (C.c_int, [c_vp, C.c_char_p, C.c_char_p, C.POINTER(C.c_int), c_vp]),
     "edb200_flux_step": (C.c_int, [c_vp, c_vp, C.c_float, c_vp, c_vp, C.c_float, c_vp, c_vp]),
     "edb200_flux_step_sched": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, C.c_float, c_vp, c_vp]),
     "edb200_flux_compute_host": (C.c_int, [c_vp, c_vp, C.c_int, C.c_int, C.c_float, c_vp, C.c_int, c_vp, C.c_float,
@@ -292,6 +302,42 @@ def make_epilogue(out, bias=None, act=ACT_NONE, residual=None, gate=None, split_
 def mul_mat_q(w: QWeight, x, ep: Epilogue):
     check(lib().edb200_mul_mat_q(w.handle, ptr(x), torch_dtype_id(x), x.shape[0], x.stride(0), C.byref(ep),
                                  current_stream()))
+
+
+class GGUF:
+    """Read-only view of a GGUF file through the library's reader (no GPU needed)."""
+
+    def __init__(self, path):
+        h = c_vp()
+        check(lib().edb200_gguf_open(str(path).encode(), C.byref(h)))
+        self.handle = h
+
+    def __len__(self):
+        return lib().edb200_gguf_tensor_count(self.handle)
+
+    def tensor(self, i):
+        """(name, ggml_type, dims in ggml order, bytes) of tensor i; bytes is None for a type that is not read."""
+        name = C.create_string_buffer(512)
+        t, nd, nb = C.c_int(), C.c_int(), c_i64()
+        dims = (c_i64 * 4)()
+        check(lib().edb200_gguf_tensor_info(self.handle, i, name, 512, C.byref(t), C.byref(nd), dims, C.byref(nb)))
+        data = None
+        if nb.value >= 0:
+            data = C.string_at(lib().edb200_gguf_tensor_data(self.handle, i), nb.value)
+        return name.value.decode(), t.value, tuple(dims[d] for d in range(nd.value)), data
+
+    def close(self):
+        if getattr(self, "handle", None) and _lib is not None:
+            _lib.edb200_gguf_close(self.handle)
+            self.handle = None
+
+    __del__ = close
+
+
+def _load_gguf(fn, handle, path, strip_prefix):
+    n = C.c_int()
+    check(fn(handle, str(path).encode(), strip_prefix.encode() if strip_prefix else None, C.byref(n), current_stream()))
+    return n.value
 
 
 def euler_update(x, model_out, sigma, sigma_next):
@@ -389,6 +435,10 @@ class FluxModel:
 
     def init_random(self, seed=0, std=0.02):
         check(lib().edb200_flux_init_random(self.handle, seed, std, current_stream()))
+
+    def load_gguf(self, path, strip_prefix="model.diffusion_model."):
+        """Loads the tensors of a GGUF file this model has parameters for; returns how many were taken."""
+        return _load_gguf(lib().edb200_flux_load_gguf, self.handle, path, strip_prefix)
 
     def prepare(self, latent_h, latent_w, n_txt):
         check(lib().edb200_flux_prepare(self.handle, latent_h, latent_w, n_txt, current_stream()))
@@ -489,6 +539,10 @@ class QwenModel:
     def init_random(self, seed=0, std=0.02):
         check(lib().edb200_qwen_init_random(self.handle, seed, std, current_stream()))
 
+    def load_gguf(self, path, strip_prefix="model.diffusion_model."):
+        """Loads the tensors of a GGUF file this model has parameters for; returns how many were taken."""
+        return _load_gguf(lib().edb200_qwen_load_gguf, self.handle, path, strip_prefix)
+
     def set_comm(self, comm):
         self._comm = comm
         check(lib().edb200_qwen_set_comm(self.handle, comm.handle if comm is not None else None))
@@ -555,6 +609,10 @@ class SD3Model:
     def init_random(self, seed=0, std=0.02):
         check(lib().edb200_sd3_init_random(self.handle, seed, std, current_stream()))
 
+    def load_gguf(self, path, strip_prefix="model.diffusion_model."):
+        """Loads the tensors of a GGUF file this model has parameters for; returns how many were taken."""
+        return _load_gguf(lib().edb200_sd3_load_gguf, self.handle, path, strip_prefix)
+
     def set_tap(self, tap):
         self._tap = tap
         check(lib().edb200_sd3_set_tap(self.handle, ptr(tap)))
@@ -610,6 +668,10 @@ class WanModel:
 
     def init_random(self, seed=0, std=0.02):
         check(lib().edb200_wan_init_random(self.handle, seed, std, current_stream()))
+
+    def load_gguf(self, path, strip_prefix="model.diffusion_model."):
+        """Loads the tensors of a GGUF file this model has parameters for; returns how many were taken."""
+        return _load_gguf(lib().edb200_wan_load_gguf, self.handle, path, strip_prefix)
 
     def set_comm(self, comm):
         self._comm = comm

@@ -419,6 +419,21 @@ EDB200_API edb200_status_t edb200_sage_attention_sp(const void* q_f16, const voi
 EDB200_API edb200_status_t edb200_cfg_parallel_combine(edb200_comm_t* c, const float* mine, float scale,
                                                        float* gathered, float* out, int64_t n, void* stream);
 
+/* ------------------------------------------------------------ weight ingest
+ * Reader for GGUF files, the container the reference's converter writes and its loader reads
+ * (src/utils/model_io/gguf_io.cpp, src/core/runtime/model_loader.cpp).  The file is mapped; tensor
+ * data pointers stay valid until edb200_gguf_close.  ggml_type is the file's own type code
+ * (0 f32, 1 f16, 8 q8_0, 12 q4_K, 30 bf16, ...); dims are in ggml order (dims[0] = row length);
+ * nbytes is -1 for a type this library does not read.  Host code: no GPU is needed. */
+typedef struct edb200_gguf edb200_gguf_t;
+EDB200_API edb200_status_t edb200_gguf_open(const char* path, edb200_gguf_t** out);
+EDB200_API void edb200_gguf_close(edb200_gguf_t* g);
+EDB200_API int edb200_gguf_tensor_count(const edb200_gguf_t* g);
+EDB200_API edb200_status_t edb200_gguf_tensor_info(const edb200_gguf_t* g, int index, char* name, int name_cap,
+                                                   int* ggml_type, int* n_dims, int64_t* dims /* [4] */,
+                                                   int64_t* nbytes);
+EDB200_API const void* edb200_gguf_tensor_data(const edb200_gguf_t* g, int index);
+
 /* ------------------------------------------------- FLUX.1 denoise-step model
  * A whole-step replacement at the reference's model seam
  * DiffusionModel::compute(n_threads, DiffusionParams) -> sd::Tensor<float>
@@ -459,6 +474,12 @@ EDB200_API edb200_status_t edb200_flux_tensor_info(const edb200_flux_t* m, int i
  * for quantised weights, f32 for everything else. */
 EDB200_API edb200_status_t edb200_flux_set_tensor(edb200_flux_t* m, const char* name, int ggml_type, const void* data,
                                                   int64_t nbytes, int on_device, void* stream);
+/* Loads every tensor of a GGUF file this model has a parameter for (names compared after removing
+ * `strip_prefix`, e.g. "model.diffusion_model."; NULL = none); other tensors are skipped.  Quantised
+ * weights must be stored in the model's block type; f16 / bf16 vectors are widened to f32.
+ * *n_loaded (may be NULL) = tensors taken. */
+EDB200_API edb200_status_t edb200_flux_load_gguf(edb200_flux_t* m, const char* path, const char* strip_prefix,
+                                               int* n_loaded, void* stream);
 /* Synthetic weights N(0, std) generated and quantised on the device. */
 EDB200_API edb200_status_t edb200_flux_init_random(edb200_flux_t* m, uint64_t seed, float std, void* stream);
 EDB200_API int64_t edb200_flux_weight_bytes(const edb200_flux_t* m);
@@ -521,6 +542,12 @@ EDB200_API edb200_status_t edb200_sd3_tensor_info(const edb200_sd3_t* m, int ind
                                                   int* ggml_type, int64_t* n_out, int64_t* k, int64_t* nbytes);
 EDB200_API edb200_status_t edb200_sd3_set_tensor(edb200_sd3_t* m, const char* name, int ggml_type, const void* data,
                                                  int64_t nbytes, int on_device, void* stream);
+/* Loads every tensor of a GGUF file this model has a parameter for (names compared after removing
+ * `strip_prefix`, e.g. "model.diffusion_model."; NULL = none); other tensors are skipped.  Quantised
+ * weights must be stored in the model's block type; f16 / bf16 vectors are widened to f32.
+ * *n_loaded (may be NULL) = tensors taken. */
+EDB200_API edb200_status_t edb200_sd3_load_gguf(edb200_sd3_t* m, const char* path, const char* strip_prefix,
+                                               int* n_loaded, void* stream);
 EDB200_API edb200_status_t edb200_sd3_init_random(edb200_sd3_t* m, uint64_t seed, float std, void* stream);
 EDB200_API int64_t edb200_sd3_weight_bytes(const edb200_sd3_t* m);
 EDB200_API edb200_status_t edb200_sd3_prepare(edb200_sd3_t* m, int lat_h, int lat_w, int n_ctx, void* stream);
@@ -571,6 +598,12 @@ EDB200_API edb200_status_t edb200_qwen_tensor_info(const edb200_qwen_t* m, int i
                                                    int* ggml_type, int64_t* n_out, int64_t* k, int64_t* nbytes);
 EDB200_API edb200_status_t edb200_qwen_set_tensor(edb200_qwen_t* m, const char* name, int ggml_type, const void* data,
                                                   int64_t nbytes, int on_device, void* stream);
+/* Loads every tensor of a GGUF file this model has a parameter for (names compared after removing
+ * `strip_prefix`, e.g. "model.diffusion_model."; NULL = none); other tensors are skipped.  Quantised
+ * weights must be stored in the model's block type; f16 / bf16 vectors are widened to f32.
+ * *n_loaded (may be NULL) = tensors taken. */
+EDB200_API edb200_status_t edb200_qwen_load_gguf(edb200_qwen_t* m, const char* path, const char* strip_prefix,
+                                               int* n_loaded, void* stream);
 EDB200_API edb200_status_t edb200_qwen_init_random(edb200_qwen_t* m, uint64_t seed, float std, void* stream);
 EDB200_API int64_t edb200_qwen_weight_bytes(const edb200_qwen_t* m);
 EDB200_API edb200_status_t edb200_qwen_prepare(edb200_qwen_t* m, int lat_h, int lat_w, int n_txt, void* stream);
@@ -614,6 +647,12 @@ EDB200_API edb200_status_t edb200_wan_tensor_info(const edb200_wan_t* m, int ind
                                                   int* ggml_type, int64_t* n_out, int64_t* k, int64_t* nbytes);
 EDB200_API edb200_status_t edb200_wan_set_tensor(edb200_wan_t* m, const char* name, int ggml_type, const void* data,
                                                  int64_t nbytes, int on_device, void* stream);
+/* Loads every tensor of a GGUF file this model has a parameter for (names compared after removing
+ * `strip_prefix`, e.g. "model.diffusion_model."; NULL = none); other tensors are skipped.  Quantised
+ * weights must be stored in the model's block type; f16 / bf16 vectors are widened to f32.
+ * *n_loaded (may be NULL) = tensors taken. */
+EDB200_API edb200_status_t edb200_wan_load_gguf(edb200_wan_t* m, const char* path, const char* strip_prefix,
+                                               int* n_loaded, void* stream);
 EDB200_API edb200_status_t edb200_wan_init_random(edb200_wan_t* m, uint64_t seed, float std, void* stream);
 EDB200_API int64_t edb200_wan_weight_bytes(const edb200_wan_t* m);
 EDB200_API int64_t edb200_wan_workspace_bytes(const edb200_wan_t* m);
