@@ -55,6 +55,10 @@ private:
 edb200_status_t load_gguf(ParamTable& table, const char* path, const char* strip_prefix, cudaStream_t stream,
                           int* n_loaded);
 
+// The same from a safetensors file; quantised parameters are encoded on the device (edb200_safetensors.cu).
+edb200_status_t load_safetensors(ParamTable& table, const char* path, const char* strip_prefix, cudaStream_t stream,
+                                 int* n_loaded);
+
 // One cudaMalloc carved into 256-byte aligned pieces.
 class Workspace {
 public:

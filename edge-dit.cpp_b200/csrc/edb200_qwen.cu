@@ -308,6 +308,12 @@ edb200_status_t edb200_qwen_load_gguf(edb200_qwen_t* m, const char* path, const 
     return load_gguf(m->params, path, strip_prefix, static_cast<cudaStream_t>(stream), n_loaded);
 }
 
+edb200_status_t edb200_qwen_load_safetensors(edb200_qwen_t* m, const char* path, const char* strip_prefix, int* n_loaded,
+                                           void* stream) {
+    if (m == nullptr || path == nullptr) return fail(EDB200_ERR_INVALID, "qwen_load_safetensors: null argument");
+    return load_safetensors(m->params, path, strip_prefix, static_cast<cudaStream_t>(stream), n_loaded);
+}
+
 edb200_status_t edb200_qwen_init_random(edb200_qwen_t* m, uint64_t seed, float std, void* stream) {
     if (m == nullptr) return fail(EDB200_ERR_INVALID, "qwen_init_random: null model");
     return m->params.init_random(seed, std, static_cast<cudaStream_t>(stream));

@@ -282,6 +282,12 @@ edb200_status_t edb200_sd3_load_gguf(edb200_sd3_t* m, const char* path, const ch
     return load_gguf(m->params, path, strip_prefix, static_cast<cudaStream_t>(stream), n_loaded);
 }
 
+edb200_status_t edb200_sd3_load_safetensors(edb200_sd3_t* m, const char* path, const char* strip_prefix, int* n_loaded,
+                                           void* stream) {
+    if (m == nullptr || path == nullptr) return fail(EDB200_ERR_INVALID, "sd3_load_safetensors: null argument");
+    return load_safetensors(m->params, path, strip_prefix, static_cast<cudaStream_t>(stream), n_loaded);
+}
+
 edb200_status_t edb200_sd3_init_random(edb200_sd3_t* m, uint64_t seed, float std, void* stream) {
     if (m == nullptr) return fail(EDB200_ERR_INVALID, "sd3_init_random: null model");
     return m->params.init_random(seed, std, static_cast<cudaStream_t>(stream));

@@ -212,6 +212,16 @@ _SIGS = {
     "edb200_gguf_tensor_info": (C.c_int, [c_vp, C.c_int, C.c_char_p, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int),
                                           C.POINTER(c_i64), C.POINTER(c_i64)]),
     "edb200_gguf_tensor_data": (c_vp, [c_vp, C.c_int]),
+    "edb200_safetensors_open": (C.c_int, [C.c_char_p, C.POINTER(c_vp)]),
+    "edb200_safetensors_close": (None, [c_vp]),
+    "edb200_safetensors_tensor_count": (C.c_int, [c_vp]),
+    "edb200_safetensors_tensor_info": (C.c_int, [c_vp, C.c_int, C.c_char_p, C.c_int, C.c_char_p, C.c_int,
+                                                 C.POINTER(C.c_int), C.POINTER(c_i64), C.POINTER(c_i64)]),
+    "edb200_safetensors_tensor_data": (c_vp, [c_vp, C.c_int]),
+    "edb200_flux_load_safetensors": (C.c_int, [c_vp, C.c_char_p, C.c_char_p, C.POINTER(C.c_int), c_vp]),
+    "edb200_sd3_load_safetensors": (C.c_int, [c_vp, C.c_char_p, C.c_char_p, C.POINTER(C.c_int), c_vp]),
+    "edb200_qwen_load_safetensors": (C.c_int, [c_vp, C.c_char_p, C.c_char_p, C.POINTER(C.c_int), c_vp]),
+    "edb200_wan_load_safetensors": (C.c_int, [c_vp, C.c_char_p, C.c_char_p, C.POINTER(C.c_int), c_vp]),
     "edb200_flux_load_gguf": (C.c_int, [c_vp, C.c_char_p, C.c_char_p, C.POINTER(C.c_int), c_vp]),
     "edb200_sd3_load_gguf": (C.c_int, [c_vp, C.c_char_p, C.c_char_p, C.POINTER(C.c_int), c_vp]),
     "edb200_qwen_load_gguf": (C.c_int, [c_vp, C.c_char_p, C.c_char_p, C.POINTER(C.c_int), c_vp]),
@@ -334,6 +344,34 @@ class GGUF:
     __del__ = close
 
 
+class SafeTensors:
+    """Read-only view of a safetensors file through the library's reader (no GPU needed)."""
+
+    def __init__(self, path):
+        h = c_vp()
+        check(lib().edb200_safetensors_open(str(path).encode(), C.byref(h)))
+        self.handle = h
+
+    def __len__(self):
+        return lib().edb200_safetensors_tensor_count(self.handle)
+
+    def tensor(self, i):
+        """(name, dtype string, row-major shape, bytes) of tensor i."""
+        name, dtype = C.create_string_buffer(512), C.create_string_buffer(16)
+        nd, nb = C.c_int(), c_i64()
+        dims = (c_i64 * 8)()
+        check(lib().edb200_safetensors_tensor_info(self.handle, i, name, 512, dtype, 16, C.byref(nd), dims, C.byref(nb)))
+        data = C.string_at(lib().edb200_safetensors_tensor_data(self.handle, i), nb.value)
+        return name.value.decode(), dtype.value.decode(), tuple(dims[d] for d in range(nd.value)), data
+
+    def close(self):
+        if getattr(self, "handle", None) and _lib is not None:
+            _lib.edb200_safetensors_close(self.handle)
+            self.handle = None
+
+    __del__ = close
+
+
 def _load_gguf(fn, handle, path, strip_prefix):
     n = C.c_int()
     check(fn(handle, str(path).encode(), strip_prefix.encode() if strip_prefix else None, C.byref(n), current_stream()))
@@ -440,6 +478,10 @@ class FluxModel:
         """Loads the tensors of a GGUF file this model has parameters for; returns how many were taken."""
         return _load_gguf(lib().edb200_flux_load_gguf, self.handle, path, strip_prefix)
 
+    def load_safetensors(self, path, strip_prefix="model.diffusion_model."):
+        """Loads (and, for quantised parameters, encodes on the device) the tensors of a safetensors file."""
+        return _load_gguf(lib().edb200_flux_load_safetensors, self.handle, path, strip_prefix)
+
     def prepare(self, latent_h, latent_w, n_txt):
         check(lib().edb200_flux_prepare(self.handle, latent_h, latent_w, n_txt, current_stream()))
 
@@ -543,6 +585,10 @@ class QwenModel:
         """Loads the tensors of a GGUF file this model has parameters for; returns how many were taken."""
         return _load_gguf(lib().edb200_qwen_load_gguf, self.handle, path, strip_prefix)
 
+    def load_safetensors(self, path, strip_prefix="model.diffusion_model."):
+        """Loads (and, for quantised parameters, encodes on the device) the tensors of a safetensors file."""
+        return _load_gguf(lib().edb200_qwen_load_safetensors, self.handle, path, strip_prefix)
+
     def set_comm(self, comm):
         self._comm = comm
         check(lib().edb200_qwen_set_comm(self.handle, comm.handle if comm is not None else None))
@@ -613,6 +659,10 @@ class SD3Model:
         """Loads the tensors of a GGUF file this model has parameters for; returns how many were taken."""
         return _load_gguf(lib().edb200_sd3_load_gguf, self.handle, path, strip_prefix)
 
+    def load_safetensors(self, path, strip_prefix="model.diffusion_model."):
+        """Loads (and, for quantised parameters, encodes on the device) the tensors of a safetensors file."""
+        return _load_gguf(lib().edb200_sd3_load_safetensors, self.handle, path, strip_prefix)
+
     def set_tap(self, tap):
         self._tap = tap
         check(lib().edb200_sd3_set_tap(self.handle, ptr(tap)))
@@ -672,6 +722,10 @@ class WanModel:
     def load_gguf(self, path, strip_prefix="model.diffusion_model."):
         """Loads the tensors of a GGUF file this model has parameters for; returns how many were taken."""
         return _load_gguf(lib().edb200_wan_load_gguf, self.handle, path, strip_prefix)
+
+    def load_safetensors(self, path, strip_prefix="model.diffusion_model."):
+        """Loads (and, for quantised parameters, encodes on the device) the tensors of a safetensors file."""
+        return _load_gguf(lib().edb200_wan_load_safetensors, self.handle, path, strip_prefix)
 
     def set_comm(self, comm):
         self._comm = comm

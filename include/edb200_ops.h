@@ -434,6 +434,17 @@ EDB200_API edb200_status_t edb200_gguf_tensor_info(const edb200_gguf_t* g, int i
                                                    int64_t* nbytes);
 EDB200_API const void* edb200_gguf_tensor_data(const edb200_gguf_t* g, int index);
 
+/* Reader for safetensors files (src/utils/model_io/safetensors_io.h): name, dtype string ("F32", "F16",
+ * "BF16", ...), row-major shape (up to 8 extents) and the mapped data of every tensor.  Host code. */
+typedef struct edb200_safetensors edb200_safetensors_t;
+EDB200_API edb200_status_t edb200_safetensors_open(const char* path, edb200_safetensors_t** out);
+EDB200_API void edb200_safetensors_close(edb200_safetensors_t* f);
+EDB200_API int edb200_safetensors_tensor_count(const edb200_safetensors_t* f);
+EDB200_API edb200_status_t edb200_safetensors_tensor_info(const edb200_safetensors_t* f, int index, char* name,
+                                                          int name_cap, char* dtype, int dtype_cap, int* n_dims,
+                                                          int64_t* dims /* [8] */, int64_t* nbytes);
+EDB200_API const void* edb200_safetensors_tensor_data(const edb200_safetensors_t* f, int index);
+
 /* ------------------------------------------------- FLUX.1 denoise-step model
  * A whole-step replacement at the reference's model seam
  * DiffusionModel::compute(n_threads, DiffusionParams) -> sd::Tensor<float>
@@ -480,6 +491,11 @@ EDB200_API edb200_status_t edb200_flux_set_tensor(edb200_flux_t* m, const char* 
  * *n_loaded (may be NULL) = tensors taken. */
 EDB200_API edb200_status_t edb200_flux_load_gguf(edb200_flux_t* m, const char* path, const char* strip_prefix,
                                                int* n_loaded, void* stream);
+/* The same from a safetensors file (F32 / F16 / BF16 tensors).  Parameters the model keeps quantised are
+ * encoded on the device in its block type while they load: q8_0 by ggml's rule (bit for bit), q4_K by this
+ * library's min/max encoder. */
+EDB200_API edb200_status_t edb200_flux_load_safetensors(edb200_flux_t* m, const char* path, const char* strip_prefix,
+                                                      int* n_loaded, void* stream);
 /* Synthetic weights N(0, std) generated and quantised on the device. */
 EDB200_API edb200_status_t edb200_flux_init_random(edb200_flux_t* m, uint64_t seed, float std, void* stream);
 EDB200_API int64_t edb200_flux_weight_bytes(const edb200_flux_t* m);
@@ -548,6 +564,11 @@ EDB200_API edb200_status_t edb200_sd3_set_tensor(edb200_sd3_t* m, const char* na
  * *n_loaded (may be NULL) = tensors taken. */
 EDB200_API edb200_status_t edb200_sd3_load_gguf(edb200_sd3_t* m, const char* path, const char* strip_prefix,
                                                int* n_loaded, void* stream);
+/* The same from a safetensors file (F32 / F16 / BF16 tensors).  Parameters the model keeps quantised are
+ * encoded on the device in its block type while they load: q8_0 by ggml's rule (bit for bit), q4_K by this
+ * library's min/max encoder. */
+EDB200_API edb200_status_t edb200_sd3_load_safetensors(edb200_sd3_t* m, const char* path, const char* strip_prefix,
+                                                      int* n_loaded, void* stream);
 EDB200_API edb200_status_t edb200_sd3_init_random(edb200_sd3_t* m, uint64_t seed, float std, void* stream);
 EDB200_API int64_t edb200_sd3_weight_bytes(const edb200_sd3_t* m);
 EDB200_API edb200_status_t edb200_sd3_prepare(edb200_sd3_t* m, int lat_h, int lat_w, int n_ctx, void* stream);
@@ -604,6 +625,11 @@ EDB200_API edb200_status_t edb200_qwen_set_tensor(edb200_qwen_t* m, const char* 
  * *n_loaded (may be NULL) = tensors taken. */
 EDB200_API edb200_status_t edb200_qwen_load_gguf(edb200_qwen_t* m, const char* path, const char* strip_prefix,
                                                int* n_loaded, void* stream);
+/* The same from a safetensors file (F32 / F16 / BF16 tensors).  Parameters the model keeps quantised are
+ * encoded on the device in its block type while they load: q8_0 by ggml's rule (bit for bit), q4_K by this
+ * library's min/max encoder. */
+EDB200_API edb200_status_t edb200_qwen_load_safetensors(edb200_qwen_t* m, const char* path, const char* strip_prefix,
+                                                      int* n_loaded, void* stream);
 EDB200_API edb200_status_t edb200_qwen_init_random(edb200_qwen_t* m, uint64_t seed, float std, void* stream);
 EDB200_API int64_t edb200_qwen_weight_bytes(const edb200_qwen_t* m);
 EDB200_API edb200_status_t edb200_qwen_prepare(edb200_qwen_t* m, int lat_h, int lat_w, int n_txt, void* stream);
@@ -653,6 +679,11 @@ EDB200_API edb200_status_t edb200_wan_set_tensor(edb200_wan_t* m, const char* na
  * *n_loaded (may be NULL) = tensors taken. */
 EDB200_API edb200_status_t edb200_wan_load_gguf(edb200_wan_t* m, const char* path, const char* strip_prefix,
                                                int* n_loaded, void* stream);
+/* The same from a safetensors file (F32 / F16 / BF16 tensors).  Parameters the model keeps quantised are
+ * encoded on the device in its block type while they load: q8_0 by ggml's rule (bit for bit), q4_K by this
+ * library's min/max encoder. */
+EDB200_API edb200_status_t edb200_wan_load_safetensors(edb200_wan_t* m, const char* path, const char* strip_prefix,
+                                                      int* n_loaded, void* stream);
 EDB200_API edb200_status_t edb200_wan_init_random(edb200_wan_t* m, uint64_t seed, float std, void* stream);
 EDB200_API int64_t edb200_wan_weight_bytes(const edb200_wan_t* m);
 EDB200_API int64_t edb200_wan_workspace_bytes(const edb200_wan_t* m);

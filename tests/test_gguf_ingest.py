@@ -130,3 +130,95 @@ def test_flux_loaded_from_gguf_equals_tensor_by_tensor_load(edb, cuda, tmp_path)
     with pytest.raises(edb.EdbError) as ei:
         c.load_gguf(path)
     assert "convert the file first" in str(ei.value)
+
+
+# ------------------------------------------------------------------ safetensors
+
+def test_safetensors_reader_matches_the_safetensors_package(edb, tmp_path):
+    st = pytest.importorskip("safetensors.numpy")
+    rng = np.random.default_rng(61)
+    tensors = {
+        "model.diffusion_model.a.weight": rng.standard_normal((12, 64), dtype=np.float32),
+        "model.diffusion_model.a.bias": rng.standard_normal(12, dtype=np.float32).astype(np.float16),
+        "other.ids": np.arange(10, dtype=np.int64),
+        "scalar": np.array(3.5, dtype=np.float32),
+    }
+    path = tmp_path / "w.safetensors"
+    st.save_file(tensors, str(path), metadata={"format": "pt", "note": "braces } and [ in \"strings\""})
+    f = edb.SafeTensors(path)
+    assert len(f) == len(tensors)
+    names = {"float32": "F32", "float16": "F16", "int64": "I64"}
+    seen = set()
+    for i in range(len(f)):
+        name, dtype, shape, data = f.tensor(i)
+        a = tensors[name]
+        seen.add(name)
+        assert dtype == names[a.dtype.name]
+        assert shape == a.shape
+        assert data == a.tobytes()
+    assert seen == set(tensors)
+    f.close()
+
+
+def test_safetensors_reader_rejects_malformed_files(edb, tmp_path):
+    st = pytest.importorskip("safetensors.numpy")
+    good = tmp_path / "g.safetensors"
+    st.save_file({"w": np.ones((4, 8), dtype=np.float32)}, str(good))
+    raw = good.read_bytes()
+    hlen = int.from_bytes(raw[:8], "little")
+    header = raw[8:8 + hlen]
+    cases = {
+        "header length": (hlen + 10_000).to_bytes(8, "little") + raw[8:],
+        "truncated data": raw[:-16],
+        "not json": raw[:8] + b"[" + header[1:] + raw[8 + hlen:],
+        "offsets": raw[:8] + header.replace(b"128", b"124") + raw[8 + hlen:],
+        "short": raw[:6],
+    }
+    assert b"128" in header
+    for what, blob in cases.items():
+        p = tmp_path / "bad.safetensors"
+        p.write_bytes(blob)
+        with pytest.raises(edb.EdbError):
+            edb.SafeTensors(p)
+
+
+@pytest.mark.gpu
+def test_flux_loaded_from_safetensors_quantises_like_ggml(edb, cuda, tmp_path):
+    """An unquantised checkpoint: the loader encodes q8_0 on the device by ggml's rule, so the model
+    equals one given the oracle's q8_0 blocks of the same f32 weights."""
+    import torch
+    st = pytest.importorskip("safetensors.numpy")
+    from oracle.flux_oracle import FluxConfig, flux_tensor_specs, _name_seed
+    cfg = FluxConfig(hidden_size=512, num_heads=4, depth=1, depth_single_blocks=1, context_in_dim=256, vec_in_dim=64)
+    f32, blocks = {}, {}
+    for name, shape, quant in flux_tensor_specs(cfg):
+        rng = np.random.Generator(np.random.Philox(_name_seed(23, name)))
+        w = (rng.standard_normal(shape, dtype=np.float32) * np.float32(0.02)).astype(np.float32)
+        if name.endswith(".scale"):
+            w = (w + np.float32(1.0)).astype(np.float32)
+        f32["model.diffusion_model." + name] = w
+        blocks[name] = (cfg.wtype, O.quantize(w, cfg.wtype)) if quant else (O.GGML_TYPE_F32, w)
+    path = tmp_path / "flux.safetensors"
+    st.save_file(f32, str(path))
+
+    def make():
+        return edb.FluxModel(hidden_size=cfg.hidden_size, num_heads=cfg.num_heads, depth=cfg.depth,
+                             depth_single_blocks=cfg.depth_single_blocks, mlp_hidden=cfg.mlp_hidden,
+                             in_channels=cfg.in_channels, context_in_dim=cfg.context_in_dim,
+                             vec_in_dim=cfg.vec_in_dim, axes_dim=cfg.axes_dim, wtype=cfg.wtype)
+    a, b = make(), make()
+    a.load_numpy(blocks)
+    assert b.load_safetensors(path) == len(blocks)
+    rng = np.random.default_rng(4)
+    lat = torch.from_numpy(rng.standard_normal((16, 16, 16), dtype=np.float32)).to(cuda)
+    ctx = torch.from_numpy(rng.standard_normal((12, 256), dtype=np.float32)).to(cuda)
+    y = torch.from_numpy(rng.standard_normal(64, dtype=np.float32)).to(cuda)
+    outs = []
+    for m in (a, b):
+        m.prepare(16, 16, 12)
+        out = torch.empty_like(lat)
+        m.step(lat, 0.5, ctx, y, 3.5, out)
+        torch.cuda.synchronize()
+        outs.append(out.cpu().numpy())
+    assert np.isfinite(outs[0]).all()
+    assert np.array_equal(outs[0], outs[1])
