@@ -128,6 +128,78 @@ struct Json {
     }
 };
 
+// Shard files named by a `*.safetensors.index.json` ({"metadata": {...}, "weight_map": {tensor: file}}),
+// each once, in order of first appearance, resolved against the index file's directory.
+edb200_status_t index_shards(const char* path, std::vector<std::string>& files) {
+    files.clear();
+    const int fd = open(path, O_RDONLY);
+    if (fd < 0) return fail(EDB200_ERR_INVALID, "safetensors index: cannot open '%s'", path);
+    struct stat st;
+    std::string text;
+    if (fstat(fd, &st) == 0 && st.st_size > 0 && st.st_size < (1 << 28)) {
+        text.resize(static_cast<size_t>(st.st_size));
+        size_t got = 0;
+        while (got < text.size()) {
+            const ssize_t r = read(fd, &text[got], text.size() - got);
+            if (r <= 0) break;
+            got += static_cast<size_t>(r);
+        }
+        text.resize(got);
+    }
+    close(fd);
+    std::string dir(path);
+    const size_t slash = dir.find_last_of('/');
+    dir = slash == std::string::npos ? std::string() : dir.substr(0, slash + 1);
+    Json j{text.data(), text.data() + text.size()};
+    bool found = false;
+    if (!j.eat('{')) return fail(EDB200_ERR_INVALID, "safetensors index '%s': not a JSON object", path);
+    if (!j.peek('}')) {
+        do {
+            const std::string key = j.str();
+            if (!j.ok || !j.eat(':')) break;
+            if (key != "weight_map") {
+                j.skip();
+                continue;
+            }
+            found = true;
+            if (!j.eat('{')) {
+                j.ok = false;
+                break;
+            }
+            if (!j.peek('}')) {
+                do {
+                    j.str();   // tensor name
+                    if (!j.ok || !j.eat(':')) {
+                        j.ok = false;
+                        break;
+                    }
+                    const std::string file = j.str();
+                    if (!j.ok) break;
+                    if (file.empty() || file.find('/') != std::string::npos || file.find("..") != std::string::npos) {
+                        return fail(EDB200_ERR_INVALID, "safetensors index '%s': shard name '%s' is not a plain file name",
+                                    path, file.c_str());
+                    }
+                    const std::string full = dir + file;
+                    bool seen = false;
+                    for (const auto& f : files) seen = seen || f == full;
+                    if (!seen) files.push_back(full);
+                } while (j.ok && j.eat(','));
+            }
+            if (!j.eat('}')) j.ok = false;
+        } while (j.ok && j.eat(','));
+    }
+    if (!j.ok || !found || files.empty()) {
+        return fail(EDB200_ERR_INVALID, "safetensors index '%s': no readable weight_map", path);
+    }
+    return EDB200_OK;
+}
+
+bool is_index(const char* path) {
+    static const char kSuffix[] = ".index.json";
+    const size_t n = strlen(path), m = sizeof(kSuffix) - 1;
+    return n >= m && strcmp(path + n - m, kSuffix) == 0;
+}
+
 int dtype_bytes(const std::string& d) {
     if (d == "F32" || d == "I32" || d == "U32") return 4;
     if (d == "F16" || d == "BF16" || d == "I16" || d == "U16") return 2;
@@ -145,6 +217,20 @@ int dtype_bytes(const std::string& d) {
 edb200_status_t load_safetensors(ParamTable& table, const char* path, const char* strip_prefix, cudaStream_t stream,
                                  int* n_loaded) {
     if (n_loaded) *n_loaded = 0;
+    if (is_index(path)) {   // a sharded checkpoint: every shard of the index in turn
+        std::vector<std::string> files;
+        edb200_status_t ist = index_shards(path, files);
+        if (ist != EDB200_OK) return ist;
+        int total = 0;
+        for (const auto& file : files) {
+            int n = 0;
+            ist = load_safetensors(table, file.c_str(), strip_prefix, stream, &n);
+            if (ist != EDB200_OK) return ist;
+            total += n;
+        }
+        if (n_loaded) *n_loaded = total;
+        return EDB200_OK;
+    }
     edb200_safetensors_t* f = nullptr;
     edb200_status_t st = edb200_safetensors_open(path, &f);
     if (st != EDB200_OK) return st;
@@ -319,6 +405,26 @@ edb200_status_t edb200_safetensors_open(const char* path, edb200_safetensors_t**
     }
     if (!j.ok || !j.eat('}')) return bail("malformed header");
     *out = f;
+    return EDB200_OK;
+}
+
+edb200_status_t edb200_safetensors_index_files(const char* index_path, char* out, int out_cap, int* n_files) {
+    if (index_path == nullptr || out == nullptr || out_cap <= 0) {
+        return fail(EDB200_ERR_INVALID, "safetensors_index_files: null argument");
+    }
+    std::vector<std::string> files;
+    edb200_status_t st = index_shards(index_path, files);
+    if (st != EDB200_OK) return st;
+    std::string joined;
+    for (const auto& f : files) {
+        joined += f;
+        joined.push_back('\n');
+    }
+    if (static_cast<int>(joined.size()) >= out_cap) {
+        return fail(EDB200_ERR_INVALID, "safetensors_index_files: %d bytes needed, %d given", (int)joined.size() + 1, out_cap);
+    }
+    memcpy(out, joined.c_str(), joined.size() + 1);
+    if (n_files) *n_files = static_cast<int>(files.size());
     return EDB200_OK;
 }
 

@@ -218,6 +218,7 @@ _SIGS = {
     "edb200_safetensors_tensor_info": (C.c_int, [c_vp, C.c_int, C.c_char_p, C.c_int, C.c_char_p, C.c_int,
                                                  C.POINTER(C.c_int), C.POINTER(c_i64), C.POINTER(c_i64)]),
     "edb200_safetensors_tensor_data": (c_vp, [c_vp, C.c_int]),
+    "edb200_safetensors_index_files": (C.c_int, [C.c_char_p, C.c_char_p, C.c_int, C.POINTER(C.c_int)]),
     "edb200_flux_load_safetensors": (C.c_int, [c_vp, C.c_char_p, C.c_char_p, C.POINTER(C.c_int), c_vp]),
     "edb200_sd3_load_safetensors": (C.c_int, [c_vp, C.c_char_p, C.c_char_p, C.POINTER(C.c_int), c_vp]),
     "edb200_qwen_load_safetensors": (C.c_int, [c_vp, C.c_char_p, C.c_char_p, C.POINTER(C.c_int), c_vp]),
@@ -370,6 +371,16 @@ class SafeTensors:
             self.handle = None
 
     __del__ = close
+
+
+def safetensors_index_files(index_path):
+    """Shard files named by a *.safetensors.index.json, in order of first appearance."""
+    buf = C.create_string_buffer(1 << 16)
+    n = C.c_int()
+    check(lib().edb200_safetensors_index_files(str(index_path).encode(), buf, len(buf), C.byref(n)))
+    files = buf.value.decode().splitlines()
+    assert len(files) == n.value
+    return files
 
 
 def _load_gguf(fn, handle, path, strip_prefix):

@@ -444,6 +444,10 @@ EDB200_API edb200_status_t edb200_safetensors_tensor_info(const edb200_safetenso
                                                           int name_cap, char* dtype, int dtype_cap, int* n_dims,
                                                           int64_t* dims /* [8] */, int64_t* nbytes);
 EDB200_API const void* edb200_safetensors_tensor_data(const edb200_safetensors_t* f, int index);
+/* The shard files a `*.safetensors.index.json` names in its weight_map (src/core/runtime/model_loader.cpp:296-327),
+ * each once, resolved against the index's directory, written to `out` one per line.  The
+ * edb200_*_load_safetensors calls accept such an index in place of a single file. */
+EDB200_API edb200_status_t edb200_safetensors_index_files(const char* index_path, char* out, int out_cap, int* n_files);
 
 /* ------------------------------------------------- FLUX.1 denoise-step model
  * A whole-step replacement at the reference's model seam

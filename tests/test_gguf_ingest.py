@@ -1,5 +1,6 @@
-"""Weight ingest: the library's GGUF reader against files written by gguf-py (CPU), and a model
-loaded from such a file against the same model loaded tensor by tensor (GPU)."""
+"""Weight ingest: the library's GGUF and safetensors readers against files written by gguf-py and the
+safetensors package (CPU), and models loaded from such files against the same model loaded tensor by
+tensor (GPU)."""
 import numpy as np
 import pytest
 
@@ -222,3 +223,23 @@ def test_flux_loaded_from_safetensors_quantises_like_ggml(edb, cuda, tmp_path):
         outs.append(out.cpu().numpy())
     assert np.isfinite(outs[0]).all()
     assert np.array_equal(outs[0], outs[1])
+
+
+def test_safetensors_index_lists_each_shard_once(edb, tmp_path):
+    import json
+    index = tmp_path / "diffusion_pytorch_model.safetensors.index.json"
+    index.write_text(json.dumps({
+        "metadata": {"total_size": 123, "note": "a } brace"},
+        "weight_map": {
+            "a.weight": "diffusion_pytorch_model-00001-of-00002.safetensors",
+            "a.bias": "diffusion_pytorch_model-00001-of-00002.safetensors",
+            "b.weight": "diffusion_pytorch_model-00002-of-00002.safetensors",
+        },
+    }, indent=2))
+    files = edb.safetensors_index_files(index)
+    assert files == [str(tmp_path / "diffusion_pytorch_model-00001-of-00002.safetensors"),
+                     str(tmp_path / "diffusion_pytorch_model-00002-of-00002.safetensors")]
+    for bad in ({"weight_map": {"a": "../escape.safetensors"}}, {"weight_map": {}}, {"metadata": {}}, [1, 2]):
+        index.write_text(json.dumps(bad))
+        with pytest.raises(edb.EdbError):
+            edb.safetensors_index_files(index)
