@@ -136,7 +136,10 @@ __global__ void cfg_combine_kernel(const float4* __restrict__ u, const float4* _
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n4) return;
     const float4 a = u[i], b = c[i];
-    o[i] = make_float4(a.x + s * (b.x - a.x), a.y + s * (b.y - a.y), a.z + s * (b.z - a.z), a.w + s * (b.w - a.w));
+    // uncond + scale * (cond - uncond), each operation rounded on its own like the reference's tensor
+    // arithmetic (flux_pipeline.cpp:1258): no FMA contraction
+    o[i] = make_float4(__fadd_rn(a.x, __fmul_rn(s, __fsub_rn(b.x, a.x))), __fadd_rn(a.y, __fmul_rn(s, __fsub_rn(b.y, a.y))),
+                       __fadd_rn(a.z, __fmul_rn(s, __fsub_rn(b.z, a.z))), __fadd_rn(a.w, __fmul_rn(s, __fsub_rn(b.w, a.w))));
 }
 
 // Qwen-Image's guidance combine (ed_qwen_apply_true_cfg, src/dit_models/pipelines/qwen_image_pipeline.cpp:29-85):

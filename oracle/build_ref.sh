@@ -1,6 +1,7 @@
 #!/bin/sh
-# Compiles the reference's header-only CPU callbacks, from where they lie in the reference
-# tree, against ref_shim/ggml.h into oracle/_ref/libedref_cpu.so.  Test infrastructure.
+# Compiles the reference's header-only CPU callbacks (against ref_shim/ggml.h) and its tensor class
+# (src/utils/tensor.hpp), from where they lie in the reference tree, into oracle/_ref/libedref_cpu.so.
+# Test infrastructure.
 # Usage: sh oracle/build_ref.sh [reference root]
 set -e
 HERE="$(cd "$(dirname "$0")" && pwd)"
@@ -11,6 +12,6 @@ if [ ! -f "$SRC/ed_ggml_modulation_ext.hpp" ]; then
     exit 0
 fi
 mkdir -p "$HERE/_ref"
-g++ -O2 -std=c++17 -fPIC -shared -ffp-contract=off -I "$HERE/ref_shim" -I "$SRC" \
-    "$HERE/ref_driver.cpp" -o "$HERE/_ref/libedref_cpu.so"
+g++ -O2 -std=c++17 -fPIC -shared -ffp-contract=off -I "$HERE/ref_shim" -I "$SRC" -I "$REF/src" \
+    "$HERE/ref_driver.cpp" "$HERE/ref_tensor_driver.cpp" -o "$HERE/_ref/libedref_cpu.so"
 echo "$HERE/_ref/libedref_cpu.so"

@@ -266,6 +266,22 @@ def euler_update(x: np.ndarray, model_out: np.ndarray, sigma: float, sigma_next:
     return (x + (d * (f(sigma_next) - f(sigma))).astype(f)).astype(f)
 
 
+def flow_update(x: np.ndarray, model_out: np.ndarray, sigma: float, sigma_next: float) -> np.ndarray:
+    """SD3's per-step update x += model_out * (sigma_next - sigma)
+    (src/dit_models/pipelines/sd3_pipeline.cpp:697), float32 operation by operation."""
+    f = np.float32
+    dt = f(f(sigma_next) - f(sigma))
+    return (x.astype(f) + (model_out.astype(f) * dt).astype(f)).astype(f)
+
+
+def cfg_combine(uncond: np.ndarray, cond: np.ndarray, cfg_scale: float) -> np.ndarray:
+    """uncond + cfg_scale * (cond - uncond) (src/dit_models/pipelines/flux_pipeline.cpp:1258),
+    float32 operation by operation."""
+    f = np.float32
+    u = uncond.astype(f)
+    return (u + (f(cfg_scale) * (cond.astype(f) - u).astype(f)).astype(f)).astype(f)
+
+
 def gelu_tanh(x: np.ndarray) -> np.ndarray:
     """0.5*x*(1+tanh(sqrt(2/pi)*x*(1+0.044715*x*x)))
     (src/core/backend/ggml/ed_ggml_sp_flux_ext.hpp:675-679; ggml_gelu call site

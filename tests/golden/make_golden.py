@@ -1,4 +1,5 @@
-"""Generates tests/golden/ref_callbacks.npz: outputs of the reference's own CPU callbacks
+"""Generates tests/golden/ref_callbacks.npz: outputs of the reference's own CPU callbacks and of
+the pipelines' per-step latent arithmetic evaluated with the reference's tensor class
 (oracle/_ref/libedref_cpu.so, built by oracle/build_ref.sh from the reference tree) on
 seeded inputs.  Run where the reference tree is available:
 
@@ -21,9 +22,18 @@ def load_ref():
     lib.ref_fused_residual_gate.argtypes = [vp, vp, vp, vp, i64, i64]
     lib.ref_rms_norm_mul_f16.argtypes = [vp, vp, vp, i64, i64, C.c_float]
     lib.ref_rope_interleaved.argtypes = [vp, vp, vp, i64, i64, i64]
-    for f in (lib.ref_fused_modulate, lib.ref_fused_residual_gate, lib.ref_rms_norm_mul_f16, lib.ref_rope_interleaved):
+    lib.ref_tensor_euler_update.argtypes = [vp, vp, i64, C.c_float, C.c_float]
+    lib.ref_tensor_flow_update.argtypes = [vp, vp, i64, C.c_float, C.c_float]
+    lib.ref_tensor_cfg_combine.argtypes = [vp, vp, i64, C.c_float, vp]
+    for f in (lib.ref_fused_modulate, lib.ref_fused_residual_gate, lib.ref_rms_norm_mul_f16, lib.ref_rope_interleaved,
+              lib.ref_tensor_euler_update, lib.ref_tensor_flow_update, lib.ref_tensor_cfg_combine):
         f.restype = None
     return lib
+
+
+# (sigma, sigma_next) pairs of the sampler updates, and the guidance scale of the combine
+SIGMA_PAIRS = ((1.0, 0.9), (0.37, 0.0), (0.0, 0.0), (0.0123, 0.0045))
+CFG_SCALE = 4.5
 
 
 def p(a):
@@ -46,6 +56,10 @@ def inputs(seed=2024):
         "rx": rng.standard_normal((21, 3, 64)).astype(np.float32),          # [seq, heads, d]
         "rpos": rng.integers(0, 40, (21, 3)).astype(np.float32),            # ids for axes (8, 28, 28)
     }
+    # drawn after everything above, so that the earlier entries keep their values
+    d["sx"] = (rng.standard_normal(4099) * np.exp(rng.uniform(-2, 2, 4099))).astype(np.float32)   # latent
+    d["sv"] = rng.standard_normal(4099).astype(np.float32)                                       # prediction
+    d["su"] = rng.standard_normal(4099).astype(np.float32)                                       # unconditional
     return d
 
 
@@ -65,6 +79,17 @@ def run_ref(lib, d, pe):
     pe_c = np.ascontiguousarray(pe, dtype=np.float32)
     lib.ref_rope_interleaved(p(d["rx"]), p(pe_c), p(r), seq, heads, dh)
     out["rope"] = r
+    n = d["sx"].size
+    for i, (s, s_next) in enumerate(SIGMA_PAIRS):
+        x = d["sx"].copy()
+        lib.ref_tensor_euler_update(p(x), p(d["sv"]), n, s, s_next)
+        out[f"euler{i}"] = x
+        x = d["sx"].copy()
+        lib.ref_tensor_flow_update(p(x), p(d["sv"]), n, s, s_next)
+        out[f"flow{i}"] = x
+    o = np.empty_like(d["sx"])
+    lib.ref_tensor_cfg_combine(p(d["su"]), p(d["sv"]), n, CFG_SCALE, p(o))
+    out["cfg"] = o
     return out
 
 

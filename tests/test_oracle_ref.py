@@ -1,4 +1,4 @@
-"""Pins the numpy oracle to the reference's own CPU callbacks: against the committed golden
+"""Pins the numpy oracle to the reference's own CPU callbacks and tensor arithmetic: against the committed golden
 vectors (tests/golden/ref_callbacks.npz, made by tests/golden/make_golden.py from the
 reference tree) everywhere, and against the compiled callbacks themselves (oracle/_ref)
 on fresh random inputs wherever that library has been built.  Bit-exact in both cases."""
@@ -23,6 +23,9 @@ def _oracle_outputs(d, pe):
         "residual_gate": O.residual_gate(d["y"], d["x"], d["gate"]),
         "rms_norm_mul_f16": O.rms_norm_mul_f16_callback(d["nx"], d["nw"], 1e-6).view(np.uint16),
         "rope": np.ascontiguousarray(O.apply_rope(d["rx"], pe).transpose(1, 0, 2)),   # -> [heads, seq, d]
+        "cfg": O.cfg_combine(d["su"], d["sv"], G.CFG_SCALE),
+        **{f"euler{i}": O.euler_update(d["sx"], d["sv"], s, sn) for i, (s, sn) in enumerate(G.SIGMA_PAIRS)},
+        **{f"flow{i}": O.flow_update(d["sx"], d["sv"], s, sn) for i, (s, sn) in enumerate(G.SIGMA_PAIRS)},
     }
 
 
@@ -39,7 +42,8 @@ def test_oracle_matches_golden_vectors_of_the_reference_callbacks():
     pe = O.embed_nd(d["rpos"], (8, 28, 28), 10000.0)
     assert _same_bits(pe, gold["pe"])          # the generator's table is the oracle's own, kept for reference
     got = _oracle_outputs(d, pe)
-    for k in ("modulate", "residual_gate", "rms_norm_mul_f16", "rope"):
+    assert set(got) == set(gold.files) - {"pe"}
+    for k in got:
         assert _same_bits(got[k], gold[k]), k
 
 
