@@ -2,32 +2,40 @@
 """Benchmark of the DiT denoise-step hot path on B200.
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+  python bench.py --kernel gemm|attention|gemv|gemvbatch|layernorm|qkpack|sagequant|probe [...]
 
-Prints ONE JSON line.  A "step" is one full FLUX.1-shaped denoise step (19 double
-+ 38 single blocks, hidden 3072, 4096 image + 512 text tokens, q8_0 weights,
-INT8-QK attention) on synthetic N(0,1) inputs and random-init N(0,0.02) weights
-that are generated and quantised on the device.
+Prints ONE JSON line.  A "step" is one full denoise step of the workload (default: FLUX.1-shaped,
+19 double + 38 single blocks, hidden 3072, 4096 image + 512 text tokens, q8_0 weights, INT8-QK
+attention) on synthetic N(0,1) inputs and random-init N(0,0.02) weights that are generated and
+quantised on the device.
 
-  value      ms per step, inputs resident in HBM, CUDA events around K steps
-  e2e        ms per step through the host-tensor entry point
-             (edb200_flux_compute_host: pinned H2D of latent/context/pooled
-             vector and D2H of the result inside the timed region)
-  roofline   the quantised GEMM class: algorithmic FLOPs / device time measured
-             with CUDA events around every GEMM launch of one extra step
-  cpu_baseline  the numpy oracle timed on this box's host cores on a bounded
-             sample (whole blocks at full token count), extrapolated to a step
+  value      ms per step, inputs resident in HBM, CUDA events around K steps (a recorded CUDA graph
+             of the step is replayed; eager with --no-graph)
+  e2e        ms per step through the host-tensor entry point (edb200_*_compute_host: pinned H2D of
+             latent / context / pooled vector and D2H of the result inside the timed region)
+  roofline   the quantised GEMM class: algorithmic FLOPs / device time measured with CUDA events
+             around every GEMM launch of one extra step; kernel_classes gives the same for the
+             attention kernel (tensor bound) and the memory-bound classes (fraction of measured HBM)
+  cpu_baseline, parity
+             N = 1 only: the numpy oracle runs the FULL-DEPTH model on the weights read back from the
+             device, at the workload's own size if --cpu-budget allows, else at a reduced latent;
+             its time (scaled by FLOPs to the workload's token count) is the CPU baseline and its
+             output is compared with the GPU's output for the same inputs (parity.step_rel_l2)
 
-With --gpus N > 1 (launched by torch.distributed.run, one process per GPU) the N
-ranks share ONE step by Ulysses sequence parallelism: every rank keeps all weights,
-owns 1/N of the tokens for the linears and norms and 1/N of the heads for
-attention; the two exchanges per block run over NCCL inside the library.  The
-total work is fixed ("scaling": "strong") and rank 0 reports the slowest rank's time.
+With --gpus N > 1 (launched by torch.distributed.run, one process per GPU) the N ranks share ONE
+step ("scaling": "strong").  FLUX and Wan: Ulysses sequence parallelism over all N ranks.  The two
+classifier-free-guidance workloads (SD3, Qwen-Image: a step is a conditional and an unconditional
+pass plus the combine): CFG-parallel x sequence-parallel, ranks 0..N/2-1 run the conditional pass
+sequence parallel over N/2 ranks, ranks N/2..N-1 the unconditional one, rank i and i + N/2 exchange
+their results for the combine.  Every rank then repeats the step on its own GPU alone and the line
+carries the relative L2 between the two results (config.parallel_vs_single_rel_l2, max over ranks).
 """
 from __future__ import annotations
 
 import argparse
 import importlib.util
 import json
+import math
 import os
 import subprocess
 import sys
@@ -40,7 +48,7 @@ sys.path.insert(0, ROOT)
 METRIC = "DiT ms/denoise-step (FLUX.1-shape 1024^2, q8_0)"
 
 WORKLOADS = {
-    # name: (model kwargs, latent [C,H,W], text tokens)
+    # name: (model kwargs, latent [C, ...], text tokens)
     "flux1024_q8_0": (dict(hidden_size=3072, num_heads=24, depth=19, depth_single_blocks=38), (16, 128, 128), 512),
     "flux512_q8_0": (dict(hidden_size=3072, num_heads=24, depth=19, depth_single_blocks=38), (16, 64, 64), 512),
     "flux_tiny": (dict(hidden_size=512, num_heads=4, depth=2, depth_single_blocks=2, context_in_dim=256,
@@ -48,119 +56,23 @@ WORKLOADS = {
     # FLUX.1 2048^2 with q4_K weights (16384 + 512 tokens), the sequence-parallel configuration
     "flux2048_q4_k": (dict(hidden_size=3072, num_heads=24, depth=19, depth_single_blocks=38, wtype=12),
                       (16, 256, 256), 512),
-    # Wan 2.1 14B: latent [16, 21, 90, 160] -> 75,600 video tokens, 512 text tokens (name starts with "wan")
+    # Wan 2.1 14B: latent [16, 21, 90, 160] -> 75,600 video tokens, 512 text tokens
     "wan14b_q8_0": (dict(), (16, 21, 90, 160), 512),
-    "wan_small": (dict(dim=1024, num_heads=8, ffn_dim=2048, num_layers=4, text_dim=256), (16, 5, 32, 32), 64),
+    "wan_small": (dict(dim=1024, num_heads=8, ffn_dim=2048, num_layers=6, text_dim=256), (16, 5, 32, 32), 64),
     # SD3-medium 512^2: 1024 image + 154 text tokens, q8_0, f16 attention (head dim 64); a step is the
-    # conditional and the unconditional pass plus the CFG combine (name starts with "sd3")
+    # conditional and the unconditional pass plus the CFG combine
     "sd3_medium_q8_0": (dict(), (16, 64, 64), 154),
     # Qwen-Image 1328^2: 6889 image + 256 text tokens, q4_K; a step is two passes plus the CFG combine
     "qwen_image_q4_k": (dict(), (16, 166, 166), 256),
+    "qwen_small": (dict(num_layers=4, num_heads=8, joint_attention_dim=512), (16, 46, 46), 33),
 }
 
 
-class Case:
-    """One workload on this rank's GPU: the model, its device inputs and the two ways of running a step."""
-
-    def __init__(self, edb, torch, name, attention, dev):
-        import numpy as np
-        kw, lat, n_txt = WORKLOADS[name]
-        self.wan = name.startswith("wan")
-        self.family = name.split("_")[0] if name.split("_")[0] in ("sd3", "qwen") else ("wan" if self.wan else "flux")
-        g = torch.Generator(device=dev).manual_seed(1234)
-        self.latent = torch.randn(lat, generator=g, device=dev)
-        g.manual_seed(1235)
-        self.torch = torch
-        if self.family in ("sd3", "qwen"):
-            # classifier-free guidance: two batch-1 passes per step
-            if self.family == "sd3":
-                self.model = edb.SD3Model(**kw)
-                self.ctx = torch.randn(n_txt, self.model.cfg.context_size, generator=g, device=dev)
-                self.y = torch.randn(self.model.cfg.adm_in_channels, generator=g, device=dev)
-                self.y0 = torch.zeros_like(self.y)
-            else:
-                self.model = edb.QwenModel(attention=attention, **kw)
-                self.ctx = torch.randn(n_txt, self.model.cfg.joint_attention_dim, generator=g, device=dev)
-                self.y = None
-            self.ctx0 = torch.zeros_like(self.ctx)
-            self.cond, self.uncond = torch.empty_like(self.latent), torch.empty_like(self.latent)
-            self.tokens = (lat[1] // 2) * (lat[2] // 2) + n_txt
-        elif self.wan:
-            self.model = edb.WanModel(attention=attention, **kw)
-            self.ctx = torch.randn(n_txt, self.model.cfg.text_dim, generator=g, device=dev)
-            ps = tuple(self.model.cfg.patch_size)
-            self.tokens = (lat[1] // ps[0]) * (lat[2] // ps[1]) * (lat[3] // ps[2])
-            self.attn_tokens = self.tokens
-            self.y = None
-        else:
-            self.model = edb.FluxModel(attention=attention, **kw)
-            self.ctx = torch.randn(n_txt, self.model.cfg.context_in_dim, generator=g, device=dev)
-            self.y = torch.randn(self.model.cfg.vec_in_dim, generator=g, device=dev)
-            self.tokens = (lat[1] // 2) * (lat[2] // 2) + n_txt
-        self.lat, self.n_txt = lat, n_txt
-        self.out = torch.empty_like(self.latent)
-        self.edb, self.np = edb, np
-
-    def prepare(self):
-        if self.family in ("sd3", "qwen"):
-            self.model.prepare(self.lat[1], self.lat[2], self.n_txt)
-        elif self.wan:
-            self.model.prepare(self.lat[1], self.lat[2], self.lat[3], self.n_txt)
-        else:
-            self.model.prepare(self.lat[1], self.lat[2], self.n_txt)
-
-    def _combine(self):
-        e = self.edb
-        if self.family == "qwen":   # Qwen-Image's per-patch norm-preserving combine (qwen_image_pipeline.cpp:29-85)
-            c, h, w = self.cond.shape
-            e.check(e.lib().edb200_cfg_combine_rescaled(e.ptr(self.uncond), e.ptr(self.cond), 4.0, 2, c, h, w,
-                                                        e.ptr(self.out), e.current_stream()))
-            return
-        e.check(e.lib().edb200_cfg_combine(e.ptr(self.uncond), e.ptr(self.cond), 4.5, e.ptr(self.out), self.out.numel(),
-                                           e.current_stream()))
-
-    def step(self):
-        if self.family == "sd3":
-            self.model.step(self.latent, 500.0, self.ctx, self.y, self.cond)
-            self.model.step(self.latent, 500.0, self.ctx0, self.y0, self.uncond)
-            self._combine()
-        elif self.family == "qwen":
-            self.model.step(self.latent, 500.0, self.ctx, self.cond)
-            self.model.step(self.latent, 500.0, self.ctx0, self.uncond)
-            self._combine()
-        elif self.wan:
-            self.model.step(self.latent, 500.0, self.ctx, self.out)
-        else:
-            self.model.step(self.latent, 0.5, self.ctx, self.y, 3.5, self.out)
-
-    def host_inputs(self):
-        if self.family == "sd3":
-            ts = (self.latent, self.ctx, self.y, self.ctx0, self.y0)
-        elif self.family == "qwen":
-            ts = (self.latent, self.ctx, self.ctx0)
-        else:
-            ts = (self.latent, self.ctx) if self.wan else (self.latent, self.ctx, self.y)
-        self.h = [t.cpu().numpy() for t in ts]
-        return sum(a.nbytes for a in self.h)
-
-    def step_host(self):
-        if self.family == "sd3":
-            c = self.model.compute_host(self.h[0], 500.0, self.h[1], self.h[2])
-            u = self.model.compute_host(self.h[0], 500.0, self.h[3], self.h[4])
-            return u + 4.5 * (c - u)
-        if self.family == "qwen":
-            c = self.model.compute_host(self.h[0], 500.0, self.h[1])
-            u = self.model.compute_host(self.h[0], 500.0, self.h[2])
-            return u + 4.5 * (c - u)
-        if self.wan:
-            return self.model.compute_host(self.h[0], 500.0, self.h[1])
-        return self.model.compute_host(self.h[0], 0.5, self.h[1], self.h[2], 3.5)
-
-    def weight_bytes(self):
-        lib = self.edb.lib()
-        fn = {"sd3": lib.edb200_sd3_weight_bytes, "qwen": lib.edb200_qwen_weight_bytes, "wan": lib.edb200_wan_weight_bytes,
-              "flux": lib.edb200_flux_weight_bytes}[self.family]
-        return fn(self.model.handle)
+def family_of(name: str) -> str:
+    head = name.split("_")[0]
+    if head in ("sd3", "qwen"):
+        return head
+    return "wan" if name.startswith("wan") else "flux"
 
 
 def load_pkg(name):
@@ -179,8 +91,39 @@ def measured_peaks():
     if os.path.exists(path):
         with open(path) as fh:
             p = json.load(fh)
-        return {"hbm_gbs": p["hbm_gbs"], "tflops": p["bf16_tflops_sustained"], "source": "measured"}
-    return {"hbm_gbs": 6650.0, "tflops": 1400.0, "source": "fallback"}
+        return {"hbm_gbs": p["hbm_gbs"], "tflops": p["bf16_tflops_sustained"], "tflops_burst": p["bf16_tflops"],
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops": 1400.0, "tflops_burst": 1590.0, "source": "fallback"}
+
+
+def host_threads() -> int:
+    """Threads for the CPU legs: every core this process may run on."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+def use_all_host_threads():
+    """torch.distributed.run exports OMP_NUM_THREADS=1 to its ranks; the CPU legs want every core.  Called
+    before numpy is imported where possible, and again through threadpoolctl for an already loaded BLAS."""
+    n = host_threads()
+    for var in ("OMP_NUM_THREADS", "OPENBLAS_NUM_THREADS", "MKL_NUM_THREADS"):
+        os.environ[var] = str(n)
+    try:
+        from threadpoolctl import threadpool_limits
+        threadpool_limits(limits=n)
+    except Exception:
+        pass
+    return n
+
+
+def blas_threads() -> int:
+    try:
+        from threadpoolctl import threadpool_info
+        return max([p.get("num_threads", 1) for p in threadpool_info()] or [1])
+    except Exception:
+        return host_threads()
 
 
 class ClockSampler:
@@ -245,62 +188,165 @@ def visible_gpu_index(local_rank: int) -> int:
     return local_rank
 
 
-# --------------------------------------------------------------------------- CPU legs
+# --------------------------------------------------------------------------- CPU legs (oracle)
 
-def cpu_sample(workload: str, budget_s: float):
-    """Times whole oracle blocks at the workload's token count; returns (ms_per_step, cores, description)."""
+def oracle_config(workload: str):
+    """(family, oracle config object, model kwargs, latent shape, text tokens) of a workload."""
+    kw, lat, n_txt = WORKLOADS[workload]
+    fam = family_of(workload)
+    if fam == "flux":
+        from oracle.flux_oracle import FluxConfig
+        cfg = FluxConfig(**kw)
+    elif fam == "wan":
+        from oracle.wan_oracle import WanConfig
+        cfg = WanConfig(**kw)
+    elif fam == "sd3":
+        from oracle.sd3_oracle import SD3Config
+        cfg = SD3Config(**kw)
+    else:
+        from oracle.qwen_oracle import QwenConfig
+        m = dict(kw)
+        if "num_heads" in m:
+            m["num_attention_heads"] = m.pop("num_heads")
+        cfg = QwenConfig(**m)
+    return fam, cfg, kw, lat, n_txt
+
+
+def step_flops(fam, cfg, lat, n_txt) -> float:
+    """Algorithmic FLOPs of one denoise step (linears 2 per MAC, attention 4 * Lq * Lk * d * heads)."""
+    if fam == "flux":
+        H, M = cfg.hidden_size, cfg.mlp_hidden
+        t_img = (lat[1] // 2) * (lat[2] // 2)
+        T = t_img + n_txt
+        lin = 2.0 * T * (cfg.depth * 12 * H * H + cfg.depth_single_blocks * ((3 * H + M) * H + (H + M) * H))
+        att = 4.0 * T * T * H * (cfg.depth + cfg.depth_single_blocks)
+        return lin + att
+    if fam == "wan":
+        D, F = cfg.dim, cfg.ffn_dim
+        pt, ph, pw = cfg.patch_size
+        T = (lat[1] // pt) * (lat[2] // ph) * (lat[3] // pw)
+        lin = 2.0 * cfg.num_layers * (T * (6 * D * D + 2 * D * F) + n_txt * 2 * D * D)
+        att = 4.0 * cfg.num_layers * (T * T * D + T * n_txt * D)
+        return lin + att
+    if fam == "sd3":
+        H, M = cfg.hidden_size, cfg.mlp_hidden
+        T = (lat[1] // 2) * (lat[2] // 2) + n_txt
+        per_pass = 2.0 * T * cfg.depth * (4 * H * H + 2 * H * M) + 4.0 * T * T * H * cfg.depth
+        return 2.0 * per_pass
+    H, M = cfg.hidden_size, cfg.mlp_hidden
+    T = (lat[1] // 2) * (lat[2] // 2) + n_txt
+    per_pass = 2.0 * T * cfg.num_layers * (4 * H * H + 2 * H * M) + 4.0 * T * T * H * cfg.num_layers
+    return 2.0 * per_pass
+
+
+def probe_gflops() -> float:
+    import numpy as np
+    a = np.random.default_rng(0).standard_normal((2048, 2048), dtype=np.float32)
+    a @ a
+    t0 = time.perf_counter()
+    for _ in range(3):
+        a @ a
+    return 3 * 2 * 2048 ** 3 / (time.perf_counter() - t0) / 1e9
+
+
+def sample_latent(fam, cfg, lat, n_txt, budget_s, gflops):
+    """The largest latent (the workload's own, or its sides halved repeatedly) whose oracle step is
+    estimated to fit `budget_s` seconds of CPU time."""
+    cur = list(lat)
+    while True:
+        est = step_flops(fam, cfg, cur, n_txt) / (gflops * 1e9)
+        sides = cur[2:] if fam == "wan" else cur[1:]
+        if est <= budget_s or min(sides) <= 8:
+            return tuple(cur), est
+        if fam == "wan":
+            cur[1] = max(1, cur[1] // 2) if cur[1] > 1 else 1
+            cur[2] = max(8, (cur[2] // 2) // 2 * 2)
+            cur[3] = max(8, (cur[3] // 2) // 2 * 2)
+        else:
+            cur[1] = max(8, (cur[1] // 2) // 2 * 2)
+            cur[2] = max(8, (cur[2] // 2) // 2 * 2)
+
+
+def synth_inputs(fam, cfg, lat, n_txt):
+    import numpy as np
+    rng = np.random.default_rng(1234)
+    latent = rng.standard_normal(lat, dtype=np.float32)
+    rng = np.random.default_rng(1235)
+    if fam == "flux":
+        return latent, rng.standard_normal((n_txt, cfg.context_in_dim), dtype=np.float32), \
+            rng.standard_normal(cfg.vec_in_dim, dtype=np.float32)
+    if fam == "wan":
+        return latent, rng.standard_normal((n_txt, cfg.text_dim), dtype=np.float32), None
+    if fam == "sd3":
+        return latent, rng.standard_normal((n_txt, cfg.context_size), dtype=np.float32), \
+            rng.standard_normal(cfg.adm_in_channels, dtype=np.float32)
+    return latent, rng.standard_normal((n_txt, cfg.joint_attention_dim), dtype=np.float32), None
+
+
+def oracle_step(fam, cfg, weights, latent, ctx, y):
+    """One denoise step of the CPU oracle (for the guidance families: both passes and the combine)."""
     import numpy as np
     from oracle import edb_oracle as O
-    from oracle.flux_oracle import FluxConfig, FluxOracle, flux_timing_weights
+    if fam == "flux":
+        from oracle.flux_oracle import FluxOracle
+        return FluxOracle(cfg, weights).forward(latent, 0.5, ctx, y, 3.5)
+    if fam == "wan":
+        from oracle.wan_oracle import WanOracle
+        return WanOracle(cfg, weights).forward(latent, 500.0, ctx)
+    if fam == "sd3":
+        from oracle.sd3_oracle import SD3Oracle
+        o = SD3Oracle(cfg, weights)
+        c = o.forward(latent, 500.0, ctx, y)
+        u = o.forward(latent, 500.0, np.zeros_like(ctx), np.zeros_like(y))
+        return O.cfg_combine(u, c, 4.5)
+    from oracle.qwen_oracle import QwenOracle, true_cfg
+    o = QwenOracle(cfg, weights)
+    c = o.forward(latent, 500.0, ctx)
+    u = o.forward(latent, 500.0, np.zeros_like(ctx))
+    return true_cfg(c, u, 4.0, cfg.patch_size)
 
-    kw, lat, n_txt = WORKLOADS[workload]
-    full = FluxConfig(**{k: v for k, v in kw.items()})
-    # a quick matmul probe decides how many tokens the sample can afford
-    a = np.random.default_rng(0).standard_normal((1024, 1024), dtype=np.float32)
-    t0 = time.perf_counter()
-    for _ in range(4):
-        a @ a
-    gflops = 4 * 2 * 1024 ** 3 / (time.perf_counter() - t0) / 1e9
-    n_img = (lat[1] // 2) * (lat[2] // 2)
-    H, M = full.hidden_size, full.mlp_hidden
 
-    def block_flops(t_img, t_txt):
-        T = t_img + t_txt
-        dbl = 2 * T * (12 * H * H) + 4 * T * T * H
-        sgl = 2 * T * ((3 * H + M) * H + (H + M) * H) + 4 * T * T * H
-        return dbl + sgl
+def timing_provider(fam, cfg):
+    """Weights for a CPU timing run without a device: one block per stack, every block index aliased to it."""
+    import dataclasses
+    from oracle.weights import AliasedBlocks, timing_weights
+    if fam == "flux":
+        from oracle.flux_oracle import flux_tensor_specs
+        specs, depth = flux_tensor_specs(dataclasses.replace(cfg, depth=1, depth_single_blocks=1)), \
+            max(cfg.depth, cfg.depth_single_blocks)
+    elif fam == "wan":
+        from oracle.wan_oracle import wan_tensor_specs
+        specs, depth = wan_tensor_specs(dataclasses.replace(cfg, num_layers=1)), cfg.num_layers
+    elif fam == "sd3":
+        from oracle.sd3_oracle import sd3_tensor_specs
+        specs, depth = sd3_tensor_specs(cfg, n_blocks=2), cfg.depth
+    else:
+        from oracle.qwen_oracle import qwen_tensor_specs
+        specs, depth = qwen_tensor_specs(dataclasses.replace(cfg, num_layers=1)), cfg.num_layers
+    return AliasedBlocks(timing_weights(specs), depth=depth)
 
-    t_img = n_img
-    while t_img > 256 and block_flops(t_img, n_txt) / (gflops * 1e9) > budget_s:
-        t_img //= 2
-    cfg = FluxConfig(**{**kw, "depth": 1, "depth_single_blocks": 1})
-    weights = flux_timing_weights(cfg, 0)
-    model = FluxOracle(cfg, weights)
-    rng = np.random.default_rng(1234)
-    img = rng.standard_normal((t_img, H), dtype=np.float32)
-    txt = rng.standard_normal((n_txt, H), dtype=np.float32)
-    vec = rng.standard_normal((1, H), dtype=np.float32)
-    cols = 64 if t_img % 64 == 0 else 16
-    pe = O.embed_nd(O.flux_ids(t_img // cols, cols, n_txt), cfg.axes_dim, cfg.theta)
+
+def cpu_leg(workload, budget_s, weights=None):
+    """Runs the oracle's full-depth step on a bounded sample of the workload.
+    Returns dict(ms_full, cores, sample, latent, inputs, out) where ms_full is the measured time scaled
+    by FLOPs to the workload's own token count."""
+    cores = use_all_host_threads()
+    fam, cfg, kw, lat, n_txt = oracle_config(workload)
+    gflops = probe_gflops()
+    s_lat, est = sample_latent(fam, cfg, lat, n_txt, budget_s, gflops)
+    latent, ctx, y = synth_inputs(fam, cfg, s_lat, n_txt)
+    w = weights if weights is not None else timing_provider(fam, cfg)
     t0 = time.perf_counter()
-    img2, txt2 = model.double_block(0, img, txt, vec, pe)
-    t_double = time.perf_counter() - t0
-    x = np.concatenate([txt2, img2], axis=0)
-    t0 = time.perf_counter()
-    model.single_block(0, x, vec, pe)
-    t_single = time.perf_counter() - t0
-    # scale the sampled token count back to the workload's (GEMMs linear, attention quadratic in tokens)
-    scale = block_flops(n_img, n_txt) / block_flops(t_img, n_txt)
-    ms = (t_double * full.depth + t_single * full.depth_single_blocks) * scale * 1e3
-    try:
-        from threadpoolctl import threadpool_info
-        cores = max([p.get("num_threads", 1) for p in threadpool_info()] or [os.cpu_count() or 1])
-    except Exception:
-        cores = os.cpu_count() or 1
-    desc = (f"numpy oracle, 1 double + 1 single block at {t_img}+{n_txt} tokens "
-            f"({t_double:.2f}s + {t_single:.2f}s), scaled by FLOPs to {full.depth}+{full.depth_single_blocks} blocks "
-            f"at {n_img}+{n_txt} tokens; prelude/final layer omitted")
-    return ms, cores, desc
+    out = oracle_step(fam, cfg, w, latent, ctx, y)
+    dt = time.perf_counter() - t0
+    scale = step_flops(fam, cfg, lat, n_txt) / step_flops(fam, cfg, s_lat, n_txt)
+    full = tuple(s_lat) == tuple(lat)
+    sample = (f"numpy oracle (fp32, non-Sage), ALL blocks of the model, latent {list(s_lat)} + {n_txt} text tokens"
+              f"{'' if full else ' (the workload is ' + str(list(lat)) + ')'}: {dt:.1f} s measured"
+              f"{'' if full else f', scaled by FLOPs x{scale:.2f} to the workload size'}; "
+              f"{'weights read back from the device' if weights is not None else 'synthetic f32 weights, one block per stack aliased to every depth'}")
+    return {"ms_full": dt * 1e3 * scale, "cores": min(cores, blas_threads()), "sample": sample, "latent": s_lat,
+            "inputs": (latent, ctx, y), "out": out, "full_size": full, "seconds": dt}
 
 
 def run_reference(args):
@@ -308,30 +354,228 @@ def run_reference(args):
     if rank != 0:
         return
     per_step_budget = max(2.0, min(20.0, 150.0 / max(1, args.steps + args.warmup)))
-    vals = []
-    desc, cores = "", 1
+    vals, leg = [], None
     for i in range(args.warmup + args.steps):
-        ms, cores, desc = cpu_sample(args.workload, per_step_budget)
+        leg = cpu_leg(args.workload, per_step_budget)
         if i >= args.warmup:
-            vals.append(ms)
+            vals.append(leg["ms_full"])
     value = sum(vals) / len(vals)
-    kw, lat, n_txt = WORKLOADS[args.workload]
-    tokens = (lat[1] // 2) * (lat[2] // 2) + n_txt
+    fam, cfg, kw, lat, n_txt = oracle_config(args.workload)
+    tokens = tokens_of(fam, cfg, lat, n_txt)
     line = {
-        "impl": "reference", "metric": METRIC, "value": value, "unit": "ms", "n_gpus": args.gpus,
+        "impl": "reference", "metric": metric_name(args.workload), "value": value, "unit": "ms", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": value, "higher_is_better": False,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "tokens_per_s": tokens / (value / 1e3),
-        "config": {"workload": args.workload, "note": "reference CPU binary cannot be built (ggml submodule absent); "
-                   "this is the CPU oracle restating its non-Sage fp32 path"},
-        "cpu_baseline": {"value": value, "unit": "ms", "cores": cores, "kind": "port", "sample": desc},
+        "config": {"workload": args.workload, "tokens": tokens,
+                   "note": "the reference's CPU binary cannot be built (its ggml submodule is absent); this is the "
+                           "CPU oracle restating its non-Sage fp32 path, all host threads"},
+        "cpu_baseline": {"value": value, "unit": "ms", "cores": leg["cores"], "kind": "port", "sample": leg["sample"]},
         "e2e": {"value": value, "unit": "ms", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
 
 
+def tokens_of(fam, cfg, lat, n_txt):
+    if fam == "wan":
+        pt, ph, pw = cfg.patch_size
+        return (lat[1] // pt) * (lat[2] // ph) * (lat[3] // pw)
+    return (lat[1] // 2) * (lat[2] // 2) + n_txt
+
+
+def metric_name(workload):
+    return METRIC if workload == "flux1024_q8_0" else f"DiT ms/denoise-step ({workload})"
+
+
 # --------------------------------------------------------------------------- GPU arm
+
+class Case:
+    """One workload on this rank's GPU: the model, its device inputs and the ways of running a step."""
+
+    def __init__(self, edb, torch, name, attention, dev, world, rank):
+        kw, lat, n_txt = WORKLOADS[name]
+        self.edb, self.torch, self.dev = edb, torch, dev
+        self.family = family_of(name)
+        self.guided = self.family in ("sd3", "qwen")          # a step = conditional + unconditional pass + combine
+        self.world, self.rank = world, rank
+        # parallel layout: guidance families split the world into two branches first
+        self.cfg_parallel = self.guided and world > 1
+        self.sp = world // 2 if self.cfg_parallel else world
+        self.branch = rank // self.sp if self.cfg_parallel else 0
+        self.lat, self.n_txt = lat, n_txt
+        if self.family == "sd3":
+            self.model = edb.SD3Model(attention=attention, **kw)
+            ctx_dim, y_dim = self.model.cfg.context_size, self.model.cfg.adm_in_channels
+        elif self.family == "qwen":
+            self.model = edb.QwenModel(attention=attention, **kw)
+            ctx_dim, y_dim = self.model.cfg.joint_attention_dim, 0
+        elif self.family == "wan":
+            self.model = edb.WanModel(attention=attention, **kw)
+            ctx_dim, y_dim = self.model.cfg.text_dim, 0
+        else:
+            self.model = edb.FluxModel(attention=attention, **kw)
+            ctx_dim, y_dim = self.model.cfg.context_in_dim, self.model.cfg.vec_in_dim
+        self.ctx_dim, self.y_dim = ctx_dim, y_dim
+        self.comms = []
+        self.pair_comm = None
+        self.set_inputs(lat)
+
+    def set_inputs(self, lat, arrays=None):
+        """Device inputs for a latent shape: seeded N(0,1) tensors, or the given numpy arrays."""
+        torch, dev = self.torch, self.dev
+        self.cur_lat = tuple(lat)
+        if arrays is None:
+            g = torch.Generator(device=dev).manual_seed(1234)
+            self.latent = torch.randn(lat, generator=g, device=dev)
+            g.manual_seed(1235)
+            self.ctx = torch.randn(self.n_txt, self.ctx_dim, generator=g, device=dev)
+            self.y = torch.randn(self.y_dim, generator=g, device=dev) if self.y_dim else None
+        else:
+            latent, ctx, y = arrays
+            self.latent = torch.from_numpy(latent).to(dev)
+            self.ctx = torch.from_numpy(ctx).to(dev)
+            self.y = torch.from_numpy(y).to(dev) if y is not None else None
+        self.ctx0 = torch.zeros_like(self.ctx)
+        self.y0 = torch.zeros_like(self.y) if self.y is not None else None
+        self.out = torch.empty_like(self.latent)
+        self.cond, self.uncond = torch.empty_like(self.latent), torch.empty_like(self.latent)
+        self.gathered = torch.empty(2, self.latent.numel(), device=dev)
+
+    def tokens(self):
+        lat = self.lat
+        if self.family == "wan":
+            ps = tuple(self.model.cfg.patch_size)
+            return (lat[1] // ps[0]) * (lat[2] // ps[1]) * (lat[3] // ps[2])
+        return (lat[1] // 2) * (lat[2] // 2) + self.n_txt
+
+    def go_parallel(self):
+        """Builds the communicators of the parallel layout (collective over the whole world)."""
+        edb = self.edb
+        if self.world == 1:
+            return
+        if self.cfg_parallel:
+            branch_comm = edb.Comm(ranks=list(range(self.branch * self.sp, (self.branch + 1) * self.sp)))
+            r = self.rank % self.sp
+            self.pair_comm = edb.Comm(ranks=[r, r + self.sp])
+            self.comms = [branch_comm, self.pair_comm]
+            if self.sp > 1:
+                self.model.set_comm(branch_comm)
+        else:
+            c = edb.Comm()
+            self.comms = [c]
+            self.model.set_comm(c)
+
+    def go_single(self):
+        """Back to this GPU alone (collective where peer mappings have to be released)."""
+        if self.world > 1 and self.sp > 1:
+            self.model.set_comm(None)
+        self.cfg_parallel_active = False
+
+    def prepare(self):
+        lat = self.cur_lat
+        if self.family == "wan":
+            self.model.prepare(lat[1], lat[2], lat[3], self.n_txt)
+        else:
+            self.model.prepare(lat[1], lat[2], self.n_txt)
+
+    def _pass(self, cond: bool, out):
+        m = self.model
+        ctx, y = (self.ctx, self.y) if cond else (self.ctx0, self.y0)
+        if self.family == "sd3":
+            m.step(self.latent, 500.0, ctx, y, out)
+        elif self.family == "qwen":
+            m.step(self.latent, 500.0, ctx, out)
+        elif self.family == "wan":
+            m.step(self.latent, 500.0, ctx, out)
+        else:
+            m.step(self.latent, 0.5, ctx, y, 3.5, out)
+
+    def _combine(self, parallel: bool):
+        e, lib = self.edb, self.edb.lib()
+        c, h, w = self.latent.shape
+        if parallel:
+            mine = self.cond                                 # this rank's branch result
+            if self.family == "qwen":
+                e.check(lib.edb200_cfg_parallel_combine_rescaled(self.pair_comm.handle, e.ptr(mine), 4.0, 2, c, h, w,
+                                                                 e.ptr(self.gathered), e.ptr(self.out), e.current_stream()))
+            else:
+                e.check(lib.edb200_cfg_parallel_combine(self.pair_comm.handle, e.ptr(mine), 4.5, e.ptr(self.gathered),
+                                                        e.ptr(self.out), self.out.numel(), e.current_stream()))
+        elif self.family == "qwen":   # Qwen-Image's per-patch norm-preserving combine (qwen_image_pipeline.cpp:29-85)
+            e.check(lib.edb200_cfg_combine_rescaled(e.ptr(self.uncond), e.ptr(self.cond), 4.0, 2, c, h, w, e.ptr(self.out),
+                                                    e.current_stream()))
+        else:
+            e.check(lib.edb200_cfg_combine(e.ptr(self.uncond), e.ptr(self.cond), 4.5, e.ptr(self.out), self.out.numel(),
+                                           e.current_stream()))
+
+    # the part of a step that a CUDA graph may hold (no library exchange inside), and the rest
+    def model_part(self, parallel: bool):
+        if not self.guided:
+            self._pass(True, self.out)
+        elif parallel:
+            self._pass(self.branch == 0, self.cond)
+        else:
+            self._pass(True, self.cond)
+            self._pass(False, self.uncond)
+
+    def tail_part(self, parallel: bool):
+        if self.guided:
+            self._combine(parallel)
+
+    def step(self, parallel: bool):
+        self.model_part(parallel)
+        self.tail_part(parallel)
+
+    def host_inputs(self):
+        ts = [t for t in (self.latent, self.ctx, self.y, self.ctx0 if self.guided else None,
+                          self.y0 if self.guided else None) if t is not None]
+        self.h = {"latent": self.latent.cpu().numpy(), "ctx": self.ctx.cpu().numpy(),
+                  "y": self.y.cpu().numpy() if self.y is not None else None,
+                  "ctx0": self.ctx0.cpu().numpy(), "y0": self.y0.cpu().numpy() if self.y0 is not None else None}
+        if self.guided and self.world > 1:    # one branch per rank
+            ts = [t for t in (self.latent, self.ctx, self.y) if t is not None]
+        return sum(t.numel() * t.element_size() for t in ts)
+
+    def _host_pass(self, cond: bool):
+        h, m = self.h, self.model
+        ctx, y = (h["ctx"], h["y"]) if cond else (h["ctx0"], h["y0"])
+        if self.family == "sd3":
+            return m.compute_host(h["latent"], 500.0, ctx, y)
+        if self.family in ("qwen", "wan"):
+            return m.compute_host(h["latent"], 500.0, ctx)
+        return m.compute_host(h["latent"], 0.5, ctx, y, 3.5)
+
+    def step_host(self, parallel: bool):
+        """The step through the host-tensor entry point; returns the host result."""
+        torch = self.torch
+        if not self.guided:
+            return self._host_pass(True)
+        if parallel:
+            mine = self._host_pass(self.branch == 0)
+            self.cond.copy_(torch.from_numpy(mine))
+            self._combine(True)
+            return self.out.cpu().numpy()
+        c, u = self._host_pass(True), self._host_pass(False)
+        self.cond.copy_(torch.from_numpy(c))
+        self.uncond.copy_(torch.from_numpy(u))
+        self._combine(False)
+        return self.out.cpu().numpy()
+
+    def weight_bytes(self):
+        lib = self.edb.lib()
+        fn = {"sd3": lib.edb200_sd3_weight_bytes, "qwen": lib.edb200_qwen_weight_bytes, "wan": lib.edb200_wan_weight_bytes,
+              "flux": lib.edb200_flux_weight_bytes}[self.family]
+        return fn(self.model.handle)
+
+    def peers_mapped(self):
+        return bool(self.comms) and self.sp > 1 and bool(self.edb.lib().edb200_comm_peers_mapped(self.comms[0].handle))
+
+    def close(self):
+        for c in self.comms:
+            c.close()
+        self.comms = []
+
 
 def run_ours(args):
     import numpy as np
@@ -352,39 +596,52 @@ def run_ours(args):
 
     load_pkg("build").build()
     edb = load_pkg("edb200")
-    attention = edb.ATTN_F16 if args.attention == "f16" else edb.ATTN_SAGE_INT8
-    case = Case(edb, torch, args.workload, attention, dev)
+    fam = family_of(args.workload)
+    att_name = args.attention
+    if att_name == "auto":
+        # the reference's Sage gate leaves Qwen-Image (K/V pre-scale != 1) on the f16 path; SD3's benchmark
+        # configuration does not ask for INT8 scores
+        att_name = "f16" if fam in ("qwen", "sd3") else "sage"
+    attention = edb.ATTN_F16 if att_name == "f16" else edb.ATTN_SAGE_INT8
+    case = Case(edb, torch, args.workload, attention, dev, world, rank)
+    if case.guided and world > 1 and world % 2:
+        raise SystemExit("bench.py: the guidance workloads need an even number of GPUs (two branches)")
     model = case.model
     model.init_random(seed=0, std=0.02)
     init_launches = int(edb.lib().edb200_launch_count())
-    comm = None
-    if world > 1:
-        # Ulysses sequence parallelism: every rank holds all weights, 1/N of the tokens for the
-        # per-token work and 1/N of the heads for attention (NCCL exchange inside the library)
-        if case.family == "sd3":
-            raise SystemExit(f"bench.py: workload {args.workload} has no sequence-parallel path; use --gpus 1")
-        comm = edb.Comm()
-        model.set_comm(comm)
+    case.go_parallel()
     case.prepare()
-    tokens = case.tokens
-    out = case.out
+    parallel = world > 1
+    tokens = case.tokens()
 
     def barrier():
         if dist is not None:
             dist.barrier()
         torch.cuda.synchronize()
 
-    # The timed steps run on a side stream; on one GPU the step is recorded once into a CUDA graph
-    # (edb200_graph_*) and replayed, which removes the launch gaps between its kernels.  The
-    # sequence-parallel step (NCCL calls inside) runs eagerly.
+    # The timed steps run on a side stream.  The model part of the step is recorded once into a CUDA graph
+    # (edb200_graph_*) and replayed, which removes the launch gaps between its kernels; a sequence-parallel
+    # step can be recorded when its exchanges run over peer memory (no library exchange inside).
     side = torch.cuda.Stream(device=dev)
-    use_graph = world == 1 and not args.no_graph
     with torch.cuda.stream(side):
         for _ in range(args.warmup):
-            case.step()
+            case.step(parallel)
         side.synchronize()
-        graph = edb.Graph(case.step) if use_graph else None
-        run_step = graph.launch if graph is not None else case.step
+        can_graph = (case.sp == 1 or case.peers_mapped()) and not args.no_graph
+        if dist is not None:   # every rank takes the same decision
+            flag = torch.tensor([1 if can_graph else 0], device=dev)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            can_graph = bool(flag.item())
+        barrier()
+        graph = edb.Graph(lambda: case.model_part(parallel)) if can_graph else None
+
+        def run_step():
+            if graph is not None:
+                graph.launch()
+                case.tail_part(parallel)
+            else:
+                case.step(parallel)
+
         if graph is not None:
             run_step()          # one replay before the clock starts
         barrier()
@@ -401,30 +658,43 @@ def run_ours(args):
         clocks = sampler.stop() if rank == 0 else None
     launches = edb.lib().edb200_launch_count() - launches0
     ms = e0.elapsed_time(e1) / args.steps
-    finite = bool(torch.isfinite(out).all().item())
+    edb.poll_status()                                   # a device-side wait that gave up would show here
+    finite = bool(torch.isfinite(case.out).all().item())
+    out_parallel = case.out.clone()
 
     # end to end through the host-tensor entry point
     h2d = case.host_inputs()
     n_e2e = 1 if args.kernel_only else args.steps
     for _ in range(0 if args.kernel_only else min(2, args.warmup)):
-        case.step_host()
+        case.step_host(parallel)
     barrier()
     t0 = time.perf_counter()
     for _ in range(n_e2e):
-        h_out = case.step_host()
+        h_out = case.step_host(parallel)
     e2e_ms = (time.perf_counter() - t0) * 1e3 / n_e2e
     barrier()
 
     # per-class device time of one extra step (CUDA events around every launch)
     edb.profile_begin()
-    case.step()
+    case.step(parallel)
     prof = edb.profile_end()
 
-    if dist is not None:
-        t = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
+    # with the barriers and peer stores taken away: the same ranks, each repeating the WHOLE step alone.
+    # Gives the parity of the parallel result and, by difference against 1/N of it, nothing else.
+    sp_rel = None
+    if parallel:
+        barrier()
+        case.go_single()
+        case.prepare()
+        case.step(False)
+        torch.cuda.synchronize()
+        a, b = out_parallel.double(), case.out.double()
+        rel = torch.linalg.vector_norm(a - b) / torch.linalg.vector_norm(b)
+        t = torch.tensor([ms, e2e_ms, float(rel)], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, e2e_ms = t.tolist()
+        ms, e2e_ms, sp_rel = t.tolist()
     if rank != 0:
+        case.close()
         if dist is not None:
             dist.destroy_process_group()
         return
@@ -432,42 +702,62 @@ def run_ours(args):
     peaks = measured_peaks()
     gemm = prof["gemm"]
     gemm_tflops = gemm["flops"] / (gemm["ms"] * 1e-3) / 1e12 if gemm["ms"] > 0 else 0.0
-    att = prof["attention"]
-    att_tflops = att["flops"] / (att["ms"] * 1e-3) / 1e12 if att["ms"] > 0 else 0.0
-    gemv = prof["gemv"]
+    traffic = profile_traffic(args.workload)
     roofline = {
-        "kernel": "qgemm_kernel (dequant-fused q8_0 GEMM, tcgen05 kind::f16)",
+        "kernel": "qgemm_kernel (dequant-fused quantised GEMM, tcgen05 kind::f16)",
         "bound": "tensor", "achieved": gemm_tflops, "peak": peaks["tflops"], "unit": "TFLOP/s",
-        "frac": gemm_tflops / peaks["tflops"], "peak_source": peaks["source"] + " bf16 sustained",
+        "frac": gemm_tflops / peaks["tflops"], "peak_source": peaks["source"] + " bf16 sustained (cuBLAS, this pool)",
         "launches_per_step": gemm["launches"], "ms_per_step": gemm["ms"],
-        # DRAM bytes of one launch of the 4608 x 9216 x 3072 shape from the ncu capture summarised in
-        # profiles/qgemm_kernel_q8_0.md (algorithmic bytes of that launch: 143.3e6)
-        "traffic": 112.8e6 if args.workload == "flux1024_q8_0" else None,
+        "algorithmic_bytes_per_step": gemm["bytes"],
+        "traffic": traffic["bytes"] if traffic else None,
+        "traffic_source": traffic["source"] if traffic else "no capture of this workload's launches is committed",
     }
-    classes = {k: {"ms": round(v["ms"], 3), "launches": v["launches"]} for k, v in prof.items()}
-    classes["attention"]["tflops"] = round(att_tflops, 1)
-    classes["gemv"]["gbs"] = round(gemv["bytes"] / (gemv["ms"] * 1e-3) / 1e9, 1) if gemv["ms"] > 0 else 0.0
+    classes = {}
+    for k, v in prof.items():
+        c = {"ms": round(v["ms"], 3), "launches": v["launches"]}
+        if v["ms"] > 0 and k in ("gemm", "attention"):
+            c["tflops"] = round(v["flops"] / (v["ms"] * 1e-3) / 1e12, 1)
+            c["frac_of_bf16_sustained"] = round(c["tflops"] / peaks["tflops"], 3)
+        if v["ms"] > 0 and k in ("gemv", "elementwise"):
+            c["gbs"] = round(v["bytes"] / (v["ms"] * 1e-3) / 1e9, 1)
+            c["hbm_frac"] = round(c["gbs"] / peaks["hbm_gbs"], 3)
+        classes[k] = c
 
+    parity, cpu_ms, cores, sample = None, None, 0, "reported at N=1 only"
     if args.kernel_only:
-        cpu_ms, cores, sample = None, 0, "skipped (--kernel-only)"
-    elif world > 1:
-        cpu_ms, cores, sample = None, 0, "reported at N=1 only"
-    else:
-        if args.workload.startswith("flux") and args.workload != "flux2048_q4_k":
-            cpu_ms, cores, sample = cpu_sample(args.workload, args.cpu_budget)
-        else:
-            cpu_ms, cores, sample = None, 0, "not sampled for this workload (default workload only)"
+        sample = "skipped (--kernel-only)"
+    elif world == 1:
+        from oracle.weights import DeviceWeights
+        from oracle import edb_oracle as O
+        leg = cpu_leg(args.workload, args.cpu_budget, DeviceWeights(model))
+        cpu_ms, cores, sample = leg["ms_full"], leg["cores"], leg["sample"]
+        # the GPU runs the very same inputs at the very same (possibly reduced) latent
+        case.set_inputs(leg["latent"], leg["inputs"])
+        case.prepare()
+        case.step(False)
+        torch.cuda.synchronize()
+        got = case.out.cpu().numpy()
+        parity = {"step_rel_l2": O.rel_l2(got, leg["out"]), "cosine": O.cosine(got, leg["out"]),
+                  "latent": list(leg["latent"]), "text_tokens": case.n_txt, "full_size": leg["full_size"],
+                  "blocks": "all", "tolerance": 2e-2,
+                  "against": "fp32 non-Sage CPU oracle on the weights read back from the device"}
+
+    par = "single GPU"
+    if world > 1:
+        par = (f"CFG-parallel x2 (conditional / unconditional branch) x Ulysses sequence parallel x{case.sp}"
+               if case.cfg_parallel else f"ulysses sequence parallel x{world} (one step shared by all ranks: tokens split "
+               "for linears/norms, heads split for attention)")
     line = {
-        "metric": METRIC if args.workload == "flux1024_q8_0" else f"DiT ms/denoise-step ({args.workload})", "value": ms, "unit": "ms", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": ms, "higher_is_better": False, "scaling": "weak" if world == 1 else "strong",
+        "metric": metric_name(args.workload), "value": ms, "unit": "ms", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": False, "scaling": "strong",
         "vs_baseline": None,
-        "dtype": "f16 operands / f32 accumulate (q8_0 weights dequantised to f16, INT8 QK^T)",
+        "dtype": "f16 operands / f32 accumulate (quantised weights dequantised to f16"
+                 + (", INT8 QK^T)" if att_name == "sage" else ")"),
         "data": "synthetic",
         "tokens_per_s": tokens / (ms / 1e3),
-        "config": {"workload": args.workload, "tokens": tokens, "attention": args.attention,
-                   "cuda_graph": bool(use_graph),
-                   "parallelism": "single GPU" if world == 1 else f"ulysses sequence parallel x{world} (one step "
-                   "shared by all ranks: tokens split for linears/norms, heads split for attention)",
+        "config": {"workload": args.workload, "tokens": tokens, "attention": att_name,
+                   "cuda_graph": graph is not None, "parallelism": par,
+                   "parallel_vs_single_rel_l2": sp_rel,
                    "l2": "inputs larger than L2: the quantised weights (GBs) stream through every step",
                    "weight_bytes": case.weight_bytes(),
                    "output_finite": finite, "init_launches": init_launches},
@@ -477,10 +767,197 @@ def run_ours(args):
         "roofline": roofline,
         "kernel_classes": classes,
         "cpu_baseline": {"value": cpu_ms, "unit": "ms", "cores": cores, "kind": "port", "sample": sample},
+        "parity": parity,
     }
     print(json.dumps(line), flush=True)
+    case.close()
     if dist is not None:
         dist.destroy_process_group()
+
+
+def profile_traffic(workload):
+    """DRAM traffic of the dominant kernel from the committed capture of this workload, if there is one
+    (profiles/traffic.json: {workload: {"bytes": per launch, "source": which capture}})."""
+    path = os.path.join(ROOT, "profiles", "traffic.json")
+    try:
+        with open(path) as fh:
+            return json.load(fh).get(workload)
+    except (OSError, ValueError):
+        return None
+
+
+# --------------------------------------------------------------------------- single kernels
+
+def run_kernel(a):
+    """Times one op of libedb200.so in isolation with CUDA events (for tuning and for small profiler
+    captures).  Between timed launches a buffer larger than L2 is rewritten."""
+    import ctypes as C
+    import torch
+
+    load_pkg("build").build()
+    edb = load_pkg("edb200")
+    lib = edb.lib()
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda:0")
+    st = edb.current_stream()
+    flush = None if a.no_flush else torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    flops = bytes_ = 0.0
+    extra = {}
+
+    def make_weight(n, k):
+        t = edb.TYPE_Q8_0 if a.wtype == "q8_0" else edb.TYPE_Q4_K
+        raw_bytes = k // 32 * 34 if a.wtype == "q8_0" else k // 256 * 144
+        wf = torch.randn(n, k, device=dev) * 0.02
+        raw = torch.empty(n, raw_bytes, dtype=torch.uint8, device=dev)
+        if a.wtype == "q8_0":
+            edb.check(lib.edb200_quantize_rows_q8_0(edb.ptr(wf), edb.ptr(raw), n, k, st))
+        else:
+            raw.random_(0, 256)
+            v = raw.view(n, k // 256, 144)
+            v[:, :, 0:4] = torch.tensor([0x66, 0x1E, 0x66, 0x1E], dtype=torch.uint8, device=dev)  # d = dmin ~ 6e-3
+        return edb.QWeight(t, raw, n, k)
+
+    if a.kernel == "probe":
+        out = {}
+        for kind, name in ((0, "f16"), (1, "i8")):
+            v = C.c_double()
+            edb.check(lib.edb200_probe_mma_rate(kind, 4000, C.byref(v), st))
+            out[name] = v.value
+        peaks = measured_peaks()
+        line = {"op": "probe", "what": "tcgen05.mma 128x256 SS issued back to back on every SM, operands resident in "
+                "shared memory (tensor-pipe rate, no loads)", "f16_tflops": out["f16"], "i8_tops": out["i8"],
+                "i8_over_f16": out["i8"] / out["f16"],
+                "int8_dense_peak_estimate_tops": {"burst": peaks["tflops_burst"] * out["i8"] / out["f16"],
+                                                  "sustained": peaks["tflops"] * out["i8"] / out["f16"],
+                                                  "how": "measured cuBLAS bf16 peak x (i8 / f16 pipe rate)"}}
+        print(json.dumps(line), flush=True)
+        return
+
+    if a.kernel == "gemm":
+        w = make_weight(a.n, a.k)
+        wbytes = lib.edb200_qweight_bytes(w.handle)
+        x = torch.randn(a.m, a.k, device=dev).half()
+        bias = torch.randn(a.n, device=dev)
+        if a.epilogue == "gate":
+            res = torch.randn(a.m, a.n, device=dev)
+            gate = torch.randn(a.n, device=dev)
+            ep = edb.make_epilogue(res, bias=bias, residual=res, gate=gate)
+        elif a.epilogue == "gelu":
+            y = torch.empty(a.m, a.n, dtype=torch.float16, device=dev)
+            ep = edb.make_epilogue(y, bias=bias, act=edb.ACT_GELU_TANH)
+        else:
+            y = torch.empty(a.m, a.n, dtype=torch.float16, device=dev)
+            ep = edb.make_epilogue(y, bias=bias)
+        flops = 2.0 * a.m * a.n * a.k
+        bytes_ = wbytes + 2.0 * a.m * a.k + 2.0 * a.m * a.n
+
+        def run():
+            edb.mul_mat_q(w, x, ep)
+    elif a.kernel == "gemv":
+        w = make_weight(a.n, a.k)
+        x = torch.randn(1, a.k, device=dev)
+        y = torch.empty(1, a.n, device=dev)
+        bytes_ = float(lib.edb200_qweight_bytes(w.handle))
+
+        def run():
+            edb.check(lib.edb200_gemv_q(w.handle, edb.ptr(x), 1, a.k, 1, None, edb.ptr(y), a.n, st))
+    elif a.kernel == "gemvbatch":
+        ws = [make_weight(a.n, a.k) for _ in range(a.count)]
+        x = torch.randn(a.k, device=dev)
+        ys = [torch.empty(a.n, device=dev) for _ in range(a.count)]
+        wp = (C.c_void_p * a.count)(*[w.handle.value for w in ws])
+        yp = (C.c_void_p * a.count)(*[y.data_ptr() for y in ys])
+        plan = C.c_void_p()
+        edb.check(lib.edb200_gemv_batch_create(wp, None, yp, a.count, st, C.byref(plan)))
+        bytes_ = float(a.count) * a.n * a.k * (34.0 / 32.0 if a.wtype == "q8_0" else 144.0 / 256.0)
+        extra["weights"] = a.count
+
+        def run():
+            edb.check(lib.edb200_gemv_batch_run(plan, edb.ptr(x), 1, None, st))
+    elif a.kernel == "attention":
+        q, k, v = (torch.randn(a.hn, a.l, a.d, device=dev).half() for _ in range(3))
+        out = torch.empty(a.l, a.hn * a.d, dtype=torch.float16, device=dev)
+        flops = 4.0 * a.l * a.l * a.d * a.hn
+        scale = 1.0 / math.sqrt(a.d)
+        if a.sage:
+            n = lib.edb200_sage_scratch_bytes(a.hn, a.l, a.d)
+            scratch = torch.empty(n, dtype=torch.uint8, device=dev)
+            offs, strides = (C.c_int64 * 8)(), (C.c_int * 3)()
+            edb.check(lib.edb200_sage_scratch_layout(a.hn, a.l, a.d, offs, strides))
+            edb.check(lib.edb200_sage_quantize_qk(edb.ptr(q), edb.ptr(k), a.hn, a.l, a.d, 2 if a.no_smooth_q else 3,
+                                                  edb.ptr(scratch), n, st))
+            base = scratch.data_ptr()
+            bias = 0 if a.no_smooth_q else base + offs[6]
+
+            def run():
+                edb.check(lib.edb200_attention_sage_int8(base + offs[0], base + offs[1], edb.ptr(v), base + offs[2],
+                                                         strides[0], base + offs[3], strides[1], bias,
+                                                         strides[2], a.hn, a.l, a.d, scale, edb.ptr(out),
+                                                         edb.TYPE_F16, out.stride(0), st))
+        else:
+            def run():
+                edb.check(lib.edb200_attention_f16(edb.ptr(q), edb.ptr(k), edb.ptr(v), a.hn, a.l, a.l, a.d, scale,
+                                                   edb.ptr(out), edb.TYPE_F16, out.stride(0), st))
+    elif a.kernel == "layernorm":
+        x = torch.randn(a.rows, a.h, device=dev)
+        sh, sc = torch.randn(a.h, device=dev), torch.randn(a.h, device=dev)
+        y = torch.empty(a.rows, a.h, dtype=torch.float16, device=dev)
+        bytes_ = a.rows * a.h * 6.0
+
+        def run():
+            edb.check(lib.edb200_layernorm_modulate(edb.ptr(x), a.h, edb.ptr(sh), edb.ptr(sc), None, None, a.rows,
+                                                    a.h, 1e-6, edb.ptr(y), edb.TYPE_F16, a.h, st))
+    elif a.kernel == "qkpack":
+        hid = a.heads * a.d
+        qkv = torch.randn(a.tokens, 3 * hid, device=dev).half()
+        qw, kw = torch.ones(a.d, device=dev), torch.ones(a.d, device=dev)
+        pe = torch.randn(a.tokens, a.d // 2, 2, 2, device=dev)
+        outs = [torch.empty(a.heads, a.tokens, a.d, dtype=torch.float16, device=dev) for _ in range(3)]
+        bytes_ = a.tokens * 3.0 * hid * 4.0
+
+        def run():
+            edb.check(lib.edb200_qk_norm_rope_pack(edb.ptr(qkv), edb.TYPE_F16, 3 * hid, 0, hid, 2 * hid, a.tokens,
+                                                   a.heads, a.d, edb.ptr(qw), edb.ptr(kw), 1e-6, edb.ptr(pe), 0,
+                                                   a.tokens, edb.ptr(outs[0]), edb.ptr(outs[1]), edb.ptr(outs[2]),
+                                                   edb.TYPE_F16, st))
+    else:  # sagequant
+        q, k = (torch.randn(a.hn, a.l, a.d, device=dev).half() for _ in range(2))
+        n = lib.edb200_sage_scratch_bytes(a.hn, a.l, a.d)
+        scratch = torch.empty(n, dtype=torch.uint8, device=dev)
+        flags = 1 if a.exact_means else 3
+        bytes_ = a.hn * a.l * a.d * (13.0 if a.exact_means else 10.0)
+
+        def run():
+            edb.check(lib.edb200_sage_quantize_qk(edb.ptr(q), edb.ptr(k), a.hn, a.l, a.d, flags, edb.ptr(scratch), n,
+                                                  st))
+
+    for _ in range(max(1, a.warmup)):
+        run()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(a.iters):
+        if flush is not None:
+            flush.fill_(1)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        run()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    times.sort()
+    med = times[len(times) // 2]
+    keys = ("m", "n", "k", "wtype", "epilogue", "hn", "l", "d", "sage", "no_smooth_q", "exact_means", "rows", "h",
+            "tokens", "heads", "count", "iters", "warmup", "no_flush")
+    line = {"op": a.kernel, "args": {k: getattr(a, k) for k in keys}, "ms_median": med, "ms_min": times[0], **extra}
+    peaks = measured_peaks()
+    if flops:
+        line["tflops"] = flops / (med * 1e-3) / 1e12
+        line["frac_of_bf16_burst"] = line["tflops"] / peaks["tflops_burst"]
+    if bytes_:
+        line["gbs"] = bytes_ / (med * 1e-3) / 1e9
+        if not flops:
+            line["hbm_frac"] = line["gbs"] / peaks["hbm_gbs"]
+    print(json.dumps(line), flush=True)
 
 
 def main():
@@ -490,15 +967,42 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="flux1024_q8_0", choices=sorted(WORKLOADS))
-    ap.add_argument("--attention", default="sage", choices=["sage", "f16"])
+    ap.add_argument("--attention", default="auto", choices=["auto", "sage", "f16"])
     ap.add_argument("--kernel-only", action="store_true",
-                    help="short run for profilers: one e2e call, no cpu_baseline leg")
+                    help="short run for profilers: one e2e call, no cpu_baseline / parity leg")
     ap.add_argument("--no-graph", action="store_true", help="launch the timed steps kernel by kernel")
-    ap.add_argument("--cpu-budget", type=float, default=15.0, help="seconds of CPU work for the cpu_baseline sample")
+    ap.add_argument("--cpu-budget", type=float, default=30.0,
+                    help="seconds of CPU work the cpu_baseline / parity leg may take (the oracle's latent is "
+                         "reduced until its estimate fits; 600 runs the default workload at full size)")
+    # single-kernel mode
+    ap.add_argument("--kernel", default=None,
+                    choices=["gemm", "attention", "gemv", "gemvbatch", "layernorm", "qkpack", "sagequant", "probe"])
+    ap.add_argument("--m", type=int, default=4608)
+    ap.add_argument("--n", type=int, default=3072)
+    ap.add_argument("--k", type=int, default=3072)
+    ap.add_argument("--wtype", default="q8_0", choices=["q8_0", "q4_k"])
+    ap.add_argument("--epilogue", default="plain", choices=["plain", "gelu", "gate"])
+    ap.add_argument("--hn", type=int, default=24)
+    ap.add_argument("--l", type=int, default=4608)
+    ap.add_argument("--d", type=int, default=128)
+    ap.add_argument("--sage", action="store_true")
+    ap.add_argument("--no-smooth-q", action="store_true", help="Sage attention without the smooth-Q bias")
+    ap.add_argument("--exact-means", action="store_true")
+    ap.add_argument("--rows", type=int, default=4608)
+    ap.add_argument("--h", type=int, default=3072)
+    ap.add_argument("--tokens", type=int, default=4608)
+    ap.add_argument("--heads", type=int, default=24)
+    ap.add_argument("--count", type=int, default=76, help="gemvbatch: number of weights in the batch")
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--no-flush", action="store_true")
     args = ap.parse_args()
+    if args.kernel is not None:
+        run_kernel(args)
+        return
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
     if args.impl == "reference":
+        use_all_host_threads()
         run_reference(args)
     else:
         run_ours(args)

@@ -83,10 +83,13 @@ struct Cfg {
     static constexpr int OFF_BAR = OFF_V + KV_STAGES * V_BYTES;
     static constexpr int OFF_BIAS = OFF_BAR + 256;
     static constexpr int SMEM_BYTES = OFF_BIAS + BIAS_STAGES * BKV * 4 + 1024;
-    // Q/K panels: rows of 128 bytes (64 f16 or 128 int8); a tile is D*QK_ELEM/128 panels.
-    static constexpr int QK_PANELS = D * QK_ELEM / 128;
-    static constexpr int QK_PANEL_BYTES = 128 * 128;
+    // Q/K panels: rows of QK_ROW_BYTES (128: 64 f16 or 128 int8; 64: the 64 int8 of a 64-wide head, which
+    // takes the 64-byte swizzle); a tile is D*QK_ELEM/QK_ROW_BYTES panels.
+    static constexpr int QK_ROW_BYTES = D * QK_ELEM < 128 ? D * QK_ELEM : 128;
+    static constexpr int QK_PANELS = D * QK_ELEM / QK_ROW_BYTES;
+    static constexpr int QK_PANEL_BYTES = 128 * QK_ROW_BYTES;
     static constexpr int QK_KSTEPS = SAGE ? D / 32 : D / 16;   // 32 bytes of K per MMA either way
+    static constexpr int QK_KSTEPS_PER_PANEL = QK_ROW_BYTES / 32;
     static constexpr int V_PANELS = D / 64;
 };
 
@@ -320,7 +323,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 #pragma unroll
                 for (int p = 0; p < C::QK_PANELS; ++p) {
                     tma_load_3d(smem + C::OFF_Q + t * C::Q_BYTES + p * C::QK_PANEL_BYTES, &map_q, q_full,
-                                p * (128 / C::QK_ELEM), q0 + t * BQ, hn);
+                                p * (C::QK_ROW_BYTES / C::QK_ELEM), q0 + t * BQ, hn);
                 }
             }
             for (int j = 0; j < n_kv; ++j) {
@@ -332,7 +335,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 #pragma unroll
                 for (int p = 0; p < C::QK_PANELS; ++p) {
                     tma_load_3d(smem + C::OFF_K + st * C::K_BYTES + p * C::QK_PANEL_BYTES, &map_k, &k_full[st],
-                                p * (128 / C::QK_ELEM), j * BKV, hn);
+                                p * (C::QK_ROW_BYTES / C::QK_ELEM), j * BKV, hn);
                 }
                 if (with_bias) {
                     // The bias piece of key block j is read by the softmax threads until their P of block j
@@ -369,14 +372,16 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             tc_fence_after_sync();
             if (elect_one()) {
                 const uint32_t q_addr = smem_u32(smem + C::OFF_Q + t * C::Q_BYTES);
-                // K-major rows of 128 bytes: 64 keys further = 64 rows = 8 KB inside every panel
-                const uint32_t k_addr = smem_u32(smem + C::OFF_K + st * C::K_BYTES) + hb * (HK * 128);
+                // K-major rows of QK_ROW_BYTES: 64 keys further = 64 rows inside every panel
+                const uint32_t k_addr = smem_u32(smem + C::OFF_K + st * C::K_BYTES) + hb * (HK * C::QK_ROW_BYTES);
                 const uint32_t tmem_s = tmem_base + TMEM_S + t * 128 + hb * HK;
 #pragma unroll
                 for (int ks = 0; ks < C::QK_KSTEPS; ++ks) {
-                    const uint32_t off = (ks / 4) * C::QK_PANEL_BYTES + (ks % 4) * 32;
-                    const uint64_t ad = make_smem_desc_sw128(q_addr + off, 16, 1024);
-                    const uint64_t bd = make_smem_desc_sw128(k_addr + off, 16, 1024);
+                    const uint32_t off = (ks / C::QK_KSTEPS_PER_PANEL) * C::QK_PANEL_BYTES + (ks % C::QK_KSTEPS_PER_PANEL) * 32;
+                    const uint64_t ad = C::QK_ROW_BYTES == 128 ? make_smem_desc_sw128(q_addr + off, 16, 1024)
+                                                               : make_smem_desc_sw64(q_addr + off, 16, 512);
+                    const uint64_t bd = C::QK_ROW_BYTES == 128 ? make_smem_desc_sw128(k_addr + off, 16, 1024)
+                                                               : make_smem_desc_sw64(k_addr + off, 16, 512);
                     if (SAGE) {
                         mma_i8_ss(tmem_s, ad, bd, idesc_qk, ks > 0 ? 1u : 0u);
                     } else {
@@ -596,7 +601,8 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 }
 
 template <int D, bool SAGE>
-static edb200_status_t launch(const void* q, const void* k, const void* v, const Params& P_in, cudaStream_t stream) {
+static edb200_status_t launch(const void* q, const void* k, const void* v, int64_t q_head_rows, int64_t k_head_rows,
+                              int64_t v_head_rows, const Params& P_in, cudaStream_t stream) {
     using C = Cfg<D, SAGE>;
     Params P = P_in;
     // Two query tiles per CTA share K/V and overlap softmax with the tensor pipe; when that leaves SMs
@@ -617,22 +623,25 @@ static edb200_status_t launch(const void* q, const void* k, const void* v, const
     CUtensorMap mq, mk, mv;
     const CUtensorMapDataType qk_dt = SAGE ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     const int es = C::QK_ELEM;
-    const uint32_t box_inner = 128 / es;
-    edb200_status_t st = make_tmap_3d(&mq, qk_dt, es, q, D, P.Lq, P.HN, (uint64_t)D * es, (uint64_t)P.Lq * D * es,
-                                      box_inner, BQ, 1, CU_TENSOR_MAP_SWIZZLE_128B);
+    const uint32_t box_inner = C::QK_ROW_BYTES / es;
+    const CUtensorMapSwizzle qk_swz = C::QK_ROW_BYTES == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+    edb200_status_t st = make_tmap_3d(&mq, qk_dt, es, q, D, P.Lq, P.HN, (uint64_t)D * es, (uint64_t)q_head_rows * D * es,
+                                      box_inner, BQ, 1, qk_swz);
     if (st != EDB200_OK) return st;
-    st = make_tmap_3d(&mk, qk_dt, es, k, D, P.Lk, P.HN, (uint64_t)D * es, (uint64_t)P.Lk * D * es, box_inner, BKV, 1,
-                      CU_TENSOR_MAP_SWIZZLE_128B);
+    st = make_tmap_3d(&mk, qk_dt, es, k, D, P.Lk, P.HN, (uint64_t)D * es, (uint64_t)k_head_rows * D * es, box_inner, BKV, 1,
+                      qk_swz);
     if (st != EDB200_OK) return st;
     st = make_tmap_3d(&mv, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, v, D, P.Lk, P.HN, (uint64_t)D * 2,
-                      (uint64_t)P.Lk * D * 2, 64, BKV, 1, CU_TENSOR_MAP_SWIZZLE_128B);
+                      (uint64_t)v_head_rows * D * 2, 64, BKV, 1, CU_TENSOR_MAP_SWIZZLE_128B);
     if (st != EDB200_OK) return st;
     auto kern = attention_kernel<D, SAGE>;
-    static bool attr_set = false;
-    if (!attr_set) {
+    static bool attr_set[64] = {false};   // the attribute is per device
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
         if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(attention)");
-        attr_set = true;
+        if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
     dim3 grid((P.Lq + P.qt * BQ - 1) / (P.qt * BQ), P.HN);
     ProfScope prof(stream, PROF_ATTENTION, 4.0 * (double)P.Lq * (double)P.Lk * D * P.HN,
@@ -670,15 +679,25 @@ static edb200_status_t set_peer_out(attn::Params& P, const edb200_sp_peers_t* ds
 edb200_status_t edb200_attention_f16(const void* q, const void* k, const void* v, int hn, int64_t lq, int64_t lk,
                                      int d_head, float scale, void* out, int out_dtype, int64_t ld_out,
                                      void* stream) {
-    return edb200_attention_f16_sp(q, k, v, hn, lq, lk, d_head, scale, out, out_dtype, ld_out, nullptr, stream);
+    return edb200_attention_f16_strided(q, k, v, hn, lq, lk, lq, lk, d_head, scale, out, out_dtype, ld_out, nullptr, stream);
 }
 
 edb200_status_t edb200_attention_f16_sp(const void* q, const void* k, const void* v, int hn, int64_t lq, int64_t lk,
                                         int d_head, float scale, void* out, int out_dtype, int64_t ld_out,
                                         const edb200_sp_peers_t* dst, void* stream) {
+    return edb200_attention_f16_strided(q, k, v, hn, lq, lk, lq, lk, d_head, scale, out, out_dtype, ld_out, dst, stream);
+}
+
+edb200_status_t edb200_attention_f16_strided(const void* q, const void* k, const void* v, int hn, int64_t lq, int64_t lk,
+                                             int64_t q_head_rows, int64_t kv_head_rows, int d_head, float scale,
+                                             void* out, int out_dtype, int64_t ld_out, const edb200_sp_peers_t* dst,
+                                             void* stream) {
     if (dst != nullptr && out == nullptr) out = dst->buf[0][dst->rank < 8 && dst->rank >= 0 ? dst->rank : 0];
     if (q == nullptr || k == nullptr || v == nullptr || out == nullptr || hn <= 0 || lq <= 0 || lk <= 0) {
         return fail(EDB200_ERR_INVALID, "attention_f16: null or empty argument");
+    }
+    if (q_head_rows < lq || kv_head_rows < lk) {
+        return fail(EDB200_ERR_INVALID, "attention_f16: the rows between heads must cover the sequence");
     }
     if (d_head != 64 && d_head != 128) return fail(EDB200_ERR_UNSUPPORTED, "attention_f16: d_head must be 64 or 128");
     if (out_dtype != EDB200_TYPE_F32 && out_dtype != EDB200_TYPE_F16 && out_dtype != EDB200_TYPE_BF16) {
@@ -703,8 +722,8 @@ edb200_status_t edb200_attention_f16_sp(const void* q, const void* k, const void
     P.err = err;
     EDB_TRY(set_peer_out(P, dst, hn, d_head, out_dtype));
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (d_head == 128) return attn::launch<128, false>(q, k, v, P, s);
-    return attn::launch<64, false>(q, k, v, P, s);
+    if (d_head == 128) return attn::launch<128, false>(q, k, v, q_head_rows, kv_head_rows, kv_head_rows, P, s);
+    return attn::launch<64, false>(q, k, v, q_head_rows, kv_head_rows, kv_head_rows, P, s);
 }
 
 edb200_status_t edb200_attention_sage_int8(const void* q_i8, const void* k_i8, const void* v_f16,
@@ -712,8 +731,8 @@ edb200_status_t edb200_attention_sage_int8(const void* q_i8, const void* k_i8, c
                                            int k_scale_stride, const float* bias, int bias_stride, int hn, int64_t l,
                                            int d_head, float scale, void* out, int out_dtype, int64_t ld_out,
                                            void* stream) {
-    return edb200_attention_sage_int8_sp(q_i8, k_i8, v_f16, q_scale, q_scale_stride, k_scale, k_scale_stride, bias,
-                                         bias_stride, hn, l, d_head, scale, out, out_dtype, ld_out, nullptr, stream);
+    return edb200_attention_sage_int8_strided(q_i8, k_i8, v_f16, l, q_scale, q_scale_stride, k_scale, k_scale_stride, bias,
+                                              bias_stride, hn, l, d_head, scale, out, out_dtype, ld_out, nullptr, stream);
 }
 
 edb200_status_t edb200_attention_sage_int8_sp(const void* q_i8, const void* k_i8, const void* v_f16,
@@ -721,12 +740,22 @@ edb200_status_t edb200_attention_sage_int8_sp(const void* q_i8, const void* k_i8
                                               int k_scale_stride, const float* bias, int bias_stride, int hn,
                                               int64_t l, int d_head, float scale, void* out, int out_dtype,
                                               int64_t ld_out, const edb200_sp_peers_t* dst, void* stream) {
+    return edb200_attention_sage_int8_strided(q_i8, k_i8, v_f16, l, q_scale, q_scale_stride, k_scale, k_scale_stride, bias,
+                                              bias_stride, hn, l, d_head, scale, out, out_dtype, ld_out, dst, stream);
+}
+
+edb200_status_t edb200_attention_sage_int8_strided(const void* q_i8, const void* k_i8, const void* v_f16,
+                                                   int64_t v_head_rows, const float* q_scale, int q_scale_stride,
+                                                   const float* k_scale, int k_scale_stride, const float* bias,
+                                                   int bias_stride, int hn, int64_t l, int d_head, float scale,
+                                                   void* out, int out_dtype, int64_t ld_out,
+                                                   const edb200_sp_peers_t* dst, void* stream) {
     if (dst != nullptr && out == nullptr) out = dst->buf[0][dst->rank < 8 && dst->rank >= 0 ? dst->rank : 0];
     if (q_i8 == nullptr || k_i8 == nullptr || v_f16 == nullptr || q_scale == nullptr || k_scale == nullptr ||
-        out == nullptr || hn <= 0 || l <= 0) {
+        out == nullptr || hn <= 0 || l <= 0 || v_head_rows < l) {
         return fail(EDB200_ERR_INVALID, "attention_sage_int8: null or empty argument");
     }
-    if (d_head != 128) return fail(EDB200_ERR_UNSUPPORTED, "attention_sage_int8: d_head must be 128");
+    if (d_head != 128 && d_head != 64) return fail(EDB200_ERR_UNSUPPORTED, "attention_sage_int8: d_head must be 64 or 128");
     const int esz = out_dtype == EDB200_TYPE_F32 ? 4 : 2;
     if (ld_out < (int64_t)hn * d_head || (ld_out * esz) % 16 != 0 || (reinterpret_cast<uintptr_t>(out) & 15u)) {
         return fail(EDB200_ERR_INVALID, "attention_sage_int8: out rows must be 16-byte aligned");
@@ -755,7 +784,9 @@ edb200_status_t edb200_attention_sage_int8_sp(const void* q_i8, const void* k_i8
     P.bias_stride = bias_stride;
     P.err = err;
     EDB_TRY(set_peer_out(P, dst, hn, d_head, out_dtype));
-    return attn::launch<128, true>(q_i8, k_i8, v_f16, P, static_cast<cudaStream_t>(stream));
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (d_head == 64) return attn::launch<64, true>(q_i8, k_i8, v_f16, l, l, v_head_rows, P, s);
+    return attn::launch<128, true>(q_i8, k_i8, v_f16, l, l, v_head_rows, P, s);
 }
 
 }  // extern "C"

@@ -6,8 +6,8 @@
 //   heads a2a   [H, T_loc, d] on every rank  ->  [H/P, T, d]   (Q, K and V)
 //   tokens a2a  [T, (H/P) d]  on every rank  ->  [T_loc, H d]  (attention output)
 // This stands in for the reference's SP pack / split / gather callbacks and their
-// NCCL all-to-all (src/parallel/sp_parallel.cpp:99-469,793-831,
-// src/parallel/nccl_process_group.cpp:394-459).
+// NCCL all-to-all (src/core/parallel/sp_parallel.cpp:99-469,757-831,
+// src/core/parallel/backends/nccl/nccl_process_group.cpp:394-459).
 //
 // The head-major layout makes every message of the first exchange one contiguous
 // run on both sides, so it needs no pack or unpack kernel at all: one grouped
@@ -24,9 +24,12 @@
 // kernel, attention epilogue) and a one-kernel flag barrier (edb200_sp_barrier)
 // orders producers and consumers across GPUs.
 #include "edb200_internal.h"
+#include "edb200_ptx.cuh"
 
 #include <dlfcn.h>
 
+#include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <vector>
@@ -93,35 +96,58 @@ __global__ void interleave_heads_kernel(const uint4* __restrict__ staging, uint4
     }
 }
 
-// Cross-GPU barrier of one kernel per rank: thread p tells rank p "rank `rank` has reached
-// epoch e" (a release store at system scope into p's flag word for this rank, after a
-// system fence that orders the stream's earlier peer stores), then waits until rank p has
-// told this rank the same.  The wait is bounded; on expiry the error word is set.
+// All-gather over peer memory: this rank's rows go straight into every rank's receive buffer.
+struct GatherArgs {
+    uint4* dst[8];
+    int world;
+};
+
+__global__ void gather_rows_peer_kernel(const uint4* __restrict__ src, const GatherArgs a, long long n16) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (long long)gridDim.x * blockDim.x) {
+        const uint4 v = src[i];
+        for (int p = 0; p < a.world; ++p) a.dst[p][i] = v;
+    }
+}
+
+// Cross-GPU barrier of one kernel per rank.  The epoch lives in device memory (one word per
+// communicator, next to the flags): lane 0 reads it, the kernel uses epoch + 1 and writes that
+// back at the end, so a recorded launch (CUDA graph) advances it on every replay just like an
+// eager one.  Thread p tells rank p "rank `rank` has reached epoch e" (a release store at
+// system scope into p's flag word for this rank, after a system fence that orders the stream's
+// earlier peer stores), then waits until rank p has told this rank the same.  The wait is
+// bounded by wall clock (`limit_ns`); on expiry the error word is set and the kernel returns.
 struct BarrierArgs {
     uint32_t* flags[8];   // flags[p] = rank p's flag array (8 words, 64 bytes apart)
+    uint32_t* epoch;      // this rank's epoch word
     int rank, world;
-    uint32_t epoch;
+    unsigned long long limit_ns;
     int* err;
 };
 
 __global__ void sp_barrier_kernel(const BarrierArgs a) {
     const int p = threadIdx.x;
-    if (p >= a.world) return;
-    __threadfence_system();
-    uint32_t* theirs = a.flags[p] + a.rank * 16;
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(theirs), "r"(a.epoch) : "memory");
-    const uint32_t* mine = a.flags[a.rank] + p * 16;
-    const long long t0 = clock64();
-    uint32_t v;
-    for (;;) {
-        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
-        if (static_cast<int32_t>(v - a.epoch) >= 0) break;
-        if (clock64() - t0 > 4000000000ll) {   // about two seconds of SM clocks
-            atomicExch(a.err, 3);
-            break;
+    uint32_t e = 0;
+    if (p == 0) e = *a.epoch + 1u;
+    e = __shfl_sync(0xffffffffu, e, 0);
+    if (p < a.world) {
+        __threadfence_system();
+        uint32_t* theirs = a.flags[p] + a.rank * 16;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(theirs), "r"(e) : "memory");
+        const uint32_t* mine = a.flags[a.rank] + p * 16;
+        const unsigned long long t0 = globaltimer_ns();
+        uint32_t v;
+        for (;;) {
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+            if (static_cast<int32_t>(v - e) >= 0) break;
+            if (globaltimer_ns() - t0 > a.limit_ns) {
+                atomicExch(a.err, 3);
+                break;
+            }
+            __nanosleep(100);
         }
-        __nanosleep(100);
     }
+    __syncwarp();
+    if (p == 0) *a.epoch = e;
 }
 
 }  // namespace
@@ -135,28 +161,41 @@ struct edb200_comm {
     // peer mappings of one device allocation per rank (same size and layout on every rank)
     char* base[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
     bool mapped = false;
-    int64_t flags_off = 0;   // 8 flag words of 64 bytes each inside the allocation
-    uint32_t epoch = 0;
+    int64_t flags_off = 0;   // 8 flag words of 64 bytes each, then the epoch word, inside the allocation
+    int64_t timeout_ms = 2000;   // limit of the barrier's device-side wait
+    bool loopback = false;       // no NCCL behind it: every "peer" is this rank's own allocation
 };
+
+// Bytes of the mapped allocation that the barrier owns (from flags_off).
+static constexpr int64_t kBarrierBytes = 1024;
+static constexpr int64_t kEpochOff = 8 * 64;
 
 extern "C" {
 
 edb200_status_t edb200_sp_shard(int64_t n_tokens, int64_t n_txt, int rank, int world, int64_t* t_loc,
-                                int64_t* n_txt_local, int64_t* img_first) {
+                                int64_t* n_txt_local, int64_t* img_first, int64_t* t_rows) {
     if (world <= 0 || rank < 0 || rank >= world || n_tokens <= 0 || n_txt < 0 || n_txt > n_tokens) {
         return fail(EDB200_ERR_INVALID, "sp_shard: bad argument");
     }
-    if (n_tokens % world) {
-        return fail(EDB200_ERR_UNSUPPORTED, "sp_shard: %lld tokens do not divide over %d ranks", (long long)n_tokens, world);
-    }
-    const int64_t tl = n_tokens / world;
+    // The sequence is padded to a multiple of the world size (sp_sequence_padding, reference
+    // src/core/parallel/sp_parallel.cpp:757-768): every rank's slot is t_loc = ceil(T / P) rows, and the
+    // slots past the last real token stay empty (the last ranks own fewer rows, possibly none).
+    const int64_t tl = (n_tokens + world - 1) / world;
     const int64_t first = (int64_t)rank * tl;
+    int64_t rows = n_tokens - first;
+    if (rows < 0) rows = 0;
+    if (rows > tl) rows = tl;
     int64_t txt = n_txt - first;
     if (txt < 0) txt = 0;
-    if (txt > tl) txt = tl;
+    if (txt > rows) txt = rows;
     if (t_loc) *t_loc = tl;
+    if (t_rows) *t_rows = rows;
     if (n_txt_local) *n_txt_local = txt;
-    if (img_first) *img_first = (first > n_txt ? first : n_txt) - n_txt;
+    if (img_first) {
+        int64_t f = (first > n_txt ? first : n_txt) - n_txt;
+        if (f > n_tokens - n_txt) f = n_tokens - n_txt;
+        *img_first = f;
+    }
     return EDB200_OK;
 }
 
@@ -213,6 +252,25 @@ edb200_status_t edb200_comm_create(const void* id128, int rank, int world, edb20
     return EDB200_OK;
 }
 
+edb200_status_t edb200_comm_create_loopback(int rank, int world, edb200_comm_t** out) {
+    if (out == nullptr || world <= 0 || world > 8 || rank < 0 || rank >= world) {
+        return fail(EDB200_ERR_INVALID, "comm_create_loopback: bad argument");
+    }
+    edb200_comm* c = new (std::nothrow) edb200_comm();
+    if (c == nullptr) return fail(EDB200_ERR_NOMEM, "comm_create_loopback: host allocation failed");
+    c->rank = rank;
+    c->world = world;
+    c->loopback = true;
+    *out = c;
+    return EDB200_OK;
+}
+
+edb200_status_t edb200_comm_set_timeout_ms(edb200_comm_t* c, int64_t ms) {
+    if (c == nullptr || ms <= 0 || ms > 60000) return fail(EDB200_ERR_INVALID, "comm_set_timeout_ms: 1..60000 ms");
+    c->timeout_ms = ms;
+    return EDB200_OK;
+}
+
 void edb200_comm_destroy(edb200_comm_t* c) {
     if (c == nullptr) return;
     edb200_comm_unmap_peers(c);
@@ -242,73 +300,136 @@ edb200_status_t edb200_comm_unmap_peers(edb200_comm_t* c) {
     if (!c->mapped) return EDB200_OK;
     // nobody may still be writing into a mapping that is about to go away
     cudaDeviceSynchronize();
-    char* dev = nullptr;
-    if (cudaMalloc(reinterpret_cast<void**>(&dev), 16 * 9) == cudaSuccess) {
-        nccl_all_gather_small(c, dev, dev + 16, 16, nullptr);
-        cudaFree(dev);
+    if (!c->loopback) {
+        char* dev = nullptr;
+        if (cudaMalloc(reinterpret_cast<void**>(&dev), 16 * 9) == cudaSuccess) {
+            nccl_all_gather_small(c, dev, dev + 16, 16, nullptr);
+            cudaFree(dev);
+        }
+        for (int p = 0; p < c->world; ++p) {
+            if (p != c->rank && c->base[p] != nullptr) cudaIpcCloseMemHandle(c->base[p]);
+        }
     }
-    for (int p = 0; p < c->world; ++p) {
-        if (p != c->rank && c->base[p] != nullptr) cudaIpcCloseMemHandle(c->base[p]);
-        c->base[p] = nullptr;
-    }
+    for (int p = 0; p < c->world; ++p) c->base[p] = nullptr;
     c->mapped = false;
     return EDB200_OK;
 }
 
+// What every rank sends in the two rendezvous of the mapping: its handle with a flag that says
+// whether it has one, then whether it could open everybody else's.
+struct MapMsg {
+    cudaIpcMemHandle_t handle;
+    unsigned char ok;
+    unsigned char pad[15];
+};
+static_assert(sizeof(cudaIpcMemHandle_t) == 64 && sizeof(MapMsg) == 80, "IPC handle size");
+
+int edb200_comm_all_ok(const unsigned char* ok, int stride, int world) {
+    if (ok == nullptr || world <= 0) return 0;
+    for (int p = 0; p < world; ++p) {
+        if (ok[(size_t)p * stride] != 1) return 0;
+    }
+    return 1;
+}
+
 edb200_status_t edb200_comm_map_peers(edb200_comm_t* c, void* base, int64_t bytes, int64_t flags_off, void* stream) {
-    if (c == nullptr || base == nullptr || bytes <= 0 || flags_off < 0 || flags_off + 8 * 64 > bytes || flags_off % 64) {
+    if (c == nullptr || base == nullptr || bytes <= 0 || flags_off < 0 || flags_off + kBarrierBytes > bytes ||
+        flags_off % 64) {
         return fail(EDB200_ERR_INVALID, "comm_map_peers: bad argument");
     }
     if (c->world > 8) return fail(EDB200_ERR_UNSUPPORTED, "comm_map_peers: at most 8 ranks");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (c->loopback) {
+        EDB_TRY(edb200_comm_unmap_peers(c));
+        EDB_TRY(check_cuda(cudaMemsetAsync(static_cast<char*>(base) + flags_off, 0, kBarrierBytes, s), "flags memset"));
+        EDB_TRY(check_cuda(cudaStreamSynchronize(s), "comm_map_peers"));
+        for (int p = 0; p < c->world; ++p) c->base[p] = static_cast<char*>(base);
+        c->mapped = true;
+        c->flags_off = flags_off;
+        return EDB200_OK;
+    }
     if (nccl_api() == nullptr) return fail(EDB200_ERR_UNSUPPORTED, "comm_map_peers: libnccl.so.2 not available");
     EDB_TRY(edb200_comm_unmap_peers(c));
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
-    cudaIpcMemHandle_t mine;
-    cudaError_t e = cudaIpcGetMemHandle(&mine, base);
+    // The call is collective: from here on every rank runs BOTH rendezvous whatever fails locally, and
+    // carries its failure in the message, so that all ranks take the same decision together and
+    // nobody is left waiting in a rendezvous that a peer has abandoned.
+    MapMsg mine;
+    memset(&mine, 0, sizeof(mine));
+    char local_err[160] = "";
+    cudaError_t e = cudaIpcGetMemHandle(&mine.handle, base);
+    const char* inject = getenv("EDB200_TEST_FAIL_IPC_RANK");   // host-side fault injection for the tests
+    if (e == cudaSuccess && inject != nullptr && atoi(inject) == c->rank) e = cudaErrorNotSupported;
     if (e != cudaSuccess) {
         cudaGetLastError();
-        return fail(EDB200_ERR_UNSUPPORTED, "comm_map_peers: cudaIpcGetMemHandle: %s", cudaGetErrorString(e));
+        snprintf(local_err, sizeof(local_err), "cudaIpcGetMemHandle: %s", cudaGetErrorString(e));
+        memset(&mine.handle, 0, sizeof(mine.handle));
+    } else {
+        mine.ok = 1;
     }
-    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
     char* dev = nullptr;
-    e = cudaMalloc(reinterpret_cast<void**>(&dev), 64 * 9);
-    if (e != cudaSuccess) return check_cuda(e, "comm_map_peers scratch");
-    cudaMemcpyAsync(dev, &mine, 64, cudaMemcpyHostToDevice, s);
-    cudaMemsetAsync(static_cast<char*>(base) + flags_off, 0, 8 * 64, s);
-    edb200_status_t st = nccl_all_gather_small(c, dev, dev + 64, 64, s);
-    cudaIpcMemHandle_t all[8];
-    if (st == EDB200_OK) st = check_cuda(cudaMemcpy(all, dev + 64, (size_t)c->world * 64, cudaMemcpyDeviceToHost), "handles");
-    cudaFree(dev);
-    if (st != EDB200_OK) return st;
-    for (int p = 0; p < c->world; ++p) {
-        if (p == c->rank) {
-            c->base[p] = static_cast<char*>(base);
-            continue;
-        }
-        void* ptr = nullptr;
-        e = cudaIpcOpenMemHandle(&ptr, all[p], cudaIpcMemLazyEnablePeerAccess);
-        if (e != cudaSuccess) {
-            cudaGetLastError();
-            for (int q = 0; q < p; ++q) {
-                if (q != c->rank && c->base[q]) cudaIpcCloseMemHandle(c->base[q]);
-                c->base[q] = nullptr;
+    e = cudaMalloc(reinterpret_cast<void**>(&dev), sizeof(MapMsg) * 9);
+    if (e != cudaSuccess) {
+        // without device scratch this rank cannot even say so: this is the one failure the peers only
+        // see as a time-out of NCCL itself
+        return check_cuda(e, "comm_map_peers scratch");
+    }
+    MapMsg all[8];
+    memset(all, 0, sizeof(all));
+    cudaMemcpyAsync(dev, &mine, sizeof(MapMsg), cudaMemcpyHostToDevice, s);
+    cudaMemsetAsync(static_cast<char*>(base) + flags_off, 0, kBarrierBytes, s);
+    edb200_status_t st = nccl_all_gather_small(c, dev, dev + sizeof(MapMsg), sizeof(MapMsg), s);
+    if (st == EDB200_OK) {
+        st = check_cuda(cudaMemcpy(all, dev + sizeof(MapMsg), (size_t)c->world * sizeof(MapMsg), cudaMemcpyDeviceToHost),
+                        "handles");
+    }
+    if (st != EDB200_OK) {   // the transport itself failed: no second rendezvous is possible either
+        cudaFree(dev);
+        return st;
+    }
+    bool have_all = edb200_comm_all_ok(&all[0].ok, (int)sizeof(MapMsg), c->world) == 1;
+    bool opened_all = have_all;
+    if (have_all) {
+        for (int p = 0; p < c->world; ++p) {
+            if (p == c->rank) {
+                c->base[p] = static_cast<char*>(base);
+                continue;
             }
-            return fail(EDB200_ERR_UNSUPPORTED, "comm_map_peers: cudaIpcOpenMemHandle(rank %d): %s", p,
-                        cudaGetErrorString(e));
+            void* ptr = nullptr;
+            e = cudaIpcOpenMemHandle(&ptr, all[p].handle, cudaIpcMemLazyEnablePeerAccess);
+            if (e != cudaSuccess) {
+                cudaGetLastError();
+                snprintf(local_err, sizeof(local_err), "cudaIpcOpenMemHandle(rank %d): %s", p, cudaGetErrorString(e));
+                opened_all = false;
+                break;
+            }
+            c->base[p] = static_cast<char*>(ptr);
         }
-        c->base[p] = static_cast<char*>(ptr);
+    }
+    // second rendezvous: did everybody open everything?  It also orders every rank's flag memset
+    // before anybody's first signal.
+    MapMsg second;
+    memset(&second, 0, sizeof(second));
+    second.ok = opened_all ? 1 : 0;
+    cudaMemcpyAsync(dev, &second, sizeof(MapMsg), cudaMemcpyHostToDevice, s);
+    st = nccl_all_gather_small(c, dev, dev + sizeof(MapMsg), sizeof(MapMsg), s);
+    if (st == EDB200_OK) {
+        st = check_cuda(cudaMemcpy(all, dev + sizeof(MapMsg), (size_t)c->world * sizeof(MapMsg), cudaMemcpyDeviceToHost),
+                        "map result");
+    }
+    cudaFree(dev);
+    const bool everybody = st == EDB200_OK && edb200_comm_all_ok(&all[0].ok, (int)sizeof(MapMsg), c->world) == 1;
+    if (!everybody) {
+        for (int p = 0; p < c->world; ++p) {
+            if (p != c->rank && c->base[p] != nullptr) cudaIpcCloseMemHandle(c->base[p]);
+            c->base[p] = nullptr;
+        }
+        if (st != EDB200_OK) return st;
+        return fail(EDB200_ERR_UNSUPPORTED, "comm_map_peers: peer mappings unavailable (%s)",
+                    local_err[0] ? local_err : "another rank could not map");
     }
     c->mapped = true;
     c->flags_off = flags_off;
-    c->epoch = 0;
-    // every rank has cleared its flags (the rendezvous above came after the memset in stream order
-    // only for this rank): meet once more before anybody signals
-    char* dev2 = nullptr;
-    e = cudaMalloc(reinterpret_cast<void**>(&dev2), 16 * 9);
-    if (e != cudaSuccess) return check_cuda(e, "comm_map_peers scratch");
-    st = nccl_all_gather_small(c, dev2, dev2 + 16, 16, s);
-    cudaFree(dev2);
-    return st;
+    return EDB200_OK;
 }
 
 int edb200_comm_peers_mapped(const edb200_comm_t* c) { return c != nullptr && c->mapped ? 1 : 0; }
@@ -325,9 +446,10 @@ edb200_status_t edb200_sp_barrier(edb200_comm_t* c, void* stream) {
     BarrierArgs a;
     memset(&a, 0, sizeof(a));
     for (int p = 0; p < c->world; ++p) a.flags[p] = reinterpret_cast<uint32_t*>(c->base[p] + c->flags_off);
+    a.epoch = reinterpret_cast<uint32_t*>(c->base[c->rank] + c->flags_off + kEpochOff);
     a.rank = c->rank;
     a.world = c->world;
-    a.epoch = ++c->epoch;
+    a.limit_ns = static_cast<unsigned long long>(c->timeout_ms) * 1000000ull;
     a.err = err;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     ProfScope prof(s, PROF_OTHER, 0.0, 0.0);
@@ -335,6 +457,8 @@ edb200_status_t edb200_sp_barrier(edb200_comm_t* c, void* stream) {
     count_launch();
     return check_cuda(cudaGetLastError(), "sp_barrier launch");
 }
+
+edb200_status_t edb200_poll_status(void* stream) { return poll_device_error(static_cast<cudaStream_t>(stream)); }
 
 int edb200_comm_rank(const edb200_comm_t* c) { return c ? c->rank : 0; }
 int edb200_comm_world(const edb200_comm_t* c) { return c ? c->world : 1; }
@@ -346,6 +470,7 @@ edb200_status_t edb200_sp_all_to_all_heads(edb200_comm_t* c, const void* const* 
     }
     NcclApi* a = nccl_api();
     if (a == nullptr) return fail(EDB200_ERR_UNSUPPORTED, "sp_all_to_all_heads: libnccl.so.2 not available");
+    if (c->comm == nullptr) return fail(EDB200_ERR_UNSUPPORTED, "sp_all_to_all_heads: a loopback communicator has no transport");
     const int n = edb200_sp_heads_plan(c->rank, c->world, heads, t_loc, row_bytes, nullptr, nullptr, nullptr, nullptr, 0);
     if (n < 0) return fail(EDB200_ERR_INVALID, "sp_all_to_all_heads: heads must divide over the ranks");
     std::vector<int> peer(n);
@@ -378,6 +503,7 @@ edb200_status_t edb200_sp_all_to_all_tokens(edb200_comm_t* c, const void* send, 
     }
     NcclApi* a = nccl_api();
     if (a == nullptr) return fail(EDB200_ERR_UNSUPPORTED, "sp_all_to_all_tokens: libnccl.so.2 not available");
+    if (c->comm == nullptr) return fail(EDB200_ERR_UNSUPPORTED, "sp_all_to_all_tokens: a loopback communicator has no transport");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const size_t piece = (size_t)(t_loc * chunk_bytes);
     EDB_TRY(check_nccl(a->GroupStart(), "ncclGroupStart"));
@@ -408,6 +534,7 @@ edb200_status_t edb200_sp_all_gather_rows(edb200_comm_t* c, const void* send, vo
     }
     NcclApi* a = nccl_api();
     if (a == nullptr) return fail(EDB200_ERR_UNSUPPORTED, "sp_all_gather_rows: libnccl.so.2 not available");
+    if (c->comm == nullptr) return fail(EDB200_ERR_UNSUPPORTED, "sp_all_gather_rows: a loopback communicator has no transport");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const size_t mine = (size_t)(row_count[c->rank] * row_bytes);
     EDB_TRY(check_nccl(a->GroupStart(), "ncclGroupStart"));
@@ -424,6 +551,39 @@ edb200_status_t edb200_sp_all_gather_rows(edb200_comm_t* c, const void* send, vo
     return check_nccl(rc_end, "ncclGroupEnd");
 }
 
+edb200_status_t edb200_sp_all_gather_rows_peer(edb200_comm_t* c, const void* send, void* recv, const int64_t* row_first,
+                                               const int64_t* row_count, int64_t row_bytes, void* stream) {
+    if (c == nullptr || recv == nullptr || row_first == nullptr || row_count == nullptr || row_bytes <= 0) {
+        return fail(EDB200_ERR_INVALID, "sp_all_gather_rows_peer: bad argument");
+    }
+    if (!c->mapped) return fail(EDB200_ERR_INVALID, "sp_all_gather_rows_peer: peers are not mapped");
+    if (row_bytes % 16 || (reinterpret_cast<uintptr_t>(recv) & 15u) || (reinterpret_cast<uintptr_t>(send) & 15u)) {
+        return fail(EDB200_ERR_INVALID, "sp_all_gather_rows_peer: rows must be multiples of 16 bytes and 16-byte aligned");
+    }
+    const char* lo = c->base[c->rank];
+    if (static_cast<const char*>(recv) < lo) return fail(EDB200_ERR_INVALID, "sp_all_gather_rows_peer: recv is outside the mapped allocation");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const long long n16 = (long long)(row_count[c->rank] * row_bytes / 16);
+    if (n16 > 0) {
+        if (send == nullptr) return fail(EDB200_ERR_INVALID, "sp_all_gather_rows_peer: null send buffer");
+        GatherArgs a;
+        memset(&a, 0, sizeof(a));
+        a.world = c->world;
+        for (int p = 0; p < c->world; ++p) {
+            char* base = static_cast<char*>(edb200_comm_peer_ptr(c, p, recv));
+            a.dst[p] = reinterpret_cast<uint4*>(base + row_first[c->rank] * row_bytes);
+        }
+        long long blocks = (n16 + 255) / 256;
+        if (blocks > 148 * 8) blocks = 148 * 8;
+        ProfScope prof(s, PROF_ELEMENTWISE, 0.0, (double)n16 * 16.0 * (1 + c->world));
+        gather_rows_peer_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(static_cast<const uint4*>(send), a, n16);
+        count_launch();
+        EDB_TRY(check_cuda(cudaGetLastError(), "sp gather launch"));
+    }
+    // every rank's rows have landed everywhere once all ranks have passed this point
+    return edb200_sp_barrier(c, stream);
+}
+
 edb200_status_t edb200_cfg_parallel_combine(edb200_comm_t* c, const float* mine, float scale, float* gathered, float* out,
                                             int64_t n, void* stream) {
     if (c == nullptr || mine == nullptr || gathered == nullptr || out == nullptr || n <= 0 || n % 4) {
@@ -434,6 +594,21 @@ edb200_status_t edb200_cfg_parallel_combine(edb200_comm_t* c, const float* mine,
     EDB_TRY(edb200_sp_all_gather_rows(c, mine, gathered, first, count, n * 4, stream));
     // rank 0 ran the conditional branch, rank 1 the unconditional one
     return edb200_cfg_combine(gathered + n, gathered, scale, out, n, stream);
+}
+
+edb200_status_t edb200_cfg_parallel_combine_rescaled(edb200_comm_t* c, const float* mine, float scale, int patch_size,
+                                                     int channels, int height, int width, float* gathered, float* out,
+                                                     void* stream) {
+    const int64_t n = (int64_t)channels * height * width;
+    if (c == nullptr || mine == nullptr || gathered == nullptr || out == nullptr || n <= 0) {
+        return fail(EDB200_ERR_INVALID, "cfg_parallel_combine_rescaled: bad argument");
+    }
+    if (c->world != 2) {
+        return fail(EDB200_ERR_UNSUPPORTED, "cfg_parallel_combine_rescaled: the communicator must have 2 ranks");
+    }
+    const int64_t first[2] = {0, 1}, count[2] = {1, 1};
+    EDB_TRY(edb200_sp_all_gather_rows(c, mine, gathered, first, count, n * 4, stream));
+    return edb200_cfg_combine_rescaled(gathered + n, gathered, scale, patch_size, channels, height, width, out, stream);
 }
 
 }  // extern "C"

@@ -42,12 +42,16 @@ struct edb200_flux {
     // sequence-parallel execution (world > 1): this rank's token slice and exchange buffers
     edb200_comm_t* comm = nullptr;
     int rank = 0, world = 1;
-    int64_t t_loc = 0, txt_l = 0, img_l = 0, img_first = 0;
+    int64_t t_loc = 0, t_rows = 0, txt_l = 0, img_l = 0, img_first = 0;   // slot rows, owned rows, ...
     void *QL = nullptr, *KL = nullptr, *VL = nullptr, *AOUT = nullptr, *STG = nullptr;
     float* TOK_LOC = nullptr;
     // peer-memory exchange: producers store into the owning rank's buffers, flag barriers order them
     bool p2p = false;
     edb200_sp_peers_t qkv_peers, cat_peers;
+    // all adaLN projections of a step as one weight-streaming launch (built in prepare)
+    edb200_gemv_batch_t* mod_batch = nullptr;
+    uint64_t mod_batch_gen = 0;
+    edb200_sp_peers_t mods_peers;
     float* tap = nullptr;
     // host staging for compute_host
     float* pinned = nullptr;
@@ -182,6 +186,9 @@ edb200_status_t attention(edb200_flux* m, int64_t T, void* out, int64_t ld_out, 
     const int d = c.hidden_size / c.num_heads;
     const int heads = c.num_heads / m->world;
     const float scale = 1.0f / std::sqrt(static_cast<float>(d));
+    // rows between heads in Q/K/V: the sequence padded to a multiple of the world size under
+    // sequence parallelism (only the T real rows are attended over)
+    const int64_t head_rows = m->world > 1 ? m->t_loc * m->world : T;
     if (m->p2p) {
         // Q/K/V rows were stored into their owners by the pack kernels; wait until every rank's are in,
         // let the attention epilogue store each output row into its owner's `out` rows, and meet
@@ -189,12 +196,13 @@ edb200_status_t attention(edb200_flux* m, int64_t T, void* out, int64_t ld_out, 
         // rank has finished reading its Q/K/V, so the next block's pack kernels may overwrite them.
         EDB_TRY(edb200_sp_barrier(m->comm, s));
         if (c.attention == EDB200_ATTN_SAGE_INT8) {
-            EDB_TRY(edb200_sage_attention_sp(m->Q, m->K, m->V, heads, T, d, scale,
-                                             (c.sage_smooth_q ? EDB200_SAGE_SMOOTH_Q : 0) | EDB200_SAGE_FAST_MEANS,
-                                             m->SAGE, m->sage_bytes, nullptr, EDB200_TYPE_F16, ld_out, &m->cat_peers, s));
+            EDB_TRY(edb200_sage_attention_strided(m->Q, m->K, m->V, heads, T, head_rows, d, scale,
+                                                  (c.sage_smooth_q ? EDB200_SAGE_SMOOTH_Q : 0) | EDB200_SAGE_FAST_MEANS,
+                                                  m->SAGE, m->sage_bytes, nullptr, EDB200_TYPE_F16, ld_out,
+                                                  &m->cat_peers, s));
         } else {
-            EDB_TRY(edb200_attention_f16_sp(m->Q, m->K, m->V, heads, T, T, d, scale, nullptr, EDB200_TYPE_F16, ld_out,
-                                            &m->cat_peers, s));
+            EDB_TRY(edb200_attention_f16_strided(m->Q, m->K, m->V, heads, T, T, head_rows, head_rows, d, scale, nullptr,
+                                                 EDB200_TYPE_F16, ld_out, &m->cat_peers, s));
         }
         return edb200_sp_barrier(m->comm, s);
     }
@@ -208,11 +216,12 @@ edb200_status_t attention(edb200_flux* m, int64_t T, void* out, int64_t ld_out, 
         att_ld = (int64_t)heads * d;
     }
     if (c.attention == EDB200_ATTN_SAGE_INT8) {
-        EDB_TRY(edb200_sage_attention(m->Q, m->K, m->V, heads, T, d, scale,
-                                      (c.sage_smooth_q ? EDB200_SAGE_SMOOTH_Q : 0) | EDB200_SAGE_FAST_MEANS, m->SAGE,
-                                      m->sage_bytes, att_out, EDB200_TYPE_F16, att_ld, s));
+        EDB_TRY(edb200_sage_attention_strided(m->Q, m->K, m->V, heads, T, head_rows, d, scale,
+                                              (c.sage_smooth_q ? EDB200_SAGE_SMOOTH_Q : 0) | EDB200_SAGE_FAST_MEANS,
+                                              m->SAGE, m->sage_bytes, att_out, EDB200_TYPE_F16, att_ld, nullptr, s));
     } else {
-        EDB_TRY(edb200_attention_f16(m->Q, m->K, m->V, heads, T, T, d, scale, att_out, EDB200_TYPE_F16, att_ld, s));
+        EDB_TRY(edb200_attention_f16_strided(m->Q, m->K, m->V, heads, T, T, head_rows, head_rows, d, scale, att_out,
+                                             EDB200_TYPE_F16, att_ld, nullptr, s));
     }
     if (m->world > 1) {
         EDB_TRY(edb200_sp_all_to_all_tokens(m->comm, m->AOUT, m->STG, out, m->t_loc, (int64_t)heads * d * 2, ld_out * 2, s));
@@ -252,6 +261,39 @@ edb200_status_t qk_pack(edb200_flux* m, const __half* qkv, int64_t rows, int64_t
     return edb200_qk_norm_rope_pack(qkv, EDB200_TYPE_F16, 3 * H, 0, H, 2 * H, rows, c.num_heads, d, qs, ks, 1e-6f, pe,
                                     local_first, m->t_loc, sp ? m->QL : m->Q, sp ? m->KL : m->K, sp ? m->VL : m->V,
                                     EDB200_TYPE_F16, s);
+}
+
+// The adaLN projections of the whole step as one batch: [double i: img 6H, txt 6H] ... [single i: 3H].
+// Built at the first step after prepare or after a tensor was reloaded (it caches device addresses).
+edb200_status_t ensure_mod_batch(edb200_flux* m, cudaStream_t s) {
+    if (m->mod_batch != nullptr && m->mod_batch_gen == m->params.generation()) return EDB200_OK;
+    const edb200_flux_config_t& c = m->cfg;
+    const int64_t H = c.hidden_size;
+    edb200_gemv_batch_destroy(m->mod_batch);
+    m->mod_batch = nullptr;
+    std::vector<const edb200_qweight_t*> bw;
+    std::vector<const float*> bb;
+    std::vector<float*> by;
+    for (int i = 0; i < c.depth; ++i) {
+        const std::string p = "double_blocks." + std::to_string(i) + ".";
+        for (int st = 0; st < 2; ++st) {
+            const Lin l = qlin(m, p + (st == 0 ? "img" : "txt") + "_mod.lin");
+            bw.push_back(l.w), bb.push_back(l.b), by.push_back(m->MODS + ((int64_t)i * 12 + st * 6) * H);
+        }
+    }
+    for (int i = 0; i < c.depth_single_blocks; ++i) {
+        const Lin l = qlin(m, "single_blocks." + std::to_string(i) + ".modulation.lin");
+        bw.push_back(l.w), bb.push_back(l.b), by.push_back(m->MODS + ((int64_t)c.depth * 12 + (int64_t)i * 3) * H);
+    }
+    EDB_TRY(edb200_gemv_batch_create(bw.data(), bb.data(), by.data(), (int)bw.size(), s, &m->mod_batch));
+    m->mod_batch_gen = m->params.generation();
+    memset(&m->mods_peers, 0, sizeof(m->mods_peers));
+    if (m->p2p) {
+        m->mods_peers.world = m->world;
+        m->mods_peers.rank = m->rank;
+        for (int r = 0; r < m->world; ++r) m->mods_peers.buf[0][r] = edb200_comm_peer_ptr(m->comm, r, m->MODS);
+    }
+    return EDB200_OK;
 }
 
 }  // namespace
@@ -294,6 +336,7 @@ edb200_status_t edb200_flux_create(const edb200_flux_config_t* cfg, edb200_flux_
 void edb200_flux_destroy(edb200_flux_t* m) {
     if (m == nullptr) return;
     if (m->pinned) cudaFreeHost(m->pinned);
+    edb200_gemv_batch_destroy(m->mod_batch);
     delete m;
 }
 
@@ -322,6 +365,12 @@ edb200_status_t edb200_flux_set_tensor(edb200_flux_t* m, const char* name, int g
                                        int64_t nbytes, int on_device, void* stream) {
     if (m == nullptr || name == nullptr) return fail(EDB200_ERR_INVALID, "flux_set_tensor: null argument");
     return m->params.set(name, ggml_type, data, nbytes, on_device != 0, static_cast<cudaStream_t>(stream));
+}
+
+edb200_status_t edb200_flux_get_tensor_f32(const edb200_flux_t* m, const char* name, float* out, int64_t n_floats,
+                                          int on_device, void* stream) {
+    if (m == nullptr || name == nullptr) return fail(EDB200_ERR_INVALID, "flux_get_tensor_f32: null argument");
+    return m->params.fetch_f32(name, out, n_floats, on_device != 0, static_cast<cudaStream_t>(stream));
 }
 
 edb200_status_t edb200_flux_load_gguf(edb200_flux_t* m, const char* path, const char* strip_prefix, int* n_loaded,
@@ -357,12 +406,13 @@ edb200_status_t edb200_flux_prepare(edb200_flux_t* m, int latent_h, int latent_w
     const int h_tok = latent_h / p, w_tok = latent_w / p;
     const int64_t n_img = (int64_t)h_tok * w_tok, T = n_img + n_txt;
     const int lat_c = c.in_channels / (p * p);
-    int64_t t_loc = T, txt_l = n_txt, img_first = 0;
+    int64_t t_loc = T, t_rows = T, txt_l = n_txt, img_first = 0;
     if (m->world > 1) {
         if (c.num_heads % m->world) {
             return fail(EDB200_ERR_UNSUPPORTED, "flux_prepare: %d heads do not divide over %d ranks", c.num_heads, m->world);
         }
-        EDB_TRY(edb200_sp_shard(T, n_txt, m->rank, m->world, &t_loc, &txt_l, &img_first));
+        EDB_TRY(edb200_sp_shard(T, n_txt, m->rank, m->world, &t_loc, &txt_l, &img_first, &t_rows));
+        if (t_rows == 0) return fail(EDB200_ERR_UNSUPPORTED, "flux_prepare: %lld tokens leave rank %d without rows", (long long)T, m->rank);
     }
     const int64_t sage =
         c.attention == EDB200_ATTN_SAGE_INT8 ? edb200_sage_scratch_bytes(c.num_heads / m->world, T, (int)d) : 0;
@@ -379,7 +429,7 @@ edb200_status_t edb200_flux_prepare(edb200_flux_t* m, int latent_h, int latent_w
     cudaStreamSynchronize(s);
     if (m->comm != nullptr) EDB_TRY(edb200_comm_unmap_peers(m->comm));   // collective; the old workspace goes away
     m->p2p = false;
-    if (m->world > 1) total += 1024;
+    if (m->world > 1) total += 2048;
     EDB_TRY(m->ws.reserve(total));
     Workspace& w = m->ws;
     m->X = w.take_n<float>(T * H);
@@ -417,7 +467,7 @@ edb200_status_t edb200_flux_prepare(edb200_flux_t* m, int latent_h, int latent_w
         if (m->TOK_LOC == nullptr) return fail(EDB200_ERR_NOMEM, "flux_prepare: workspace accounting error");
     }
     if (m->world > 1) {
-        void* flags = w.take(8 * 64);
+        void* flags = w.take(1024);   // barrier flags + epoch
         if (flags == nullptr) return fail(EDB200_ERR_NOMEM, "flux_prepare: workspace accounting error");
         const char* how = getenv("EDB200_SP_EXCHANGE");   // "nccl" keeps the library exchanges (comparison runs)
         const bool want_p2p = how == nullptr || strcmp(how, "nccl") != 0;
@@ -443,12 +493,16 @@ edb200_status_t edb200_flux_prepare(edb200_flux_t* m, int latent_h, int latent_w
         }
     }
     m->t_loc = t_loc;
+    m->t_rows = t_rows;
     m->txt_l = txt_l;
-    m->img_l = t_loc - txt_l;
+    m->img_l = t_rows - txt_l;
     m->img_first = img_first;
     if (m->YVEC == nullptr || (sage > 0 && m->SAGE == nullptr)) {
         return fail(EDB200_ERR_NOMEM, "flux_prepare: workspace accounting error");
     }
+    // the batch of adaLN projections points into the workspace: rebuilt at the next step
+    edb200_gemv_batch_destroy(m->mod_batch);
+    m->mod_batch = nullptr;
     // position table and sinusoid frequencies are computed once per shape on the host
     std::vector<float> pe = build_flux_pe(c, h_tok, w_tok, n_txt);
     std::vector<float> freq(128);
@@ -503,8 +557,8 @@ static edb200_status_t flux_step_body(edb200_flux_t* m, const float* latent, flo
     const int64_t H = c.hidden_size, M = c.mlp_hidden;
     const int64_t T = (int64_t)m->n_txt + m->n_img;   // whole sequence (attention length)
     // rows this rank owns: all of them on one GPU, a slice [text rows ; image rows] otherwise
-    const int64_t n_txt = m->txt_l, n_img = m->img_l, TL = m->t_loc;
-    const int64_t txt_first = m->world > 1 ? (int64_t)m->rank * TL : 0;   // first owned text row (if any)
+    const int64_t n_txt = m->txt_l, n_img = m->img_l, TL = m->t_rows;
+    const int64_t txt_first = m->world > 1 ? (int64_t)m->rank * m->t_loc : 0;   // first owned text row (if any)
     // A sequence-parallel rank's out-projections have few output tiles and long reductions: let
     // them be cut along k (their adds into the residual stream are then unordered).  A single
     // GPU keeps every sum in one fixed order.
@@ -545,20 +599,13 @@ static edb200_status_t flux_step_body(edb200_flux_t* m, const float* latent, flo
     EDB_TRY(dense(m, "vector_in.out_layer", m->TMP_H, 1, H, 0, EDB200_ACT_NONE, m->TMP_H + H, H, s));
     launch_add_inplace(m->VEC, m->TMP_H + H, H, s);
 
-    // ---- every adaLN vector of the step: lin(silu(vec)), weight streaming
+    // ---- every adaLN vector of the step: lin(silu(vec)), weight streaming, one launch for all of them
+    // (sequence-parallel ranks with peer memory each stream 1/N of the weights and store to all)
     float* mods = m->MODS;
-    for (int i = 0; i < c.depth; ++i) {
-        const std::string p = "double_blocks." + std::to_string(i) + ".";
-        for (int st = 0; st < 2; ++st) {
-            const Lin l = qlin(m, p + (st == 0 ? "img" : "txt") + "_mod.lin");
-            EDB_TRY(edb200_gemv_q(l.w, m->VEC, 1, H, 1, l.b, mods + ((int64_t)i * 12 + st * 6) * H, 6 * H, s));
-        }
-    }
     float* smods = mods + (int64_t)c.depth * 12 * H;
-    for (int i = 0; i < c.depth_single_blocks; ++i) {
-        const Lin l = qlin(m, "single_blocks." + std::to_string(i) + ".modulation.lin");
-        EDB_TRY(edb200_gemv_q(l.w, m->VEC, 1, H, 1, l.b, smods + (int64_t)i * 3 * H, 3 * H, s));
-    }
+    EDB_TRY(ensure_mod_batch(m, s));
+    EDB_TRY(edb200_gemv_batch_run(m->mod_batch, m->VEC, 1, m->p2p ? &m->mods_peers : nullptr, s));
+    if (m->p2p) EDB_TRY(edb200_sp_barrier(m->comm, s));
     float* fmods = smods + (int64_t)c.depth_single_blocks * 3 * H;
     EDB_TRY(dense(m, "final_layer.adaLN_modulation.1", m->VEC, 1, H, 1, EDB200_ACT_NONE, fmods, 2 * H, s));
 
@@ -650,13 +697,17 @@ static edb200_status_t flux_step_body(edb200_flux_t* m, const float* latent, flo
         }
         std::vector<int64_t> first(m->world), count(m->world);
         for (int r = 0; r < m->world; ++r) {
-            int64_t tl = 0, tx = 0, f = 0;
-            EDB_TRY(edb200_sp_shard(T, m->n_txt, r, m->world, &tl, &tx, &f));
+            int64_t tx = 0, f = 0, rows = 0;
+            EDB_TRY(edb200_sp_shard(T, m->n_txt, r, m->world, nullptr, &tx, &f, &rows));
             first[r] = f;
-            count[r] = tl - tx;
+            count[r] = rows - tx;
         }
-        EDB_TRY(edb200_sp_all_gather_rows(m->comm, m->TOK_LOC, m->TOK_OUT, first.data(), count.data(),
-                                          (int64_t)c.in_channels * 4, s));
+        if (m->p2p) {
+            // peer stores + barrier: nothing of the step goes through a library exchange
+            EDB_TRY(edb200_sp_all_gather_rows_peer(m->comm, m->TOK_LOC, m->TOK_OUT, first.data(), count.data(), (int64_t)c.in_channels * 4, s));
+        } else {
+            EDB_TRY(edb200_sp_all_gather_rows(m->comm, m->TOK_LOC, m->TOK_OUT, first.data(), count.data(), (int64_t)c.in_channels * 4, s));
+        }
     }
     launch_unpatchify(m->TOK_OUT, out, lat_c, m->lat_h, m->lat_w, c.patch_size, s);
     return check_cuda(cudaGetLastError(), "flux_step");

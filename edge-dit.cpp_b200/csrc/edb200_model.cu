@@ -240,6 +240,7 @@ edb200_status_t ParamTable::set(const std::string& name, int ggml_type, const vo
         if (e != cudaSuccess) return check_cuda(e, "set_tensor copy");
     }
     p->loaded = true;
+    ++generation_;
     return EDB200_OK;
 }
 
@@ -300,6 +301,35 @@ edb200_status_t ParamTable::init_random(uint64_t seed, float std, cudaStream_t s
     cudaFree(tmp);
     cudaFree(raw);
     return st;
+}
+
+edb200_status_t ParamTable::fetch_f32(const std::string& name, float* out, int64_t n_floats, bool on_device,
+                                      cudaStream_t stream) const {
+    const Param* p = get(name);
+    if (p == nullptr) return fail(EDB200_ERR_INVALID, "get_tensor: unknown tensor '%s'", name.c_str());
+    if (!p->loaded) return fail(EDB200_ERR_INVALID, "get_tensor: '%s' has not been set", name.c_str());
+    const int64_t n = p->spec.n_out * p->spec.k;
+    if (out == nullptr || n_floats != n) {
+        return fail(EDB200_ERR_INVALID, "get_tensor: '%s' has %lld values, room for %lld given", name.c_str(),
+                    (long long)n, (long long)n_floats);
+    }
+    float* dev = out;
+    if (!on_device && p->spec.quantised) {
+        cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&dev), n * 4);
+        if (e != cudaSuccess) return fail(EDB200_ERR_NOMEM, "get_tensor: cudaMalloc: %s", cudaGetErrorString(e));
+    }
+    edb200_status_t st = EDB200_OK;
+    cudaError_t e = cudaSuccess;
+    if (p->spec.quantised) {
+        st = edb200_qweight_dequantize(p->qw, dev, stream);
+        if (st == EDB200_OK && !on_device) e = cudaMemcpyAsync(out, dev, n * 4, cudaMemcpyDeviceToHost, stream);
+    } else {
+        e = cudaMemcpyAsync(out, p->f32, n * 4, on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyDeviceToHost, stream);
+    }
+    if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+    if (dev != out) cudaFree(dev);
+    if (st != EDB200_OK) return st;
+    return check_cuda(e, "get_tensor copy");
 }
 
 edb200_status_t ParamTable::all_loaded() const {

@@ -41,14 +41,21 @@ public:
     // Synthetic weights generated on the device: N(0, std) (norm scales 1 + N(0, std)),
     // quantised with the device q8_0 / q4_K encoders.
     edb200_status_t init_random(uint64_t seed, float std, cudaStream_t stream);
+    // The tensor's values as f32 [n_out, k] (quantised weights dequantised from the repacked device form,
+    // bit-identical to ggml's dequantize_row of the blocks that were loaded) into host or device memory.
+    edb200_status_t fetch_f32(const std::string& name, float* out, int64_t n_floats, bool on_device,
+                              cudaStream_t stream) const;
     edb200_status_t all_loaded() const;
     int64_t device_bytes() const { return bytes_; }
+    // Changes whenever a tensor is (re)loaded: cached views of the weights (e.g. a GEMV batch) are rebuilt.
+    uint64_t generation() const { return generation_; }
     std::vector<Param>& params() { return params_; }
 
 private:
     std::vector<Param> params_;
     std::map<std::string, size_t> index_;
     int64_t bytes_ = 0;
+    uint64_t generation_ = 0;
 };
 
 // Loads every tensor of a GGUF file that `table` knows (edb200_gguf.cu).

@@ -239,6 +239,17 @@ __device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr, uin
     return d;
 }
 
+// The same with the 64-byte swizzle (rows of 64 bytes, 8-row groups of 512 bytes; layout 4 = SWIZZLE_64B).
+__device__ __forceinline__ uint64_t make_smem_desc_sw64(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+    d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
+    d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
+    d |= 1ull << 46;
+    d |= 4ull << 61;
+    return d;
+}
+
 // Instruction descriptor (32 bit):
 //   [4,6) D format (0 f16, 1 f32, 2 s32)   [7,10) A format   [10,13) B format
 //   bit 15 A major (0 = K)                 bit 16 B major (0 = K, 1 = MN)

@@ -2,6 +2,10 @@
 // raw ggml blocks, the exact dequantiser that proves the repack changes no value,
 // and the small-m weight-streaming GEMV that reads the tiles directly.
 #include "edb200_internal.h"
+
+#include <cstring>
+#include <new>
+#include <vector>
 #include "edb200_codec.cuh"
 
 #include <cuda_fp16.h>
@@ -215,6 +219,146 @@ gemv_q_kernel(const uint8_t* __restrict__ tiles, const float* __restrict__ x, in
     }
 }
 
+
+// ------------------------------------------------------------ batched GEMV --
+// Every adaLN projection of a denoise step has the same input vector (silu of the conditioning
+// vector) and the same row length, so all of them run as ONE launch that streams their weights
+// back to back: CTA b works on 32 rows of the weight that owns row block b (table of first
+// blocks, binary search), the input is activated once by a small kernel and staged per CTA with
+// 16-byte loads, and every warp has the loads of two k-steps in flight before it waits for the
+// staging barrier.  Sequence-parallel ranks split the row blocks between them and store their
+// results into every rank's output (peer pointers), so the weight stream is not replicated.
+struct GemvBatchItem {
+    const uint8_t* tiles;
+    const float* bias;
+    float* y;
+    int n_out;
+    int block0;   // first row block (32 rows) of this weight in the launch
+};
+
+__global__ void gemv_activate_kernel(const float* __restrict__ x, float* __restrict__ xa, int k, int pre_silu) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= k) return;
+    float v = x[i];
+    if (pre_silu) v = v / (1.0f + __expf(-v));
+    xa[i] = v;
+}
+
+struct GemvPeers {
+    long long delta[8];   // byte offset from this rank's output address to the same place on rank p
+    int world;
+};
+
+template <int WT>
+__global__ void __launch_bounds__(GEMV_WARPS * 32)
+gemv_q_batch_kernel(const GemvBatchItem* __restrict__ items, int n_items, const float* __restrict__ xa, int k, int ksteps,
+                    int block_first, const GemvPeers peers) {
+    extern __shared__ float xs[];  // [k], then [GEMV_WARPS][32] partial sums
+    const int b = block_first + blockIdx.x;
+    int lo = 0, hi = n_items - 1;
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (items[mid].block0 <= b) lo = mid; else hi = mid - 1;
+    }
+    const GemvBatchItem it = items[lo];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n = (b - it.block0) * 32 + lane;
+    const int64_t t = n / kQwTileRows;
+    const int r = n % kQwTileRows;
+    constexpr int TB = WT == EDB200_TYPE_Q8_0 ? kQwTileBytesQ8 : kQwTileBytesQ4;
+    constexpr int NV = WT == EDB200_TYPE_Q8_0 ? 4 : 2;
+    const uint8_t* base = it.tiles + t * ksteps * (int64_t)TB;
+    // weight loads of the first two k-steps go out before the input is staged
+    uint4 raw[2][NV];
+    uint32_t sc[2][2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+        const int s = warp + u * GEMV_WARPS;
+        if (s < ksteps) {
+            const uint8_t* tile = base + (int64_t)s * TB;
+#pragma unroll
+            for (int c = 0; c < NV; ++c) raw[u][c] = __ldg(reinterpret_cast<const uint4*>(tile + (c * 128 + r) * 16));
+            if (WT == EDB200_TYPE_Q8_0) {
+                sc[u][0] = *reinterpret_cast<const uint16_t*>(tile + 8192 + r * 2) |
+                           (static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(tile + 8192 + (128 + r) * 2)) << 16);
+            } else {
+                sc[u][0] = *reinterpret_cast<const uint16_t*>(tile + 4096 + r * 2) |
+                           (static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(tile + 4096 + (128 + r) * 2)) << 16);
+                sc[u][1] = *reinterpret_cast<const uint16_t*>(tile + 4608 + r * 2) |
+                           (static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(tile + 4608 + (128 + r) * 2)) << 16);
+            }
+        }
+    }
+    for (int i = threadIdx.x; i < k / 4; i += blockDim.x) {
+        reinterpret_cast<float4*>(xs)[i] = __ldg(reinterpret_cast<const float4*>(xa) + i);
+    }
+    __syncthreads();
+    float acc = 0.0f;
+    for (int s0 = warp; s0 < ksteps; s0 += 2 * GEMV_WARPS) {
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int s = s0 + u * GEMV_WARPS;
+            if (s >= ksteps) break;
+            const float* xp = xs + s * 64;
+            const __half2 h0 = *reinterpret_cast<const __half2*>(&sc[u][0]);
+            if (WT == EDB200_TYPE_Q8_0) {
+                const float p0 = dot16_s8(raw[u][0], xp) + dot16_s8(raw[u][1], xp + 16);
+                const float p1 = dot16_s8(raw[u][2], xp + 32) + dot16_s8(raw[u][3], xp + 48);
+                acc += __low2float(h0) * p0 + __high2float(h0) * p1;
+            } else {
+                const __half2 h1 = *reinterpret_cast<const __half2*>(&sc[u][1]);
+                float pl = 0.f, ph = 0.f, sl = 0.f, sh = 0.f;
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    const uint32_t w[4] = {raw[u][c].x, raw[u][c].y, raw[u][c].z, raw[u][c].w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const uint32_t byte = (w[j] >> (8 * e)) & 0xFF;
+                            const float xlo = xp[c * 16 + 4 * j + e], xhi = xp[32 + c * 16 + 4 * j + e];
+                            pl = fmaf(static_cast<float>(byte & 0x0F), xlo, pl);
+                            ph = fmaf(static_cast<float>(byte >> 4), xhi, ph);
+                            sl += xlo;
+                            sh += xhi;
+                        }
+                    }
+                }
+                acc += __low2float(h0) * pl - __low2float(h1) * sl + __high2float(h0) * ph - __high2float(h1) * sh;
+            }
+            // refill this slot with the k-step two rounds ahead
+            const int sn = s + 2 * GEMV_WARPS;
+            if (sn < ksteps) {
+                const uint8_t* tile = base + (int64_t)sn * TB;
+#pragma unroll
+                for (int c = 0; c < NV; ++c) raw[u][c] = __ldg(reinterpret_cast<const uint4*>(tile + (c * 128 + r) * 16));
+                if (WT == EDB200_TYPE_Q8_0) {
+                    sc[u][0] = *reinterpret_cast<const uint16_t*>(tile + 8192 + r * 2) |
+                               (static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(tile + 8192 + (128 + r) * 2)) << 16);
+                } else {
+                    sc[u][0] = *reinterpret_cast<const uint16_t*>(tile + 4096 + r * 2) |
+                               (static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(tile + 4096 + (128 + r) * 2)) << 16);
+                    sc[u][1] = *reinterpret_cast<const uint16_t*>(tile + 4608 + r * 2) |
+                               (static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(tile + 4608 + (128 + r) * 2)) << 16);
+                }
+            }
+        }
+    }
+    float* part = xs + k;
+    part[warp * 32 + lane] = acc;
+    __syncthreads();
+    if (warp == 0) {
+        float v = 0.0f;
+#pragma unroll
+        for (int g = 0; g < GEMV_WARPS; ++g) v += part[g * 32 + lane];
+        if (n < it.n_out) {
+            v += it.bias ? it.bias[n] : 0.0f;
+            char* dst = reinterpret_cast<char*>(it.y + n);
+            for (int p = 0; p < peers.world; ++p) *reinterpret_cast<float*>(dst + peers.delta[p]) = v;
+        }
+    }
+}
+
 template <int WT>
 static edb200_status_t launch_gemv_q(const edb200_qweight_t* w, const float* x, int64_t m, int64_t ldx, int pre_silu,
                                      const float* bias, float* y, int64_t ldy, cudaStream_t stream) {
@@ -323,6 +467,118 @@ edb200_status_t edb200_qweight_dequantize(const edb200_qweight_t* w, float* out,
     }
     count_launch();
     return check_cuda(cudaGetLastError(), "qweight_dequantize launch");
+}
+
+struct edb200_gemv_batch {
+    int n = 0;
+    int ggml_type = 0;
+    int64_t k = 0, ksteps = 0;
+    int total_blocks = 0;
+    double weight_bytes = 0.0, flops = 0.0;
+    edb::GemvBatchItem* items = nullptr;   // device
+    float* xa = nullptr;                   // device, [k]
+};
+
+edb200_status_t edb200_gemv_batch_create(const edb200_qweight_t* const* w, const float* const* bias, float* const* y, int n,
+                                         void* stream, edb200_gemv_batch_t** out) {
+    if (w == nullptr || y == nullptr || out == nullptr || n <= 0) return fail(EDB200_ERR_INVALID, "gemv_batch_create: null or empty argument");
+    std::vector<edb::GemvBatchItem> items(n);
+    edb200_gemv_batch* b = new (std::nothrow) edb200_gemv_batch();
+    if (b == nullptr) return fail(EDB200_ERR_NOMEM, "gemv_batch_create: host allocation failed");
+    int blocks = 0;
+    for (int i = 0; i < n; ++i) {
+        if (w[i] == nullptr || y[i] == nullptr) {
+            delete b;
+            return fail(EDB200_ERR_INVALID, "gemv_batch_create: null weight or output %d", i);
+        }
+        if (i == 0) {
+            b->ggml_type = w[i]->ggml_type;
+            b->k = w[i]->k;
+            b->ksteps = w[i]->ksteps;
+        } else if (w[i]->ggml_type != b->ggml_type || w[i]->k != b->k) {
+            delete b;
+            return fail(EDB200_ERR_INVALID, "gemv_batch_create: all weights must share one block type and row length");
+        }
+        items[i].tiles = w[i]->tiles;
+        items[i].bias = bias ? bias[i] : nullptr;
+        items[i].y = y[i];
+        items[i].n_out = static_cast<int>(w[i]->n_out);
+        items[i].block0 = blocks;
+        blocks += static_cast<int>(w[i]->n_tiles * (kQwTileRows / 32));
+        b->weight_bytes += (double)w[i]->n_out * (double)w[i]->k * (w[i]->ggml_type == EDB200_TYPE_Q8_0 ? 34.0 / 32.0 : 144.0 / 256.0);
+        b->flops += 2.0 * (double)w[i]->n_out * (double)w[i]->k;
+    }
+    if ((b->k * 4 + GEMV_WARPS * 32 * 4) > 200 * 1024 || b->k % 4) {
+        delete b;
+        return fail(EDB200_ERR_UNSUPPORTED, "gemv_batch_create: row length too large for the shared-memory stage");
+    }
+    b->n = n;
+    b->total_blocks = blocks;
+    cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&b->items), sizeof(edb::GemvBatchItem) * n);
+    if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&b->xa), b->k * 4);
+    if (e == cudaSuccess) {
+        e = cudaMemcpyAsync(b->items, items.data(), sizeof(edb::GemvBatchItem) * n, cudaMemcpyHostToDevice,
+                            static_cast<cudaStream_t>(stream));
+    }
+    if (e == cudaSuccess) e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) {
+        edb200_gemv_batch_destroy(b);
+        return check_cuda(e, "gemv_batch_create");
+    }
+    *out = b;
+    return EDB200_OK;
+}
+
+void edb200_gemv_batch_destroy(edb200_gemv_batch_t* b) {
+    if (b == nullptr) return;
+    cudaFree(b->items);
+    cudaFree(b->xa);
+    delete b;
+}
+
+edb200_status_t edb200_gemv_batch_run(const edb200_gemv_batch_t* b, const float* x, int pre_silu, const edb200_sp_peers_t* share,
+                                      void* stream) {
+    if (b == nullptr || x == nullptr) return fail(EDB200_ERR_INVALID, "gemv_batch_run: null argument");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    edb::GemvPeers peers;
+    memset(&peers, 0, sizeof(peers));
+    peers.world = 1;
+    int first = 0, count = b->total_blocks;
+    if (share != nullptr) {
+        if (share->world <= 0 || share->world > 8 || share->rank < 0 || share->rank >= share->world) {
+            return fail(EDB200_ERR_INVALID, "gemv_batch_run: bad peer description");
+        }
+        // rank r computes row blocks [r * per, (r + 1) * per) and stores them on every rank:
+        // buf[0][p] is rank p's copy of one common reference address
+        peers.world = share->world;
+        for (int p = 0; p < share->world; ++p) {
+            if (share->buf[0][p] == nullptr) return fail(EDB200_ERR_INVALID, "gemv_batch_run: null peer buffer");
+            peers.delta[p] = static_cast<const char*>(share->buf[0][p]) - static_cast<const char*>(share->buf[0][share->rank]);
+        }
+        const int per = (b->total_blocks + share->world - 1) / share->world;
+        first = share->rank * per;
+        count = b->total_blocks - first;
+        if (count > per) count = per;
+        if (count < 0) count = 0;
+    }
+    const size_t smem = (static_cast<size_t>(b->k) + GEMV_WARPS * 32) * sizeof(float);
+    const double frac = b->total_blocks > 0 ? (double)count / b->total_blocks : 0.0;
+    ProfScope prof(s, PROF_GEMV, b->flops * frac, b->weight_bytes * frac);
+    gemv_activate_kernel<<<static_cast<unsigned>((b->k + 255) / 256), 256, 0, s>>>(x, b->xa, static_cast<int>(b->k), pre_silu);
+    count_launch();
+    if (count > 0) {
+        if (b->ggml_type == EDB200_TYPE_Q8_0) {
+            auto kern = edb::gemv_q_batch_kernel<EDB200_TYPE_Q8_0>;
+            if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            kern<<<count, GEMV_WARPS * 32, smem, s>>>(b->items, b->n, b->xa, (int)b->k, (int)b->ksteps, first, peers);
+        } else {
+            auto kern = edb::gemv_q_batch_kernel<EDB200_TYPE_Q4_K>;
+            if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            kern<<<count, GEMV_WARPS * 32, smem, s>>>(b->items, b->n, b->xa, (int)b->k, (int)b->ksteps, first, peers);
+        }
+        count_launch();
+    }
+    return check_cuda(cudaGetLastError(), "gemv_batch launch");
 }
 
 edb200_status_t edb200_gemv_q(const edb200_qweight_t* w, const float* x, int64_t m, int64_t ldx, int pre_silu,

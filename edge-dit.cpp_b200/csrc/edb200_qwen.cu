@@ -43,11 +43,15 @@ struct edb200_qwen {
     // [text ; image] sequence and the exchange buffers (see edb200_flux.cu for the scheme)
     edb200_comm_t* comm = nullptr;
     int rank = 0, world = 1;
-    int64_t t_loc = 0, txt_l = 0, img_l = 0, img_first = 0;
+    int64_t t_loc = 0, t_rows = 0, txt_l = 0, img_l = 0, img_first = 0;   // slot rows, owned rows, ...
     bool p2p = false;
     void *QL = nullptr, *KL = nullptr, *VL = nullptr, *AOUT = nullptr, *STG = nullptr;
     float* TOK_LOC = nullptr;
     edb200_sp_peers_t qkv_peers, att_peers;
+    // all img_mod.1 / txt_mod.1 projections of a pass as one weight-streaming launch
+    edb200_gemv_batch_t* mod_batch = nullptr;
+    uint64_t mod_batch_gen = 0;
+    edb200_sp_peers_t mods_peers;
 };
 
 namespace {
@@ -82,10 +86,15 @@ void register_params(edb200_qwen* m) {
     const edb200_qwen_config_t& c = m->cfg;
     const int64_t H = hidden(c), M = c.mlp_hidden;
     ParamTable& t = m->params;
-    // Quantised: 2-D weights whose row length is a multiple of 256 (tensor_should_be_converted,
-    // reference src/core/runtime/model_loader.cpp:2141-2172); img_in (row length 64) stays f32.
+    // Quantised: 2-D weights whose row length is a multiple of 256, except the in-embedders `img_in.`
+    // and `txt_in.` that tensor_should_be_converted excludes by name (reference
+    // src/core/runtime/model_loader.cpp:2141-2172).  The modulation projections img_mod.1 / txt_mod.1
+    // are floored at q8_0: a block type with fewer bits per weight is lifted (set_wtype_override, :1746-1761).
     auto lin = [&](const std::string& name, int64_t n_out, int64_t k) {
-        t.add(name + ".weight", n_out, k, k % 256 == 0, c.wtype);
+        const bool embedder = name.rfind("img_in", 0) == 0 || name.rfind("txt_in", 0) == 0;
+        const bool mod = name.size() > 6 && name.compare(name.size() - 6, 6, "_mod.1") == 0;
+        const int wt = (mod && c.wtype == EDB200_TYPE_Q4_K) ? EDB200_TYPE_Q8_0 : c.wtype;
+        t.add(name + ".weight", n_out, k, k % 256 == 0 && !embedder, wt);
         t.add(name + ".bias", 1, n_out, false, c.wtype);
     };
     lin("time_text_embed.timestep_embedder.linear_1", H, 256);
@@ -150,12 +159,13 @@ std::vector<float> build_qwen_pe(const edb200_qwen_config_t& c, int h_tok, int w
     return pe;
 }
 
-// y[row, c] = f16(x[row, c] * rstd[row] * w[c])   (txt_norm: RMSNorm over the whole context row)
+// y[row, c] = (x[row, c] * rstd[row]) * w[c]   (txt_norm: RMSNorm over the whole context row, f32 like
+// the f32 txt_in linear that reads it)
 __global__ void rms_apply_kernel(const float* __restrict__ x, const float* __restrict__ rstd, const float* __restrict__ w,
-                                 __half* __restrict__ y, int cols, int64_t total) {
+                                 float* __restrict__ y, int cols, int64_t total) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
-    y[i] = __float2half_rn((x[i] * rstd[i / cols]) * w[i % cols]);
+    y[i] = (x[i] * rstd[i / cols]) * w[i % cols];
 }
 
 edb200_status_t ln_mod(const float* x, int64_t H, const float* shift, const float* scale, int64_t rows, void* y,
@@ -201,14 +211,16 @@ edb200_status_t joint_attention(edb200_qwen* m, int64_t T, cudaStream_t s) {
     const float scale = 1.0f / std::sqrt(static_cast<float>(d));
     const int flags = (c.sage_smooth_q ? EDB200_SAGE_SMOOTH_Q : 0) | EDB200_SAGE_FAST_MEANS;
     const bool sage = c.attention == EDB200_ATTN_SAGE_INT8;
+    // rows between heads in Q/K/V: the sequence padded to a multiple of the world size
+    const int64_t head_rows = m->world > 1 ? m->t_loc * m->world : T;
     if (m->p2p) {
         EDB_TRY(edb200_sp_barrier(m->comm, s));
         if (sage) {
-            EDB_TRY(edb200_sage_attention_sp(m->Q, m->K, m->V, heads, T, d, scale, flags, m->SAGE, m->sage_bytes, nullptr,
-                                             EDB200_TYPE_F16, H, &m->att_peers, s));
+            EDB_TRY(edb200_sage_attention_strided(m->Q, m->K, m->V, heads, T, head_rows, d, scale, flags, m->SAGE,
+                                                  m->sage_bytes, nullptr, EDB200_TYPE_F16, H, &m->att_peers, s));
         } else {
-            EDB_TRY(edb200_attention_f16_sp(m->Q, m->K, m->V, heads, T, T, d, scale, nullptr, EDB200_TYPE_F16, H,
-                                            &m->att_peers, s));
+            EDB_TRY(edb200_attention_f16_strided(m->Q, m->K, m->V, heads, T, T, head_rows, head_rows, d, scale, nullptr,
+                                                 EDB200_TYPE_F16, H, &m->att_peers, s));
         }
         return edb200_sp_barrier(m->comm, s);
     }
@@ -222,13 +234,42 @@ edb200_status_t joint_attention(edb200_qwen* m, int64_t T, cudaStream_t s) {
         att_ld = (int64_t)heads * d;
     }
     if (sage) {
-        EDB_TRY(edb200_sage_attention(m->Q, m->K, m->V, heads, T, d, scale, flags, m->SAGE, m->sage_bytes, att_out,
-                                      EDB200_TYPE_F16, att_ld, s));
+        EDB_TRY(edb200_sage_attention_strided(m->Q, m->K, m->V, heads, T, head_rows, d, scale, flags, m->SAGE,
+                                              m->sage_bytes, att_out, EDB200_TYPE_F16, att_ld, nullptr, s));
     } else {
-        EDB_TRY(edb200_attention_f16(m->Q, m->K, m->V, heads, T, T, d, scale, att_out, EDB200_TYPE_F16, att_ld, s));
+        EDB_TRY(edb200_attention_f16_strided(m->Q, m->K, m->V, heads, T, T, head_rows, head_rows, d, scale, att_out,
+                                             EDB200_TYPE_F16, att_ld, nullptr, s));
     }
     if (m->world > 1) {
         EDB_TRY(edb200_sp_all_to_all_tokens(m->comm, m->AOUT, m->STG, m->ATT, m->t_loc, (int64_t)heads * d * 2, H * 2, s));
+    }
+    return EDB200_OK;
+}
+
+// Every img_mod.1 / txt_mod.1 projection of the pass as one batch (block i: img 6H then txt 6H); built at the
+// first pass after prepare or after a tensor was reloaded (it caches device addresses).
+edb200_status_t ensure_mod_batch(edb200_qwen* m, cudaStream_t s) {
+    if (m->mod_batch != nullptr && m->mod_batch_gen == m->params.generation()) return EDB200_OK;
+    const edb200_qwen_config_t& c = m->cfg;
+    const int64_t H = hidden(c);
+    edb200_gemv_batch_destroy(m->mod_batch);
+    m->mod_batch = nullptr;
+    std::vector<const edb200_qweight_t*> bw;
+    std::vector<const float*> bb;
+    std::vector<float*> by;
+    for (int i = 0; i < c.num_layers; ++i) {
+        const std::string pb = "transformer_blocks." + std::to_string(i) + ".";
+        const Lin li = qlin(m, pb + "img_mod.1"), lt = qlin(m, pb + "txt_mod.1");
+        bw.push_back(li.w), bb.push_back(li.b), by.push_back(m->MODS + (int64_t)i * 12 * H);
+        bw.push_back(lt.w), bb.push_back(lt.b), by.push_back(m->MODS + ((int64_t)i * 12 + 6) * H);
+    }
+    EDB_TRY(edb200_gemv_batch_create(bw.data(), bb.data(), by.data(), (int)bw.size(), s, &m->mod_batch));
+    m->mod_batch_gen = m->params.generation();
+    memset(&m->mods_peers, 0, sizeof(m->mods_peers));
+    if (m->p2p) {
+        m->mods_peers.world = m->world;
+        m->mods_peers.rank = m->rank;
+        for (int r = 0; r < m->world; ++r) m->mods_peers.buf[0][r] = edb200_comm_peer_ptr(m->comm, r, m->MODS);
     }
     return EDB200_OK;
 }
@@ -272,6 +313,7 @@ edb200_status_t edb200_qwen_create(const edb200_qwen_config_t* cfg, edb200_qwen_
 void edb200_qwen_destroy(edb200_qwen_t* m) {
     if (m == nullptr) return;
     if (m->pinned) cudaFreeHost(m->pinned);
+    edb200_gemv_batch_destroy(m->mod_batch);
     delete m;
 }
 
@@ -300,6 +342,12 @@ edb200_status_t edb200_qwen_set_tensor(edb200_qwen_t* m, const char* name, int g
                                        int64_t nbytes, int on_device, void* stream) {
     if (m == nullptr || name == nullptr) return fail(EDB200_ERR_INVALID, "qwen_set_tensor: null argument");
     return m->params.set(name, ggml_type, data, nbytes, on_device != 0, static_cast<cudaStream_t>(stream));
+}
+
+edb200_status_t edb200_qwen_get_tensor_f32(const edb200_qwen_t* m, const char* name, float* out, int64_t n_floats,
+                                          int on_device, void* stream) {
+    if (m == nullptr || name == nullptr) return fail(EDB200_ERR_INVALID, "qwen_get_tensor_f32: null argument");
+    return m->params.fetch_f32(name, out, n_floats, on_device != 0, static_cast<cudaStream_t>(stream));
 }
 
 edb200_status_t edb200_qwen_load_gguf(edb200_qwen_t* m, const char* path, const char* strip_prefix, int* n_loaded,
@@ -353,12 +401,13 @@ edb200_status_t edb200_qwen_prepare(edb200_qwen_t* m, int lat_h, int lat_w, int 
     const int lat_c = c.in_channels / (p * p);
     const int64_t pf_out = (int64_t)c.out_channels * p * p;
     const int64_t lat_in = (int64_t)lat_c * lat_h * lat_w, lat_out = (int64_t)c.out_channels * lat_h * lat_w;
-    int64_t t_loc = T, txt_l = n_txt, img_first = 0;
+    int64_t t_loc = T, t_rows = T, txt_l = n_txt, img_first = 0;
     if (m->world > 1) {
         if (c.num_heads % m->world) {
             return fail(EDB200_ERR_UNSUPPORTED, "qwen_prepare: %d heads do not divide over %d ranks", c.num_heads, m->world);
         }
-        EDB_TRY(edb200_sp_shard(T, n_txt, m->rank, m->world, &t_loc, &txt_l, &img_first));
+        EDB_TRY(edb200_sp_shard(T, n_txt, m->rank, m->world, &t_loc, &txt_l, &img_first, &t_rows));
+        if (t_rows == 0) return fail(EDB200_ERR_UNSUPPORTED, "qwen_prepare: %lld tokens leave rank %d without rows", (long long)T, m->rank);
     }
     const int64_t sage =
         c.attention == EDB200_ATTN_SAGE_INT8 ? edb200_sage_scratch_bytes(c.num_heads / m->world, T, (int)d) : 0;
@@ -366,14 +415,16 @@ edb200_status_t edb200_qwen_prepare(edb200_qwen_t* m, int lat_h, int lat_w, int 
     auto al = [](int64_t b) { return (b + 255) & ~int64_t(255); };
     int64_t total = al(T * H * 4) + al(T * H * 2) + al(T * 3 * H * 2) + 4 * al(T * H * 2) + al(T * M * 2);
     total += al(((int64_t)12 * c.num_layers + 2) * H * 4) + al(H * 4) + al(H * 4) + al(256 * 4) + al(128 * 4) + al(pe_elems * 4);
-    total += al((int64_t)n_txt * c.joint_attention_dim * 2) + al(n_txt * 4) + al(n_img * c.in_channels * 4) +
+    total += al((int64_t)n_txt * c.joint_attention_dim * 4) + al(n_txt * 4) + al(n_img * c.in_channels * 4) +
              al(n_img * pf_out * 4) + al(lat_in * 4) + al(lat_out * 4) + al((int64_t)n_txt * c.joint_attention_dim * 4) +
              al(sage) + 8192;
-    if (m->world > 1) total += 5 * al(t_loc * H * 2) + al(n_img * pf_out * 4) + 1024;
+    if (m->world > 1) total += 5 * al(t_loc * H * 2) + al(n_img * pf_out * 4) + 2048;
     cudaStreamSynchronize(s);
     if (m->comm != nullptr) EDB_TRY(edb200_comm_unmap_peers(m->comm));   // collective; the old workspace goes away
     m->p2p = false;
     EDB_TRY(m->ws.reserve(total));
+    edb200_gemv_batch_destroy(m->mod_batch);   // it points into the old workspace: rebuilt at the next pass
+    m->mod_batch = nullptr;
     Workspace& w = m->ws;
     m->X = w.take_n<float>(T * H);
     m->XMOD = w.take(T * H * 2);
@@ -389,7 +440,7 @@ edb200_status_t edb200_qwen_prepare(edb200_qwen_t* m, int lat_h, int lat_w, int 
     m->TEMB = w.take_n<float>(256);
     m->FREQ = w.take_n<float>(128);
     m->PE = w.take_n<float>(pe_elems);
-    m->CTXN = w.take((int64_t)n_txt * c.joint_attention_dim * 2);
+    m->CTXN = w.take((int64_t)n_txt * c.joint_attention_dim * 4);
     m->RSTD = w.take_n<float>(n_txt);
     m->TOK_IN = w.take_n<float>(n_img * c.in_channels);
     m->TOK_OUT = w.take_n<float>(n_img * pf_out);
@@ -404,7 +455,7 @@ edb200_status_t edb200_qwen_prepare(edb200_qwen_t* m, int lat_h, int lat_w, int 
     m->QL = m->KL = m->VL = m->AOUT = m->STG = nullptr;
     m->TOK_LOC = nullptr;
     if (m->world > 1) {
-        void* flags = w.take(8 * 64);
+        void* flags = w.take(1024);   // barrier flags + epoch
         m->QL = w.take(t_loc * H * 2);
         m->KL = w.take(t_loc * H * 2);
         m->VL = w.take(t_loc * H * 2);
@@ -435,8 +486,9 @@ edb200_status_t edb200_qwen_prepare(edb200_qwen_t* m, int lat_h, int lat_w, int 
         }
     }
     m->t_loc = t_loc;
+    m->t_rows = t_rows;
     m->txt_l = txt_l;
-    m->img_l = t_loc - txt_l;
+    m->img_l = t_rows - txt_l;
     m->img_first = img_first;
     std::vector<float> pe = build_qwen_pe(c, h_tok, w_tok, n_txt);
     std::vector<float> freq(128);
@@ -501,11 +553,11 @@ edb200_status_t edb200_qwen_step(edb200_qwen_t* m, const float* latent, float ti
         EDB_TRY(edb200_row_rstd(ctx_l, EDB200_TYPE_F32, c.joint_attention_dim, n_txt, c.joint_attention_dim, 1e-6f, m->RSTD, s));
         const int64_t total = n_txt * c.joint_attention_dim;
         rms_apply_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, s>>>(
-            ctx_l, m->RSTD, fparam(m, "txt_norm.weight"), static_cast<__half*>(m->CTXN), c.joint_attention_dim, total);
+            ctx_l, m->RSTD, fparam(m, "txt_norm.weight"), static_cast<float*>(m->CTXN), c.joint_attention_dim, total);
         count_launch();
-        const Lin l = qlin(m, "txt_in");
-        edb200_epilogue_t ep = make_ep(X_txt, EDB200_TYPE_F32, H, l.b);
-        EDB_TRY(edb200_mul_mat_q(l.w, m->CTXN, F16, n_txt, c.joint_attention_dim, &ep, s));
+        EDB_TRY(edb200_linear_f32(m->params.get("txt_in.weight")->f32, fparam(m, "txt_in.bias"),
+                                  static_cast<const float*>(m->CTXN), n_txt, c.joint_attention_dim, H,
+                                  c.joint_attention_dim, 0, EDB200_ACT_NONE, X_txt, H, s));
     }
     launch_timestep_embedding(m->FREQ, timestep, 1.0f, 128, m->TEMB, s);
     {
@@ -515,14 +567,12 @@ edb200_status_t edb200_qwen_step(edb200_qwen_t* m, const float* latent, float ti
         EDB_TRY(edb200_gemv_q(l2.w, m->TMP, 1, H, 1, l2.b, m->TVEC, H, s));   // SiLU between the two
     }
 
-    // ---- every adaLN vector of the pass: mod.1(silu(t)), weight streaming
+    // ---- every adaLN vector of the pass: mod.1(silu(t)), weight streaming, one launch for all of them
+    // (sequence-parallel ranks with peer memory each stream 1/N of the weights and store to all)
     float* mods = m->MODS;
-    for (int i = 0; i < c.num_layers; ++i) {
-        const std::string pb = "transformer_blocks." + std::to_string(i) + ".";
-        const Lin li = qlin(m, pb + "img_mod.1"), lt = qlin(m, pb + "txt_mod.1");
-        EDB_TRY(edb200_gemv_q(li.w, m->TVEC, 1, H, 1, li.b, mods + (int64_t)i * 12 * H, 6 * H, s));
-        EDB_TRY(edb200_gemv_q(lt.w, m->TVEC, 1, H, 1, lt.b, mods + ((int64_t)i * 12 + 6) * H, 6 * H, s));
-    }
+    EDB_TRY(ensure_mod_batch(m, s));
+    EDB_TRY(edb200_gemv_batch_run(m->mod_batch, m->TVEC, 1, m->p2p ? &m->mods_peers : nullptr, s));
+    if (m->p2p) EDB_TRY(edb200_sp_barrier(m->comm, s));
     float* fmods = mods + (int64_t)c.num_layers * 12 * H;
     {
         const Lin lf = qlin(m, "norm_out.linear");
@@ -576,7 +626,7 @@ edb200_status_t edb200_qwen_step(edb200_qwen_t* m, const float* latent, float ti
             EDB_TRY(mm_pair(i2.w, hid + n_txt * M, n_img, M, &fi, t2.w, hid, n_txt, M, &ft, s));
         }
         if (m->tap) {
-            cudaMemcpyAsync(m->tap + (int64_t)i * m->t_loc * H, m->X, m->t_loc * H * 4, cudaMemcpyDeviceToDevice, s);
+            cudaMemcpyAsync(m->tap + (int64_t)i * m->t_rows * H, m->X, m->t_rows * H * 4, cudaMemcpyDeviceToDevice, s);
         }
     }
 
@@ -590,12 +640,17 @@ edb200_status_t edb200_qwen_step(edb200_qwen_t* m, const float* latent, float ti
     if (sp) {
         std::vector<int64_t> first(m->world), count(m->world);
         for (int r = 0; r < m->world; ++r) {
-            int64_t tl = 0, tx = 0, f = 0;
-            EDB_TRY(edb200_sp_shard(T, m->n_txt, r, m->world, &tl, &tx, &f));
+            int64_t tx = 0, f = 0, rows = 0;
+            EDB_TRY(edb200_sp_shard(T, m->n_txt, r, m->world, nullptr, &tx, &f, &rows));
             first[r] = f;
-            count[r] = tl - tx;
+            count[r] = rows - tx;
         }
-        EDB_TRY(edb200_sp_all_gather_rows(m->comm, m->TOK_LOC, m->TOK_OUT, first.data(), count.data(), pf_out * 4, s));
+        if (m->p2p) {
+            // peer stores + barrier: nothing of the step goes through a library exchange
+            EDB_TRY(edb200_sp_all_gather_rows_peer(m->comm, m->TOK_LOC, m->TOK_OUT, first.data(), count.data(), pf_out * 4, s));
+        } else {
+            EDB_TRY(edb200_sp_all_gather_rows(m->comm, m->TOK_LOC, m->TOK_OUT, first.data(), count.data(), pf_out * 4, s));
+        }
     }
     launch_unpatchify(m->TOK_OUT, out, c.out_channels, m->lat_h, m->lat_w, p, s);
     return check_cuda(cudaGetLastError(), "qwen_step");

@@ -25,10 +25,10 @@ constexpr int kKBlock = 64;
 // x [HN, L, D] f16 -> mean [HN, D]; thread per (hn, d), sequential over tokens.
 template <int D>
 __global__ void __launch_bounds__(D)
-channel_mean_kernel(const __half* __restrict__ x, float* __restrict__ mean, int L) {
+channel_mean_kernel(const __half* __restrict__ x, float* __restrict__ mean, int L, int64_t head_rows) {
     const int hn = blockIdx.x;
     const int d = threadIdx.x;
-    const __half* p = x + (int64_t)hn * L * D + d;
+    const __half* p = x + (int64_t)hn * head_rows * D + d;
     float sum = 0.0f;
     int t = 0;
     for (; t + 8 <= L; t += 8) {
@@ -53,13 +53,13 @@ constexpr int kMeanChunk = 128;
 template <int D>
 __global__ void __launch_bounds__(D)
 channel_partial_kernel(const __half* __restrict__ q, const __half* __restrict__ k, float* __restrict__ part_q,
-                       float* __restrict__ part_k, int L, int n_chunks) {
+                       float* __restrict__ part_k, int L, int n_chunks, int64_t head_rows) {
     const int hn = blockIdx.x, chunk = blockIdx.y, d = threadIdx.x;
     const __half* x = blockIdx.z == 0 ? k : q;
     float* part = blockIdx.z == 0 ? part_k : part_q;
     const int t0 = chunk * kMeanChunk;
     const int t1 = min(L, t0 + kMeanChunk);
-    const __half* p = x + (int64_t)hn * L * D + d;
+    const __half* p = x + (int64_t)hn * head_rows * D + d;
     float s[4] = {0.f, 0.f, 0.f, 0.f};
     int t = t0;
     for (; t + 16 <= t1; t += 16) {
@@ -91,12 +91,12 @@ channel_finalize_kernel(const float* __restrict__ part_q, const float* __restric
 template <int D, int BLK>
 __global__ void __launch_bounds__(128)
 quant_block_kernel(const __half* __restrict__ x, const float* __restrict__ mean, int8_t* __restrict__ x8,
-                   float* __restrict__ scale, int L, int scale_stride) {
+                   float* __restrict__ scale, int L, int scale_stride, int64_t head_rows) {
     __shared__ float sh[4];
     __shared__ float s_inv;
     const int blk = blockIdx.x, hn = blockIdx.y, tid = threadIdx.x;
     const int tok0 = blk * BLK;
-    const __half* xp = x + (int64_t)hn * L * D;
+    const __half* xp = x + (int64_t)hn * head_rows * D;
     const float* mrow = mean ? mean + hn * D : nullptr;
     constexpr int VPT = BLK * D / 8 / 128;   // 8-channel vectors per thread
     float vals[VPT][8];
@@ -167,14 +167,14 @@ quant_block_kernel(const __half* __restrict__ x, const float* __restrict__ mean,
 template <int D>
 __global__ void __launch_bounds__(256)
 smooth_q_bias_kernel(const __half* __restrict__ k, const float* __restrict__ qm, float* __restrict__ bias, int L,
-                     int HN, int bias_stride) {
+                     int HN, int bias_stride, int64_t head_rows) {
     __shared__ float q_sh[D];
     const int hn = blockIdx.y;
     for (int i = threadIdx.x; i < D; i += blockDim.x) q_sh[i] = qm[hn * D + i];
     __syncthreads();
     const int tok = blockIdx.x * blockDim.x + threadIdx.x;
     if (tok >= L) return;
-    const uint4* kp = reinterpret_cast<const uint4*>(k + ((int64_t)hn * L + tok) * D);
+    const uint4* kp = reinterpret_cast<const uint4*>(k + ((int64_t)hn * head_rows + tok) * D);
     float total = 0.0f;
 #pragma unroll
     for (int w = 0; w < D / 32; ++w) {
@@ -198,6 +198,163 @@ smooth_q_bias_kernel(const __half* __restrict__ k, const float* __restrict__ qm,
         total = __fadd_rn(total, p[0]);
     }
     bias[(int64_t)hn * bias_stride + tok] = total;
+}
+
+// Fast pre-pass, one launch for everything after the channel means: CTA (128 threads) per
+// (64-token block, head) quantises the K block (one scale) and the two 32-token Q tiles of the same
+// rows (one scale each) with the arithmetic of quant_block_kernel, and, with smooth-Q, produces the
+// bias of its 64 keys from the K values it already holds.  The bias sum runs in a fixed order of its
+// own (not the reference kernel's): per thread the 8 products of its channels as
+// ((p0+p1)+(p2+p3))+((p4+p5)+(p6+p7)), then a pairwise tree over the D/8 threads of the token
+// (xor-shuffles 1, 2, 4[, 8]).  Rows between l and the padded end of a bias row are set to zero.
+template <int D>
+__global__ void __launch_bounds__(128)
+fused_quant_kernel(const __half* __restrict__ q, const __half* __restrict__ k, const float* __restrict__ qm,
+                   const float* __restrict__ km, int8_t* __restrict__ q8, int8_t* __restrict__ k8,
+                   float* __restrict__ q_scale, float* __restrict__ k_scale, float* __restrict__ bias, int L,
+                   int q_scale_stride, int k_scale_stride, int bias_stride, int64_t head_rows) {
+    __shared__ float sh[8];
+    __shared__ float s_inv[2];
+    constexpr int TPT = D / 8;                 // threads per token
+    constexpr int VK = 64 * D / 8 / 128;       // 8-channel vectors per thread for 64 tokens
+    const int blk = blockIdx.x, hn = blockIdx.y, tid = threadIdx.x;
+    const int tok0 = blk * 64;
+    const int d0 = (tid % TPT) * 8;
+    const __half* kp = k + (int64_t)hn * head_rows * D;
+    const __half* qp = q + (int64_t)hn * head_rows * D;
+    float km8[8], qm8[8];
+    {
+        const float4 a = __ldg(reinterpret_cast<const float4*>(km + hn * D + d0));
+        const float4 b = __ldg(reinterpret_cast<const float4*>(km + hn * D + d0 + 4));
+        km8[0] = a.x, km8[1] = a.y, km8[2] = a.z, km8[3] = a.w, km8[4] = b.x, km8[5] = b.y, km8[6] = b.z, km8[7] = b.w;
+    }
+    const bool smooth = qm != nullptr;
+    if (smooth) {
+        const float4 a = __ldg(reinterpret_cast<const float4*>(qm + hn * D + d0));
+        const float4 b = __ldg(reinterpret_cast<const float4*>(qm + hn * D + d0 + 4));
+        qm8[0] = a.x, qm8[1] = a.y, qm8[2] = a.z, qm8[3] = a.w, qm8[4] = b.x, qm8[5] = b.y, qm8[6] = b.z, qm8[7] = b.w;
+    } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) qm8[e] = 0.0f;
+    }
+    float vals[VK][8];
+    // ---- K block: subtract the mean, exact maximum, bias from the unsmoothed values
+    float amax = 1e-7f;
+#pragma unroll
+    for (int i = 0; i < VK; ++i) {
+        const int t = (tid + i * 128) / TPT;
+        const bool live = tok0 + t < L;
+        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+        if (live) raw = *reinterpret_cast<const uint4*>(kp + (int64_t)(tok0 + t) * D + d0);
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+        float p[8];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[e]));
+            p[2 * e] = __fmul_rn(f.x, qm8[2 * e]);
+            p[2 * e + 1] = __fmul_rn(f.y, qm8[2 * e + 1]);
+            float v0 = __fsub_rn(f.x, km8[2 * e]), v1 = __fsub_rn(f.y, km8[2 * e + 1]);
+            if (!live) v0 = v1 = 0.0f;
+            vals[i][2 * e] = v0;
+            vals[i][2 * e + 1] = v1;
+            amax = fmaxf(amax, fmaxf(fabsf(v0), fabsf(v1)));
+        }
+        if (smooth) {
+            float b = __fadd_rn(__fadd_rn(__fadd_rn(p[0], p[1]), __fadd_rn(p[2], p[3])),
+                                __fadd_rn(__fadd_rn(p[4], p[5]), __fadd_rn(p[6], p[7])));
+#pragma unroll
+            for (int m = 1; m < TPT; m <<= 1) b = __fadd_rn(b, __shfl_xor_sync(0xffffffffu, b, m));
+            if (tid % TPT == 0) bias[(int64_t)hn * bias_stride + tok0 + t] = live ? b : 0.0f;
+        }
+    }
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
+    if ((tid & 31) == 0) sh[tid >> 5] = amax;
+    __syncthreads();
+    if (tid == 0) {
+        const float a = fmaxf(fmaxf(sh[0], sh[1]), fmaxf(sh[2], sh[3]));
+        const float sc = __fdiv_rn(a, 127.0f);
+        k_scale[(int64_t)hn * k_scale_stride + blk] = sc;
+        s_inv[0] = __fdiv_rn(1.0f, sc);
+    }
+    __syncthreads();
+    {
+        const float inv = s_inv[0];
+        int8_t* op = k8 + (int64_t)hn * L * D;
+#pragma unroll
+        for (int i = 0; i < VK; ++i) {
+            const int t = (tid + i * 128) / TPT;
+            if (tok0 + t < L) {
+                uint32_t packed[2] = {0u, 0u};
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    float v = __fmul_rn(vals[i][e], inv);
+                    v = fmaxf(fminf(v, 127.0f), -127.0f);
+                    packed[e >> 2] |= (static_cast<uint32_t>(__float2int_rn(v)) & 0xffu) << (8 * (e & 3));
+                }
+                *reinterpret_cast<uint2*>(op + (int64_t)(tok0 + t) * D + d0) = make_uint2(packed[0], packed[1]);
+            }
+        }
+    }
+    // ---- Q: the same 64 rows as two 32-token tiles; vectors i < VK/2 belong to tile 0, the rest to tile 1
+    float am[2] = {1e-7f, 1e-7f};
+#pragma unroll
+    for (int i = 0; i < VK; ++i) {
+        const int t = (tid + i * 128) / TPT;
+        const bool live = tok0 + t < L;
+        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+        if (live) raw = *reinterpret_cast<const uint4*>(qp + (int64_t)(tok0 + t) * D + d0);
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[e]));
+            float v0 = f.x, v1 = f.y;
+            if (smooth) {
+                v0 = __fsub_rn(v0, qm8[2 * e]);
+                v1 = __fsub_rn(v1, qm8[2 * e + 1]);
+            }
+            if (!live) v0 = v1 = 0.0f;
+            vals[i][2 * e] = v0;
+            vals[i][2 * e + 1] = v1;
+            am[i / (VK / 2)] = fmaxf(am[i / (VK / 2)], fmaxf(fabsf(v0), fabsf(v1)));
+        }
+    }
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) {
+        am[0] = fmaxf(am[0], __shfl_xor_sync(0xffffffffu, am[0], m));
+        am[1] = fmaxf(am[1], __shfl_xor_sync(0xffffffffu, am[1], m));
+    }
+    __syncthreads();   // sh and s_inv of the K part are no longer read
+    if ((tid & 31) == 0) {
+        sh[tid >> 5] = am[0];
+        sh[4 + (tid >> 5)] = am[1];
+    }
+    __syncthreads();
+    if (tid < 2) {
+        const float a = fmaxf(fmaxf(sh[4 * tid], sh[4 * tid + 1]), fmaxf(sh[4 * tid + 2], sh[4 * tid + 3]));
+        const float sc = __fdiv_rn(a, 127.0f);
+        q_scale[(int64_t)hn * q_scale_stride + 2 * blk + tid] = sc;
+        s_inv[tid] = __fdiv_rn(1.0f, sc);
+    }
+    __syncthreads();
+    {
+        int8_t* op = q8 + (int64_t)hn * L * D;
+#pragma unroll
+        for (int i = 0; i < VK; ++i) {
+            const int t = (tid + i * 128) / TPT;
+            const float inv = s_inv[i / (VK / 2)];
+            if (tok0 + t < L) {
+                uint32_t packed[2] = {0u, 0u};
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    float v = __fmul_rn(vals[i][e], inv);
+                    v = fmaxf(fminf(v, 127.0f), -127.0f);
+                    packed[e >> 2] |= (static_cast<uint32_t>(__float2int_rn(v)) & 0xffu) << (8 * (e & 3));
+                }
+                *reinterpret_cast<uint2*>(op + (int64_t)(tok0 + t) * D + d0) = make_uint2(packed[0], packed[1]);
+            }
+        }
+    }
 }
 
 struct Layout {
@@ -237,39 +394,50 @@ static Layout make_layout(int hn, int64_t l, int d) {
 }
 
 template <int D>
-static edb200_status_t quantize(const __half* q, const __half* k, int hn, int l, bool smooth_q, bool fast_means,
-                                char* scratch, const Layout& lo, cudaStream_t s) {
+static edb200_status_t quantize(const __half* q, const __half* k, int hn, int l, int64_t head_rows, bool smooth_q,
+                                bool fast_means, char* scratch, const Layout& lo, cudaStream_t s) {
     float* qm = reinterpret_cast<float*>(scratch + lo.qm);
     float* km = reinterpret_cast<float*>(scratch + lo.km);
-    // algorithmic traffic: read q,k (f16) for the means, again for the quantisers, k once more for the bias; write int8
-    ProfScope prof(s, PROF_ELEMENTWISE, 0.0, (double)hn * l * D * (smooth_q ? 13.0 : 8.0));
+    // algorithmic traffic: read q,k (f16) for the means, again for the quantisers (the bit-compatible path reads k
+    // once more for the bias); write int8
+    ProfScope prof(s, PROF_ELEMENTWISE, 0.0, (double)hn * l * D * (fast_means ? 10.0 : (smooth_q ? 13.0 : 8.0)));
     int launches = 0;
     if (fast_means) {
         float* pq = reinterpret_cast<float*>(scratch + lo.part_q);
         float* pk = reinterpret_cast<float*>(scratch + lo.part_k);
         const int nc = (l + kMeanChunk - 1) / kMeanChunk;
-        channel_partial_kernel<D><<<dim3(hn, nc, smooth_q ? 2 : 1), D, 0, s>>>(q, k, pq, pk, l, nc);
+        channel_partial_kernel<D><<<dim3(hn, nc, smooth_q ? 2 : 1), D, 0, s>>>(q, k, pq, pk, l, nc, head_rows);
         channel_finalize_kernel<D><<<dim3(hn, smooth_q ? 2 : 1), D, 0, s>>>(pq, pk, qm, km, l, nc);
         launches += 2;
     } else {
-        channel_mean_kernel<D><<<hn, D, 0, s>>>(k, km, l);
-        if (smooth_q) channel_mean_kernel<D><<<hn, D, 0, s>>>(q, qm, l);
+        channel_mean_kernel<D><<<hn, D, 0, s>>>(k, km, l, head_rows);
+        if (smooth_q) channel_mean_kernel<D><<<hn, D, 0, s>>>(q, qm, l, head_rows);
         launches += 1 + (smooth_q ? 1 : 0);
     }
     const int lpad = (l + 127) / 128 * 128;
-    quant_block_kernel<D, kQTile><<<dim3(lpad / kQTile, hn), 128, 0, s>>>(
-        q, smooth_q ? qm : nullptr, reinterpret_cast<int8_t*>(scratch + lo.q8),
-        reinterpret_cast<float*>(scratch + lo.q_scale), l, lo.q_scale_stride);
-    quant_block_kernel<D, kKBlock><<<dim3(lpad / kKBlock, hn), 128, 0, s>>>(
-        k, km, reinterpret_cast<int8_t*>(scratch + lo.k8), reinterpret_cast<float*>(scratch + lo.k_scale), l,
-        lo.k_scale_stride);
-    launches += 2;
-    if (smooth_q) {
-        // the padded tail of each bias row is read by the attention kernel: keep it finite
-        cudaMemsetAsync(scratch + lo.bias, 0, (size_t)hn * lo.bias_stride * 4, s);
-        smooth_q_bias_kernel<D><<<dim3((l + 255) / 256, hn), 256, 0, s>>>(
-            k, qm, reinterpret_cast<float*>(scratch + lo.bias), l, hn, lo.bias_stride);
+    if (fast_means) {
+        // the fast pre-pass: everything after the means in one launch (K and Q read once more, no memset)
+        fused_quant_kernel<D><<<dim3(lpad / kKBlock, hn), 128, 0, s>>>(
+            q, k, smooth_q ? qm : nullptr, km, reinterpret_cast<int8_t*>(scratch + lo.q8),
+            reinterpret_cast<int8_t*>(scratch + lo.k8), reinterpret_cast<float*>(scratch + lo.q_scale),
+            reinterpret_cast<float*>(scratch + lo.k_scale), reinterpret_cast<float*>(scratch + lo.bias), l,
+            lo.q_scale_stride, lo.k_scale_stride, lo.bias_stride, head_rows);
         ++launches;
+    } else {
+        quant_block_kernel<D, kQTile><<<dim3(lpad / kQTile, hn), 128, 0, s>>>(
+            q, smooth_q ? qm : nullptr, reinterpret_cast<int8_t*>(scratch + lo.q8),
+            reinterpret_cast<float*>(scratch + lo.q_scale), l, lo.q_scale_stride, head_rows);
+        quant_block_kernel<D, kKBlock><<<dim3(lpad / kKBlock, hn), 128, 0, s>>>(
+            k, km, reinterpret_cast<int8_t*>(scratch + lo.k8), reinterpret_cast<float*>(scratch + lo.k_scale), l,
+            lo.k_scale_stride, head_rows);
+        launches += 2;
+        if (smooth_q) {
+            // the padded tail of each bias row is read by the attention kernel: keep it finite
+            cudaMemsetAsync(scratch + lo.bias, 0, (size_t)hn * lo.bias_stride * 4, s);
+            smooth_q_bias_kernel<D><<<dim3((l + 255) / 256, hn), 256, 0, s>>>(
+                k, qm, reinterpret_cast<float*>(scratch + lo.bias), l, hn, lo.bias_stride, head_rows);
+            ++launches;
+        }
     }
     count_launch(launches);
     return check_cuda(cudaGetLastError(), "sage quantize launch");
@@ -306,7 +474,7 @@ template <int D>
 static edb200_status_t key_means_static(const __half* k, int hn, int l, float* part, float* mean_out, cudaStream_t s) {
     const int nc = (l + kMeanChunk - 1) / kMeanChunk;
     ProfScope prof(s, PROF_ELEMENTWISE, 0.0, (double)hn * l * D * 2.0);
-    channel_partial_kernel<D><<<dim3(hn, nc, 1), D, 0, s>>>(nullptr, k, nullptr, part, l, nc);
+    channel_partial_kernel<D><<<dim3(hn, nc, 1), D, 0, s>>>(nullptr, k, nullptr, part, l, nc, l);
     channel_finalize_kernel<D><<<dim3(hn, 1), D, 0, s>>>(nullptr, part, nullptr, mean_out, l, nc);
     count_launch(2);
     return check_cuda(cudaGetLastError(), "sage key means launch");
@@ -346,7 +514,13 @@ edb200_status_t edb200_sage_scratch_layout(int hn, int64_t l, int d_head, int64_
 
 edb200_status_t edb200_sage_quantize_qk(const void* q_f16, const void* k_f16, int hn, int64_t l, int d_head,
                                         int smooth_q, void* scratch, int64_t scratch_bytes, void* stream) {
-    if (q_f16 == nullptr || k_f16 == nullptr || scratch == nullptr || hn <= 0 || l <= 0) {
+    return edb200_sage_quantize_qk_strided(q_f16, k_f16, hn, l, l, d_head, smooth_q, scratch, scratch_bytes, stream);
+}
+
+edb200_status_t edb200_sage_quantize_qk_strided(const void* q_f16, const void* k_f16, int hn, int64_t l,
+                                                int64_t head_rows, int d_head, int smooth_q, void* scratch,
+                                                int64_t scratch_bytes, void* stream) {
+    if (q_f16 == nullptr || k_f16 == nullptr || scratch == nullptr || hn <= 0 || l <= 0 || head_rows < l) {
         return fail(EDB200_ERR_INVALID, "sage_quantize_qk: null or empty argument");
     }
     if (d_head != 64 && d_head != 128) return fail(EDB200_ERR_UNSUPPORTED, "sage_quantize_qk: d_head must be 64 or 128");
@@ -358,38 +532,47 @@ edb200_status_t edb200_sage_quantize_qk(const void* q_f16, const void* k_f16, in
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (d_head == 128) {
         return sage::quantize<128>(static_cast<const __half*>(q_f16), static_cast<const __half*>(k_f16), hn,
-                                   static_cast<int>(l), (smooth_q & 1) != 0, (smooth_q & 2) != 0,
+                                   static_cast<int>(l), head_rows, (smooth_q & 1) != 0, (smooth_q & 2) != 0,
                                    static_cast<char*>(scratch), lo, s);
     }
     return sage::quantize<64>(static_cast<const __half*>(q_f16), static_cast<const __half*>(k_f16), hn,
-                              static_cast<int>(l), (smooth_q & 1) != 0, (smooth_q & 2) != 0,
+                              static_cast<int>(l), head_rows, (smooth_q & 1) != 0, (smooth_q & 2) != 0,
                               static_cast<char*>(scratch), lo, s);
 }
 
 edb200_status_t edb200_sage_attention(const void* q_f16, const void* k_f16, const void* v_f16, int hn, int64_t l,
                                       int d_head, float scale, int smooth_q, void* scratch, int64_t scratch_bytes,
                                       void* out, int out_dtype, int64_t ld_out, void* stream) {
-    return edb200_sage_attention_sp(q_f16, k_f16, v_f16, hn, l, d_head, scale, smooth_q, scratch, scratch_bytes, out,
-                                    out_dtype, ld_out, nullptr, stream);
+    return edb200_sage_attention_strided(q_f16, k_f16, v_f16, hn, l, l, d_head, scale, smooth_q, scratch, scratch_bytes,
+                                         out, out_dtype, ld_out, nullptr, stream);
 }
 
 edb200_status_t edb200_sage_attention_sp(const void* q_f16, const void* k_f16, const void* v_f16, int hn, int64_t l,
                                          int d_head, float scale, int smooth_q, void* scratch, int64_t scratch_bytes,
                                          void* out, int out_dtype, int64_t ld_out, const edb200_sp_peers_t* dst,
                                          void* stream) {
+    return edb200_sage_attention_strided(q_f16, k_f16, v_f16, hn, l, l, d_head, scale, smooth_q, scratch, scratch_bytes,
+                                         out, out_dtype, ld_out, dst, stream);
+}
+
+edb200_status_t edb200_sage_attention_strided(const void* q_f16, const void* k_f16, const void* v_f16, int hn, int64_t l,
+                                              int64_t head_rows, int d_head, float scale, int smooth_q, void* scratch,
+                                              int64_t scratch_bytes, void* out, int out_dtype, int64_t ld_out,
+                                              const edb200_sp_peers_t* dst, void* stream) {
     if (v_f16 == nullptr || (out == nullptr && dst == nullptr)) {
         return fail(EDB200_ERR_INVALID, "sage_attention: null argument");
     }
-    if (d_head != 128) return fail(EDB200_ERR_UNSUPPORTED, "sage_attention: d_head must be 128");
-    edb200_status_t st = edb200_sage_quantize_qk(q_f16, k_f16, hn, l, d_head, smooth_q, scratch, scratch_bytes, stream);
+    if (d_head != 128 && d_head != 64) return fail(EDB200_ERR_UNSUPPORTED, "sage_attention: d_head must be 64 or 128");
+    edb200_status_t st = edb200_sage_quantize_qk_strided(q_f16, k_f16, hn, l, head_rows, d_head, smooth_q, scratch,
+                                                         scratch_bytes, stream);
     if (st != EDB200_OK) return st;
     const sage::Layout lo = sage::make_layout(hn, l, d_head);
     char* sc = static_cast<char*>(scratch);
-    return edb200_attention_sage_int8_sp(sc + lo.q8, sc + lo.k8, v_f16, reinterpret_cast<const float*>(sc + lo.q_scale),
-                                         lo.q_scale_stride, reinterpret_cast<const float*>(sc + lo.k_scale),
-                                         lo.k_scale_stride,
-                                         (smooth_q & 1) ? reinterpret_cast<const float*>(sc + lo.bias) : nullptr,
-                                         lo.bias_stride, hn, l, d_head, scale, out, out_dtype, ld_out, dst, stream);
+    return edb200_attention_sage_int8_strided(
+        sc + lo.q8, sc + lo.k8, v_f16, head_rows, reinterpret_cast<const float*>(sc + lo.q_scale), lo.q_scale_stride,
+        reinterpret_cast<const float*>(sc + lo.k_scale), lo.k_scale_stride,
+        (smooth_q & 1) ? reinterpret_cast<const float*>(sc + lo.bias) : nullptr, lo.bias_stride, hn, l, d_head, scale, out,
+        out_dtype, ld_out, dst, stream);
 }
 
 edb200_status_t edb200_sage_key_means_static(const void* k_f16, int hn, int64_t l, int d_head, float* mean_out,

@@ -21,6 +21,7 @@
 #include <cuda_fp16.h>
 
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <vector>
 
@@ -35,9 +36,24 @@ struct edb200_sd3 {
     void *XMOD = nullptr, *QKV = nullptr, *Q = nullptr, *K = nullptr, *V = nullptr, *ATT = nullptr, *HID = nullptr;
     float *MODS = nullptr, *CVEC = nullptr, *TMP = nullptr, *TEMB = nullptr, *FREQ = nullptr, *TOK_IN = nullptr,
           *TOK_OUT = nullptr, *LAT_IN = nullptr, *LAT_OUT = nullptr, *CTX_IN = nullptr, *Y_IN = nullptr;
+    void* SAGE = nullptr;
+    int64_t sage_bytes = 0;
     float* tap = nullptr;
     float* pinned = nullptr;
     int64_t pinned_bytes = 0;
+    // sequence-parallel execution (world > 1): this rank's slice [context rows ; image rows] of the
+    // [context ; image] sequence and the exchange buffers (see edb200_flux.cu for the scheme)
+    edb200_comm_t* comm = nullptr;
+    int rank = 0, world = 1;
+    int64_t t_loc = 0, t_rows = 0, ctx_l = 0, img_l = 0, img_first = 0;
+    bool p2p = false;
+    void *QL = nullptr, *KL = nullptr, *VL = nullptr, *AOUT = nullptr, *STG = nullptr;
+    float* TOK_LOC = nullptr;
+    edb200_sp_peers_t qkv_peers, att_peers;
+    // all adaLN projections of a pass (and the final layer's) as one weight-streaming launch
+    edb200_gemv_batch_t* mod_batch = nullptr;
+    uint64_t mod_batch_gen = 0;
+    edb200_sp_peers_t mods_peers;
 };
 
 namespace {
@@ -108,12 +124,13 @@ void register_params(edb200_sd3* m) {
     lin("final_layer.linear", (int64_t)c.patch_size * c.patch_size * c.out_channels, H, true);
 }
 
-// x[t, :] += pos_embed[(top + t / w_tok) * max + left + t % w_tok, :]  (cropped_pos_embed, mmdit.hpp:3263-3301)
+// x[t, :] += pos_embed[(top + t / w_tok) * max + left + t % w_tok, :]  (cropped_pos_embed, mmdit.hpp:3263-3301);
+// row 0 of x is image token t0.
 __global__ void add_pos_embed_kernel(float* __restrict__ x, const float* __restrict__ pos, int H, int w_tok, int max_size,
-                                     int top, int left, int64_t total) {
+                                     int top, int left, int64_t t0, int64_t total) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
-    const int64_t t = i / H;
+    const int64_t t = t0 + i / H;
     const int c = static_cast<int>(i % H);
     const int64_t row = (int64_t)(top + t / w_tok) * max_size + left + t % w_tok;
     x[i] += pos[row * H + c];
@@ -182,6 +199,94 @@ edb200_status_t ln_mod(const float* x, int64_t H, const float* shift, const floa
     return edb200_layernorm_modulate(x, H, shift, scale, nullptr, nullptr, rows, H, 1e-6f, y, y_dtype, H, s);
 }
 
+// Row-count-tolerant two-problem GEMM: under sequence parallelism a rank may own no context rows.
+edb200_status_t mm_pair(const edb200_qweight_t* w0, const void* x0, int64_t m0, int64_t ldx0, const edb200_epilogue_t* e0,
+                        const edb200_qweight_t* w1, const void* x1, int64_t m1, int64_t ldx1, const edb200_epilogue_t* e1,
+                        cudaStream_t s) {
+    if (m0 > 0 && m1 > 0) return edb200_mul_mat_q_pair(w0, x0, m0, ldx0, e0, w1, x1, m1, ldx1, e1, EDB200_TYPE_F16, s);
+    if (m0 > 0) return edb200_mul_mat_q(w0, x0, EDB200_TYPE_F16, m0, ldx0, e0, s);
+    if (m1 > 0) return edb200_mul_mat_q(w1, x1, EDB200_TYPE_F16, m1, ldx1, e1, s);
+    return EDB200_OK;
+}
+
+// Joint attention over [context ; image] into the local rows of ATT: single GPU, NCCL exchange, or
+// peer-memory exchange with flag barriers (MMDiT forward_sp, mmdit.hpp:3117-3128, 3439-3466).
+// INT8 scores (when configured) run on the middle layers only: sage_attn_skip_layer,
+// src/core/backend/ggml/ed_ggml_sage_attn_ext.hpp:146-159, layer index from mmdit.hpp:3349-3350.
+edb200_status_t joint_attention(edb200_sd3* m, int layer, int64_t T, cudaStream_t s) {
+    const edb200_sd3_config_t& c = m->cfg;
+    const int64_t H = c.hidden_size;
+    const int d = static_cast<int>(H / c.num_heads);
+    const int heads = c.num_heads / m->world;
+    const float scale = 1.0f / std::sqrt(static_cast<float>(d));
+    const int flags = (c.sage_smooth_q ? EDB200_SAGE_SMOOTH_Q : 0) | EDB200_SAGE_FAST_MEANS;
+    const bool sage = c.attention == EDB200_ATTN_SAGE_INT8 && layer >= c.sage_skip_first &&
+                      layer < c.depth - c.sage_skip_last;
+    const int64_t head_rows = m->world > 1 ? m->t_loc * m->world : T;
+    __half* att = static_cast<__half*>(m->ATT);
+    if (m->p2p) {
+        EDB_TRY(edb200_sp_barrier(m->comm, s));
+        if (sage) {
+            EDB_TRY(edb200_sage_attention_strided(m->Q, m->K, m->V, heads, T, head_rows, d, scale, flags, m->SAGE,
+                                                  m->sage_bytes, nullptr, EDB200_TYPE_F16, H, &m->att_peers, s));
+        } else {
+            EDB_TRY(edb200_attention_f16_strided(m->Q, m->K, m->V, heads, T, T, head_rows, head_rows, d, scale, nullptr,
+                                                 EDB200_TYPE_F16, H, &m->att_peers, s));
+        }
+        return edb200_sp_barrier(m->comm, s);
+    }
+    void* att_out = att;
+    int64_t att_ld = H;
+    if (m->world > 1) {
+        const void* send[3] = {m->QL, m->KL, m->VL};
+        void* recv[3] = {m->Q, m->K, m->V};
+        EDB_TRY(edb200_sp_all_to_all_heads(m->comm, send, recv, 3, c.num_heads, m->t_loc, (int64_t)d * 2, s));
+        att_out = m->AOUT;
+        att_ld = (int64_t)heads * d;
+    }
+    if (sage) {
+        EDB_TRY(edb200_sage_attention_strided(m->Q, m->K, m->V, heads, T, head_rows, d, scale, flags, m->SAGE,
+                                              m->sage_bytes, att_out, EDB200_TYPE_F16, att_ld, nullptr, s));
+    } else {
+        EDB_TRY(edb200_attention_f16_strided(m->Q, m->K, m->V, heads, T, T, head_rows, head_rows, d, scale, att_out,
+                                             EDB200_TYPE_F16, att_ld, nullptr, s));
+    }
+    if (m->world > 1) {
+        EDB_TRY(edb200_sp_all_to_all_tokens(m->comm, m->AOUT, m->STG, att, m->t_loc, (int64_t)heads * d * 2, H * 2, s));
+    }
+    return EDB200_OK;
+}
+
+// Every adaLN projection of the pass as one batch (block i: context 6H (2H on the pre_only side), x 6H; then
+// the final layer's 2H); built at the first pass after prepare or after a tensor was reloaded.
+edb200_status_t ensure_mod_batch(edb200_sd3* m, cudaStream_t s) {
+    if (m->mod_batch != nullptr && m->mod_batch_gen == m->params.generation()) return EDB200_OK;
+    const edb200_sd3_config_t& c = m->cfg;
+    const int64_t H = c.hidden_size;
+    edb200_gemv_batch_destroy(m->mod_batch);
+    m->mod_batch = nullptr;
+    std::vector<const edb200_qweight_t*> bw;
+    std::vector<const float*> bb;
+    std::vector<float*> by;
+    for (int i = 0; i < c.depth; ++i) {
+        const std::string pb = "joint_blocks." + std::to_string(i) + ".";
+        const Lin lc = qlin(m, pb + "context_block.adaLN_modulation.1"), lx = qlin(m, pb + "x_block.adaLN_modulation.1");
+        bw.push_back(lc.w), bb.push_back(lc.b), by.push_back(m->MODS + (int64_t)i * 12 * H);
+        bw.push_back(lx.w), bb.push_back(lx.b), by.push_back(m->MODS + ((int64_t)i * 12 + 6) * H);
+    }
+    const Lin lf = qlin(m, "final_layer.adaLN_modulation.1");
+    bw.push_back(lf.w), bb.push_back(lf.b), by.push_back(m->MODS + (int64_t)c.depth * 12 * H);
+    EDB_TRY(edb200_gemv_batch_create(bw.data(), bb.data(), by.data(), (int)bw.size(), s, &m->mod_batch));
+    m->mod_batch_gen = m->params.generation();
+    memset(&m->mods_peers, 0, sizeof(m->mods_peers));
+    if (m->p2p) {
+        m->mods_peers.world = m->world;
+        m->mods_peers.rank = m->rank;
+        for (int r = 0; r < m->world; ++r) m->mods_peers.buf[0][r] = edb200_comm_peer_ptr(m->comm, r, m->MODS);
+    }
+    return EDB200_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -229,9 +334,10 @@ edb200_status_t edb200_sd3_create(const edb200_sd3_config_t* cfg, edb200_sd3_t**
     if (c.hidden_size % 256 || c.mlp_hidden % 256 || c.hidden_size > 8192) {
         return fail(EDB200_ERR_UNSUPPORTED, "sd3_create: hidden_size (<= 8192) and mlp_hidden must be multiples of 256");
     }
-    if (c.attention != EDB200_ATTN_F16) {
-        return fail(EDB200_ERR_UNSUPPORTED, "sd3_create: this build runs MMDiT attention in f16 only");
+    if (c.attention != EDB200_ATTN_F16 && c.attention != EDB200_ATTN_SAGE_INT8) {
+        return fail(EDB200_ERR_INVALID, "sd3_create: attention must be EDB200_ATTN_F16 or EDB200_ATTN_SAGE_INT8");
     }
+    if (c.sage_skip_first < 0 || c.sage_skip_last < 0) return fail(EDB200_ERR_INVALID, "sd3_create: negative layer skip");
     const int pf = c.patch_size * c.patch_size * c.out_channels;
     if (c.patch_size <= 0 || pf % 32 || (c.patch_size * c.patch_size * c.in_channels) % 4 || c.adm_in_channels % 4 ||
         c.context_size % 4 || c.pos_embed_max_size <= 0) {
@@ -249,6 +355,7 @@ edb200_status_t edb200_sd3_create(const edb200_sd3_config_t* cfg, edb200_sd3_t**
 void edb200_sd3_destroy(edb200_sd3_t* m) {
     if (m == nullptr) return;
     if (m->pinned) cudaFreeHost(m->pinned);
+    edb200_gemv_batch_destroy(m->mod_batch);
     delete m;
 }
 
@@ -279,6 +386,12 @@ edb200_status_t edb200_sd3_set_tensor(edb200_sd3_t* m, const char* name, int ggm
     return m->params.set(name, ggml_type, data, nbytes, on_device != 0, static_cast<cudaStream_t>(stream));
 }
 
+edb200_status_t edb200_sd3_get_tensor_f32(const edb200_sd3_t* m, const char* name, float* out, int64_t n_floats,
+                                          int on_device, void* stream) {
+    if (m == nullptr || name == nullptr) return fail(EDB200_ERR_INVALID, "sd3_get_tensor_f32: null argument");
+    return m->params.fetch_f32(name, out, n_floats, on_device != 0, static_cast<cudaStream_t>(stream));
+}
+
 edb200_status_t edb200_sd3_load_gguf(edb200_sd3_t* m, const char* path, const char* strip_prefix, int* n_loaded,
                                     void* stream) {
     if (m == nullptr || path == nullptr) return fail(EDB200_ERR_INVALID, "sd3_load_gguf: null argument");
@@ -297,6 +410,17 @@ edb200_status_t edb200_sd3_init_random(edb200_sd3_t* m, uint64_t seed, float std
 }
 
 int64_t edb200_sd3_weight_bytes(const edb200_sd3_t* m) { return m ? m->params.device_bytes() : 0; }
+
+edb200_status_t edb200_sd3_set_comm(edb200_sd3_t* m, edb200_comm_t* comm) {
+    if (m == nullptr) return fail(EDB200_ERR_INVALID, "sd3_set_comm: null model");
+    if (m->comm != nullptr && m->comm != comm) edb200_comm_unmap_peers(m->comm);   // collective
+    m->comm = comm;
+    m->rank = comm ? edb200_comm_rank(comm) : 0;
+    m->world = comm ? edb200_comm_world(comm) : 1;
+    m->lat_h = m->lat_w = m->n_ctx = 0;   // the workspace must be prepared again
+    m->p2p = false;
+    return EDB200_OK;
+}
 
 edb200_status_t edb200_sd3_set_tap(edb200_sd3_t* m, float* tap) {
     if (m == nullptr) return fail(EDB200_ERR_INVALID, "sd3_set_tap: null model");
@@ -319,12 +443,28 @@ edb200_status_t edb200_sd3_prepare(edb200_sd3_t* m, int lat_h, int lat_w, int n_
     const int64_t pf_in = (int64_t)c.in_channels * p * p, pf_out = (int64_t)c.out_channels * p * p;
     const int64_t lat_in = (int64_t)c.in_channels * lat_h * lat_w, lat_out = (int64_t)c.out_channels * lat_h * lat_w;
     auto al = [](int64_t b) { return (b + 255) & ~int64_t(255); };
+    int64_t t_loc = T, t_rows = T, ctx_l = n_ctx, img_first = 0;
+    if (m->world > 1) {
+        if (c.num_heads % m->world) {
+            return fail(EDB200_ERR_UNSUPPORTED, "sd3_prepare: %d heads do not divide over %d ranks", c.num_heads, m->world);
+        }
+        EDB_TRY(edb200_sp_shard(T, n_ctx, m->rank, m->world, &t_loc, &ctx_l, &img_first, &t_rows));
+        if (t_rows == 0) return fail(EDB200_ERR_UNSUPPORTED, "sd3_prepare: %lld tokens leave rank %d without rows", (long long)T, m->rank);
+    }
+    const int64_t sage = c.attention == EDB200_ATTN_SAGE_INT8
+                             ? edb200_sage_scratch_bytes(c.num_heads / m->world, T, static_cast<int>(H / c.num_heads))
+                             : 0;
     int64_t total = al(T * H * 4) + al(T * H * 2) + al(T * 3 * H * 2) + 4 * al(T * H * 2) + al(T * M * 2);
     total += al((mods_per_block(c) * c.depth + 2 * H) * 4) + al(H * 4) + al(2 * H * 4) + al(256 * 4) + al(128 * 4);
     total += al(n_img * pf_in * 4) + al(n_img * pf_out * 4) + al(lat_in * 4) + al(lat_out * 4) +
-             al((int64_t)n_ctx * c.context_size * 4) + al(c.adm_in_channels * 4) + 8192;
+             al((int64_t)n_ctx * c.context_size * 4) + al(c.adm_in_channels * 4) + al(sage) + 8192;
+    if (m->world > 1) total += 5 * al(t_loc * H * 2) + al(n_img * pf_out * 4) + 2048;
     cudaStreamSynchronize(s);
+    if (m->comm != nullptr) EDB_TRY(edb200_comm_unmap_peers(m->comm));   // collective; the old workspace goes away
+    m->p2p = false;
     EDB_TRY(m->ws.reserve(total));
+    edb200_gemv_batch_destroy(m->mod_batch);   // it points into the old workspace: rebuilt at the next pass
+    m->mod_batch = nullptr;
     Workspace& w = m->ws;
     m->X = w.take_n<float>(T * H);
     m->XMOD = w.take(T * H * 2);
@@ -345,7 +485,49 @@ edb200_status_t edb200_sd3_prepare(edb200_sd3_t* m, int lat_h, int lat_w, int n_
     m->LAT_OUT = w.take_n<float>(lat_out);
     m->CTX_IN = w.take_n<float>((int64_t)n_ctx * c.context_size);
     m->Y_IN = w.take_n<float>(c.adm_in_channels);
-    if (m->Y_IN == nullptr) return fail(EDB200_ERR_NOMEM, "sd3_prepare: workspace accounting error");
+    m->SAGE = sage > 0 ? w.take(sage) : nullptr;
+    m->sage_bytes = sage;
+    if (m->Y_IN == nullptr || (sage > 0 && m->SAGE == nullptr)) {
+        return fail(EDB200_ERR_NOMEM, "sd3_prepare: workspace accounting error");
+    }
+    m->QL = m->KL = m->VL = m->AOUT = m->STG = nullptr;
+    m->TOK_LOC = nullptr;
+    if (m->world > 1) {
+        void* flags = w.take(1024);   // barrier flags + epoch
+        m->QL = w.take(t_loc * H * 2);
+        m->KL = w.take(t_loc * H * 2);
+        m->VL = w.take(t_loc * H * 2);
+        m->AOUT = w.take(t_loc * H * 2);
+        m->STG = w.take(t_loc * H * 2);
+        m->TOK_LOC = w.take_n<float>(n_img * pf_out);
+        if (flags == nullptr || m->TOK_LOC == nullptr) return fail(EDB200_ERR_NOMEM, "sd3_prepare: workspace accounting error");
+        const char* how = getenv("EDB200_SP_EXCHANGE");
+        const bool want_p2p = how == nullptr || strcmp(how, "nccl") != 0;
+        edb200_status_t st = want_p2p ? edb200_comm_map_peers(m->comm, w.base(), w.capacity(),
+                                                              static_cast<char*>(flags) - static_cast<char*>(w.base()), s)
+                                      : EDB200_ERR_UNSUPPORTED;
+        if (st == EDB200_OK) {
+            m->p2p = true;
+            memset(&m->qkv_peers, 0, sizeof(m->qkv_peers));
+            memset(&m->att_peers, 0, sizeof(m->att_peers));
+            m->qkv_peers.world = m->att_peers.world = m->world;
+            m->qkv_peers.rank = m->att_peers.rank = m->rank;
+            m->qkv_peers.t_loc = m->att_peers.t_loc = t_loc;
+            for (int r = 0; r < m->world; ++r) {
+                m->qkv_peers.buf[0][r] = edb200_comm_peer_ptr(m->comm, r, m->Q);
+                m->qkv_peers.buf[1][r] = edb200_comm_peer_ptr(m->comm, r, m->K);
+                m->qkv_peers.buf[2][r] = edb200_comm_peer_ptr(m->comm, r, m->V);
+                m->att_peers.buf[0][r] = edb200_comm_peer_ptr(m->comm, r, m->ATT);
+            }
+        } else if (st != EDB200_ERR_UNSUPPORTED) {
+            return st;
+        }
+    }
+    m->t_loc = t_loc;
+    m->t_rows = t_rows;
+    m->ctx_l = ctx_l;
+    m->img_l = t_rows - ctx_l;
+    m->img_first = img_first;
     std::vector<float> freq(128);
     for (int i = 0; i < 128; ++i) freq[i] = (float)std::exp(-std::log(10000) * i / 128);
     cudaError_t e = cudaMemcpyAsync(m->FREQ, freq.data(), 128 * 4, cudaMemcpyHostToDevice, s);
@@ -378,7 +560,13 @@ edb200_status_t edb200_sd3_step(edb200_sd3_t* m, const float* latent, float time
     const int64_t H = c.hidden_size, M = c.mlp_hidden;
     const int d = static_cast<int>(H / c.num_heads);
     const int p = c.patch_size;
-    const int64_t n_ctx = m->n_ctx, n_img = m->n_img, T = n_ctx + n_img;
+    const int64_t T = (int64_t)m->n_ctx + m->n_img;            // whole sequence (attention length)
+    const int64_t n_ctx = m->ctx_l, n_img = m->img_l;          // rows this rank owns
+    const int64_t TL = m->t_rows;
+    const bool sp = m->world > 1;
+    const int64_t ctx_first = sp ? (int64_t)m->rank * m->t_loc : 0;
+    // few output tiles per rank: let the long out-projection reductions be cut along k (unordered adds)
+    const int split_k = sp ? EDB200_SPLIT_K_UNORDERED : EDB200_SPLIT_K_NEVER;
     const int64_t pf_in = (int64_t)c.in_channels * p * p, pf_out = (int64_t)c.out_channels * p * p;
     const int F16 = EDB200_TYPE_F16;
     float* X_ctx = m->X;
@@ -390,13 +578,13 @@ edb200_status_t edb200_sd3_step(edb200_sd3_t* m, const float* latent, float time
 
     // ---- prelude (MMDiT::forward, mmdit.hpp:3409-3428)
     launch_patchify(latent, m->TOK_IN, c.in_channels, m->lat_h, m->lat_w, p, s);
-    EDB_TRY(dense(m, "x_embedder.proj", m->TOK_IN, n_img, pf_in, EDB200_ACT_NONE, X_img, H, s));
-    {
+    if (n_img > 0) {
+        EDB_TRY(dense(m, "x_embedder.proj", m->TOK_IN + m->img_first * pf_in, n_img, pf_in, EDB200_ACT_NONE, X_img, H, s));
         const int h_tok = m->lat_h / p, w_tok = m->lat_w / p;
         const int top = (c.pos_embed_max_size - h_tok) / 2, left = (c.pos_embed_max_size - w_tok) / 2;
         const int64_t total = n_img * H;
         add_pos_embed_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, s>>>(
-            X_img, fparam(m, "pos_embed"), static_cast<int>(H), w_tok, c.pos_embed_max_size, top, left, total);
+            X_img, fparam(m, "pos_embed"), static_cast<int>(H), w_tok, c.pos_embed_max_size, top, left, m->img_first, total);
         count_launch();
     }
     launch_timestep_embedding(m->FREQ, timestep, 1.0f, 128, m->TEMB, s);
@@ -405,24 +593,18 @@ edb200_status_t edb200_sd3_step(edb200_sd3_t* m, const float* latent, float time
     EDB_TRY(dense(m, "y_embedder.mlp.0", y, 1, c.adm_in_channels, EDB200_ACT_SILU, m->TMP, H, s));
     EDB_TRY(dense(m, "y_embedder.mlp.2", m->TMP, 1, H, EDB200_ACT_NONE, m->TMP + H, H, s));
     launch_add_inplace(m->CVEC, m->TMP + H, H, s);
-    EDB_TRY(dense(m, "context_embedder", context, n_ctx, c.context_size, EDB200_ACT_NONE, X_ctx, H, s));
+    if (n_ctx > 0) {
+        EDB_TRY(dense(m, "context_embedder", context + ctx_first * c.context_size, n_ctx, c.context_size, EDB200_ACT_NONE,
+                      X_ctx, H, s));
+    }
 
-    // ---- every adaLN vector of the pass: lin(silu(c)), weight streaming
+    // ---- every adaLN vector of the pass: lin(silu(c)), weight streaming, one launch for all of them
+    // (sequence-parallel ranks with peer memory each stream 1/N of the weights and store to all)
     float* mods = m->MODS;
-    for (int i = 0; i < c.depth; ++i) {
-        const std::string pb = "joint_blocks." + std::to_string(i) + ".";
-        const bool pre_only = i == c.depth - 1;
-        const Lin lc = qlin(m, pb + "context_block.adaLN_modulation.1");
-        const Lin lx = qlin(m, pb + "x_block.adaLN_modulation.1");
-        float* mc = mods + (int64_t)i * 12 * H;
-        EDB_TRY(edb200_gemv_q(lc.w, m->CVEC, 1, H, 1, lc.b, mc, (pre_only ? 2 : 6) * H, s));
-        EDB_TRY(edb200_gemv_q(lx.w, m->CVEC, 1, H, 1, lx.b, mc + 6 * H, 6 * H, s));
-    }
     float* fmods = mods + (int64_t)c.depth * 12 * H;
-    {
-        const Lin lf = qlin(m, "final_layer.adaLN_modulation.1");
-        EDB_TRY(edb200_gemv_q(lf.w, m->CVEC, 1, H, 1, lf.b, fmods, 2 * H, s));
-    }
+    EDB_TRY(ensure_mod_batch(m, s));
+    EDB_TRY(edb200_gemv_batch_run(m->mod_batch, m->CVEC, 1, m->p2p ? &m->mods_peers : nullptr, s));
+    if (m->p2p) EDB_TRY(edb200_sp_barrier(m->comm, s));
 
     // ---- joint blocks (block_mixing, mmdit.hpp:2685-2775)
     for (int i = 0; i < c.depth; ++i) {
@@ -439,21 +621,29 @@ edb200_status_t edb200_sd3_step(edb200_sd3_t* m, const float* latent, float time
             const Lin lx = qlin(m, px + "attn.qkv"), lc = qlin(m, pc + "attn.qkv");
             edb200_epilogue_t ex = make_ep(qkv + n_ctx * 3 * H, F16, 3 * H, lx.b);
             edb200_epilogue_t ec = make_ep(qkv, F16, 3 * H, lc.b);
-            EDB_TRY(edb200_mul_mat_q_pair(lx.w, xmod + n_ctx * H, n_img, H, &ex, lc.w, xmod, n_ctx, H, &ec, F16, s));
+            EDB_TRY(mm_pair(lx.w, xmod + n_ctx * H, n_img, H, &ex, lc.w, xmod, n_ctx, H, &ec, s));
         }
-        EDB_TRY(edb200_qk_norm_rope_pack(qkv, F16, 3 * H, 0, H, 2 * H, T, c.num_heads, d, nullptr, nullptr, 1e-6f, nullptr,
-                                         0, T, m->Q, m->K, m->V, F16, s));
-        EDB_TRY(edb200_attention_f16(m->Q, m->K, m->V, c.num_heads, T, T, d, 1.0f / std::sqrt((float)d), att, F16, H, s));
+        // head-major pack of the local rows (no norm, no RoPE); under the peer-memory exchange straight
+        // into the owning ranks' Q/K/V
+        if (m->p2p) {
+            EDB_TRY(edb200_qk_norm_rope_pack_sp(qkv, F16, 3 * H, 0, H, 2 * H, TL, c.num_heads, d, nullptr, nullptr, 1e-6f,
+                                                nullptr, 0, m->t_loc * m->world, &m->qkv_peers, F16, s));
+        } else {
+            EDB_TRY(edb200_qk_norm_rope_pack(qkv, F16, 3 * H, 0, H, 2 * H, TL, c.num_heads, d, nullptr, nullptr, 1e-6f,
+                                             nullptr, 0, sp ? m->t_loc : T, sp ? m->QL : m->Q, sp ? m->KL : m->K,
+                                             sp ? m->VL : m->V, F16, s));
+        }
+        EDB_TRY(joint_attention(m, i, T, s));
         {
             const Lin lx = qlin(m, px + "attn.proj");
             edb200_epilogue_t ex = make_ep(X_img, EDB200_TYPE_F32, H, lx.b);
-            ex.residual = X_img, ex.ld_res = H, ex.gate = mx + 2 * H;
+            ex.residual = X_img, ex.ld_res = H, ex.gate = mx + 2 * H, ex.split_k = split_k;
             if (!pre_only) {
                 const Lin lc = qlin(m, pc + "attn.proj");
                 edb200_epilogue_t ec = make_ep(X_ctx, EDB200_TYPE_F32, H, lc.b);
-                ec.residual = X_ctx, ec.ld_res = H, ec.gate = mc + 2 * H;
-                EDB_TRY(edb200_mul_mat_q_pair(lx.w, att + n_ctx * H, n_img, H, &ex, lc.w, att, n_ctx, H, &ec, F16, s));
-            } else {
+                ec.residual = X_ctx, ec.ld_res = H, ec.gate = mc + 2 * H, ec.split_k = split_k;
+                EDB_TRY(mm_pair(lx.w, att + n_ctx * H, n_img, H, &ex, lc.w, att, n_ctx, H, &ec, s));
+            } else if (n_img > 0) {
                 EDB_TRY(edb200_mul_mat_q(lx.w, att + n_ctx * H, F16, n_img, H, &ex, s));
             }
         }
@@ -464,29 +654,44 @@ edb200_status_t edb200_sd3_step(edb200_sd3_t* m, const float* latent, float time
             edb200_epilogue_t e1 = make_ep(hid + n_ctx * M, F16, M, l1.b);
             e1.act = EDB200_ACT_GELU_TANH;
             edb200_epilogue_t e2 = make_ep(X_img, EDB200_TYPE_F32, H, l2.b);
-            e2.residual = X_img, e2.ld_res = H, e2.gate = mx + 5 * H;
+            e2.residual = X_img, e2.ld_res = H, e2.gate = mx + 5 * H, e2.split_k = split_k;
             if (!pre_only) {
                 const Lin c1 = qlin(m, pc + "mlp.fc1"), c2 = qlin(m, pc + "mlp.fc2");
                 edb200_epilogue_t f1 = make_ep(hid, F16, M, c1.b);
                 f1.act = EDB200_ACT_GELU_TANH;
                 edb200_epilogue_t f2 = make_ep(X_ctx, EDB200_TYPE_F32, H, c2.b);
-                f2.residual = X_ctx, f2.ld_res = H, f2.gate = mc + 5 * H;
-                EDB_TRY(edb200_mul_mat_q_pair(l1.w, xmod + n_ctx * H, n_img, H, &e1, c1.w, xmod, n_ctx, H, &f1, F16, s));
-                EDB_TRY(edb200_mul_mat_q_pair(l2.w, hid + n_ctx * M, n_img, M, &e2, c2.w, hid, n_ctx, M, &f2, F16, s));
-            } else {
+                f2.residual = X_ctx, f2.ld_res = H, f2.gate = mc + 5 * H, f2.split_k = split_k;
+                EDB_TRY(mm_pair(l1.w, xmod + n_ctx * H, n_img, H, &e1, c1.w, xmod, n_ctx, H, &f1, s));
+                EDB_TRY(mm_pair(l2.w, hid + n_ctx * M, n_img, M, &e2, c2.w, hid, n_ctx, M, &f2, s));
+            } else if (n_img > 0) {
                 EDB_TRY(edb200_mul_mat_q(l1.w, xmod + n_ctx * H, F16, n_img, H, &e1, s));
                 EDB_TRY(edb200_mul_mat_q(l2.w, hid + n_ctx * M, F16, n_img, M, &e2, s));
             }
         }
-        if (m->tap) cudaMemcpyAsync(m->tap + (int64_t)i * T * H, m->X, T * H * 4, cudaMemcpyDeviceToDevice, s);
+        if (m->tap) cudaMemcpyAsync(m->tap + (int64_t)i * TL * H, m->X, TL * H * 4, cudaMemcpyDeviceToDevice, s);
     }
 
     // ---- final layer: (scale, shift) order (FinalLayer::forward, mmdit.hpp:3143-3160) + unpatchify
     EDB_TRY(ln_mod(X_img, H, fmods + H, fmods, n_img, xmod, F16, s));
-    {
+    if (n_img > 0) {
         const Lin lf = qlin(m, "final_layer.linear");
-        edb200_epilogue_t ep = make_ep(m->TOK_OUT, EDB200_TYPE_F32, pf_out, lf.b);
+        edb200_epilogue_t ep = make_ep(sp ? m->TOK_LOC : m->TOK_OUT, EDB200_TYPE_F32, pf_out, lf.b);
         EDB_TRY(edb200_mul_mat_q(lf.w, xmod, F16, n_img, H, &ep, s));
+    }
+    if (sp) {
+        std::vector<int64_t> first(m->world), count(m->world);
+        for (int r = 0; r < m->world; ++r) {
+            int64_t tx = 0, f = 0, rows = 0;
+            EDB_TRY(edb200_sp_shard(T, m->n_ctx, r, m->world, nullptr, &tx, &f, &rows));
+            first[r] = f;
+            count[r] = rows - tx;
+        }
+        if (m->p2p) {
+            // peer stores + barrier: nothing of the step goes through a library exchange
+            EDB_TRY(edb200_sp_all_gather_rows_peer(m->comm, m->TOK_LOC, m->TOK_OUT, first.data(), count.data(), pf_out * 4, s));
+        } else {
+            EDB_TRY(edb200_sp_all_gather_rows(m->comm, m->TOK_LOC, m->TOK_OUT, first.data(), count.data(), pf_out * 4, s));
+        }
     }
     {
         const int64_t total = (int64_t)c.out_channels * m->lat_h * m->lat_w;

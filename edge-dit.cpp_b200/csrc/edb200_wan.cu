@@ -21,6 +21,7 @@
 
 #include <cuda_fp16.h>
 
+#include <algorithm>
 #include <cmath>
 #include <cstdlib>
 #include <cstring>
@@ -48,7 +49,7 @@ struct edb200_wan {
     // sequence parallel
     edb200_comm_t* comm = nullptr;
     int rank = 0, world = 1;
-    int64_t t_loc = 0;
+    int64_t t_loc = 0, t_rows = 0;   // this rank's slot of the padded sequence and the rows it owns
     bool p2p = false;
     void *QL = nullptr, *KL = nullptr, *VL = nullptr, *AOUT = nullptr, *STG = nullptr;
     edb200_sp_peers_t qkv_peers, att_peers;
@@ -207,21 +208,26 @@ edb200_status_t ln_mod(const float* x, int64_t D, const float* shift, const floa
 namespace {
 
 // Self-attention over the whole clip (see edb200_flux.cu for the single-GPU / NCCL / peer-memory cases).
-edb200_status_t self_attention(edb200_wan* m, cudaStream_t s) {
+edb200_status_t self_attention(edb200_wan* m, int layer, cudaStream_t s) {
     const edb200_wan_config_t& c = m->cfg;
     const int d = c.dim / c.num_heads;
     const int heads = c.num_heads / m->world;
     const float scale = 1.0f / std::sqrt(static_cast<float>(d));
     const int flags = (c.sage_smooth_q ? EDB200_SAGE_SMOOTH_Q : 0) | EDB200_SAGE_FAST_MEANS;
-    const bool sage = c.attention == EDB200_ATTN_SAGE_INT8;
+    // INT8 scores only on the middle layers: the first sage_skip_first and the last sage_skip_last stay f16
+    // (sage_attn_skip_layer, reference src/core/backend/ggml/ed_ggml_sage_attn_ext.hpp:146-159; the layer
+    // index reaches it from WanAttentionBlock, wan.hpp:4673-4674)
+    const bool sage = c.attention == EDB200_ATTN_SAGE_INT8 && layer >= c.sage_skip_first &&
+                      layer < c.num_layers - c.sage_skip_last;
+    const int64_t head_rows = m->world > 1 ? m->t_loc * m->world : m->T;   // padded sequence under SP
     if (m->p2p) {
         EDB_TRY(edb200_sp_barrier(m->comm, s));
         if (sage) {
-            EDB_TRY(edb200_sage_attention_sp(m->Q, m->K, m->V, heads, m->T, d, scale, flags, m->SAGE, m->sage_bytes, nullptr,
-                                             EDB200_TYPE_F16, c.dim, &m->att_peers, s));
+            EDB_TRY(edb200_sage_attention_strided(m->Q, m->K, m->V, heads, m->T, head_rows, d, scale, flags, m->SAGE,
+                                                  m->sage_bytes, nullptr, EDB200_TYPE_F16, c.dim, &m->att_peers, s));
         } else {
-            EDB_TRY(edb200_attention_f16_sp(m->Q, m->K, m->V, heads, m->T, m->T, d, scale, nullptr, EDB200_TYPE_F16, c.dim,
-                                            &m->att_peers, s));
+            EDB_TRY(edb200_attention_f16_strided(m->Q, m->K, m->V, heads, m->T, m->T, head_rows, head_rows, d, scale,
+                                                 nullptr, EDB200_TYPE_F16, c.dim, &m->att_peers, s));
         }
         return edb200_sp_barrier(m->comm, s);
     }
@@ -235,10 +241,11 @@ edb200_status_t self_attention(edb200_wan* m, cudaStream_t s) {
         att_ld = (int64_t)heads * d;
     }
     if (sage) {
-        EDB_TRY(edb200_sage_attention(m->Q, m->K, m->V, heads, m->T, d, scale, flags, m->SAGE, m->sage_bytes, att_out,
-                                      EDB200_TYPE_F16, att_ld, s));
+        EDB_TRY(edb200_sage_attention_strided(m->Q, m->K, m->V, heads, m->T, head_rows, d, scale, flags, m->SAGE,
+                                              m->sage_bytes, att_out, EDB200_TYPE_F16, att_ld, nullptr, s));
     } else {
-        EDB_TRY(edb200_attention_f16(m->Q, m->K, m->V, heads, m->T, m->T, d, scale, att_out, EDB200_TYPE_F16, att_ld, s));
+        EDB_TRY(edb200_attention_f16_strided(m->Q, m->K, m->V, heads, m->T, m->T, head_rows, head_rows, d, scale, att_out,
+                                             EDB200_TYPE_F16, att_ld, nullptr, s));
     }
     if (m->world > 1) {
         EDB_TRY(edb200_sp_all_to_all_tokens(m->comm, m->AOUT, m->STG, m->ATT, m->t_loc, (int64_t)heads * d * 2,
@@ -319,6 +326,12 @@ edb200_status_t edb200_wan_set_tensor(edb200_wan_t* m, const char* name, int ggm
     return m->params.set(name, ggml_type, data, nbytes, on_device != 0, static_cast<cudaStream_t>(stream));
 }
 
+edb200_status_t edb200_wan_get_tensor_f32(const edb200_wan_t* m, const char* name, float* out, int64_t n_floats,
+                                          int on_device, void* stream) {
+    if (m == nullptr || name == nullptr) return fail(EDB200_ERR_INVALID, "wan_get_tensor_f32: null argument");
+    return m->params.fetch_f32(name, out, n_floats, on_device != 0, static_cast<cudaStream_t>(stream));
+}
+
 edb200_status_t edb200_wan_load_gguf(edb200_wan_t* m, const char* path, const char* strip_prefix, int* n_loaded,
                                     void* stream) {
     if (m == nullptr || path == nullptr) return fail(EDB200_ERR_INVALID, "wan_load_gguf: null argument");
@@ -369,12 +382,13 @@ edb200_status_t edb200_wan_prepare(edb200_wan_t* m, int frames, int lat_h, int l
     const int t_len = frames / pt, h_len = lat_h / ph, w_len = lat_w / pw;
     const int64_t T = (int64_t)t_len * h_len * w_len;
     const int64_t pf_in = (int64_t)c.in_dim * pt * ph * pw, pf_out = (int64_t)c.out_dim * pt * ph * pw;
-    int64_t TL = T;
+    int64_t TL = T, t_rows = T;   // TL: rows of a rank's slot (buffers are laid out for it), t_rows: rows owned
     if (m->world > 1) {
         if (c.num_heads % m->world) {
             return fail(EDB200_ERR_UNSUPPORTED, "wan_prepare: %d heads do not divide over %d ranks", c.num_heads, m->world);
         }
-        EDB_TRY(edb200_sp_shard(T, 0, m->rank, m->world, &TL, nullptr, nullptr));
+        EDB_TRY(edb200_sp_shard(T, 0, m->rank, m->world, &TL, nullptr, nullptr, &t_rows));
+        if (t_rows == 0) return fail(EDB200_ERR_UNSUPPORTED, "wan_prepare: %lld tokens leave rank %d without rows", (long long)T, m->rank);
     }
     const int64_t sage =
         c.attention == EDB200_ATTN_SAGE_INT8 ? edb200_sage_scratch_bytes(c.num_heads / m->world, T, (int)d) : 0;
@@ -386,7 +400,7 @@ edb200_status_t edb200_wan_prepare(edb200_wan_t* m, int frames, int lat_h, int l
     total += al(6 * D * 4) * 2 + al(D * 4) * 2 + al(2 * D * 4) * 2 + al(256 * 4) + al(128 * 4) + al(pe_elems * 4);
     total += al((2 * TL + n_ctx) * 4) + al(T * pf_in * 4) + 2 * al(T * pf_out * 4) + al(lat_in * 4) + al(lat_out * 4);
     total += al((int64_t)n_ctx * c.text_dim * 4) + al(sage) + 8192;
-    if (m->world > 1) total += 6 * al(TL * D * 2) + 1024;
+    if (m->world > 1) total += 6 * al(TL * D * 2) + 2048;
     cudaStreamSynchronize(s);
     if (m->comm != nullptr) EDB_TRY(edb200_comm_unmap_peers(m->comm));   // collective; the old workspace goes away
     m->p2p = false;
@@ -434,7 +448,7 @@ edb200_status_t edb200_wan_prepare(edb200_wan_t* m, int frames, int lat_h, int l
     m->QX = w.take(TL * D * 2);
     if (m->QX == nullptr) return fail(EDB200_ERR_NOMEM, "wan_prepare: workspace accounting error");
     if (m->world > 1) {
-        void* flags = w.take(8 * 64);
+        void* flags = w.take(1024);   // barrier flags + epoch
         m->QL = w.take(TL * D * 2);
         m->KL = w.take(TL * D * 2);
         m->VL = w.take(TL * D * 2);
@@ -486,6 +500,7 @@ edb200_status_t edb200_wan_prepare(edb200_wan_t* m, int frames, int lat_h, int l
     m->n_ctx = n_ctx;
     m->T = T;
     m->t_loc = TL;
+    m->t_rows = t_rows;
     return EDB200_OK;
 }
 
@@ -498,11 +513,12 @@ edb200_status_t edb200_wan_step(edb200_wan_t* m, const float* latent, float time
     EDB_TRY(m->params.all_loaded());
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const edb200_wan_config_t& c = m->cfg;
-    const int64_t D = c.dim, F = c.ffn_dim, T = m->T, TL = m->t_loc, n_ctx = m->n_ctx;
+    // TL: rows this rank owns (computed on); SL: rows of a rank's slot of the padded sequence (layout)
+    const int64_t D = c.dim, F = c.ffn_dim, T = m->T, TL = m->t_rows, SL = m->t_loc, n_ctx = m->n_ctx;
     const int d = static_cast<int>(D / c.num_heads);
     const int pt = c.patch_size[0], ph = c.patch_size[1], pw = c.patch_size[2];
     const int64_t pf_in = (int64_t)c.in_dim * pt * ph * pw, pf_out = (int64_t)c.out_dim * pt * ph * pw;
-    const int64_t first = (int64_t)m->rank * TL;   // first token this rank owns
+    const int64_t first = (int64_t)m->rank * SL;   // first token this rank owns
     const int F16 = EDB200_TYPE_F16;
     __half* xmod = static_cast<__half*>(m->XMOD);
     __half* qkv = static_cast<__half*>(m->QKV);
@@ -558,17 +574,17 @@ edb200_status_t edb200_wan_step(edb200_wan_t* m, const float* latent, float time
             const float* wk = fparam(m, p + "self_attn.norm_k.weight");
             if (m->p2p) {
                 EDB_TRY(edb200_qk_rownorm_rope_pack(qkv, F16, 3 * D, 0, D, 2 * D, TL, c.num_heads, d, wq, wk, m->RSTD,
-                                                    m->RSTD + TL, m->PE, 0, T, nullptr, nullptr, nullptr, F16,
+                                                    m->RSTD + TL, m->PE, 0, SL * m->world, nullptr, nullptr, nullptr, F16,
                                                     &m->qkv_peers, s));
             } else {
                 // NCCL exchange: local head-major buffers, position rows of this rank's tokens
                 const float* pe = m->PE + first * (d / 2) * 4;
                 EDB_TRY(edb200_qk_rownorm_rope_pack(qkv, F16, 3 * D, 0, D, 2 * D, TL, c.num_heads, d, wq, wk, m->RSTD,
-                                                    m->RSTD + TL, pe, 0, TL, sp ? m->QL : m->Q, sp ? m->KL : m->K,
+                                                    m->RSTD + TL, pe, 0, SL, sp ? m->QL : m->Q, sp ? m->KL : m->K,
                                                     sp ? m->VL : m->V, F16, nullptr, s));
             }
         }
-        EDB_TRY(self_attention(m, s));
+        EDB_TRY(self_attention(m, i, s));
         {
             const Lin lo = qlin(m, p + "self_attn.o");
             edb200_epilogue_t ep = make_ep(m->X, EDB200_TYPE_F32, D, lo.b);
@@ -626,9 +642,17 @@ edb200_status_t edb200_wan_step(edb200_wan_t* m, const float* latent, float time
         EDB_TRY(edb200_mul_mat_q(lh.w, xmod, F16, TL, D, &ep, s));
     }
     if (sp) {
-        std::vector<int64_t> firsts(m->world), counts(m->world, TL);
-        for (int r = 0; r < m->world; ++r) firsts[r] = (int64_t)r * TL;
-        EDB_TRY(edb200_sp_all_gather_rows(m->comm, m->TOK_LOC, m->TOK_OUT, firsts.data(), counts.data(), pf_out * 4, s));
+        std::vector<int64_t> firsts(m->world), counts(m->world);
+        for (int r = 0; r < m->world; ++r) {
+            firsts[r] = std::min<int64_t>((int64_t)r * SL, T);
+            counts[r] = std::min<int64_t>(SL, T - firsts[r]);
+        }
+        if (m->p2p) {
+            // peer stores + barrier: nothing of the step goes through a library exchange
+            EDB_TRY(edb200_sp_all_gather_rows_peer(m->comm, m->TOK_LOC, m->TOK_OUT, firsts.data(), counts.data(), pf_out * 4, s));
+        } else {
+            EDB_TRY(edb200_sp_all_gather_rows(m->comm, m->TOK_LOC, m->TOK_OUT, firsts.data(), counts.data(), pf_out * 4, s));
+        }
     }
     {
         const int64_t total = (int64_t)c.out_dim * m->frames * m->lat_h * m->lat_w;

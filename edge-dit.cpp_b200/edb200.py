@@ -47,6 +47,7 @@ class SD3Config(C.Structure):
         ("hidden_size", C.c_int), ("num_heads", C.c_int), ("depth", C.c_int), ("mlp_hidden", C.c_int),
         ("in_channels", C.c_int), ("out_channels", C.c_int), ("patch_size", C.c_int), ("adm_in_channels", C.c_int),
         ("context_size", C.c_int), ("pos_embed_max_size", C.c_int), ("wtype", C.c_int), ("attention", C.c_int),
+        ("sage_smooth_q", C.c_int), ("sage_skip_first", C.c_int), ("sage_skip_last", C.c_int),
     ]
 
 
@@ -57,6 +58,7 @@ class WanConfig(C.Structure):
         ("in_dim", C.c_int), ("out_dim", C.c_int), ("text_dim", C.c_int), ("freq_dim", C.c_int),
         ("patch_size", C.c_int * 3), ("axes_dim", C.c_int * 3), ("theta", C.c_int),
         ("wtype", C.c_int), ("attention", C.c_int), ("sage_smooth_q", C.c_int),
+        ("sage_skip_first", C.c_int), ("sage_skip_last", C.c_int),
     ]
 
 
@@ -82,6 +84,7 @@ _SIGS = {
     "edb200_last_error": (C.c_char_p, []),
     "edb200_version": (C.c_char_p, []),
     "edb200_launch_count": (c_i64, []),
+    "edb200_probe_mma_rate": (C.c_int, [C.c_int, C.c_int, C.POINTER(C.c_double), c_vp]),
     "edb200_profile_begin": (C.c_int, []),
     "edb200_profile_end": (C.c_int, [C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_double),
                                      C.POINTER(c_i64)]),
@@ -96,6 +99,9 @@ _SIGS = {
     "edb200_mul_mat_q_pair": (C.c_int, [c_vp, c_vp, c_i64, c_i64, C.POINTER(Epilogue),
                                         c_vp, c_vp, c_i64, c_i64, C.POINTER(Epilogue), C.c_int, c_vp]),
     "edb200_gemv_q": (C.c_int, [c_vp, c_vp, c_i64, c_i64, C.c_int, c_vp, c_vp, c_i64, c_vp]),
+    "edb200_gemv_batch_create": (C.c_int, [C.POINTER(c_vp), C.POINTER(c_vp), C.POINTER(c_vp), C.c_int, c_vp, C.POINTER(c_vp)]),
+    "edb200_gemv_batch_destroy": (None, [c_vp]),
+    "edb200_gemv_batch_run": (C.c_int, [c_vp, c_vp, C.c_int, c_vp, c_vp]),
     "edb200_linear_f32": (C.c_int, [c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_i64, C.c_int, C.c_int, c_vp, c_i64,
                                     c_vp]),
     "edb200_layernorm_modulate": (C.c_int, [c_vp, c_i64, c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, C.c_float, c_vp,
@@ -119,7 +125,27 @@ _SIGS = {
     "edb200_sage_attention": (C.c_int, [c_vp, c_vp, c_vp, C.c_int, c_i64, C.c_int, C.c_float, C.c_int, c_vp, c_i64,
                                         c_vp, C.c_int, c_i64, c_vp]),
     "edb200_sage_key_means_static": (C.c_int, [c_vp, C.c_int, c_i64, C.c_int, c_vp, c_vp]),
-    "edb200_sp_shard": (C.c_int, [c_i64, c_i64, C.c_int, C.c_int, C.POINTER(c_i64), C.POINTER(c_i64), C.POINTER(c_i64)]),
+    "edb200_sp_shard": (C.c_int, [c_i64, c_i64, C.c_int, C.c_int, C.POINTER(c_i64), C.POINTER(c_i64), C.POINTER(c_i64),
+                                  C.POINTER(c_i64)]),
+    "edb200_poll_status": (C.c_int, [c_vp]),
+    "edb200_comm_create_loopback": (C.c_int, [C.c_int, C.c_int, C.POINTER(c_vp)]),
+    "edb200_comm_set_timeout_ms": (C.c_int, [c_vp, c_i64]),
+    "edb200_comm_all_ok": (C.c_int, [c_vp, C.c_int, C.c_int]),
+    "edb200_cfg_parallel_combine_rescaled": (C.c_int, [c_vp, c_vp, C.c_float, C.c_int, C.c_int, C.c_int, C.c_int, c_vp,
+                                                       c_vp, c_vp]),
+    "edb200_attention_f16_strided": (C.c_int, [c_vp, c_vp, c_vp, C.c_int, c_i64, c_i64, c_i64, c_i64, C.c_int, C.c_float,
+                                               c_vp, C.c_int, c_i64, c_vp, c_vp]),
+    "edb200_sage_quantize_qk_strided": (C.c_int, [c_vp, c_vp, C.c_int, c_i64, c_i64, C.c_int, C.c_int, c_vp, c_i64, c_vp]),
+    "edb200_attention_sage_int8_strided": (C.c_int, [c_vp, c_vp, c_vp, c_i64, c_vp, C.c_int, c_vp, C.c_int, c_vp, C.c_int,
+                                                     C.c_int, c_i64, C.c_int, C.c_float, c_vp, C.c_int, c_i64, c_vp,
+                                                     c_vp]),
+    "edb200_sage_attention_strided": (C.c_int, [c_vp, c_vp, c_vp, C.c_int, c_i64, c_i64, C.c_int, C.c_float, C.c_int,
+                                                c_vp, c_i64, c_vp, C.c_int, c_i64, c_vp, c_vp]),
+    "edb200_sd3_set_comm": (C.c_int, [c_vp, c_vp]),
+    "edb200_flux_get_tensor_f32": (C.c_int, [c_vp, C.c_char_p, c_vp, c_i64, C.c_int, c_vp]),
+    "edb200_sd3_get_tensor_f32": (C.c_int, [c_vp, C.c_char_p, c_vp, c_i64, C.c_int, c_vp]),
+    "edb200_qwen_get_tensor_f32": (C.c_int, [c_vp, C.c_char_p, c_vp, c_i64, C.c_int, c_vp]),
+    "edb200_wan_get_tensor_f32": (C.c_int, [c_vp, C.c_char_p, c_vp, c_i64, C.c_int, c_vp]),
     "edb200_sp_heads_plan": (C.c_int, [C.c_int, C.c_int, C.c_int, c_i64, c_i64, C.POINTER(C.c_int), C.POINTER(c_i64),
                                        C.POINTER(c_i64), C.POINTER(c_i64), C.c_int]),
     "edb200_comm_unique_id": (C.c_int, [c_vp]),
@@ -131,6 +157,7 @@ _SIGS = {
                                              c_vp]),
     "edb200_sp_all_to_all_tokens": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_vp]),
     "edb200_sp_all_gather_rows": (C.c_int, [c_vp, c_vp, c_vp, C.POINTER(c_i64), C.POINTER(c_i64), c_i64, c_vp]),
+    "edb200_sp_all_gather_rows_peer": (C.c_int, [c_vp, c_vp, c_vp, C.POINTER(c_i64), C.POINTER(c_i64), c_i64, c_vp]),
     "edb200_comm_map_peers": (C.c_int, [c_vp, c_vp, c_i64, c_i64, c_vp]),
     "edb200_comm_unmap_peers": (C.c_int, [c_vp]),
     "edb200_comm_peers_mapped": (C.c_int, [c_vp]),
@@ -389,16 +416,51 @@ def _load_gguf(fn, handle, path, strip_prefix):
     return n.value
 
 
+class _ParamAccess:
+    """Parameter table access shared by the model classes (`_FAMILY` names the C entry points)."""
+
+    def tensor_table(self):
+        """[(name, ggml_type, n_out, k, raw bytes)] of every parameter."""
+        l = lib()
+        count = getattr(l, f"edb200_{self._FAMILY}_tensor_count")
+        info = getattr(l, f"edb200_{self._FAMILY}_tensor_info")
+        buf = C.create_string_buffer(256)
+        t, no, k, nb = C.c_int(), c_i64(), c_i64(), c_i64()
+        out = []
+        for i in range(count(self.handle)):
+            check(info(self.handle, i, buf, 256, C.byref(t), C.byref(no), C.byref(k), C.byref(nb)))
+            out.append((buf.value.decode(), t.value, no.value, k.value, nb.value))
+        return out
+
+    def get_tensor(self, name):
+        """The tensor as the device holds it, read back as numpy f32 [n_out, k] (vectors: [k]);
+        quantised weights come back dequantised."""
+        import numpy as np
+        if not hasattr(self, "_shapes"):
+            self._shapes = {n: (no, k) for n, _, no, k, _ in self.tensor_table()}
+        no, k = self._shapes[name]
+        out = np.empty((no, k), dtype=np.float32)
+        fn = getattr(lib(), f"edb200_{self._FAMILY}_get_tensor_f32")
+        check(fn(self.handle, name.encode(), out.ctypes.data_as(c_vp), out.size, 0, current_stream()))
+        return out[0] if no == 1 else out
+
+
 def euler_update(x, model_out, sigma, sigma_next):
     """In place on the device: x <- x + ((x - denoised)/sigma)*(sigma_next - sigma), denoised = x - sigma*model_out."""
     check(lib().edb200_euler_update(ptr(x), ptr(model_out), sigma, sigma_next, x.numel(), current_stream()))
 
 
 def sp_shard(n_tokens, n_txt, rank, world):
-    """(t_loc, n_txt_local, img_first) of `rank`'s token slice."""
-    a, b, c = c_i64(), c_i64(), c_i64()
-    check(lib().edb200_sp_shard(n_tokens, n_txt, rank, world, C.byref(a), C.byref(b), C.byref(c)))
-    return a.value, b.value, c.value
+    """(t_loc, n_txt_local, img_first, t_rows) of `rank`'s token slice: its slot of the padded
+    sequence has t_loc rows, of which it owns the first t_rows."""
+    a, b, c, d = c_i64(), c_i64(), c_i64(), c_i64()
+    check(lib().edb200_sp_shard(n_tokens, n_txt, rank, world, C.byref(a), C.byref(b), C.byref(c), C.byref(d)))
+    return a.value, b.value, c.value, d.value
+
+
+def poll_status():
+    """Synchronises the current stream and raises EdbError(status 4) if a device-side wait gave up."""
+    check(lib().edb200_poll_status(current_stream()))
 
 
 def sp_heads_plan(rank, world, heads, t_loc, row_bytes):
@@ -412,21 +474,31 @@ def sp_heads_plan(rank, world, heads, t_loc, row_bytes):
 
 
 class Comm:
-    """NCCL communicator of the library over the ranks of an initialised torch.distributed
-    group (one process per GPU); torch.distributed only carries the 128-byte id."""
+    """NCCL communicator of the library over ranks of an initialised torch.distributed group (one
+    process per GPU); torch.distributed only carries the 128-byte id.
 
-    def __init__(self):
+    ranks = None: all ranks.  ranks = [global ranks]: a communicator over that subset, this process
+    being one of them (its rank inside is its position in the list); EVERY process of the world must
+    then call Comm(...) at the same point, each with the subset it belongs to, because the ids
+    travel in one collective over the whole world.  This is how a CFG-parallel x sequence-parallel
+    world is built: one communicator per guidance branch and one per pair of branch partners."""
+
+    def __init__(self, ranks=None):
         import torch
         import torch.distributed as dist
-        rank, world = dist.get_rank(), dist.get_world_size()
+        g_rank, g_world = dist.get_rank(), dist.get_world_size()
+        ranks = list(range(g_world)) if ranks is None else [int(r) for r in ranks]
+        if g_rank not in ranks:
+            raise ValueError(f"rank {g_rank} is not in {ranks}")
+        rank, world = ranks.index(g_rank), len(ranks)
         buf = C.create_string_buffer(128)
         if rank == 0:
             check(lib().edb200_comm_unique_id(buf))
-        obj = [bytes(buf.raw)]
-        dist.broadcast_object_list(obj, src=0)
+        ids = [None] * g_world
+        dist.all_gather_object(ids, bytes(buf.raw) if rank == 0 else None)
         h = c_vp()
-        check(lib().edb200_comm_create(obj[0], rank, world, C.byref(h)))
-        self.handle, self.rank, self.world = h, rank, world
+        check(lib().edb200_comm_create(ids[ranks[0]], rank, world, C.byref(h)))
+        self.handle, self.rank, self.world, self.ranks = h, rank, world, ranks
         torch.cuda.synchronize()
 
     def close(self):
@@ -435,7 +507,9 @@ class Comm:
             self.handle = None
 
 
-class FluxModel:
+class FluxModel(_ParamAccess):
+    _FAMILY = "flux"
+
     """Thin owner of an edb200_flux_t: the host-side mirror of the reference's
     FluxModel adapter (src/dit_models/diffusion_model.hpp) over the C ABI."""
 
@@ -551,7 +625,9 @@ class FluxModel:
         return out
 
 
-class QwenModel:
+class QwenModel(_ParamAccess):
+    _FAMILY = "qwen"
+
     """Thin owner of an edb200_qwen_t (host-side mirror of the reference's QwenImageModel adapter,
     src/dit_models/diffusion_model.hpp) over the C ABI; one call is one batch-1 pass."""
 
@@ -625,19 +701,22 @@ class QwenModel:
         return out
 
 
-class SD3Model:
+class SD3Model(_ParamAccess):
+    _FAMILY = "sd3"
+
     """Thin owner of an edb200_sd3_t (host-side mirror of the reference's MMDiTModel adapter,
     src/dit_models/diffusion_model.hpp) over the C ABI; one call is one batch-1 pass."""
 
     def __init__(self, hidden_size=1536, num_heads=24, depth=24, mlp_hidden=None, in_channels=16, out_channels=16,
                  patch_size=2, adm_in_channels=2048, context_size=4096, pos_embed_max_size=192, wtype=TYPE_Q8_0,
-                 attention=ATTN_F16):
+                 attention=ATTN_F16, sage_smooth_q=False, sage_skip_first=2, sage_skip_last=2):
         cfg = SD3Config()
         cfg.hidden_size, cfg.num_heads, cfg.depth = hidden_size, num_heads, depth
         cfg.mlp_hidden = mlp_hidden if mlp_hidden is not None else 4 * hidden_size
         cfg.in_channels, cfg.out_channels, cfg.patch_size = in_channels, out_channels, patch_size
         cfg.adm_in_channels, cfg.context_size, cfg.pos_embed_max_size = adm_in_channels, context_size, pos_embed_max_size
         cfg.wtype, cfg.attention = wtype, attention
+        cfg.sage_smooth_q, cfg.sage_skip_first, cfg.sage_skip_last = int(sage_smooth_q), sage_skip_first, sage_skip_last
         self.cfg = cfg
         h = c_vp()
         check(lib().edb200_sd3_create(C.byref(cfg), C.byref(h)))
@@ -674,6 +753,10 @@ class SD3Model:
         """Loads (and, for quantised parameters, encodes on the device) the tensors of a safetensors file."""
         return _load_gguf(lib().edb200_sd3_load_safetensors, self.handle, path, strip_prefix)
 
+    def set_comm(self, comm):
+        self._comm = comm
+        check(lib().edb200_sd3_set_comm(self.handle, comm.handle if comm is not None else None))
+
     def set_tap(self, tap):
         self._tap = tap
         check(lib().edb200_sd3_set_tap(self.handle, ptr(tap)))
@@ -696,19 +779,22 @@ class SD3Model:
         return out
 
 
-class WanModel:
+class WanModel(_ParamAccess):
+    _FAMILY = "wan"
+
     """Thin owner of an edb200_wan_t (host-side mirror of the reference's WanModel adapter,
     src/dit_models/diffusion_model.hpp) over the C ABI."""
 
     def __init__(self, dim=5120, num_heads=40, ffn_dim=13824, num_layers=40, in_dim=16, out_dim=16, text_dim=4096,
                  freq_dim=256, patch_size=(1, 2, 2), axes_dim=(44, 42, 42), theta=10000, wtype=TYPE_Q8_0,
-                 attention=ATTN_SAGE_INT8, sage_smooth_q=True):
+                 attention=ATTN_SAGE_INT8, sage_smooth_q=True, sage_skip_first=2, sage_skip_last=2):
         cfg = WanConfig()
         cfg.dim, cfg.num_heads, cfg.ffn_dim, cfg.num_layers = dim, num_heads, ffn_dim, num_layers
         cfg.in_dim, cfg.out_dim, cfg.text_dim, cfg.freq_dim = in_dim, out_dim, text_dim, freq_dim
         cfg.patch_size = (C.c_int * 3)(*patch_size)
         cfg.axes_dim = (C.c_int * 3)(*axes_dim)
         cfg.theta, cfg.wtype, cfg.attention, cfg.sage_smooth_q = theta, wtype, attention, int(sage_smooth_q)
+        cfg.sage_skip_first, cfg.sage_skip_last = sage_skip_first, sage_skip_last
         self.cfg = cfg
         h = c_vp()
         check(lib().edb200_wan_create(C.byref(cfg), C.byref(h)))

@@ -68,6 +68,14 @@ EDB200_API const char* edb200_version(void);
 /* Number of kernels this library has launched in the calling process. */
 EDB200_API int64_t edb200_launch_count(void);
 
+/* Status of the device-side bounded waits.  Kernels of this library never wait without a limit (TMA
+ * and tensor-pipe barriers about two seconds, the cross-GPU barrier edb200_comm_set_timeout_ms); a wait
+ * that gives up sets a status word on the device and the kernel returns.  This call synchronises
+ * `stream`, reads and clears the word: EDB200_OK, or EDB200_ERR_TIMEOUT when a wait has given up since
+ * the last poll (results produced after that point are not valid).  The *_compute_host entry points
+ * poll by themselves; callers of the device-resident *_step entry points poll where they synchronise. */
+EDB200_API edb200_status_t edb200_poll_status(void* stream);
+
 /* Per-kernel-class timing for measurement runs.  Between begin and end every
  * kernel launch of this library is bracketed by CUDA events on its stream;
  * end synchronises the device and fills arrays of 5 entries indexed by class
@@ -77,6 +85,13 @@ EDB200_API int64_t edb200_launch_count(void);
  * (src/core/backend/ggml/ggml_extend.hpp:2842, src/dit_models/models/flux.hpp:82-95). */
 EDB200_API edb200_status_t edb200_profile_begin(void);
 EDB200_API edb200_status_t edb200_profile_end(double* ms, double* flops, double* bytes, int64_t* launches);
+
+/* Tensor-pipe rate of this GPU: every SM issues tcgen05.mma 128 x 256 instructions back to back with
+ * operands resident in shared memory (no loads), kind 0 = kind::f16 (f32 accumulate), 1 = kind::i8
+ * (s32 accumulate); *tera_ops = 2 * MACs / time / 1e12.  Synchronises the stream.  A measurement aid
+ * without a counterpart in the reference: the i8 / f16 ratio carries a measured dense bf16 GEMM peak
+ * over to an INT8 peak for the roofline of the INT8-QK attention kernel. */
+EDB200_API edb200_status_t edb200_probe_mma_rate(int kind, int iters, double* tera_ops, void* stream);
 
 /* CUDA graphs.  Everything this library enqueues on `stream` between begin and end (for
  * example one whole edb200_*_step with fixed buffers) is recorded instead of executed and
@@ -175,6 +190,24 @@ EDB200_API edb200_status_t edb200_mul_mat_q_pair(const edb200_qweight_t* w0, con
 EDB200_API edb200_status_t edb200_gemv_q(const edb200_qweight_t* w, const float* x, int64_t m, int64_t ldx, int pre_silu,
                               const float* bias, float* y, int64_t ldy, void* stream);
 
+/* Many weight-streaming products of ONE input vector in one launch: y_i[n_out_i] = act(x[k]) . W_i^T + bias_i
+ * for i < n.  All weights share one block type and row length.  The adaLN projections of a whole
+ * denoise step are such a batch (every Modulation::forward of the step reads silu(vec),
+ * src/dit_models/models/flux.hpp:1617-1634, :3547-3555): one launch streams all their weights back to
+ * back instead of one small launch per projection.  create stores the weight / bias / output
+ * addresses on the device (they must stay valid; bias may be NULL, or hold NULL entries); run
+ * may be recorded into a CUDA graph.  `share` != NULL (sequence parallel, peer memory mapped): the
+ * ranks split the rows of the batch between them and store their part into every rank's outputs;
+ * share->buf[0][p] is rank p's mapping of one common address (e.g. the start of the output
+ * area), outputs must lie at the same offsets on every rank, and a barrier (edb200_sp_barrier)
+ * must follow before the results are read. */
+typedef struct edb200_gemv_batch edb200_gemv_batch_t;
+EDB200_API edb200_status_t edb200_gemv_batch_create(const edb200_qweight_t* const* w, const float* const* bias,
+                                                    float* const* y, int n, void* stream, edb200_gemv_batch_t** out);
+EDB200_API void edb200_gemv_batch_destroy(edb200_gemv_batch_t* b);
+EDB200_API edb200_status_t edb200_gemv_batch_run(const edb200_gemv_batch_t* b, const float* x, int pre_silu,
+                                                 const edb200_sp_peers_t* share, void* stream);
+
 /* Dense f32 weight, small problems of the prelude / final layer:
  * y[m, n] = act(x[m, k] . W[n, k]^T + bias).  x f32, y f32. */
 EDB200_API edb200_status_t edb200_linear_f32(const float* w, const float* bias, const float* x, int64_t m, int64_t k,
@@ -242,7 +275,7 @@ EDB200_API edb200_status_t edb200_qk_norm_rope_pack(const void* qkv, int in_dtyp
  * [n_heads / world, l_total, d_head] q, k, v buffers (dst->buf[0..2]) at global token
  * position rank * t_loc + tok_off + t; `pe` is the table of the whole sequence.
  * Replaces the SP pack callbacks plus the seq->head all-to-all
- * (src/parallel/sp_parallel.cpp:99-469, src/parallel/nccl_process_group.cpp:394-459). */
+ * (src/core/parallel/sp_parallel.cpp:99-469, src/core/parallel/backends/nccl/nccl_process_group.cpp:394-459). */
 EDB200_API edb200_status_t edb200_qk_norm_rope_pack_sp(const void* qkv, int in_dtype, int64_t ld, int64_t q_off,
                                                        int64_t k_off, int64_t v_off, int64_t tokens, int n_heads,
                                                        int d_head, const float* q_weight, const float* k_weight,
@@ -283,6 +316,16 @@ EDB200_API edb200_status_t edb200_attention_f16(const void* q, const void* k, co
                                                 int64_t lk, int d_head, float scale, void* out, int out_dtype,
                                                 int64_t ld_out, void* stream);
 
+/* The same on buffers laid out for a longer (padded) sequence: consecutive heads are q_head_rows
+ * (>= lq) rows apart in q and kv_head_rows (>= lk) rows apart in k and v, and only the first lq / lk
+ * rows of every head are read.  This is how a sequence-parallel rank attends over a sequence that was
+ * padded to a multiple of the world size (src/core/parallel/sp_parallel.cpp:757-768) without computing
+ * on the padding.  dst may be NULL (plain output) or the peer description of edb200_attention_f16_sp. */
+EDB200_API edb200_status_t edb200_attention_f16_strided(const void* q, const void* k, const void* v, int hn, int64_t lq,
+                                                        int64_t lk, int64_t q_head_rows, int64_t kv_head_rows,
+                                                        int d_head, float scale, void* out, int out_dtype,
+                                                        int64_t ld_out, const edb200_sp_peers_t* dst, void* stream);
+
 /* Sage path.  Scratch is caller-allocated like the reference's
  * (src/core/backend/ggml/cuda/ed_cuda_sage_attn.h:19-71): query the size, pass a
  * 256-byte aligned device buffer. */
@@ -304,7 +347,8 @@ EDB200_API edb200_status_t edb200_sage_quantize_qk(const void* q_f16, const void
 /* INT8 QK^T attention on already quantised operands (main kernel of run_sage,
  * src/core/backend/ggml/cuda/ed_cuda_sage_attn.cu:834-1122).  q_scale one per 32
  * query rows, k_scale one per 64 keys, bias one per key (NULL = no smooth-Q);
- * rows of all three must cover l rounded up to 128.  d_head 128. */
+ * rows of all three must cover l rounded up to 128.  d_head 64 or 128 (the reference gates its
+ * Sage path on exactly these, src/core/backend/ggml/ggml_extend.hpp:1916-1928). */
 EDB200_API edb200_status_t edb200_attention_sage_int8(const void* q_i8, const void* k_i8, const void* v_f16,
                                                       const float* q_scale, int q_scale_stride,
                                                       const float* k_scale, int k_scale_stride, const float* bias,
@@ -315,6 +359,23 @@ EDB200_API edb200_status_t edb200_sage_attention(const void* q_f16, const void* 
                                                  int64_t l, int d_head, float scale, int smooth_q, void* scratch,
                                                  int64_t scratch_bytes, void* out, int out_dtype, int64_t ld_out,
                                                  void* stream);
+/* Variants for inputs whose heads are head_rows (>= l) rows apart (padded sequence, see
+ * edb200_attention_f16_strided); the INT8 copies and their scales in the scratch buffer stay dense. */
+EDB200_API edb200_status_t edb200_sage_quantize_qk_strided(const void* q_f16, const void* k_f16, int hn, int64_t l,
+                                                           int64_t head_rows, int d_head, int smooth_q, void* scratch,
+                                                           int64_t scratch_bytes, void* stream);
+EDB200_API edb200_status_t edb200_attention_sage_int8_strided(const void* q_i8, const void* k_i8, const void* v_f16,
+                                                              int64_t v_head_rows, const float* q_scale,
+                                                              int q_scale_stride, const float* k_scale,
+                                                              int k_scale_stride, const float* bias, int bias_stride,
+                                                              int hn, int64_t l, int d_head, float scale, void* out,
+                                                              int out_dtype, int64_t ld_out,
+                                                              const edb200_sp_peers_t* dst, void* stream);
+EDB200_API edb200_status_t edb200_sage_attention_strided(const void* q_f16, const void* k_f16, const void* v_f16, int hn,
+                                                         int64_t l, int64_t head_rows, int d_head, float scale,
+                                                         int smooth_q, void* scratch, int64_t scratch_bytes, void* out,
+                                                         int out_dtype, int64_t ld_out, const edb200_sp_peers_t* dst,
+                                                         void* stream);
 /* Per-channel key means (the smooth-K vector, chunked sum as with
  * EDB200_SAGE_FAST_MEANS) for callers that cannot hand over or allocate device
  * scratch.  No counterpart in the reference, whose means always live in the
@@ -334,14 +395,18 @@ EDB200_API edb200_status_t edb200_sage_key_means_static(const void* k_f16, int h
  * One process per GPU.  Every rank owns n_tokens / world consecutive tokens of the
  * [text ; image] sequence for the per-token work and heads / world heads for
  * attention.  Replaces the reference's SP pack / split / gather callbacks
- * (src/parallel/sp_parallel.cpp:99-469,793-831) and NCCL all-to-all
- * (src/parallel/nccl_process_group.cpp:394-459). */
+ * (src/core/parallel/sp_parallel.cpp:99-469,793-831) and NCCL all-to-all
+ * (src/core/parallel/backends/nccl/nccl_process_group.cpp:394-459). */
 typedef struct edb200_comm edb200_comm_t;
-/* Token slice of `rank`: t_loc tokens, of which the first n_txt_local are text
- * rows; img_first = index of its first image token among the image tokens.
+/* Token slice of `rank`.  The sequence is padded to a multiple of the world size like the reference's
+ * sp_sequence_padding (src/core/parallel/sp_parallel.cpp:757-768): every rank has a slot of
+ * t_loc = ceil(n_tokens / world) rows, of which it owns the first t_rows (less than t_loc, possibly 0,
+ * on the last ranks when the sequence does not divide); the first n_txt_local of them are text rows;
+ * img_first = index of its first image token among the image tokens.  Padding rows are never
+ * computed: attention runs over the n_tokens real rows of buffers laid out for world * t_loc.
  * Pure host arithmetic (no device needed). */
 EDB200_API edb200_status_t edb200_sp_shard(int64_t n_tokens, int64_t n_txt, int rank, int world, int64_t* t_loc,
-                                           int64_t* n_txt_local, int64_t* img_first);
+                                           int64_t* n_txt_local, int64_t* img_first, int64_t* t_rows);
 /* Message list of the heads exchange [heads, t_loc, row] -> [heads/world, T, row]:
  * message i goes to and comes from peer[i], `bytes[i]` bytes from send_off[i] of the
  * send buffer and to recv_off[i] of the receive buffer.  Returns the number of
@@ -355,15 +420,29 @@ EDB200_API int edb200_sp_heads_plan(int rank, int world, int heads, int64_t t_lo
 EDB200_API edb200_status_t edb200_comm_unique_id(void* id128);
 EDB200_API edb200_status_t edb200_comm_create(const void* id128, int rank, int world, edb200_comm_t** out);
 EDB200_API void edb200_comm_destroy(edb200_comm_t* c);
+/* A communicator of `world` ranks with no transport behind it: edb200_comm_map_peers maps every
+ * "peer" onto the caller's own allocation, the NCCL exchanges return EDB200_ERR_UNSUPPORTED.  For
+ * single-process tests of code that needs a mapped communicator, e.g. letting edb200_sp_barrier run
+ * into its time limit because no other rank ever arrives (ProcessGroup stubs of the reference:
+ * src/core/parallel/backends/cpu/cpu_process_group.cpp). */
+EDB200_API edb200_status_t edb200_comm_create_loopback(int rank, int world, edb200_comm_t** out);
+/* Limit of the device-side wait of edb200_sp_barrier in milliseconds (default 2000, 1..60000). */
+EDB200_API edb200_status_t edb200_comm_set_timeout_ms(edb200_comm_t* c, int64_t ms);
+/* The decision rule of edb200_comm_map_peers, exported for host tests: 1 when ok[p * stride] == 1
+ * for every rank p, else 0.  Every rank evaluates it on the same gathered bytes. */
+EDB200_API int edb200_comm_all_ok(const unsigned char* ok, int stride, int world);
 EDB200_API int edb200_comm_rank(const edb200_comm_t* c);
 EDB200_API int edb200_comm_world(const edb200_comm_t* c);
 /* Peer memory.  Every rank passes ONE device allocation of the same size and layout
  * (`base`, from cudaMalloc); afterwards edb200_comm_peer_ptr translates an address
  * inside this rank's allocation into the same place of `peer`'s allocation as
  * addressed from this GPU (CUDA IPC mapping, plain loads and stores over NVLink).
- * flags_off names 512 bytes inside the allocation that the barrier below owns.
- * Collective over the communicator (it meets the other ranks); returns
- * EDB200_ERR_UNSUPPORTED where IPC mappings are not available, and the NCCL
+ * flags_off names 1024 bytes inside the allocation that the barrier below owns (eight flag
+ * words and the barrier's epoch counter).
+ * Collective over the communicator: every rank runs both of its rendezvous even when its own
+ * handle export or one of its handle imports fails, and carries that failure in the message, so
+ * all ranks return the same status together: EDB200_OK, or EDB200_ERR_UNSUPPORTED (nothing stays
+ * mapped on any rank) where IPC mappings are not available on some rank, and the NCCL
  * exchanges below remain usable.  unmap is collective too and must come before the
  * allocation is freed. */
 EDB200_API edb200_status_t edb200_comm_map_peers(edb200_comm_t* c, void* base, int64_t bytes, int64_t flags_off,
@@ -373,8 +452,10 @@ EDB200_API int edb200_comm_peers_mapped(const edb200_comm_t* c);
 EDB200_API void* edb200_comm_peer_ptr(const edb200_comm_t* c, int peer, const void* local_ptr);
 /* Barrier across the ranks' streams, one small kernel per rank: everything this rank
  * enqueued before it (including its stores into peer memory) is visible to every
- * rank's work enqueued after it.  The device-side wait gives up after about two
- * seconds and reports EDB200_ERR_TIMEOUT at the next status poll. */
+ * rank's work enqueued after it.  The barrier's epoch counter lives in device memory and the
+ * kernel advances it, so a recorded barrier (edb200_graph_*) works on every replay.  The
+ * device-side wait gives up after the communicator's time limit (edb200_comm_set_timeout_ms,
+ * default two seconds) and edb200_poll_status then reports EDB200_ERR_TIMEOUT. */
 EDB200_API edb200_status_t edb200_sp_barrier(edb200_comm_t* c, void* stream);
 /* Heads exchange of n_tensors buffers (Q, K, V) in one NCCL group; no pack or
  * unpack kernel: every message is contiguous on both sides. */
@@ -392,6 +473,14 @@ EDB200_API edb200_status_t edb200_sp_all_to_all_tokens(edb200_comm_t* c, const v
 EDB200_API edb200_status_t edb200_sp_all_gather_rows(edb200_comm_t* c, const void* send, void* recv,
                                                      const int64_t* row_first, const int64_t* row_count,
                                                      int64_t row_bytes, void* stream);
+
+/* The same over peer memory (needs edb200_comm_map_peers; `recv` must lie inside the mapped allocation at the
+ * same offset on every rank): a kernel stores this rank's rows into every rank's `recv`, then
+ * edb200_sp_barrier orders the stores before whatever reads `recv` next.  No library exchange is
+ * involved, so the call can be recorded into a CUDA graph.  Rows must be multiples of 16 bytes. */
+EDB200_API edb200_status_t edb200_sp_all_gather_rows_peer(edb200_comm_t* c, const void* send, void* recv,
+                                                          const int64_t* row_first, const int64_t* row_count,
+                                                          int64_t row_bytes, void* stream);
 
 /* Attention with the tokens exchange of sequence parallelism fused in: this rank
  * computes `hn` heads for all l tokens and stores query row r into rank r / t_loc's
@@ -412,12 +501,18 @@ EDB200_API edb200_status_t edb200_sage_attention_sp(const void* q_f16, const voi
                                                     int64_t scratch_bytes, void* out, int out_dtype, int64_t ld_out,
                                                     const edb200_sp_peers_t* dst, void* stream);
 
-/* CFG-parallel step on a 2-rank communicator (cfg_all_gather, src/parallel/cfg_parallel.cpp:38-108):
+/* CFG-parallel step on a 2-rank communicator (cfg_all_gather, src/core/parallel/cfg_parallel.cpp:38-108):
  * rank 0 has run the conditional pass, rank 1 the unconditional one; both receive
  * out = uncond + scale * (cond - uncond).  `gathered` is scratch for 2 * n floats.  Combine it with
  * sequence parallelism by giving every branch its own edb200_comm_t for the model. */
 EDB200_API edb200_status_t edb200_cfg_parallel_combine(edb200_comm_t* c, const float* mine, float scale,
                                                        float* gathered, float* out, int64_t n, void* stream);
+
+/* The same with Qwen-Image's norm-preserving combine (edb200_cfg_combine_rescaled) after the gather;
+ * tensors f32 [channels, height, width], `gathered` holds 2 * channels * height * width floats. */
+EDB200_API edb200_status_t edb200_cfg_parallel_combine_rescaled(edb200_comm_t* c, const float* mine, float scale,
+                                                                int patch_size, int channels, int height, int width,
+                                                                float* gathered, float* out, void* stream);
 
 /* ------------------------------------------------------------ weight ingest
  * Reader for GGUF files, the container the reference's converter writes and its loader reads
@@ -489,6 +584,12 @@ EDB200_API edb200_status_t edb200_flux_tensor_info(const edb200_flux_t* m, int i
  * for quantised weights, f32 for everything else. */
 EDB200_API edb200_status_t edb200_flux_set_tensor(edb200_flux_t* m, const char* name, int ggml_type, const void* data,
                                                   int64_t nbytes, int on_device, void* stream);
+/* Reads one tensor back as f32 [n_out, k] into host (on_device = 0) or device memory; a quantised weight
+ * is dequantised from its repacked device form (the values ggml's dequantize_row gives for the blocks
+ * that were loaded).  n_floats must equal n_out * k.  Synchronises the stream.  Lets a checker run on
+ * exactly the weights the device holds, e.g. after edb200_flux_init_random. */
+EDB200_API edb200_status_t edb200_flux_get_tensor_f32(const edb200_flux_t* m, const char* name, float* out,
+                                                      int64_t n_floats, int on_device, void* stream);
 /* Loads every tensor of a GGUF file this model has a parameter for (names compared after removing
  * `strip_prefix`, e.g. "model.diffusion_model."; NULL = none); other tensors are skipped.  Quantised
  * weights must be stored in the model's block type; f16 / bf16 vectors are widened to f32.
@@ -530,8 +631,9 @@ EDB200_API edb200_status_t edb200_flux_compute_host(edb200_flux_t* m, const floa
 
 /* Sequence-parallel execution of the step (FLUX forward_sp, src/dit_models/models/flux.hpp:4529-5156):
  * call before edb200_flux_prepare; NULL returns to single-GPU execution.  Every
- * rank passes the full inputs and receives the full output latent; n_tokens and
- * num_heads must divide by the communicator size.  The communicator is borrowed. */
+ * rank passes the full inputs and receives the full output latent; num_heads must divide
+ * by the communicator size, the token count need not (edb200_sp_shard pads it).  The
+ * communicator is borrowed. */
 EDB200_API edb200_status_t edb200_flux_set_comm(edb200_flux_t* m, edb200_comm_t* comm);
 
 /* ------------------------------------------------ SD3-medium (MMDiT) denoise pass
@@ -550,7 +652,11 @@ typedef struct {
     int context_size;       /* 4096 */
     int pos_embed_max_size; /* 192 */
     int wtype;              /* EDB200_TYPE_Q8_0 / EDB200_TYPE_Q4_K */
-    int attention;          /* EDB200_ATTN_F16 (head dim 64 has no INT8 kernel in this build) */
+    int attention;          /* EDB200_ATTN_F16 / EDB200_ATTN_SAGE_INT8 (ED_SAGE_ATTN) */
+    int sage_smooth_q;      /* ED_SAGE_SMOOTH_Q; the reference's default for head dim 64 is off
+                               (src/core/backend/ggml/ed_ggml_sage_attn_ext.hpp:67-86) */
+    int sage_skip_first;    /* ED_SAGE_SKIP_FIRST / ED_SAGE_SKIP_LAST: that many first / last joint blocks keep f16 */
+    int sage_skip_last;     /* attention (reference default 2 and 2, ed_ggml_sage_attn_ext.hpp:146-159) */
 } edb200_sd3_config_t;
 
 typedef struct edb200_sd3 edb200_sd3_t;
@@ -562,6 +668,12 @@ EDB200_API edb200_status_t edb200_sd3_tensor_info(const edb200_sd3_t* m, int ind
                                                   int* ggml_type, int64_t* n_out, int64_t* k, int64_t* nbytes);
 EDB200_API edb200_status_t edb200_sd3_set_tensor(edb200_sd3_t* m, const char* name, int ggml_type, const void* data,
                                                  int64_t nbytes, int on_device, void* stream);
+/* Reads one tensor back as f32 [n_out, k] into host (on_device = 0) or device memory; a quantised weight
+ * is dequantised from its repacked device form (the values ggml's dequantize_row gives for the blocks
+ * that were loaded).  n_floats must equal n_out * k.  Synchronises the stream.  Lets a checker run on
+ * exactly the weights the device holds, e.g. after edb200_sd3_init_random. */
+EDB200_API edb200_status_t edb200_sd3_get_tensor_f32(const edb200_sd3_t* m, const char* name, float* out,
+                                                      int64_t n_floats, int on_device, void* stream);
 /* Loads every tensor of a GGUF file this model has a parameter for (names compared after removing
  * `strip_prefix`, e.g. "model.diffusion_model."; NULL = none); other tensors are skipped.  Quantised
  * weights must be stored in the model's block type; f16 / bf16 vectors are widened to f32.
@@ -578,6 +690,9 @@ EDB200_API int64_t edb200_sd3_weight_bytes(const edb200_sd3_t* m);
 EDB200_API edb200_status_t edb200_sd3_prepare(edb200_sd3_t* m, int lat_h, int lat_w, int n_ctx, void* stream);
 /* Optional f32 tap [depth, n_ctx + image tokens, hidden]: both streams after every block. */
 EDB200_API edb200_status_t edb200_sd3_set_tap(edb200_sd3_t* m, float* tap);
+/* Sequence parallel over `comm` (MMDiT forward_sp, src/dit_models/models/mmdit.hpp:3117-3128, 3439-3466):
+ * before prepare; NULL returns to single-GPU execution. */
+EDB200_API edb200_status_t edb200_sd3_set_comm(edb200_sd3_t* m, edb200_comm_t* comm);
 /* latent f32 [in_channels, lat_h, lat_w], context f32 [n_ctx, context_size], y f32 [adm_in_channels]. */
 EDB200_API edb200_status_t edb200_sd3_step(edb200_sd3_t* m, const float* latent, float timestep, const float* context,
                                            const float* y, float* out, void* stream);
@@ -585,7 +700,7 @@ EDB200_API edb200_status_t edb200_sd3_compute_host(edb200_sd3_t* m, const float*
                                                    float timestep, const float* context, int n_ctx, const float* y,
                                                    float* out, void* stream);
 /* out = uncond + scale * (cond - uncond), f32, n a multiple of 4: the pipeline-side CFG combine
- * (src/pipelines/sd3_pipeline.cpp:631-669, src/pipelines/flux_pipeline.cpp:1218-1258). */
+ * (src/dit_models/pipelines/sd3_pipeline.cpp:631-669, src/dit_models/pipelines/flux_pipeline.cpp:1218-1258). */
 EDB200_API edb200_status_t edb200_cfg_combine(const float* uncond, const float* cond, float scale, float* out, int64_t n,
                                               void* stream);
 /* Qwen-Image's guidance combine (ed_qwen_apply_true_cfg, src/dit_models/pipelines/qwen_image_pipeline.cpp:29-85):
@@ -609,7 +724,9 @@ typedef struct {
     int patch_size;           /* 2 */
     int axes_dim[3];          /* (16, 56, 56) */
     int theta;
-    int wtype;                /* EDB200_TYPE_Q8_0 / EDB200_TYPE_Q4_K: every 2-D weight with row length % 256 == 0 */
+    int wtype;                /* EDB200_TYPE_Q8_0 / EDB200_TYPE_Q4_K for every 2-D weight with row length % 256 == 0
+                                 except img_in / txt_in (kept f32, src/core/runtime/model_loader.cpp:2152-2155);
+                                 img_mod.1 / txt_mod.1 are at least q8_0 (:1746-1761) */
     int attention;            /* EDB200_ATTN_F16 / EDB200_ATTN_SAGE_INT8 */
     int sage_smooth_q;
 } edb200_qwen_config_t;
@@ -623,6 +740,12 @@ EDB200_API edb200_status_t edb200_qwen_tensor_info(const edb200_qwen_t* m, int i
                                                    int* ggml_type, int64_t* n_out, int64_t* k, int64_t* nbytes);
 EDB200_API edb200_status_t edb200_qwen_set_tensor(edb200_qwen_t* m, const char* name, int ggml_type, const void* data,
                                                   int64_t nbytes, int on_device, void* stream);
+/* Reads one tensor back as f32 [n_out, k] into host (on_device = 0) or device memory; a quantised weight
+ * is dequantised from its repacked device form (the values ggml's dequantize_row gives for the blocks
+ * that were loaded).  n_floats must equal n_out * k.  Synchronises the stream.  Lets a checker run on
+ * exactly the weights the device holds, e.g. after edb200_qwen_init_random. */
+EDB200_API edb200_status_t edb200_qwen_get_tensor_f32(const edb200_qwen_t* m, const char* name, float* out,
+                                                      int64_t n_floats, int on_device, void* stream);
 /* Loads every tensor of a GGUF file this model has a parameter for (names compared after removing
  * `strip_prefix`, e.g. "model.diffusion_model."; NULL = none); other tensors are skipped.  Quantised
  * weights must be stored in the model's block type; f16 / bf16 vectors are widened to f32.
@@ -666,6 +789,8 @@ typedef struct {
     int wtype;          /* EDB200_TYPE_Q8_0 / EDB200_TYPE_Q4_K for the block linears */
     int attention;      /* self-attention: EDB200_ATTN_F16 / EDB200_ATTN_SAGE_INT8; cross-attention is always f16 */
     int sage_smooth_q;
+    int sage_skip_first;  /* ED_SAGE_SKIP_FIRST / ED_SAGE_SKIP_LAST: that many first / last layers keep f16 */
+    int sage_skip_last;   /* self-attention (reference default 2 and 2, ed_ggml_sage_attn_ext.hpp:146-159) */
 } edb200_wan_config_t;
 
 typedef struct edb200_wan edb200_wan_t;
@@ -677,6 +802,12 @@ EDB200_API edb200_status_t edb200_wan_tensor_info(const edb200_wan_t* m, int ind
                                                   int* ggml_type, int64_t* n_out, int64_t* k, int64_t* nbytes);
 EDB200_API edb200_status_t edb200_wan_set_tensor(edb200_wan_t* m, const char* name, int ggml_type, const void* data,
                                                  int64_t nbytes, int on_device, void* stream);
+/* Reads one tensor back as f32 [n_out, k] into host (on_device = 0) or device memory; a quantised weight
+ * is dequantised from its repacked device form (the values ggml's dequantize_row gives for the blocks
+ * that were loaded).  n_floats must equal n_out * k.  Synchronises the stream.  Lets a checker run on
+ * exactly the weights the device holds, e.g. after edb200_wan_init_random. */
+EDB200_API edb200_status_t edb200_wan_get_tensor_f32(const edb200_wan_t* m, const char* name, float* out,
+                                                      int64_t n_floats, int on_device, void* stream);
 /* Loads every tensor of a GGUF file this model has a parameter for (names compared after removing
  * `strip_prefix`, e.g. "model.diffusion_model."; NULL = none); other tensors are skipped.  Quantised
  * weights must be stored in the model's block type; f16 / bf16 vectors are widened to f32.

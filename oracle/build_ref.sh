@@ -3,9 +3,11 @@
 # (src/utils/tensor.hpp), from where they lie in the reference tree, into oracle/_ref/libedref_cpu.so.
 # Test infrastructure.
 # Usage: sh oracle/build_ref.sh [reference root]
+# The reference root comes from the argument, else from EDB200_REFERENCE_DIR, else a directory named
+# "reference" beside this repository is tried; without one nothing is built.
 set -e
 HERE="$(cd "$(dirname "$0")" && pwd)"
-REF="${1:-/root/reference}"
+REF="${1:-${EDB200_REFERENCE_DIR:-$(dirname "$(dirname "$HERE")")/reference}}"
 SRC="$REF/src/core/backend/ggml"
 if [ ! -f "$SRC/ed_ggml_modulation_ext.hpp" ]; then
     echo "build_ref.sh: reference tree not found at $REF (nothing built)" >&2

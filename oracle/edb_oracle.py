@@ -163,6 +163,14 @@ def q4_k_quantize(x: np.ndarray) -> np.ndarray:
     return out.reshape(rows, (K // QK_K) * Q4_K_BLOCK_BYTES)
 
 
+def resolve_weights(weights):
+    """{name: (ggml_type, array)} -> {name: f32 array} (dequantised); any other mapping is returned as is
+    (it must give f32 arrays by name, support .get(name) and iteration over names)."""
+    if isinstance(weights, dict):
+        return {k: dequantize(v, t) if t != GGML_TYPE_F32 else v for k, (t, v) in weights.items()}
+    return weights
+
+
 def quantize(x: np.ndarray, ggml_type: int) -> np.ndarray:
     if ggml_type == GGML_TYPE_Q8_0:
         return q8_0_quantize(x)
@@ -416,6 +424,43 @@ def sage_channel_mean(x: np.ndarray) -> np.ndarray:
     for t in range(L):
         acc = acc + x[:, t, :].astype(np.float32)
     return (acc / np.float32(L)).astype(np.float32)
+
+
+def sage_channel_mean_chunked(x: np.ndarray) -> np.ndarray:
+    """Model of this library's fast channel mean (EDB200_SAGE_FAST_MEANS; no counterpart in the reference,
+    whose mean is sage_channel_mean above): the token axis is cut into chunks of 128 rows; inside a
+    chunk groups of 16 rows are added into four running sums (row i of a group into sum i % 4), rows
+    left over after the last whole group into sum 0, the chunk sum is (s0 + s1) + (s2 + s3); the chunk
+    sums are then added in chunk order and divided by L.  Every operation rounded to f32."""
+    f = np.float32
+    HN, L, d = x.shape
+    total = np.zeros((HN, d), dtype=f)
+    for c0 in range(0, L, 128):
+        blk = x[:, c0:min(L, c0 + 128), :].astype(f)
+        n = blk.shape[1]
+        s = [np.zeros((HN, d), dtype=f) for _ in range(4)]
+        whole = n // 16 * 16
+        for t in range(whole):
+            s[t & 3] = (s[t & 3] + blk[:, t, :]).astype(f)
+        for t in range(whole, n):
+            s[0] = (s[0] + blk[:, t, :]).astype(f)
+        total = (total + ((s[0] + s[1]).astype(f) + (s[2] + s[3]).astype(f)).astype(f)).astype(f)
+    return (total / f(L)).astype(f)
+
+
+def sage_smooth_q_bias_fused(k: np.ndarray, qm: np.ndarray) -> np.ndarray:
+    """Model of the bias sum of this library's fused pre-pass kernel (same products as
+    sage_smooth_q_bias, another fixed order): per run of 8 channels ((p0+p1)+(p2+p3))+((p4+p5)+(p6+p7)),
+    then a pairwise tree over the d/8 runs."""
+    f = np.float32
+    HN, L, d = k.shape
+    p = (k.astype(f) * qm[:, None, :]).astype(f).reshape(HN, L, d // 8, 8)
+    a = ((p[..., 0] + p[..., 1]).astype(f) + (p[..., 2] + p[..., 3]).astype(f)).astype(f)
+    b = ((p[..., 4] + p[..., 5]).astype(f) + (p[..., 6] + p[..., 7]).astype(f)).astype(f)
+    v = (a + b).astype(f)                      # [HN, L, d/8]
+    while v.shape[-1] > 1:
+        v = (v[..., 0::2] + v[..., 1::2]).astype(f)
+    return v[..., 0]
 
 
 def _sage_quant(x: np.ndarray, mean: np.ndarray | None, blk: int):

@@ -136,7 +136,9 @@ def flux_timing_weights(cfg: FluxConfig, seed: int = 0, std: float = 0.02, prefi
 class FluxOracle:
     def __init__(self, cfg: FluxConfig, weights: dict):
         self.cfg = cfg
-        self.w = {k: O.dequantize(v, t) if t != O.GGML_TYPE_F32 else v for k, (t, v) in weights.items()}
+        # a dict {name: (ggml_type, array)} is dequantised up front; anything else is taken as a
+        # mapping name -> f32 array that fetches on use (oracle.weights: device read-back, aliased blocks)
+        self.w = O.resolve_weights(weights)
 
     def lin(self, name, x):
         return O.linear(x, self.w[name + ".weight"], self.w.get(name + ".bias"))

@@ -48,19 +48,28 @@ class QwenConfig:
 
 
 def qwen_tensor_specs(cfg: QwenConfig):
-    """Ordered (name, shape, quantised?).  Every 2-D weight whose row length is a multiple of
-    256 is quantised (tensor_should_be_converted, src/core/runtime/model_loader.cpp:2141-2172);
-    img_in (row length 64), biases and norm weights stay f32."""
+    """Ordered (name, shape, ggml type).  Every 2-D weight whose row length is a multiple of the
+    block size is stored in cfg.wtype, except what tensor_should_be_converted excludes by name
+    (src/core/runtime/model_loader.cpp:2141-2172): `img_in.` and `txt_in.` (and biases, norm
+    weights) stay f32.  The modulation projections img_mod.1 / txt_mod.1 are floored at q8_0: a
+    block type with fewer bits per weight (q4_K) is lifted to q8_0 (set_wtype_override,
+    model_loader.cpp:1746-1761)."""
     H, M = cfg.hidden_size, cfg.mlp_hidden
     specs = []
+    F32 = O.GGML_TYPE_F32
 
     def lin(name, n_out, n_in):
-        specs.append((name + ".weight", (n_out, n_in), n_in % 256 == 0))
-        specs.append((name + ".bias", (n_out,), False))
+        t = cfg.wtype if n_in % 256 == 0 else F32
+        if name.startswith("img_in") or name.startswith("txt_in"):
+            t = F32
+        if (name.endswith("img_mod.1") or name.endswith("txt_mod.1")) and t == O.GGML_TYPE_Q4_K:
+            t = O.GGML_TYPE_Q8_0
+        specs.append((name + ".weight", (n_out, n_in), t))
+        specs.append((name + ".bias", (n_out,), F32))
 
     lin("time_text_embed.timestep_embedder.linear_1", H, 256)
     lin("time_text_embed.timestep_embedder.linear_2", H, H)
-    specs.append(("txt_norm.weight", (cfg.joint_attention_dim,), False))
+    specs.append(("txt_norm.weight", (cfg.joint_attention_dim,), F32))
     lin("img_in", H, cfg.in_channels)
     lin("txt_in", H, cfg.joint_attention_dim)
     for i in range(cfg.num_layers):
@@ -70,7 +79,7 @@ def qwen_tensor_specs(cfg: QwenConfig):
         for l in ("to_q", "to_k", "to_v", "add_q_proj", "add_k_proj", "add_v_proj", "to_out.0", "to_add_out"):
             lin(p + "attn." + l, H, H)
         for n in ("norm_q", "norm_k", "norm_added_q", "norm_added_k"):
-            specs.append((p + f"attn.{n}.weight", (cfg.attention_head_dim,), False))
+            specs.append((p + f"attn.{n}.weight", (cfg.attention_head_dim,), F32))
         for s in ("img_mlp", "txt_mlp"):
             lin(p + s + ".net.0.proj", M, H)
             lin(p + s + ".net.2", H, M)
@@ -81,12 +90,12 @@ def qwen_tensor_specs(cfg: QwenConfig):
 
 def qwen_make_weights(cfg: QwenConfig, seed: int = 0, std: float = 0.02):
     out = {}
-    for name, shape, quant in qwen_tensor_specs(cfg):
+    for name, shape, t in qwen_tensor_specs(cfg):
         rng = np.random.Generator(np.random.Philox(_name_seed(seed, name)))
         w = (rng.standard_normal(shape, dtype=np.float32) * np.float32(std)).astype(np.float32)
         if name.endswith("txt_norm.weight") or ".attn.norm_" in name:
             w = (w + np.float32(1.0)).astype(np.float32)
-        out[name] = (cfg.wtype, O.quantize(w, cfg.wtype)) if quant else (O.GGML_TYPE_F32, w)
+        out[name] = (t, O.quantize(w, t)) if t != O.GGML_TYPE_F32 else (O.GGML_TYPE_F32, w)
     return out
 
 
@@ -105,7 +114,9 @@ def qwen_ids(h_tok: int, w_tok: int, context_len: int) -> np.ndarray:
 class QwenOracle:
     def __init__(self, cfg: QwenConfig, weights: dict):
         self.cfg = cfg
-        self.w = {k: O.dequantize(v, t) if t != O.GGML_TYPE_F32 else v for k, (t, v) in weights.items()}
+        # a dict {name: (ggml_type, array)} is dequantised up front; anything else is taken as a
+        # mapping name -> f32 array that fetches on use (oracle.weights: device read-back, aliased blocks)
+        self.w = O.resolve_weights(weights)
 
     def lin(self, name, x):
         return O.linear(x, self.w[name + ".weight"], self.w.get(name + ".bias"))

@@ -103,7 +103,9 @@ def unpatchify_channel_fastest(t: np.ndarray, h: int, w: int, p: int) -> np.ndar
 class SD3Oracle:
     def __init__(self, cfg: SD3Config, weights: dict):
         self.cfg = cfg
-        self.w = {k: O.dequantize(v, t) if t != O.GGML_TYPE_F32 else v for k, (t, v) in weights.items()}
+        # a dict {name: (ggml_type, array)} is dequantised up front; anything else is taken as a
+        # mapping name -> f32 array that fetches on use (oracle.weights: device read-back, aliased blocks)
+        self.w = O.resolve_weights(weights)
         self.n_blocks = 1 + max(int(k.split(".")[1]) for k in weights if k.startswith("joint_blocks."))
 
     def lin(self, name, x):

@@ -137,7 +137,9 @@ def unpatchify_3d(tokens: np.ndarray, t_len: int, h_len: int, w_len: int, patch,
 class WanOracle:
     def __init__(self, cfg: WanConfig, weights: dict):
         self.cfg = cfg
-        self.w = {k: O.dequantize(v, t) if t != O.GGML_TYPE_F32 else v for k, (t, v) in weights.items()}
+        # a dict {name: (ggml_type, array)} is dequantised up front; anything else is taken as a
+        # mapping name -> f32 array that fetches on use (oracle.weights: device read-back, aliased blocks)
+        self.w = O.resolve_weights(weights)
 
     def lin(self, name, x):
         return O.linear(x, self.w[name + ".weight"], self.w.get(name + ".bias"))
