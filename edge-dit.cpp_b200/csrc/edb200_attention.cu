@@ -144,13 +144,12 @@ __device__ __forceinline__ float magic_i2f_biased(uint32_t s, int one) {
     return __int_as_float(r);
 }
 
-// Half a score row (64 columns, raw tensor-memory words) -> maximum of the scaled
-// scores.  MASKED: only the first `valid` columns are real keys.
-// With a smooth-Q bias the words are replaced by the f32 scores
-// v = s * (q_scale * k_scale) + bias (softmax scale not yet applied: `cq` is c0 / sl2),
-// so that the second sweep only needs one multiply-add per score.
+// Half a score row (64 columns, raw tensor-memory words) -> maximum of the scaled scores (log2
+// domain).  MASKED: only the first `valid` columns are real keys.  The words are not changed.
+// Only the first half of a row, a ragged last half and halves whose scores outgrow the running
+// maximum take this sweep (see the softmax loop).
 template <bool SAGE, bool MASKED>
-__device__ __forceinline__ float half_row_max(uint32_t (&rr)[64], float c0, float cq, const float4* bias, float sl2,
+__device__ __forceinline__ float half_row_max(const uint32_t (&rr)[64], float c0, float cq, const float4* bias, float sl2,
                                               int valid, int one) {
     if (SAGE && bias == nullptr) {
         int mi[4] = {INT_MIN, INT_MIN, INT_MIN, INT_MIN};
@@ -174,10 +173,6 @@ __device__ __forceinline__ float half_row_max(uint32_t (&rr)[64], float c0, floa
             add2(f2, f3, f2, f3, -kMagicFloat, -kMagicFloat);
             fma2(f0, f1, f0, f1, cq, cq, b.x, b.y);
             fma2(f2, f3, f2, f3, cq, cq, b.z, b.w);
-            rr[4 * i + 0] = __float_as_uint(f0);
-            rr[4 * i + 1] = __float_as_uint(f1);
-            rr[4 * i + 2] = __float_as_uint(f2);
-            rr[4 * i + 3] = __float_as_uint(f3);
             if (MASKED) {
                 if (4 * i + 0 >= valid) f0 = -INFINITY;
                 if (4 * i + 1 >= valid) f1 = -INFINITY;
@@ -220,28 +215,40 @@ __device__ __forceinline__ void ex2_poly2(float e0, float e1, float& a, float& b
     b = __int_as_float(__float_as_int(p1) + (__float_as_int(r1) << 23));
 }
 
-constexpr int kPolyEvery = 4;   // one score pair in kPolyEvery takes the polynomial path
+// POLY: one score pair in POLY takes the polynomial path (0: none)
 
-// Half a score row -> P = exp2(score * c0 - m) as 32 packed f16 pairs; the pair
-// (sum0, sum1) accumulates the row sum.  RAW_INT: the words are s32 dot products,
-// otherwise f32 scores.  MASKED: columns >= valid are padding and get P = 0.
-template <bool RAW_INT, bool MASKED>
-__device__ __forceinline__ void half_row_exp(const uint32_t (&rr)[64], uint32_t (&p2)[32], float c0, float m, int valid,
-                                             float& sum0, float& sum1, int one) {
-    const float negm = -m;
+// Half a score row -> P = exp2(score - m) as 32 packed f16 pairs in ONE sweep over the raw words; the
+// pair (sum0, sum1) accumulates the row sum of this half.  MASKED: columns >= valid are padding and get
+// P = 0.  MODE 0: the words are f32 scores, exponent = s * c0 - m.  MODE 1: s32 dot products; with
+// f = 12582912 + s (the magic-number reinterpretation) the exponent is f * c0 + kr, kr = -(m + 12582912 * c0),
+// one multiply-add and no separate subtraction.  MODE 2: s32 dot products plus a per-key smooth-Q bias b
+// (shared memory, not yet scaled): exponent = f * c0 + (b * sl2 + kr).  Rounding kr (magnitude about
+// 12582912 * c0, a few thousand at most) costs below 1e-4 of absolute exponent error, under the f16
+// rounding of P.
+template <int MODE, bool MASKED, int POLY>
+__device__ __forceinline__ void half_row_exp(const uint32_t (&rr)[64], uint32_t (&p2)[32], float c0, float m,
+                                             const float4* bias, float sl2, int valid, float& sum0, float& sum1,
+                                             int one) {
+    const float kr = MODE == 0 ? -m : -fmaf(kMagicFloat, c0, m);
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
         float e0, e1;
-        if (RAW_INT) {
-            float f0 = magic_i2f_biased(rr[2 * i + 0], one);
-            float f1 = magic_i2f_biased(rr[2 * i + 1], one);
-            add2(f0, f1, f0, f1, -kMagicFloat, -kMagicFloat);
-            fma2(e0, e1, f0, f1, c0, c0, negm, negm);
+        if (MODE == 0) {
+            fma2(e0, e1, __uint_as_float(rr[2 * i]), __uint_as_float(rr[2 * i + 1]), c0, c0, kr, kr);
         } else {
-            fma2(e0, e1, __uint_as_float(rr[2 * i]), __uint_as_float(rr[2 * i + 1]), c0, c0, negm, negm);
+            const float f0 = magic_i2f_biased(rr[2 * i + 0], one);
+            const float f1 = magic_i2f_biased(rr[2 * i + 1], one);
+            if (MODE == 2) {
+                const float2 b = reinterpret_cast<const float2*>(bias)[i];   // same address in every lane
+                float t0, t1;
+                fma2(t0, t1, b.x, b.y, sl2, sl2, kr, kr);
+                fma2(e0, e1, f0, f1, c0, c0, t0, t1);
+            } else {
+                fma2(e0, e1, f0, f1, c0, c0, kr, kr);
+            }
         }
         float a, b;
-        if (i % kPolyEvery == kPolyEvery - 1) {
+        if (POLY > 0 && i % (POLY > 0 ? POLY : 1) == (POLY > 0 ? POLY : 1) - 1) {
             ex2_poly2(e0, e1, a, b);
         } else {
             a = ex2(e0);
@@ -256,7 +263,11 @@ __device__ __forceinline__ void half_row_exp(const uint32_t (&rr)[64], uint32_t 
     }
 }
 
-template <int D, bool SAGE>
+// A half whose row sum (against the running maximum the row already uses) stays below this needs no new
+// maximum: every P of it is below the limit too, far inside the f16 range.
+constexpr float kHalfSumLimit = 4096.0f;
+
+template <int D, bool SAGE, int POLY>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                  const __grid_constant__ CUtensorMap map_v, const __grid_constant__ Params P) {
@@ -477,51 +488,83 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             const float4* bias_h =
                 biased ? reinterpret_cast<const float4*>(smem + C::OFF_BIAS + (j % BIAS_STAGES) * (BKV * 4)) + 16 * hb
                        : nullptr;
-            const float mx = valid >= HK ? half_row_max<SAGE, false>(rr, c0, cq, bias_h, P.scale_log2, valid, P.one)
-                                         : half_row_max<SAGE, true>(rr, c0, cq, bias_h, P.scale_log2, valid, P.one);
-            // lazy rescale: keep exponentiating against the old maximum until it is stale by > 2^8
-            float alpha = 1.0f;
-            const bool grow = mx > m_used + kRescaleThreshold;
-            if (grow) {
-                alpha = ex2(m_used - mx);   // 0 on the very first half (m_used = -inf)
-                m_used = mx;
-                sum0 *= alpha;
-                sum1 *= alpha;
-            }
-            if (g > 0 && __any_sync(0xffffffffu, grow)) {
-                // O_t holds the PV products up to half g - 1; the next one waits for this thread's P.
-                // S(g) complete means the product of half g - 2 has completed, so pv_done is in
-                // phase g - 1 or g and the parity wait below cannot alias.
-                if (!mbar_wait(&pv_done[t], static_cast<uint32_t>((g - 1) & 1), abort_flag, P.err)) {
-                    ok = false;
-                    break;
-                }
-                tc_fence_after_sync();
-#pragma unroll
-                for (int c = 0; c < D / 32; ++c) {
-                    uint32_t oo[32];
-                    tmem_ld_cols<32>(o_addr + c * 32, oo);
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) oo[i] = __float_as_uint(__uint_as_float(oo[i]) * alpha);
-                    tmem_st_cols<32>(o_addr + c * 32, oo);
-                }
-            }
-            // P = exp2(score - m) as f16 pairs over the first 32 columns of the buffer just read
+            // P = exp2(score - m) as f16 pairs over the first 32 columns of the buffer just read.
+            // Fast path: one sweep against the maximum the row already uses (it may be stale: any maximum
+            // gives the same softmax as long as nothing overflows), accepted when the half's row sum shows
+            // that no score has outgrown it.  Otherwise, and for the first and a ragged last half: the
+            // maximum sweep, a rescale of what has been accumulated if the maximum moved by more than 2^8,
+            // and the exponentials again.
             uint32_t p2[32];
-            const float ce = biased ? P.scale_log2 : c0;
-            if (valid >= HK) {   // uniform; only the last key block can be ragged
-                if (SAGE && !biased) {
-                    half_row_exp<true, false>(rr, p2, ce, m_used, valid, sum0, sum1, P.one);
+            const bool ragged = valid < HK;          // uniform; only the last key block can be ragged
+            bool slow = g == 0 || ragged;
+            if (!slow) {
+                float h0 = 0.0f, h1 = 0.0f;
+                if (!SAGE) {
+                    half_row_exp<0, false, POLY>(rr, p2, c0, m_used, nullptr, P.scale_log2, valid, h0, h1, P.one);
+                } else if (biased) {
+                    half_row_exp<2, false, POLY>(rr, p2, c0, m_used, bias_h, P.scale_log2, valid, h0, h1, P.one);
                 } else {
-                    half_row_exp<false, false>(rr, p2, ce, m_used, valid, sum0, sum1, P.one);
+                    half_row_exp<1, false, POLY>(rr, p2, c0, m_used, nullptr, P.scale_log2, valid, h0, h1, P.one);
                 }
-            } else {
-                if (SAGE && !biased) {
-                    half_row_exp<true, true>(rr, p2, ce, m_used, valid, sum0, sum1, P.one);
+                const bool over = !(h0 + h1 <= kHalfSumLimit);   // also true for inf / NaN
+                if (__any_sync(0xffffffffu, over)) {
+                    slow = true;
                 } else {
-                    half_row_exp<false, true>(rr, p2, ce, m_used, valid, sum0, sum1, P.one);
+                    sum0 += h0;
+                    sum1 += h1;
                 }
+            }
+            if (slow) {
+                const float mx = ragged ? half_row_max<SAGE, true>(rr, c0, cq, bias_h, P.scale_log2, valid, P.one)
+                                        : half_row_max<SAGE, false>(rr, c0, cq, bias_h, P.scale_log2, valid, P.one);
+                // lazy rescale: keep exponentiating against the old maximum until it is stale by > 2^8
+                float alpha = 1.0f;
+                const bool grow = mx > m_used + kRescaleThreshold;
+                if (grow) {
+                    alpha = ex2(m_used - mx);   // 0 on the very first half (m_used = -inf)
+                    m_used = mx;
+                    sum0 *= alpha;
+                    sum1 *= alpha;
+                }
+                if (g > 0 && __any_sync(0xffffffffu, grow)) {
+                    // O_t holds the PV products up to half g - 1; the next one waits for this thread's P.
+                    // S(g) complete means the product of half g - 2 has completed, so pv_done is in
+                    // phase g - 1 or g and the parity wait below cannot alias.
+                    if (!mbar_wait(&pv_done[t], static_cast<uint32_t>((g - 1) & 1), abort_flag, P.err)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+#pragma unroll
+                    for (int c = 0; c < D / 32; ++c) {
+                        uint32_t oo[32];
+                        tmem_ld_cols<32>(o_addr + c * 32, oo);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) oo[i] = __float_as_uint(__uint_as_float(oo[i]) * alpha);
+                        tmem_st_cols<32>(o_addr + c * 32, oo);
+                    }
+                }
+                float h0 = 0.0f, h1 = 0.0f;
+                if (!ragged) {
+                    if (!SAGE) {
+                        half_row_exp<0, false, POLY>(rr, p2, c0, m_used, nullptr, P.scale_log2, valid, h0, h1, P.one);
+                    } else if (biased) {
+                        half_row_exp<2, false, POLY>(rr, p2, c0, m_used, bias_h, P.scale_log2, valid, h0, h1, P.one);
+                    } else {
+                        half_row_exp<1, false, POLY>(rr, p2, c0, m_used, nullptr, P.scale_log2, valid, h0, h1, P.one);
+                    }
+                } else {
+                    if (!SAGE) {
+                        half_row_exp<0, true, POLY>(rr, p2, c0, m_used, nullptr, P.scale_log2, valid, h0, h1, P.one);
+                    } else if (biased) {
+                        half_row_exp<2, true, POLY>(rr, p2, c0, m_used, bias_h, P.scale_log2, valid, h0, h1, P.one);
+                    } else {
+                        half_row_exp<1, true, POLY>(rr, p2, c0, m_used, nullptr, P.scale_log2, valid, h0, h1, P.one);
+                    }
+                }
+                sum0 += h0;
+                sum1 += h1;
             }
             if (g + 1 < n_half) {
                 // all of rr has been consumed; the other buffer holds the next half
@@ -600,8 +643,8 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     }
 }
 
-template <int D, bool SAGE>
-static edb200_status_t launch(const void* q, const void* k, const void* v, int64_t q_head_rows, int64_t k_head_rows,
+template <int D, bool SAGE, int POLY>
+static edb200_status_t launch_poly(const void* q, const void* k, const void* v, int64_t q_head_rows, int64_t k_head_rows,
                               int64_t v_head_rows, const Params& P_in, cudaStream_t stream) {
     using C = Cfg<D, SAGE>;
     Params P = P_in;
@@ -634,7 +677,7 @@ static edb200_status_t launch(const void* q, const void* k, const void* v, int64
     st = make_tmap_3d(&mv, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, v, D, P.Lk, P.HN, (uint64_t)D * 2,
                       (uint64_t)v_head_rows * D * 2, 64, BKV, 1, CU_TENSOR_MAP_SWIZZLE_128B);
     if (st != EDB200_OK) return st;
-    auto kern = attention_kernel<D, SAGE>;
+    auto kern = attention_kernel<D, SAGE, POLY>;
     static bool attr_set[64] = {false};   // the attribute is per device
     int dev = 0;
     cudaGetDevice(&dev);
@@ -649,6 +692,17 @@ static edb200_status_t launch(const void* q, const void* k, const void* v, int64
     kern<<<grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(mq, mk, mv, P);
     count_launch();
     return check_cuda(cudaGetLastError(), "attention launch");
+}
+
+// Share of the exponentials evaluated as a polynomial on the FMA pipe instead of the ex2 unit, per variant
+// (measured at 24 heads x 4608 and 5 heads x 75600 tokens, d 128): the f16 kernel is fastest with one
+// pair in eight (1148 / 1271 TFLOP/s against 1147 / 1199 with one in four and 1089 / 1196 with none), the
+// INT8 kernel, which already spends more FMA-pipe instructions per score, with none (930 / 1087 against
+// 917 / 1059 and 891 / 1025).
+template <int D, bool SAGE>
+static edb200_status_t launch(const void* q, const void* k, const void* v, int64_t q_head_rows, int64_t k_head_rows,
+                              int64_t v_head_rows, const Params& P_in, cudaStream_t stream) {
+    return launch_poly<D, SAGE, SAGE ? 0 : 8>(q, k, v, q_head_rows, k_head_rows, v_head_rows, P_in, stream);
 }
 
 }  // namespace attn

@@ -60,6 +60,28 @@ struct ProfScope {
     }
 };
 
+
+// Buffers of the Sage quantisation (int8 Q/K, their scales, channel means, smooth-Q bias, chunk sums of the
+// fast channel mean) and the strides of the scale / bias rows.
+struct SagePtrs {
+    int8_t* q8 = nullptr;
+    int8_t* k8 = nullptr;
+    float* q_scale = nullptr;
+    float* k_scale = nullptr;
+    float* qm = nullptr;
+    float* km = nullptr;
+    float* bias = nullptr;
+    float* part_q = nullptr;
+    float* part_k = nullptr;
+    int q_scale_stride = 0, k_scale_stride = 0, bias_stride = 0;
+};
+SagePtrs sage_ptrs_from_scratch(void* scratch, int hn, int64_t l, int d);
+// Quantise q and k ([hn, l, d] f16, heads head_rows rows apart) and, if `attend`, run the INT8-QK attention
+// with v ([hn, l, d] f16, heads v_head_rows rows apart).  smooth_q is the EDB200_SAGE_* bit set.
+edb200_status_t sage_run(const void* q_f16, const void* k_f16, const void* v_f16, int hn, int64_t l, int64_t head_rows,
+                         int64_t v_head_rows, int d_head, float scale, int smooth_q, const SagePtrs& sp, void* out,
+                         int out_dtype, int64_t ld_out, const edb200_sp_peers_t* dst, void* stream, bool attend);
+
 }  // namespace edb
 
 #define EDB_TRY(expr)                          \

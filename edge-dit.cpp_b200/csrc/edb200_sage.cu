@@ -43,34 +43,74 @@ channel_mean_kernel(const __half* __restrict__ x, float* __restrict__ mean, int 
 }
 
 // Fast (not bit-compatible) channel means: the token axis is cut into chunks of
-// kMeanChunk rows that are summed in parallel, then the chunk sums are added in
-// chunk order.  Deterministic, but the f32 rounding differs from the sequential
-// sum above, so the means can differ in the last bits.  Any vector subtracted
+// kMeanChunk rows that are summed in parallel (channel_partial_kernel), then the chunk
+// sums are added in chunk order.  Deterministic, but the f32 rounding differs from the
+// sequential sum above, so the means can differ in the last bits.  Any vector subtracted
 // from K cancels in the softmax, and the smooth-Q bias compensates the Q mean
 // exactly, so attention results are unaffected beyond rounding.
 constexpr int kMeanChunk = 128;
 
+// One CTA of 128 threads per (head, chunk, q|k).  Thread = (row group g, run of 8 channels): it adds rows
+// g, g + G, g + 2G, ... of the chunk (G = 128 / (D / 8) row groups) in that order into one f32 sum per
+// channel, with all of its 16-byte loads issued before the first add; the G sums of a channel are then
+// added as a pairwise tree ((s0 + s1) + (s2 + s3)) + ... in shared memory.
 template <int D>
-__global__ void __launch_bounds__(D)
+__global__ void __launch_bounds__(128)
 channel_partial_kernel(const __half* __restrict__ q, const __half* __restrict__ k, float* __restrict__ part_q,
                        float* __restrict__ part_k, int L, int n_chunks, int64_t head_rows) {
-    const int hn = blockIdx.x, chunk = blockIdx.y, d = threadIdx.x;
+    constexpr int CG = D / 8;            // channel runs per row
+    constexpr int G = 128 / CG;          // row groups
+    constexpr int RPT = kMeanChunk / G;  // rows per thread
+    __shared__ float sh[G][D];
+    const int hn = blockIdx.x, chunk = blockIdx.y;
     const __half* x = blockIdx.z == 0 ? k : q;
     float* part = blockIdx.z == 0 ? part_k : part_q;
+    const int g = threadIdx.x / CG, d0 = (threadIdx.x % CG) * 8;
     const int t0 = chunk * kMeanChunk;
-    const int t1 = min(L, t0 + kMeanChunk);
-    const __half* p = x + (int64_t)hn * head_rows * D + d;
-    float s[4] = {0.f, 0.f, 0.f, 0.f};
-    int t = t0;
-    for (; t + 16 <= t1; t += 16) {
-        float v[16];
+    const __half* p = x + ((int64_t)hn * head_rows + t0) * D + d0;
+    uint4 raw[RPT];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) v[i] = __half2float(p[(int64_t)(t + i) * D]);
-#pragma unroll
-        for (int i = 0; i < 16; ++i) s[i & 3] += v[i];
+    for (int i = 0; i < RPT; ++i) {
+        const int t = g + i * G;
+        raw[i] = make_uint4(0u, 0u, 0u, 0u);
+        if (t0 + t < L) {
+            // volatile: the compiler must not sink the loads to their uses, all of them are to be in flight at once
+            asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(raw[i].x), "=r"(raw[i].y), "=r"(raw[i].z), "=r"(raw[i].w)
+                         : "l"(p + (int64_t)t * D));
+        }
     }
-    for (; t < t1; ++t) s[0] += __half2float(p[(int64_t)t * D]);
-    part[((int64_t)hn * n_chunks + chunk) * D + d] = (s[0] + s[1]) + (s[2] + s[3]);
+    // every value passes an empty volatile statement placed after the last load: no add can be
+    // scheduled between the loads
+#pragma unroll
+    for (int i = 0; i < RPT; ++i) {
+        asm volatile("" : "+r"(raw[i].x), "+r"(raw[i].y), "+r"(raw[i].z), "+r"(raw[i].w));
+    }
+    float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < RPT; ++i) {
+        const uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[e]));
+            s[2 * e] = __fadd_rn(s[2 * e], f.x);
+            s[2 * e + 1] = __fadd_rn(s[2 * e + 1], f.y);
+        }
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) sh[g][d0 + e] = s[e];
+    __syncthreads();
+    for (int d = threadIdx.x; d < D; d += 128) {
+        float v[G];
+#pragma unroll
+        for (int i = 0; i < G; ++i) v[i] = sh[i][d];
+#pragma unroll
+        for (int m = 1; m < G; m <<= 1) {
+#pragma unroll
+            for (int i = 0; i < G; i += 2 * m) v[i] = __fadd_rn(v[i], v[i + m]);
+        }
+        part[((int64_t)hn * n_chunks + chunk) * D + d] = v[0];
+    }
 }
 
 template <int D>
@@ -393,21 +433,44 @@ static Layout make_layout(int hn, int64_t l, int d) {
     return lo;
 }
 
+}  // namespace sage
+
+// Where the pieces of the quantised operands live: one caller buffer cut up by make_layout, or the
+// separate buffers of the reference's plugin interface (ed_cuda_sage_attn_scratch).
+SagePtrs sage_ptrs_from_scratch(void* scratch, int hn, int64_t l, int d) {
+    const sage::Layout lo = sage::make_layout(hn, l, d);
+    char* sc = static_cast<char*>(scratch);
+    SagePtrs p;
+    p.q8 = reinterpret_cast<int8_t*>(sc + lo.q8);
+    p.k8 = reinterpret_cast<int8_t*>(sc + lo.k8);
+    p.q_scale = reinterpret_cast<float*>(sc + lo.q_scale);
+    p.k_scale = reinterpret_cast<float*>(sc + lo.k_scale);
+    p.qm = reinterpret_cast<float*>(sc + lo.qm);
+    p.km = reinterpret_cast<float*>(sc + lo.km);
+    p.bias = reinterpret_cast<float*>(sc + lo.bias);
+    p.part_q = reinterpret_cast<float*>(sc + lo.part_q);
+    p.part_k = reinterpret_cast<float*>(sc + lo.part_k);
+    p.q_scale_stride = lo.q_scale_stride;
+    p.k_scale_stride = lo.k_scale_stride;
+    p.bias_stride = lo.bias_stride;
+    return p;
+}
+
+namespace sage {
+
 template <int D>
 static edb200_status_t quantize(const __half* q, const __half* k, int hn, int l, int64_t head_rows, bool smooth_q,
-                                bool fast_means, char* scratch, const Layout& lo, cudaStream_t s) {
-    float* qm = reinterpret_cast<float*>(scratch + lo.qm);
-    float* km = reinterpret_cast<float*>(scratch + lo.km);
+                                bool fast_means, const SagePtrs& sp, cudaStream_t s) {
+    float* qm = sp.qm;
+    float* km = sp.km;
     // algorithmic traffic: read q,k (f16) for the means, again for the quantisers (the bit-compatible path reads k
     // once more for the bias); write int8
     ProfScope prof(s, PROF_ELEMENTWISE, 0.0, (double)hn * l * D * (fast_means ? 10.0 : (smooth_q ? 13.0 : 8.0)));
     int launches = 0;
     if (fast_means) {
-        float* pq = reinterpret_cast<float*>(scratch + lo.part_q);
-        float* pk = reinterpret_cast<float*>(scratch + lo.part_k);
         const int nc = (l + kMeanChunk - 1) / kMeanChunk;
-        channel_partial_kernel<D><<<dim3(hn, nc, smooth_q ? 2 : 1), D, 0, s>>>(q, k, pq, pk, l, nc, head_rows);
-        channel_finalize_kernel<D><<<dim3(hn, smooth_q ? 2 : 1), D, 0, s>>>(pq, pk, qm, km, l, nc);
+        channel_partial_kernel<D><<<dim3(hn, nc, smooth_q ? 2 : 1), 128, 0, s>>>(q, k, sp.part_q, sp.part_k, l, nc, head_rows);
+        channel_finalize_kernel<D><<<dim3(hn, smooth_q ? 2 : 1), D, 0, s>>>(sp.part_q, sp.part_k, qm, km, l, nc);
         launches += 2;
     } else {
         channel_mean_kernel<D><<<hn, D, 0, s>>>(k, km, l, head_rows);
@@ -417,31 +480,52 @@ static edb200_status_t quantize(const __half* q, const __half* k, int hn, int l,
     const int lpad = (l + 127) / 128 * 128;
     if (fast_means) {
         // the fast pre-pass: everything after the means in one launch (K and Q read once more, no memset)
-        fused_quant_kernel<D><<<dim3(lpad / kKBlock, hn), 128, 0, s>>>(
-            q, k, smooth_q ? qm : nullptr, km, reinterpret_cast<int8_t*>(scratch + lo.q8),
-            reinterpret_cast<int8_t*>(scratch + lo.k8), reinterpret_cast<float*>(scratch + lo.q_scale),
-            reinterpret_cast<float*>(scratch + lo.k_scale), reinterpret_cast<float*>(scratch + lo.bias), l,
-            lo.q_scale_stride, lo.k_scale_stride, lo.bias_stride, head_rows);
+        fused_quant_kernel<D><<<dim3(lpad / kKBlock, hn), 128, 0, s>>>(q, k, smooth_q ? qm : nullptr, km, sp.q8, sp.k8,
+                                                                       sp.q_scale, sp.k_scale, sp.bias, l,
+                                                                       sp.q_scale_stride, sp.k_scale_stride,
+                                                                       sp.bias_stride, head_rows);
         ++launches;
     } else {
-        quant_block_kernel<D, kQTile><<<dim3(lpad / kQTile, hn), 128, 0, s>>>(
-            q, smooth_q ? qm : nullptr, reinterpret_cast<int8_t*>(scratch + lo.q8),
-            reinterpret_cast<float*>(scratch + lo.q_scale), l, lo.q_scale_stride, head_rows);
-        quant_block_kernel<D, kKBlock><<<dim3(lpad / kKBlock, hn), 128, 0, s>>>(
-            k, km, reinterpret_cast<int8_t*>(scratch + lo.k8), reinterpret_cast<float*>(scratch + lo.k_scale), l,
-            lo.k_scale_stride, head_rows);
+        quant_block_kernel<D, kQTile><<<dim3(lpad / kQTile, hn), 128, 0, s>>>(q, smooth_q ? qm : nullptr, sp.q8, sp.q_scale,
+                                                                              l, sp.q_scale_stride, head_rows);
+        quant_block_kernel<D, kKBlock><<<dim3(lpad / kKBlock, hn), 128, 0, s>>>(k, km, sp.k8, sp.k_scale, l,
+                                                                                sp.k_scale_stride, head_rows);
         launches += 2;
         if (smooth_q) {
             // the padded tail of each bias row is read by the attention kernel: keep it finite
-            cudaMemsetAsync(scratch + lo.bias, 0, (size_t)hn * lo.bias_stride * 4, s);
-            smooth_q_bias_kernel<D><<<dim3((l + 255) / 256, hn), 256, 0, s>>>(
-                k, qm, reinterpret_cast<float*>(scratch + lo.bias), l, hn, lo.bias_stride, head_rows);
+            cudaMemsetAsync(sp.bias, 0, (size_t)hn * sp.bias_stride * 4, s);
+            smooth_q_bias_kernel<D><<<dim3((l + 255) / 256, hn), 256, 0, s>>>(k, qm, sp.bias, l, hn, sp.bias_stride,
+                                                                               head_rows);
             ++launches;
         }
     }
     count_launch(launches);
     return check_cuda(cudaGetLastError(), "sage quantize launch");
 }
+
+}  // namespace sage
+
+// Quantise + attend on separately placed buffers (shared by the scratch-buffer entry points and the
+// plugin entry point).
+edb200_status_t sage_run(const void* q_f16, const void* k_f16, const void* v_f16, int hn, int64_t l, int64_t head_rows,
+                         int64_t v_head_rows, int d_head, float scale, int smooth_q, const SagePtrs& sp, void* out,
+                         int out_dtype, int64_t ld_out, const edb200_sp_peers_t* dst, void* stream, bool attend) {
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    edb200_status_t st;
+    if (d_head == 128) {
+        st = sage::quantize<128>(static_cast<const __half*>(q_f16), static_cast<const __half*>(k_f16), hn,
+                                 static_cast<int>(l), head_rows, (smooth_q & 1) != 0, (smooth_q & 2) != 0, sp, s);
+    } else {
+        st = sage::quantize<64>(static_cast<const __half*>(q_f16), static_cast<const __half*>(k_f16), hn,
+                                static_cast<int>(l), head_rows, (smooth_q & 1) != 0, (smooth_q & 2) != 0, sp, s);
+    }
+    if (st != EDB200_OK || !attend) return st;
+    return edb200_attention_sage_int8_strided(sp.q8, sp.k8, v_f16, v_head_rows, sp.q_scale, sp.q_scale_stride, sp.k_scale,
+                                              sp.k_scale_stride, (smooth_q & 1) ? sp.bias : nullptr, sp.bias_stride, hn, l,
+                                              d_head, scale, out, out_dtype, ld_out, dst, stream);
+}
+
+namespace sage {
 
 // ---------------------------------------------------------------------------
 // Key-mean entry point without any caller- or library-side allocation: the chunk
@@ -474,7 +558,7 @@ template <int D>
 static edb200_status_t key_means_static(const __half* k, int hn, int l, float* part, float* mean_out, cudaStream_t s) {
     const int nc = (l + kMeanChunk - 1) / kMeanChunk;
     ProfScope prof(s, PROF_ELEMENTWISE, 0.0, (double)hn * l * D * 2.0);
-    channel_partial_kernel<D><<<dim3(hn, nc, 1), D, 0, s>>>(nullptr, k, nullptr, part, l, nc, l);
+    channel_partial_kernel<D><<<dim3(hn, nc, 1), 128, 0, s>>>(nullptr, k, nullptr, part, l, nc, l);
     channel_finalize_kernel<D><<<dim3(hn, 1), D, 0, s>>>(nullptr, part, nullptr, mean_out, l, nc);
     count_launch(2);
     return check_cuda(cudaGetLastError(), "sage key means launch");
@@ -484,7 +568,6 @@ static edb200_status_t key_means_static(const __half* k, int hn, int l, float* p
 }  // namespace edb
 
 using namespace edb;
-
 
 extern "C" {
 
@@ -529,15 +612,8 @@ edb200_status_t edb200_sage_quantize_qk_strided(const void* q_f16, const void* k
         return fail(EDB200_ERR_INVALID, "sage_quantize_qk: scratch must be 256-byte aligned and hold %lld bytes",
                     (long long)lo.total);
     }
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (d_head == 128) {
-        return sage::quantize<128>(static_cast<const __half*>(q_f16), static_cast<const __half*>(k_f16), hn,
-                                   static_cast<int>(l), head_rows, (smooth_q & 1) != 0, (smooth_q & 2) != 0,
-                                   static_cast<char*>(scratch), lo, s);
-    }
-    return sage::quantize<64>(static_cast<const __half*>(q_f16), static_cast<const __half*>(k_f16), hn,
-                              static_cast<int>(l), head_rows, (smooth_q & 1) != 0, (smooth_q & 2) != 0,
-                              static_cast<char*>(scratch), lo, s);
+    return sage_run(q_f16, k_f16, nullptr, hn, l, head_rows, head_rows, d_head, 0.0f, smooth_q,
+                    sage_ptrs_from_scratch(scratch, hn, l, d_head), nullptr, 0, 0, nullptr, stream, false);
 }
 
 edb200_status_t edb200_sage_attention(const void* q_f16, const void* k_f16, const void* v_f16, int hn, int64_t l,
@@ -563,16 +639,16 @@ edb200_status_t edb200_sage_attention_strided(const void* q_f16, const void* k_f
         return fail(EDB200_ERR_INVALID, "sage_attention: null argument");
     }
     if (d_head != 128 && d_head != 64) return fail(EDB200_ERR_UNSUPPORTED, "sage_attention: d_head must be 64 or 128");
-    edb200_status_t st = edb200_sage_quantize_qk_strided(q_f16, k_f16, hn, l, head_rows, d_head, smooth_q, scratch,
-                                                         scratch_bytes, stream);
-    if (st != EDB200_OK) return st;
+    if (q_f16 == nullptr || k_f16 == nullptr || scratch == nullptr || hn <= 0 || l <= 0 || head_rows < l) {
+        return fail(EDB200_ERR_INVALID, "sage_attention: null or empty argument");
+    }
     const sage::Layout lo = sage::make_layout(hn, l, d_head);
-    char* sc = static_cast<char*>(scratch);
-    return edb200_attention_sage_int8_strided(
-        sc + lo.q8, sc + lo.k8, v_f16, head_rows, reinterpret_cast<const float*>(sc + lo.q_scale), lo.q_scale_stride,
-        reinterpret_cast<const float*>(sc + lo.k_scale), lo.k_scale_stride,
-        (smooth_q & 1) ? reinterpret_cast<const float*>(sc + lo.bias) : nullptr, lo.bias_stride, hn, l, d_head, scale, out,
-        out_dtype, ld_out, dst, stream);
+    if (scratch_bytes < lo.total || (reinterpret_cast<uintptr_t>(scratch) & 255u)) {
+        return fail(EDB200_ERR_INVALID, "sage_attention: scratch must be 256-byte aligned and hold %lld bytes",
+                    (long long)lo.total);
+    }
+    return sage_run(q_f16, k_f16, v_f16, hn, l, head_rows, head_rows, d_head, scale, smooth_q,
+                    sage_ptrs_from_scratch(scratch, hn, l, d_head), out, out_dtype, ld_out, dst, stream, true);
 }
 
 edb200_status_t edb200_sage_key_means_static(const void* k_f16, int hn, int64_t l, int d_head, float* mean_out,

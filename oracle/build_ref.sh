@@ -14,6 +14,6 @@ if [ ! -f "$SRC/ed_ggml_modulation_ext.hpp" ]; then
     exit 0
 fi
 mkdir -p "$HERE/_ref"
-g++ -O2 -std=c++17 -fPIC -shared -ffp-contract=off -I "$HERE/ref_shim" -I "$SRC" -I "$REF/src" \
+g++ -O2 -std=c++17 -fPIC -shared -ffp-contract=off -I "$HERE/ref_shim" -I "$SRC" -I "$REF/src/core" -I "$REF/src" \
     "$HERE/ref_driver.cpp" "$HERE/ref_tensor_driver.cpp" -o "$HERE/_ref/libedref_cpu.so"
 echo "$HERE/_ref/libedref_cpu.so"

@@ -429,22 +429,25 @@ def sage_channel_mean(x: np.ndarray) -> np.ndarray:
 def sage_channel_mean_chunked(x: np.ndarray) -> np.ndarray:
     """Model of this library's fast channel mean (EDB200_SAGE_FAST_MEANS; no counterpart in the reference,
     whose mean is sage_channel_mean above): the token axis is cut into chunks of 128 rows; inside a
-    chunk groups of 16 rows are added into four running sums (row i of a group into sum i % 4), rows
-    left over after the last whole group into sum 0, the chunk sum is (s0 + s1) + (s2 + s3); the chunk
-    sums are then added in chunk order and divided by L.  Every operation rounded to f32."""
+    chunk the rows are dealt round-robin to G = 1024 / d row groups (8 for d = 128, 16 for d = 64), each
+    group is summed in row order, the G sums are added as a pairwise tree; the chunk sums are then added
+    in chunk order and divided by L.  Every operation rounded to f32."""
     f = np.float32
     HN, L, d = x.shape
+    G = 128 // (d // 8)
     total = np.zeros((HN, d), dtype=f)
     for c0 in range(0, L, 128):
         blk = x[:, c0:min(L, c0 + 128), :].astype(f)
         n = blk.shape[1]
-        s = [np.zeros((HN, d), dtype=f) for _ in range(4)]
-        whole = n // 16 * 16
-        for t in range(whole):
-            s[t & 3] = (s[t & 3] + blk[:, t, :]).astype(f)
-        for t in range(whole, n):
-            s[0] = (s[0] + blk[:, t, :]).astype(f)
-        total = (total + ((s[0] + s[1]).astype(f) + (s[2] + s[3]).astype(f)).astype(f)).astype(f)
+        s = np.zeros((G, HN, d), dtype=f)
+        for t in range(n):
+            s[t % G] = (s[t % G] + blk[:, t, :]).astype(f)
+        m = 1
+        while m < G:
+            for i in range(0, G, 2 * m):
+                s[i] = (s[i] + s[i + m]).astype(f)
+            m *= 2
+        total = (total + s[0]).astype(f)
     return (total / f(L)).astype(f)
 
 

@@ -4,9 +4,13 @@
 //   modulate / residual gate  src/core/backend/ggml/ed_ggml_modulation_ext.hpp:168-228
 //   rms_norm_mul_f16          src/core/backend/ggml/ed_ggml_norm_ext.hpp:223-263
 //   rope                      src/core/backend/ggml/ed_ggml_rope_ext.hpp:105-184
+//   attention layout glue     src/core/backend/ggml/ed_ggml_attention_ext.hpp:269-369
+//   GELU (bf16 out), concat-linear (+ gated residual)  src/core/backend/ggml/ed_ggml_sp_flux_ext.hpp:675-804
+#include "ed_ggml_attention_ext.hpp"
 #include "ed_ggml_modulation_ext.hpp"
 #include "ed_ggml_norm_ext.hpp"
 #include "ed_ggml_rope_ext.hpp"
+#include "ed_ggml_sp_flux_ext.hpp"
 
 namespace {
 
@@ -65,6 +69,56 @@ void ref_rope_interleaved(const float* x, const float* pe, float* out, int64_t s
     ggml_tensor dst = make(GGML_TYPE_F32, out, d, seq, heads, 1);
     dst.src[0] = &tx, dst.src[1] = &tp;
     rope_cpu_custom_op(&dst, 0, 1, rope_params_to_userdata(RopeInputLayout::NSeqHeadDim, true, d));
+}
+
+// Runs the reference CPU callback that a custom-op node describes: `dst` is a ggml_tensor (the structure of
+// include/edb200_ggml.h) in host memory whose op_params hold {callback, n_tasks, userdata} and whose src[]
+// point at host tensors.  The callback is chosen by the magic in userdata, as the reference's dispatch does.
+// Returns 0 when the magic is not one of the operators below.
+int ref_custom_op(ggml_tensor* dst) {
+    struct Params {
+        ggml_custom_op_t fun;
+        int n_tasks;
+        void* userdata;
+    } p;
+    std::memcpy(&p, dst->op_params, sizeof(p));
+    const uint32_t magic = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(p.userdata) & 0xffffffffu);
+    switch (magic) {
+        case kFusedModulateCustomMagic: fused_modulate_cpu_custom_op(dst, 0, 1, p.userdata); return 1;
+        case kFusedResidualGateCustomMagic: fused_residual_gate_cpu_custom_op(dst, 0, 1, p.userdata); return 1;
+        case kFusedWhereSelectCustomMagic: fused_where_select_cpu_custom_op(dst, 0, 1, p.userdata); return 1;
+        case kRmsNormMulF16CustomMagic: rms_norm_mul_f16_cpu_custom_op(dst, 0, 1, p.userdata); return 1;
+        case kRopeCustomMagic: rope_cpu_custom_op(dst, 0, 1, p.userdata); return 1;
+        case kAttentionVPrepCustomMagic: attention_v_prep_cpu_custom_op(dst, 0, 1, p.userdata); return 1;
+        case kAttentionPairPackCustomMagic: attention_pair_pack_cpu_custom_op(dst, 0, 1, p.userdata); return 1;
+        case kAttentionQKVPairPackCustomMagic: attention_qkv_pair_pack_cpu_custom_op(dst, 0, 1, p.userdata); return 1;
+        case kFluxSPGeluBF16CustomMagic: flux_sp_gelu_bf16_cpu_custom_op(dst, 0, 1, p.userdata); return 1;
+        case kFluxSPConcatLinearCustomMagic: flux_sp_concat_linear_cpu_custom_op(dst, 0, 1, p.userdata); return 1;
+        case kFluxSPConcatLinearResidualGateCustomMagic:
+            flux_sp_concat_linear_residual_gate_cpu_custom_op(dst, 0, 1, p.userdata);
+            return 1;
+        default: return 0;
+    }
+}
+
+// The userdata words the reference's graph builders attach to these operators.
+uint64_t ref_userdata(int which, int64_t a, int64_t b, int64_t c, float f) {
+    void* u = nullptr;
+    switch (which) {
+        case 0: u = fused_modulate_params_to_userdata(); break;
+        case 1: u = fused_residual_gate_params_to_userdata(); break;
+        case 2: u = fused_where_select_params_to_userdata(); break;
+        case 3: u = rms_norm_mul_f16_params_to_userdata(f); break;
+        case 4: u = rope_params_to_userdata(static_cast<RopeInputLayout>(a), b != 0, c); break;
+        case 5: u = attention_v_prep_params_to_userdata(a != 0); break;
+        case 6: u = attention_pair_pack_params_to_userdata(a); break;
+        case 7: u = attention_qkv_pair_pack_params_to_userdata(a); break;
+        case 8: u = flux_sp_gelu_bf16_params_to_userdata(); break;
+        case 9: u = flux_sp_concat_linear_params_to_userdata(); break;
+        case 10: u = flux_sp_concat_linear_residual_gate_params_to_userdata(); break;
+        default: break;
+    }
+    return static_cast<uint64_t>(reinterpret_cast<uintptr_t>(u));
 }
 
 }  // extern "C"

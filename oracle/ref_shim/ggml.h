@@ -11,10 +11,8 @@
 #include <cstdlib>
 #include <cstring>
 
-#define GGML_MAX_DIMS 4
-#define GGML_MAX_SRC 10
-#define GGML_MAX_OP_PARAMS 64
-#define GGML_N_TASKS_MAX (-1)
+/* the tensor structure, type ids and operation kinds are the ones the library's plugin entry points use */
+#include "../../include/edb200_ggml.h"
 
 #define GGML_ASSERT(x)                                                                  \
     do {                                                                                \
@@ -24,32 +22,12 @@
         }                                                                               \
     } while (0)
 
-enum ggml_type {
-    GGML_TYPE_F32 = 0,
-    GGML_TYPE_F16 = 1,
-    GGML_TYPE_Q8_0 = 8,
-    GGML_TYPE_Q4_K = 12,
-    GGML_TYPE_I8 = 24,
-    GGML_TYPE_BF16 = 30,
-};
-
 typedef uint16_t ggml_fp16_t;
 typedef struct {
     uint16_t bits;
 } ggml_bf16_t;
 
-struct ggml_tensor {
-    enum ggml_type type;
-    int64_t ne[GGML_MAX_DIMS];
-    size_t nb[GGML_MAX_DIMS];
-    int32_t op_params[GGML_MAX_OP_PARAMS / sizeof(int32_t)];
-    struct ggml_tensor* src[GGML_MAX_SRC];
-    void* data;
-    char name[64];
-};
-
 struct ggml_context;
-typedef void (*ggml_custom_op_t)(struct ggml_tensor* dst, int ith, int nth, void* userdata);
 
 static inline size_t ggml_type_size(enum ggml_type t) {
     switch (t) {
@@ -70,6 +48,15 @@ static inline bool ggml_is_contiguous(const struct ggml_tensor* t) {
         expect *= (size_t)t->ne[i];
     }
     return true;
+}
+
+static inline bool ggml_are_same_shape(const struct ggml_tensor* a, const struct ggml_tensor* b) {
+    return a->ne[0] == b->ne[0] && a->ne[1] == b->ne[1] && a->ne[2] == b->ne[2] && a->ne[3] == b->ne[3];
+}
+
+/* rows (dimension 0) are dense; the rows themselves may be strided */
+static inline bool ggml_is_contiguous_rows(const struct ggml_tensor* t) {
+    return t->ne[0] == 1 || t->nb[0] == ggml_type_size(t->type);
 }
 
 static inline float ggml_fp16_to_fp32(ggml_fp16_t h) {
