@@ -173,9 +173,23 @@ __global__ void fused_residual_gate_kernel(const float4* __restrict__ res, const
 __global__ void advance_step_kernel(int* step) { *step += 1; }
 
 // SD3's form of the sampler update (sd3_pipeline.cpp:697): x += model_out * (sigma_next - sigma).
-__global__ void flow_update_kernel(float* __restrict__ x, const float* __restrict__ v, float dt, int64_t n) {
+// `sched` != NULL: dt = sched[*step + 1] - sched[*step], read on the device.
+__global__ void flow_update_kernel(float* __restrict__ x, const float* __restrict__ v, float dt,
+                                   const float* __restrict__ sched, const int* __restrict__ step, int64_t n) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) x[i] = __fadd_rn(x[i], __fmul_rn(v[i], dt));
+    if (i >= n) return;
+    if (sched != nullptr) {
+        const int k = *step;
+        dt = __fsub_rn(sched[k + 1], sched[k]);
+    }
+    x[i] = __fadd_rn(x[i], __fmul_rn(v[i], dt));
+}
+
+__global__ void sub_kernel(const float4* __restrict__ a, const float4* __restrict__ b, float4* __restrict__ out, int64_t n4) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n4) return;
+    const float4 x = a[i], y = b[i];
+    out[i] = make_float4(__fsub_rn(x.x, y.x), __fsub_rn(x.y, y.y), __fsub_rn(x.z, y.z), __fsub_rn(x.w, y.w));
 }
 
 // Sampler update of one step (flux_pipeline.cpp:1290-1297): every operation rounded on its own.
@@ -394,9 +408,32 @@ edb200_status_t edb200_flow_update(float* x, const float* model_out, float sigma
                                    void* stream) {
     if (x == nullptr || model_out == nullptr || n <= 0) return fail(EDB200_ERR_INVALID, "flow_update: null or empty argument");
     flow_update_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        x, model_out, sigma_next - sigma, n);
+        x, model_out, sigma_next - sigma, nullptr, nullptr, n);
     count_launch();
     return check_cuda(cudaGetLastError(), "flow_update launch");
+}
+
+edb200_status_t edb200_flow_update_sched(float* x, const float* model_out, const float* sigmas, int* step, int64_t n,
+                                         void* stream) {
+    if (x == nullptr || model_out == nullptr || sigmas == nullptr || step == nullptr || n <= 0) {
+        return fail(EDB200_ERR_INVALID, "flow_update_sched: null or empty argument");
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    flow_update_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, s>>>(x, model_out, 0.0f, sigmas, step, n);
+    count_launch();
+    advance_step_kernel<<<1, 1, 0, s>>>(step);   // after every thread above has read the old value (stream order)
+    count_launch();
+    return check_cuda(cudaGetLastError(), "flow_update_sched launch");
+}
+
+edb200_status_t edb200_sub_f32(const float* a, const float* b, float* out, int64_t n, void* stream) {
+    if (a == nullptr || b == nullptr || out == nullptr || n <= 0 || n % 4) {
+        return fail(EDB200_ERR_INVALID, "sub_f32: bad argument (n %% 4 == 0 required)");
+    }
+    sub_kernel<<<static_cast<unsigned>((n / 4 + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const float4*>(a), reinterpret_cast<const float4*>(b), reinterpret_cast<float4*>(out), n / 4);
+    count_launch();
+    return check_cuda(cudaGetLastError(), "sub_f32 launch");
 }
 
 edb200_status_t edb200_euler_update_sched(float* x, const float* model_out, const float* sigmas, int* step, int64_t n,

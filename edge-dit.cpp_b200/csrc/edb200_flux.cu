@@ -53,6 +53,12 @@ struct edb200_flux {
     uint64_t mod_batch_gen = 0;
     edb200_sp_peers_t mods_peers;
     float* tap = nullptr;
+    // computation-reuse seam: captures of the image stream at the anchors, probe stop, whole-stack inject
+    float* anchor_in = nullptr;
+    float* anchor_out = nullptr;
+    std::vector<float*> anchor_block;   // [depth], NULL = not captured
+    int stop_after = -1;
+    const float* stream_override = nullptr;
     // host staging for compute_host
     float* pinned = nullptr;
     int64_t pinned_bytes = 0;
@@ -538,6 +544,35 @@ edb200_status_t edb200_flux_set_comm(edb200_flux_t* m, edb200_comm_t* comm) {
     return EDB200_OK;
 }
 
+edb200_status_t edb200_flux_set_anchor_capture(edb200_flux_t* m, int anchor, float* dst) {
+    if (m == nullptr) return fail(EDB200_ERR_INVALID, "flux_set_anchor_capture: null model");
+    if (anchor == EDB200_ANCHOR_MODEL_IN) {
+        m->anchor_in = dst;
+    } else if (anchor == EDB200_ANCHOR_MODEL_OUT) {
+        m->anchor_out = dst;
+    } else if (anchor >= 0 && anchor < m->cfg.depth) {
+        m->anchor_block.resize(m->cfg.depth, nullptr);
+        m->anchor_block[anchor] = dst;
+    } else {
+        return fail(EDB200_ERR_INVALID, "flux_set_anchor_capture: anchor %d (block outputs are 0..%d)", anchor, m->cfg.depth - 1);
+    }
+    return EDB200_OK;
+}
+
+edb200_status_t edb200_flux_set_stop_after(edb200_flux_t* m, int block) {
+    if (m == nullptr || block < -1 || block >= m->cfg.depth) {
+        return fail(EDB200_ERR_INVALID, "flux_set_stop_after: block must be -1 (off) or a double block index");
+    }
+    m->stop_after = block;
+    return EDB200_OK;
+}
+
+edb200_status_t edb200_flux_set_stream_override(edb200_flux_t* m, const float* residual) {
+    if (m == nullptr) return fail(EDB200_ERR_INVALID, "flux_set_stream_override: null model");
+    m->stream_override = residual;
+    return EDB200_OK;
+}
+
 edb200_status_t edb200_flux_set_tap(edb200_flux_t* m, float* tap) {
     if (m == nullptr) return fail(EDB200_ERR_INVALID, "flux_set_tap: null model");
     m->tap = tap;
@@ -583,7 +618,7 @@ static edb200_status_t flux_step_body(edb200_flux_t* m, const float* latent, flo
                       X_txt, H, s));
     }
     if (sched != nullptr) {
-        launch_timestep_embedding_sched(m->FREQ, sched, sched_step, 1000.0f, 128, m->TEMB, s);
+        launch_timestep_embedding_sched(m->FREQ, sched, sched_step, 1.0f, 1000.0f, 128, m->TEMB, s);
     } else {
         launch_timestep_embedding(m->FREQ, timestep, 1000.0f, 128, m->TEMB, s);
     }
@@ -599,6 +634,13 @@ static edb200_status_t flux_step_body(edb200_flux_t* m, const float* latent, flo
     EDB_TRY(dense(m, "vector_in.out_layer", m->TMP_H, 1, H, 0, EDB200_ACT_NONE, m->TMP_H + H, H, s));
     launch_add_inplace(m->VEC, m->TMP_H + H, H, s);
 
+    // ---- reuse seam (Flux::forward_orig, flux.hpp:3968-3978): the block stack transforms the image stream;
+    // ModelIn is that stream before the stack
+    if (m->anchor_in != nullptr && n_img > 0) {
+        cudaMemcpyAsync(m->anchor_in, X_img, n_img * H * 4, cudaMemcpyDeviceToDevice, s);
+    }
+    const bool whole_inject = m->stream_override != nullptr;
+
     // ---- every adaLN vector of the step: lin(silu(vec)), weight streaming, one launch for all of them
     // (sequence-parallel ranks with peer memory each stream 1/N of the weights and store to all)
     float* mods = m->MODS;
@@ -609,8 +651,8 @@ static edb200_status_t flux_step_body(edb200_flux_t* m, const float* latent, flo
     float* fmods = smods + (int64_t)c.depth_single_blocks * 3 * H;
     EDB_TRY(dense(m, "final_layer.adaLN_modulation.1", m->VEC, 1, H, 1, EDB200_ACT_NONE, fmods, 2 * H, s));
 
-    // ---- double-stream blocks
-    for (int i = 0; i < c.depth; ++i) {
+    // ---- double-stream blocks (none of them under a whole-stack inject, flux.hpp:4511-4515)
+    for (int i = 0; i < (whole_inject ? 0 : c.depth); ++i) {
         const std::string p = "double_blocks." + std::to_string(i) + ".";
         const float* im = mods + (int64_t)i * 12 * H;   // shift1 scale1 gate1 shift2 scale2 gate2
         const float* tm = im + 6 * H;
@@ -656,10 +698,15 @@ static edb200_status_t flux_step_body(edb200_flux_t* m, const float* latent, flo
         if (m->tap) {
             cudaMemcpyAsync(m->tap + (int64_t)i * TL * H, m->X, TL * H * 4, cudaMemcpyDeviceToDevice, s);
         }
+        // BlockOut[i]: the image stream after double block i, and the probe stop (flux.hpp:4260-4266)
+        if (i < (int)m->anchor_block.size() && m->anchor_block[i] != nullptr && n_img > 0) {
+            cudaMemcpyAsync(m->anchor_block[i], X_img, n_img * H * 4, cudaMemcpyDeviceToDevice, s);
+        }
+        if (m->stop_after == i) return check_cuda(cudaGetLastError(), "flux_step");
     }
 
     // ---- single-stream blocks over [txt ; img]
-    for (int i = 0; i < c.depth_single_blocks; ++i) {
+    for (int i = 0; i < (whole_inject ? 0 : c.depth_single_blocks); ++i) {
         const std::string p = "single_blocks." + std::to_string(i) + ".";
         const float* sm = smods + (int64_t)i * 3 * H;   // shift scale gate
         EDB_TRY(ln_mod(m->X, H, sm, sm + H, TL, xmod, F16, s));
@@ -684,6 +731,14 @@ static edb200_status_t flux_step_body(edb200_flux_t* m, const float* latent, flo
         if (m->tap) {
             cudaMemcpyAsync(m->tap + (int64_t)(c.depth + i) * TL * H, m->X, TL * H * 4, cudaMemcpyDeviceToDevice, s);
         }
+    }
+
+    // whole-stack inject: the loops ran zero blocks; the stream after the stack is rebuilt as
+    // x_before + residual (build_stream_override, flux.hpp:4511-4515)
+    if (whole_inject && n_img > 0) launch_add_inplace(X_img, m->stream_override, n_img * H, s);
+    // ModelOut: the image stream after the stack, before the final layer (flux.hpp:4516-4520)
+    if (m->anchor_out != nullptr && n_img > 0) {
+        cudaMemcpyAsync(m->anchor_out, X_img, n_img * H * 4, cudaMemcpyDeviceToDevice, s);
     }
 
     // ---- final layer on the image rows + unpatchify (LastLayer::forward, flux.hpp:3533-3559)

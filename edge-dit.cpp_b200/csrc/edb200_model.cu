@@ -53,11 +53,11 @@ __global__ void unpatchify_kernel(const float* __restrict__ t, float* __restrict
 // `sched` != NULL: the timestep is sched[*step], read on the device (a recorded step then follows a
 // schedule without being re-recorded).
 __global__ void timestep_embedding_kernel(const float* __restrict__ freq, float t, const float* __restrict__ sched,
-                                          const int* __restrict__ step, float scale, int half,
+                                          const int* __restrict__ step, float pre_scale, float scale, int half,
                                           float* __restrict__ out) {
     const int j = blockIdx.x * blockDim.x + threadIdx.x;
     if (j >= half) return;
-    if (sched != nullptr) t = sched[*step];
+    if (sched != nullptr) t = __fmul_rn(sched[*step], pre_scale);   // the f32 product a host caller would pass
     const float arg = __fmul_rn(__fmul_rn(t, freq[j]), scale);
     out[j] = cosf(arg);
     out[half + j] = sinf(arg);
@@ -138,13 +138,13 @@ void launch_unpatchify(const float* tokens, float* latent, int C, int H, int W, 
 }
 
 void launch_timestep_embedding(const float* freq, float t, float scale, int half, float* out, cudaStream_t s) {
-    timestep_embedding_kernel<<<(half + 127) / 128, 128, 0, s>>>(freq, t, nullptr, nullptr, scale, half, out);
+    timestep_embedding_kernel<<<(half + 127) / 128, 128, 0, s>>>(freq, t, nullptr, nullptr, 1.0f, scale, half, out);
     count_launch();
 }
 
-void launch_timestep_embedding_sched(const float* freq, const float* sched, const int* step, float scale, int half,
-                                     float* out, cudaStream_t s) {
-    timestep_embedding_kernel<<<(half + 127) / 128, 128, 0, s>>>(freq, 0.0f, sched, step, scale, half, out);
+void launch_timestep_embedding_sched(const float* freq, const float* sched, const int* step, float pre_scale, float scale,
+                                     int half, float* out, cudaStream_t s) {
+    timestep_embedding_kernel<<<(half + 127) / 128, 128, 0, s>>>(freq, 0.0f, sched, step, pre_scale, scale, half, out);
     count_launch();
 }
 

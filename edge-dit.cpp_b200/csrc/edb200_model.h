@@ -88,8 +88,9 @@ void launch_patchify(const float* latent, float* tokens, int C, int H, int W, in
 void launch_unpatchify(const float* tokens, float* latent, int C, int H, int W, int p, cudaStream_t s);
 // out[j] = cos((t*freq[j])*scale), out[half+j] = sin(...); freq is a device table of `half` floats.
 void launch_timestep_embedding(const float* freq, float t, float scale, int half, float* out, cudaStream_t s);
-void launch_timestep_embedding_sched(const float* freq, const float* sched, const int* step, float scale, int half,
-                                     float* out, cudaStream_t s);
+// The same with the timestep read on the device: t = sched[*step] * pre_scale.
+void launch_timestep_embedding_sched(const float* freq, const float* sched, const int* step, float pre_scale, float scale,
+                                     int half, float* out, cudaStream_t s);
 void launch_add_inplace(float* dst, const float* src, int64_t n, cudaStream_t s);
 // Device q4_K encoder used for synthetic weights (min/max per 32 sub-block).
 edb200_status_t quantize_rows_q4_k_device(const float* x, void* blocks, int64_t rows, int64_t k, cudaStream_t s);

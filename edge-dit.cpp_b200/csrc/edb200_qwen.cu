@@ -512,8 +512,8 @@ edb200_status_t edb200_qwen_prepare(edb200_qwen_t* m, int lat_h, int lat_w, int 
     return EDB200_OK;
 }
 
-edb200_status_t edb200_qwen_step(edb200_qwen_t* m, const float* latent, float timestep, const float* context, float* out,
-                                 void* stream) {
+static edb200_status_t qwen_step_body(edb200_qwen_t* m, const float* latent, float timestep, const float* sched,
+                                      const int* sched_step, float t_scale, const float* context, float* out, void* stream) {
     if (m == nullptr || latent == nullptr || context == nullptr || out == nullptr) {
         return fail(EDB200_ERR_INVALID, "qwen_step: null argument");
     }
@@ -559,7 +559,11 @@ edb200_status_t edb200_qwen_step(edb200_qwen_t* m, const float* latent, float ti
                                   static_cast<const float*>(m->CTXN), n_txt, c.joint_attention_dim, H,
                                   c.joint_attention_dim, 0, EDB200_ACT_NONE, X_txt, H, s));
     }
-    launch_timestep_embedding(m->FREQ, timestep, 1.0f, 128, m->TEMB, s);
+    if (sched != nullptr) {
+        launch_timestep_embedding_sched(m->FREQ, sched, sched_step, t_scale, 1.0f, 128, m->TEMB, s);
+    } else {
+        launch_timestep_embedding(m->FREQ, timestep, 1.0f, 128, m->TEMB, s);
+    }
     {
         const Lin l1 = qlin(m, "time_text_embed.timestep_embedder.linear_1");
         const Lin l2 = qlin(m, "time_text_embed.timestep_embedder.linear_2");
@@ -654,6 +658,17 @@ edb200_status_t edb200_qwen_step(edb200_qwen_t* m, const float* latent, float ti
     }
     launch_unpatchify(m->TOK_OUT, out, c.out_channels, m->lat_h, m->lat_w, p, s);
     return check_cuda(cudaGetLastError(), "qwen_step");
+}
+
+edb200_status_t edb200_qwen_step(edb200_qwen_t* m, const float* latent, float timestep, const float* context, float* out,
+                                 void* stream) {
+    return qwen_step_body(m, latent, timestep, nullptr, nullptr, 1.0f, context, out, stream);
+}
+
+edb200_status_t edb200_qwen_step_sched(edb200_qwen_t* m, const float* latent, const float* sigmas, const int* step, float t_scale,
+                                       const float* context, float* out, void* stream) {
+    if (sigmas == nullptr || step == nullptr) return fail(EDB200_ERR_INVALID, "qwen_step_sched: null schedule");
+    return qwen_step_body(m, latent, 0.0f, sigmas, step, t_scale, context, out, stream);
 }
 
 edb200_status_t edb200_qwen_compute_host(edb200_qwen_t* m, const float* latent, int lat_h, int lat_w, float timestep,

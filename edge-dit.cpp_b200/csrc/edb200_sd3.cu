@@ -548,8 +548,9 @@ edb200_status_t edb200_sd3_prepare(edb200_sd3_t* m, int lat_h, int lat_w, int n_
     return EDB200_OK;
 }
 
-edb200_status_t edb200_sd3_step(edb200_sd3_t* m, const float* latent, float timestep, const float* context,
-                                const float* y, float* out, void* stream) {
+static edb200_status_t sd3_step_body(edb200_sd3_t* m, const float* latent, float timestep, const float* sched,
+                                     const int* sched_step, float t_scale, const float* context, const float* y, float* out,
+                                     void* stream) {
     if (m == nullptr || latent == nullptr || context == nullptr || y == nullptr || out == nullptr) {
         return fail(EDB200_ERR_INVALID, "sd3_step: null argument");
     }
@@ -587,7 +588,11 @@ edb200_status_t edb200_sd3_step(edb200_sd3_t* m, const float* latent, float time
             X_img, fparam(m, "pos_embed"), static_cast<int>(H), w_tok, c.pos_embed_max_size, top, left, m->img_first, total);
         count_launch();
     }
-    launch_timestep_embedding(m->FREQ, timestep, 1.0f, 128, m->TEMB, s);
+    if (sched != nullptr) {
+        launch_timestep_embedding_sched(m->FREQ, sched, sched_step, t_scale, 1.0f, 128, m->TEMB, s);
+    } else {
+        launch_timestep_embedding(m->FREQ, timestep, 1.0f, 128, m->TEMB, s);
+    }
     EDB_TRY(dense(m, "t_embedder.mlp.0", m->TEMB, 1, 256, EDB200_ACT_SILU, m->TMP, H, s));
     EDB_TRY(dense(m, "t_embedder.mlp.2", m->TMP, 1, H, EDB200_ACT_NONE, m->CVEC, H, s));
     EDB_TRY(dense(m, "y_embedder.mlp.0", y, 1, c.adm_in_channels, EDB200_ACT_SILU, m->TMP, H, s));
@@ -700,6 +705,17 @@ edb200_status_t edb200_sd3_step(edb200_sd3_t* m, const float* latent, float time
         count_launch();
     }
     return check_cuda(cudaGetLastError(), "sd3_step");
+}
+
+edb200_status_t edb200_sd3_step(edb200_sd3_t* m, const float* latent, float timestep, const float* context,
+                                const float* y, float* out, void* stream) {
+    return sd3_step_body(m, latent, timestep, nullptr, nullptr, 1.0f, context, y, out, stream);
+}
+
+edb200_status_t edb200_sd3_step_sched(edb200_sd3_t* m, const float* latent, const float* sigmas, const int* step, float t_scale,
+                                      const float* context, const float* y, float* out, void* stream) {
+    if (sigmas == nullptr || step == nullptr) return fail(EDB200_ERR_INVALID, "sd3_step_sched: null schedule");
+    return sd3_step_body(m, latent, 0.0f, sigmas, step, t_scale, context, y, out, stream);
 }
 
 edb200_status_t edb200_sd3_compute_host(edb200_sd3_t* m, const float* latent, int lat_h, int lat_w, float timestep,

@@ -504,8 +504,8 @@ edb200_status_t edb200_wan_prepare(edb200_wan_t* m, int frames, int lat_h, int l
     return EDB200_OK;
 }
 
-edb200_status_t edb200_wan_step(edb200_wan_t* m, const float* latent, float timestep, const float* context, float* out,
-                                void* stream) {
+static edb200_status_t wan_step_body(edb200_wan_t* m, const float* latent, float timestep, const float* sched,
+                                     const int* sched_step, float t_scale, const float* context, float* out, void* stream) {
     if (m == nullptr || latent == nullptr || context == nullptr || out == nullptr) {
         return fail(EDB200_ERR_INVALID, "wan_step: null argument");
     }
@@ -535,7 +535,11 @@ edb200_status_t edb200_wan_step(edb200_wan_t* m, const float* latent, float time
         count_launch();
     }
     EDB_TRY(dense(m, "patch_embedding", m->TOK_IN + first * pf_in, TL, pf_in, 0, EDB200_ACT_NONE, m->X, D, s));
-    launch_timestep_embedding(m->FREQ, timestep, 1.0f, 128, m->TEMB, s);
+    if (sched != nullptr) {
+        launch_timestep_embedding_sched(m->FREQ, sched, sched_step, t_scale, 1.0f, 128, m->TEMB, s);
+    } else {
+        launch_timestep_embedding(m->FREQ, timestep, 1.0f, 128, m->TEMB, s);
+    }
     EDB_TRY(dense(m, "time_embedding.0", m->TEMB, 1, 256, 0, EDB200_ACT_SILU, m->TMP, D, s));
     EDB_TRY(dense(m, "time_embedding.2", m->TMP, 1, D, 0, EDB200_ACT_NONE, m->E, D, s));
     {
@@ -661,6 +665,17 @@ edb200_status_t edb200_wan_step(edb200_wan_t* m, const float* latent, float time
         count_launch();
     }
     return check_cuda(cudaGetLastError(), "wan_step");
+}
+
+edb200_status_t edb200_wan_step(edb200_wan_t* m, const float* latent, float timestep, const float* context, float* out,
+                                void* stream) {
+    return wan_step_body(m, latent, timestep, nullptr, nullptr, 1.0f, context, out, stream);
+}
+
+edb200_status_t edb200_wan_step_sched(edb200_wan_t* m, const float* latent, const float* sigmas, const int* step, float t_scale,
+                                      const float* context, float* out, void* stream) {
+    if (sigmas == nullptr || step == nullptr) return fail(EDB200_ERR_INVALID, "wan_step_sched: null schedule");
+    return wan_step_body(m, latent, 0.0f, sigmas, step, t_scale, context, out, stream);
 }
 
 edb200_status_t edb200_wan_compute_host(edb200_wan_t* m, const float* latent, int frames, int lat_h, int lat_w,

@@ -72,6 +72,7 @@ class FluxConfig(C.Structure):
 
 
 ATTN_F16, ATTN_SAGE_INT8 = 0, 1
+ANCHOR_MODEL_IN, ANCHOR_MODEL_OUT = -1, -2
 
 
 class EdbError(RuntimeError):
@@ -111,6 +112,14 @@ _SIGS = {
     "edb200_euler_update": (C.c_int, [c_vp, c_vp, C.c_float, C.c_float, c_i64, c_vp]),
     "edb200_euler_update_sched": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_i64, c_vp]),
     "edb200_flow_update": (C.c_int, [c_vp, c_vp, C.c_float, C.c_float, c_i64, c_vp]),
+    "edb200_flow_update_sched": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_i64, c_vp]),
+    "edb200_sub_f32": (C.c_int, [c_vp, c_vp, c_vp, c_i64, c_vp]),
+    "edb200_flux_set_anchor_capture": (C.c_int, [c_vp, C.c_int, c_vp]),
+    "edb200_flux_set_stop_after": (C.c_int, [c_vp, C.c_int]),
+    "edb200_flux_set_stream_override": (C.c_int, [c_vp, c_vp]),
+    "edb200_sd3_step_sched": (C.c_int, [c_vp, c_vp, c_vp, c_vp, C.c_float, c_vp, c_vp, c_vp, c_vp]),
+    "edb200_qwen_step_sched": (C.c_int, [c_vp, c_vp, c_vp, c_vp, C.c_float, c_vp, c_vp, c_vp]),
+    "edb200_wan_step_sched": (C.c_int, [c_vp, c_vp, c_vp, c_vp, C.c_float, c_vp, c_vp, c_vp]),
     "edb200_qk_norm_rope_pack": (C.c_int, [c_vp, C.c_int, c_i64, c_i64, c_i64, c_i64, c_i64, C.c_int, C.c_int,
                                            c_vp, c_vp, C.c_float, c_vp, c_i64, c_i64, c_vp, c_vp, c_vp, C.c_int,
                                            c_vp]),

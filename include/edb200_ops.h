@@ -249,6 +249,13 @@ EDB200_API edb200_status_t edb200_euler_update(float* x, const float* model_out,
  * x += model_out * (sigma_next - sigma), f32, the difference, the product and the sum each rounded. */
 EDB200_API edb200_status_t edb200_flow_update(float* x, const float* model_out, float sigma, float sigma_next, int64_t n,
                                    void* stream);
+/* SD3's update with the schedule on the device: dt = sigmas[*step + 1] - sigmas[*step], then *step is
+ * incremented (see edb200_euler_update_sched). */
+EDB200_API edb200_status_t edb200_flow_update_sched(float* x, const float* model_out, const float* sigmas, int* step,
+                                                    int64_t n, void* stream);
+/* out = a - b, f32, n a multiple of 4 (e.g. the block stack's residual ModelOut - ModelIn that a reuse policy
+ * stores, src/core/optimization/cache/tensor_cache_utils.hpp). */
+EDB200_API edb200_status_t edb200_sub_f32(const float* a, const float* b, float* out, int64_t n, void* stream);
 /* The same update with the schedule on the device: sigma = sigmas[*step], sigma_next =
  * sigmas[*step + 1]; afterwards *step is incremented (a second, one-thread kernel).  Together with
  * edb200_flux_step_sched this makes one recorded step + update (edb200_graph_*) replayable for
@@ -611,6 +618,20 @@ EDB200_API edb200_status_t edb200_flux_prepare(edb200_flux_t* m, int latent_h, i
 /* Optional debug tap: after block b (double blocks first) the f32 residual
  * stream [n_txt + n_img, hidden] is copied to tap + b * T * hidden.  NULL disables. */
 EDB200_API edb200_status_t edb200_flux_set_tap(edb200_flux_t* m, float* tap);
+/* Computation-reuse seam: the three anchors the reference's cache engine taps in the FLUX graph
+ * (src/dit_models/models/flux.hpp:3968-3978 ModelIn, :4260-4266 BlockOut[i] with the probe stop,
+ * :4511-4520 whole-stack inject and ModelOut).  All of them are views of the IMAGE stream
+ * [image tokens (of this rank), hidden] f32.
+ *   set_anchor_capture  during the following steps the stream at `anchor` is copied to dst (device);
+ *                       anchor = EDB200_ANCHOR_MODEL_IN / _MODEL_OUT or a double-block index; NULL stops it
+ *   set_stop_after      the step returns right after double block `block` (its BlockOut capture made,
+ *                       `out` untouched): the probe pass of a policy that decides from an early block; -1 = off
+ *   set_stream_override the step runs no block at all: the stream after the stack is ModelIn + residual
+ *                       (device, same shape), then the final layer as usual; NULL = off */
+enum { EDB200_ANCHOR_MODEL_IN = -1, EDB200_ANCHOR_MODEL_OUT = -2 };
+EDB200_API edb200_status_t edb200_flux_set_anchor_capture(edb200_flux_t* m, int anchor, float* dst);
+EDB200_API edb200_status_t edb200_flux_set_stop_after(edb200_flux_t* m, int block);
+EDB200_API edb200_status_t edb200_flux_set_stream_override(edb200_flux_t* m, const float* residual);
 /* One denoise step on device-resident tensors, asynchronous on `stream`:
  * latent/out f32 [C, H, W]; context f32 [n_txt, context_in_dim]; y f32 [vec_in_dim];
  * timestep and guidance as the reference passes them (sigma in 0..1, guidance scale). */
@@ -696,6 +717,12 @@ EDB200_API edb200_status_t edb200_sd3_set_comm(edb200_sd3_t* m, edb200_comm_t* c
 /* latent f32 [in_channels, lat_h, lat_w], context f32 [n_ctx, context_size], y f32 [adm_in_channels]. */
 EDB200_API edb200_status_t edb200_sd3_step(edb200_sd3_t* m, const float* latent, float timestep, const float* context,
                                            const float* y, float* out, void* stream);
+/* The same pass with the timestep read on the device: timestep = sigmas[*step] * t_scale (the pipelines pass
+ * sigma * 1000).  With edb200_flow_update_sched and edb200_cfg_combine, one recorded (conditional pass,
+ * unconditional pass, combine, update) replays for every step of a schedule. */
+EDB200_API edb200_status_t edb200_sd3_step_sched(edb200_sd3_t* m, const float* latent, const float* sigmas, const int* step,
+                                                 float t_scale, const float* context, const float* y, float* out,
+                                                 void* stream);
 EDB200_API edb200_status_t edb200_sd3_compute_host(edb200_sd3_t* m, const float* latent, int lat_h, int lat_w,
                                                    float timestep, const float* context, int n_ctx, const float* y,
                                                    float* out, void* stream);
@@ -767,6 +794,10 @@ EDB200_API edb200_status_t edb200_qwen_set_comm(edb200_qwen_t* m, edb200_comm_t*
 /* latent f32 [in_channels / patch^2, lat_h, lat_w], context f32 [n_txt, joint_attention_dim]. */
 EDB200_API edb200_status_t edb200_qwen_step(edb200_qwen_t* m, const float* latent, float timestep, const float* context,
                                             float* out, void* stream);
+/* The same pass with the timestep read on the device: timestep = sigmas[*step] * t_scale. */
+EDB200_API edb200_status_t edb200_qwen_step_sched(edb200_qwen_t* m, const float* latent, const float* sigmas,
+                                                  const int* step, float t_scale, const float* context, float* out,
+                                                  void* stream);
 EDB200_API edb200_status_t edb200_qwen_compute_host(edb200_qwen_t* m, const float* latent, int lat_h, int lat_w,
                                                     float timestep, const float* context, int n_txt, float* out,
                                                     void* stream);
@@ -833,6 +864,9 @@ EDB200_API edb200_status_t edb200_wan_set_comm(edb200_wan_t* m, edb200_comm_t* c
  * [n_ctx, text_dim], out f32 like latent. */
 EDB200_API edb200_status_t edb200_wan_step(edb200_wan_t* m, const float* latent, float timestep, const float* context,
                                            float* out, void* stream);
+/* The same step with the timestep read on the device: timestep = sigmas[*step] * t_scale. */
+EDB200_API edb200_status_t edb200_wan_step_sched(edb200_wan_t* m, const float* latent, const float* sigmas, const int* step,
+                                                 float t_scale, const float* context, float* out, void* stream);
 /* The same with host tensors (DiffusionModel::compute seam); synchronises. */
 EDB200_API edb200_status_t edb200_wan_compute_host(edb200_wan_t* m, const float* latent, int frames, int lat_h,
                                                    int lat_w, float timestep, const float* context, int n_ctx,

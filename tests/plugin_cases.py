@@ -70,7 +70,9 @@ class Node:
             strides = tuple(reversed(arr.strides)) if nb is None else nb
             for i in range(4):
                 t.ne[i] = shape[i]
-                t.nb[i] = strides[i] if i < len(strides) else t.nb[i - 1] * t.ne[i - 1]
+                # extent-1 dimensions get the dense stride, as ggml always sets it (numpy may report 0 there)
+                dense = SIZE_OF[gtype] if i == 0 else t.nb[i - 1] * t.ne[i - 1]
+                t.nb[i] = strides[i] if i < len(strides) and shape[i] != 1 else dense
             t.data = ptr_of(arr)
             keep.append(t)
             return t

@@ -176,3 +176,57 @@ def test_flux_denoise_loop_stays_on_the_device(edb, cuda):
         model.denoise_graph(g_lat, sigmas, d_ctx, d_y, 3.5)
     torch.cuda.synchronize()
     assert torch.equal(g_lat, d_lat)
+
+
+def test_flux_reuse_anchors_capture_probe_and_inject(edb, cuda):
+    """The computation-reuse seam (flux.hpp:3968-3978, 4260-4266, 4511-4520): ModelIn / BlockOut[i] / ModelOut
+    captures equal the image rows of the residual stream at those points; the probe stop returns after
+    the chosen double block without touching the output; a step with the stored residual injected runs
+    no block and reproduces the full step's output."""
+    lib = edb.lib()
+    model = edb.FluxModel(hidden_size=512, num_heads=4, depth=2, depth_single_blocks=2, context_in_dim=256, vec_in_dim=64)
+    model.init_random(seed=2, std=0.05)
+    n_txt, H = 24, 512
+    model.prepare(32, 32, n_txt)
+    n_img, T = 256, 256 + n_txt
+    g = torch.Generator(device="cpu").manual_seed(3)
+    lat, ctx, y = torch.randn(16, 32, 32, generator=g).to(cuda), torch.randn(n_txt, 256, generator=g).to(cuda), \
+        torch.randn(64, generator=g).to(cuda)
+    tap = torch.zeros(4, T, H, device=cuda)
+    a_in, a_b0, a_out = (torch.zeros(n_img, H, device=cuda) for _ in range(3))
+    edb.check(lib.edb200_flux_set_tap(model.handle, edb.ptr(tap)))
+    edb.check(lib.edb200_flux_set_anchor_capture(model.handle, edb.ANCHOR_MODEL_IN, edb.ptr(a_in)))
+    edb.check(lib.edb200_flux_set_anchor_capture(model.handle, 0, edb.ptr(a_b0)))
+    edb.check(lib.edb200_flux_set_anchor_capture(model.handle, edb.ANCHOR_MODEL_OUT, edb.ptr(a_out)))
+    full = torch.empty_like(lat)
+    model.step(lat, 0.5, ctx, y, 3.5, full)
+    torch.cuda.synchronize()
+    assert torch.equal(a_b0, tap[0, n_txt:]) and torch.equal(a_out, tap[3, n_txt:])
+    assert torch.isfinite(a_in).all() and not torch.equal(a_in, a_out)
+    assert lib.edb200_flux_set_anchor_capture(model.handle, 2, None) == 1          # only double blocks are anchors
+    # probe: stop after double block 0
+    launches = lib.edb200_launch_count()
+    edb.check(lib.edb200_flux_set_stop_after(model.handle, 0))
+    probe_out = torch.full_like(lat, float("nan"))
+    a_b0.zero_()
+    model.step(lat, 0.5, ctx, y, 3.5, probe_out)
+    torch.cuda.synchronize()
+    probe_launches = lib.edb200_launch_count() - launches
+    assert torch.equal(a_b0, tap[0, n_txt:]) and torch.isnan(probe_out).all()
+    edb.check(lib.edb200_flux_set_stop_after(model.handle, -1))
+    # inject: residual = ModelOut - ModelIn, no block runs
+    residual = torch.empty_like(a_in)
+    edb.check(lib.edb200_sub_f32(edb.ptr(a_out), edb.ptr(a_in), edb.ptr(residual), residual.numel(), edb.current_stream()))
+    edb.check(lib.edb200_flux_set_stream_override(model.handle, edb.ptr(residual)))
+    launches = lib.edb200_launch_count()
+    reused = torch.empty_like(lat)
+    model.step(lat, 0.5, ctx, y, 3.5, reused)
+    torch.cuda.synchronize()
+    assert lib.edb200_launch_count() - launches < probe_launches                      # cheaper than one block
+    rel = float(torch.linalg.vector_norm(reused - full) / torch.linalg.vector_norm(full))
+    assert rel < 1e-5, rel                                                            # in + (out - in) rounds once more
+    edb.check(lib.edb200_flux_set_stream_override(model.handle, None))
+    again = torch.empty_like(lat)
+    model.step(lat, 0.5, ctx, y, 3.5, again)
+    torch.cuda.synchronize()
+    assert torch.equal(again, full)

@@ -86,3 +86,55 @@ def test_cfg_combine(edb, cuda):
     torch.cuda.synchronize()
     want = O.cfg_combine(u.cpu().numpy(), c.cpu().numpy(), 4.5)
     assert np.array_equal(out.cpu().numpy().view(np.uint32), want.view(np.uint32))   # the reference's bits
+
+
+def test_sd3_guided_sampler_loop_as_one_recorded_step(edb, cuda):
+    """SD3's sampler step with guidance - conditional pass, unconditional pass, combine, latent update
+    (sd3_pipeline.cpp:631-699) - recorded ONCE with the schedule and the step counter in device memory
+    and replayed for every step: the eager loop's bits."""
+    lib = edb.lib()
+    model = edb.SD3Model(hidden_size=512, num_heads=8, depth=2, adm_in_channels=64, context_size=128, pos_embed_max_size=16)
+    model.init_random(seed=4, std=0.05)
+    model.prepare(16, 24, 11)
+    g = torch.Generator(device="cpu").manual_seed(21)
+    x0 = torch.randn(16, 16, 24, generator=g).to(cuda)
+    ctx_c, ctx_u = torch.randn(11, 128, generator=g).to(cuda), torch.zeros(11, 128, device=cuda)
+    y_c, y_u = torch.randn(64, generator=g).to(cuda), torch.zeros(64, device=cuda)
+    sigmas = [1.0, 0.75, 0.4, 0.0]
+    cond, uncond, guided = (torch.empty_like(x0) for _ in range(3))
+    n = x0.numel()
+    # eager: sigma passed by value
+    x = x0.clone()
+    for s, s_next in zip(sigmas[:-1], sigmas[1:]):
+        t = float(np.float32(s) * np.float32(1000.0))
+        model.step(x, t, ctx_c, y_c, cond)
+        model.step(x, t, ctx_u, y_u, uncond)
+        edb.check(lib.edb200_cfg_combine(edb.ptr(uncond), edb.ptr(cond), 4.5, edb.ptr(guided), n, edb.current_stream()))
+        edb.check(lib.edb200_flow_update(edb.ptr(x), edb.ptr(guided), s, s_next, n, edb.current_stream()))
+    torch.cuda.synchronize()
+    # recorded once, replayed three times
+    sched = torch.tensor(sigmas, dtype=torch.float32, device=cuda)
+    step = torch.zeros(1, dtype=torch.int32, device=cuda)
+    xg = x0.clone()
+
+    def one():
+        edb.check(lib.edb200_sd3_step_sched(model.handle, edb.ptr(xg), edb.ptr(sched), edb.ptr(step), 1000.0, edb.ptr(ctx_c),
+                                            edb.ptr(y_c), edb.ptr(cond), edb.current_stream()))
+        edb.check(lib.edb200_sd3_step_sched(model.handle, edb.ptr(xg), edb.ptr(sched), edb.ptr(step), 1000.0, edb.ptr(ctx_u),
+                                            edb.ptr(y_u), edb.ptr(uncond), edb.current_stream()))
+        edb.check(lib.edb200_cfg_combine(edb.ptr(uncond), edb.ptr(cond), 4.5, edb.ptr(guided), n, edb.current_stream()))
+        edb.check(lib.edb200_flow_update_sched(edb.ptr(xg), edb.ptr(guided), edb.ptr(sched), edb.ptr(step), n,
+                                               edb.current_stream()))
+
+    side = torch.cuda.Stream(device=cuda)
+    with torch.cuda.stream(side):
+        one()                                  # warm on this stream
+        xg.copy_(x0)
+        step.zero_()
+        side.synchronize()
+        graph = edb.Graph(one)
+        for _ in range(3):
+            graph.launch()
+        side.synchronize()
+    assert int(step.item()) == 3
+    assert torch.equal(xg, x)

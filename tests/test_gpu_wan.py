@@ -89,3 +89,33 @@ def test_wan_rejects_bad_shapes(edb, cuda):
         model.prepare(2, 15, 16, 8)                    # latent not a multiple of the patch size
     with pytest.raises(edb.EdbError):
         edb.WanModel(dim=500, num_heads=4)             # width not a multiple of 256
+
+
+def test_wan_and_qwen_steps_follow_a_device_schedule(edb, cuda):
+    """edb200_{wan,qwen}_step_sched read the timestep from a schedule in device memory (sigma * 1000) and give
+    the bits of the by-value step."""
+    lib = edb.lib()
+    sched = torch.tensor([0.9, 0.35], dtype=torch.float32, device=cuda)
+    step = torch.ones(1, dtype=torch.int32, device=cuda)               # points at 0.35
+    t = float(np.float32(0.35) * np.float32(1000.0))
+    wan = edb.WanModel(dim=512, num_heads=4, ffn_dim=1024, num_layers=2, text_dim=128)
+    wan.init_random(seed=9, std=0.05)
+    wan.prepare(2, 16, 20, 24)
+    g = torch.Generator(device="cpu").manual_seed(12)
+    lat, ctx = torch.randn(16, 2, 16, 20, generator=g).to(cuda), torch.randn(24, 128, generator=g).to(cuda)
+    a, b = torch.empty_like(lat), torch.empty_like(lat)
+    wan.step(lat, t, ctx, a)
+    edb.check(lib.edb200_wan_step_sched(wan.handle, edb.ptr(lat), edb.ptr(sched), edb.ptr(step), 1000.0, edb.ptr(ctx),
+                                        edb.ptr(b), edb.current_stream()))
+    torch.cuda.synchronize()
+    assert torch.equal(a, b)
+    qwen = edb.QwenModel(num_layers=2, num_heads=4, joint_attention_dim=256)
+    qwen.init_random(seed=13, std=0.05)
+    qwen.prepare(24, 24, 16)
+    lat, ctx = torch.randn(16, 24, 24, generator=g).to(cuda), torch.randn(16, 256, generator=g).to(cuda)
+    a, b = torch.empty_like(lat), torch.empty_like(lat)
+    qwen.step(lat, t, ctx, a)
+    edb.check(lib.edb200_qwen_step_sched(qwen.handle, edb.ptr(lat), edb.ptr(sched), edb.ptr(step), 1000.0, edb.ptr(ctx),
+                                         edb.ptr(b), edb.current_stream()))
+    torch.cuda.synchronize()
+    assert torch.equal(a, b)
