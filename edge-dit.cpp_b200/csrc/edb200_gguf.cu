@@ -127,13 +127,11 @@ int64_t tensor_bytes(int ggml_type, int64_t n, int64_t k) {
 
 }  // namespace
 
-// Hands every tensor of the file that `table` knows (after removing `strip_prefix`, e.g.
-// "model.diffusion_model.", src/utils/name_conversion.cpp) to ParamTable::set.  Tensors of other
-// components (VAE, text encoders) are skipped; tensors the model needs and the file lacks are
-// reported by all_loaded() at the first step.  Quantised weights must already be stored in the
-// model's block type (what `ed-convert` wrote): nothing is requantised here.  f16 / bf16
-// vectors are widened to f32.
-edb200_status_t load_gguf(ParamTable& table, const char* path, const char* strip_prefix, cudaStream_t stream,
+// Hands every tensor of the file to the ingest stage, which keeps the ones `table` knows (after removing
+// `strip_prefix`, e.g. "model.diffusion_model.", and canonicalising the name for `family`).  Tensors of
+// other components (VAE, text encoders) are skipped; tensors the model needs and the file lacks are
+// reported by all_loaded() at the first step.
+edb200_status_t load_gguf(ParamTable& table, int family, const char* path, const char* strip_prefix, cudaStream_t stream,
                           int* n_loaded) {
     if (n_loaded) *n_loaded = 0;
     edb200_gguf_t* g = nullptr;
@@ -143,50 +141,20 @@ edb200_status_t load_gguf(ParamTable& table, const char* path, const char* strip
         edb200_gguf_t* g;
         ~Closer() { edb200_gguf_close(g); }
     } closer{g};
-    const size_t plen = strip_prefix ? strlen(strip_prefix) : 0;
-    std::vector<float> widened;
-    int count = 0;
-    for (size_t i = 0; i < g->tensors.size(); ++i) {
-        const auto& t = g->tensors[i];
-        std::string name = t.name;
-        if (plen && name.compare(0, plen, strip_prefix) == 0) name = name.substr(plen);
-        Param* p = table.find(name);
-        if (p == nullptr) continue;
-        int64_t n = 1;
-        for (int d = 0; d < t.n_dims; ++d) n *= t.dims[d];
-        if (n != p->spec.n_out * p->spec.k || (t.n_dims == 2 && t.dims[0] != p->spec.k)) {
-            return fail(EDB200_ERR_INVALID, "load_gguf: '%s' has %lld elements (row length %lld), the model expects %lld x %lld",
-                        t.name.c_str(), (long long)n, (long long)t.dims[0], (long long)p->spec.n_out, (long long)p->spec.k);
-        }
-        if (t.nbytes < 0) {
-            return fail(EDB200_ERR_UNSUPPORTED, "load_gguf: '%s' is stored as ggml type %d, which is not read here",
-                        t.name.c_str(), t.ggml_type);
-        }
-        const void* data = g->base + t.offset;
-        if (t.ggml_type == p->spec.ggml_type) {
-            st = table.set(name, t.ggml_type, data, t.nbytes, false, stream);
-        } else if (p->spec.ggml_type == EDB200_TYPE_F32 && (t.ggml_type == kGgufTypeF16 || t.ggml_type == kGgufTypeBF16)) {
-            widened.resize(static_cast<size_t>(n));
-            const uint16_t* src = static_cast<const uint16_t*>(data);
-            for (int64_t j = 0; j < n; ++j) {
-                if (t.ggml_type == kGgufTypeF16) {
-                    widened[static_cast<size_t>(j)] = __half2float(__ushort_as_half(src[j]));
-                } else {
-                    const uint32_t bits = static_cast<uint32_t>(src[j]) << 16;
-                    memcpy(&widened[static_cast<size_t>(j)], &bits, 4);
-                }
-            }
-            st = table.set(name, EDB200_TYPE_F32, widened.data(), n * 4, false, stream);
-        } else {
-            return fail(EDB200_ERR_UNSUPPORTED,
-                        "load_gguf: '%s' is stored as ggml type %d but the model expects type %d (convert the file first)",
-                        t.name.c_str(), t.ggml_type, p->spec.ggml_type);
-        }
+    Ingest ingest(table, family, strip_prefix, stream);
+    for (const auto& t : g->tensors) {
+        SourceTensor src;
+        src.name = t.name;
+        src.type = t.ggml_type;
+        src.n_elements = 1;
+        for (int d = 0; d < t.n_dims; ++d) src.n_elements *= t.dims[d];
+        src.row_len = t.n_dims == 2 ? t.dims[0] : 0;
+        src.data = g->base + t.offset;
+        src.nbytes = t.nbytes;
+        st = ingest.offer(src);
         if (st != EDB200_OK) return st;
-        ++count;
     }
-    if (n_loaded) *n_loaded = count;
-    return EDB200_OK;
+    return ingest.finish(n_loaded);
 }
 
 }  // namespace edb

@@ -58,13 +58,57 @@ private:
     uint64_t generation_ = 0;
 };
 
-// Loads every tensor of a GGUF file that `table` knows (edb200_gguf.cu).
-edb200_status_t load_gguf(ParamTable& table, const char* path, const char* strip_prefix, cudaStream_t stream,
+// One tensor of a checkpoint file as the readers see it.
+struct SourceTensor {
+    std::string name;
+    int type = 0;             // ggml type code (f32 0, f16 1, q8_0 8, q4_K 12, bf16 30)
+    int64_t n_elements = 0;
+    int64_t row_len = 0;      // innermost extent of a 2-D tensor, 0 otherwise
+    const void* data = nullptr;
+    int64_t nbytes = 0;       // < 0: a storage type this library does not read
+};
+
+// `name` in the layout the executors register, plus the part index of a fused tensor (edb200_ingest.cu).
+void canonical_name(int family, const std::string& name, std::string& out, int& part);
+
+// Takes the tensors of one or more files in any order and hands the ones `table` knows to it: names
+// canonicalised for the model family, parts of fused tensors assembled, storage types converted.
+class Ingest {
+public:
+    Ingest(ParamTable& table, int family, const char* strip_prefix, cudaStream_t stream);
+    edb200_status_t offer(const SourceTensor& t);
+    // Fails if a fused tensor was left incomplete; *n_loaded = parameters set.
+    edb200_status_t finish(int* n_loaded);
+
+private:
+    struct Part {
+        int type = 0;
+        int64_t n = 0;
+        std::vector<uint8_t> bytes;
+    };
+    struct Staged {
+        std::map<int, Part> parts;
+        int64_t elements = 0;
+    };
+    edb200_status_t set_from_f32(const std::string& name, Param* p, const float* src);
+    edb200_status_t assemble(const std::string& name, Param* p, Staged& s);
+
+    ParamTable& table_;
+    int family_;
+    std::string prefix_;
+    cudaStream_t stream_;
+    std::map<std::string, Staged> staged_;
+    std::vector<float> scratch_;
+    int count_ = 0;
+};
+
+// Loads every tensor of a GGUF file that `table` knows (edb200_gguf.cu); `family` is an EDB200_FAMILY_* code.
+edb200_status_t load_gguf(ParamTable& table, int family, const char* path, const char* strip_prefix, cudaStream_t stream,
                           int* n_loaded);
 
-// The same from a safetensors file; quantised parameters are encoded on the device (edb200_safetensors.cu).
-edb200_status_t load_safetensors(ParamTable& table, const char* path, const char* strip_prefix, cudaStream_t stream,
-                                 int* n_loaded);
+// The same from a safetensors file or a sharded checkpoint's index (edb200_safetensors.cu).
+edb200_status_t load_safetensors(ParamTable& table, int family, const char* path, const char* strip_prefix,
+                                 cudaStream_t stream, int* n_loaded);
 
 // One cudaMalloc carved into 256-byte aligned pieces.
 class Workspace {

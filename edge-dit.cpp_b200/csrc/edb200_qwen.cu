@@ -353,13 +353,13 @@ edb200_status_t edb200_qwen_get_tensor_f32(const edb200_qwen_t* m, const char* n
 edb200_status_t edb200_qwen_load_gguf(edb200_qwen_t* m, const char* path, const char* strip_prefix, int* n_loaded,
                                     void* stream) {
     if (m == nullptr || path == nullptr) return fail(EDB200_ERR_INVALID, "qwen_load_gguf: null argument");
-    return load_gguf(m->params, path, strip_prefix, static_cast<cudaStream_t>(stream), n_loaded);
+    return load_gguf(m->params, EDB200_FAMILY_QWEN, path, strip_prefix, static_cast<cudaStream_t>(stream), n_loaded);
 }
 
 edb200_status_t edb200_qwen_load_safetensors(edb200_qwen_t* m, const char* path, const char* strip_prefix, int* n_loaded,
                                            void* stream) {
     if (m == nullptr || path == nullptr) return fail(EDB200_ERR_INVALID, "qwen_load_safetensors: null argument");
-    return load_safetensors(m->params, path, strip_prefix, static_cast<cudaStream_t>(stream), n_loaded);
+    return load_safetensors(m->params, EDB200_FAMILY_QWEN, path, strip_prefix, static_cast<cudaStream_t>(stream), n_loaded);
 }
 
 edb200_status_t edb200_qwen_init_random(edb200_qwen_t* m, uint64_t seed, float std, void* stream) {

@@ -210,27 +210,8 @@ int dtype_bytes(const std::string& d) {
 
 }  // namespace
 
-// Hands every F32 / F16 / BF16 tensor of the file that `table` knows to it.  Parameters the model
-// keeps as f32 are widened on the host; parameters it keeps quantised are uploaded as f32 rows and
-// encoded on the device in the model's block type (q8_0: ggml's rule, bit for bit; q4_K: this
-// library's min/max encoder, the one init_random uses), then repacked like any other tensor.
-edb200_status_t load_safetensors(ParamTable& table, const char* path, const char* strip_prefix, cudaStream_t stream,
-                                 int* n_loaded) {
-    if (n_loaded) *n_loaded = 0;
-    if (is_index(path)) {   // a sharded checkpoint: every shard of the index in turn
-        std::vector<std::string> files;
-        edb200_status_t ist = index_shards(path, files);
-        if (ist != EDB200_OK) return ist;
-        int total = 0;
-        for (const auto& file : files) {
-            int n = 0;
-            ist = load_safetensors(table, file.c_str(), strip_prefix, stream, &n);
-            if (ist != EDB200_OK) return ist;
-            total += n;
-        }
-        if (n_loaded) *n_loaded = total;
-        return EDB200_OK;
-    }
+// Hands every F32 / F16 / BF16 tensor of one file to the ingest stage.
+static edb200_status_t offer_file(Ingest& ingest, const char* path) {
     edb200_safetensors_t* f = nullptr;
     edb200_status_t st = edb200_safetensors_open(path, &f);
     if (st != EDB200_OK) return st;
@@ -238,68 +219,50 @@ edb200_status_t load_safetensors(ParamTable& table, const char* path, const char
         edb200_safetensors_t* f;
         ~Closer() { edb200_safetensors_close(f); }
     } closer{f};
-    const size_t plen = strip_prefix ? strlen(strip_prefix) : 0;
-    std::vector<float> wide;
-    int count = 0;
     for (const auto& t : f->tensors) {
-        std::string name = t.name;
-        if (plen && name.compare(0, plen, strip_prefix) == 0) name = name.substr(plen);
-        Param* p = table.find(name);
-        if (p == nullptr) continue;
-        int64_t n = 1;
-        for (int d = 0; d < t.n_dims; ++d) n *= t.dims[d];
-        const int64_t rows = p->spec.n_out, k = p->spec.k;
-        if (n != rows * k || (t.n_dims == 2 && t.dims[1] != k)) {
-            return fail(EDB200_ERR_INVALID, "load_safetensors: '%s' has %lld elements, the model expects %lld x %lld",
-                        t.name.c_str(), (long long)n, (long long)rows, (long long)k);
-        }
-        const void* data = f->base + t.begin;
-        const float* src = nullptr;
+        SourceTensor src;
+        src.name = t.name;
+        src.n_elements = 1;
+        for (int d = 0; d < t.n_dims; ++d) src.n_elements *= t.dims[d];
+        src.row_len = t.n_dims == 2 ? t.dims[1] : 0;
+        src.data = f->base + t.begin;
+        src.nbytes = static_cast<int64_t>(t.end - t.begin);
         if (t.dtype == "F32") {
-            src = static_cast<const float*>(data);
-        } else if (t.dtype == "F16" || t.dtype == "BF16") {
-            wide.resize(static_cast<size_t>(n));
-            const uint16_t* h = static_cast<const uint16_t*>(data);
-            for (int64_t j = 0; j < n; ++j) {
-                if (t.dtype == "F16") {
-                    wide[static_cast<size_t>(j)] = __half2float(__ushort_as_half(h[j]));
-                } else {
-                    const uint32_t bits = static_cast<uint32_t>(h[j]) << 16;
-                    memcpy(&wide[static_cast<size_t>(j)], &bits, 4);
-                }
-            }
-            src = wide.data();
+            src.type = EDB200_TYPE_F32;
+        } else if (t.dtype == "F16") {
+            src.type = 1;
+        } else if (t.dtype == "BF16") {
+            src.type = 30;
         } else {
-            return fail(EDB200_ERR_UNSUPPORTED, "load_safetensors: '%s' has dtype %s (F32, F16 and BF16 are read)",
-                        t.name.c_str(), t.dtype.c_str());
+            src.type = -1;   // integer tables and the like: refused only if the model asks for the tensor
+            src.nbytes = -1;
         }
-        if (!p->spec.quantised) {
-            st = table.set(name, EDB200_TYPE_F32, src, n * 4, false, stream);
-        } else {
-            const int wt = p->spec.ggml_type;
-            const int64_t qbytes = rows * ggml_row_bytes(wt, k);
-            float* x_dev = nullptr;
-            void* q_dev = nullptr;
-            cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&x_dev), static_cast<size_t>(n) * 4);
-            if (e == cudaSuccess) e = cudaMalloc(&q_dev, static_cast<size_t>(qbytes));
-            if (e == cudaSuccess) e = cudaMemcpyAsync(x_dev, src, static_cast<size_t>(n) * 4, cudaMemcpyHostToDevice, stream);
-            if (e != cudaSuccess) {
-                cudaFree(x_dev);
-                cudaFree(q_dev);
-                return fail(EDB200_ERR_NOMEM, "load_safetensors: staging '%s': %s", t.name.c_str(), cudaGetErrorString(e));
-            }
-            st = wt == EDB200_TYPE_Q8_0 ? edb200_quantize_rows_q8_0(x_dev, q_dev, rows, k, stream)
-                                        : quantize_rows_q4_k_device(x_dev, q_dev, rows, k, stream);
-            if (st == EDB200_OK) st = table.set(name, wt, q_dev, qbytes, true, stream);
-            cudaStreamSynchronize(stream);   // `wide` and the staging buffers are reused or freed next
-            cudaFree(x_dev);
-            cudaFree(q_dev);
-        }
+        st = ingest.offer(src);
         if (st != EDB200_OK) return st;
-        ++count;
     }
-    if (n_loaded) *n_loaded = count;
     return EDB200_OK;
+}
+
+// Parameters the model keeps as f32 are widened on the host; parameters it keeps quantised are uploaded as
+// f32 rows and encoded on the device in the model's block type (q8_0: ggml's rule, bit for bit; q4_K: this
+// library's min/max encoder, the one init_random uses), then repacked like any other tensor.  The parts of
+// a fused tensor may sit in different shards of a sharded checkpoint.
+edb200_status_t load_safetensors(ParamTable& table, int family, const char* path, const char* strip_prefix,
+                                 cudaStream_t stream, int* n_loaded) {
+    if (n_loaded) *n_loaded = 0;
+    std::vector<std::string> files;
+    if (is_index(path)) {   // a sharded checkpoint: every shard of the index in turn
+        const edb200_status_t ist = index_shards(path, files);
+        if (ist != EDB200_OK) return ist;
+    } else {
+        files.push_back(path);
+    }
+    Ingest ingest(table, family, strip_prefix, stream);
+    for (const auto& file : files) {
+        const edb200_status_t st = offer_file(ingest, file.c_str());
+        if (st != EDB200_OK) return st;
+    }
+    return ingest.finish(n_loaded);
 }
 
 }  // namespace edb

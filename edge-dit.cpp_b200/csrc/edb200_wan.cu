@@ -335,13 +335,13 @@ edb200_status_t edb200_wan_get_tensor_f32(const edb200_wan_t* m, const char* nam
 edb200_status_t edb200_wan_load_gguf(edb200_wan_t* m, const char* path, const char* strip_prefix, int* n_loaded,
                                     void* stream) {
     if (m == nullptr || path == nullptr) return fail(EDB200_ERR_INVALID, "wan_load_gguf: null argument");
-    return load_gguf(m->params, path, strip_prefix, static_cast<cudaStream_t>(stream), n_loaded);
+    return load_gguf(m->params, EDB200_FAMILY_WAN, path, strip_prefix, static_cast<cudaStream_t>(stream), n_loaded);
 }
 
 edb200_status_t edb200_wan_load_safetensors(edb200_wan_t* m, const char* path, const char* strip_prefix, int* n_loaded,
                                            void* stream) {
     if (m == nullptr || path == nullptr) return fail(EDB200_ERR_INVALID, "wan_load_safetensors: null argument");
-    return load_safetensors(m->params, path, strip_prefix, static_cast<cudaStream_t>(stream), n_loaded);
+    return load_safetensors(m->params, EDB200_FAMILY_WAN, path, strip_prefix, static_cast<cudaStream_t>(stream), n_loaded);
 }
 
 edb200_status_t edb200_wan_init_random(edb200_wan_t* m, uint64_t seed, float std, void* stream) {

@@ -255,6 +255,7 @@ _SIGS = {
                                                  C.POINTER(C.c_int), C.POINTER(c_i64), C.POINTER(c_i64)]),
     "edb200_safetensors_tensor_data": (c_vp, [c_vp, C.c_int]),
     "edb200_safetensors_index_files": (C.c_int, [C.c_char_p, C.c_char_p, C.c_int, C.POINTER(C.c_int)]),
+    "edb200_canonical_tensor_name": (C.c_int, [C.c_int, C.c_char_p, C.c_char_p, C.c_int64, C.POINTER(C.c_int)]),
     "edb200_flux_load_safetensors": (C.c_int, [c_vp, C.c_char_p, C.c_char_p, C.POINTER(C.c_int), c_vp]),
     "edb200_sd3_load_safetensors": (C.c_int, [c_vp, C.c_char_p, C.c_char_p, C.POINTER(C.c_int), c_vp]),
     "edb200_qwen_load_safetensors": (C.c_int, [c_vp, C.c_char_p, C.c_char_p, C.POINTER(C.c_int), c_vp]),
@@ -407,6 +408,18 @@ class SafeTensors:
             self.handle = None
 
     __del__ = close
+
+
+FAMILY_FLUX, FAMILY_SD3, FAMILY_QWEN, FAMILY_WAN = 0, 1, 2, 3
+
+
+def canonical_tensor_name(family, name):
+    """(name in the executors' layout, part index) for a checkpoint tensor name, as the loaders see it
+    (convert_diffusion_model_name, reference src/utils/name_conversion.cpp:802-822)."""
+    buf = C.create_string_buffer(1024)
+    part = C.c_int(0)
+    check(lib().edb200_canonical_tensor_name(int(family), str(name).encode(), buf, len(buf), C.byref(part)))
+    return buf.value.decode(), part.value
 
 
 def safetensors_index_files(index_path):

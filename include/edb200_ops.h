@@ -551,6 +551,20 @@ EDB200_API const void* edb200_safetensors_tensor_data(const edb200_safetensors_t
  * edb200_*_load_safetensors calls accept such an index in place of a single file. */
 EDB200_API edb200_status_t edb200_safetensors_index_files(const char* index_path, char* out, int out_cap, int* n_files);
 
+/* Tensor-name canonicalisation of the weight loaders.  A checkpoint in the diffusers layout names the DiT's
+ * tensors differently from the layout the step executors register; convert_diffusion_model_name
+ * (src/utils/name_conversion.cpp:802-822, per family :439-543 SD3, :545-657 FLUX, :773-800 Wan) maps one to
+ * the other, marking the 2nd, 3rd, ... projection of a fused tensor (q,k,v -> qkv; q,k,v,mlp -> linear1) with a
+ * numeric suffix.  `out` receives the base name, `*part` the part index (0 for whole tensors and first parts).
+ * Names already in the executors' layout pass through.  Qwen-Image keeps the diffusers names natively.
+ * Every edb200_*_load_gguf / _load_safetensors call applies this, assembles fused tensors from their parts in
+ * part order (ModelLoader::load_tensors, src/core/runtime/model_loader.cpp:2019-2113) and converts a tensor
+ * stored in another type than the model keeps (f32 / f16 / bf16 / q8_0 / q4_K in, convert_tensor_data,
+ * src/core/runtime/model_loader.cpp:663-704).  Host code. */
+enum { EDB200_FAMILY_FLUX = 0, EDB200_FAMILY_SD3 = 1, EDB200_FAMILY_QWEN = 2, EDB200_FAMILY_WAN = 3 };
+EDB200_API edb200_status_t edb200_canonical_tensor_name(int family, const char* name, char* out, int64_t capacity,
+                                                        int* part);
+
 /* ------------------------------------------------- FLUX.1 denoise-step model
  * A whole-step replacement at the reference's model seam
  * DiffusionModel::compute(n_threads, DiffusionParams) -> sd::Tensor<float>

@@ -35,7 +35,32 @@ static inline size_t ggml_type_size(enum ggml_type t) {
         case GGML_TYPE_F16: return 2;
         case GGML_TYPE_BF16: return 2;
         case GGML_TYPE_I8: return 1;
+        case GGML_TYPE_Q8_0: return 34;  /* bytes per block */
+        case GGML_TYPE_Q4_K: return 144;
         default: return 0;
+    }
+}
+
+/* array extents in the reference's loader headers; no table here is indexed beyond the ids above */
+#define GGML_TYPE_COUNT ((enum ggml_type)64)
+
+static inline int64_t ggml_blck_size(enum ggml_type t) {
+    switch (t) {
+        case GGML_TYPE_Q8_0: return 32;
+        case GGML_TYPE_Q4_K: return 256;
+        default: return 1;
+    }
+}
+
+static inline const char* ggml_type_name(enum ggml_type t) {
+    switch (t) {
+        case GGML_TYPE_F32: return "f32";
+        case GGML_TYPE_F16: return "f16";
+        case GGML_TYPE_BF16: return "bf16";
+        case GGML_TYPE_Q8_0: return "q8_0";
+        case GGML_TYPE_Q4_K: return "q4_K";
+        case GGML_TYPE_I8: return "i8";
+        default: return "?";
     }
 }
 
