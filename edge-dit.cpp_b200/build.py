@@ -26,7 +26,7 @@ NVCC_FLAGS = [
     "-Xptxas", "-v",
     "-I", os.path.join(ROOT, "include"),
     "-I", CSRC,
-]
+] + os.environ.get("EDB200_EXTRA_NVCC_FLAGS", "").split()   # e.g. -DEDB200_GEMM_STATS for a tuning build
 
 
 def sources():

@@ -498,7 +498,422 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x0, const __grid_constant__
     }
 }
 
+// ------------------------------------------------------------------------------------------------
+// The same GEMM on CTA pairs (a cluster of two CTAs on neighbouring SMs, tcgen05 .cta_group::2).
+//
+// A pair computes 256 weight rows x 192 tokens.  Each CTA owns one 128-row weight tile (raw record in its
+// shared memory, dequantised into its tensor memory, accumulators in its tensor memory, its own epilogue)
+// and stages only HALF of the token tile: 96 tokens x 64 k = 12 KB per k-step instead of 24 KB.  One
+// 256 x 192 x 16 MMA issued by the leader CTA reads rows 0-95 of B from the leader's shared memory and rows
+// 96-191 from the peer's.  Per SM and k-step the shared-memory traffic drops from about 65 KB (24 KB TMA
+// write + 24 KB MMA read + 2 x 8.5 KB weights) to about 41 KB for the same 384 tensor clocks, which takes
+// the single-CTA kernel's limit (the 128 B/clk shared-memory port) out of the way.
+//
+// Signals across the pair (all others stay inside a CTA):
+//   a_full     16 arrivals on the LEADER's barrier: the 8 dequantiser warps of either CTA.  A dequantiser
+//              arrives only after it has seen its own CTA's ld_full for that stage, so a_full also tells
+//              the leader that both halves of the token tile have landed.
+//   a_empty, ld_empty, acc_full   tcgen05.commit signalling the barrier of the same name in both CTAs
+//   acc_empty  16 arrivals on the leader's barrier: the 8 epilogue warps of either CTA
+// Loads are addressed to the issuing CTA only.
+#ifdef EDB200_GEMM_STATS
+// Tuning build only: cycles spent waiting, per role, of the first pair of a launch.
+__device__ long long g_pair_stats[16];
+#define PAIR_STAT_T0() const long long stat_t0 = clock64()
+#define PAIR_STAT_ADD(acc) acc += clock64() - stat_t0
+#define PAIR_STAT_FLUSH(slot, v) atomicAdd(reinterpret_cast<unsigned long long*>(&g_pair_stats[slot]), (unsigned long long)(v))
+#else
+#define PAIR_STAT_T0()
+#define PAIR_STAT_ADD(acc)
+#define PAIR_STAT_FLUSH(slot, v)
+#endif
+
+constexpr int PAIR_TOK = TN / 2;                                  // tokens staged per CTA
+constexpr int PAIR_X_BYTES = PAIR_TOK * BK * 2;                   // 12 KB
+constexpr int PAIR_STAGE_BYTES = PAIR_X_BYTES + 9 * 1024;         // + one weight tile record, 1 KB granular
+constexpr int PAIR_LD_STAGES = 8;
+constexpr int PAIR_OFF_STAGE = PAIR_LD_STAGES * PAIR_STAGE_BYTES;    // epilogue transposition: 2 sets x 2 buffers
+constexpr int PAIR_STAGE_OUT_BYTES = 2 * 2 * EC * TW * 4;           //   of 16 tokens x 128 features f32 (32 KB)
+constexpr int PAIR_OFF_BAR = PAIR_OFF_STAGE + PAIR_STAGE_OUT_BYTES;
+constexpr int PAIR_SMEM_BYTES = PAIR_OFF_BAR + 512 + 1024;
+static_assert(PAIR_SMEM_BYTES <= 227 * 1024, "shared memory plan");
+static_assert(W_BYTES_MAX <= 9 * 1024, "weight tile record must fit its slot");
+
+template <int WT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+qgemm_pair_kernel(const __grid_constant__ CUtensorMap map_x0, const __grid_constant__ CUtensorMap map_x1,
+                  const __grid_constant__ Params P) {
+    constexpr bool kQ4 = (WT == EDB200_TYPE_Q4_K);
+    constexpr uint32_t kWBytes = kQ4 ? kQwTileBytesQ4 : kQwTileBytesQ8;
+    constexpr uint32_t kTxBytes = PAIR_X_BYTES + kWBytes;
+    constexpr int ACC_STAGES = 2;
+    constexpr int A_COLS = 32;            // tensor-memory columns of one A stage: 64 k of the CTA's 128 rows
+    constexpr int A_STAGES = 4;
+    constexpr uint32_t TMEM_A = 384;      // accumulators: 2 stages x 192 columns
+    constexpr int LDS = PAIR_LD_STAGES;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + PAIR_OFF_BAR);
+    uint64_t* ld_full = bars;                       // [LDS]
+    uint64_t* ld_empty = ld_full + LDS;             // [LDS]
+    uint64_t* a_full = ld_empty + LDS;              // [4]  (the leader's are used)
+    uint64_t* a_empty = a_full + A_STAGES;          // [4]
+    uint64_t* acc_full = a_empty + A_STAGES;        // [2]
+    uint64_t* acc_empty = acc_full + ACC_STAGES;    // [2]  (the leader's are used)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + ACC_STAGES);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();        // 0: leader (issues the MMAs), 1: peer
+    const int pair = blockIdx.x >> 1;
+    const int n_pairs = gridDim.x >> 1;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < LDS; ++i) {
+            mbar_init(&ld_full[i], 1);
+            mbar_init(&ld_empty[i], 1 + 8);          // the commit + this CTA's 8 dequantiser warps of the stage
+        }
+        for (int i = 0; i < A_STAGES; ++i) {
+            mbar_init(&a_full[i], 16);
+            mbar_init(&a_empty[i], 1);
+        }
+        for (int i = 0; i < ACC_STAGES; ++i) {
+            mbar_init(&acc_full[i], 1);
+            mbar_init(&acc_empty[i], 2 * EPI_WARPS);
+        }
+        *abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 2) {
+        tmem_alloc_pair(tmem_slot, TMEM_COLS);
+        tmem_relinquish_pair();
+    }
+    if (warp == 0 && lane == 0) {
+        tma_prefetch_desc(&map_x0);
+        if (P.total_tiles > P.tiles0) tma_prefetch_desc(&map_x1);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();     // the peer's barriers are initialised before anything arrives on them
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------- producer (both CTAs)
+        uint32_t s = 0, ph = 0;
+        bool ok = true;
+        long long st_wait = 0;
+        (void)st_wait;
+        for (int t = pair; ok && t < P.total_tiles; t += n_pairs) {
+            const TileCoord tc = tile_coord(P, t, 2);
+            const Problem& pr = tc.prob ? P.p[1] : P.p[0];
+            const int ksteps_all = pr.K / BK;
+            const int k_first = tc.kpart * (ksteps_all / pr.ksplit);
+            const int k_last = k_first + ksteps_all / pr.ksplit;
+            const CUtensorMap* mx = tc.prob ? &map_x1 : &map_x0;
+            const uint8_t* wsrc = pr.tiles + (long long)(tc.n_tile + (int)rank) * ksteps_all * kWBytes;
+            const int m_half = tc.m0 + (int)rank * PAIR_TOK;
+            for (int ks = k_first; ks < k_last; ++ks) {
+                PAIR_STAT_T0();
+                if (!mbar_wait(&ld_empty[s], ph ^ 1u, abort_flag, P.err)) {
+                    ok = false;
+                    break;
+                }
+                PAIR_STAT_ADD(st_wait);
+                if (elect_one()) {
+                    uint8_t* stage = smem + s * PAIR_STAGE_BYTES;
+                    mbar_arrive_expect_tx(&ld_full[s], kTxBytes);
+                    tma_load_2d(stage, mx, &ld_full[s], ks * BK, m_half);
+                    bulk_load_1d(stage + PAIR_X_BYTES, wsrc + (long long)ks * kWBytes, kWBytes, &ld_full[s]);
+                }
+                __syncwarp();
+                if (++s == LDS) {
+                    s = 0;
+                    ph ^= 1u;
+                }
+            }
+        }
+        if (blockIdx.x < 2 && lane == 0) PAIR_STAT_FLUSH(3 + 8 * rank, st_wait);
+    } else if (warp == 1) {
+        // -------------------------------------------------------- MMA issuer (leader CTA only)
+        if (rank == 0) {
+            const uint32_t idesc = make_idesc(kDFmtF32, kFmtF16, kFmtF16, 0, 0, 2 * TW, TN);
+            uint32_t s = 0, as = 0, aph = 0, cs = 0, cph = 0;
+            bool ok = true;
+            long long st_acc = 0, st_a = 0;
+            (void)st_acc;
+            (void)st_a;
+#ifdef EDB200_GEMM_STATS
+            const long long st_begin = clock64();
+#endif
+            for (int t = pair; ok && t < P.total_tiles; t += n_pairs) {
+                const TileCoord tc = tile_coord(P, t, 2);
+                const int ksteps = (tc.prob ? P.p[1].K / P.p[1].ksplit : P.p[0].K / P.p[0].ksplit) / BK;
+                {
+                    PAIR_STAT_T0();
+                    if (!mbar_wait(&acc_empty[cs], cph ^ 1u, abort_flag, P.err)) {
+                        ok = false;
+                        break;
+                    }
+                    PAIR_STAT_ADD(st_acc);
+                }
+                tc_fence_after_sync();
+                const uint32_t tmem_d = tmem_base + TMEM_ACC + cs * TN;
+                for (int ks = 0; ok && ks < ksteps; ++ks) {
+                    {
+                        PAIR_STAT_T0();
+                        if (!mbar_wait(&a_full[as], aph, abort_flag, P.err)) {
+                            ok = false;
+                            break;
+                        }
+                        PAIR_STAT_ADD(st_a);
+                    }
+                    tc_fence_after_sync();
+                    if (elect_one()) {
+                        const uint32_t x_addr = smem_u32(smem + s * PAIR_STAGE_BYTES);
+#pragma unroll
+                        for (int j = 0; j < BK / 16; ++j) {
+                            const uint64_t bd = make_smem_desc_sw128(x_addr + j * 32, 16, 1024);
+                            mma_f16_ts_pair(tmem_d, tmem_base + TMEM_A + as * A_COLS + j * 8, bd, idesc,
+                                            (ks > 0 || j > 0) ? 1u : 0u);
+                        }
+                        mma_commit_pair(&a_empty[as]);
+                        mma_commit_pair(&ld_empty[s]);
+                    }
+                    __syncwarp();
+                    if (++as == A_STAGES) {
+                        as = 0;
+                        aph ^= 1u;
+                    }
+                    if (++s == LDS) s = 0;
+                }
+                if (!ok) break;
+                if (elect_one()) mma_commit_pair(&acc_full[cs]);
+                __syncwarp();
+                if (++cs == ACC_STAGES) {
+                    cs = 0;
+                    cph ^= 1u;
+                }
+            }
+#ifdef EDB200_GEMM_STATS
+            if (blockIdx.x == 0 && lane == 0) {
+                PAIR_STAT_FLUSH(0, clock64() - st_begin);
+                PAIR_STAT_FLUSH(1, st_acc);
+                PAIR_STAT_FLUSH(2, st_a);
+            }
+#endif
+        }
+    } else if (warp >= 4 && warp < 12) {
+        // ----------------------------------------------------------- epilogue (both CTAs, own weight rows)
+        const int quarter = warp & 3;
+        const int set = warp >= 8 ? 1 : 0;   // the two warp sets alternate 16-token steps
+        const int tid = quarter * 32 + lane;  // thread of the set
+        float* stage = reinterpret_cast<float*>(smem + PAIR_OFF_STAGE) + set * (2 * EC * TW);
+        uint32_t buf = 0;
+        uint32_t cs = 0, cph = 0;
+        bool ok = true;
+        long long st_wait = 0, st_busy = 0;
+        (void)st_wait;
+        (void)st_busy;
+        for (int t = pair; ok && t < P.total_tiles; t += n_pairs) {
+            const TileCoord tc = tile_coord(P, t, 2);
+            const Problem& pr = tc.prob ? P.p[1] : P.p[0];
+            {
+                PAIR_STAT_T0();
+                if (!mbar_wait(&acc_full[cs], cph, abort_flag, P.err)) {
+                    ok = false;
+                    break;
+                }
+                PAIR_STAT_ADD(st_wait);
+            }
+            PAIR_STAT_T0();
+            tc_fence_after_sync();
+            const int n_tile = tc.n_tile + (int)rank;
+            const int n0 = n_tile * TW;
+            const int n = n0 + tid;                  // this thread's weight row = its tensor-memory lane
+            const bool n_ok = n < pr.N;
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + TMEM_ACC + cs * TN;
+            if (n0 < pr.N && pr.ksplit > 1) {
+                // split reduction: atomic adds, one output feature per lane
+#pragma unroll 1
+                for (int c = set; c < TN / EC; c += 2) {
+                    const int m_first = tc.m0 + c * EC;
+                    if (m_first >= pr.M) break;   // uniform
+                    uint32_t r[EC];
+                    tmem_ld_32x32b_x16(taddr + c * EC, r);
+                    tmem_wait_ld();
+                    float v[EC];
+#pragma unroll
+                    for (int j = 0; j < EC; ++j) v[j] = __uint_as_float(r[j]);
+                    epilogue_store(pr, v, n, m_first, n_ok, tc.kpart);
+                }
+            } else if (n0 < pr.N) {   // uniform: the whole weight tile may lie beyond N
+                // The accumulators arrive one output feature per lane, 16 tokens per step; memory wants whole
+                // 128-byte lines of one token's consecutive features.  Each warp set transposes its 16 x 128
+                // step through shared memory (two buffers, one named barrier per step) and stores 16 bytes
+                // per thread: a lane-per-feature store of 64 B per token row ran at a seventh of this rate.
+                const bool second = (pr.split_n > 0) && (n0 >= pr.split_n);   // tile-uniform: split_n % 128 == 0
+                const int act = second ? pr.act2 : pr.act;
+                const int dt = second ? pr.out2_dtype : pr.out_dtype;
+                const long long ld = second ? pr.ldo2 : pr.ldo;
+                const long long col0 = second ? (n0 - pr.split_n) : n0;
+                char* obase = reinterpret_cast<char*>(second ? pr.out2 : pr.out);
+                const bool gated = !second && pr.gate != nullptr;
+                const float bias_v = (pr.bias != nullptr && n_ok) ? __ldg(pr.bias + n) : 0.0f;
+                const int row = tid >> 3, cc = tid & 7;
+#pragma unroll 1
+                for (int c = set; c < TN / EC; c += 2) {
+                    const int m_first = tc.m0 + c * EC;
+                    if (m_first >= pr.M) break;   // uniform over the set
+                    uint32_t r[EC];
+                    tmem_ld_32x32b_x16(taddr + c * EC, r);
+                    tmem_wait_ld();
+                    float* st = stage + buf * (EC * TW);
+                    if (dt == EDB200_TYPE_F32) {
+#pragma unroll
+                        for (int j = 0; j < EC; ++j) st[j * TW + tid] = apply_act(__uint_as_float(r[j]) + bias_v, act);
+                    } else if (dt == EDB200_TYPE_BF16) {
+                        __nv_bfloat16* sh = reinterpret_cast<__nv_bfloat16*>(st);
+#pragma unroll
+                        for (int j = 0; j < EC; ++j) {
+                            sh[j * TW + tid] = __float2bfloat16_rn(apply_act(__uint_as_float(r[j]) + bias_v, act));
+                        }
+                    } else {
+                        __half* sh = reinterpret_cast<__half*>(st);
+#pragma unroll
+                        for (int j = 0; j < EC; ++j) {
+                            sh[j * TW + tid] = __float2half_rn(apply_act(__uint_as_float(r[j]) + bias_v, act));
+                        }
+                    }
+                    named_bar_sync(1 + set, 128);
+                    const long long m = m_first + row;
+                    if (m < pr.M) {
+                        if (dt == EDB200_TYPE_F32) {
+                            float* orow = reinterpret_cast<float*>(obase) + m * ld + col0;
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const int nl = j * 32 + cc * 4;
+                                if (n0 + nl >= pr.N) continue;
+                                float4 x = *reinterpret_cast<const float4*>(st + row * TW + nl);
+                                if (gated) {
+                                    const float4 g = __ldg(reinterpret_cast<const float4*>(pr.gate + n0 + nl));
+                                    const float4 q = *reinterpret_cast<const float4*>(pr.residual + m * pr.ld_res + n0 + nl);
+                                    x.x = q.x + g.x * x.x;
+                                    x.y = q.y + g.y * x.y;
+                                    x.z = q.z + g.z * x.z;
+                                    x.w = q.w + g.w * x.w;
+                                }
+                                *reinterpret_cast<float4*>(orow + nl) = x;
+                            }
+                        } else {
+                            const uint16_t* sh = reinterpret_cast<const uint16_t*>(st);
+                            uint16_t* orow = reinterpret_cast<uint16_t*>(obase) + m * ld + col0;
+#pragma unroll
+                            for (int j = 0; j < 2; ++j) {
+                                const int nl = j * 64 + cc * 8;
+                                if (n0 + nl >= pr.N) continue;
+                                *reinterpret_cast<uint4*>(orow + nl) = *reinterpret_cast<const uint4*>(sh + row * TW + nl);
+                            }
+                        }
+                    }
+                    buf ^= 1u;
+                }
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_leader(&acc_empty[cs]);
+            PAIR_STAT_ADD(st_busy);
+            if (++cs == ACC_STAGES) {
+                cs = 0;
+                cph ^= 1u;
+            }
+        }
+        if (blockIdx.x < 2 && warp == 4 && lane == 0) {
+            PAIR_STAT_FLUSH(6 + 8 * rank, st_wait);
+            PAIR_STAT_FLUSH(7 + 8 * rank, st_busy);
+        }
+    } else if (warp >= 12) {
+        // -------------------------------------------------------- dequantisers (both CTAs, own weight tile)
+        // warp = (lane quarter, k half, stage parity): 32 rows x 32 k per job, every other 64-k stage.
+        const int quarter = warp & 3;
+        const int kh = ((warp - 12) >> 2) & 1;
+        const uint32_t par = static_cast<uint32_t>((warp - 12) >> 3);
+        const int r = quarter * 32 + lane;       // weight row of the tile = tensor-memory lane
+        const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+        uint32_t g = 0;   // 64-k stages seen so far (all tiles)
+        bool ok = true;
+        long long st_ld = 0, st_a = 0;
+        (void)st_ld;
+        (void)st_a;
+        for (int t = pair; ok && t < P.total_tiles; t += n_pairs) {
+            const TileCoord tc = tile_coord(P, t, 2);
+            const int ksteps = (tc.prob ? P.p[1].K / P.p[1].ksplit : P.p[0].K / P.p[0].ksplit) / BK;
+            for (int ks = 0; ok && ks < ksteps; ++ks, ++g) {
+                if ((g & 1u) != par) continue;
+                const uint32_t s = g % LDS;
+                const uint32_t ph = (g / LDS) & 1u;
+                {
+                    PAIR_STAT_T0();
+                    if (!mbar_wait(&ld_full[s], ph, abort_flag, P.err)) {
+                        ok = false;
+                        break;
+                    }
+                    PAIR_STAT_ADD(st_ld);
+                }
+                const uint8_t* tile = smem + s * PAIR_STAGE_BYTES + PAIR_X_BYTES;
+                uint32_t o[16];
+                if (kQ4) {
+                    dequant_q4_k(tile, r, kh, o);
+                } else {
+                    dequant_q8_0(tile, r, kh, o);
+                }
+                const uint32_t as = g % A_STAGES;
+                const uint32_t aph = (g / A_STAGES) & 1u;
+                {
+                    PAIR_STAT_T0();
+                    if (!mbar_wait(&a_empty[as], aph ^ 1u, abort_flag, P.err)) {
+                        ok = false;
+                        break;
+                    }
+                    PAIR_STAT_ADD(st_a);
+                }
+                tc_fence_after_sync();
+                tmem_st_32x32b_x16(tmem_base + lane_base + TMEM_A + as * A_COLS + kh * 16, o);
+                tmem_wait_st();
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive_leader(&a_full[as]);
+                    mbar_arrive(&ld_empty[s]);
+                }
+            }
+        }
+        if (blockIdx.x < 2 && warp == 12 && lane == 0) {
+            PAIR_STAT_FLUSH(4 + 8 * rank, st_ld);
+            PAIR_STAT_FLUSH(5 + 8 * rank, st_a);
+        }
+    }
+
+    // ---------------------------------------------------------------- teardown
+    tc_fence_before_sync();
+    __syncthreads();
+    if (*abort_flag) {
+        // Give copies and MMAs still in flight time to land before shared and tensor memory are released.
+        for (int i = 0; i < 200; ++i) __nanosleep(1000);
+        __syncthreads();
+    }
+    // Neither CTA leaves while the other may still signal its barriers or the pair's MMAs read its memory.
+    cluster_sync_all();
+    if (warp == 2) {
+        tc_fence_after_sync();
+        tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    }
+}
+
 }  // namespace gemm
+
 
 static edb200_status_t validate_problem(const edb200_qweight_t* w, const void* x, int64_t m, int64_t ldx,
                                         const edb200_epilogue_t* ep) {
@@ -607,6 +1022,15 @@ static edb200_status_t launch_qgemm(int nprob, const edb200_qweight_t* const* ws
         }
         if (force == 1 || force == 2) wh = force;
     }
+    // CTA pairs (256 weight rows x 192 tokens per pair, half the token tile staged per CTA) are the
+    // default; EDB200_GEMM_PAIR=0 selects the single-CTA kernels (tuning and comparison only).
+    static int pair_mode = -1;
+    if (pair_mode < 0) {
+        const char* e = getenv("EDB200_GEMM_PAIR");
+        pair_mode = (e != nullptr && atoi(e) == 0) ? 0 : 1;
+    }
+    const bool pair = pair_mode == 1;
+    if (pair) wh = 2;   // tile bookkeeping: two weight tiles per (pair) tile
     gemm::Params P;
     memset(&P, 0, sizeof(P));
     CUtensorMap map_a[2];
@@ -615,7 +1039,8 @@ static edb200_status_t launch_qgemm(int nprob, const edb200_qweight_t* const* ws
     for (int i = 0; i < nprob; ++i) {
         fill_problem(P.p[i], ws[i], ms[i], eps[i], wh);
         edb200_status_t st = make_tmap_2d(&map_a[i], adt, 2, xs[i], (uint64_t)ws[i]->k, (uint64_t)ms[i],
-                                          (uint64_t)ldxs[i] * 2, gemm::BK, gemm::TN, CU_TENSOR_MAP_SWIZZLE_128B);
+                                          (uint64_t)ldxs[i] * 2, gemm::BK, pair ? gemm::PAIR_TOK : gemm::TN,
+                                          CU_TENSOR_MAP_SWIZZLE_128B);
         if (st != EDB200_OK) return st;
     }
     if (nprob == 1) {
@@ -638,7 +1063,7 @@ static edb200_status_t launch_qgemm(int nprob, const edb200_qweight_t* const* ws
                        ep->out_dtype == EDB200_TYPE_F32 && ep->act == EDB200_ACT_NONE && ep->split_n == 0;
         }
         if (eligible) {
-            int parts = sm_count() / base_tiles;
+            int parts = (pair ? sm_count() / 2 : sm_count()) / base_tiles;
             if (parts > 4) parts = 4;
             for (; parts > 1; --parts) {
                 bool divides = true;
@@ -657,19 +1082,40 @@ static edb200_status_t launch_qgemm(int nprob, const edb200_qweight_t* const* ws
     P.total_tiles = P.tiles0 + (nprob == 2 ? P.p[1].m_tiles * P.p[1].n_tiles * P.p[1].ksplit : 0);
     P.err = err;
 
-    const int grid = P.total_tiles < sm_count() ? P.total_tiles : sm_count();
     const bool q4 = ws[0]->ggml_type == EDB200_TYPE_Q4_K;
     using KernT = void (*)(const CUtensorMap, const CUtensorMap, const gemm::Params);
-    static const KernT kerns[4] = {gemm::qgemm_kernel<EDB200_TYPE_Q8_0, 1>, gemm::qgemm_kernel<EDB200_TYPE_Q8_0, 2>,
-                                   gemm::qgemm_kernel<EDB200_TYPE_Q4_K, 1>, gemm::qgemm_kernel<EDB200_TYPE_Q4_K, 2>};
-    const int ki = (q4 ? 2 : 0) + (wh - 1);
+    static const KernT kerns[6] = {gemm::qgemm_kernel<EDB200_TYPE_Q8_0, 1>,    gemm::qgemm_kernel<EDB200_TYPE_Q8_0, 2>,
+                                   gemm::qgemm_kernel<EDB200_TYPE_Q4_K, 1>,    gemm::qgemm_kernel<EDB200_TYPE_Q4_K, 2>,
+                                   gemm::qgemm_pair_kernel<EDB200_TYPE_Q8_0>, gemm::qgemm_pair_kernel<EDB200_TYPE_Q4_K>};
+    const int ki = pair ? 4 + (q4 ? 1 : 0) : (q4 ? 2 : 0) + (wh - 1);
     KernT kern = kerns[ki];
-    static bool attr_set[4] = {false, false, false, false};
+    const int smem_bytes = pair ? gemm::PAIR_SMEM_BYTES : gemm::SMEM_BYTES;
+    static bool attr_set[6] = {false, false, false, false, false, false};
+    static int max_pairs = 0;   // CTA pairs that can be resident at once
     if (!attr_set[ki]) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm::SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
         if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(qgemm)");
+        if (pair && max_pairs == 0) {
+            cudaLaunchConfig_t cfg;
+            memset(&cfg, 0, sizeof(cfg));
+            cfg.gridDim = dim3(static_cast<unsigned>(sm_count() & ~1), 1, 1);
+            cfg.blockDim = dim3(gemm::NUM_THREADS, 1, 1);
+            cfg.dynamicSmemBytes = static_cast<size_t>(smem_bytes);
+            int n = 0;
+            e = cudaOccupancyMaxActiveClusters(&n, kern, &cfg);
+            if (e != cudaSuccess || n <= 0) {
+                (void)cudaGetLastError();
+                n = sm_count() / 2;
+            }
+            max_pairs = n < sm_count() / 2 ? n : sm_count() / 2;
+#ifdef EDB200_GEMM_STATS
+            fprintf(stderr, "qgemm: %d CTA pairs resident (occupancy query %d)\n", max_pairs, n);
+#endif
+        }
         attr_set[ki] = true;
     }
+    const int grid = pair ? 2 * (P.total_tiles < max_pairs ? P.total_tiles : max_pairs)
+                          : (P.total_tiles < sm_count() ? P.total_tiles : sm_count());
     double flops = 0.0, bytes = 0.0;
     for (int i = 0; i < nprob; ++i) {
         flops += 2.0 * (double)ms[i] * (double)ws[i]->n_out * (double)ws[i]->k;
@@ -677,8 +1123,7 @@ static edb200_status_t launch_qgemm(int nprob, const edb200_qweight_t* const* ws
                  (double)ms[i] * (double)ws[i]->n_out * (eps[i]->out_dtype == EDB200_TYPE_F32 ? 4.0 : 2.0);
     }
     ProfScope prof(stream, PROF_GEMM, flops, bytes);
-    kern<<<grid, gemm::NUM_THREADS, gemm::SMEM_BYTES, stream>>>(
-        map_a[0], map_a[1], P);
+    kern<<<grid, gemm::NUM_THREADS, smem_bytes, stream>>>(map_a[0], map_a[1], P);
     count_launch();
     return check_cuda(cudaGetLastError(), "qgemm launch");
 }
@@ -686,6 +1131,17 @@ static edb200_status_t launch_qgemm(int nprob, const edb200_qweight_t* const* ws
 }  // namespace edb
 
 extern "C" {
+
+#ifdef EDB200_GEMM_STATS
+EDB200_API void edb200_debug_pair_stats(long long* out16, int reset) {
+    cudaDeviceSynchronize();
+    if (out16) cudaMemcpyFromSymbol(out16, edb::gemm::g_pair_stats, 16 * sizeof(long long));
+    if (reset) {
+        long long zero[16] = {0};
+        cudaMemcpyToSymbol(edb::gemm::g_pair_stats, zero, sizeof(zero));
+    }
+}
+#endif
 
 edb200_status_t edb200_mul_mat_q(const edb200_qweight_t* w, const void* x, int x_dtype, int64_t m, int64_t ldx,
                                  const edb200_epilogue_t* ep, void* stream) {

@@ -307,4 +307,72 @@ __device__ __forceinline__ void mma_commit(uint64_t* bar) {
                  : "memory");
 }
 
+// ------------------------------------------------------ CTA pairs (cluster of two) --
+// tcgen05 with .cta_group::2: one MMA spans the tensor memory of both CTAs of a pair (256 rows, 128 per
+// CTA) and reads half of the B tile from each CTA's shared memory, so a CTA stages - and its shared memory
+// serves - only half of the shared operand.  Every tcgen05.alloc / dealloc / mma / commit of such a kernel
+// carries .cta_group::2.  Loads stay addressed to the issuing CTA; only mbarrier arrivals cross the pair.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+
+// Barrier `id` (1..15; 0 is __syncthreads) over `threads` threads of the CTA, whole warps.
+__device__ __forceinline__ void named_bar_sync(int id, int threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+// Both CTAs of the cluster arrive; returns when both have.  Every thread calls it.
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// Arrive on the barrier that sits at `bar`'s offset in the shared memory of cluster CTA 0 (the pair's leader).
+// Default (CTA-scope release) semantics: what crosses the pair behind this signal is tensor memory written by
+// tcgen05.st (completed by tcgen05.wait::st before the arrive) and shared memory written by TMA (complete
+// when its mbarrier fired), neither of which a wider fence would order; a cluster-scope release here costs
+// about a microsecond per arrival.
+__device__ __forceinline__ void mbar_arrive_leader(uint64_t* bar) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, 0;" : "=r"(remote) : "r"(smem_u32(bar)));
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(remote) : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* slot, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(ncols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+
+// D[256 x N] (+)= A[256 x 16] * B[N x 16]^T over the pair: A rows 0-127 from the leader's tensor memory, rows
+// 128-255 from the peer's (same address in both); B rows 0..N/2-1 from the leader's shared memory, the rest
+// from the peer's (same descriptor in both).  Issued by one thread of the leader CTA.
+__device__ __forceinline__ void mma_f16_ts_pair(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc,
+                                                uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+        "}\n"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// Arrive on the barrier at `bar`'s offset in BOTH CTAs of the pair once every tcgen05 op issued so far by
+// this thread is done (an mbarrier signal to two CTAs; no data moves).
+__device__ __forceinline__ void mma_commit_pair(uint64_t* bar) {
+    const uint16_t both = 3;
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+        ::"r"(smem_u32(bar)), "h"(both)
+        : "memory");
+}
+
 }  // namespace edb
