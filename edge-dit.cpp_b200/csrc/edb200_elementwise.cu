@@ -5,6 +5,8 @@
 // shuffles.
 #include "edb200_internal.h"
 
+#include <type_traits>
+
 #include <cstring>
 
 #include <cuda_bf16.h>
@@ -70,6 +72,10 @@ __device__ __forceinline__ float4 load_vec4(const void* base, int dtype, int64_t
 constexpr int LN_THREADS = 256;
 constexpr int LN_MAXV = 8;  // float4 per thread -> H <= 8192
 
+// NV > 0: the row is exactly NV * LN_THREADS float4 wide and every bound check folds away (the common hidden
+// sizes: 3072 -> 3, 5120 -> 5); NV == 0: any width up to LN_MAXV * LN_THREADS float4.  Same arithmetic, same
+// order of additions in both.
+template <int NV>
 __global__ void __launch_bounds__(LN_THREADS)
 layernorm_modulate_kernel(const float* __restrict__ x, int64_t ldx, const float* __restrict__ shift,
                           const float* __restrict__ scale, const float* __restrict__ ln_w,
@@ -79,12 +85,14 @@ layernorm_modulate_kernel(const float* __restrict__ x, int64_t ldx, const float*
     const int64_t row = blockIdx.x;
     const float* xr = x + row * ldx;
     const int nvec = H >> 2;
-    float4 v[LN_MAXV];
+    constexpr bool EXACT = NV > 0;
+    constexpr int NI = EXACT ? NV : LN_MAXV;
+    float4 v[NI];
     float s = 0.0f;
 #pragma unroll
-    for (int i = 0; i < LN_MAXV; ++i) {
+    for (int i = 0; i < NI; ++i) {
         const int c = threadIdx.x + i * LN_THREADS;
-        if (c < nvec) {
+        if (EXACT || c < nvec) {
             v[i] = *reinterpret_cast<const float4*>(xr + 4 * c);
             s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
         }
@@ -92,9 +100,9 @@ layernorm_modulate_kernel(const float* __restrict__ x, int64_t ldx, const float*
     const float mean = block_sum<LN_THREADS>(s, sh) / static_cast<float>(H);
     float q = 0.0f;
 #pragma unroll
-    for (int i = 0; i < LN_MAXV; ++i) {
+    for (int i = 0; i < NI; ++i) {
         const int c = threadIdx.x + i * LN_THREADS;
-        if (c < nvec) {
+        if (EXACT || c < nvec) {
             v[i].x -= mean;
             v[i].y -= mean;
             v[i].z -= mean;
@@ -105,9 +113,9 @@ layernorm_modulate_kernel(const float* __restrict__ x, int64_t ldx, const float*
     const float var = block_sum<LN_THREADS>(q, sh) / static_cast<float>(H);
     const float rstd = 1.0f / sqrtf(var + eps);
 #pragma unroll
-    for (int i = 0; i < LN_MAXV; ++i) {
+    for (int i = 0; i < NI; ++i) {
         const int c = threadIdx.x + i * LN_THREADS;
-        if (c < nvec) {
+        if (EXACT || c < nvec) {
             float o[4] = {v[i].x * rstd, v[i].y * rstd, v[i].z * rstd, v[i].w * rstd};
             if (ln_w != nullptr) {
                 const float4 w4 = __ldg(reinterpret_cast<const float4*>(ln_w) + c);
@@ -237,28 +245,28 @@ struct PackPeers {
     int skip_mask;            // bit i set: tensor i (0 q, 1 k, 2 v) is not produced
 };
 
-template <int D>
-__global__ void __launch_bounds__(256)
+// A warp walks `heads_per_warp` consecutive heads of one token: the token's RoPE table and the norm weights
+// are read once, the address arithmetic is incremental, and the rows of the next two heads are already on
+// their way while one head is normalised and rotated (about 1.5 KB in flight per warp).
+template <int D, bool IN16>
+__global__ void __launch_bounds__(256, 3)
 qk_norm_rope_pack_kernel(const void* __restrict__ qkv, int in_dtype, int64_t ld, int64_t q_off, int64_t k_off,
-                         int64_t v_off, int64_t T, int n_heads, const float* __restrict__ q_w,
+                         int64_t v_off, int64_t T, int n_heads, int heads_per_warp, const float* __restrict__ q_w,
                          const float* __restrict__ k_w, float eps, const float* __restrict__ pe, int64_t tok_off,
                          int64_t L_total, void* __restrict__ q_out, void* __restrict__ k_out,
                          void* __restrict__ v_out, int out_dtype, const PackPeers peers) {
     constexpr int E = D / 32;  // elements per lane: 4 or 2
-    const int64_t gw = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    constexpr int AHEAD = 2;   // heads fetched ahead of the one being processed
+    using Raw = typename std::conditional<IN16, uint2, float4>::type;   // E values as loaded
     const int lane = threadIdx.x & 31;
-    if (gw >= T * n_heads) return;
-    const int64_t t = gw / n_heads;
-    const int h = static_cast<int>(gw % n_heads);
-    const int64_t row = t * ld;
-    int64_t out_base = ((int64_t)h * L_total + tok_off + t) * D + lane * E;
-    if (peers.hp > 0) {
-        const int dst_rank = h / peers.hp;
-        out_base = ((int64_t)(h % peers.hp) * L_total + peers.global_first + tok_off + t) * D + lane * E;
-        q_out = peers.q[dst_rank];
-        k_out = peers.k[dst_rank];
-        v_out = peers.v[dst_rank];
-    }
+    const int groups = n_heads / heads_per_warp;
+    const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    // items (token, head group) are dealt round-robin to the warps of a grid that is resident all at once
+#pragma unroll 1
+    for (int64_t item = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; item < T * groups; item += n_warps) {
+    const int64_t t = item / groups;
+    const int h_first = static_cast<int>(item % groups) * heads_per_warp;
+    const int64_t row = t * ld + lane * E;
 
     float pe_v[E * 2];  // per pair: pe00, pe10, pe01, pe11  (ggml [row,col] = flat row + 2*col)
     if (pe != nullptr) {
@@ -272,67 +280,135 @@ qk_norm_rope_pack_kernel(const void* __restrict__ qkv, int in_dtype, int64_t ld,
             pe_v[4 * p + 3] = m.w;  // (row1,col1)
         }
     }
+    const bool need[3] = {!(peers.skip_mask & 1), !(peers.skip_mask & 2), !(peers.skip_mask & 4)};
+    const int64_t offs[3] = {q_off, k_off, v_off};
+    // per-token scale of a whole-row norm; per-head weights are fetched inside the loop, shared ones here
+    float rs[2] = {1.0f, 1.0f};
+    if (q_w != nullptr && peers.rstd_q != nullptr) rs[0] = __ldg(peers.rstd_q + t);
+    if (k_w != nullptr && peers.rstd_k != nullptr) rs[1] = __ldg(peers.rstd_k + t);
+    float wsh[2][E];
 #pragma unroll
-    for (int which = 0; which < 3; ++which) {
-        if ((peers.skip_mask >> which) & 1) continue;   // uniform
-        const int64_t off = row + (which == 0 ? q_off : which == 1 ? k_off : v_off) + (int64_t)h * D + lane * E;
-        float v[E];
-        if (E == 4) {
-            const float4 f = load_vec4(qkv, in_dtype, off);
-            v[0] = f.x, v[1] = f.y, v[2] = f.z, v[3] = f.w;
-        } else {
-            if (in_dtype == EDB200_TYPE_F32) {
-                const float2 f = *reinterpret_cast<const float2*>(static_cast<const float*>(qkv) + off);
-                v[0] = f.x, v[1] = f.y;
-            } else {
-                const uint32_t u = *reinterpret_cast<const uint32_t*>(static_cast<const uint16_t*>(qkv) + off);
-                const float2 f = in_dtype == EDB200_TYPE_BF16
-                                     ? __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u))
-                                     : __half22float2(*reinterpret_cast<const __half2*>(&u));
-                v[0] = f.x, v[1] = f.y;
-            }
-        }
-        void* dst = which == 0 ? q_out : which == 1 ? k_out : v_out;
-        if (which < 2) {
-            const float* w = which == 0 ? q_w : k_w;
-            const float* rstd = which == 0 ? peers.rstd_q : peers.rstd_k;
-            if (w != nullptr) {
-                float sc;
-                if (rstd != nullptr) {
-                    sc = __ldg(rstd + t);
+    for (int which = 0; which < 2; ++which) {
+        const float* w = which == 0 ? q_w : k_w;
+#pragma unroll
+        for (int e = 0; e < E; ++e) wsh[which][e] = (w != nullptr && peers.w_head_stride == 0) ? __ldg(w + lane * E + e) : 1.0f;
+    }
+
+    auto fetch = [&](int h, Raw (&dst)[3]) {
+#pragma unroll
+        for (int which = 0; which < 3; ++which) {
+            if (!need[which]) continue;   // uniform
+            const int64_t off = row + offs[which] + (int64_t)h * D;
+            if (IN16) {
+                if (E == 4) {
+                    *reinterpret_cast<uint2*>(&dst[which]) = *reinterpret_cast<const uint2*>(static_cast<const uint16_t*>(qkv) + off);
                 } else {
-                    float ss = 0.0f;
-#pragma unroll
-                    for (int e = 0; e < E; ++e) ss += v[e] * v[e];
-                    ss = warp_sum(ss);
-                    sc = 1.0f / sqrtf(ss / static_cast<float>(D) + eps);
+                    reinterpret_cast<uint2*>(&dst[which])->x = *reinterpret_cast<const uint32_t*>(static_cast<const uint16_t*>(qkv) + off);
                 }
-                const float* wh = w + (int64_t)h * peers.w_head_stride + lane * E;
-#pragma unroll
-                for (int e = 0; e < E; ++e) v[e] = (v[e] * sc) * __ldg(wh + e);
-            }
-            if (pe != nullptr) {
-#pragma unroll
-                for (int p = 0; p < E / 2; ++p) {
-                    const float x0 = v[2 * p], x1 = v[2 * p + 1];
-                    v[2 * p] = __fadd_rn(__fmul_rn(x0, pe_v[4 * p + 0]), __fmul_rn(x1, pe_v[4 * p + 1]));
-                    v[2 * p + 1] = __fadd_rn(__fmul_rn(x0, pe_v[4 * p + 2]), __fmul_rn(x1, pe_v[4 * p + 3]));
+            } else {
+                if (E == 4) {
+                    *reinterpret_cast<float4*>(&dst[which]) = *reinterpret_cast<const float4*>(static_cast<const float*>(qkv) + off);
+                } else {
+                    const float2 f = *reinterpret_cast<const float2*>(static_cast<const float*>(qkv) + off);
+                    reinterpret_cast<float4*>(&dst[which])->x = f.x;
+                    reinterpret_cast<float4*>(&dst[which])->y = f.y;
                 }
             }
         }
-        if (E == 4) {
-            store_vec4(dst, out_dtype, out_base, v[0], v[1], v[2], v[3]);
-        } else {
-            if (out_dtype == EDB200_TYPE_F32) {
-                *reinterpret_cast<float2*>(static_cast<float*>(dst) + out_base) = make_float2(v[0], v[1]);
-            } else if (out_dtype == EDB200_TYPE_BF16) {
-                *reinterpret_cast<__nv_bfloat162*>(static_cast<__nv_bfloat16*>(dst) + out_base) =
-                    __floats2bfloat162_rn(v[0], v[1]);
+    };
+    auto widen = [&](const Raw& r, float (&v)[E]) {
+        if (IN16) {
+            const uint2& u = *reinterpret_cast<const uint2*>(&r);
+            float2 lo, hi = make_float2(0.f, 0.f);
+            if (in_dtype == EDB200_TYPE_BF16) {
+                lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+                if (E == 4) hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
             } else {
-                *reinterpret_cast<__half2*>(static_cast<__half*>(dst) + out_base) = __floats2half2_rn(v[0], v[1]);
+                lo = __half22float2(*reinterpret_cast<const __half2*>(&u.x));
+                if (E == 4) hi = __half22float2(*reinterpret_cast<const __half2*>(&u.y));
+            }
+            v[0] = lo.x, v[1] = lo.y;
+            if (E == 4) v[E - 2] = hi.x, v[E - 1] = hi.y;
+        } else {
+            const float4& f = *reinterpret_cast<const float4*>(&r);
+            v[0] = f.x, v[1] = f.y;
+            if (E == 4) v[E - 2] = f.z, v[E - 1] = f.w;
+        }
+    };
+
+    Raw ring[AHEAD + 1][3];
+#pragma unroll
+    for (int a = 0; a < AHEAD; ++a) {
+        if (a < heads_per_warp) fetch(h_first + a, ring[a]);
+    }
+#pragma unroll 1
+    for (int hh0 = 0; hh0 < heads_per_warp; hh0 += AHEAD + 1) {
+#pragma unroll
+        for (int slot = 0; slot < AHEAD + 1; ++slot) {   // ring slots are compile-time indices
+            const int hh = hh0 + slot;
+            if (hh >= heads_per_warp) break;   // uniform
+            const int h = h_first + hh;
+            if (hh + AHEAD < heads_per_warp) fetch(h + AHEAD, ring[(slot + AHEAD) % (AHEAD + 1)]);
+            int64_t out_base = ((int64_t)h * L_total + tok_off + t) * D + lane * E;
+            void* dsts[3] = {q_out, k_out, v_out};
+            if (peers.hp > 0) {
+                const int dst_rank = h / peers.hp;
+                out_base = ((int64_t)(h % peers.hp) * L_total + peers.global_first + tok_off + t) * D + lane * E;
+                dsts[0] = peers.q[dst_rank];
+                dsts[1] = peers.k[dst_rank];
+                dsts[2] = peers.v[dst_rank];
+            }
+#pragma unroll
+            for (int which = 0; which < 3; ++which) {
+                if (!need[which]) continue;   // uniform
+                float v[E];
+                widen(ring[slot][which], v);
+                if (which < 2) {
+                    const float* w = which == 0 ? q_w : k_w;
+                    if (w != nullptr) {
+                        float sc = rs[which];
+                        if ((which == 0 ? peers.rstd_q : peers.rstd_k) == nullptr) {
+                            float ss = 0.0f;
+#pragma unroll
+                            for (int e = 0; e < E; ++e) ss += v[e] * v[e];
+                            ss = warp_sum(ss);
+                            sc = 1.0f / sqrtf(ss / static_cast<float>(D) + eps);
+                        }
+                        if (peers.w_head_stride == 0) {
+#pragma unroll
+                            for (int e = 0; e < E; ++e) v[e] = (v[e] * sc) * wsh[which][e];
+                        } else {
+                            const float* wh = w + (int64_t)h * peers.w_head_stride + lane * E;
+#pragma unroll
+                            for (int e = 0; e < E; ++e) v[e] = (v[e] * sc) * __ldg(wh + e);
+                        }
+                    }
+                    if (pe != nullptr) {
+#pragma unroll
+                        for (int p = 0; p < E / 2; ++p) {
+                            const float x0 = v[2 * p], x1 = v[2 * p + 1];
+                            v[2 * p] = __fadd_rn(__fmul_rn(x0, pe_v[4 * p + 0]), __fmul_rn(x1, pe_v[4 * p + 1]));
+                            v[2 * p + 1] = __fadd_rn(__fmul_rn(x0, pe_v[4 * p + 2]), __fmul_rn(x1, pe_v[4 * p + 3]));
+                        }
+                    }
+                }
+                void* dst = dsts[which];
+                if (E == 4) {
+                    store_vec4(dst, out_dtype, out_base, v[0], v[1], v[E - 2], v[E - 1]);
+                } else {
+                    if (out_dtype == EDB200_TYPE_F32) {
+                        *reinterpret_cast<float2*>(static_cast<float*>(dst) + out_base) = make_float2(v[0], v[1]);
+                    } else if (out_dtype == EDB200_TYPE_BF16) {
+                        *reinterpret_cast<__nv_bfloat162*>(static_cast<__nv_bfloat16*>(dst) + out_base) =
+                            __floats2bfloat162_rn(v[0], v[1]);
+                    } else {
+                        *reinterpret_cast<__half2*>(static_cast<__half*>(dst) + out_base) = __floats2half2_rn(v[0], v[1]);
+                    }
+                }
             }
         }
     }
+    }   // items
 }
 
 __global__ void cast_kernel(const void* __restrict__ x, int in_dtype, void* __restrict__ y, int out_dtype,
@@ -362,8 +438,22 @@ edb200_status_t edb200_layernorm_modulate(const float* x, int64_t ldx, const flo
     }
     ProfScope prof(static_cast<cudaStream_t>(stream), PROF_ELEMENTWISE, 0.0,
                    (double)rows * (double)h * (4.0 + (y_dtype == EDB200_TYPE_F32 ? 4.0 : 2.0)));
-    layernorm_modulate_kernel<<<static_cast<unsigned>(rows), LN_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
-        x, ldx, shift, scale, ln_weight, ln_bias, static_cast<int>(h), eps, y, y_dtype, ldy);
+    const unsigned grid = static_cast<unsigned>(rows);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int hi = static_cast<int>(h);
+    const int nv = (h % (4 * LN_THREADS) == 0) ? static_cast<int>(h / (4 * LN_THREADS)) : 0;
+#define EDB_LN_LAUNCH(NVAL) \
+    layernorm_modulate_kernel<NVAL><<<grid, LN_THREADS, 0, s>>>(x, ldx, shift, scale, ln_weight, ln_bias, hi, eps, y, y_dtype, ldy)
+    switch (nv) {
+        case 1: EDB_LN_LAUNCH(1); break;
+        case 2: EDB_LN_LAUNCH(2); break;
+        case 3: EDB_LN_LAUNCH(3); break;
+        case 4: EDB_LN_LAUNCH(4); break;
+        case 5: EDB_LN_LAUNCH(5); break;
+        case 6: EDB_LN_LAUNCH(6); break;
+        default: EDB_LN_LAUNCH(0); break;
+    }
+#undef EDB_LN_LAUNCH
     count_launch();
     return check_cuda(cudaGetLastError(), "layernorm_modulate launch");
 }
@@ -466,21 +556,33 @@ static edb200_status_t qk_pack_launch(const void* qkv, int in_dtype, int64_t ld,
         peers.global_first + tok_off + tokens > l_total) {
         return fail(EDB200_ERR_INVALID, "qk_norm_rope_pack: offsets must be multiples of 4 and fit l_total");
     }
-    const int64_t warps = tokens * n_heads;
-    const unsigned grid = static_cast<unsigned>((warps * 32 + 255) / 256);
+    // An item is one token x a group of at most 8 consecutive heads (more groups when tokens are few, so that
+    // there are about 16 warps of work per SM); the grid is no larger than what is resident at once.
+    int groups = 1;
+    while (groups < n_heads &&
+           (n_heads % groups != 0 || n_heads / groups > 8 || tokens * groups < (int64_t)sm_count() * 16)) {
+        ++groups;
+    }
+    const int heads_per_warp = n_heads / groups;
+    const int64_t items = tokens * groups;
+    int64_t blocks = (items + 7) / 8;
+    if (blocks > (int64_t)sm_count() * 3) blocks = (int64_t)sm_count() * 3;
+    const unsigned grid = static_cast<unsigned>(blocks);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     ProfScope prof(s, PROF_ELEMENTWISE, 0.0,
                    (double)tokens * 3.0 * n_heads * d_head *
                        ((in_dtype == EDB200_TYPE_F32 ? 4.0 : 2.0) + (out_dtype == EDB200_TYPE_F32 ? 4.0 : 2.0)));
+    const bool in16 = in_dtype != EDB200_TYPE_F32;
+#define EDB_PACK_LAUNCH(DH, I16)                                                                                      \
+    qk_norm_rope_pack_kernel<DH, I16><<<grid, 256, 0, s>>>(qkv, in_dtype, ld, q_off, k_off, v_off, tokens, n_heads,   \
+                                                           heads_per_warp, q_weight, k_weight, eps, pe, tok_off,      \
+                                                           l_total, q_out, k_out, v_out, out_dtype, peers)
     if (d_head == 128) {
-        qk_norm_rope_pack_kernel<128><<<grid, 256, 0, s>>>(qkv, in_dtype, ld, q_off, k_off, v_off, tokens, n_heads,
-                                                           q_weight, k_weight, eps, pe, tok_off, l_total, q_out,
-                                                           k_out, v_out, out_dtype, peers);
+        if (in16) EDB_PACK_LAUNCH(128, true); else EDB_PACK_LAUNCH(128, false);
     } else {
-        qk_norm_rope_pack_kernel<64><<<grid, 256, 0, s>>>(qkv, in_dtype, ld, q_off, k_off, v_off, tokens, n_heads,
-                                                          q_weight, k_weight, eps, pe, tok_off, l_total, q_out, k_out,
-                                                          v_out, out_dtype, peers);
+        if (in16) EDB_PACK_LAUNCH(64, true); else EDB_PACK_LAUNCH(64, false);
     }
+#undef EDB_PACK_LAUNCH
     count_launch();
     return check_cuda(cudaGetLastError(), "qk_norm_rope_pack launch");
 }

@@ -240,7 +240,9 @@ smooth_q_bias_kernel(const __half* __restrict__ k, const float* __restrict__ qm,
     bias[(int64_t)hn * bias_stride + tok] = total;
 }
 
-// Fast pre-pass, one launch for everything after the channel means: CTA (128 threads) per
+constexpr int kFusedQuantThreads = 256;
+
+// Fast pre-pass, one launch for everything after the channel means: CTA (256 threads) per
 // (64-token block, head) quantises the K block (one scale) and the two 32-token Q tiles of the same
 // rows (one scale each) with the arithmetic of quant_block_kernel, and, with smooth-Q, produces the
 // bias of its 64 keys from the K values it already holds.  The bias sum runs in a fixed order of its
@@ -248,15 +250,16 @@ smooth_q_bias_kernel(const __half* __restrict__ k, const float* __restrict__ qm,
 // ((p0+p1)+(p2+p3))+((p4+p5)+(p6+p7)), then a pairwise tree over the D/8 threads of the token
 // (xor-shuffles 1, 2, 4[, 8]).  Rows between l and the padded end of a bias row are set to zero.
 template <int D>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(kFusedQuantThreads)
 fused_quant_kernel(const __half* __restrict__ q, const __half* __restrict__ k, const float* __restrict__ qm,
                    const float* __restrict__ km, int8_t* __restrict__ q8, int8_t* __restrict__ k8,
                    float* __restrict__ q_scale, float* __restrict__ k_scale, float* __restrict__ bias, int L,
                    int q_scale_stride, int k_scale_stride, int bias_stride, int64_t head_rows) {
-    __shared__ float sh[8];
+    constexpr int NT = kFusedQuantThreads, NW = NT / 32;
+    __shared__ float sh[2 * NW];
     __shared__ float s_inv[2];
     constexpr int TPT = D / 8;                 // threads per token
-    constexpr int VK = 64 * D / 8 / 128;       // 8-channel vectors per thread for 64 tokens
+    constexpr int VK = 64 * D / 8 / NT;        // 8-channel vectors per thread for 64 tokens
     const int blk = blockIdx.x, hn = blockIdx.y, tid = threadIdx.x;
     const int tok0 = blk * 64;
     const int d0 = (tid % TPT) * 8;
@@ -282,7 +285,7 @@ fused_quant_kernel(const __half* __restrict__ q, const __half* __restrict__ k, c
     float amax = 1e-7f;
 #pragma unroll
     for (int i = 0; i < VK; ++i) {
-        const int t = (tid + i * 128) / TPT;
+        const int t = (tid + i * NT) / TPT;
         const bool live = tok0 + t < L;
         uint4 raw = make_uint4(0u, 0u, 0u, 0u);
         if (live) raw = *reinterpret_cast<const uint4*>(kp + (int64_t)(tok0 + t) * D + d0);
@@ -312,7 +315,9 @@ fused_quant_kernel(const __half* __restrict__ q, const __half* __restrict__ k, c
     if ((tid & 31) == 0) sh[tid >> 5] = amax;
     __syncthreads();
     if (tid == 0) {
-        const float a = fmaxf(fmaxf(sh[0], sh[1]), fmaxf(sh[2], sh[3]));
+        float a = sh[0];
+#pragma unroll
+        for (int w = 1; w < NW; ++w) a = fmaxf(a, sh[w]);
         const float sc = __fdiv_rn(a, 127.0f);
         k_scale[(int64_t)hn * k_scale_stride + blk] = sc;
         s_inv[0] = __fdiv_rn(1.0f, sc);
@@ -323,7 +328,7 @@ fused_quant_kernel(const __half* __restrict__ q, const __half* __restrict__ k, c
         int8_t* op = k8 + (int64_t)hn * L * D;
 #pragma unroll
         for (int i = 0; i < VK; ++i) {
-            const int t = (tid + i * 128) / TPT;
+            const int t = (tid + i * NT) / TPT;
             if (tok0 + t < L) {
                 uint32_t packed[2] = {0u, 0u};
 #pragma unroll
@@ -340,7 +345,7 @@ fused_quant_kernel(const __half* __restrict__ q, const __half* __restrict__ k, c
     float am[2] = {1e-7f, 1e-7f};
 #pragma unroll
     for (int i = 0; i < VK; ++i) {
-        const int t = (tid + i * 128) / TPT;
+        const int t = (tid + i * NT) / TPT;
         const bool live = tok0 + t < L;
         uint4 raw = make_uint4(0u, 0u, 0u, 0u);
         if (live) raw = *reinterpret_cast<const uint4*>(qp + (int64_t)(tok0 + t) * D + d0);
@@ -367,11 +372,13 @@ fused_quant_kernel(const __half* __restrict__ q, const __half* __restrict__ k, c
     __syncthreads();   // sh and s_inv of the K part are no longer read
     if ((tid & 31) == 0) {
         sh[tid >> 5] = am[0];
-        sh[4 + (tid >> 5)] = am[1];
+        sh[NW + (tid >> 5)] = am[1];
     }
     __syncthreads();
     if (tid < 2) {
-        const float a = fmaxf(fmaxf(sh[4 * tid], sh[4 * tid + 1]), fmaxf(sh[4 * tid + 2], sh[4 * tid + 3]));
+        float a = sh[NW * tid];
+#pragma unroll
+        for (int w = 1; w < NW; ++w) a = fmaxf(a, sh[NW * tid + w]);
         const float sc = __fdiv_rn(a, 127.0f);
         q_scale[(int64_t)hn * q_scale_stride + 2 * blk + tid] = sc;
         s_inv[tid] = __fdiv_rn(1.0f, sc);
@@ -381,7 +388,7 @@ fused_quant_kernel(const __half* __restrict__ q, const __half* __restrict__ k, c
         int8_t* op = q8 + (int64_t)hn * L * D;
 #pragma unroll
         for (int i = 0; i < VK; ++i) {
-            const int t = (tid + i * 128) / TPT;
+            const int t = (tid + i * NT) / TPT;
             const float inv = s_inv[i / (VK / 2)];
             if (tok0 + t < L) {
                 uint32_t packed[2] = {0u, 0u};
@@ -480,7 +487,7 @@ static edb200_status_t quantize(const __half* q, const __half* k, int hn, int l,
     const int lpad = (l + 127) / 128 * 128;
     if (fast_means) {
         // the fast pre-pass: everything after the means in one launch (K and Q read once more, no memset)
-        fused_quant_kernel<D><<<dim3(lpad / kKBlock, hn), 128, 0, s>>>(q, k, smooth_q ? qm : nullptr, km, sp.q8, sp.k8,
+        fused_quant_kernel<D><<<dim3(lpad / kKBlock, hn), kFusedQuantThreads, 0, s>>>(q, k, smooth_q ? qm : nullptr, km, sp.q8, sp.k8,
                                                                        sp.q_scale, sp.k_scale, sp.bias, l,
                                                                        sp.q_scale_stride, sp.k_scale_stride,
                                                                        sp.bias_stride, head_rows);
