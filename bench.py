@@ -704,7 +704,7 @@ def run_ours(args):
     gemm_tflops = gemm["flops"] / (gemm["ms"] * 1e-3) / 1e12 if gemm["ms"] > 0 else 0.0
     traffic = profile_traffic(args.workload)
     roofline = {
-        "kernel": "qgemm_kernel (dequant-fused quantised GEMM, tcgen05 kind::f16)",
+        "kernel": "qgemm_pair_kernel (dequant-fused quantised GEMM on CTA pairs, tcgen05 cta_group::2 kind::f16)",
         "bound": "tensor", "achieved": gemm_tflops, "peak": peaks["tflops"], "unit": "TFLOP/s",
         "frac": gemm_tflops / peaks["tflops"], "peak_source": peaks["source"] + " bf16 sustained (cuBLAS, this pool)",
         "launches_per_step": gemm["launches"], "ms_per_step": gemm["ms"],
