@@ -269,6 +269,42 @@ edb200_status_t qk_pack(edb200_flux* m, const __half* qkv, int64_t rows, int64_t
                                     EDB200_TYPE_F16, s);
 }
 
+// Whether the QKV projections pack q / k / v themselves (fused epilogue) instead of a separate pass.
+bool fused_pack(const edb200_flux* m) {
+    static int on = -1;
+    if (on < 0) {
+        const char* e = getenv("EDB200_FUSED_QK_PACK");
+        on = (e != nullptr && atoi(e) == 0) ? 0 : edb200_mul_mat_q_fuses_qk_pack();
+    }
+    return on == 1 && m->cfg.hidden_size / m->cfg.num_heads == 128;
+}
+
+// The destination of qk_pack() as a fused-epilogue description (same positions, same table rows).
+edb200_qk_pack_t pack_desc(edb200_flux* m, int64_t local_first, const float* qs, const float* ks) {
+    const edb200_flux_config_t& c = m->cfg;
+    const int d = static_cast<int>(c.hidden_size / c.num_heads);
+    const bool sp = m->world > 1;
+    edb200_qk_pack_t k;
+    memset(&k, 0, sizeof(k));
+    k.n_heads = c.num_heads;
+    k.d_head = d;
+    k.q_weight = qs;
+    k.k_weight = ks;
+    k.eps = 1e-6f;
+    k.pe = m->PE + (int64_t)m->rank * m->t_loc * (d / 2) * 4;
+    k.tok_off = local_first;
+    if (m->p2p) {
+        k.peers = &m->qkv_peers;
+        k.l_total = m->t_loc * m->world;
+    } else {
+        k.l_total = m->t_loc;
+        k.q_out = sp ? m->QL : m->Q;
+        k.k_out = sp ? m->KL : m->K;
+        k.v_out = sp ? m->VL : m->V;
+    }
+    return k;
+}
+
 // The adaLN projections of the whole step as one batch: [double i: img 6H, txt 6H] ... [single i: 3H].
 // Built at the first step after prepare or after a tensor was reloaded (it caches device addresses).
 edb200_status_t ensure_mod_batch(edb200_flux* m, cudaStream_t s) {
@@ -640,6 +676,7 @@ static edb200_status_t flux_step_body(edb200_flux_t* m, const float* latent, flo
         cudaMemcpyAsync(m->anchor_in, X_img, n_img * H * 4, cudaMemcpyDeviceToDevice, s);
     }
     const bool whole_inject = m->stream_override != nullptr;
+    const bool fused = fused_pack(m);   // q / k / v packed by the QKV projections' own epilogue
 
     // ---- every adaLN vector of the step: lin(silu(vec)), weight streaming, one launch for all of them
     // (sequence-parallel ranks with peer memory each stream 1/N of the weights and store to all)
@@ -662,12 +699,18 @@ static edb200_status_t flux_step_body(edb200_flux_t* m, const float* latent, flo
             const Lin li = qlin(m, p + "img_attn.qkv"), lt = qlin(m, p + "txt_attn.qkv");
             edb200_epilogue_t ei = make_ep(qkv + n_txt * 3 * H, F16, 3 * H, li.b);
             edb200_epilogue_t et = make_ep(qkv, F16, 3 * H, lt.b);
+            const float* iq = fparam(m, p + "img_attn.norm.query_norm.scale");
+            const float* ik = fparam(m, p + "img_attn.norm.key_norm.scale");
+            const float* tq = fparam(m, p + "txt_attn.norm.query_norm.scale");
+            const float* tk = fparam(m, p + "txt_attn.norm.key_norm.scale");
+            const edb200_qk_pack_t pi = pack_desc(m, n_txt, iq, ik), pt = pack_desc(m, 0, tq, tk);
+            if (fused) ei.pack = &pi, et.pack = &pt;
             EDB_TRY(mm_pair(li.w, xmod + n_txt * H, n_img, H, &ei, lt.w, xmod, n_txt, H, &et, s));
+            if (!fused) {
+                EDB_TRY(qk_pack(m, qkv + n_txt * 3 * H, n_img, n_txt, iq, ik, s));
+                EDB_TRY(qk_pack(m, qkv, n_txt, 0, tq, tk, s));
+            }
         }
-        EDB_TRY(qk_pack(m, qkv + n_txt * 3 * H, n_img, n_txt, fparam(m, p + "img_attn.norm.query_norm.scale"),
-                        fparam(m, p + "img_attn.norm.key_norm.scale"), s));
-        EDB_TRY(qk_pack(m, qkv, n_txt, 0, fparam(m, p + "txt_attn.norm.query_norm.scale"),
-                        fparam(m, p + "txt_attn.norm.key_norm.scale"), s));
         EDB_TRY(attention(m, T, cat, H + M, s));
         {
             const Lin li = qlin(m, p + "img_attn.proj"), lt = qlin(m, p + "txt_attn.proj");
@@ -718,9 +761,13 @@ static edb200_status_t flux_step_body(edb200_flux_t* m, const float* latent, flo
             ep.out2_dtype = F16;
             ep.ldo2 = H + M;
             ep.act2 = EDB200_ACT_GELU_TANH;
+            const float* nq = fparam(m, p + "norm.query_norm.scale");
+            const float* nk = fparam(m, p + "norm.key_norm.scale");
+            const edb200_qk_pack_t pk = pack_desc(m, 0, nq, nk);
+            if (fused) ep.pack = &pk;
             EDB_TRY(edb200_mul_mat_q(l1.w, xmod, F16, TL, H, &ep, s));
+            if (!fused) EDB_TRY(qk_pack(m, qkv, TL, 0, nq, nk, s));
         }
-        EDB_TRY(qk_pack(m, qkv, TL, 0, fparam(m, p + "norm.query_norm.scale"), fparam(m, p + "norm.key_norm.scale"), s));
         EDB_TRY(attention(m, T, cat, H + M, s));
         {
             const Lin l2 = qlin(m, p + "linear2");

@@ -63,6 +63,18 @@ struct Problem {
     int M, N, K;
     int m_tiles, n_tiles;
     int chunk;   // token tiles per L2-resident activation chunk (tile order below)
+    // Fused head-major pack of the leading q | k | v features (edb200_qk_pack_t); n_pack = 0: off.
+    int n_pack;          // 3 * heads * 128, or heads * 128 when the output is q, k or v alone
+    int pk_first;        // kind of the first packed head block: 0 q, 1 k, 2 v
+    int pk_heads, pk_hp; // heads; heads per rank when the destination is sharded (0: local)
+    float pk_eps;
+    const float* pk_qw;
+    const float* pk_kw;
+    const float* pk_pe;      // row i of the problem reads table row pk_pe_row0 + i
+    long long pk_pe_row0;
+    long long pk_pos0;       // token position of row 0 in the destination
+    long long pk_ltotal;
+    void* pk_dst[3][8];      // q, k, v of every destination rank (index 0 when local)
     int ksplit;  // parts the reduction is cut into (1: whole k per tile); parts add into `out` atomically
 };
 
@@ -749,6 +761,91 @@ qgemm_pair_kernel(const __grid_constant__ CUtensorMap map_x0, const __grid_const
                     for (int j = 0; j < EC; ++j) v[j] = __uint_as_float(r[j]);
                     epilogue_store(pr, v, n, m_first, n_ok, tc.kpart);
                 }
+            } else if (n0 < pr.n_pack) {
+                // This weight tile is one head of q, k or v: RMSNorm over its 128 features and the rotary
+                // embedding on the f32 accumulators, then f16 rows of the head-major attention operand.
+                // After the transposition a token's 128 features sit in 8 neighbouring lanes, 16 each.
+                const int blk = n0 / (pr.pk_heads * TW);
+                const int which = pr.pk_first + blk;                   // 0 q, 1 k, 2 v
+                const int head = (n0 - blk * pr.pk_heads * TW) / TW;
+                const int dst_rank = pr.pk_hp > 0 ? head / pr.pk_hp : 0;
+                const int head_l = pr.pk_hp > 0 ? head % pr.pk_hp : head;
+                __half* dst = reinterpret_cast<__half*>(pr.pk_dst[which][dst_rank]) +
+                              ((long long)head_l * pr.pk_ltotal + pr.pk_pos0) * TW;
+                const float* wn = which == 0 ? pr.pk_qw : which == 1 ? pr.pk_kw : nullptr;
+                const bool rope = which < 2 && pr.pk_pe != nullptr;
+                const float bias_v = (pr.bias != nullptr && n_ok) ? __ldg(pr.bias + n) : 0.0f;
+                const int row = tid >> 3, cc = tid & 7;
+#pragma unroll 1
+                for (int c = set; c < TN / EC; c += 2) {
+                    const int m_first = tc.m0 + c * EC;
+                    if (m_first >= pr.M) break;   // uniform over the set
+                    uint32_t r[EC];
+                    tmem_ld_32x32b_x16(taddr + c * EC, r);
+                    tmem_wait_ld();
+                    float* st = stage + buf * (EC * TW);
+#pragma unroll
+                    for (int j = 0; j < EC; ++j) st[j * TW + tid] = __uint_as_float(r[j]) + bias_v;
+                    named_bar_sync(1u + static_cast<uint32_t>(set), 128u);
+                    const long long m = m_first + row;
+                    const long long mc = m < pr.M ? m : pr.M - 1;   // rows past the end compute on the last row, store nothing
+                    float v[16];
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+                        const float* sp = st + row * TW + j * 64 + cc * 8;
+                        const float4 a = *reinterpret_cast<const float4*>(sp);
+                        const float4 b = *reinterpret_cast<const float4*>(sp + 4);
+                        v[8 * j + 0] = a.x, v[8 * j + 1] = a.y, v[8 * j + 2] = a.z, v[8 * j + 3] = a.w;
+                        v[8 * j + 4] = b.x, v[8 * j + 5] = b.y, v[8 * j + 6] = b.z, v[8 * j + 7] = b.w;
+                    }
+                    if (wn != nullptr) {   // uniform
+                        float ss = 0.0f;
+#pragma unroll
+                        for (int e = 0; e < 16; ++e) ss += v[e] * v[e];
+                        ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+                        ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+                        ss += __shfl_xor_sync(0xffffffffu, ss, 4);
+                        const float sc = 1.0f / sqrtf(ss / static_cast<float>(TW) + pr.pk_eps);
+#pragma unroll
+                        for (int j = 0; j < 2; ++j) {
+                            const float4 wa = __ldg(reinterpret_cast<const float4*>(wn + j * 64 + cc * 8));
+                            const float4 wb = __ldg(reinterpret_cast<const float4*>(wn + j * 64 + cc * 8 + 4));
+                            v[8 * j + 0] = (v[8 * j + 0] * sc) * wa.x, v[8 * j + 1] = (v[8 * j + 1] * sc) * wa.y;
+                            v[8 * j + 2] = (v[8 * j + 2] * sc) * wa.z, v[8 * j + 3] = (v[8 * j + 3] * sc) * wa.w;
+                            v[8 * j + 4] = (v[8 * j + 4] * sc) * wb.x, v[8 * j + 5] = (v[8 * j + 5] * sc) * wb.y;
+                            v[8 * j + 6] = (v[8 * j + 6] * sc) * wb.z, v[8 * j + 7] = (v[8 * j + 7] * sc) * wb.w;
+                        }
+                    }
+                    if (rope) {   // uniform
+                        const float4* pp = reinterpret_cast<const float4*>(pr.pk_pe) + (pr.pk_pe_row0 + mc) * (TW / 2);
+#pragma unroll
+                        for (int j = 0; j < 2; ++j) {
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                const float4 mt = __ldg(pp + (j * 64 + cc * 8) / 2 + q);   // pe00, pe10, pe01, pe11
+                                const float x0 = v[8 * j + 2 * q], x1 = v[8 * j + 2 * q + 1];
+                                v[8 * j + 2 * q] = __fadd_rn(__fmul_rn(x0, mt.x), __fmul_rn(x1, mt.y));
+                                v[8 * j + 2 * q + 1] = __fadd_rn(__fmul_rn(x0, mt.z), __fmul_rn(x1, mt.w));
+                            }
+                        }
+                    }
+                    if (m < pr.M) {
+#pragma unroll
+                        for (int j = 0; j < 2; ++j) {
+                            uint4 o;
+                            __half2 h0 = __floats2half2_rn(v[8 * j + 0], v[8 * j + 1]);
+                            __half2 h1 = __floats2half2_rn(v[8 * j + 2], v[8 * j + 3]);
+                            __half2 h2 = __floats2half2_rn(v[8 * j + 4], v[8 * j + 5]);
+                            __half2 h3 = __floats2half2_rn(v[8 * j + 6], v[8 * j + 7]);
+                            o.x = *reinterpret_cast<uint32_t*>(&h0);
+                            o.y = *reinterpret_cast<uint32_t*>(&h1);
+                            o.z = *reinterpret_cast<uint32_t*>(&h2);
+                            o.w = *reinterpret_cast<uint32_t*>(&h3);
+                            *reinterpret_cast<uint4*>(dst + m * TW + j * 64 + cc * 8) = o;
+                        }
+                    }
+                    buf ^= 1u;
+                }
             } else if (n0 < pr.N) {   // uniform: the whole weight tile may lie beyond N
                 // The accumulators arrive one output feature per lane, 16 tokens per step; memory wants whole
                 // 128-byte lines of one token's consecutive features.  Each warp set transposes its 16 x 128
@@ -787,7 +884,7 @@ qgemm_pair_kernel(const __grid_constant__ CUtensorMap map_x0, const __grid_const
                             sh[j * TW + tid] = __float2half_rn(apply_act(__uint_as_float(r[j]) + bias_v, act));
                         }
                     }
-                    named_bar_sync(1 + set, 128);
+                    named_bar_sync(1u + static_cast<uint32_t>(set), 128u);
                     const long long m = m_first + row;
                     if (m < pr.M) {
                         if (dt == EDB200_TYPE_F32) {
@@ -945,6 +1042,37 @@ static edb200_status_t validate_problem(const edb200_qweight_t* w, const void* x
     if (ep->bias != nullptr && (reinterpret_cast<uintptr_t>(ep->bias) & 15u)) {
         return fail(EDB200_ERR_INVALID, "mul_mat_q: bias must be 16-byte aligned");
     }
+    if (ep->pack != nullptr) {
+        const edb200_qk_pack_t& k = *ep->pack;
+        const int64_t n_pack = (k.only ? 1ll : 3ll) * k.n_heads * k.d_head;
+        const int64_t n_primary_cols = ep->split_n > 0 ? ep->split_n : w->n_out;
+        if (k.d_head != 128 || k.n_heads <= 0 || k.only < 0 || k.only > 3 || n_pack != n_primary_cols || ep->gate != nullptr ||
+            ep->act != EDB200_ACT_NONE || ep->split_k != EDB200_SPLIT_K_NEVER || k.l_total <= 0 || k.tok_off < 0) {
+            return fail(EDB200_ERR_INVALID,
+                        "mul_mat_q: a fused q/k/v pack needs d_head 128 and (3 or 1) * n_heads * 128 plain primary columns");
+        }
+        auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
+        if (!al16(k.q_weight) || !al16(k.k_weight) || !al16(k.pe)) {
+            return fail(EDB200_ERR_INVALID, "mul_mat_q: pack weights and position table must be 16-byte aligned");
+        }
+        if (k.peers != nullptr) {
+            const edb200_sp_peers_t& pp = *k.peers;
+            if (pp.world <= 0 || pp.world > 8 || pp.rank < 0 || pp.rank >= pp.world || k.n_heads % pp.world ||
+                (long long)pp.rank * pp.t_loc + k.tok_off + m > k.l_total) {
+                return fail(EDB200_ERR_INVALID, "mul_mat_q: bad peer description of the fused pack");
+            }
+            for (int t = 0; t < 3; ++t) {
+                for (int r = 0; r < pp.world; ++r) {
+                    if (pp.buf[t][r] == nullptr || !al16(pp.buf[t][r])) {
+                        return fail(EDB200_ERR_INVALID, "mul_mat_q: null or unaligned peer buffer of the fused pack");
+                    }
+                }
+            }
+        } else if (k.q_out == nullptr || k.k_out == nullptr || k.v_out == nullptr || !al16(k.q_out) || !al16(k.k_out) ||
+                   !al16(k.v_out) || k.tok_off + m > k.l_total) {
+            return fail(EDB200_ERR_INVALID, "mul_mat_q: pack outputs must be set, 16-byte aligned and hold tok_off + m rows");
+        }
+    }
     if (ep->split_n > 0) {
         if (ep->split_n % gemm::TW != 0 || ep->split_n >= w->n_out || ep->out2 == nullptr || !dt_ok(ep->out2_dtype)) {
             return fail(EDB200_ERR_INVALID, "mul_mat_q: split_n must be a multiple of 128 below n_out with out2 set");
@@ -987,6 +1115,32 @@ static void fill_problem(gemm::Problem& p, const edb200_qweight_t* w, int64_t m,
         if (ch < 4) ch = 4;
         if (ch > p.m_tiles) ch = p.m_tiles;
         p.chunk = static_cast<int>(ch);
+    }
+    p.n_pack = 0;
+    if (ep->pack != nullptr) {
+        const edb200_qk_pack_t& k = *ep->pack;
+        p.n_pack = (k.only ? 1 : 3) * k.n_heads * k.d_head;
+        p.pk_first = k.only ? k.only - 1 : 0;
+        p.pk_heads = k.n_heads;
+        p.pk_eps = k.eps;
+        p.pk_qw = k.q_weight;
+        p.pk_kw = k.k_weight;
+        p.pk_pe = k.pe;
+        p.pk_pe_row0 = k.tok_off;
+        p.pk_ltotal = k.l_total;
+        if (k.peers != nullptr) {
+            p.pk_hp = k.n_heads / k.peers->world;
+            p.pk_pos0 = (long long)k.peers->rank * k.peers->t_loc + k.tok_off;
+            for (int t = 0; t < 3; ++t) {
+                for (int r = 0; r < k.peers->world; ++r) p.pk_dst[t][r] = k.peers->buf[t][r];
+            }
+        } else {
+            p.pk_hp = 0;
+            p.pk_pos0 = k.tok_off;
+            p.pk_dst[0][0] = k.q_out;
+            p.pk_dst[1][0] = k.k_out;
+            p.pk_dst[2][0] = k.v_out;
+        }
     }
 }
 
@@ -1031,6 +1185,11 @@ static edb200_status_t launch_qgemm(int nprob, const edb200_qweight_t* const* ws
     }
     const bool pair = pair_mode == 1;
     if (pair) wh = 2;   // tile bookkeeping: two weight tiles per (pair) tile
+    for (int i = 0; i < nprob; ++i) {
+        if (eps[i]->pack != nullptr && !pair) {
+            return fail(EDB200_ERR_UNSUPPORTED, "mul_mat_q: the fused q/k/v pack exists in the CTA-pair kernel only");
+        }
+    }
     gemm::Params P;
     memset(&P, 0, sizeof(P));
     CUtensorMap map_a[2];
@@ -1090,8 +1249,11 @@ static edb200_status_t launch_qgemm(int nprob, const edb200_qweight_t* const* ws
     const int ki = pair ? 4 + (q4 ? 1 : 0) : (q4 ? 2 : 0) + (wh - 1);
     KernT kern = kerns[ki];
     const int smem_bytes = pair ? gemm::PAIR_SMEM_BYTES : gemm::SMEM_BYTES;
-    static bool attr_set[6] = {false, false, false, false, false, false};
+    static bool attr_set_dev[64][6] = {};   // the attribute is per device
     static int max_pairs = 0;   // CTA pairs that can be resident at once
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+    bool* attr_set = attr_set_dev[dev];
     if (!attr_set[ki]) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
         if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(qgemm)");
@@ -1142,6 +1304,11 @@ EDB200_API void edb200_debug_pair_stats(long long* out16, int reset) {
     }
 }
 #endif
+
+int edb200_mul_mat_q_fuses_qk_pack(void) {
+    const char* e = getenv("EDB200_GEMM_PAIR");
+    return (e != nullptr && atoi(e) == 0) ? 0 : 1;
+}
 
 edb200_status_t edb200_mul_mat_q(const edb200_qweight_t* w, const void* x, int x_dtype, int64_t m, int64_t ldx,
                                  const edb200_epilogue_t* ep, void* stream) {

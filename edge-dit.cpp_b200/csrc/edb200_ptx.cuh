@@ -318,11 +318,6 @@ __device__ __forceinline__ uint32_t cluster_ctarank() {
     return r;
 }
 
-// Barrier `id` (1..15; 0 is __syncthreads) over `threads` threads of the CTA, whole warps.
-__device__ __forceinline__ void named_bar_sync(int id, int threads) {
-    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
-}
-
 // Both CTAs of the cluster arrive; returns when both have.  Every thread calls it.
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");

@@ -201,6 +201,42 @@ edb200_status_t qk_pack(edb200_qwen* m, const __half* qkv, int64_t rows, int64_t
                                     EDB200_TYPE_F16, s);
 }
 
+// Whether the q / k / v projections pack their output themselves (fused epilogue) instead of a separate pass.
+bool fused_pack(const edb200_qwen* m) {
+    static int on = -1;
+    if (on < 0) {
+        const char* e = getenv("EDB200_FUSED_QK_PACK");
+        on = (e != nullptr && atoi(e) == 0) ? 0 : edb200_mul_mat_q_fuses_qk_pack();
+    }
+    return on == 1 && m->cfg.head_dim == 128;
+}
+
+// The destination of qk_pack() as a fused-epilogue description (same positions, same table rows).
+edb200_qk_pack_t pack_desc(edb200_qwen* m, int64_t local_first, const float* qs, const float* ks) {
+    const edb200_qwen_config_t& c = m->cfg;
+    const int d = c.head_dim;
+    const bool sp = m->world > 1;
+    edb200_qk_pack_t k;
+    memset(&k, 0, sizeof(k));
+    k.n_heads = c.num_heads;
+    k.d_head = d;
+    k.q_weight = qs;
+    k.k_weight = ks;
+    k.eps = 1e-6f;
+    k.pe = m->PE + (int64_t)m->rank * m->t_loc * (d / 2) * 4;
+    k.tok_off = local_first;
+    if (m->p2p) {
+        k.peers = &m->qkv_peers;
+        k.l_total = m->t_loc * m->world;
+    } else {
+        k.l_total = m->t_loc;
+        k.q_out = sp ? m->QL : m->Q;
+        k.k_out = sp ? m->KL : m->K;
+        k.v_out = sp ? m->VL : m->V;
+    }
+    return k;
+}
+
 // Joint attention over the whole sequence into the local rows of ATT (single GPU, NCCL exchange,
 // or peer-memory exchange with flag barriers; QwenImageTransformerBlock::forward_sp, qwen_image.hpp:2969-3040).
 edb200_status_t joint_attention(edb200_qwen* m, int64_t T, cudaStream_t s) {
@@ -529,6 +565,7 @@ static edb200_status_t qwen_step_body(edb200_qwen_t* m, const float* latent, flo
     const bool sp = m->world > 1;
     // few output tiles per rank: let the long out-projection reductions be cut along k (unordered adds)
     const int split_k = sp ? EDB200_SPLIT_K_UNORDERED : EDB200_SPLIT_K_NEVER;
+    const bool fused = fused_pack(m);   // q / k / v packed by their projections' own epilogue
     const int lat_c = c.in_channels / (p * p);
     const int64_t pf_out = (int64_t)c.out_channels * p * p;
     const int F16 = EDB200_TYPE_F16;
@@ -594,16 +631,25 @@ static edb200_status_t qwen_step_body(edb200_qwen_t* m, const float* latent, flo
         {
             const char* img_names[3] = {"to_q", "to_k", "to_v"};
             const char* txt_names[3] = {"add_q_proj", "add_k_proj", "add_v_proj"};
+            const float* iq = fparam(m, pa + "norm_q.weight");
+            const float* ik = fparam(m, pa + "norm_k.weight");
+            const float* tq = fparam(m, pa + "norm_added_q.weight");
+            const float* tk = fparam(m, pa + "norm_added_k.weight");
             for (int j = 0; j < 3; ++j) {
                 const Lin li = qlin(m, pa + img_names[j]), lt = qlin(m, pa + txt_names[j]);
                 edb200_epilogue_t ei = make_ep(qkv + n_txt * 3 * H + j * H, F16, 3 * H, li.b);
                 edb200_epilogue_t et = make_ep(qkv + j * H, F16, 3 * H, lt.b);
+                // each projection's epilogue packs its own tensor head-major (norm and RoPE for q and k)
+                edb200_qk_pack_t pi = pack_desc(m, n_txt, iq, ik), pt = pack_desc(m, 0, tq, tk);
+                pi.only = pt.only = j + 1;
+                if (fused) ei.pack = &pi, et.pack = &pt;
                 EDB_TRY(mm_pair(li.w, xmod + n_txt * H, n_img, H, &ei, lt.w, xmod, n_txt, H, &et, s));
             }
+            if (!fused) {
+                EDB_TRY(qk_pack(m, qkv + n_txt * 3 * H, n_img, n_txt, iq, ik, s));
+                EDB_TRY(qk_pack(m, qkv, n_txt, 0, tq, tk, s));
+            }
         }
-        EDB_TRY(qk_pack(m, qkv + n_txt * 3 * H, n_img, n_txt, fparam(m, pa + "norm_q.weight"),
-                        fparam(m, pa + "norm_k.weight"), s));
-        EDB_TRY(qk_pack(m, qkv, n_txt, 0, fparam(m, pa + "norm_added_q.weight"), fparam(m, pa + "norm_added_k.weight"), s));
         EDB_TRY(joint_attention(m, T, s));
         {
             const Lin li = qlin(m, pa + "to_out.0"), lt = qlin(m, pa + "to_add_out");

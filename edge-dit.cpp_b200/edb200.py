@@ -27,7 +27,17 @@ class Epilogue(C.Structure):
         ("bias", c_vp), ("act", C.c_int), ("out", c_vp), ("out_dtype", C.c_int), ("ldo", c_i64),
         ("residual", c_vp), ("ld_res", c_i64), ("gate", c_vp),
         ("split_n", c_i64), ("out2", c_vp), ("out2_dtype", C.c_int), ("ldo2", c_i64), ("act2", C.c_int),
-        ("split_k", C.c_int),
+        ("split_k", C.c_int), ("pack", c_vp),
+    ]
+
+
+class QkPack(C.Structure):
+    """edb200_qk_pack_t: head-major destination of a QKV projection's leading q | k | v features."""
+    _fields_ = [
+        ("n_heads", C.c_int), ("d_head", C.c_int), ("only", C.c_int), ("q_weight", c_vp), ("k_weight", c_vp),
+        ("eps", C.c_float),
+        ("pe", c_vp), ("tok_off", c_i64), ("l_total", c_i64), ("q_out", c_vp), ("k_out", c_vp), ("v_out", c_vp),
+        ("peers", c_vp),
     ]
 
 
@@ -256,6 +266,7 @@ _SIGS = {
     "edb200_safetensors_tensor_data": (c_vp, [c_vp, C.c_int]),
     "edb200_safetensors_index_files": (C.c_int, [C.c_char_p, C.c_char_p, C.c_int, C.POINTER(C.c_int)]),
     "edb200_canonical_tensor_name": (C.c_int, [C.c_int, C.c_char_p, C.c_char_p, C.c_int64, C.POINTER(C.c_int)]),
+    "edb200_mul_mat_q_fuses_qk_pack": (C.c_int, []),
     "edb200_flux_load_safetensors": (C.c_int, [c_vp, C.c_char_p, C.c_char_p, C.POINTER(C.c_int), c_vp]),
     "edb200_sd3_load_safetensors": (C.c_int, [c_vp, C.c_char_p, C.c_char_p, C.POINTER(C.c_int), c_vp]),
     "edb200_qwen_load_safetensors": (C.c_int, [c_vp, C.c_char_p, C.c_char_p, C.POINTER(C.c_int), c_vp]),

@@ -144,6 +144,33 @@ EDB200_API int64_t edb200_qweight_bytes(const edb200_qweight_t* w);
  * (src/core/backend/ggml/ggml_extend.hpp:1308-1347) and Linear::forward
  * (:7675-7698), forward_output_slice (:7700-7731) and
  * forward_input_concat_residual_gate_fused (:7733-7831). */
+/* Optional last stage of a QKV projection's epilogue: the first 3 * n_heads * d_head output features
+ * (q heads | k heads | v heads; or one of the three, see `only`) do not go to `out` but straight to head-major attention operands, with the
+ * per-head RMSNorm of q and k and the rotary embedding applied to the f32 accumulators on the way
+ * (QKNorm, src/dit_models/components/common/normalization.cpp:71-99; apply_rope,
+ * src/dit_models/components/common/rope.hpp:733-778) - the work of edb200_qk_norm_rope_pack without the
+ * round trip of the projection's output through memory.  d_head must be 128 (one 128-row weight tile = one
+ * head); available when edb200_mul_mat_q_fuses_qk_pack() returns 1. */
+typedef struct edb200_qk_pack {
+    int n_heads, d_head;
+    int only;                /* 0: the packed features are q | k | v (3 * n_heads * d_head of them);
+                              * 1, 2, 3: they are the heads of q, k or v alone (n_heads * d_head), for models
+                              * with separate to_q / to_k / to_v projections */
+    const float* q_weight;   /* [d_head] RMSNorm weights, NULL = no norm */
+    const float* k_weight;
+    float eps;
+    const float* pe;         /* [positions, d_head/2, 2, 2] f32 as edb200_qk_norm_rope_pack takes it, NULL = no RoPE;
+                              * row `tok_off + i` belongs to output row i */
+    int64_t tok_off;         /* position of output row 0 on the token axis of q_out / k_out / v_out */
+    int64_t l_total;         /* tokens per head in the destination */
+    void* q_out;             /* f16 [n_heads, l_total, d_head] (unused when `peers` is given) */
+    void* k_out;
+    void* v_out;
+    /* sequence parallel: head h goes to rank h / (n_heads / world), at token position
+     * rank * t_loc + tok_off + i of that rank's [n_heads / world, l_total, d_head] buffers */
+    const edb200_sp_peers_t* peers;
+} edb200_qk_pack_t;
+
 typedef struct {
     const float* bias;     /* [n_out] or NULL */
     int act;               /* EDB200_ACT_* applied to columns < split_n */
@@ -169,7 +196,13 @@ typedef struct {
      * of those adds, hence the last bit of the result, can differ between runs.  The
      * sequence-parallel executors ask for it: a rank's out-projections have few output tiles. */
     int split_k;
+    /* NULL, or the head-major destination of the leading q | k | v features (see edb200_qk_pack_t).  The
+     * packed features must end where the column split starts (split_n) or cover the whole output. */
+    const edb200_qk_pack_t* pack;
 } edb200_epilogue_t;
+
+/* 1 when edb200_mul_mat_q honours edb200_epilogue_t.pack (the CTA-pair kernel is in use), else 0. */
+EDB200_API int edb200_mul_mat_q_fuses_qk_pack(void);
 
 /* x: [m, ldx] f16 (x_dtype = EDB200_TYPE_F16), 16-byte aligned rows.  Tensor-core
  * path (tcgen05 kind::f16: both operands share one 16-bit format and the weights
