@@ -66,6 +66,7 @@ struct Problem {
     // Fused head-major pack of the leading q | k | v features (edb200_qk_pack_t); n_pack = 0: off.
     int n_pack;          // 3 * heads * 128, or heads * 128 when the output is q, k or v alone
     int pk_first;        // kind of the first packed head block: 0 q, 1 k, 2 v
+    int pk_d;            // head width: 128 (one head per weight tile) or 64 (two)
     int pk_heads, pk_hp; // heads; heads per rank when the destination is sharded (0: local)
     float pk_eps;
     const float* pk_qw;
@@ -551,7 +552,110 @@ constexpr int PAIR_SMEM_BYTES = PAIR_OFF_BAR + 512 + 1024;
 static_assert(PAIR_SMEM_BYTES <= 227 * 1024, "shared memory plan");
 static_assert(W_BYTES_MAX <= 9 * 1024, "weight tile record must fit its slot");
 
-template <int WT>
+// Epilogue of a weight tile that holds one head (D 128) or two heads (D 64) of q, k or v: RMSNorm over the head's
+// features and the rotary embedding on the f32 accumulators, then f16 rows of the head-major attention operand
+// (edb200_qk_pack_t).  Run by the 128 threads of one epilogue warp set; after the transposition through `stage`
+// a token's 128 features sit in 8 neighbouring lanes, 2 x 8 each (features cc*8.. and 64 + cc*8..: with D 64 one
+// group per head).
+template <int D>
+__device__ __forceinline__ void pack_qkv_tile(const Problem& pr, float* stage, uint32_t& buf, uint32_t taddr, int set,
+                                              int tid, int n0, int n, bool n_ok, int m0) {
+    const int blk = n0 / (pr.pk_heads * D);
+    const int which = pr.pk_first + blk;                   // 0 q, 1 k, 2 v
+    const int head0 = (n0 - blk * pr.pk_heads * D) / D;    // first head of the tile
+    const float* wn = which == 0 ? pr.pk_qw : which == 1 ? pr.pk_kw : nullptr;
+    const bool rope = which < 2 && pr.pk_pe != nullptr;
+    const float bias_v = (pr.bias != nullptr && n_ok) ? __ldg(pr.bias + n) : 0.0f;
+    const int row = tid >> 3, cc = tid & 7;
+#pragma unroll 1
+    for (int c = set; c < TN / EC; c += 2) {
+        const int m_first = m0 + c * EC;
+        if (m_first >= pr.M) break;   // uniform over the set
+        uint32_t r[EC];
+        tmem_ld_32x32b_x16(taddr + c * EC, r);
+        tmem_wait_ld();
+        float* st = stage + buf * (EC * TW);
+#pragma unroll
+        for (int j = 0; j < EC; ++j) st[j * TW + tid] = __uint_as_float(r[j]) + bias_v;
+        named_bar_sync(1u + static_cast<uint32_t>(set), 128u);
+        const long long m = m_first + row;
+        const long long mc = m < pr.M ? m : pr.M - 1;   // rows past the end compute on the last row, store nothing
+        float v[16];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const float* sp = st + row * TW + j * 64 + cc * 8;
+            const float4 a = *reinterpret_cast<const float4*>(sp);
+            const float4 b = *reinterpret_cast<const float4*>(sp + 4);
+            v[8 * j + 0] = a.x, v[8 * j + 1] = a.y, v[8 * j + 2] = a.z, v[8 * j + 3] = a.w;
+            v[8 * j + 4] = b.x, v[8 * j + 5] = b.y, v[8 * j + 6] = b.z, v[8 * j + 7] = b.w;
+        }
+        if (wn != nullptr) {   // uniform
+            float ss[2] = {0.0f, 0.0f};
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) ss[j] += v[8 * j + e] * v[8 * j + e];
+            }
+            if (D == TW) ss[0] = ss[1] = ss[0] + ss[1];
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                if (D == TW && j == 1) {
+                    ss[1] = ss[0];
+                } else {
+                    ss[j] += __shfl_xor_sync(0xffffffffu, ss[j], 1);
+                    ss[j] += __shfl_xor_sync(0xffffffffu, ss[j], 2);
+                    ss[j] += __shfl_xor_sync(0xffffffffu, ss[j], 4);
+                }
+                const float sc = 1.0f / sqrtf(ss[j] / static_cast<float>(D) + pr.pk_eps);
+                const int fh = (D == TW ? j * 64 : 0) + cc * 8;     // feature within the head
+                const float4 wa = __ldg(reinterpret_cast<const float4*>(wn + fh));
+                const float4 wb = __ldg(reinterpret_cast<const float4*>(wn + fh + 4));
+                v[8 * j + 0] = (v[8 * j + 0] * sc) * wa.x, v[8 * j + 1] = (v[8 * j + 1] * sc) * wa.y;
+                v[8 * j + 2] = (v[8 * j + 2] * sc) * wa.z, v[8 * j + 3] = (v[8 * j + 3] * sc) * wa.w;
+                v[8 * j + 4] = (v[8 * j + 4] * sc) * wb.x, v[8 * j + 5] = (v[8 * j + 5] * sc) * wb.y;
+                v[8 * j + 6] = (v[8 * j + 6] * sc) * wb.z, v[8 * j + 7] = (v[8 * j + 7] * sc) * wb.w;
+            }
+        }
+        if (rope) {   // uniform
+            const float4* pp = reinterpret_cast<const float4*>(pr.pk_pe) + (pr.pk_pe_row0 + mc) * (D / 2);
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int fh = (D == TW ? j * 64 : 0) + cc * 8;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float4 mt = __ldg(pp + fh / 2 + q);   // pe00, pe10, pe01, pe11
+                    const float x0 = v[8 * j + 2 * q], x1 = v[8 * j + 2 * q + 1];
+                    v[8 * j + 2 * q] = __fadd_rn(__fmul_rn(x0, mt.x), __fmul_rn(x1, mt.y));
+                    v[8 * j + 2 * q + 1] = __fadd_rn(__fmul_rn(x0, mt.z), __fmul_rn(x1, mt.w));
+                }
+            }
+        }
+        if (m < pr.M) {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int head = head0 + (D == TW ? 0 : j);
+                const int fh = (D == TW ? j * 64 : 0) + cc * 8;
+                const int dst_rank = pr.pk_hp > 0 ? head / pr.pk_hp : 0;
+                const int head_l = pr.pk_hp > 0 ? head % pr.pk_hp : head;
+                __half* dst = reinterpret_cast<__half*>(pr.pk_dst[which][dst_rank]) +
+                              ((long long)head_l * pr.pk_ltotal + pr.pk_pos0 + m) * D + fh;
+                uint4 o;
+                __half2 h0 = __floats2half2_rn(v[8 * j + 0], v[8 * j + 1]);
+                __half2 h1 = __floats2half2_rn(v[8 * j + 2], v[8 * j + 3]);
+                __half2 h2 = __floats2half2_rn(v[8 * j + 4], v[8 * j + 5]);
+                __half2 h3 = __floats2half2_rn(v[8 * j + 6], v[8 * j + 7]);
+                o.x = *reinterpret_cast<uint32_t*>(&h0);
+                o.y = *reinterpret_cast<uint32_t*>(&h1);
+                o.z = *reinterpret_cast<uint32_t*>(&h2);
+                o.w = *reinterpret_cast<uint32_t*>(&h3);
+                *reinterpret_cast<uint4*>(dst) = o;
+            }
+        }
+        buf ^= 1u;
+    }
+}
+
+template <int WT, int DQ>   // DQ: 64-k stages whose conversion is in flight at once per CTA (2 or 4)
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 qgemm_pair_kernel(const __grid_constant__ CUtensorMap map_x0, const __grid_constant__ CUtensorMap map_x1,
                   const __grid_constant__ Params P) {
@@ -585,10 +689,10 @@ qgemm_pair_kernel(const __grid_constant__ CUtensorMap map_x0, const __grid_const
     if (threadIdx.x == 0) {
         for (int i = 0; i < LDS; ++i) {
             mbar_init(&ld_full[i], 1);
-            mbar_init(&ld_empty[i], 1 + 8);          // the commit + this CTA's 8 dequantiser warps of the stage
+            mbar_init(&ld_empty[i], 1 + 16 / DQ);    // the commit + this CTA's dequantiser warps of the stage
         }
         for (int i = 0; i < A_STAGES; ++i) {
-            mbar_init(&a_full[i], 16);
+            mbar_init(&a_full[i], 2 * (16 / DQ));   // the stage's dequantiser warps of both CTAs
             mbar_init(&a_empty[i], 1);
         }
         for (int i = 0; i < ACC_STAGES; ++i) {
@@ -762,89 +866,11 @@ qgemm_pair_kernel(const __grid_constant__ CUtensorMap map_x0, const __grid_const
                     epilogue_store(pr, v, n, m_first, n_ok, tc.kpart);
                 }
             } else if (n0 < pr.n_pack) {
-                // This weight tile is one head of q, k or v: RMSNorm over its 128 features and the rotary
-                // embedding on the f32 accumulators, then f16 rows of the head-major attention operand.
-                // After the transposition a token's 128 features sit in 8 neighbouring lanes, 16 each.
-                const int blk = n0 / (pr.pk_heads * TW);
-                const int which = pr.pk_first + blk;                   // 0 q, 1 k, 2 v
-                const int head = (n0 - blk * pr.pk_heads * TW) / TW;
-                const int dst_rank = pr.pk_hp > 0 ? head / pr.pk_hp : 0;
-                const int head_l = pr.pk_hp > 0 ? head % pr.pk_hp : head;
-                __half* dst = reinterpret_cast<__half*>(pr.pk_dst[which][dst_rank]) +
-                              ((long long)head_l * pr.pk_ltotal + pr.pk_pos0) * TW;
-                const float* wn = which == 0 ? pr.pk_qw : which == 1 ? pr.pk_kw : nullptr;
-                const bool rope = which < 2 && pr.pk_pe != nullptr;
-                const float bias_v = (pr.bias != nullptr && n_ok) ? __ldg(pr.bias + n) : 0.0f;
-                const int row = tid >> 3, cc = tid & 7;
-#pragma unroll 1
-                for (int c = set; c < TN / EC; c += 2) {
-                    const int m_first = tc.m0 + c * EC;
-                    if (m_first >= pr.M) break;   // uniform over the set
-                    uint32_t r[EC];
-                    tmem_ld_32x32b_x16(taddr + c * EC, r);
-                    tmem_wait_ld();
-                    float* st = stage + buf * (EC * TW);
-#pragma unroll
-                    for (int j = 0; j < EC; ++j) st[j * TW + tid] = __uint_as_float(r[j]) + bias_v;
-                    named_bar_sync(1u + static_cast<uint32_t>(set), 128u);
-                    const long long m = m_first + row;
-                    const long long mc = m < pr.M ? m : pr.M - 1;   // rows past the end compute on the last row, store nothing
-                    float v[16];
-#pragma unroll
-                    for (int j = 0; j < 2; ++j) {
-                        const float* sp = st + row * TW + j * 64 + cc * 8;
-                        const float4 a = *reinterpret_cast<const float4*>(sp);
-                        const float4 b = *reinterpret_cast<const float4*>(sp + 4);
-                        v[8 * j + 0] = a.x, v[8 * j + 1] = a.y, v[8 * j + 2] = a.z, v[8 * j + 3] = a.w;
-                        v[8 * j + 4] = b.x, v[8 * j + 5] = b.y, v[8 * j + 6] = b.z, v[8 * j + 7] = b.w;
-                    }
-                    if (wn != nullptr) {   // uniform
-                        float ss = 0.0f;
-#pragma unroll
-                        for (int e = 0; e < 16; ++e) ss += v[e] * v[e];
-                        ss += __shfl_xor_sync(0xffffffffu, ss, 1);
-                        ss += __shfl_xor_sync(0xffffffffu, ss, 2);
-                        ss += __shfl_xor_sync(0xffffffffu, ss, 4);
-                        const float sc = 1.0f / sqrtf(ss / static_cast<float>(TW) + pr.pk_eps);
-#pragma unroll
-                        for (int j = 0; j < 2; ++j) {
-                            const float4 wa = __ldg(reinterpret_cast<const float4*>(wn + j * 64 + cc * 8));
-                            const float4 wb = __ldg(reinterpret_cast<const float4*>(wn + j * 64 + cc * 8 + 4));
-                            v[8 * j + 0] = (v[8 * j + 0] * sc) * wa.x, v[8 * j + 1] = (v[8 * j + 1] * sc) * wa.y;
-                            v[8 * j + 2] = (v[8 * j + 2] * sc) * wa.z, v[8 * j + 3] = (v[8 * j + 3] * sc) * wa.w;
-                            v[8 * j + 4] = (v[8 * j + 4] * sc) * wb.x, v[8 * j + 5] = (v[8 * j + 5] * sc) * wb.y;
-                            v[8 * j + 6] = (v[8 * j + 6] * sc) * wb.z, v[8 * j + 7] = (v[8 * j + 7] * sc) * wb.w;
-                        }
-                    }
-                    if (rope) {   // uniform
-                        const float4* pp = reinterpret_cast<const float4*>(pr.pk_pe) + (pr.pk_pe_row0 + mc) * (TW / 2);
-#pragma unroll
-                        for (int j = 0; j < 2; ++j) {
-#pragma unroll
-                            for (int q = 0; q < 4; ++q) {
-                                const float4 mt = __ldg(pp + (j * 64 + cc * 8) / 2 + q);   // pe00, pe10, pe01, pe11
-                                const float x0 = v[8 * j + 2 * q], x1 = v[8 * j + 2 * q + 1];
-                                v[8 * j + 2 * q] = __fadd_rn(__fmul_rn(x0, mt.x), __fmul_rn(x1, mt.y));
-                                v[8 * j + 2 * q + 1] = __fadd_rn(__fmul_rn(x0, mt.z), __fmul_rn(x1, mt.w));
-                            }
-                        }
-                    }
-                    if (m < pr.M) {
-#pragma unroll
-                        for (int j = 0; j < 2; ++j) {
-                            uint4 o;
-                            __half2 h0 = __floats2half2_rn(v[8 * j + 0], v[8 * j + 1]);
-                            __half2 h1 = __floats2half2_rn(v[8 * j + 2], v[8 * j + 3]);
-                            __half2 h2 = __floats2half2_rn(v[8 * j + 4], v[8 * j + 5]);
-                            __half2 h3 = __floats2half2_rn(v[8 * j + 6], v[8 * j + 7]);
-                            o.x = *reinterpret_cast<uint32_t*>(&h0);
-                            o.y = *reinterpret_cast<uint32_t*>(&h1);
-                            o.z = *reinterpret_cast<uint32_t*>(&h2);
-                            o.w = *reinterpret_cast<uint32_t*>(&h3);
-                            *reinterpret_cast<uint4*>(dst + m * TW + j * 64 + cc * 8) = o;
-                        }
-                    }
-                    buf ^= 1u;
+                // one head (or two) of q, k or v: norm, rotary embedding and the head-major store happen here
+                if (pr.pk_d == TW) {
+                    pack_qkv_tile<TW>(pr, stage, buf, taddr, set, tid, n0, n, n_ok, tc.m0);
+                } else {
+                    pack_qkv_tile<64>(pr, stage, buf, taddr, set, tid, n0, n, n_ok, tc.m0);
                 }
             } else if (n0 < pr.N) {   // uniform: the whole weight tile may lie beyond N
                 // The accumulators arrive one output feature per lane, 16 tokens per step; memory wants whole
@@ -933,10 +959,13 @@ qgemm_pair_kernel(const __grid_constant__ CUtensorMap map_x0, const __grid_const
         }
     } else if (warp >= 12) {
         // -------------------------------------------------------- dequantisers (both CTAs, own weight tile)
-        // warp = (lane quarter, k half, stage parity): 32 rows x 32 k per job, every other 64-k stage.
+        // DQ = 2: warp = (lane quarter, k half, stage parity): 32 rows x 32 k per job, every other 64-k stage.
+        // DQ = 4: warp = (lane quarter, stage mod 4): 32 rows x 64 k per job (two stores, one wait), every fourth
+        //         stage - as many conversions in flight as there are A stages, so the chain load -> convert ->
+        //         tcgen05.st -> wait -> arrive of one stage has four stages' tensor time to complete.
         const int quarter = warp & 3;
-        const int kh = ((warp - 12) >> 2) & 1;
-        const uint32_t par = static_cast<uint32_t>((warp - 12) >> 3);
+        const int kh0 = DQ == 2 ? ((warp - 12) >> 2) & 1 : 0;
+        const uint32_t slot = DQ == 2 ? static_cast<uint32_t>((warp - 12) >> 3) : static_cast<uint32_t>((warp - 12) >> 2);
         const int r = quarter * 32 + lane;       // weight row of the tile = tensor-memory lane
         const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
         uint32_t g = 0;   // 64-k stages seen so far (all tiles)
@@ -948,7 +977,7 @@ qgemm_pair_kernel(const __grid_constant__ CUtensorMap map_x0, const __grid_const
             const TileCoord tc = tile_coord(P, t, 2);
             const int ksteps = (tc.prob ? P.p[1].K / P.p[1].ksplit : P.p[0].K / P.p[0].ksplit) / BK;
             for (int ks = 0; ok && ks < ksteps; ++ks, ++g) {
-                if ((g & 1u) != par) continue;
+                if ((g % DQ) != slot) continue;
                 const uint32_t s = g % LDS;
                 const uint32_t ph = (g / LDS) & 1u;
                 {
@@ -960,14 +989,14 @@ qgemm_pair_kernel(const __grid_constant__ CUtensorMap map_x0, const __grid_const
                     PAIR_STAT_ADD(st_ld);
                 }
                 const uint8_t* tile = smem + s * PAIR_STAGE_BYTES + PAIR_X_BYTES;
-                uint32_t o[16];
-                if (kQ4) {
-                    dequant_q4_k(tile, r, kh, o);
-                } else {
-                    dequant_q8_0(tile, r, kh, o);
-                }
                 const uint32_t as = g % A_STAGES;
                 const uint32_t aph = (g / A_STAGES) & 1u;
+                uint32_t o[16];
+                if (kQ4) {
+                    dequant_q4_k(tile, r, kh0, o);
+                } else {
+                    dequant_q8_0(tile, r, kh0, o);
+                }
                 {
                     PAIR_STAT_T0();
                     if (!mbar_wait(&a_empty[as], aph ^ 1u, abort_flag, P.err)) {
@@ -977,7 +1006,15 @@ qgemm_pair_kernel(const __grid_constant__ CUtensorMap map_x0, const __grid_const
                     PAIR_STAT_ADD(st_a);
                 }
                 tc_fence_after_sync();
-                tmem_st_32x32b_x16(tmem_base + lane_base + TMEM_A + as * A_COLS + kh * 16, o);
+                tmem_st_32x32b_x16(tmem_base + lane_base + TMEM_A + as * A_COLS + kh0 * 16, o);
+                if (DQ == 4) {   // the other 32 k of the same rows
+                    if (kQ4) {
+                        dequant_q4_k(tile, r, 1, o);
+                    } else {
+                        dequant_q8_0(tile, r, 1, o);
+                    }
+                    tmem_st_32x32b_x16(tmem_base + lane_base + TMEM_A + as * A_COLS + 16, o);
+                }
                 tmem_wait_st();
                 tc_fence_before_sync();
                 __syncwarp();
@@ -1046,10 +1083,11 @@ static edb200_status_t validate_problem(const edb200_qweight_t* w, const void* x
         const edb200_qk_pack_t& k = *ep->pack;
         const int64_t n_pack = (k.only ? 1ll : 3ll) * k.n_heads * k.d_head;
         const int64_t n_primary_cols = ep->split_n > 0 ? ep->split_n : w->n_out;
-        if (k.d_head != 128 || k.n_heads <= 0 || k.only < 0 || k.only > 3 || n_pack != n_primary_cols || ep->gate != nullptr ||
+        if ((k.d_head != 128 && k.d_head != 64) || k.n_heads <= 0 || (k.n_heads * k.d_head) % 128 != 0 || k.only < 0 ||
+            k.only > 3 || n_pack != n_primary_cols || ep->gate != nullptr ||
             ep->act != EDB200_ACT_NONE || ep->split_k != EDB200_SPLIT_K_NEVER || k.l_total <= 0 || k.tok_off < 0) {
             return fail(EDB200_ERR_INVALID,
-                        "mul_mat_q: a fused q/k/v pack needs d_head 128 and (3 or 1) * n_heads * 128 plain primary columns");
+                        "mul_mat_q: a fused q/k/v pack needs d_head 64 or 128 and (3 or 1) * n_heads * d_head plain primary columns");
         }
         auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
         if (!al16(k.q_weight) || !al16(k.k_weight) || !al16(k.pe)) {
@@ -1122,6 +1160,7 @@ static void fill_problem(gemm::Problem& p, const edb200_qweight_t* w, int64_t m,
         p.n_pack = (k.only ? 1 : 3) * k.n_heads * k.d_head;
         p.pk_first = k.only ? k.only - 1 : 0;
         p.pk_heads = k.n_heads;
+        p.pk_d = k.d_head;
         p.pk_eps = k.eps;
         p.pk_qw = k.q_weight;
         p.pk_kw = k.k_weight;
@@ -1243,13 +1282,19 @@ static edb200_status_t launch_qgemm(int nprob, const edb200_qweight_t* const* ws
 
     const bool q4 = ws[0]->ggml_type == EDB200_TYPE_Q4_K;
     using KernT = void (*)(const CUtensorMap, const CUtensorMap, const gemm::Params);
-    static const KernT kerns[6] = {gemm::qgemm_kernel<EDB200_TYPE_Q8_0, 1>,    gemm::qgemm_kernel<EDB200_TYPE_Q8_0, 2>,
-                                   gemm::qgemm_kernel<EDB200_TYPE_Q4_K, 1>,    gemm::qgemm_kernel<EDB200_TYPE_Q4_K, 2>,
-                                   gemm::qgemm_pair_kernel<EDB200_TYPE_Q8_0>, gemm::qgemm_pair_kernel<EDB200_TYPE_Q4_K>};
-    const int ki = pair ? 4 + (q4 ? 1 : 0) : (q4 ? 2 : 0) + (wh - 1);
+    static const KernT kerns[8] = {gemm::qgemm_kernel<EDB200_TYPE_Q8_0, 1>,       gemm::qgemm_kernel<EDB200_TYPE_Q8_0, 2>,
+                                   gemm::qgemm_kernel<EDB200_TYPE_Q4_K, 1>,       gemm::qgemm_kernel<EDB200_TYPE_Q4_K, 2>,
+                                   gemm::qgemm_pair_kernel<EDB200_TYPE_Q8_0, 2>, gemm::qgemm_pair_kernel<EDB200_TYPE_Q4_K, 2>,
+                                   gemm::qgemm_pair_kernel<EDB200_TYPE_Q8_0, 4>, gemm::qgemm_pair_kernel<EDB200_TYPE_Q4_K, 4>};
+    static int dq_depth = 0;   // EDB200_GEMM_DQ=2|4: conversions in flight per CTA (tuning)
+    if (dq_depth == 0) {
+        const char* e = getenv("EDB200_GEMM_DQ");
+        dq_depth = (e != nullptr && atoi(e) == 2) ? 2 : 4;
+    }
+    const int ki = pair ? 4 + (dq_depth == 4 ? 2 : 0) + (q4 ? 1 : 0) : (q4 ? 2 : 0) + (wh - 1);
     KernT kern = kerns[ki];
     const int smem_bytes = pair ? gemm::PAIR_SMEM_BYTES : gemm::SMEM_BYTES;
-    static bool attr_set_dev[64][6] = {};   // the attribute is per device
+    static bool attr_set_dev[64][8] = {};   // the attribute is per device
     static int max_pairs = 0;   // CTA pairs that can be resident at once
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;

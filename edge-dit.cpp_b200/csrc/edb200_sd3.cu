@@ -568,6 +568,13 @@ static edb200_status_t sd3_step_body(edb200_sd3_t* m, const float* latent, float
     const int64_t ctx_first = sp ? (int64_t)m->rank * m->t_loc : 0;
     // few output tiles per rank: let the long out-projection reductions be cut along k (unordered adds)
     const int split_k = sp ? EDB200_SPLIT_K_UNORDERED : EDB200_SPLIT_K_NEVER;
+    // q / k / v packed head-major by the QKV projections' own epilogue (EDB200_FUSED_QK_PACK=0: separate pass)
+    static int fused_env = -1;
+    if (fused_env < 0) {
+        const char* e = getenv("EDB200_FUSED_QK_PACK");
+        fused_env = (e != nullptr && atoi(e) == 0) ? 0 : edb200_mul_mat_q_fuses_qk_pack();
+    }
+    const bool fused = fused_env == 1 && (d == 64 || d == 128) && (H % 128) == 0;
     const int64_t pf_in = (int64_t)c.in_channels * p * p, pf_out = (int64_t)c.out_channels * p * p;
     const int F16 = EDB200_TYPE_F16;
     float* X_ctx = m->X;
@@ -626,11 +633,29 @@ static edb200_status_t sd3_step_body(edb200_sd3_t* m, const float* latent, float
             const Lin lx = qlin(m, px + "attn.qkv"), lc = qlin(m, pc + "attn.qkv");
             edb200_epilogue_t ex = make_ep(qkv + n_ctx * 3 * H, F16, 3 * H, lx.b);
             edb200_epilogue_t ec = make_ep(qkv, F16, 3 * H, lc.b);
+            // head-major pack of the local rows (no norm, no RoPE) by the projections' own epilogue
+            edb200_qk_pack_t px_, pc_;
+            memset(&px_, 0, sizeof(px_));
+            px_.n_heads = c.num_heads;
+            px_.d_head = d;
+            px_.eps = 1e-6f;
+            if (m->p2p) {
+                px_.peers = &m->qkv_peers;
+                px_.l_total = m->t_loc * m->world;
+            } else {
+                px_.l_total = sp ? m->t_loc : T;
+                px_.q_out = sp ? m->QL : m->Q;
+                px_.k_out = sp ? m->KL : m->K;
+                px_.v_out = sp ? m->VL : m->V;
+            }
+            pc_ = px_;
+            px_.tok_off = n_ctx;   // the context rows of this rank come first
+            if (fused) ex.pack = &px_, ec.pack = &pc_;
             EDB_TRY(mm_pair(lx.w, xmod + n_ctx * H, n_img, H, &ex, lc.w, xmod, n_ctx, H, &ec, s));
         }
-        // head-major pack of the local rows (no norm, no RoPE); under the peer-memory exchange straight
-        // into the owning ranks' Q/K/V
-        if (m->p2p) {
+        // the same as a separate pass; under the peer-memory exchange straight into the owning ranks' Q/K/V
+        if (fused) {
+        } else if (m->p2p) {
             EDB_TRY(edb200_qk_norm_rope_pack_sp(qkv, F16, 3 * H, 0, H, 2 * H, TL, c.num_heads, d, nullptr, nullptr, 1e-6f,
                                                 nullptr, 0, m->t_loc * m->world, &m->qkv_peers, F16, s));
         } else {

@@ -149,8 +149,8 @@ EDB200_API int64_t edb200_qweight_bytes(const edb200_qweight_t* w);
  * per-head RMSNorm of q and k and the rotary embedding applied to the f32 accumulators on the way
  * (QKNorm, src/dit_models/components/common/normalization.cpp:71-99; apply_rope,
  * src/dit_models/components/common/rope.hpp:733-778) - the work of edb200_qk_norm_rope_pack without the
- * round trip of the projection's output through memory.  d_head must be 128 (one 128-row weight tile = one
- * head); available when edb200_mul_mat_q_fuses_qk_pack() returns 1. */
+ * round trip of the projection's output through memory.  d_head is 128 (one 128-row weight tile = one head) or
+ * 64 (two heads; n_heads must then be even); available when edb200_mul_mat_q_fuses_qk_pack() returns 1. */
 typedef struct edb200_qk_pack {
     int n_heads, d_head;
     int only;                /* 0: the packed features are q | k | v (3 * n_heads * d_head of them);

@@ -323,7 +323,8 @@ def test_mul_mat_q_column_split(edb, cuda):
     assert not cat[:, :256].any()
 
 
-def test_mul_mat_q_fused_qkv_pack(edb, cuda):
+@pytest.mark.parametrize("heads,d,normed", [(3, 128, True), (4, 64, True), (6, 64, False)])
+def test_mul_mat_q_fused_qkv_pack(edb, cuda, heads, d, normed):
     """The QKV projection's own epilogue packs q | k | v head-major with RMSNorm and RoPE on the f32
     accumulators; features past the packed ones take the column split with GELU (FLUX linear1).  Against the
     oracle (fp32 GEMM on the dequantised weights, then norm and rotation) and against the separate
@@ -331,7 +332,7 @@ def test_mul_mat_q_fused_qkv_pack(edb, cuda):
     import ctypes as C
     if not edb.lib().edb200_mul_mat_q_fuses_qk_pack():
         pytest.skip("the CTA-pair GEMM is switched off")
-    heads, d, k, extra = 3, 128, 512, 256
+    k, extra = 512, 256
     hid = heads * d
     m, nt, L = 300, 20, 384            # 300 rows written at token offset 20 of a 384-token sequence
     n_out = 3 * hid + extra
@@ -340,14 +341,15 @@ def test_mul_mat_q_fused_qkv_pack(edb, cuda):
     qw = (1 + 0.1 * rng.standard_normal(d)).astype(np.float32)
     kw = (1 + 0.1 * rng.standard_normal(d)).astype(np.float32)
     ids = rng.integers(0, 40, size=(L, 3)).astype(np.float32)
-    pe = O.embed_nd(ids, (16, 56, 56), 10000.0)
+    pe = O.embed_nd(ids, (16, 56, 56) if d == 128 else (16, 24, 24), 10000.0)
     t_bias, t_qw, t_kw, t_pe = dev(bias, cuda), dev(qw, cuda), dev(kw, cuda), dev(pe, cuda)
     outs = [torch.zeros(heads, L, d, dtype=torch.float16, device=cuda) for _ in range(3)]
     qkv = torch.zeros(m, 3 * hid, dtype=torch.float16, device=cuda)
     tail = torch.zeros(m, extra, dtype=torch.float16, device=cuda)
     pack = edb.QkPack()
     pack.n_heads, pack.d_head, pack.eps = heads, d, 1e-6
-    pack.q_weight, pack.k_weight, pack.pe = edb.ptr(t_qw), edb.ptr(t_kw), edb.ptr(t_pe)
+    if normed:
+        pack.q_weight, pack.k_weight, pack.pe = edb.ptr(t_qw), edb.ptr(t_kw), edb.ptr(t_pe)
     pack.tok_off, pack.l_total = nt, L
     pack.q_out, pack.k_out, pack.v_out = (edb.ptr(o) for o in outs)
     ep = edb.make_epilogue(qkv, bias=t_bias, split_n=3 * hid, out2=tail, act2=edb.ACT_GELU_TANH)
@@ -360,8 +362,11 @@ def test_mul_mat_q_fused_qkv_pack(edb, cuda):
     q = y[:, :hid].reshape(m, heads, d)
     kk = y[:, hid:2 * hid].reshape(m, heads, d)
     v = y[:, 2 * hid:3 * hid].reshape(m, heads, d)
-    rq = O.apply_rope(O.rms_norm(q, qw), pe[nt:nt + m]).transpose(1, 0, 2)
-    rk = O.apply_rope(O.rms_norm(kk, kw), pe[nt:nt + m]).transpose(1, 0, 2)
+    if normed:
+        rq = O.apply_rope(O.rms_norm(q, qw), pe[nt:nt + m]).transpose(1, 0, 2)
+        rk = O.apply_rope(O.rms_norm(kk, kw), pe[nt:nt + m]).transpose(1, 0, 2)
+    else:                                              # SD3-medium: plain head-major layout
+        rq, rk = q.transpose(1, 0, 2), kk.transpose(1, 0, 2)
     assert O.rel_l2(got[0][:, nt:nt + m], rq) < 2e-3
     assert O.rel_l2(got[1][:, nt:nt + m], rk) < 2e-3
     assert O.rel_l2(got[2][:, nt:nt + m], v.transpose(1, 0, 2)) < 2e-3
@@ -375,7 +380,8 @@ def test_mul_mat_q_fused_qkv_pack(edb, cuda):
     edb.mul_mat_q(w, xt, ep2)
     outs2 = [torch.zeros(heads, L, d, dtype=torch.float16, device=cuda) for _ in range(3)]
     edb.check(edb.lib().edb200_qk_norm_rope_pack(edb.ptr(qkv), edb.TYPE_F16, 3 * hid, 0, hid, 2 * hid, m, heads, d,
-                                                 edb.ptr(t_qw), edb.ptr(t_kw), 1e-6, edb.ptr(t_pe), nt, L,
+                                                 edb.ptr(t_qw) if normed else None, edb.ptr(t_kw) if normed else None, 1e-6,
+                                                 edb.ptr(t_pe) if normed else None, nt, L,
                                                  edb.ptr(outs2[0]), edb.ptr(outs2[1]), edb.ptr(outs2[2]), edb.TYPE_F16,
                                                  edb.current_stream()))
     torch.cuda.synchronize()
@@ -383,11 +389,11 @@ def test_mul_mat_q_fused_qkv_pack(edb, cuda):
         assert O.rel_l2(a.float().cpu().numpy(), b.float().cpu().numpy()) < 2e-3
     assert torch.equal(outs[2], outs2[2])              # v is a copy of the same f16 values either way
 
-    # refused: head dim 64, or packed features that do not end at the split
-    pack.d_head = 64
+    # refused: another head width, or packed features that do not end at the split
+    pack.d_head = 32
     with pytest.raises(edb.EdbError):
         edb.mul_mat_q(w, xt, ep)
-    pack.d_head, pack.n_heads = 128, 2
+    pack.d_head, pack.n_heads = d, heads - 1
     with pytest.raises(edb.EdbError):
         edb.mul_mat_q(w, xt, ep)
 
