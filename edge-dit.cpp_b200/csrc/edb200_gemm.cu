@@ -13,6 +13,10 @@
 // 8.5 KB of raw weights per weight tile, instead of also writing and re-reading
 // 16-32 KB of dequantised weights.
 //
+// Two kernels share this scheme.  qgemm_pair_kernel (further down; the default) runs it on pairs of CTAs
+// with tcgen05 .cta_group::2, each CTA staging half of the token tile; qgemm_kernel, described here, is the
+// single-CTA form kept for comparison (EDB200_GEMM_PAIR=0).
+//
 // One persistent CTA per SM, 896 threads, warp-specialised:
 //   warp 0       producer (elect.sync): TMA tile of 192 tokens x 64 k (f16, 128B
 //                swizzle) and one bulk copy per 128-row x 64-k weight tile record,
