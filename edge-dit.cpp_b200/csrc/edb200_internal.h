@@ -29,6 +29,11 @@ typedef CUresult (*PFN_encodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_
                                     CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 PFN_encodeTiled get_encode_tiled();
 
+// Dense f32 linear on the tensor cores (edb200_linear_tf32.cu): whether the problem qualifies, and the launch.
+bool linear_tf32_usable(const float* w, const float* x, int64_t m, int64_t k, int64_t n, int64_t ldx);
+edb200_status_t launch_linear_tf32(const float* w, const float* bias, const float* x, int64_t m, int64_t k, int64_t n,
+                                   int64_t ldx, int act, float* y, int64_t ldy, cudaStream_t s);
+
 // 2-D row-major tensor map: dims {inner, outer}, row pitch in bytes, box {box_inner, box_outer}.
 edb200_status_t make_tmap_2d(CUtensorMap* map, CUtensorMapDataType dt, int elem_bytes, const void* base,
                              uint64_t inner, uint64_t outer, uint64_t pitch_bytes, uint32_t box_inner,

@@ -336,6 +336,9 @@ edb200_status_t edb200_linear_f32(const float* w, const float* bias, const float
             EDB_GEMVF_CASE(8)
         }
 #undef EDB_GEMVF_CASE
+    } else if (!pre_silu && linear_tf32_usable(w, x, m, k, n, ldx)) {
+        // enough rows for the tensor cores: tf32 MMA straight on the f32 operands (edb200_linear_tf32.cu)
+        EDB_TRY(launch_linear_tf32(w, bias, x, m, k, n, ldx, act, y, ldy, s));
     } else {
         if (pre_silu) return fail(EDB200_ERR_UNSUPPORTED, "linear_f32: pre_silu only for m <= 8");
         const bool aligned = (k % SG_BK) == 0 && (ldx % 4) == 0 && ((reinterpret_cast<uintptr_t>(w) |

@@ -205,7 +205,9 @@ def test_gemv_q(edb, cuda, wtype, m):
 
 @pytest.mark.parametrize("m,k,n,act", [(1, 256, 3072, 2), (300, 64, 200, 0), (70, 4096, 128, 1),
                                          (512, 4096, 3072, 0),   # FLUX txt_in: tiled kernel, full tiles
-                                         (130, 48, 64, 0),       # ragged m, one partial n tile
+                                         (130, 48, 64, 0),       # ragged m, one partial n tile, k tail
+                                         (4096, 64, 3072, 0),    # FLUX img_in: two k steps
+                                         (200, 3072, 64, 2),     # final linear: fewer features than a tile
                                          (77, 24, 200, 3)])      # k not a multiple of 16: simple kernel
 def test_linear_f32(edb, cuda, m, k, n, act):
     rng = np.random.default_rng(10)
@@ -218,7 +220,9 @@ def test_linear_f32(edb, cuda, m, k, n, act):
     ref = O.linear(x, w, b)
     from oracle.wan_oracle import gelu_erf
     ref = {0: lambda v: v, 1: O.gelu_tanh, 2: O.silu, 3: gelu_erf}[act](ref)
-    assert O.rel_l2(y.cpu().numpy(), ref) < 1e-5
+    # 64 rows and more go through the tensor cores, which read the f32 operands as tf32 (10 mantissa bits)
+    tensor_cores = m >= 64 and n >= 32 and k >= 32 and k % 4 == 0
+    assert O.rel_l2(y.cpu().numpy(), ref) < (1e-3 if tensor_cores else 1e-5)
 
 
 # ------------------------------------------------------ quantised GEMM ----
