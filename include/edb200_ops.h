@@ -243,7 +243,7 @@ EDB200_API edb200_status_t edb200_gemv_batch_run(const edb200_gemv_batch_t* b, c
 
 /* Dense f32 weight, the unquantised linears of the prelude / final layer:
  * y[m, n] = act(x[m, k] . W[n, k]^T + bias).  x f32, y f32.  Up to 8 rows: weight-streaming GEMV (exact f32).
- * From 64 rows on (k a multiple of 4, 16-byte aligned operands): tensor cores, which read the f32 operands as
+ * From 9 rows on (k >= 32 and a multiple of 4, n >= 32, 16-byte aligned operands): tensor cores, which read the f32 operands as
  * tf32 - 10 mantissa bits, f32 accumulation (EDB200_LINEAR_TF32=0 in the environment keeps it on SIMT f32). */
 EDB200_API edb200_status_t edb200_linear_f32(const float* w, const float* bias, const float* x, int64_t m, int64_t k,
                                   int64_t n, int64_t ldx, int pre_silu, int act, float* y, int64_t ldy,
