@@ -68,7 +68,12 @@ struct Params {
     void* out_peer[8];
     int t_loc;
     int one;   // always 1: an operand the compiler cannot fold (see magic_i2f_biased)
-    int qt;    // query tiles this launch gives every CTA: 2, or 1 when two would leave SMs without a CTA
+    int qt;    // query tiles per CTA: 2, or 1 when two would leave SMs without a CTA
+    // Mixed schedule (n_mixed_two >= 0; the grid is then 1-D): the first n_mixed_two CTAs take two-tile slabs in
+    // (head, slab) order, the CTAs after them the remaining slabs one tile each - the last, partial wave of
+    // two-tile CTAs becomes a wave of one-tile CTAs, which finish in about two thirds of the time.
+    int n_mixed_two;
+    int slabs2;   // two-tile slabs per head
 };
 
 template <int D, bool SAGE>
@@ -289,17 +294,32 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int q0 = blockIdx.x * (P.qt * BQ);
-    const int hn = blockIdx.y;
+    // which query rows and head this CTA owns, and how many 128-row tiles (qt)
+    int qt = P.qt, q0 = blockIdx.x * (P.qt * BQ), hn = blockIdx.y;
+    if (P.n_mixed_two >= 0) {
+        const int b = blockIdx.x;
+        if (b < P.n_mixed_two) {
+            qt = 2;
+            hn = b / P.slabs2;
+            q0 = (b % P.slabs2) * (2 * BQ);
+        } else {
+            const int j = b - P.n_mixed_two;
+            const int item = P.n_mixed_two + (j >> 1);
+            qt = 1;
+            hn = item / P.slabs2;
+            q0 = (item % P.slabs2) * (2 * BQ) + (j & 1) * BQ;
+            if (q0 >= P.Lq) return;   // the second half of a slab that holds one tile only (whole CTA leaves)
+        }
+    }
     const int n_kv = (P.Lk + BKV - 1) / BKV;
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
         for (int i = 0; i < KV_STAGES; ++i) {
             mbar_init(&k_full[i], 1);
-            mbar_init(&k_empty[i], P.qt);
+            mbar_init(&k_empty[i], qt);
             mbar_init(&v_full[i], 1);
-            mbar_init(&v_empty[i], P.qt);
+            mbar_init(&v_empty[i], qt);
         }
         for (int i = 0; i < QT; ++i) {
             for (int b = 0; b < 2; ++b) {
@@ -329,8 +349,8 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     if (warp == 0) {
         // ------------------------------------------------------ TMA producer
         if (elect_one()) {
-            mbar_arrive_expect_tx(q_full, P.qt * C::Q_BYTES);
-            for (int t = 0; t < P.qt; ++t) {
+            mbar_arrive_expect_tx(q_full, qt * C::Q_BYTES);
+            for (int t = 0; t < qt; ++t) {
 #pragma unroll
                 for (int p = 0; p < C::QK_PANELS; ++p) {
                     tma_load_3d(smem + C::OFF_Q + t * C::Q_BYTES + p * C::QK_PANEL_BYTES, &map_q, q_full,
@@ -364,7 +384,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 }
             }
         }
-    } else if (warp == 1 || (warp == 3 && P.qt == 2)) {
+    } else if (warp == 1 || (warp == 3 && qt == 2)) {
         // ------------------------------------------- MMA issuers, one per query tile
         // (one thread cannot issue the small products of both tiles fast enough)
         const int t = warp >> 1;
@@ -436,7 +456,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             ok = issue_pv(g);
             if (ok && g + 2 < n_half) ok = issue_qk(g + 2);
         }
-    } else if (warp >= 4 && warp < 4 + 4 * P.qt) {
+    } else if (warp >= 4 && warp < 4 + 4 * qt) {
         // ------------------------------------------------------------ softmax
         const int t = (warp - 4) >> 2;              // query tile
         const int quarter = warp & 3;
@@ -658,9 +678,23 @@ static edb200_status_t launch_poly(const void* q, const void* k, const void* v, 
         const int64_t w1 = (((P.Lq + BQ - 1) / BQ) * P.HN + sms - 1) / sms;
         P.qt = (P.Lq > BQ && 2 * w1 < 3 * w2) ? 1 : QT;
     }
-    if (const char* e = getenv("EDB200_ATTN_QT")) {   // tuning and tests: force one of the two schedules
-        if (e[0] == '1') P.qt = 1;
-        if (e[0] == '2') P.qt = QT;
+    P.n_mixed_two = -1;
+    P.slabs2 = static_cast<int>((P.Lq + QT * BQ - 1) / (QT * BQ));
+    if (P.qt == QT) {
+        // at least one full wave of two-tile CTAs and a partial last wave whose slabs, taken one tile per CTA,
+        // still fit one wave: run that last wave as one-tile CTAs
+        const int64_t sms = sm_count();
+        const int64_t items = (int64_t)P.slabs2 * P.HN, tail = items % sms;
+        static int mix = -1;   // EDB200_ATTN_MIX=0: every CTA takes two tiles (comparison runs)
+        if (mix < 0) {
+            const char* e = getenv("EDB200_ATTN_MIX");
+            mix = (e != nullptr && atoi(e) == 0) ? 0 : 1;
+        }
+        if (mix == 1 && items / sms >= 1 && tail > 0 && 2 * tail <= sms) P.n_mixed_two = static_cast<int>(items - tail);
+    }
+    if (const char* e = getenv("EDB200_ATTN_QT")) {   // tuning and tests: force one of the schedules
+        if (e[0] == '1') P.qt = 1, P.n_mixed_two = -1;
+        if (e[0] == '2') P.qt = QT, P.n_mixed_two = -1;
     }
 
     CUtensorMap mq, mk, mv;
@@ -687,6 +721,10 @@ static edb200_status_t launch_poly(const void* q, const void* k, const void* v, 
         if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
     dim3 grid((P.Lq + P.qt * BQ - 1) / (P.qt * BQ), P.HN);
+    if (P.n_mixed_two >= 0) {
+        const int64_t items = (int64_t)P.slabs2 * P.HN;
+        grid = dim3(static_cast<unsigned>(P.n_mixed_two + 2 * (items - P.n_mixed_two)), 1);
+    }
     ProfScope prof(stream, PROF_ATTENTION, 4.0 * (double)P.Lq * (double)P.Lk * D * P.HN,
                    (double)P.HN * D * ((double)P.Lq * (C::QK_ELEM + 2) + (double)P.Lk * (C::QK_ELEM + 2)));
     kern<<<grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(mq, mk, mv, P);
