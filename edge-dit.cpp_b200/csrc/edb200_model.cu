@@ -361,4 +361,42 @@ void* Workspace::take(int64_t bytes) {
     return p;
 }
 
+edb200_status_t ReuseAnchors::set_capture(int anchor, float* dst, int depth, const char* who) {
+    if (anchor == EDB200_ANCHOR_MODEL_IN) {
+        in = dst;
+    } else if (anchor == EDB200_ANCHOR_MODEL_OUT) {
+        out = dst;
+    } else if (anchor >= 0 && anchor < depth) {
+        block.resize(static_cast<size_t>(depth), nullptr);
+        block[static_cast<size_t>(anchor)] = dst;
+    } else {
+        return fail(EDB200_ERR_INVALID, "%s_set_anchor_capture: anchor %d (block outputs are 0..%d)", who, anchor, depth - 1);
+    }
+    return EDB200_OK;
+}
+
+edb200_status_t ReuseAnchors::set_stop(int blk, int depth, const char* who) {
+    if (blk < -1 || blk >= depth) {
+        return fail(EDB200_ERR_INVALID, "%s_set_stop_after: block must be -1 (off) or a block index below %d", who, depth);
+    }
+    stop_after = blk;
+    return EDB200_OK;
+}
+
+void ReuseAnchors::capture_in(const float* stream, int64_t n, cudaStream_t s) const {
+    if (in != nullptr && n > 0) cudaMemcpyAsync(in, stream, static_cast<size_t>(n) * 4, cudaMemcpyDeviceToDevice, s);
+}
+
+void ReuseAnchors::capture_block(int i, const float* stream, int64_t n, cudaStream_t s) const {
+    if (i < static_cast<int>(block.size()) && block[static_cast<size_t>(i)] != nullptr && n > 0) {
+        cudaMemcpyAsync(block[static_cast<size_t>(i)], stream, static_cast<size_t>(n) * 4, cudaMemcpyDeviceToDevice, s);
+    }
+}
+
+void ReuseAnchors::finish(float* stream, int64_t n, cudaStream_t s) const {
+    if (n <= 0) return;
+    if (stream_override != nullptr) launch_add_inplace(stream, stream_override, n, s);
+    if (out != nullptr) cudaMemcpyAsync(out, stream, static_cast<size_t>(n) * 4, cudaMemcpyDeviceToDevice, s);
+}
+
 }  // namespace edb

@@ -110,6 +110,27 @@ edb200_status_t load_gguf(ParamTable& table, int family, const char* path, const
 edb200_status_t load_safetensors(ParamTable& table, int family, const char* path, const char* strip_prefix,
                                  cudaStream_t stream, int* n_loaded);
 
+// The computation-reuse seam of a step executor: the three anchors the reference's cache engine taps in every
+// model graph (ModelIn before the block stack, BlockOut[i] after block i with the probe stop, ModelOut after
+// the stack with the whole-stack inject; src/dit_models/models/mmdit.hpp:3318-3385, wan.hpp:4640-4729,
+// qwen_image.hpp:3209-3274).  All of them are views of the stream the blocks transform, f32 [rows of this
+// rank, width].
+struct ReuseAnchors {
+    float* in = nullptr;
+    float* out = nullptr;
+    std::vector<float*> block;           // [depth], NULL = not captured
+    int stop_after = -1;                 // probe pass: return right after this block
+    const float* stream_override = nullptr;   // whole-stack inject: stream after the stack = ModelIn + this
+
+    edb200_status_t set_capture(int anchor, float* dst, int depth, const char* who);
+    edb200_status_t set_stop(int blk, int depth, const char* who);
+    bool inject() const { return stream_override != nullptr; }
+    // copies on `s`; no-ops where nothing was asked for
+    void capture_in(const float* stream, int64_t n, cudaStream_t s) const;
+    void capture_block(int i, const float* stream, int64_t n, cudaStream_t s) const;
+    void finish(float* stream, int64_t n, cudaStream_t s) const;   // inject (stream += override), then ModelOut
+};
+
 // One cudaMalloc carved into 256-byte aligned pieces.
 class Workspace {
 public:

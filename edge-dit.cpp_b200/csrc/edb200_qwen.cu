@@ -37,6 +37,7 @@ struct edb200_qwen {
     void* SAGE = nullptr;
     int64_t sage_bytes = 0;
     float* tap = nullptr;
+    ReuseAnchors anchors;   // computation-reuse seam (capture / probe stop / whole-stack inject)
     float* pinned = nullptr;
     int64_t pinned_bytes = 0;
     // sequence-parallel execution (world > 1): this rank's slice [text rows ; image rows] of the
@@ -416,6 +417,22 @@ edb200_status_t edb200_qwen_set_comm(edb200_qwen_t* m, edb200_comm_t* comm) {
     return EDB200_OK;
 }
 
+edb200_status_t edb200_qwen_set_anchor_capture(edb200_qwen_t* m, int anchor, float* dst) {
+    if (m == nullptr) return fail(EDB200_ERR_INVALID, "qwen_set_anchor_capture: null model");
+    return m->anchors.set_capture(anchor, dst, m->cfg.num_layers, "qwen");
+}
+
+edb200_status_t edb200_qwen_set_stop_after(edb200_qwen_t* m, int block) {
+    if (m == nullptr) return fail(EDB200_ERR_INVALID, "qwen_set_stop_after: null model");
+    return m->anchors.set_stop(block, m->cfg.num_layers, "qwen");
+}
+
+edb200_status_t edb200_qwen_set_stream_override(edb200_qwen_t* m, const float* residual) {
+    if (m == nullptr) return fail(EDB200_ERR_INVALID, "qwen_set_stream_override: null model");
+    m->anchors.stream_override = residual;
+    return EDB200_OK;
+}
+
 edb200_status_t edb200_qwen_set_tap(edb200_qwen_t* m, float* tap) {
     if (m == nullptr) return fail(EDB200_ERR_INVALID, "qwen_set_tap: null model");
     m->tap = tap;
@@ -620,8 +637,9 @@ static edb200_status_t qwen_step_body(edb200_qwen_t* m, const float* latent, flo
         EDB_TRY(edb200_gemv_q(lf.w, m->TVEC, 1, H, 1, lf.b, fmods, 2 * H, s));
     }
 
+    m->anchors.capture_in(X_img, n_img * H, s);
     // ---- blocks (QwenImageTransformerBlock::forward, qwen_image.hpp:2825-2967)
-    for (int i = 0; i < c.num_layers; ++i) {
+    for (int i = 0; i < (m->anchors.inject() ? 0 : c.num_layers); ++i) {
         const std::string pb = "transformer_blocks." + std::to_string(i) + ".";
         const std::string pa = pb + "attn.";
         const float* im = mods + (int64_t)i * 12 * H;   // shift1 scale1 gate1 shift2 scale2 gate2
@@ -678,7 +696,11 @@ static edb200_status_t qwen_step_body(edb200_qwen_t* m, const float* latent, flo
         if (m->tap) {
             cudaMemcpyAsync(m->tap + (int64_t)i * m->t_rows * H, m->X, m->t_rows * H * 4, cudaMemcpyDeviceToDevice, s);
         }
+        m->anchors.capture_block(i, X_img, n_img * H, s);
+        if (m->anchors.stop_after == i) return check_cuda(cudaGetLastError(), "qwen_step");
     }
+
+    m->anchors.finish(X_img, n_img * H, s);   // whole-stack inject, ModelOut
 
     // ---- norm_out: (scale, shift) order (AdaLayerNormContinuous, qwen_image.hpp:3062-3068), proj_out, unpatchify
     EDB_TRY(ln_mod(X_img, H, fmods + H, fmods, n_img, xmod, F16, s));

@@ -39,6 +39,7 @@ struct edb200_sd3 {
     void* SAGE = nullptr;
     int64_t sage_bytes = 0;
     float* tap = nullptr;
+    ReuseAnchors anchors;   // computation-reuse seam (capture / probe stop / whole-stack inject)
     float* pinned = nullptr;
     int64_t pinned_bytes = 0;
     // sequence-parallel execution (world > 1): this rank's slice [context rows ; image rows] of the
@@ -422,6 +423,22 @@ edb200_status_t edb200_sd3_set_comm(edb200_sd3_t* m, edb200_comm_t* comm) {
     return EDB200_OK;
 }
 
+edb200_status_t edb200_sd3_set_anchor_capture(edb200_sd3_t* m, int anchor, float* dst) {
+    if (m == nullptr) return fail(EDB200_ERR_INVALID, "sd3_set_anchor_capture: null model");
+    return m->anchors.set_capture(anchor, dst, m->cfg.depth, "sd3");
+}
+
+edb200_status_t edb200_sd3_set_stop_after(edb200_sd3_t* m, int block) {
+    if (m == nullptr) return fail(EDB200_ERR_INVALID, "sd3_set_stop_after: null model");
+    return m->anchors.set_stop(block, m->cfg.depth, "sd3");
+}
+
+edb200_status_t edb200_sd3_set_stream_override(edb200_sd3_t* m, const float* residual) {
+    if (m == nullptr) return fail(EDB200_ERR_INVALID, "sd3_set_stream_override: null model");
+    m->anchors.stream_override = residual;
+    return EDB200_OK;
+}
+
 edb200_status_t edb200_sd3_set_tap(edb200_sd3_t* m, float* tap) {
     if (m == nullptr) return fail(EDB200_ERR_INVALID, "sd3_set_tap: null model");
     m->tap = tap;
@@ -618,8 +635,9 @@ static edb200_status_t sd3_step_body(edb200_sd3_t* m, const float* latent, float
     EDB_TRY(edb200_gemv_batch_run(m->mod_batch, m->CVEC, 1, m->p2p ? &m->mods_peers : nullptr, s));
     if (m->p2p) EDB_TRY(edb200_sp_barrier(m->comm, s));
 
+    m->anchors.capture_in(X_img, n_img * H, s);
     // ---- joint blocks (block_mixing, mmdit.hpp:2685-2775)
-    for (int i = 0; i < c.depth; ++i) {
+    for (int i = 0; i < (m->anchors.inject() ? 0 : c.depth); ++i) {
         const std::string pc = "joint_blocks." + std::to_string(i) + ".context_block.";
         const std::string px = "joint_blocks." + std::to_string(i) + ".x_block.";
         const bool pre_only = i == c.depth - 1;
@@ -699,7 +717,11 @@ static edb200_status_t sd3_step_body(edb200_sd3_t* m, const float* latent, float
             }
         }
         if (m->tap) cudaMemcpyAsync(m->tap + (int64_t)i * TL * H, m->X, TL * H * 4, cudaMemcpyDeviceToDevice, s);
+        m->anchors.capture_block(i, X_img, n_img * H, s);
+        if (m->anchors.stop_after == i) return check_cuda(cudaGetLastError(), "sd3_step");
     }
+
+    m->anchors.finish(X_img, n_img * H, s);   // whole-stack inject, ModelOut
 
     // ---- final layer: (scale, shift) order (FinalLayer::forward, mmdit.hpp:3143-3160) + unpatchify
     EDB_TRY(ln_mod(X_img, H, fmods + H, fmods, n_img, xmod, F16, s));

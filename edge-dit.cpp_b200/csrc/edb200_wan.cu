@@ -44,6 +44,7 @@ struct edb200_wan {
     void* SAGE = nullptr;
     int64_t sage_bytes = 0;
     float* tap = nullptr;
+    ReuseAnchors anchors;   // computation-reuse seam (capture / probe stop / whole-stack inject)
     float* pinned = nullptr;
     int64_t pinned_bytes = 0;
     // sequence parallel
@@ -352,6 +353,22 @@ edb200_status_t edb200_wan_init_random(edb200_wan_t* m, uint64_t seed, float std
 int64_t edb200_wan_weight_bytes(const edb200_wan_t* m) { return m ? m->params.device_bytes() : 0; }
 int64_t edb200_wan_workspace_bytes(const edb200_wan_t* m) { return m ? m->ws.capacity() : 0; }
 
+edb200_status_t edb200_wan_set_anchor_capture(edb200_wan_t* m, int anchor, float* dst) {
+    if (m == nullptr) return fail(EDB200_ERR_INVALID, "wan_set_anchor_capture: null model");
+    return m->anchors.set_capture(anchor, dst, m->cfg.num_layers, "wan");
+}
+
+edb200_status_t edb200_wan_set_stop_after(edb200_wan_t* m, int block) {
+    if (m == nullptr) return fail(EDB200_ERR_INVALID, "wan_set_stop_after: null model");
+    return m->anchors.set_stop(block, m->cfg.num_layers, "wan");
+}
+
+edb200_status_t edb200_wan_set_stream_override(edb200_wan_t* m, const float* residual) {
+    if (m == nullptr) return fail(EDB200_ERR_INVALID, "wan_set_stream_override: null model");
+    m->anchors.stream_override = residual;
+    return EDB200_OK;
+}
+
 edb200_status_t edb200_wan_set_tap(edb200_wan_t* m, float* tap) {
     if (m == nullptr) return fail(EDB200_ERR_INVALID, "wan_set_tap: null model");
     m->tap = tap;
@@ -553,8 +570,9 @@ static edb200_status_t wan_step_body(edb200_wan_t* m, const float* latent, float
     EDB_TRY(dense(m, "text_embedding.2", m->TMP, n_ctx, D, 0, EDB200_ACT_NONE, m->CTX32, D, s));
     EDB_TRY(edb200_cast(m->CTX32, EDB200_TYPE_F32, m->CTXE, F16, n_ctx * D, s));
 
+    m->anchors.capture_in(m->X, TL * D, s);
     // ---- blocks (WanAttentionBlock::forward, wan.hpp:4136-4187)
-    for (int i = 0; i < c.num_layers; ++i) {
+    for (int i = 0; i < (m->anchors.inject() ? 0 : c.num_layers); ++i) {
         const std::string p = "blocks." + std::to_string(i) + ".";
         add_rows_kernel<<<static_cast<unsigned>((6 * D + 255) / 256), 256, 0, s>>>(m->E0, 6, fparam(m, p + "modulation"),
                                                                                    m->ES, 6 * D, static_cast<int>(D));
@@ -636,7 +654,11 @@ static edb200_status_t wan_step_body(edb200_wan_t* m, const float* latent, float
             EDB_TRY(edb200_mul_mat_q(l2.w, hid, F16, TL, F, &e2, s));
         }
         if (m->tap) cudaMemcpyAsync(m->tap + (int64_t)i * TL * D, m->X, TL * D * 4, cudaMemcpyDeviceToDevice, s);
+        m->anchors.capture_block(i, m->X, TL * D, s);
+        if (m->anchors.stop_after == i) return check_cuda(cudaGetLastError(), "wan_step");
     }
+
+    m->anchors.finish(m->X, TL * D, s);   // whole-stack inject, ModelOut
 
     // ---- head (Head::forward, wan.hpp:4309-4330) + unpatchify (:4489-4514)
     EDB_TRY(ln_mod(m->X, D, m->HMOD, m->HMOD + D, nullptr, nullptr, TL, xmod, F16, s));

@@ -758,6 +758,12 @@ EDB200_API edb200_status_t edb200_sd3_load_safetensors(edb200_sd3_t* m, const ch
 EDB200_API edb200_status_t edb200_sd3_init_random(edb200_sd3_t* m, uint64_t seed, float std, void* stream);
 EDB200_API int64_t edb200_sd3_weight_bytes(const edb200_sd3_t* m);
 EDB200_API edb200_status_t edb200_sd3_prepare(edb200_sd3_t* m, int lat_h, int lat_w, int n_ctx, void* stream);
+/* The computation-reuse seam of edb200_flux_set_anchor_capture / _set_stop_after / _set_stream_override for
+ * this family (src/dit_models/models/mmdit.hpp:3318-3385): the anchors are views of the stream the blocks transform,
+ * the image rows of this rank, [rows, hidden], f32 on the device. */
+EDB200_API edb200_status_t edb200_sd3_set_anchor_capture(edb200_sd3_t* m, int anchor, float* dst);
+EDB200_API edb200_status_t edb200_sd3_set_stop_after(edb200_sd3_t* m, int block);
+EDB200_API edb200_status_t edb200_sd3_set_stream_override(edb200_sd3_t* m, const float* residual);
 /* Optional f32 tap [depth, n_ctx + image tokens, hidden]: both streams after every block. */
 EDB200_API edb200_status_t edb200_sd3_set_tap(edb200_sd3_t* m, float* tap);
 /* Sequence parallel over `comm` (MMDiT forward_sp, src/dit_models/models/mmdit.hpp:3117-3128, 3439-3466):
@@ -836,6 +842,12 @@ EDB200_API edb200_status_t edb200_qwen_load_safetensors(edb200_qwen_t* m, const 
 EDB200_API edb200_status_t edb200_qwen_init_random(edb200_qwen_t* m, uint64_t seed, float std, void* stream);
 EDB200_API int64_t edb200_qwen_weight_bytes(const edb200_qwen_t* m);
 EDB200_API edb200_status_t edb200_qwen_prepare(edb200_qwen_t* m, int lat_h, int lat_w, int n_txt, void* stream);
+/* The computation-reuse seam of edb200_flux_set_anchor_capture / _set_stop_after / _set_stream_override for
+ * this family (src/dit_models/models/qwen_image.hpp:3209-3274): the anchors are views of the stream the blocks transform,
+ * the image rows of this rank, [rows, hidden], f32 on the device. */
+EDB200_API edb200_status_t edb200_qwen_set_anchor_capture(edb200_qwen_t* m, int anchor, float* dst);
+EDB200_API edb200_status_t edb200_qwen_set_stop_after(edb200_qwen_t* m, int block);
+EDB200_API edb200_status_t edb200_qwen_set_stream_override(edb200_qwen_t* m, const float* residual);
 /* Optional f32 tap [num_layers, n_txt + image tokens, hidden]: both streams after every block. */
 EDB200_API edb200_status_t edb200_qwen_set_tap(edb200_qwen_t* m, float* tap);
 /* Sequence parallel over `comm` (QwenImageTransformerBlock::forward_sp, qwen_image.hpp:2969-3040): before prepare. */
@@ -905,6 +917,12 @@ EDB200_API int64_t edb200_wan_workspace_bytes(const edb200_wan_t* m);
 /* Latent [in_dim, frames, lat_h, lat_w] (frames, lat_h, lat_w multiples of the patch), n_ctx text tokens. */
 EDB200_API edb200_status_t edb200_wan_prepare(edb200_wan_t* m, int frames, int lat_h, int lat_w, int n_ctx,
                                               void* stream);
+/* The computation-reuse seam of edb200_flux_set_anchor_capture / _set_stop_after / _set_stream_override for
+ * this family (src/dit_models/models/wan.hpp:4640-4729): the anchors are views of the stream the blocks transform,
+ * the video-token rows of this rank, [rows, dim], f32 on the device. */
+EDB200_API edb200_status_t edb200_wan_set_anchor_capture(edb200_wan_t* m, int anchor, float* dst);
+EDB200_API edb200_status_t edb200_wan_set_stop_after(edb200_wan_t* m, int block);
+EDB200_API edb200_status_t edb200_wan_set_stream_override(edb200_wan_t* m, const float* residual);
 /* Optional f32 tap [num_layers, tokens (this rank's), dim]: residual stream after every block. */
 EDB200_API edb200_status_t edb200_wan_set_tap(edb200_wan_t* m, float* tap);
 /* Sequence parallel over `comm` (WanAttentionBlock::forward_sp, wan.hpp:4189-4235): before prepare. */
