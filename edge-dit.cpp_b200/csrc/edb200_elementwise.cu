@@ -70,13 +70,16 @@ __device__ __forceinline__ float4 load_vec4(const void* base, int dtype, int64_t
 // the association the reference's modulate uses
 // (src/core/backend/ggml/ed_ggml_modulation_ext.hpp:168-199) applied to ggml_norm's output.
 constexpr int LN_THREADS = 256;
+#ifndef LN_MIN_BLOCKS
+#define LN_MIN_BLOCKS 1
+#endif
 constexpr int LN_MAXV = 8;  // float4 per thread -> H <= 8192
 
 // NV > 0: the row is exactly NV * LN_THREADS float4 wide and every bound check folds away (the common hidden
 // sizes: 3072 -> 3, 5120 -> 5); NV == 0: any width up to LN_MAXV * LN_THREADS float4.  Same arithmetic, same
 // order of additions in both.
 template <int NV>
-__global__ void __launch_bounds__(LN_THREADS)
+__global__ void __launch_bounds__(LN_THREADS, LN_MIN_BLOCKS)
 layernorm_modulate_kernel(const float* __restrict__ x, int64_t ldx, const float* __restrict__ shift,
                           const float* __restrict__ scale, const float* __restrict__ ln_w,
                           const float* __restrict__ ln_b, int H, float eps, void* __restrict__ y, int y_dtype,

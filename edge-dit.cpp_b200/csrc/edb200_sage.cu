@@ -241,6 +241,9 @@ smooth_q_bias_kernel(const __half* __restrict__ k, const float* __restrict__ qm,
 }
 
 constexpr int kFusedQuantThreads = 256;
+#ifndef FQ_MIN_BLOCKS
+#define FQ_MIN_BLOCKS 4
+#endif
 
 // Fast pre-pass, one launch for everything after the channel means: CTA (256 threads) per
 // (64-token block, head) quantises the K block (one scale) and the two 32-token Q tiles of the same
@@ -250,7 +253,7 @@ constexpr int kFusedQuantThreads = 256;
 // ((p0+p1)+(p2+p3))+((p4+p5)+(p6+p7)), then a pairwise tree over the D/8 threads of the token
 // (xor-shuffles 1, 2, 4[, 8]).  Rows between l and the padded end of a bias row are set to zero.
 template <int D>
-__global__ void __launch_bounds__(kFusedQuantThreads)
+__global__ void __launch_bounds__(kFusedQuantThreads, FQ_MIN_BLOCKS)
 fused_quant_kernel(const __half* __restrict__ q, const __half* __restrict__ k, const float* __restrict__ qm,
                    const float* __restrict__ km, int8_t* __restrict__ q8, int8_t* __restrict__ k8,
                    float* __restrict__ q_scale, float* __restrict__ k_scale, float* __restrict__ bias, int L,
