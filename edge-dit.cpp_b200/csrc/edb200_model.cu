@@ -383,6 +383,37 @@ edb200_status_t ReuseAnchors::set_stop(int blk, int depth, const char* who) {
     return EDB200_OK;
 }
 
+edb200_status_t ReuseAnchors::set_region(int at, int resume, const float* residual, int depth, const char* who) {
+    if (residual == nullptr || at < 0) {   // off
+        inject_at = -1;
+        inject_residual = nullptr;
+        return EDB200_OK;
+    }
+    if (at >= depth || resume <= at || resume > depth) {
+        return fail(EDB200_ERR_INVALID, "%s_set_region_inject: need 0 <= at < resume <= %d", who, depth);
+    }
+    if (at > 0 && in == nullptr) {
+        return fail(EDB200_ERR_INVALID,
+                    "%s_set_region_inject: a region that starts after block 0 needs the ModelIn capture buffer set "
+                    "(the stream is rebuilt from it)", who);
+    }
+    inject_at = at;
+    inject_resume = resume;
+    inject_residual = residual;
+    return EDB200_OK;
+}
+
+bool ReuseAnchors::region_inject(int& i, float* stream, int64_t n, cudaStream_t s) const {
+    if (inject_residual == nullptr || i != inject_at) return false;
+    if (n > 0) {
+        // x = x_before + residual; at block 0 the stream still is x_before
+        if (i > 0) cudaMemcpyAsync(stream, in, static_cast<size_t>(n) * 4, cudaMemcpyDeviceToDevice, s);
+        launch_add_inplace(stream, inject_residual, n, s);
+    }
+    i = inject_resume - 1;
+    return true;
+}
+
 void ReuseAnchors::capture_in(const float* stream, int64_t n, cudaStream_t s) const {
     if (in != nullptr && n > 0) cudaMemcpyAsync(in, stream, static_cast<size_t>(n) * 4, cudaMemcpyDeviceToDevice, s);
 }

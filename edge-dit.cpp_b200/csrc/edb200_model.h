@@ -121,10 +121,18 @@ struct ReuseAnchors {
     std::vector<float*> block;           // [depth], NULL = not captured
     int stop_after = -1;                 // probe pass: return right after this block
     const float* stream_override = nullptr;   // whole-stack inject: stream after the stack = ModelIn + this
+    // region inject (substep reuse, mmdit.hpp:3336-3343, wan.hpp:4658-4665): at block `inject_at` the stream becomes
+    // ModelIn + inject_residual and the loop resumes at block `inject_resume`
+    int inject_at = -1, inject_resume = 0;
+    const float* inject_residual = nullptr;
 
     edb200_status_t set_capture(int anchor, float* dst, int depth, const char* who);
     edb200_status_t set_stop(int blk, int depth, const char* who);
     bool inject() const { return stream_override != nullptr; }
+    edb200_status_t set_region(int at, int resume, const float* residual, int depth, const char* who);
+    // true when block i starts an injected region: the stream has been rebuilt and `i` moved to the block before
+    // the one to resume at (the caller's loop increment does the rest)
+    bool region_inject(int& i, float* stream, int64_t n, cudaStream_t s) const;
     // copies on `s`; no-ops where nothing was asked for
     void capture_in(const float* stream, int64_t n, cudaStream_t s) const;
     void capture_block(int i, const float* stream, int64_t n, cudaStream_t s) const;

@@ -439,6 +439,11 @@ edb200_status_t edb200_sd3_set_stream_override(edb200_sd3_t* m, const float* res
     return EDB200_OK;
 }
 
+edb200_status_t edb200_sd3_set_region_inject(edb200_sd3_t* m, int at, int resume, const float* residual) {
+    if (m == nullptr) return fail(EDB200_ERR_INVALID, "sd3_set_region_inject: null model");
+    return m->anchors.set_region(at, resume, residual, m->cfg.depth, "sd3");
+}
+
 edb200_status_t edb200_sd3_set_tap(edb200_sd3_t* m, float* tap) {
     if (m == nullptr) return fail(EDB200_ERR_INVALID, "sd3_set_tap: null model");
     m->tap = tap;
@@ -638,6 +643,7 @@ static edb200_status_t sd3_step_body(edb200_sd3_t* m, const float* latent, float
     m->anchors.capture_in(X_img, n_img * H, s);
     // ---- joint blocks (block_mixing, mmdit.hpp:2685-2775)
     for (int i = 0; i < (m->anchors.inject() ? 0 : c.depth); ++i) {
+        if (m->anchors.region_inject(i, X_img, n_img * H, s)) continue;   // skip a cached span of blocks
         const std::string pc = "joint_blocks." + std::to_string(i) + ".context_block.";
         const std::string px = "joint_blocks." + std::to_string(i) + ".x_block.";
         const bool pre_only = i == c.depth - 1;

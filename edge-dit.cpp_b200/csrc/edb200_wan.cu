@@ -369,6 +369,11 @@ edb200_status_t edb200_wan_set_stream_override(edb200_wan_t* m, const float* res
     return EDB200_OK;
 }
 
+edb200_status_t edb200_wan_set_region_inject(edb200_wan_t* m, int at, int resume, const float* residual) {
+    if (m == nullptr) return fail(EDB200_ERR_INVALID, "wan_set_region_inject: null model");
+    return m->anchors.set_region(at, resume, residual, m->cfg.num_layers, "wan");
+}
+
 edb200_status_t edb200_wan_set_tap(edb200_wan_t* m, float* tap) {
     if (m == nullptr) return fail(EDB200_ERR_INVALID, "wan_set_tap: null model");
     m->tap = tap;
@@ -573,6 +578,7 @@ static edb200_status_t wan_step_body(edb200_wan_t* m, const float* latent, float
     m->anchors.capture_in(m->X, TL * D, s);
     // ---- blocks (WanAttentionBlock::forward, wan.hpp:4136-4187)
     for (int i = 0; i < (m->anchors.inject() ? 0 : c.num_layers); ++i) {
+        if (m->anchors.region_inject(i, m->X, TL * D, s)) continue;   // skip a cached span of blocks
         const std::string p = "blocks." + std::to_string(i) + ".";
         add_rows_kernel<<<static_cast<unsigned>((6 * D + 255) / 256), 256, 0, s>>>(m->E0, 6, fparam(m, p + "modulation"),
                                                                                    m->ES, 6 * D, static_cast<int>(D));

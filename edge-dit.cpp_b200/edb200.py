@@ -130,9 +130,11 @@ _SIGS = {
     "edb200_sd3_set_anchor_capture": (C.c_int, [c_vp, C.c_int, c_vp]),
     "edb200_sd3_set_stop_after": (C.c_int, [c_vp, C.c_int]),
     "edb200_sd3_set_stream_override": (C.c_int, [c_vp, c_vp]),
+    "edb200_sd3_set_region_inject": (C.c_int, [c_vp, C.c_int, C.c_int, c_vp]),
     "edb200_wan_set_anchor_capture": (C.c_int, [c_vp, C.c_int, c_vp]),
     "edb200_wan_set_stop_after": (C.c_int, [c_vp, C.c_int]),
     "edb200_wan_set_stream_override": (C.c_int, [c_vp, c_vp]),
+    "edb200_wan_set_region_inject": (C.c_int, [c_vp, C.c_int, C.c_int, c_vp]),
     "edb200_qwen_set_anchor_capture": (C.c_int, [c_vp, C.c_int, c_vp]),
     "edb200_qwen_set_stop_after": (C.c_int, [c_vp, C.c_int]),
     "edb200_qwen_set_stream_override": (C.c_int, [c_vp, c_vp]),

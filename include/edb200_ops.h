@@ -764,6 +764,10 @@ EDB200_API edb200_status_t edb200_sd3_prepare(edb200_sd3_t* m, int lat_h, int la
 EDB200_API edb200_status_t edb200_sd3_set_anchor_capture(edb200_sd3_t* m, int anchor, float* dst);
 EDB200_API edb200_status_t edb200_sd3_set_stop_after(edb200_sd3_t* m, int block);
 EDB200_API edb200_status_t edb200_sd3_set_stream_override(edb200_sd3_t* m, const float* residual);
+/* Region inject (src/dit_models/models/mmdit.hpp:3336-3343): at block `at` the stream becomes ModelIn + residual and the
+ * blocks [at, resume) are skipped.  A region that starts after block 0 rebuilds the stream from the ModelIn
+ * capture buffer, which must be set.  residual NULL or at < 0 switches it off. */
+EDB200_API edb200_status_t edb200_sd3_set_region_inject(edb200_sd3_t* m, int at, int resume, const float* residual);
 /* Optional f32 tap [depth, n_ctx + image tokens, hidden]: both streams after every block. */
 EDB200_API edb200_status_t edb200_sd3_set_tap(edb200_sd3_t* m, float* tap);
 /* Sequence parallel over `comm` (MMDiT forward_sp, src/dit_models/models/mmdit.hpp:3117-3128, 3439-3466):
@@ -923,6 +927,10 @@ EDB200_API edb200_status_t edb200_wan_prepare(edb200_wan_t* m, int frames, int l
 EDB200_API edb200_status_t edb200_wan_set_anchor_capture(edb200_wan_t* m, int anchor, float* dst);
 EDB200_API edb200_status_t edb200_wan_set_stop_after(edb200_wan_t* m, int block);
 EDB200_API edb200_status_t edb200_wan_set_stream_override(edb200_wan_t* m, const float* residual);
+/* Region inject (src/dit_models/models/wan.hpp:4658-4665): at block `at` the stream becomes ModelIn + residual and the
+ * blocks [at, resume) are skipped.  A region that starts after block 0 rebuilds the stream from the ModelIn
+ * capture buffer, which must be set.  residual NULL or at < 0 switches it off. */
+EDB200_API edb200_status_t edb200_wan_set_region_inject(edb200_wan_t* m, int at, int resume, const float* residual);
 /* Optional f32 tap [num_layers, tokens (this rank's), dim]: residual stream after every block. */
 EDB200_API edb200_status_t edb200_wan_set_tap(edb200_wan_t* m, float* tap);
 /* Sequence parallel over `comm` (WanAttentionBlock::forward_sp, wan.hpp:4189-4235): before prepare. */

@@ -85,3 +85,59 @@ def test_reuse_anchors_capture_probe_and_inject(edb, cuda, make):
     step(again)
     torch.cuda.synchronize()
     assert torch.equal(again, full)
+
+
+def test_wan_region_inject_skips_a_cached_span(edb, cuda):
+    """Region inject (wan.hpp:4658-4665): at block 1 the stream becomes ModelIn + residual and block 1 is skipped.
+    With residual = BlockOut[1] - ModelIn of a full step the step's output is reproduced (Wan's blocks transform
+    one stream; the text context does not change)."""
+    lib = edb.lib()
+    g = torch.Generator(device="cpu").manual_seed(9)
+    model, fam, depth, width, rows, stream, tap_rows, step, lat = _wan(edb, cuda, g)
+    a_in, a_b1 = (torch.zeros(rows, width, device=cuda) for _ in range(2))
+    edb.check(lib.edb200_wan_set_anchor_capture(model.handle, edb.ANCHOR_MODEL_IN, edb.ptr(a_in)))
+    edb.check(lib.edb200_wan_set_anchor_capture(model.handle, 1, edb.ptr(a_b1)))
+    full = torch.empty_like(lat)
+    launches = lib.edb200_launch_count()
+    step(full)
+    torch.cuda.synchronize()
+    full_launches = lib.edb200_launch_count() - launches
+    residual = torch.empty_like(a_in)
+    edb.check(lib.edb200_sub_f32(edb.ptr(a_b1), edb.ptr(a_in), edb.ptr(residual), residual.numel(), edb.current_stream()))
+    edb.check(lib.edb200_wan_set_anchor_capture(model.handle, 1, None))
+    edb.check(lib.edb200_wan_set_region_inject(model.handle, 1, 2, edb.ptr(residual)))
+    launches = lib.edb200_launch_count()
+    reused = torch.empty_like(lat)
+    step(reused)
+    torch.cuda.synchronize()
+    assert lib.edb200_launch_count() - launches < full_launches
+    rel = float(torch.linalg.vector_norm(reused - full) / torch.linalg.vector_norm(full))
+    # in + (out - in) differs from out in the last bit, and block 2 rounds its activations to f16 on top of that
+    assert rel < 2e-3, rel
+    # bad regions are refused; a region after block 0 needs the ModelIn buffer
+    assert lib.edb200_wan_set_region_inject(model.handle, 2, 2, edb.ptr(residual)) != 0
+    assert lib.edb200_wan_set_region_inject(model.handle, 0, depth + 1, edb.ptr(residual)) != 0
+    edb.check(lib.edb200_wan_set_anchor_capture(model.handle, edb.ANCHOR_MODEL_IN, None))
+    assert lib.edb200_wan_set_region_inject(model.handle, 1, 2, edb.ptr(residual)) != 0
+    edb.check(lib.edb200_wan_set_region_inject(model.handle, -1, 0, None))
+    again = torch.empty_like(lat)
+    step(again)
+    torch.cuda.synchronize()
+    assert torch.equal(again, full)
+
+
+def test_sd3_region_over_the_whole_stack_equals_the_stream_override(edb, cuda):
+    """mmdit.hpp:3336-3343 with the region [0, depth): the same stream as the whole-stack override."""
+    lib = edb.lib()
+    g = torch.Generator(device="cpu").manual_seed(9)
+    model, fam, depth, width, rows, stream, tap_rows, step, lat = _sd3(edb, cuda, g)
+    residual = torch.randn(rows, width, generator=g).to(cuda)
+    edb.check(lib.edb200_sd3_set_stream_override(model.handle, edb.ptr(residual)))
+    a = torch.empty_like(lat)
+    step(a)
+    edb.check(lib.edb200_sd3_set_stream_override(model.handle, None))
+    edb.check(lib.edb200_sd3_set_region_inject(model.handle, 0, depth, edb.ptr(residual)))
+    b = torch.empty_like(lat)
+    step(b)
+    torch.cuda.synchronize()
+    assert torch.isfinite(a).all() and torch.equal(a, b)
